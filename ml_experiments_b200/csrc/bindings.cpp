@@ -5,6 +5,8 @@
 #include <torch/library.h>
 #include <torch/types.h>
 
+#include "attn/attn.h"
+#include "fused/fused.h"
 #include "gemm/gemm.h"
 
 namespace {
@@ -61,16 +63,241 @@ void gemm(const Tensor& a, const Tensor& b, Tensor c, const c10::optional<Tensor
   b200::gemm_sm100(g);
 }
 
+
+// ---------------------------------------------------------------------------------------------- attention
+void fill_thd(const Tensor& t, const char* name, int T, int H, int D) {
+  TORCH_CHECK(t.is_cuda() && t.dim() == 3, name, ": expected a CUDA [T, H, D] tensor");
+  TORCH_CHECK(t.size(0) == T && t.size(1) == H && t.size(2) == D, name, ": shape mismatch");
+  TORCH_CHECK(t.stride(2) == 1 && t.stride(1) == D, name, ": heads must be contiguous (stride(1) == D, stride(2) == 1)");
+}
+
+void attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor o, Tensor lse, const Tensor& doc_start,
+              const Tensor& doc_end, double scale, int64_t window_blocks, Tensor status) {
+  const c10::cuda::CUDAGuard guard(q.device());
+  b200::AttnArgs a;
+  a.T = (int)q.size(0); a.H = (int)q.size(1); a.D = (int)q.size(2);
+  fill_thd(q, "q", a.T, a.H, a.D); fill_thd(k, "k", a.T, a.H, a.D); fill_thd(v, "v", a.T, a.H, a.D);
+  fill_thd(o, "o", a.T, a.H, a.D);
+  TORCH_CHECK(q.scalar_type() == at::kBFloat16 && k.scalar_type() == at::kBFloat16 && v.scalar_type() == at::kBFloat16 &&
+              o.scalar_type() == at::kBFloat16, "attention tensors must be bf16");
+  TORCH_CHECK(lse.scalar_type() == at::kFloat && lse.is_contiguous() && lse.numel() == (int64_t)a.T * a.H, "lse: fp32 [H, T]");
+  TORCH_CHECK(doc_start.scalar_type() == at::kInt && doc_end.scalar_type() == at::kInt && doc_start.numel() == a.T &&
+              doc_end.numel() == a.T, "doc_start / doc_end: int32 [T]");
+  a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr(); a.o = o.data_ptr();
+  a.ld_q = q.stride(0); a.ld_k = k.stride(0); a.ld_v = v.stride(0); a.ld_o = o.stride(0);
+  a.lse = lse.data_ptr<float>();
+  a.doc_start = doc_start.data_ptr<int>(); a.doc_end = doc_end.data_ptr<int>();
+  a.scale = (float)scale; a.window_blocks = (int)window_blocks;
+  a.status = status.data_ptr<int>(); a.stream = cur_stream();
+  b200::attn_fwd_sm100(a);
+}
+
+void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o, const Tensor& d_o,
+              const Tensor& lse, Tensor delta, Tensor dq_acc, Tensor dk, Tensor dv, const Tensor& doc_start,
+              const Tensor& doc_end, double scale, int64_t window_blocks, Tensor status) {
+  const c10::cuda::CUDAGuard guard(q.device());
+  b200::AttnArgs a;
+  a.T = (int)q.size(0); a.H = (int)q.size(1); a.D = (int)q.size(2);
+  fill_thd(q, "q", a.T, a.H, a.D); fill_thd(k, "k", a.T, a.H, a.D); fill_thd(v, "v", a.T, a.H, a.D);
+  fill_thd(o, "o", a.T, a.H, a.D); fill_thd(d_o, "do", a.T, a.H, a.D);
+  fill_thd(dq_acc, "dq_acc", a.T, a.H, a.D); fill_thd(dk, "dk", a.T, a.H, a.D); fill_thd(dv, "dv", a.T, a.H, a.D);
+  TORCH_CHECK(dq_acc.scalar_type() == at::kFloat, "dq_acc must be fp32 (zero-initialised accumulator)");
+  TORCH_CHECK(dk.scalar_type() == at::kBFloat16 && dv.scalar_type() == at::kBFloat16 && d_o.scalar_type() == at::kBFloat16,
+              "dk, dv, do must be bf16");
+  TORCH_CHECK(delta.scalar_type() == at::kFloat && delta.is_contiguous() && delta.numel() == (int64_t)a.T * a.H, "delta: fp32 [H, T]");
+  a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr(); a.o = const_cast<void*>(o.data_ptr());
+  a.d_o = d_o.data_ptr(); a.dq_acc = dq_acc.data_ptr(); a.dk = dk.data_ptr(); a.dv = dv.data_ptr();
+  a.ld_q = q.stride(0); a.ld_k = k.stride(0); a.ld_v = v.stride(0); a.ld_o = o.stride(0); a.ld_do = d_o.stride(0);
+  a.ld_dq = dq_acc.stride(0); a.ld_dk = dk.stride(0); a.ld_dv = dv.stride(0);
+  a.lse = const_cast<float*>(lse.data_ptr<float>()); a.delta = delta.data_ptr<float>();
+  a.doc_start = doc_start.data_ptr<int>(); a.doc_end = doc_end.data_ptr<int>();
+  a.scale = (float)scale; a.window_blocks = (int)window_blocks;
+  a.status = status.data_ptr<int>(); a.stream = cur_stream();
+  b200::attn_delta_sm100(a);
+  b200::attn_bwd_sm100(a);
+}
+
+// ---------------------------------------------------------------------------------------------- fused row kernels
+const void* optp(const c10::optional<Tensor>& t) { return t.has_value() ? t->data_ptr() : nullptr; }
+const float* optf(const c10::optional<Tensor>& t) { return t.has_value() ? t->data_ptr<float>() : nullptr; }
+void chk_bf16c(const Tensor& t, const char* n) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.is_contiguous(), n, ": contiguous bf16 CUDA tensor expected");
+}
+
+void mix_norm_fwd(const Tensor& x, const c10::optional<Tensor>& x0, const c10::optional<Tensor>& skip,
+                  const c10::optional<Tensor>& lam, const c10::optional<Tensor>& skip_w,
+                  const c10::optional<Tensor>& x_mix, const c10::optional<Tensor>& xn, double eps) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  chk_bf16c(x, "x");
+  const int C = (int)x.size(-1), R = (int)(x.numel() / C);
+  b200::mix_norm_fwd(x.data_ptr(), optp(x0), optp(skip), optf(lam), optf(skip_w),
+                     x_mix.has_value() ? x_mix->data_ptr() : nullptr, xn.has_value() ? xn->data_ptr() : nullptr, R, C,
+                     (float)eps, cur_stream());
+}
+
+void norm_bwd_add(const Tensor& dy, const Tensor& x, const c10::optional<Tensor>& dres, Tensor out, double eps) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  chk_bf16c(dy, "dy"); chk_bf16c(x, "x"); chk_bf16c(out, "out");
+  const int C = (int)x.size(-1), R = (int)(x.numel() / C);
+  b200::norm_bwd_add(dy.data_ptr(), x.data_ptr(), optp(dres), out.data_ptr(), R, C, (float)eps, cur_stream());
+}
+
+void mix_bwd(const Tensor& dmix, const Tensor& x, const Tensor& x0, const c10::optional<Tensor>& skip,
+             const Tensor& lam, const c10::optional<Tensor>& skip_w, Tensor dx, const c10::optional<Tensor>& dskip,
+             Tensor dx0_acc, Tensor dlam, const c10::optional<Tensor>& dskip_w) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  chk_bf16c(dmix, "dmix"); chk_bf16c(x, "x"); chk_bf16c(x0, "x0"); chk_bf16c(dx, "dx");
+  TORCH_CHECK(dx0_acc.scalar_type() == at::kFloat && dx0_acc.is_contiguous(), "dx0_acc: contiguous fp32");
+  const int C = (int)x.size(-1), R = (int)(x.numel() / C);
+  b200::mix_bwd(dmix.data_ptr(), x.data_ptr(), x0.data_ptr(), optp(skip), lam.data_ptr<float>(), optf(skip_w),
+                dx.data_ptr(), dskip.has_value() ? dskip->data_ptr() : nullptr, dx0_acc.data_ptr<float>(),
+                dlam.data_ptr<float>(), dskip_w.has_value() ? dskip_w->data_ptr<float>() : nullptr, R, C, cur_stream());
+}
+
+void qkv_post_fwd(const Tensor& qkv, const c10::optional<Tensor>& ve, const Tensor& lam, const Tensor& cos,
+                  const Tensor& sin, Tensor out, int64_t H, int64_t D, double eps) {
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  chk_bf16c(qkv, "qkv"); chk_bf16c(out, "out");
+  const int T = (int)(qkv.numel() / (3 * H * D));
+  TORCH_CHECK(cos.scalar_type() == at::kFloat && cos.size(0) >= T && cos.size(1) == D / 2 && cos.is_contiguous(), "cos table");
+  TORCH_CHECK(sin.scalar_type() == at::kFloat && sin.size(0) >= T && sin.size(1) == D / 2 && sin.is_contiguous(), "sin table");
+  b200::qkv_post_fwd(qkv.data_ptr(), optp(ve), lam.data_ptr<float>(), cos.data_ptr<float>(), sin.data_ptr<float>(),
+                     out.data_ptr(), T, (int)H, (int)D, (float)eps, cur_stream());
+}
+
+void qkv_post_bwd(const Tensor& dq, const Tensor& dk, const Tensor& dv, const Tensor& qkv,
+                  const c10::optional<Tensor>& ve, const Tensor& lam, const Tensor& cos, const Tensor& sin,
+                  Tensor dqkv, const c10::optional<Tensor>& dve, Tensor dlam, int64_t H, int64_t D, double eps) {
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  chk_bf16c(qkv, "qkv"); chk_bf16c(dk, "dk"); chk_bf16c(dv, "dv"); chk_bf16c(dqkv, "dqkv");
+  TORCH_CHECK(dq.scalar_type() == at::kFloat && dq.is_contiguous(), "dq: contiguous fp32");
+  const int T = (int)(qkv.numel() / (3 * H * D));
+  b200::qkv_post_bwd(dq.data_ptr<float>(), dk.data_ptr(), dv.data_ptr(), qkv.data_ptr(), optp(ve),
+                     lam.data_ptr<float>(), cos.data_ptr<float>(), sin.data_ptr<float>(), dqkv.data_ptr(),
+                     dve.has_value() ? dve->data_ptr() : nullptr, dlam.data_ptr<float>(), T, (int)H, (int)D, (float)eps,
+                     cur_stream());
+}
+
+void embed_gather(const Tensor& idx, const Tensor& table, Tensor out, bool normalize, double eps) {
+  const c10::cuda::CUDAGuard guard(table.device());
+  chk_bf16c(table, "table"); chk_bf16c(out, "out");
+  TORCH_CHECK(idx.scalar_type() == at::kInt && idx.is_contiguous(), "idx: contiguous int32");
+  b200::embed_gather(idx.data_ptr<int>(), table.data_ptr(), out.data_ptr(), (int)idx.numel(), (int)table.size(1),
+                     normalize, (float)eps, cur_stream());
+}
+
+void embed_scatter_add(const Tensor& idx, const Tensor& src, Tensor grad_table) {
+  const c10::cuda::CUDAGuard guard(src.device());
+  TORCH_CHECK(idx.scalar_type() == at::kInt && idx.is_contiguous() && src.is_contiguous(), "embed_scatter_add: layout");
+  TORCH_CHECK(grad_table.scalar_type() == at::kFloat && grad_table.is_contiguous(), "grad_table: contiguous fp32");
+  const bool f32 = src.scalar_type() == at::kFloat;
+  TORCH_CHECK(f32 || src.scalar_type() == at::kBFloat16, "src: fp32 or bf16");
+  b200::embed_scatter_add(idx.data_ptr<int>(), src.data_ptr(), f32, grad_table.data_ptr<float>(), (int)idx.numel(),
+                          (int)grad_table.size(1), cur_stream());
+}
+
+void cast_fp8(const Tensor& x, Tensor out, double scale) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_contiguous() && out.is_contiguous() && x.numel() == out.numel(), "cast_fp8: layout");
+  const int in_kind = x.scalar_type() == at::kBFloat16 ? 0 : 1;
+  TORCH_CHECK(in_kind == 0 || x.scalar_type() == at::kFloat, "cast_fp8: input must be bf16 or fp32");
+  const int out_kind = out.scalar_type() == at::kFloat8_e4m3fn ? 0 : 1;
+  TORCH_CHECK(out_kind == 0 || out.scalar_type() == at::kFloat8_e5m2, "cast_fp8: output must be e4m3fn or e5m2");
+  b200::cast_fp8(x.data_ptr(), out.data_ptr(), (float)scale, x.numel(), in_kind, out_kind, cur_stream());
+}
+
+void softcap_ce(const Tensor& logits, const Tensor& targets, Tensor loss_rows, const c10::optional<Tensor>& grad,
+                double cap, double div, double loss_scale, double grad_scale) {
+  const c10::cuda::CUDAGuard guard(logits.device());
+  TORCH_CHECK(logits.dim() == 2 && logits.scalar_type() == at::kBFloat16 && logits.stride(1) == 1, "logits: bf16 [T, V]");
+  TORCH_CHECK(targets.scalar_type() == at::kLong && targets.is_contiguous(), "targets: int64");
+  TORCH_CHECK(loss_rows.scalar_type() == at::kFloat && loss_rows.numel() == logits.size(0), "loss_rows: fp32 [T]");
+  int grad_bf16 = 0;
+  if (grad.has_value()) {
+    grad_bf16 = grad->scalar_type() == at::kBFloat16;
+    TORCH_CHECK(grad_bf16 || grad->scalar_type() == at::kFloat8_e5m2, "grad: bf16 or e5m2");
+    TORCH_CHECK(grad->stride(0) == logits.stride(0) && grad->stride(1) == 1, "grad must share the logits layout");
+  }
+  b200::softcap_ce(logits.data_ptr(), targets.data_ptr<int64_t>() ? (const long long*)targets.data_ptr<int64_t>() : nullptr,
+                   loss_rows.data_ptr<float>(), grad.has_value() ? grad->data_ptr() : nullptr, grad_bf16,
+                   (int)logits.size(0), (int)logits.size(1), logits.stride(0), (float)cap, (float)div, (float)loss_scale,
+                   (float)grad_scale, cur_stream());
+}
+
+void adam_step(Tensor p, const Tensor& g, Tensor m, Tensor v, double lr, double beta1, double beta2, double eps,
+               double wd, double bias1, double bias2, double grad_scale) {
+  const c10::cuda::CUDAGuard guard(p.device());
+  TORCH_CHECK(p.is_contiguous() && g.is_contiguous() && m.is_contiguous() && v.is_contiguous(), "adam_step: contiguous");
+  TORCH_CHECK(g.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat, "adam_step: fp32 g/m/v");
+  const bool pb = p.scalar_type() == at::kBFloat16;
+  TORCH_CHECK(pb || p.scalar_type() == at::kFloat, "adam_step: p must be fp32 or bf16");
+  b200::adam_step(p.data_ptr(), pb, g.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), p.numel(), (float)lr,
+                  (float)beta1, (float)beta2, (float)eps, (float)wd, (float)bias1, (float)bias2, (float)grad_scale, cur_stream());
+}
+
+void muon_momentum(const Tensor& g, Tensor buf, Tensor out, Tensor sumsq, double mu, bool nesterov, double grad_scale) {
+  const c10::cuda::CUDAGuard guard(g.device());
+  TORCH_CHECK(g.is_contiguous() && buf.is_contiguous() && out.is_contiguous(), "muon_momentum: contiguous");
+  TORCH_CHECK(g.scalar_type() == at::kFloat && buf.scalar_type() == at::kFloat && out.scalar_type() == at::kBFloat16 &&
+              sumsq.scalar_type() == at::kFloat, "muon_momentum: dtypes");
+  b200::muon_momentum(g.data_ptr<float>(), buf.data_ptr<float>(), out.data_ptr(), sumsq.data_ptr<float>(), g.numel(),
+                      (float)mu, nesterov, (float)grad_scale, cur_stream());
+}
+
+void scale_by_inv_norm(Tensor x, const Tensor& sumsq, double eps) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  chk_bf16c(x, "x");
+  b200::scale_by_inv_norm(x.data_ptr(), sumsq.data_ptr<float>(), x.numel(), (float)eps, cur_stream());
+}
+
+void axpy_bf16_to_f32(Tensor p, const Tensor& u, const c10::optional<Tensor>& p_bf16, double alpha) {
+  const c10::cuda::CUDAGuard guard(p.device());
+  TORCH_CHECK(p.scalar_type() == at::kFloat && p.is_contiguous() && u.is_contiguous() && u.scalar_type() == at::kBFloat16 &&
+              u.numel() == p.numel(), "axpy: p fp32, u bf16, same numel");
+  b200::axpy_bf16_to_f32(p.data_ptr<float>(), u.data_ptr(), p_bf16.has_value() ? p_bf16->data_ptr() : nullptr, p.numel(),
+                         (float)alpha, cur_stream());
+}
+
 }  // namespace
 
 TORCH_LIBRARY(b200, m) {
   m.def(
       "gemm(Tensor a, Tensor b, Tensor(a!) c, Tensor? aux, bool a_mn, bool b_mn, int epilogue, float alpha, "
       "float beta, int split_k, bool accumulate, Tensor status) -> ()");
+  m.def("attn_fwd(Tensor q, Tensor k, Tensor v, Tensor(a!) o, Tensor(b!) lse, Tensor doc_start, Tensor doc_end, float scale, int window_blocks, Tensor status) -> ()");
+  m.def("attn_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor d_o, Tensor lse, Tensor(a!) delta, Tensor(b!) dq_acc, Tensor(c!) dk, Tensor(d!) dv, Tensor doc_start, Tensor doc_end, float scale, int window_blocks, Tensor status) -> ()");
+  m.def("mix_norm_fwd(Tensor x, Tensor? x0, Tensor? skip, Tensor? lam, Tensor? skip_w, Tensor(a!)? x_mix, Tensor(b!)? xn, float eps) -> ()");
+  m.def("norm_bwd_add(Tensor dy, Tensor x, Tensor? dres, Tensor(a!) out, float eps) -> ()");
+  m.def("mix_bwd(Tensor dmix, Tensor x, Tensor x0, Tensor? skip, Tensor lam, Tensor? skip_w, Tensor(a!) dx, Tensor(b!)? dskip, Tensor(c!) dx0_acc, Tensor(d!) dlam, Tensor(e!)? dskip_w) -> ()");
+  m.def("qkv_post_fwd(Tensor qkv, Tensor? ve, Tensor lam, Tensor cos, Tensor sin, Tensor(a!) out, int H, int D, float eps) -> ()");
+  m.def("qkv_post_bwd(Tensor dq, Tensor dk, Tensor dv, Tensor qkv, Tensor? ve, Tensor lam, Tensor cos, Tensor sin, Tensor(a!) dqkv, Tensor(b!)? dve, Tensor(c!) dlam, int H, int D, float eps) -> ()");
+  m.def("embed_gather(Tensor idx, Tensor table, Tensor(a!) out, bool normalize, float eps) -> ()");
+  m.def("embed_scatter_add(Tensor idx, Tensor src, Tensor(a!) grad_table) -> ()");
+  m.def("cast_fp8(Tensor x, Tensor(a!) out, float scale) -> ()");
+  m.def("softcap_ce(Tensor logits, Tensor targets, Tensor(a!) loss_rows, Tensor(b!)? grad, float cap, float div, float loss_scale, float grad_scale) -> ()");
+  m.def("adam_step(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, float lr, float beta1, float beta2, float eps, float wd, float bias1, float bias2, float grad_scale) -> ()");
+  m.def("muon_momentum(Tensor g, Tensor(a!) buf, Tensor(b!) out, Tensor(c!) sumsq, float mu, bool nesterov, float grad_scale) -> ()");
+  m.def("scale_by_inv_norm(Tensor(a!) x, Tensor sumsq, float eps) -> ()");
+  m.def("axpy_bf16_to_f32(Tensor(a!) p, Tensor u, Tensor(b!)? p_bf16, float alpha) -> ()");
   // <<DEFS>>
 }
 
 TORCH_LIBRARY_IMPL(b200, CUDA, m) {
   m.impl("gemm", &gemm);
+  m.impl("attn_fwd", &attn_fwd);
+  m.impl("attn_bwd", &attn_bwd);
+  m.impl("mix_norm_fwd", &mix_norm_fwd);
+  m.impl("norm_bwd_add", &norm_bwd_add);
+  m.impl("mix_bwd", &mix_bwd);
+  m.impl("qkv_post_fwd", &qkv_post_fwd);
+  m.impl("qkv_post_bwd", &qkv_post_bwd);
+  m.impl("embed_gather", &embed_gather);
+  m.impl("embed_scatter_add", &embed_scatter_add);
+  m.impl("cast_fp8", &cast_fp8);
+  m.impl("softcap_ce", &softcap_ce);
+  m.impl("adam_step", &adam_step);
+  m.impl("muon_momentum", &muon_momentum);
+  m.impl("scale_by_inv_norm", &scale_by_inv_norm);
+  m.impl("axpy_bf16_to_f32", &axpy_bf16_to_f32);
   // <<IMPLS>>
 }

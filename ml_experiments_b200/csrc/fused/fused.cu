@@ -1,0 +1,687 @@
+// Memory-bound fused kernels of the GPT step: RMSNorm (+ residual mixing), QK-norm + RoPE + value mixing,
+// embedding gather / scatter-add, fp8 casts, soft-capped cross entropy, Adam and Muon element-wise parts.
+// One warp owns one row wherever a row reduction is needed; all global accesses are 16-byte vectors.
+#include "fused.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+
+#include <stdexcept>
+#include <string>
+
+namespace b200 {
+namespace {
+
+using bf16 = __nv_bfloat16;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) v += __shfl_xor_sync(0xffffffffu, v, s);
+  return v;
+}
+__device__ __forceinline__ void load8(const bf16* p, float (&f)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 x = __bfloat1622float2(h[i]);
+    f[2 * i] = x.x;
+    f[2 * i + 1] = x.y;
+  }
+}
+__device__ __forceinline__ void store8(bf16* p, const float (&f)[8]) {
+  uint4 u;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+__device__ __forceinline__ void round8(float (&f)[8]) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) f[i] = __bfloat162float(__float2bfloat16_rn(f[i]));
+}
+
+void check(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+constexpr int kRowThreads = 256;  // 8 rows per block
+inline int row_blocks(int R) { return (R + 7) / 8; }
+
+// ---------------------------------------------------------------------------------------------- RMSNorm
+template <int NCH>
+__global__ void __launch_bounds__(kRowThreads)
+mix_norm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ x0, const bf16* __restrict__ skip,
+                    const float* __restrict__ lam, const float* __restrict__ skip_w, bf16* __restrict__ x_mix,
+                    bf16* __restrict__ xn, int R, int C, float eps) {
+  const int row = (blockIdx.x * kRowThreads + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= R) return;
+  const long long base = (long long)row * C;
+  const float l0 = (x0 && lam) ? lam[0] : 1.f, l1 = (x0 && lam) ? lam[1] : 0.f;
+  const float w = (skip && skip_w) ? skip_w[0] : 0.f;
+  float v[NCH][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < NCH; ++k) {
+    const int c = (lane + 32 * k) * 8;
+    if (c < C) {
+      load8(x + base + c, v[k]);
+      if (skip) {
+        float s8[8];
+        load8(skip + base + c, s8);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[k][i] = fmaf(w, s8[i], v[k][i]);
+      }
+      if (x0) {
+        float z8[8];
+        load8(x0 + base + c, z8);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[k][i] = l0 * v[k][i] + l1 * z8[i];
+      }
+      if (x_mix) {
+        round8(v[k]);
+        store8(x_mix + base + c, v[k]);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss = fmaf(v[k][i], v[k][i], ss);
+    }
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / C + eps);
+  if (xn) {
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
+      const int c = (lane + 32 * k) * 8;
+      if (c < C) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[k][i] *= r;
+        store8(xn + base + c, v[k]);
+      }
+    }
+  }
+}
+
+template <int NCH>
+__global__ void __launch_bounds__(kRowThreads)
+norm_bwd_add_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ dres,
+                    bf16* __restrict__ out, int R, int C, float eps) {
+  const int row = (blockIdx.x * kRowThreads + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= R) return;
+  const long long base = (long long)row * C;
+  float xv[NCH][8], gv[NCH][8];
+  float ss = 0.f, dot = 0.f;
+#pragma unroll
+  for (int k = 0; k < NCH; ++k) {
+    const int c = (lane + 32 * k) * 8;
+    if (c < C) {
+      load8(x + base + c, xv[k]);
+      load8(dy + base + c, gv[k]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        ss = fmaf(xv[k][i], xv[k][i], ss);
+        dot = fmaf(xv[k][i], gv[k][i], dot);
+      }
+    }
+  }
+  ss = warp_sum(ss);
+  dot = warp_sum(dot);
+  const float r = rsqrtf(ss / C + eps);
+  const float coef = dot * r * r * r / C;  // mean(dy * y) * r / |x| scaling folded: dx = r*dy - x * coef
+#pragma unroll
+  for (int k = 0; k < NCH; ++k) {
+    const int c = (lane + 32 * k) * 8;
+    if (c < C) {
+      float o[8];
+      if (dres) load8(dres + base + c, o);
+      else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] += r * gv[k][i] - xv[k][i] * coef;
+      store8(out + base + c, o);
+    }
+  }
+}
+
+template <int NCH>
+__global__ void __launch_bounds__(kRowThreads)
+mix_bwd_kernel(const bf16* __restrict__ dmix, const bf16* __restrict__ x, const bf16* __restrict__ x0,
+               const bf16* __restrict__ skip, const float* __restrict__ lam, const float* __restrict__ skip_w,
+               bf16* __restrict__ dx, bf16* __restrict__ dskip, float* __restrict__ dx0_acc, float* __restrict__ dlam,
+               float* __restrict__ dskip_w, int R, int C) {
+  __shared__ float red[3][kRowThreads / 32];
+  const int warp_in_block = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const float l0 = lam[0], l1 = lam[1];
+  const float w = (skip && skip_w) ? skip_w[0] : 0.f;
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f;
+  for (int row = blockIdx.x * (kRowThreads / 32) + warp_in_block; row < R; row += gridDim.x * (kRowThreads / 32)) {
+    const long long base = (long long)row * C;
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
+      const int c = (lane + 32 * k) * 8;
+      if (c < C) {
+        float g[8], xv[8], zv[8], sv[8], o[8];
+        load8(dmix + base + c, g);
+        load8(x + base + c, xv);
+        load8(x0 + base + c, zv);
+        if (skip) {
+          load8(skip + base + c, sv);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            a2 = fmaf(l0 * g[i], sv[i], a2);
+            xv[i] = fmaf(w, sv[i], xv[i]);
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = l0 * w * g[i];
+          store8(dskip + base + c, o);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          a0 = fmaf(g[i], xv[i], a0);
+          a1 = fmaf(g[i], zv[i], a1);
+          o[i] = l0 * g[i];
+        }
+        store8(dx + base + c, o);
+        float4* acc = reinterpret_cast<float4*>(dx0_acc + base + c);
+        float4 p0 = acc[0], p1 = acc[1];
+        p0.x = fmaf(l1, g[0], p0.x); p0.y = fmaf(l1, g[1], p0.y); p0.z = fmaf(l1, g[2], p0.z); p0.w = fmaf(l1, g[3], p0.w);
+        p1.x = fmaf(l1, g[4], p1.x); p1.y = fmaf(l1, g[5], p1.y); p1.z = fmaf(l1, g[6], p1.z); p1.w = fmaf(l1, g[7], p1.w);
+        acc[0] = p0; acc[1] = p1;
+      }
+    }
+  }
+  a0 = warp_sum(a0); a1 = warp_sum(a1); a2 = warp_sum(a2);
+  if (lane == 0) { red[0][warp_in_block] = a0; red[1][warp_in_block] = a1; red[2][warp_in_block] = a2; }
+  __syncthreads();
+  if (threadIdx.x < 3) {
+    float t = 0.f;
+    for (int i = 0; i < kRowThreads / 32; ++i) t += red[threadIdx.x][i];
+    if (threadIdx.x == 0) atomicAdd(&dlam[0], t);
+    else if (threadIdx.x == 1) atomicAdd(&dlam[1], t);
+    else if (skip && dskip_w) atomicAdd(dskip_w, t);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- QK-norm + RoPE + value mix
+// One warp per (token, slot) with slot in [0, 3H): q heads, k heads, v heads.
+template <int D>
+__global__ void __launch_bounds__(256)
+qkv_post_fwd_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ ve, const float* __restrict__ lam,
+                    const float* __restrict__ cs, const float* __restrict__ sn, bf16* __restrict__ out, int T, int H,
+                    float eps) {
+  constexpr int E = D / 64;  // elements per lane per half
+  const long long gw = ((long long)blockIdx.x * 256 + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (gw >= (long long)T * 3 * H) return;
+  const int t = (int)(gw / (3 * H));
+  const int slot = (int)(gw % (3 * H));
+  const bf16* src = qkv + gw * D;
+  bf16* dst = out + gw * D;
+  float a[E], b[E];
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    a[e] = __bfloat162float(src[lane * E + e]);
+    b[e] = __bfloat162float(src[D / 2 + lane * E + e]);
+  }
+  if (slot < 2 * H) {
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < E; ++e) ss += a[e] * a[e] + b[e] * b[e];
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss / D + eps);
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      // the reference normalises in bf16, then rotates in fp32
+      const float x1 = __bfloat162float(__float2bfloat16_rn(a[e] * r));
+      const float x2 = __bfloat162float(__float2bfloat16_rn(b[e] * r));
+      const float c = cs[(long long)t * (D / 2) + lane * E + e], s = sn[(long long)t * (D / 2) + lane * E + e];
+      dst[lane * E + e] = __float2bfloat16_rn(x1 * c + x2 * s);
+      dst[D / 2 + lane * E + e] = __float2bfloat16_rn(-x1 * s + x2 * c);
+    }
+  } else {
+    const float l0 = lam[0], l1 = lam[1];
+    const int hv = slot - 2 * H;
+    if (ve) {
+      const bf16* vs = ve + ((long long)t * H + hv) * D;
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        a[e] = l0 * a[e] + l1 * __bfloat162float(vs[lane * E + e]);
+        b[e] = l0 * b[e] + l1 * __bfloat162float(vs[D / 2 + lane * E + e]);
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < E; ++e) { a[e] *= l0; b[e] *= l0; }
+    }
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      dst[lane * E + e] = __float2bfloat16_rn(a[e]);
+      dst[D / 2 + lane * E + e] = __float2bfloat16_rn(b[e]);
+    }
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(256)
+qkv_post_bwd_kernel(const float* __restrict__ dq, const bf16* __restrict__ dk, const bf16* __restrict__ dv,
+                    const bf16* __restrict__ qkv, const bf16* __restrict__ ve, const float* __restrict__ lam,
+                    const float* __restrict__ cs, const float* __restrict__ sn, bf16* __restrict__ dqkv,
+                    bf16* __restrict__ dve, float* __restrict__ dlam, int T, int H, float eps) {
+  constexpr int E = D / 64;
+  __shared__ float red[2][8];
+  const long long gw = ((long long)blockIdx.x * 256 + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int wib = threadIdx.x >> 5;
+  float s0 = 0.f, s1 = 0.f;
+  if (gw < (long long)T * 3 * H) {
+    const int t = (int)(gw / (3 * H));
+    const int slot = (int)(gw % (3 * H));
+    const bf16* src = qkv + gw * D;
+    bf16* dst = dqkv + gw * D;
+    float a[E], b[E], ga[E], gb[E];
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      a[e] = __bfloat162float(src[lane * E + e]);
+      b[e] = __bfloat162float(src[D / 2 + lane * E + e]);
+    }
+    if (slot < 2 * H) {
+      const int hh = slot < H ? slot : slot - H;
+      const long long g0 = ((long long)t * H + hh) * D;
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        float y1, y2;
+        if (slot < H) { y1 = dq[g0 + lane * E + e]; y2 = dq[g0 + D / 2 + lane * E + e]; }
+        else { y1 = __bfloat162float(dk[g0 + lane * E + e]); y2 = __bfloat162float(dk[g0 + D / 2 + lane * E + e]); }
+        const float c = cs[(long long)t * (D / 2) + lane * E + e], s = sn[(long long)t * (D / 2) + lane * E + e];
+        ga[e] = y1 * c - y2 * s;  // transpose of the rotation
+        gb[e] = y1 * s + y2 * c;
+      }
+      float ss = 0.f, dot = 0.f;
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        ss += a[e] * a[e] + b[e] * b[e];
+        dot += a[e] * ga[e] + b[e] * gb[e];
+      }
+      ss = warp_sum(ss);
+      dot = warp_sum(dot);
+      const float r = rsqrtf(ss / D + eps);
+      const float coef = dot * r * r * r / D;
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        dst[lane * E + e] = __float2bfloat16_rn(r * ga[e] - a[e] * coef);
+        dst[D / 2 + lane * E + e] = __float2bfloat16_rn(r * gb[e] - b[e] * coef);
+      }
+    } else {
+      const int hv = slot - 2 * H;
+      const long long g0 = ((long long)t * H + hv) * D;
+      const float l0 = lam[0], l1 = lam[1];
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        ga[e] = __bfloat162float(dv[g0 + lane * E + e]);
+        gb[e] = __bfloat162float(dv[g0 + D / 2 + lane * E + e]);
+        s0 += ga[e] * a[e] + gb[e] * b[e];
+        dst[lane * E + e] = __float2bfloat16_rn(l0 * ga[e]);
+        dst[D / 2 + lane * E + e] = __float2bfloat16_rn(l0 * gb[e]);
+      }
+      if (ve) {
+        const bf16* vs = ve + g0;
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          s1 += ga[e] * __bfloat162float(vs[lane * E + e]) + gb[e] * __bfloat162float(vs[D / 2 + lane * E + e]);
+          if (dve) {
+            dve[g0 + lane * E + e] = __float2bfloat16_rn(l1 * ga[e]);
+            dve[g0 + D / 2 + lane * E + e] = __float2bfloat16_rn(l1 * gb[e]);
+          }
+        }
+      }
+    }
+  }
+  s0 = warp_sum(s0);
+  s1 = warp_sum(s1);
+  if (lane == 0) { red[0][wib] = s0; red[1][wib] = s1; }
+  __syncthreads();
+  if (threadIdx.x < 2) {
+    float tsum = 0.f;
+    for (int i = 0; i < 8; ++i) tsum += red[threadIdx.x][i];
+    if (tsum != 0.f) atomicAdd(&dlam[threadIdx.x], tsum);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- embeddings
+template <int NCH>
+__global__ void __launch_bounds__(kRowThreads)
+embed_gather_kernel(const int* __restrict__ idx, const bf16* __restrict__ table, bf16* __restrict__ out, int T, int C,
+                    int normalize, float eps) {
+  const int row = (blockIdx.x * kRowThreads + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= T) return;
+  const bf16* src = table + (long long)idx[row] * C;
+  bf16* dst = out + (long long)row * C;
+  float v[NCH][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < NCH; ++k) {
+    const int c = (lane + 32 * k) * 8;
+    if (c < C) {
+      load8(src + c, v[k]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss = fmaf(v[k][i], v[k][i], ss);
+    }
+  }
+  float r = 1.f;
+  if (normalize) {
+    ss = warp_sum(ss);
+    r = rsqrtf(ss / C + eps);
+  }
+#pragma unroll
+  for (int k = 0; k < NCH; ++k) {
+    const int c = (lane + 32 * k) * 8;
+    if (c < C) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[k][i] *= r;
+      store8(dst + c, v[k]);
+    }
+  }
+}
+
+template <typename TS>
+__global__ void embed_scatter_add_kernel(const int* __restrict__ idx, const TS* __restrict__ src,
+                                         float* __restrict__ grad_table, int T, int C) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int cq = C / 4;
+  if (i >= (long long)T * cq) return;
+  const int t = (int)(i / cq), c = (int)(i % cq) * 4;
+  float* dst = grad_table + (long long)idx[t] * C + c;
+  const TS* s = src + (long long)t * C + c;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) atomicAdd(dst + k, (float)s[k]);
+}
+
+// ---------------------------------------------------------------------------------------------- fp8 cast
+template <typename TI>
+__global__ void cast_fp8_kernel(const TI* __restrict__ x, uint8_t* __restrict__ out, float scale, long long n,
+                                int out_kind) {
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (i >= n) return;
+  const __nv_fp8_interpretation_t kind = out_kind ? __NV_E5M2 : __NV_E4M3;
+  if (i + 8 <= n) {
+    float f[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) f[k] = (float)x[i + k] * scale;
+    uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      w0 |= (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(f[2 * k], f[2 * k + 1]), __NV_SATFINITE, kind) << (16 * k);
+      w1 |= (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(f[4 + 2 * k], f[5 + 2 * k]), __NV_SATFINITE, kind) << (16 * k);
+    }
+    *reinterpret_cast<uint2*>(out + i) = make_uint2(w0, w1);
+  } else {
+    for (long long k = i; k < n; ++k) out[k] = __nv_cvt_float_to_fp8((float)x[k] * scale, __NV_SATFINITE, kind);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- soft-capped CE
+// One block per row. z = cap * sigmoid(x / div) is bounded by cap (30), so exp(z) needs no running maximum.
+__global__ void __launch_bounds__(512)
+softcap_ce_kernel(const bf16* __restrict__ logits, const long long* __restrict__ targets,
+                  float* __restrict__ loss_rows, uint8_t* __restrict__ grad, int grad_is_bf16, int V, long long ld,
+                  float cap, float inv_div, float loss_scale, float grad_scale) {
+  __shared__ float red[16];
+  __shared__ float s_total;
+  const int row = blockIdx.x;
+  const bf16* x = logits + (long long)row * ld;
+  const int tgt = (int)targets[row];
+  const int nch = V / 8;
+  const float L2E = 1.4426950408889634f;
+  float sum = 0.f;
+  for (int ci = threadIdx.x; ci < nch; ci += blockDim.x) {
+    float f[8];
+    load8(x + ci * 8, f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float sg = 0.5f * tanhf(0.5f * f[i] * inv_div) + 0.5f;  // sigmoid, one MUFU under fast-math
+      sum += exp2f(cap * sg * L2E);
+    }
+  }
+  sum = warp_sum(sum);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sum;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    t = warp_sum(t);
+    if (threadIdx.x == 0) s_total = t;
+  }
+  __syncthreads();
+  const float total = s_total;
+  const float lse = logf(total);
+  if (threadIdx.x == 0) {
+    float zt = 0.f;
+    if (tgt >= 0 && tgt < V) {
+      const float sg = 0.5f * tanhf(0.5f * __bfloat162float(x[tgt]) * inv_div) + 0.5f;
+      zt = cap * sg;
+      loss_rows[row] = (lse - zt) * loss_scale;
+    } else {
+      loss_rows[row] = 0.f;  // ignored position
+    }
+  }
+  if (!grad) return;
+  const bool ignore = !(tgt >= 0 && tgt < V);
+  const float inv_total = 1.f / total;
+  const float gs = ignore ? 0.f : grad_scale * cap * inv_div;
+  for (int ci = threadIdx.x; ci < nch; ci += blockDim.x) {
+    float f[8], g[8];
+    load8(x + ci * 8, f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float sg = 0.5f * tanhf(0.5f * f[i] * inv_div) + 0.5f;
+      const float pr = exp2f(cap * sg * L2E) * inv_total;
+      const float onehot = (ci * 8 + i == tgt) ? 1.f : 0.f;
+      g[i] = (pr - onehot) * sg * (1.f - sg) * gs;
+    }
+    if (grad_is_bf16) {
+      store8(reinterpret_cast<bf16*>(grad) + (long long)row * ld + ci * 8, g);
+    } else {
+      uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        w0 |= (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(g[2 * k], g[2 * k + 1]), __NV_SATFINITE, __NV_E5M2) << (16 * k);
+        w1 |= (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(g[4 + 2 * k], g[5 + 2 * k]), __NV_SATFINITE, __NV_E5M2) << (16 * k);
+      }
+      *reinterpret_cast<uint2*>(grad + (long long)row * ld + ci * 8) = make_uint2(w0, w1);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- optimizer pieces
+template <typename TP>
+__global__ void adam_kernel(TP* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
+                            float* __restrict__ v, long long n, float lr, float b1, float b2, float eps, float wd,
+                            float bias1, float bias2, float grad_scale) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float gi = g[i] * grad_scale;
+  const float mi = b1 * m[i] + (1.f - b1) * gi;
+  const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
+  m[i] = mi;
+  v[i] = vi;
+  float pi = (float)p[i];
+  pi -= lr * wd * pi;
+  const float denom = sqrtf(vi) / sqrtf(bias2) + eps;
+  pi -= (lr / bias1) * mi / denom;
+  p[i] = (TP)pi;
+}
+
+__global__ void muon_momentum_kernel(const float* __restrict__ g, float* __restrict__ buf, bf16* __restrict__ out,
+                                     float* __restrict__ sumsq, long long n, float mu, int nesterov,
+                                     float grad_scale) {
+  __shared__ float red[8];
+  float acc = 0.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float gi = g[i] * grad_scale;
+    const float b = mu * buf[i] + (1.f - mu) * gi;
+    buf[i] = b;
+    const float u = nesterov ? (1.f - mu) * gi + mu * b : b;
+    const bf16 ub = __float2bfloat16_rn(u);
+    out[i] = ub;
+    const float uf = __bfloat162float(ub);
+    acc = fmaf(uf, uf, acc);
+  }
+  acc = warp_sum(acc);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) t += red[i];
+    atomicAdd(sumsq, t);
+  }
+}
+
+__global__ void scale_by_inv_norm_kernel(bf16* __restrict__ x, const float* __restrict__ sumsq, long long n,
+                                         float eps) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float s = 1.f / (sqrtf(sumsq[0]) + eps);
+  x[i] = __float2bfloat16_rn(__bfloat162float(x[i]) * s);
+}
+
+__global__ void axpy_kernel(float* __restrict__ p, const bf16* __restrict__ u, bf16* __restrict__ p_bf16, long long n,
+                            float alpha) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float v = fmaf(alpha, __bfloat162float(u[i]), p[i]);
+  p[i] = v;
+  if (p_bf16) p_bf16[i] = __float2bfloat16_rn(v);
+}
+
+int pick_nch(int C) {
+  if (C % 8 != 0) throw std::runtime_error("row kernels need the row length to be a multiple of 8");
+  const int nch = (C + 255) / 256;
+  if (nch <= 3) return 3;
+  if (nch <= 4) return 4;
+  if (nch <= 8) return 8;
+  throw std::runtime_error("row kernels support row lengths up to 2048");
+}
+
+#define DISPATCH_NCH(C, CALL)            \
+  switch (pick_nch(C)) {                 \
+    case 3: { constexpr int N_ = 3; CALL; break; } \
+    case 4: { constexpr int N_ = 4; CALL; break; } \
+    default: { constexpr int N_ = 8; CALL; break; } \
+  }
+
+}  // namespace
+
+void rmsnorm_fwd(const void* x, void* y, int R, int C, float eps, cudaStream_t s) {
+  mix_norm_fwd(x, nullptr, nullptr, nullptr, nullptr, nullptr, y, R, C, eps, s);
+}
+
+void mix_norm_fwd(const void* x, const void* x0, const void* skip, const float* lam, const float* skip_w,
+                  void* x_mix, void* xn, int R, int C, float eps, cudaStream_t s) {
+  DISPATCH_NCH(C, (mix_norm_fwd_kernel<N_><<<row_blocks(R), kRowThreads, 0, s>>>(
+                      (const bf16*)x, (const bf16*)x0, (const bf16*)skip, lam, skip_w, (bf16*)x_mix, (bf16*)xn, R, C, eps)));
+  check("mix_norm_fwd");
+}
+
+void norm_bwd_add(const void* dy, const void* x, const void* dres, void* out, int R, int C, float eps,
+                  cudaStream_t s) {
+  DISPATCH_NCH(C, (norm_bwd_add_kernel<N_><<<row_blocks(R), kRowThreads, 0, s>>>((const bf16*)dy, (const bf16*)x,
+                                                                                 (const bf16*)dres, (bf16*)out, R, C, eps)));
+  check("norm_bwd_add");
+}
+
+void mix_bwd(const void* dmix, const void* x, const void* x0, const void* skip, const float* lam,
+             const float* skip_w, void* dx, void* dskip, float* dx0_acc, float* dlam, float* dskip_w, int R, int C,
+             cudaStream_t s) {
+  const int blocks = 148 * 4;
+  DISPATCH_NCH(C, (mix_bwd_kernel<N_><<<blocks, kRowThreads, 0, s>>>((const bf16*)dmix, (const bf16*)x, (const bf16*)x0,
+                                                                    (const bf16*)skip, lam, skip_w, (bf16*)dx,
+                                                                    (bf16*)dskip, dx0_acc, dlam, dskip_w, R, C)));
+  check("mix_bwd");
+}
+
+void qkv_post_fwd(const void* qkv, const void* ve, const float* lam, const float* cos, const float* sin, void* out,
+                  int T, int H, int D, float eps, cudaStream_t s) {
+  const long long warps = (long long)T * 3 * H;
+  const int blocks = (int)((warps + 7) / 8);
+  if (D == 128) qkv_post_fwd_kernel<128><<<blocks, 256, 0, s>>>((const bf16*)qkv, (const bf16*)ve, lam, cos, sin, (bf16*)out, T, H, eps);
+  else if (D == 64) qkv_post_fwd_kernel<64><<<blocks, 256, 0, s>>>((const bf16*)qkv, (const bf16*)ve, lam, cos, sin, (bf16*)out, T, H, eps);
+  else throw std::runtime_error("qkv_post: head_dim must be 64 or 128");
+  check("qkv_post_fwd");
+}
+
+void qkv_post_bwd(const float* dq, const void* dk, const void* dv, const void* qkv, const void* ve,
+                  const float* lam, const float* cos, const float* sin, void* dqkv, void* dve, float* dlam, int T,
+                  int H, int D, float eps, cudaStream_t s) {
+  const long long warps = (long long)T * 3 * H;
+  const int blocks = (int)((warps + 7) / 8);
+  if (D == 128) qkv_post_bwd_kernel<128><<<blocks, 256, 0, s>>>(dq, (const bf16*)dk, (const bf16*)dv, (const bf16*)qkv, (const bf16*)ve, lam, cos, sin, (bf16*)dqkv, (bf16*)dve, dlam, T, H, eps);
+  else if (D == 64) qkv_post_bwd_kernel<64><<<blocks, 256, 0, s>>>(dq, (const bf16*)dk, (const bf16*)dv, (const bf16*)qkv, (const bf16*)ve, lam, cos, sin, (bf16*)dqkv, (bf16*)dve, dlam, T, H, eps);
+  else throw std::runtime_error("qkv_post: head_dim must be 64 or 128");
+  check("qkv_post_bwd");
+}
+
+void embed_gather(const int* idx, const void* table, void* out, int T, int C, int normalize, float eps,
+                  cudaStream_t s) {
+  DISPATCH_NCH(C, (embed_gather_kernel<N_><<<row_blocks(T), kRowThreads, 0, s>>>(idx, (const bf16*)table, (bf16*)out, T, C, normalize, eps)));
+  check("embed_gather");
+}
+
+void embed_scatter_add(const int* idx, const void* src, int src_is_f32, float* grad_table, int T, int C,
+                       cudaStream_t s) {
+  if (C % 4 != 0) throw std::runtime_error("embed_scatter_add: C must be a multiple of 4");
+  const long long n = (long long)T * (C / 4);
+  const int blocks = (int)((n + 255) / 256);
+  if (src_is_f32) embed_scatter_add_kernel<float><<<blocks, 256, 0, s>>>(idx, (const float*)src, grad_table, T, C);
+  else embed_scatter_add_kernel<bf16><<<blocks, 256, 0, s>>>(idx, (const bf16*)src, grad_table, T, C);
+  check("embed_scatter_add");
+}
+
+void cast_fp8(const void* x, void* out, float scale, long long n, int in_kind, int out_kind, cudaStream_t s) {
+  const long long thr = (n + 7) / 8;
+  const int blocks = (int)((thr + 255) / 256);
+  if (in_kind == 0) cast_fp8_kernel<bf16><<<blocks, 256, 0, s>>>((const bf16*)x, (uint8_t*)out, scale, n, out_kind);
+  else cast_fp8_kernel<float><<<blocks, 256, 0, s>>>((const float*)x, (uint8_t*)out, scale, n, out_kind);
+  check("cast_fp8");
+}
+
+void softcap_ce(const void* logits, const long long* targets, float* loss_rows, void* grad, int grad_is_bf16, int T,
+                int V, long long ld, float cap, float div, float loss_scale, float grad_scale, cudaStream_t s) {
+  if (V % 8 != 0 || ld % 8 != 0) throw std::runtime_error("softcap_ce: vocabulary and row pitch must be multiples of 8");
+  softcap_ce_kernel<<<T, 512, 0, s>>>((const bf16*)logits, targets, loss_rows, (uint8_t*)grad, grad_is_bf16, V, ld, cap,
+                                      1.f / div, loss_scale, grad_scale);
+  check("softcap_ce");
+}
+
+void adam_step(void* p, int p_is_bf16, const float* g, float* m, float* v, long long n, float lr, float beta1,
+               float beta2, float eps, float wd, float bias1, float bias2, float grad_scale, cudaStream_t s) {
+  const int blocks = (int)((n + 255) / 256);
+  if (p_is_bf16) adam_kernel<bf16><<<blocks, 256, 0, s>>>((bf16*)p, g, m, v, n, lr, beta1, beta2, eps, wd, bias1, bias2, grad_scale);
+  else adam_kernel<float><<<blocks, 256, 0, s>>>((float*)p, g, m, v, n, lr, beta1, beta2, eps, wd, bias1, bias2, grad_scale);
+  check("adam_step");
+}
+
+void muon_momentum(const float* g, float* buf, void* out_bf16, float* sumsq, long long n, float mu, int nesterov,
+                   float grad_scale, cudaStream_t s) {
+  int blocks = (int)((n + 255) / 256);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  muon_momentum_kernel<<<blocks, 256, 0, s>>>(g, buf, (bf16*)out_bf16, sumsq, n, mu, nesterov, grad_scale);
+  check("muon_momentum");
+}
+
+void scale_by_inv_norm(void* x_bf16, const float* sumsq, long long n, float eps, cudaStream_t s) {
+  const int blocks = (int)((n + 255) / 256);
+  scale_by_inv_norm_kernel<<<blocks, 256, 0, s>>>((bf16*)x_bf16, sumsq, n, eps);
+  check("scale_by_inv_norm");
+}
+
+void axpy_bf16_to_f32(float* p, const void* u_bf16, void* p_bf16, long long n, float alpha, cudaStream_t s) {
+  const int blocks = (int)((n + 255) / 256);
+  axpy_kernel<<<blocks, 256, 0, s>>>(p, (const bf16*)u_bf16, (bf16*)p_bf16, n, alpha);
+  check("axpy_bf16_to_f32");
+}
+
+}  // namespace b200

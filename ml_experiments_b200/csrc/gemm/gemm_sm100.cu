@@ -61,7 +61,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   constexpr int CHUNK_BYTES = BK * 128; // one MN-major box: BK k-rows x 128 B
   constexpr uint32_t TMEM_COLS = 2 * BN;
 
-  extern __shared__ uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* staging = smem + STAGES * L::kStageBytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);

@@ -1,0 +1,54 @@
+"""tcgen05 flash attention (forward and backward) against a dense fp32 oracle."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _setup(t, h, d, doc_len, seed=0):
+    torch.manual_seed(seed)
+    qkv = torch.randn(t, 3, h, d, device="cuda", dtype=torch.bfloat16)
+    q, k, v = qkv[:, 0], qkv[:, 1], qkv[:, 2]  # strided views, heads contiguous
+    from ml_experiments_b200.ops.attention import doc_bounds_from_starts
+
+    is_start = torch.zeros(t, dtype=torch.bool, device="cuda")
+    is_start[::doc_len] = True
+    ds, de = doc_bounds_from_starts(is_start)
+    return q, k, v, ds, de
+
+
+@pytest.mark.parametrize("t,doc_len,window", [(256, 256, 0), (1024, 1024, 0), (1024, 384, 0), (2048, 1000, 3), (1536, 1536, 2)])
+@pytest.mark.parametrize("d", [128, 64])
+def test_attention_forward(t, doc_len, window, d):
+    from ml_experiments_b200.ops import attention as A
+
+    q, k, v, ds, de = _setup(t, 3, d, doc_len)
+    o, lse = A.flash_attention_forward(q, k, v, ds, de, 0.12, window)
+    ref = A.attention_reference(q, k, v, ds, 0.12, window)
+    err = (o.float() - ref).abs().max().item()
+    assert err < 2e-2, err
+
+
+@pytest.mark.parametrize("t,doc_len,window", [(256, 256, 0), (1024, 1024, 0), (1024, 384, 0), (2048, 1000, 3)])
+def test_attention_backward(t, doc_len, window):
+    from ml_experiments_b200.ops import attention as A
+
+    q, k, v, ds, de = _setup(t, 2, 128, doc_len, seed=1)
+    d_o = torch.randn(t, 2, 128, device="cuda", dtype=torch.bfloat16)
+    qf, kf, vf = (x.float().detach().requires_grad_(True) for x in (q, k, v))
+    ref = A.attention_reference(qf, kf, vf, ds, 0.12, window)
+    ref.backward(d_o.float())
+    o, lse = A.flash_attention_forward(q, k, v, ds, de, 0.12, window)
+    dq, dk, dv = A.flash_attention_backward(q, k, v, o, d_o, lse, ds, de, 0.12, window)
+    for name, got, want in (("dq", dq, qf.grad), ("dk", dk, kf.grad), ("dv", dv, vf.grad)):
+        rel = ((got.float() - want).norm() / want.norm()).item()
+        assert rel < 2e-2, (name, rel)
+
+
+def test_doc_bounds():
+    from ml_experiments_b200.ops.attention import doc_bounds_from_starts
+
+    s = torch.tensor([1, 0, 0, 1, 0, 1, 0, 0], dtype=torch.bool)
+    ds, de = doc_bounds_from_starts(s)
+    assert ds.tolist() == [0, 0, 0, 3, 3, 5, 5, 5]
+    assert de.tolist() == [3, 3, 3, 5, 5, 8, 8, 8]

@@ -1,0 +1,165 @@
+"""Fused row kernels against fp32 torch restatements."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+EPS = torch.finfo(torch.bfloat16).eps
+
+
+def _close(a, b, tol):
+    err = (a.float() - b.float()).abs().max().item()
+    scale = b.float().abs().max().item() + 1e-6
+    assert err <= tol * scale, (err, scale)
+
+
+@pytest.mark.parametrize("c", [768, 1024, 256, 2048])
+def test_rmsnorm_and_backward(c):
+    from ml_experiments_b200.ops import fused as Fz
+
+    torch.manual_seed(0)
+    x = torch.randn(1000, c, device="cuda").bfloat16()
+    _close(Fz.rmsnorm(x), Fz.rmsnorm_ref(x), 1e-2)
+    dy = torch.randn_like(x)
+    dres = torch.randn_like(x)
+    xf = x.float().requires_grad_(True)
+    y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + EPS)
+    y.backward(dy.float())
+    _close(Fz.norm_bwd_add(dy, x, dres), dres.float() + xf.grad, 1.5e-2)
+    _close(Fz.norm_bwd_add(dy, x, None), xf.grad, 1.5e-2)
+
+
+def test_mix_norm_and_backward():
+    from ml_experiments_b200.ops import fused as Fz
+    from ml_experiments_b200.ops.runtime import ops
+
+    torch.manual_seed(1)
+    r, c = 777, 768
+    x, x0, skip, dmix = (torch.randn(r, c, device="cuda").bfloat16() for _ in range(4))
+    lam = torch.tensor([0.9, 0.3], device="cuda")
+    w = torch.tensor([0.7], device="cuda")
+    x_mix, xn = Fz.mix_norm(x, x0, lam, skip, w)
+    ref_mix = 0.9 * (x.float() + 0.7 * skip.float()) + 0.3 * x0.float()
+    _close(x_mix, ref_mix, 1e-2)
+    _close(xn, Fz.rmsnorm_ref(x_mix), 1e-2)
+    dx = torch.empty_like(x); dskip = torch.empty_like(x)
+    dx0 = torch.zeros(r, c, device="cuda"); dlam = torch.zeros(2, device="cuda"); dw = torch.zeros(1, device="cuda")
+    ops().mix_bwd(dmix, x, x0, skip, lam, w, dx, dskip, dx0, dlam, dw)
+    g = dmix.float()
+    _close(dx, 0.9 * g, 1e-2)
+    _close(dskip, 0.9 * 0.7 * g, 1e-2)
+    _close(dx0, 0.3 * g, 1e-3)
+    ref_dlam = torch.stack([(g * (x.float() + 0.7 * skip.float())).sum(), (g * x0.float()).sum()])
+    assert torch.allclose(dlam, ref_dlam, rtol=2e-3, atol=1.0)
+    assert torch.allclose(dw, (0.9 * g * skip.float()).sum().view(1), rtol=2e-3, atol=1.0)
+
+
+@pytest.mark.parametrize("d", [128, 64])
+def test_qkv_post(d):
+    from ml_experiments_b200.ops import fused as Fz
+    from ml_experiments_b200.ops.runtime import ops
+
+    torch.manual_seed(2)
+    t, h = 300, 3
+    qkv = torch.randn(t, 3, h, d, device="cuda").bfloat16()
+    ve = torch.randn(t, h * d, device="cuda").bfloat16()
+    lam = torch.tensor([0.6, 0.4], device="cuda")
+    cos, sin = Fz.rotary_tables(d, 512, "cuda")
+    out = torch.empty_like(qkv)
+    ops().qkv_post_fwd(qkv, ve, lam, cos, sin, out, h, d, EPS)
+
+    def ref_fwd(qkv_f, ve_f, lam_f):
+        q, k, v = qkv_f[:, 0], qkv_f[:, 1], qkv_f[:, 2]
+        nrm = lambda z: z * torch.rsqrt(z.pow(2).mean(-1, keepdim=True) + EPS)
+        rope = lambda z: torch.cat((z[..., : d // 2] * cos[:t, None] + z[..., d // 2:] * sin[:t, None],
+                                    -z[..., : d // 2] * sin[:t, None] + z[..., d // 2:] * cos[:t, None]), -1)
+        return torch.stack([rope(nrm(q)), rope(nrm(k)), lam_f[0] * v + lam_f[1] * ve_f.view(t, h, d)], 1)
+
+    qf = qkv.float().requires_grad_(True); vf = ve.float().requires_grad_(True); lf = lam.clone().requires_grad_(True)
+    ref = ref_fwd(qf, vf, lf)
+    _close(out, ref, 2e-2)
+    g = torch.randn(t, 3, h, d, device="cuda")
+    ref.backward(g)
+    dq = g[:, 0].contiguous(); dk = g[:, 1].contiguous().bfloat16(); dv = g[:, 2].contiguous().bfloat16()
+    dqkv = torch.empty_like(qkv); dve = torch.empty_like(ve); dlam = torch.zeros(2, device="cuda")
+    ops().qkv_post_bwd(dq, dk, dv, qkv, ve, lam, cos, sin, dqkv, dve, dlam, h, d, EPS)
+    _close(dqkv, qf.grad, 2e-2)
+    _close(dve, vf.grad, 2e-2)
+    assert torch.allclose(dlam, lf.grad, rtol=1e-2, atol=0.5)
+
+
+def test_embed_gather_scatter():
+    from ml_experiments_b200.ops import fused as Fz
+    from ml_experiments_b200.ops.runtime import ops
+
+    torch.manual_seed(3)
+    table = torch.randn(1000, 768, device="cuda").bfloat16()
+    idx = torch.randint(0, 1000, (4096,), device="cuda", dtype=torch.int32)
+    assert torch.equal(Fz.embed_gather(idx, table), table[idx.long()])
+    _close(Fz.embed_gather(idx, table, normalize=True), Fz.rmsnorm_ref(table[idx.long()]), 1e-2)
+    src = torch.randn(4096, 768, device="cuda").bfloat16()
+    gt = torch.zeros(1000, 768, device="cuda")
+    ops().embed_scatter_add(idx, src, gt)
+    ref = torch.zeros(1000, 768, device="cuda").index_add_(0, idx.long(), src.float())
+    assert torch.allclose(gt, ref, rtol=1e-4, atol=1e-3)
+
+
+def test_cast_fp8():
+    from ml_experiments_b200.ops import fused as Fz
+
+    x = torch.randn(1000, 777, device="cuda").bfloat16()
+    for dt in (torch.float8_e4m3fn, torch.float8_e5m2):
+        got = Fz.cast_fp8(x, 2.0, dt)
+        ref = (x.float() * 2.0).to(dt)
+        assert torch.equal(got.float(), ref.float())
+
+
+def test_softcap_ce():
+    from ml_experiments_b200.ops import fused as Fz
+
+    torch.manual_seed(4)
+    t, v = 300, 50304
+    logits = (torch.randn(t, v, device="cuda") * 3).bfloat16()
+    tg = torch.randint(0, 50257, (t,), device="cuda")
+    lf = logits.float().requires_grad_(True)
+    ref = Fz.softcap_ce_ref(lf, tg)
+    ref.mean().backward()
+    g16 = torch.empty_like(logits)
+    rows = Fz.softcap_ce(logits, tg, g16, grad_scale=1.0 / t * 1024)
+    assert torch.allclose(rows, ref.detach(), rtol=2e-3, atol=2e-3)
+    rel = ((g16.float() / 1024 - lf.grad).norm() / lf.grad.norm()).item()
+    assert rel < 1e-2, rel
+    g8 = torch.empty(t, v, device="cuda", dtype=torch.float8_e5m2)
+    Fz.softcap_ce(logits, tg, g8, grad_scale=1.0 / t * 2.0 ** 19)
+    rel8 = ((g8.float() / 2.0 ** 19 - lf.grad).norm() / lf.grad.norm()).item()
+    assert rel8 < 0.15, rel8
+
+
+def test_optimizer_pieces():
+    from ml_experiments_b200.ops.runtime import ops
+
+    torch.manual_seed(5)
+    n = 768 * 3072
+    p = torch.randn(n, device="cuda"); g = torch.randn(n, device="cuda") * 1e-2
+    m = torch.zeros(n, device="cuda"); v = torch.zeros(n, device="cuda")
+    p_ref = p.clone().requires_grad_(True)
+    opt = torch.optim.Adam([p_ref], lr=0.01, betas=(0.8, 0.95), eps=1e-10)
+    for step in range(1, 4):
+        p_ref.grad = g.clone()
+        opt.step()
+        ops().adam_step(p, g, m, v, 0.01, 0.8, 0.95, 1e-10, 0.0, 1 - 0.8 ** step, 1 - 0.95 ** step, 1.0)
+    assert torch.allclose(p, p_ref.detach(), rtol=1e-4, atol=1e-5)
+    buf = torch.zeros(n, device="cuda"); out = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    ss = torch.zeros(1, device="cuda")
+    ops().muon_momentum(g, buf, out, ss, 0.95, True, 1.0)
+    b_ref = 0.05 * g
+    u_ref = 0.05 * g + 0.95 * b_ref
+    assert torch.allclose(buf, b_ref, rtol=1e-5, atol=1e-8)
+    assert torch.allclose(out.float(), u_ref, rtol=1e-2, atol=1e-6)
+    assert torch.allclose(ss, out.float().pow(2).sum().view(1), rtol=1e-3)
+    ops().scale_by_inv_norm(out, ss, 1e-7)
+    assert abs(out.float().norm().item() - 1.0) < 1e-2
+    pb = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    p2 = p.clone()
+    ops().axpy_bf16_to_f32(p2, out, pb, -0.5)
+    assert torch.allclose(p2, p - 0.5 * out.float(), rtol=1e-5, atol=1e-6)
+    assert torch.equal(pb, p2.bfloat16())
