@@ -228,10 +228,13 @@ void adam_step(Tensor p, const Tensor& g, Tensor m, Tensor v, double lr, double 
                double wd, double bias1, double bias2, double grad_scale) {
   const c10::cuda::CUDAGuard guard(p.device());
   TORCH_CHECK(p.is_contiguous() && g.is_contiguous() && m.is_contiguous() && v.is_contiguous(), "adam_step: contiguous");
-  TORCH_CHECK(g.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat, "adam_step: fp32 g/m/v");
+  TORCH_CHECK(m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat, "adam_step: fp32 m/v");
   const bool pb = p.scalar_type() == at::kBFloat16;
+  const bool gb = g.scalar_type() == at::kBFloat16;
   TORCH_CHECK(pb || p.scalar_type() == at::kFloat, "adam_step: p must be fp32 or bf16");
-  b200::adam_step(p.data_ptr(), pb, g.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), p.numel(), (float)lr,
+  TORCH_CHECK(gb || g.scalar_type() == at::kFloat, "adam_step: g must be fp32 or bf16");
+  TORCH_CHECK(g.numel() == p.numel() && m.numel() == p.numel() && v.numel() == p.numel(), "adam_step: size mismatch");
+  b200::adam_step(p.data_ptr(), pb, g.data_ptr(), gb, m.data_ptr<float>(), v.data_ptr<float>(), p.numel(), (float)lr,
                   (float)beta1, (float)beta2, (float)eps, (float)wd, (float)bias1, (float)bias2, (float)grad_scale, cur_stream());
 }
 

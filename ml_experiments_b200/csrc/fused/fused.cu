@@ -497,13 +497,13 @@ softcap_ce_kernel(const bf16* __restrict__ logits, const long long* __restrict__
 }
 
 // ---------------------------------------------------------------------------------------------- optimizer pieces
-template <typename TP>
-__global__ void adam_kernel(TP* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
+template <typename TP, typename TG>
+__global__ void adam_kernel(TP* __restrict__ p, const TG* __restrict__ g, float* __restrict__ m,
                             float* __restrict__ v, long long n, float lr, float b1, float b2, float eps, float wd,
                             float bias1, float bias2, float grad_scale) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
-  const float gi = g[i] * grad_scale;
+  const float gi = (float)g[i] * grad_scale;
   const float mi = b1 * m[i] + (1.f - b1) * gi;
   const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
   m[i] = mi;
@@ -656,11 +656,14 @@ void softcap_ce(const void* logits, const long long* targets, float* loss_rows, 
   check("softcap_ce");
 }
 
-void adam_step(void* p, int p_is_bf16, const float* g, float* m, float* v, long long n, float lr, float beta1,
-               float beta2, float eps, float wd, float bias1, float bias2, float grad_scale, cudaStream_t s) {
+void adam_step(void* p, int p_is_bf16, const void* g, int g_is_bf16, float* m, float* v, long long n, float lr,
+               float beta1, float beta2, float eps, float wd, float bias1, float bias2, float grad_scale,
+               cudaStream_t s) {
   const int blocks = (int)((n + 255) / 256);
-  if (p_is_bf16) adam_kernel<bf16><<<blocks, 256, 0, s>>>((bf16*)p, g, m, v, n, lr, beta1, beta2, eps, wd, bias1, bias2, grad_scale);
-  else adam_kernel<float><<<blocks, 256, 0, s>>>((float*)p, g, m, v, n, lr, beta1, beta2, eps, wd, bias1, bias2, grad_scale);
+  if (p_is_bf16 && g_is_bf16) adam_kernel<bf16, bf16><<<blocks, 256, 0, s>>>((bf16*)p, (const bf16*)g, m, v, n, lr, beta1, beta2, eps, wd, bias1, bias2, grad_scale);
+  else if (p_is_bf16) adam_kernel<bf16, float><<<blocks, 256, 0, s>>>((bf16*)p, (const float*)g, m, v, n, lr, beta1, beta2, eps, wd, bias1, bias2, grad_scale);
+  else if (g_is_bf16) adam_kernel<float, bf16><<<blocks, 256, 0, s>>>((float*)p, (const bf16*)g, m, v, n, lr, beta1, beta2, eps, wd, bias1, bias2, grad_scale);
+  else adam_kernel<float, float><<<blocks, 256, 0, s>>>((float*)p, (const float*)g, m, v, n, lr, beta1, beta2, eps, wd, bias1, bias2, grad_scale);
   check("adam_step");
 }
 

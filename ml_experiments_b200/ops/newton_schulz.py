@@ -1,0 +1,69 @@
+"""Newton-Schulz / Polar-Express orthogonalisation on the tcgen05 GEMM.
+
+Each iteration is three batched GEMMs with the polynomial folded into their epilogues
+(``A = X·Xᵀ``, ``B = b·A + c·A·A``, ``X ← a·X + B·X``); tall matrices are handled through the operand-majorness flags
+(``A = Xᵀ·X``, ``X ← a·X + X·B``) so no transposed copy is ever made. Counterparts in the reference:
+``zeropower_via_newtonschulz5`` (records/track_1_short/2025-01-26_BatchSize/...txt:110-133) and ``polar_express`` with
+the Triton ``XXT`` / ``ba_plus_cAA`` kernels (modded-nanogpt/train_gpt.py:143-195, triton_kernels.py:54-254).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import gemm as G
+
+NS5_COEFFS = [(3.4445, -4.7750, 2.0315)] * 5
+
+# Per-iteration coefficients of the "Polar Express" schedule (Amsel et al., 2025), safety factor 1.01 folded in.
+POLAR_EXPRESS_COEFFS = [
+    (8.156554524902461, -22.48329292557795, 15.878769915207462),
+    (4.042929935166739, -2.808917465908714, 0.5000178451051316),
+    (3.8916678022926607, -2.772484153217685, 0.5060648178503393),
+    (3.285753657755655, -2.3681294933425376, 0.46449024233003106),
+    (2.3465413258596377, -1.7097828382687081, 0.42323551169305323),
+]
+
+
+def newton_schulz_torch(G_: torch.Tensor, coeffs=NS5_COEFFS, eps: float = 1e-7, norm_scale: float = 1.0) -> torch.Tensor:
+    """Plain-torch restatement (any device); input of any float dtype, result bf16 (as the reference computes it)."""
+    X = G_.bfloat16()
+    tall = G_.size(-2) > G_.size(-1)
+    if tall:
+        X = X.mT
+    X = X / (X.norm(dim=(-2, -1), keepdim=True) * norm_scale + eps)
+    for a, b, c in coeffs:
+        A = X @ X.mT
+        B = b * A + c * A @ A
+        X = a * X + B @ X
+    return X.mT if tall else X
+
+
+def newton_schulz_(X: torch.Tensor, coeffs=NS5_COEFFS, work: dict | None = None) -> torch.Tensor:
+    """Orthogonalises the batch ``X [B, r, c]`` (bf16, CUDA, already divided by its Frobenius norm).
+
+    Returns a tensor holding the result (either ``X`` or the ping-pong buffer kept in ``work``)."""
+    assert X.is_cuda and X.dtype == torch.bfloat16 and X.dim() == 3
+    bsz, r, c = X.shape
+    wide = r <= c
+    n = min(r, c)
+    work = {} if work is None else work
+    key = (bsz, r, c)
+    bufs = work.get(key)
+    if bufs is None:
+        bufs = (torch.empty(bsz, n, n, dtype=torch.bfloat16, device=X.device),
+                torch.empty(bsz, n, n, dtype=torch.bfloat16, device=X.device), torch.empty_like(X))
+        work[key] = bufs
+    A, Bm, X2 = bufs
+    for a_, b_, c_ in coeffs:
+        if wide:
+            G.gemm(X, X, out=A)
+        else:
+            G.gemm(X, X, a_mn=True, b_mn=True, out=A)
+        G.gemm(A, A, out=Bm, epilogue=G.EPI_AXPBY, aux=A, alpha=c_, beta=b_)
+        if wide:
+            G.gemm(Bm, X, b_mn=True, out=X2, epilogue=G.EPI_AXPBY, aux=X, alpha=1.0, beta=a_)
+        else:
+            G.gemm(X, Bm, out=X2, epilogue=G.EPI_AXPBY, aux=X, alpha=1.0, beta=a_)
+        X, X2 = X2, X
+    work[key] = (A, Bm, X2)
+    return X

@@ -1,0 +1,120 @@
+"""Muon: momentum orthogonalised by Newton-Schulz (classic modded-nanogpt semantics).
+
+Reference: ``Muon`` in records/track_1_short/2025-01-26_BatchSize/c44090cc-...txt:134-212 — fp32 momentum ``lerp``,
+Nesterov mix, 5 quintic Newton-Schulz steps in bf16 on the (batched) 2-D update, update scale
+``max(1, rows/cols)**0.5``. There the work is distributed by round-robin parameter ownership followed by
+``all_gather_into_tensor``; here the single-process path stacks all equally shaped matrices into one batch and runs
+the three GEMMs of each iteration on the tcgen05 kernel, and the multi-GPU path lives in
+:mod:`ml_experiments_b200.parallel.muon_dist`.
+"""
+from __future__ import annotations
+
+from collections import defaultdict
+
+import torch
+
+from ..ops.newton_schulz import NS5_COEFFS, newton_schulz_, newton_schulz_torch
+from ..ops.runtime import ops
+from ..utils.shadow import get_shadow_buffer, set_shadow
+
+
+class Muon(torch.optim.Optimizer):
+    def __init__(self, params, lr: float = 0.02, momentum: float = 0.95, nesterov: bool = True, ns_steps: int = 5,
+                 rank: int = 0, world_size: int = 1):
+        self.rank, self.world_size = rank, world_size
+        defaults = dict(lr=lr, momentum=momentum, nesterov=nesterov, ns_steps=ns_steps)
+        params = [*params]
+        assert all(isinstance(p, torch.Tensor) for p in params)
+        super().__init__(params, defaults)
+        self._work: dict = {}
+        self._stacks: dict = {}
+
+    # ------------------------------------------------------------------------------------------ torch path
+    @torch.no_grad()
+    def _step_torch(self, group):
+        coeffs = NS5_COEFFS[: group["ns_steps"]] if group["ns_steps"] <= 5 else [NS5_COEFFS[0]] * group["ns_steps"]
+        for p in group["params"]:
+            if p.grad is None:
+                continue
+            g = p.grad.float()
+            st = self.state[p]
+            if "momentum_buffer" not in st:
+                st["momentum_buffer"] = torch.zeros_like(g)
+            buf = st["momentum_buffer"]
+            buf.lerp_(g, 1 - group["momentum"])
+            g = g.lerp(buf, group["momentum"]) if group["nesterov"] else buf
+            u = newton_schulz_torch(g, coeffs)
+            p.add_(u.to(p.dtype), alpha=-group["lr"] * max(1, p.size(-2) / p.size(-1)) ** 0.5)
+
+    # ------------------------------------------------------------------------------------------ fused path
+    def _slots(self, params):
+        """Groups parameters by matrix shape; every 2-D slice of a parameter gets one slot of a stacked buffer."""
+        key = tuple(id(p) for p in params)
+        ent = self._stacks.get(key)
+        if ent is not None:
+            return ent
+        by_shape = defaultdict(list)
+        for p in params:
+            r, c = p.shape[-2], p.shape[-1]
+            nmat = p.numel() // (r * c)
+            by_shape[(r, c)].append((p, nmat))
+        out = []
+        for (r, c), plist in by_shape.items():
+            total = sum(n for _, n in plist)
+            dev = plist[0][0].device
+            stack = torch.empty(total, r, c, dtype=torch.bfloat16, device=dev)
+            sumsq = torch.zeros(total, dtype=torch.float32, device=dev)
+            out.append((r, c, plist, stack, sumsq))
+        self._stacks[key] = out
+        return out
+
+    @torch.no_grad()
+    def _step_fused(self, group):
+        o = ops()
+        mu, nesterov, lr = float(group["momentum"]), bool(group["nesterov"]), float(group["lr"])
+        coeffs = [NS5_COEFFS[0]] * group["ns_steps"]
+        params = [p for p in group["params"] if p.grad is not None]
+        for r, c, plist, stack, sumsq in self._slots(params):
+            sumsq.zero_()
+            slot = 0
+            for p, nmat in plist:
+                st = self.state[p]
+                if "momentum_buffer" not in st:
+                    st["momentum_buffer"] = torch.zeros(p.shape, dtype=torch.float32, device=p.device)
+                g = p.grad if p.grad.dtype == torch.float32 else p.grad.float()
+                g = g.contiguous().view(nmat, r, c)
+                buf = st["momentum_buffer"].view(nmat, r, c)
+                for j in range(nmat):
+                    o.muon_momentum(g[j], buf[j], stack[slot + j], sumsq[slot + j:slot + j + 1], mu, nesterov, 1.0)
+                    o.scale_by_inv_norm(stack[slot + j], sumsq[slot + j:slot + j + 1], 1e-7)
+                slot += nmat
+            u = newton_schulz_(stack, coeffs, self._work)
+            alpha = -lr * max(1.0, r / c) ** 0.5
+            slot = 0
+            for p, nmat in plist:
+                upd = u[slot:slot + nmat].view(p.shape)
+                if p.dtype == torch.float32:
+                    sh = get_shadow_buffer(p, torch.bfloat16)
+                    if sh is None:
+                        sh = torch.empty(p.shape, dtype=torch.bfloat16, device=p.device)
+                    o.axpy_bf16_to_f32(p, upd, sh, alpha)
+                    set_shadow(p, sh)
+                else:
+                    p.add_(upd.to(p.dtype), alpha=alpha)
+                slot += nmat
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        for group in self.param_groups:
+            ps = [p for p in group["params"] if p.grad is not None]
+            if not ps:
+                continue
+            if all(p.is_cuda and p.is_contiguous() for p in ps):
+                self._step_fused(group)
+            else:
+                self._step_torch(group)
+        return loss

@@ -1,0 +1,162 @@
+"""Trainer of the "classic" modded-nanogpt configuration (GPT-2 124M, Muon + Adam, one 48x1024-token sequence per
+rank per step) and of the same family at other sizes.
+
+Follows the training section of records/track_1_short/2025-01-26_BatchSize/c44090cc-...txt:462-625: Adam
+(betas 0.8/0.95, eps 1e-10) on head (lr 0.008), embeddings (0.6) and scalars (0.04); Muon (lr 0.05, momentum warm-up
+0.85 -> 0.95 over 300 steps) on the hidden matrices; learning-rate multiplier 1 then linear to 0.1 over the last 40 % of
+the run; sliding window growing 128 -> 1792 tokens in 128-token blocks; gradients averaged over ranks every step.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from ..models.gpt import GPT, GPTConfig, next_multiple_of_n
+from ..optim import FusedAdam, Muon
+
+
+@dataclass
+class Hyperparameters:
+    train_files: str = "data/fineweb10B/fineweb_train_*.bin"
+    val_files: str = "data/fineweb10B/fineweb_val_*.bin"
+    val_tokens: int = 10485760
+    num_iterations: int = 1770
+    cooldown_frac: float = 0.4
+    val_loss_every: int = 125
+    seq_len: int = 48 * 1024
+    val_seq_len: int = 4 * 64 * 1024
+    save_checkpoint: bool = False
+    head_lr: float = 0.008
+    embed_lr: float = 0.6
+    scalar_lr: float = 0.04
+    muon_lr: float = 0.05
+    muon_momentum: float = 0.95
+    muon_momentum_warmup_steps: int = 300
+
+
+def get_lr(step: int, hp: Hyperparameters) -> float:
+    t = 1 - step / hp.num_iterations
+    w = min(max(t, 0.0) / hp.cooldown_frac, 1.0)
+    return w * 1.0 + (1 - w) * 0.1
+
+
+def window_blocks(step: int, hp: Hyperparameters) -> int:
+    """Sliding window (in 128-token blocks) at ``step``: 128 -> 1792 tokens, linear over the run."""
+    return next_multiple_of_n(1728 * step / hp.num_iterations, n=128) // 128
+
+
+class GPTTrainer:
+    """Owns model, optimizers and (optionally) the process group; ``train_step`` runs one optimizer step."""
+
+    def __init__(self, config: GPTConfig | None = None, hp: Hyperparameters | None = None, device="cuda",
+                 rank: int = 0, world_size: int = 1, seed: int = 0, grad_sync: str = "auto"):
+        self.hp = hp or Hyperparameters()
+        self.config = config or GPTConfig(max_seq_len=max(self.hp.seq_len, 65536))
+        self.rank, self.world_size = rank, world_size
+        self.device = torch.device(device)
+        torch.manual_seed(seed)
+        model = GPT(config=self.config).to(self.device)
+        model.cast_embeddings_bf16()
+        self.model = model
+        if world_size > 1:
+            for p in model.parameters():
+                dist.broadcast(p.detach(), 0)
+        hidden, embed, scalar, head = model.param_groups()
+        hp_ = self.hp
+        adam_groups = [dict(params=head, lr=hp_.head_lr), dict(params=embed, lr=hp_.embed_lr),
+                       dict(params=scalar, lr=hp_.scalar_lr)]
+        self.optimizer1 = FusedAdam(adam_groups, betas=(0.8, 0.95), eps=1e-10)
+        self.grad_sync = grad_sync
+        self.comm = None
+        if world_size > 1 and grad_sync in ("auto", "fused") and self.device.type == "cuda":
+            from ..parallel.muon_dist import DistMuon, GradSync
+
+            self.comm = GradSync(model, hidden, rank, world_size)
+            self.optimizer2 = DistMuon(hidden, self.comm, lr=hp_.muon_lr, momentum=hp_.muon_momentum)
+        else:
+            self.optimizer2 = Muon(hidden, lr=hp_.muon_lr, momentum=hp_.muon_momentum, rank=rank, world_size=world_size)
+        self.optimizers = [self.optimizer1, self.optimizer2]
+        for opt in self.optimizers:
+            for g in opt.param_groups:
+                g["initial_lr"] = g["lr"]
+        self.step = 0
+
+    # ------------------------------------------------------------------------------------------
+    def _sync_grads(self):
+        if self.world_size == 1:
+            return
+        if self.comm is not None:
+            self.comm.sync_non_muon_grads()
+            return
+        for p in self.model.parameters():
+            if p.grad is not None:
+                dist.all_reduce(p.grad, op=dist.ReduceOp.AVG)
+
+    def train_step(self, inputs: torch.Tensor, targets: torch.Tensor, window: int | None = None) -> torch.Tensor:
+        """One optimizer step on a flat token sequence. Host tensors are copied to the device (non-blocking)."""
+        hp = self.hp
+        if inputs.device != self.device:
+            inputs = inputs.to(self.device, non_blocking=True)
+            targets = targets.to(self.device, non_blocking=True)
+        if targets.dtype != torch.int64:
+            targets = targets.to(torch.int64)
+        w = window_blocks(self.step, hp) if window is None else window
+        loss = self.model(inputs, targets, w)
+        loss.backward()
+        self._sync_grads()
+        frac = min(self.step / hp.muon_momentum_warmup_steps, 1)
+        for g in self.optimizer2.param_groups:
+            g["momentum"] = (1 - frac) * 0.85 + frac * 0.95
+        lr_mul = get_lr(min(self.step, hp.num_iterations), hp)
+        for opt in self.optimizers:
+            for g in opt.param_groups:
+                g["lr"] = g["initial_lr"] * lr_mul
+            opt.step()
+        self.model.zero_grad(set_to_none=True)
+        self.step += 1
+        return loss.detach()
+
+    @torch.no_grad()
+    def eval_loss(self, inputs: torch.Tensor, targets: torch.Tensor, window: int) -> torch.Tensor:
+        self.model.eval()
+        loss = self.model(inputs.to(self.device), targets.to(self.device).long(), window)
+        self.model.train()
+        if self.world_size > 1:
+            dist.all_reduce(loss, op=dist.ReduceOp.AVG)
+        return loss
+
+    def state_dict(self):
+        return dict(step=self.step, model=self.model.state_dict(),
+                    optimizers=[opt.state_dict() for opt in self.optimizers])
+
+    def load_state_dict(self, sd):
+        self.step = sd["step"]
+        self.model.load_state_dict(sd["model"])
+        for opt, s in zip(self.optimizers, sd["optimizers"]):
+            opt.load_state_dict(s)
+
+
+def synthetic_batch(seq_len: int, vocab: int = 50257, doc_len: int = 1024, seed: int = 0, pin: bool = True):
+    """Uniform random token ids with a BOS token every ``doc_len`` positions (host tensors, optionally pinned)."""
+    g = torch.Generator().manual_seed(seed)
+    toks = torch.randint(0, vocab, (seq_len + 1,), generator=g, dtype=torch.int32)
+    toks[:-1][::doc_len] = 50256
+    inputs = toks[:-1].clone()
+    targets = toks[1:].to(torch.int64)
+    if pin and torch.cuda.is_available():
+        inputs, targets = inputs.pin_memory(), targets.pin_memory()
+    return inputs, targets
+
+
+def init_distributed():
+    """Reads the torchrun environment; returns ``(rank, local_rank, world_size)`` after creating the NCCL group."""
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    if world > 1 and not dist.is_initialized():
+        torch.cuda.set_device(local)
+        dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local))
+    return rank, local, world

@@ -1,0 +1,70 @@
+"""Fused GPT step (loss and every parameter gradient) against the plain PyTorch path of the same module."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _model(fp8):
+    from ml_experiments_b200.models.gpt import GPT, GPTConfig
+
+    torch.manual_seed(0)
+    cfg = GPTConfig(vocab_size=50257, num_layers=4, num_heads=2, model_dim=256, head_dim=128, max_seq_len=2048,
+                    skip_attn_layers=(2,), num_value_embeds=1, use_fp8_head=fp8)
+    m = GPT(config=cfg).cuda().cast_embeddings_bf16()
+    # non-trivial values for the zero-initialised / identity parameters so every gradient path is exercised
+    with torch.no_grad():
+        for blk in m.blocks:
+            blk.lambdas.copy_(torch.tensor([0.9, 0.2]))
+            blk.mlp.c_proj.weight.normal_(0, 0.02)
+            if blk.attn is not None:
+                blk.attn.c_proj.weight.normal_(0, 0.02)
+                blk.attn.lambdas.copy_(torch.tensor([0.6, 0.4]))
+        m.lm_head.weight.normal_(0, 0.02)
+        m.skip_weights.copy_(torch.tensor([0.8, 1.1]))
+    return m
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+def test_fused_matches_reference(fp8):
+    m = _model(fp8)
+    t = 2048
+    x = torch.randint(0, 50257, (t,), device="cuda")
+    x[::512] = 50256
+    y = torch.randint(0, 50257, (t,), device="cuda")
+    m.fused = False
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        loss_ref = m(x, y, 2)
+    loss_ref.backward()
+    ref = {n: p.grad.float().clone() for n, p in m.named_parameters()}
+    m.zero_grad(set_to_none=True)
+    m.fused = True
+    loss = m(x, y, 2)
+    loss.backward()
+    assert abs(loss.item() - loss_ref.item()) < 2e-2 * abs(loss_ref.item())
+    tol = 0.12 if fp8 else 0.06
+    for n, p in m.named_parameters():
+        assert p.grad is not None, n
+        assert p.grad.dtype == p.dtype and p.grad.shape == p.shape, n
+        g, r = p.grad.float(), ref[n]
+        rel = ((g - r).norm() / (r.norm() + 1e-12)).item()
+        assert rel < tol, (n, rel, r.norm().item())
+
+
+def test_muon_fused_matches_torch():
+    from ml_experiments_b200.optim import Muon
+
+    torch.manual_seed(1)
+    shapes = [(3, 256, 256), (256, 256), (1024, 256), (256, 1024)]
+    ps = [torch.randn(s, device="cuda").requires_grad_(True) for s in shapes]
+    qs = [p.detach().cpu().clone().requires_grad_(True) for p in ps]
+    oa, ob = Muon(ps, lr=0.05, momentum=0.95), Muon(qs, lr=0.05, momentum=0.95)
+    for _ in range(2):
+        for p, q in zip(ps, qs):
+            g = torch.randn_like(p)
+            p.grad, q.grad = g, g.cpu()
+        oa.step(); ob.step()
+    for p, q in zip(ps, qs):
+        delta = (p.detach().cpu() - q.detach()).norm() / (q.detach() - q.detach().round()).norm().clamp_min(1e-3)
+        upd_err = (p.detach().cpu() - q.detach()).abs().max().item()
+        assert upd_err < 2e-2, upd_err
