@@ -48,6 +48,9 @@ __device__ __forceinline__ void cta_wait(uint64_t* bar, uint32_t parity, volatil
 // ------------------------------------------------------------------------------------------------
 // forward
 // ------------------------------------------------------------------------------------------------
+// The output accumulator stays in tensor memory across key tiles (PV MMAs accumulate in place). The running
+// maximum is only raised when a tile exceeds it by more than 2^8, so the TMEM read-scale-write of the accumulator
+// is rare; probabilities are then at most 2^8, well inside bf16 / fp32 range.
 template <int D>
 __global__ void __launch_bounds__(128, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -68,12 +71,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint8_t* sP = sV + 2 * KV_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES);
   uint64_t* bar_q = bars;
-  uint64_t* bar_kv = bars + 1;  // [2]
-  uint64_t* bar_s = bars + 3;
-  uint64_t* bar_o = bars + 4;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+  uint64_t* bar_k = bars + 1;  // [2]
+  uint64_t* bar_v = bars + 3;  // [2]
+  uint64_t* bar_s = bars + 5;
+  uint64_t* bar_o = bars + 6;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+  if (status_poisoned(p.status)) return;
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int qb = gridDim.x - 1 - blockIdx.x;  // late (long-context) tiles first
@@ -84,8 +89,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   if (tid == 0) {
     mbar_init(bar_q, 1);
-    mbar_init(&bar_kv[0], 1);
-    mbar_init(&bar_kv[1], 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&bar_k[i], 1); mbar_init(&bar_v[i], 1); }
     mbar_init(bar_s, 1);
     mbar_init(bar_o, 1);
     *abort_flag = 0;
@@ -102,6 +106,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t lane_off = uint32_t(warp * 32) << 16;
 
   const int ds = row_ok ? p.doc_start[q] : q;
+  const int ds_last = p.doc_start[min(q0 + BQ, p.T) - 1];
   int kv_lo = p.doc_start[q0] & ~(BKV - 1);
   if (p.window_blocks > 0) kv_lo = max(kv_lo, (qb - p.window_blocks + 1) * 128);
   kv_lo = max(kv_lo, 0);
@@ -111,49 +116,52 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t idesc_s = make_idesc(FMT_BF16, FMT_BF16, 0, 0, 128, BKV);
   const uint32_t idesc_o = make_idesc(FMT_BF16, FMT_BF16, 0, 1, 128, D);
 
+  auto load_k = [&](int j) {
+    const int b = j & 1;
+    mbar_arrive_expect_tx(&bar_k[b], KV_BYTES);
+    for (int s = 0; s < NS; ++s) tma_load_3d(sK + b * KV_BYTES + s * BKV * 128, &tmK, &bar_k[b], s * 64, kv_lo + j * BKV, h);
+  };
+  auto load_v = [&](int j) {
+    const int b = j & 1;
+    mbar_arrive_expect_tx(&bar_v[b], KV_BYTES);
+    for (int s = 0; s < NS; ++s) tma_load_3d(sV + b * KV_BYTES + s * BKV * 128, &tmV, &bar_v[b], s * 64, kv_lo + j * BKV, h);
+  };
+  auto issue_s = [&](int j) {
+    const int b = j & 1;
+    cta_wait(&bar_k[b], (j >> 1) & 1, abort_flag, p.status, ERR_WAIT_SMEM_FULL);
+    tc_fence_after_sync();
+    const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + b * KV_BYTES);
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      const uint64_t ad = make_smem_desc_sw128(qa + (ks / 4) * (BQ * 128) + (ks % 4) * 32, 16, 1024);
+      const uint64_t bd = make_smem_desc_sw128(ka + (ks / 4) * (BKV * 128) + (ks % 4) * 32, 16, 1024);
+      tc_mma_f16(tmem_base + S_COL, ad, bd, idesc_s, ks != 0);
+    }
+    tc_commit(bar_s);
+  };
+
   if (tid == 0) {
     mbar_arrive_expect_tx(bar_q, Q_BYTES);
     for (int s = 0; s < NS; ++s) tma_load_3d(sQ + s * BQ * 128, &tmQ, bar_q, s * 64, q0, h);
-    mbar_arrive_expect_tx(&bar_kv[0], 2 * KV_BYTES);
-    for (int s = 0; s < NS; ++s) {
-      tma_load_3d(sK + s * BKV * 128, &tmK, &bar_kv[0], s * 64, kv_lo, h);
-      tma_load_3d(sV + s * BKV * 128, &tmV, &bar_kv[0], s * 64, kv_lo, h);
-    }
+    load_k(0);
+    load_v(0);
+    if (nblk > 1) load_k(1);
+    cta_wait(bar_q, 0, abort_flag, p.status, ERR_WAIT_SMEM_FULL);
+    issue_s(0);
   }
+  __syncwarp();
 
-  float o[D];
-#pragma unroll
-  for (int i = 0; i < D; ++i) o[i] = 0.f;
-  float m = -INFINITY, l = 0.f;
+  float m_run = -INFINITY, l = 0.f;
 
   for (int jb = 0; jb < nblk; ++jb) {
     const int buf = jb & 1;
     const int kvb = kv_lo + jb * BKV;
-    if (tid == 0) {
-      if (jb + 1 < nblk) {  // prefetch the next key/value tile (its buffer was released by bar_o of block jb-1)
-        const int nb = buf ^ 1;
-        mbar_arrive_expect_tx(&bar_kv[nb], 2 * KV_BYTES);
-        for (int s = 0; s < NS; ++s) {
-          tma_load_3d(sK + nb * KV_BYTES + s * BKV * 128, &tmK, &bar_kv[nb], s * 64, kvb + BKV, h);
-          tma_load_3d(sV + nb * KV_BYTES + s * BKV * 128, &tmV, &bar_kv[nb], s * 64, kvb + BKV, h);
-        }
-      }
-      if (jb == 0) cta_wait(bar_q, 0, abort_flag, p.status, ERR_WAIT_SMEM_FULL);
-      cta_wait(&bar_kv[buf], (jb >> 1) & 1, abort_flag, p.status, ERR_WAIT_SMEM_FULL);
-      tc_fence_after_sync();
-      const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + buf * KV_BYTES);
-#pragma unroll
-      for (int ks = 0; ks < D / 16; ++ks) {
-        const uint64_t ad = make_smem_desc_sw128(qa + (ks / 4) * (BQ * 128) + (ks % 4) * 32, 16, 1024);
-        const uint64_t bd = make_smem_desc_sw128(ka + (ks / 4) * (BKV * 128) + (ks % 4) * 32, 16, 1024);
-        tc_mma_f16(tmem_base + S_COL, ad, bd, idesc_s, ks != 0);
-      }
-      tc_commit(bar_s);
-    }
-    __syncwarp();
-    cta_wait(bar_s, jb & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
+    cta_wait(bar_s, jb & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL);  // S(jb) done => PV(jb-1) done as well
     tc_fence_after_sync();
+    if (tid == 0 && jb + 1 < nblk) load_v(jb + 1);
+    __syncwarp();
 
+    const bool need_mask = (kvb + BKV - 1 > q0) || (kvb < ds_last);
     float sc[BKV];
     float mblk = -INFINITY;
 #pragma unroll
@@ -161,17 +169,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       uint32_t v[32];
       tmem_ld_32x32b_x32(tmem_base + lane_off + S_COL + c * 32, v);
       tmem_ld_wait();
+      if (need_mask) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const int kv = kvb + c * 32 + i;
-        const float s = (kv >= ds && kv <= q) ? __uint_as_float(v[i]) * p.sl2 : -INFINITY;
-        sc[c * 32 + i] = s;
-        mblk = fmaxf(mblk, s);
+        for (int i = 0; i < 32; ++i) {
+          const int kv = kvb + c * 32 + i;
+          const float s = (kv >= ds && kv <= q) ? __uint_as_float(v[i]) * p.sl2 : -INFINITY;
+          sc[c * 32 + i] = s;
+          mblk = fmaxf(mblk, s);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float s = __uint_as_float(v[i]) * p.sl2;
+          sc[c * 32 + i] = s;
+          mblk = fmaxf(mblk, s);
+        }
       }
     }
-    const float m_new = fmaxf(m, mblk);
-    const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-    const float alpha = exp2f(m - m_use);
+    float alpha = 1.f;
+    bool rescale = false;
+    if (mblk > m_run + 8.f) {
+      alpha = exp2f(m_run - mblk);  // m_run == -inf gives 0
+      m_run = mblk;
+      rescale = jb > 0;
+    }
+    const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
     float lsum = 0.f;
     uint8_t* prow = sP + tid * 128;
 #pragma unroll
@@ -187,47 +209,64 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       *reinterpret_cast<uint4*>(prow + ((j ^ (tid & 7)) << 4)) = u;
     }
     l = l * alpha + lsum;
-    m = m_new;
+    if (__any_sync(0xffffffffu, rescale)) {  // rare: bring this warp's accumulator rows to the new maximum
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem_base + lane_off + O_COL + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+        tmem_st_32x32b_x32(tmem_base + lane_off + O_COL + c * 32, v);
+      }
+      tmem_st_wait();
+    }
     fence_proxy_async_smem();
     tc_fence_before_sync();
     __syncthreads();
     if (tid == 0) {
+      tc_fence_after_sync();
+      cta_wait(&bar_v[buf], (jb >> 1) & 1, abort_flag, p.status, ERR_WAIT_SMEM_FULL);
       tc_fence_after_sync();
       const uint32_t pa = smem_u32(sP), va = smem_u32(sV + buf * KV_BYTES);
 #pragma unroll
       for (int ks = 0; ks < BKV / 16; ++ks) {
         const uint64_t ad = make_smem_desc_sw128(pa + ks * 32, 16, 1024);
         const uint64_t bd = make_smem_desc_sw128(va + ks * 2048, BKV * 128, 1024);
-        tc_mma_f16(tmem_base + O_COL, ad, bd, idesc_o, ks != 0);
+        tc_mma_f16(tmem_base + O_COL, ad, bd, idesc_o, (jb | ks) != 0);
       }
-      tc_commit(bar_o);
+      if (jb + 1 < nblk) {
+        issue_s(jb + 1);
+        if (jb + 2 < nblk) load_k(jb + 2);  // its buffer held K(jb), which S(jb) has finished reading
+      } else {
+        tc_commit(bar_o);
+      }
     }
     __syncwarp();
-#pragma unroll
-    for (int i = 0; i < D; ++i) o[i] *= alpha;
-    cta_wait(bar_o, jb & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
-    tc_fence_after_sync();
+  }
+
+  cta_wait(bar_o, 0, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
+  tc_fence_after_sync();
+  {
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    __nv_bfloat16* orow = p.o + (long long)q * p.ld_o + h * D;
 #pragma unroll
     for (int c = 0; c < D / 32; ++c) {
       uint32_t v[32];
       tmem_ld_32x32b_x32(tmem_base + lane_off + O_COL + c * 32, v);
       tmem_ld_wait();
+      if (row_ok) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) o[c * 32 + i] += __uint_as_float(v[i]);
+        for (int j = 0; j < 4; ++j) {
+          uint4 u = make_uint4(pack_bf16x2(__uint_as_float(v[8 * j]) * inv, __uint_as_float(v[8 * j + 1]) * inv),
+                               pack_bf16x2(__uint_as_float(v[8 * j + 2]) * inv, __uint_as_float(v[8 * j + 3]) * inv),
+                               pack_bf16x2(__uint_as_float(v[8 * j + 4]) * inv, __uint_as_float(v[8 * j + 5]) * inv),
+                               pack_bf16x2(__uint_as_float(v[8 * j + 6]) * inv, __uint_as_float(v[8 * j + 7]) * inv));
+          reinterpret_cast<uint4*>(orow + c * 32)[j] = u;
+        }
+      }
     }
-    tc_fence_before_sync();
-  }
-
-  if (row_ok) {
-    const float inv = l > 0.f ? 1.f / l : 0.f;
-    __nv_bfloat16* orow = p.o + (long long)q * p.ld_o + h * D;
-#pragma unroll
-    for (int j = 0; j < D / 8; ++j) {
-      uint4 u = make_uint4(pack_bf16x2(o[8 * j] * inv, o[8 * j + 1] * inv), pack_bf16x2(o[8 * j + 2] * inv, o[8 * j + 3] * inv),
-                           pack_bf16x2(o[8 * j + 4] * inv, o[8 * j + 5] * inv), pack_bf16x2(o[8 * j + 6] * inv, o[8 * j + 7] * inv));
-      reinterpret_cast<uint4*>(orow)[j] = u;
-    }
-    p.lse[(long long)h * p.T + q] = m + log2f(l);
+    if (row_ok) p.lse[(long long)h * p.T + q] = m_run + log2f(l);
   }
   if (*abort_flag && tid == 0) {  // let loads still in flight land before shared memory is released
     const uint64_t t0 = globaltimer_ns();
@@ -267,8 +306,9 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, long long
 // ------------------------------------------------------------------------------------------------
 // backward
 // ------------------------------------------------------------------------------------------------
+// 8 warps: warps w and w+4 share TMEM lane quarter (w & 3) and split the columns of every accumulator in halves.
 template <int D>
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(256, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                 const __grid_constant__ CUtensorMap tmdQ, const KP p) {
@@ -290,9 +330,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint8_t* sPT = sdO + 2 * Q_BYTES;
   uint8_t* sdST = sPT + PT_BYTES;
   float* sdQ = reinterpret_cast<float*>(sdST + PT_BYTES);
-  float* s_lse = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sdQ) + DQ_BYTES);  // [64]
-  float* s_delta = s_lse + BQ;
-  int* s_ds = reinterpret_cast<int*>(s_delta + BQ);
+  float2* s_ld = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(sdQ) + DQ_BYTES);  // [64] {lse, delta}
+  int* s_ds = reinterpret_cast<int*>(s_ld + BQ);                                          // [64]
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_ds + BQ);
   uint64_t* bar_kv = bars;
   uint64_t* bar_q = bars + 1;  // [2]
@@ -301,12 +340,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+  if (status_poisoned(p.status)) return;
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int quarter = warp & 3;
+  const int half = warp >> 2;
+  const int r = quarter * 32 + lane;  // accumulator row owned by this thread
   const int jb = blockIdx.x;
   const int h = blockIdx.y;
   const int kv0 = jb * BKV;
-  const int kv = kv0 + tid;
+  const int kv = kv0 + r;
 
   if (tid == 0) {
     mbar_init(bar_kv, 1);
@@ -325,7 +369,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t lane_off = uint32_t(warp * 32) << 16;
+  const uint32_t lane_off = uint32_t(quarter * 32) << 16;
 
   // query range that can see any key of this tile
   const int last_kv = min(kv0 + BKV, p.T) - 1;
@@ -360,8 +404,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (tid < BQ) {
       const int qq = qt0 + tid;
       const bool okq = qq < p.T;
-      s_lse[tid] = okq ? p.lse[(long long)h * p.T + qq] : INFINITY;
-      s_delta[tid] = okq ? p.delta[(long long)h * p.T + qq] : 0.f;
+      s_ld[tid] = make_float2(okq ? p.lse[(long long)h * p.T + qq] : INFINITY, okq ? p.delta[(long long)h * p.T + qq] : 0.f);
       s_ds[tid] = okq ? p.doc_start[qq] : 0x7fffffff;
     }
     if (tid == 0) {
@@ -392,36 +435,38 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       tc_commit(bar_m1);
     }
-    __syncthreads();  // s_lse / s_delta / s_ds visible; also orders the previous tile's staging reads
+    __syncthreads();  // s_ld / s_ds visible
     cta_wait(bar_m1, it & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
     tc_fence_after_sync();
 
-    uint8_t* prow = sPT + tid * 128;
-    uint8_t* drow = sdST + tid * 128;
-#pragma unroll
-    for (int c = 0; c < BQ / 32; ++c) {
+    // masks are needed only where the tile touches the causal diagonal, a document boundary or the sequence end
+    const bool need_mask = (qt0 < kv0 + BKV) || (s_ds[BQ - 1] > kv0) || (kv0 + BKV > p.T) || (qt0 + BQ > p.T);
+    {
       uint32_t sv[32], dv_[32];
-      tmem_ld_32x32b_x32(tmem_base + lane_off + ST_COL + c * 32, sv);
-      tmem_ld_32x32b_x32(tmem_base + lane_off + DPT_COL + c * 32, dv_);
+      tmem_ld_32x32b_x32(tmem_base + lane_off + ST_COL + half * 32, sv);
+      tmem_ld_32x32b_x32(tmem_base + lane_off + DPT_COL + half * 32, dv_);
       tmem_ld_wait();
-      float pr[32], dsv[32];
+      uint32_t pp[16], dd[16];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const int qi = c * 32 + i;
-        const int qq = qt0 + qi;
-        const bool valid = (qq >= kv) && (kv >= s_ds[qi]) && (kv < p.T);
-        const float pv = valid ? exp2f(__uint_as_float(sv[i]) * p.sl2 - s_lse[qi]) : 0.f;
-        pr[i] = pv;
-        dsv[i] = pv * (__uint_as_float(dv_[i]) - s_delta[qi]);
+      for (int i = 0; i < 32; i += 2) {
+        const int qi = half * 32 + i;
+        const float2 ld0 = s_ld[qi], ld1 = s_ld[qi + 1];
+        float p0 = exp2f(fmaf(__uint_as_float(sv[i]), p.sl2, -ld0.x));
+        float p1 = exp2f(fmaf(__uint_as_float(sv[i + 1]), p.sl2, -ld1.x));
+        if (need_mask) {
+          const int qq = qt0 + qi;
+          if (!((qq >= kv) && (kv >= s_ds[qi]) && (kv < p.T))) p0 = 0.f;
+          if (!((qq + 1 >= kv) && (kv >= s_ds[qi + 1]) && (kv < p.T))) p1 = 0.f;
+        }
+        pp[i >> 1] = pack_bf16x2(p0, p1);
+        dd[i >> 1] = pack_bf16x2(p0 * (__uint_as_float(dv_[i]) - ld0.y), p1 * (__uint_as_float(dv_[i + 1]) - ld1.y));
       }
+      uint8_t* prow = sPT + r * 128;
+      uint8_t* drow = sdST + r * 128;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        uint4 u = make_uint4(pack_bf16x2(pr[8 * j], pr[8 * j + 1]), pack_bf16x2(pr[8 * j + 2], pr[8 * j + 3]),
-                             pack_bf16x2(pr[8 * j + 4], pr[8 * j + 5]), pack_bf16x2(pr[8 * j + 6], pr[8 * j + 7]));
-        *reinterpret_cast<uint4*>(prow + (((c * 4 + j) ^ (tid & 7)) << 4)) = u;
-        uint4 w = make_uint4(pack_bf16x2(dsv[8 * j], dsv[8 * j + 1]), pack_bf16x2(dsv[8 * j + 2], dsv[8 * j + 3]),
-                             pack_bf16x2(dsv[8 * j + 4], dsv[8 * j + 5]), pack_bf16x2(dsv[8 * j + 6], dsv[8 * j + 7]));
-        *reinterpret_cast<uint4*>(drow + (((c * 4 + j) ^ (tid & 7)) << 4)) = w;
+        *reinterpret_cast<uint4*>(prow + (((half * 4 + j) ^ (r & 7)) << 4)) = make_uint4(pp[4 * j], pp[4 * j + 1], pp[4 * j + 2], pp[4 * j + 3]);
+        *reinterpret_cast<uint4*>(drow + (((half * 4 + j) ^ (r & 7)) << 4)) = make_uint4(dd[4 * j], dd[4 * j + 1], dd[4 * j + 2], dd[4 * j + 3]);
       }
     }
     fence_proxy_async_smem();
@@ -455,16 +500,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     __syncthreads();
     cta_wait(bar_m2, it & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
     tc_fence_after_sync();
-    // dQᵀ row (= head-dim index tid) -> staging[q][tid]
-    if (tid < D) {
+    // dQᵀ row (= head-dim index r), this warp's half of the query columns -> staging[q][r]
+    if (r < D) {
+      uint32_t v[32];
+      tmem_ld_32x32b_x32(tmem_base + lane_off + DQT_COL + half * 32, v);
+      tmem_ld_wait();
 #pragma unroll
-      for (int c = 0; c < BQ / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_base + lane_off + DQT_COL + c * 32, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) sdQ[(c * 32 + i) * D + tid] = __uint_as_float(v[i]) * p.scale;
-      }
+      for (int i = 0; i < 32; ++i) sdQ[(half * 32 + i) * D + r] = __uint_as_float(v[i]) * p.scale;
     }
     fence_proxy_async_smem();
     tc_fence_before_sync();
@@ -475,33 +517,37 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   }
 
-  // final: dV, dK rows
+  // final: dV, dK rows; each warp writes its half of the head dimension
   tc_fence_after_sync();
-  if (ntile > 0 && kv < p.T) {
-    __nv_bfloat16* dvrow = p.dv + (long long)kv * p.ld_dv + h * D;
-    __nv_bfloat16* dkrow = p.dk + (long long)kv * p.ld_dk + h * D;
+  if (ntile > 0) {
+    __nv_bfloat16* dvrow = p.dv + (long long)kv * p.ld_dv + h * D + half * (D / 2);
+    __nv_bfloat16* dkrow = p.dk + (long long)kv * p.ld_dk + h * D + half * (D / 2);
 #pragma unroll
-    for (int c = 0; c < D / 32; ++c) {
+    for (int c = 0; c < D / 64; ++c) {
       uint32_t v[32];
-      tmem_ld_32x32b_x32(tmem_base + lane_off + DV_COL + c * 32, v);
+      tmem_ld_32x32b_x32(tmem_base + lane_off + DV_COL + half * (D / 2) + c * 32, v);
       tmem_ld_wait();
+      if (kv < p.T) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        uint4 u = make_uint4(pack_bf16x2(__uint_as_float(v[8 * j]), __uint_as_float(v[8 * j + 1])),
-                             pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3])),
-                             pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5])),
-                             pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7])));
-        reinterpret_cast<uint4*>(dvrow + c * 32)[j] = u;
+        for (int j = 0; j < 4; ++j) {
+          uint4 u = make_uint4(pack_bf16x2(__uint_as_float(v[8 * j]), __uint_as_float(v[8 * j + 1])),
+                               pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3])),
+                               pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5])),
+                               pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7])));
+          reinterpret_cast<uint4*>(dvrow + c * 32)[j] = u;
+        }
       }
-      tmem_ld_32x32b_x32(tmem_base + lane_off + DK_COL + c * 32, v);
+      tmem_ld_32x32b_x32(tmem_base + lane_off + DK_COL + half * (D / 2) + c * 32, v);
       tmem_ld_wait();
+      if (kv < p.T) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        uint4 u = make_uint4(pack_bf16x2(__uint_as_float(v[8 * j]) * p.scale, __uint_as_float(v[8 * j + 1]) * p.scale),
-                             pack_bf16x2(__uint_as_float(v[8 * j + 2]) * p.scale, __uint_as_float(v[8 * j + 3]) * p.scale),
-                             pack_bf16x2(__uint_as_float(v[8 * j + 4]) * p.scale, __uint_as_float(v[8 * j + 5]) * p.scale),
-                             pack_bf16x2(__uint_as_float(v[8 * j + 6]) * p.scale, __uint_as_float(v[8 * j + 7]) * p.scale));
-        reinterpret_cast<uint4*>(dkrow + c * 32)[j] = u;
+        for (int j = 0; j < 4; ++j) {
+          uint4 u = make_uint4(pack_bf16x2(__uint_as_float(v[8 * j]) * p.scale, __uint_as_float(v[8 * j + 1]) * p.scale),
+                               pack_bf16x2(__uint_as_float(v[8 * j + 2]) * p.scale, __uint_as_float(v[8 * j + 3]) * p.scale),
+                               pack_bf16x2(__uint_as_float(v[8 * j + 4]) * p.scale, __uint_as_float(v[8 * j + 5]) * p.scale),
+                               pack_bf16x2(__uint_as_float(v[8 * j + 6]) * p.scale, __uint_as_float(v[8 * j + 7]) * p.scale));
+          reinterpret_cast<uint4*>(dkrow + c * 32)[j] = u;
+        }
       }
     }
   }
@@ -559,7 +605,7 @@ template <int D>
 void fwd_impl(const AttnArgs& a) {
   constexpr int NS = D / 64;
   // no alignment slack: the dynamic shared-memory window is declared 1024-byte aligned, and two CTAs must fit per SM
-  const int smem = NS * 128 * 128 + 4 * NS * 64 * 128 + 128 * 128 + 64;
+  const int smem = NS * 128 * 128 + 4 * NS * 64 * 128 + 128 * 128 + 96;
   CUtensorMap tq = qkv_map(a.q, a.T, a.H, D, a.ld_q, 128);
   CUtensorMap tk = qkv_map(a.k, a.T, a.H, D, a.ld_k, 64);
   CUtensorMap tv = qkv_map(a.v, a.T, a.H, D, a.ld_v, 64);
@@ -585,7 +631,7 @@ void bwd_impl(const AttnArgs& a) {
   static bool cfg = false;
   if (!cfg) { set_smem(kern, smem); cfg = true; }
   dim3 grid((a.T + 127) / 128, a.H);
-  kern<<<grid, 128, smem, a.stream>>>(tq, tk, tv, tdo, tdq, make_kp(a));
+  kern<<<grid, 256, smem, a.stream>>>(tq, tk, tv, tdo, tdq, make_kp(a));
   check_launch("attn_bwd launch");
 }
 

@@ -14,7 +14,7 @@ namespace b200 {
 
 // Upper bound for any single in-kernel wait (nanoseconds of %globaltimer).
 #ifndef B200_WAIT_LIMIT_NS
-#define B200_WAIT_LIMIT_NS 2000000000ull
+#define B200_WAIT_LIMIT_NS 250000000ull
 #endif
 
 enum : int {
@@ -83,6 +83,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// True when an earlier wait anywhere on the device has expired and the status word has not been cleared by the
+// host yet; kernels test this first and return without doing any work.
+__device__ __forceinline__ bool status_poisoned(const int* status) {
+  return status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0;
+}
+
 // Bounded wait. Returns false (and records `code` in *status if it is still 0) on time-out.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
   for (int i = 0; i < 64; ++i)
@@ -91,6 +97,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
   for (;;) {
     for (int i = 0; i < 128; ++i)
       if (mbar_try_wait(bar, parity)) return true;
+    // another CTA (or an earlier kernel) already gave up: do not spend a full time-out per CTA
+    if (status && *reinterpret_cast<volatile int*>(status) != 0) return false;
     if (globaltimer_ns() - t0 > B200_WAIT_LIMIT_NS) {
       if (status) atomicCAS(status, 0, code);
       return false;

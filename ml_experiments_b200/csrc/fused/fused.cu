@@ -208,60 +208,69 @@ mix_bwd_kernel(const bf16* __restrict__ dmix, const bf16* __restrict__ x, const 
 }
 
 // ---------------------------------------------------------------------------------------------- QK-norm + RoPE + value mix
-// One warp per (token, slot) with slot in [0, 3H): q heads, k heads, v heads.
+// A (token, slot) row of D elements (slot in [0, 3H): q heads, k heads, v heads) is owned by D/16 adjacent lanes;
+// every lane holds 8 elements of the first half and the 8 partner elements of the second half (16-byte accesses).
+template <int LPR>
+__device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+  for (int s = LPR / 2; s > 0; s >>= 1) v += __shfl_xor_sync(0xffffffffu, v, s);
+  return v;
+}
+__device__ __forceinline__ void load8f(const float* p, float (&f)[8]) {
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+
 template <int D>
 __global__ void __launch_bounds__(256)
 qkv_post_fwd_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ ve, const float* __restrict__ lam,
                     const float* __restrict__ cs, const float* __restrict__ sn, bf16* __restrict__ out, int T, int H,
                     float eps) {
-  constexpr int E = D / 64;  // elements per lane per half
-  const long long gw = ((long long)blockIdx.x * 256 + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (gw >= (long long)T * 3 * H) return;
-  const int t = (int)(gw / (3 * H));
-  const int slot = (int)(gw % (3 * H));
-  const bf16* src = qkv + gw * D;
-  bf16* dst = out + gw * D;
-  float a[E], b[E];
-#pragma unroll
-  for (int e = 0; e < E; ++e) {
-    a[e] = __bfloat162float(src[lane * E + e]);
-    b[e] = __bfloat162float(src[D / 2 + lane * E + e]);
-  }
+  constexpr int LPR = D / 16;
+  const long long row = ((long long)blockIdx.x * 256 + threadIdx.x) / LPR;
+  const int sub = threadIdx.x % LPR;
+  const bool active = row < (long long)T * 3 * H;
+  const long long rr = active ? row : 0;
+  const int t = (int)(rr / (3 * H));
+  const int slot = (int)(rr % (3 * H));
+  const bf16* src = qkv + rr * D;
+  bf16* dst = out + rr * D;
+  float a[8], b[8];
+  load8(src + sub * 8, a);
+  load8(src + D / 2 + sub * 8, b);
   if (slot < 2 * H) {
     float ss = 0.f;
 #pragma unroll
-    for (int e = 0; e < E; ++e) ss += a[e] * a[e] + b[e] * b[e];
-    ss = warp_sum(ss);
+    for (int i = 0; i < 8; ++i) ss += a[i] * a[i] + b[i] * b[i];
+    ss = group_sum<LPR>(ss);
     const float r = rsqrtf(ss / D + eps);
+    float c[8], s8[8], y1[8], y2[8];
+    load8f(cs + (long long)t * (D / 2) + sub * 8, c);
+    load8f(sn + (long long)t * (D / 2) + sub * 8, s8);
 #pragma unroll
-    for (int e = 0; e < E; ++e) {
+    for (int i = 0; i < 8; ++i) {
       // the reference normalises in bf16, then rotates in fp32
-      const float x1 = __bfloat162float(__float2bfloat16_rn(a[e] * r));
-      const float x2 = __bfloat162float(__float2bfloat16_rn(b[e] * r));
-      const float c = cs[(long long)t * (D / 2) + lane * E + e], s = sn[(long long)t * (D / 2) + lane * E + e];
-      dst[lane * E + e] = __float2bfloat16_rn(x1 * c + x2 * s);
-      dst[D / 2 + lane * E + e] = __float2bfloat16_rn(-x1 * s + x2 * c);
+      const float x1 = __bfloat162float(__float2bfloat16_rn(a[i] * r));
+      const float x2 = __bfloat162float(__float2bfloat16_rn(b[i] * r));
+      y1[i] = x1 * c[i] + x2 * s8[i];
+      y2[i] = -x1 * s8[i] + x2 * c[i];
     }
+    if (active) { store8(dst + sub * 8, y1); store8(dst + D / 2 + sub * 8, y2); }
   } else {
     const float l0 = lam[0], l1 = lam[1];
     const int hv = slot - 2 * H;
     if (ve) {
       const bf16* vs = ve + ((long long)t * H + hv) * D;
+      float e1[8], e2[8];
+      load8(vs + sub * 8, e1);
+      load8(vs + D / 2 + sub * 8, e2);
 #pragma unroll
-      for (int e = 0; e < E; ++e) {
-        a[e] = l0 * a[e] + l1 * __bfloat162float(vs[lane * E + e]);
-        b[e] = l0 * b[e] + l1 * __bfloat162float(vs[D / 2 + lane * E + e]);
-      }
+      for (int i = 0; i < 8; ++i) { a[i] = l0 * a[i] + l1 * e1[i]; b[i] = l0 * b[i] + l1 * e2[i]; }
     } else {
 #pragma unroll
-      for (int e = 0; e < E; ++e) { a[e] *= l0; b[e] *= l0; }
+      for (int i = 0; i < 8; ++i) { a[i] *= l0; b[i] *= l0; }
     }
-#pragma unroll
-    for (int e = 0; e < E; ++e) {
-      dst[lane * E + e] = __float2bfloat16_rn(a[e]);
-      dst[D / 2 + lane * E + e] = __float2bfloat16_rn(b[e]);
-    }
+    if (active) { store8(dst + sub * 8, a); store8(dst + D / 2 + sub * 8, b); }
   }
 }
 
@@ -271,74 +280,72 @@ qkv_post_bwd_kernel(const float* __restrict__ dq, const bf16* __restrict__ dk, c
                     const bf16* __restrict__ qkv, const bf16* __restrict__ ve, const float* __restrict__ lam,
                     const float* __restrict__ cs, const float* __restrict__ sn, bf16* __restrict__ dqkv,
                     bf16* __restrict__ dve, float* __restrict__ dlam, int T, int H, float eps) {
-  constexpr int E = D / 64;
+  constexpr int LPR = D / 16;
   __shared__ float red[2][8];
-  const long long gw = ((long long)blockIdx.x * 256 + threadIdx.x) >> 5;
+  const long long row = ((long long)blockIdx.x * 256 + threadIdx.x) / LPR;
+  const int sub = threadIdx.x % LPR;
   const int lane = threadIdx.x & 31;
   const int wib = threadIdx.x >> 5;
+  const bool active = row < (long long)T * 3 * H;
+  const long long rr = active ? row : 0;
+  const int t = (int)(rr / (3 * H));
+  const int slot = (int)(rr % (3 * H));
+  const bf16* src = qkv + rr * D;
+  bf16* dst = dqkv + rr * D;
   float s0 = 0.f, s1 = 0.f;
-  if (gw < (long long)T * 3 * H) {
-    const int t = (int)(gw / (3 * H));
-    const int slot = (int)(gw % (3 * H));
-    const bf16* src = qkv + gw * D;
-    bf16* dst = dqkv + gw * D;
-    float a[E], b[E], ga[E], gb[E];
+  float a[8], b[8], ga[8], gb[8];
+  load8(src + sub * 8, a);
+  load8(src + D / 2 + sub * 8, b);
+  if (slot < 2 * H) {
+    const int hh = slot < H ? slot : slot - H;
+    const long long g0 = ((long long)t * H + hh) * D;
+    float y1[8], y2[8], c[8], s8[8];
+    if (slot < H) { load8f(dq + g0 + sub * 8, y1); load8f(dq + g0 + D / 2 + sub * 8, y2); }
+    else { load8(dk + g0 + sub * 8, y1); load8(dk + g0 + D / 2 + sub * 8, y2); }
+    load8f(cs + (long long)t * (D / 2) + sub * 8, c);
+    load8f(sn + (long long)t * (D / 2) + sub * 8, s8);
+    float ss = 0.f, dot = 0.f;
 #pragma unroll
-    for (int e = 0; e < E; ++e) {
-      a[e] = __bfloat162float(src[lane * E + e]);
-      b[e] = __bfloat162float(src[D / 2 + lane * E + e]);
+    for (int i = 0; i < 8; ++i) {
+      ga[i] = y1[i] * c[i] - y2[i] * s8[i];  // transpose of the rotation
+      gb[i] = y1[i] * s8[i] + y2[i] * c[i];
+      ss += a[i] * a[i] + b[i] * b[i];
+      dot += a[i] * ga[i] + b[i] * gb[i];
     }
-    if (slot < 2 * H) {
-      const int hh = slot < H ? slot : slot - H;
-      const long long g0 = ((long long)t * H + hh) * D;
+    ss = group_sum<LPR>(ss);
+    dot = group_sum<LPR>(dot);
+    const float r = rsqrtf(ss / D + eps);
+    const float coef = dot * r * r * r / D;
 #pragma unroll
-      for (int e = 0; e < E; ++e) {
-        float y1, y2;
-        if (slot < H) { y1 = dq[g0 + lane * E + e]; y2 = dq[g0 + D / 2 + lane * E + e]; }
-        else { y1 = __bfloat162float(dk[g0 + lane * E + e]); y2 = __bfloat162float(dk[g0 + D / 2 + lane * E + e]); }
-        const float c = cs[(long long)t * (D / 2) + lane * E + e], s = sn[(long long)t * (D / 2) + lane * E + e];
-        ga[e] = y1 * c - y2 * s;  // transpose of the rotation
-        gb[e] = y1 * s + y2 * c;
-      }
-      float ss = 0.f, dot = 0.f;
+    for (int i = 0; i < 8; ++i) { ga[i] = r * ga[i] - a[i] * coef; gb[i] = r * gb[i] - b[i] * coef; }
+    if (active) { store8(dst + sub * 8, ga); store8(dst + D / 2 + sub * 8, gb); }
+  } else {
+    const int hv = slot - 2 * H;
+    const long long g0 = ((long long)t * H + hv) * D;
+    const float l0 = lam[0], l1 = lam[1];
+    load8(dv + g0 + sub * 8, ga);
+    load8(dv + g0 + D / 2 + sub * 8, gb);
+    float o1[8], o2[8];
 #pragma unroll
-      for (int e = 0; e < E; ++e) {
-        ss += a[e] * a[e] + b[e] * b[e];
-        dot += a[e] * ga[e] + b[e] * gb[e];
-      }
-      ss = warp_sum(ss);
-      dot = warp_sum(dot);
-      const float r = rsqrtf(ss / D + eps);
-      const float coef = dot * r * r * r / D;
-#pragma unroll
-      for (int e = 0; e < E; ++e) {
-        dst[lane * E + e] = __float2bfloat16_rn(r * ga[e] - a[e] * coef);
-        dst[D / 2 + lane * E + e] = __float2bfloat16_rn(r * gb[e] - b[e] * coef);
-      }
-    } else {
-      const int hv = slot - 2 * H;
-      const long long g0 = ((long long)t * H + hv) * D;
-      const float l0 = lam[0], l1 = lam[1];
-#pragma unroll
-      for (int e = 0; e < E; ++e) {
-        ga[e] = __bfloat162float(dv[g0 + lane * E + e]);
-        gb[e] = __bfloat162float(dv[g0 + D / 2 + lane * E + e]);
-        s0 += ga[e] * a[e] + gb[e] * b[e];
-        dst[lane * E + e] = __float2bfloat16_rn(l0 * ga[e]);
-        dst[D / 2 + lane * E + e] = __float2bfloat16_rn(l0 * gb[e]);
-      }
-      if (ve) {
-        const bf16* vs = ve + g0;
-#pragma unroll
-        for (int e = 0; e < E; ++e) {
-          s1 += ga[e] * __bfloat162float(vs[lane * E + e]) + gb[e] * __bfloat162float(vs[D / 2 + lane * E + e]);
-          if (dve) {
-            dve[g0 + lane * E + e] = __float2bfloat16_rn(l1 * ga[e]);
-            dve[g0 + D / 2 + lane * E + e] = __float2bfloat16_rn(l1 * gb[e]);
-          }
-        }
-      }
+    for (int i = 0; i < 8; ++i) {
+      s0 += ga[i] * a[i] + gb[i] * b[i];
+      o1[i] = l0 * ga[i];
+      o2[i] = l0 * gb[i];
     }
+    if (active) { store8(dst + sub * 8, o1); store8(dst + D / 2 + sub * 8, o2); }
+    if (ve) {
+      float e1[8], e2[8];
+      load8(ve + g0 + sub * 8, e1);
+      load8(ve + g0 + D / 2 + sub * 8, e2);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        s1 += ga[i] * e1[i] + gb[i] * e2[i];
+        o1[i] = l1 * ga[i];
+        o2[i] = l1 * gb[i];
+      }
+      if (dve && active) { store8(dve + g0 + sub * 8, o1); store8(dve + g0 + D / 2 + sub * 8, o2); }
+    }
+    if (!active) { s0 = 0.f; s1 = 0.f; }
   }
   s0 = warp_sum(s0);
   s1 = warp_sum(s1);
@@ -605,8 +612,9 @@ void mix_bwd(const void* dmix, const void* x, const void* x0, const void* skip, 
 
 void qkv_post_fwd(const void* qkv, const void* ve, const float* lam, const float* cos, const float* sin, void* out,
                   int T, int H, int D, float eps, cudaStream_t s) {
-  const long long warps = (long long)T * 3 * H;
-  const int blocks = (int)((warps + 7) / 8);
+  const long long rows = (long long)T * 3 * H;
+  const int rpb = 256 / (D / 16);
+  const int blocks = (int)((rows + rpb - 1) / rpb);
   if (D == 128) qkv_post_fwd_kernel<128><<<blocks, 256, 0, s>>>((const bf16*)qkv, (const bf16*)ve, lam, cos, sin, (bf16*)out, T, H, eps);
   else if (D == 64) qkv_post_fwd_kernel<64><<<blocks, 256, 0, s>>>((const bf16*)qkv, (const bf16*)ve, lam, cos, sin, (bf16*)out, T, H, eps);
   else throw std::runtime_error("qkv_post: head_dim must be 64 or 128");
@@ -616,8 +624,9 @@ void qkv_post_fwd(const void* qkv, const void* ve, const float* lam, const float
 void qkv_post_bwd(const float* dq, const void* dk, const void* dv, const void* qkv, const void* ve,
                   const float* lam, const float* cos, const float* sin, void* dqkv, void* dve, float* dlam, int T,
                   int H, int D, float eps, cudaStream_t s) {
-  const long long warps = (long long)T * 3 * H;
-  const int blocks = (int)((warps + 7) / 8);
+  const long long rows = (long long)T * 3 * H;
+  const int rpb = 256 / (D / 16);
+  const int blocks = (int)((rows + rpb - 1) / rpb);
   if (D == 128) qkv_post_bwd_kernel<128><<<blocks, 256, 0, s>>>(dq, (const bf16*)dk, (const bf16*)dv, (const bf16*)qkv, (const bf16*)ve, lam, cos, sin, (bf16*)dqkv, (bf16*)dve, dlam, T, H, eps);
   else if (D == 64) qkv_post_bwd_kernel<64><<<blocks, 256, 0, s>>>(dq, (const bf16*)dk, (const bf16*)dv, (const bf16*)qkv, (const bf16*)ve, lam, cos, sin, (bf16*)dqkv, (bf16*)dve, dlam, T, H, eps);
   else throw std::runtime_error("qkv_post: head_dim must be 64 or 128");

@@ -70,6 +70,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   uint64_t* tempty_bar = tfull_bar + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
 
+  if (status_poisoned(p.status)) return;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 

@@ -32,12 +32,13 @@ def test_fused_matches_reference(fp8):
     x = torch.randint(0, 50257, (t,), device="cuda")
     x[::512] = 50256
     y = torch.randint(0, 50257, (t,), device="cuda")
-    m.fused = False
-    with torch.autocast("cuda", dtype=torch.bfloat16):
-        loss_ref = m(x, y, 2)
+    import copy
+
+    oracle = copy.deepcopy(m).float()  # fp32 everywhere, plain autograd
+    oracle.fused = False
+    loss_ref = oracle(x, y, 2)
     loss_ref.backward()
-    ref = {n: p.grad.float().clone() for n, p in m.named_parameters()}
-    m.zero_grad(set_to_none=True)
+    ref = {n: p.grad.float().clone() for n, p in oracle.named_parameters()}
     m.fused = True
     loss = m(x, y, 2)
     loss.backward()
@@ -48,7 +49,8 @@ def test_fused_matches_reference(fp8):
         assert p.grad.dtype == p.dtype and p.grad.shape == p.shape, n
         g, r = p.grad.float(), ref[n]
         rel = ((g - r).norm() / (r.norm() + 1e-12)).item()
-        assert rel < tol, (n, rel, r.norm().item())
+        # scalar parameters have tiny gradients that are sums of bf16-rounded products: looser bound
+        assert rel < (3 * tol if p.ndim < 2 else tol), (n, rel, r.norm().item())
 
 
 def test_muon_fused_matches_torch():
