@@ -210,10 +210,14 @@ mix_bwd_kernel(const bf16* __restrict__ dmix, const bf16* __restrict__ x, const 
 // ---------------------------------------------------------------------------------------------- QK-norm + RoPE + value mix
 // A (token, slot) row of D elements (slot in [0, 3H): q heads, k heads, v heads) is owned by D/16 adjacent lanes;
 // every lane holds 8 elements of the first half and the 8 partner elements of the second half (16-byte accesses).
+// Sum over the LPR adjacent lanes that own one row. Rows of one warp may take different branches (q/k versus v
+// slots), so the shuffle names only the lanes of its own row group.
 template <int LPR>
 __device__ __forceinline__ float group_sum(float v) {
+  const unsigned lane = threadIdx.x & 31u;
+  const unsigned mask = (LPR == 32 ? 0xffffffffu : ((1u << LPR) - 1u)) << (lane & ~unsigned(LPR - 1));
 #pragma unroll
-  for (int s = LPR / 2; s > 0; s >>= 1) v += __shfl_xor_sync(0xffffffffu, v, s);
+  for (int s = LPR / 2; s > 0; s >>= 1) v += __shfl_xor_sync(mask, v, s);
   return v;
 }
 __device__ __forceinline__ void load8f(const float* p, float (&f)[8]) {

@@ -50,7 +50,10 @@ def test_fused_matches_reference(fp8):
         g, r = p.grad.float(), ref[n]
         rel = ((g - r).norm() / (r.norm() + 1e-12)).item()
         # scalar parameters have tiny gradients that are sums of bf16-rounded products: looser bound
-        assert rel < (3 * tol if p.ndim < 2 else tol), (n, rel, r.norm().item())
+        if p.ndim < 2:
+            assert (g - r).norm().item() <= max(3 * tol * r.norm().item(), 3e-4), (n, rel, r.norm().item())
+        else:
+            assert rel < tol, (n, rel, r.norm().item())
 
 
 def test_muon_fused_matches_torch():
