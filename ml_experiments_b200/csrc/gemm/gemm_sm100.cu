@@ -105,8 +105,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       bool ok = true;
       for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
         int r = t;
+        const int nt = r % p.tiles_n; r /= p.tiles_n;  // N fastest: concurrent CTAs share one A panel through L2
         const int mt = r % p.tiles_m; r /= p.tiles_m;
-        const int nt = r % p.tiles_n; r /= p.tiles_n;
         const int sp = r % p.splits;
         const int b = r / p.splits;
         const int m0 = mt * BM, n0 = nt * BN;
@@ -193,8 +193,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const int out_cols_per_buf = p.out_f32 ? 32 : 64;
     for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
       int r = t;
-      const int mt = r % p.tiles_m; r /= p.tiles_m;
       const int nt = r % p.tiles_n; r /= p.tiles_n;
+      const int mt = r % p.tiles_m; r /= p.tiles_m;
       const int b = r / p.splits;
       const int m0 = mt * BM, n0 = nt * BN;
       const int row = m0 + q * 32 + lane;
@@ -204,10 +204,33 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           p.aux ? p.aux + (long long)b * p.stride_aux + (long long)row * p.ld_aux : nullptr;
       int filled = 0;      // columns written into the current staging buffer
       int buf_col0 = n0;   // first output column of the current staging buffer
+      const bool use_aux = (p.epi == EPI_AXPBY || p.epi == EPI_RELU2_BWD);
+      const bool aux_vec = use_aux && row < p.M && ((p.ld_aux & 7) == 0);
+      uint4 aux_next[4];
+      auto fetch_aux = [&](int c) {  // 32 bf16 of this thread's row, columns n0+c .. n0+c+31
+        const int col = n0 + c;
+        if (aux_vec && col + 32 <= p.N) {
+          const uint4* src = reinterpret_cast<const uint4*>(aux_row + col);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) aux_next[i] = __ldg(src + i);
+        } else {
+          __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(aux_next);
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            e[i] = (row < p.M && col + i < p.N) ? aux_row[col + i] : __float2bfloat16(0.f);
+        }
+      };
+      if (use_aux) fetch_aux(0);
       for (int c = 0; c < BN; c += 32) {
         if (n0 + c >= p.N) break;
         uint32_t v[32];
         tmem_ld_32x32b_x32(tmem_base + (uint32_t(q * 32) << 16) + acc * BN + c, v);
+        uint4 aux_cur[4];
+        if (use_aux) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) aux_cur[i] = aux_next[i];
+          if (c + 32 < BN && n0 + c + 32 < p.N) fetch_aux(c + 32);  // in flight while this chunk is processed
+        }
         tmem_ld_wait();
         float f[32];
 #pragma unroll
@@ -215,22 +238,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (p.epi == EPI_RELU2) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) { float rr = fmaxf(f[i], 0.f); f[i] = rr * rr; }
-        } else if (p.epi == EPI_AXPBY || p.epi == EPI_RELU2_BWD) {
+        } else if (use_aux) {
           float a[32];
-          const int col = n0 + c;
-          if (row < p.M && col + 32 <= p.N && ((p.ld_aux & 7) == 0)) {
-            const uint4* src = reinterpret_cast<const uint4*>(aux_row + col);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              uint4 u = __ldg(src + i);
-              float2 x0 = unpack_bf16x2(u.x), x1 = unpack_bf16x2(u.y), x2 = unpack_bf16x2(u.z), x3 = unpack_bf16x2(u.w);
-              a[8 * i + 0] = x0.x; a[8 * i + 1] = x0.y; a[8 * i + 2] = x1.x; a[8 * i + 3] = x1.y;
-              a[8 * i + 4] = x2.x; a[8 * i + 5] = x2.y; a[8 * i + 6] = x3.x; a[8 * i + 7] = x3.y;
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              a[i] = (row < p.M && col + i < p.N) ? __bfloat162float(aux_row[col + i]) : 0.f;
+          for (int i = 0; i < 4; ++i) {
+            const uint4 u = aux_cur[i];
+            float2 x0 = unpack_bf16x2(u.x), x1 = unpack_bf16x2(u.y), x2 = unpack_bf16x2(u.z), x3 = unpack_bf16x2(u.w);
+            a[8 * i + 0] = x0.x; a[8 * i + 1] = x0.y; a[8 * i + 2] = x1.x; a[8 * i + 3] = x1.y;
+            a[8 * i + 4] = x2.x; a[8 * i + 5] = x2.y; a[8 * i + 6] = x3.x; a[8 * i + 7] = x3.y;
           }
           if (p.epi == EPI_AXPBY) {
 #pragma unroll
