@@ -1,0 +1,308 @@
+// Fused compute + collective kernels over peer memory: plain peer loads / stores through NVLink (no TMA, no
+// multicast), epoch flags with release / acquire at system scope, every spin bounded by a wall-clock limit.
+#include "comm.h"
+
+#include <cuda_bf16.h>
+
+#include <stdexcept>
+#include <string>
+
+#include "../common/ptx.cuh"
+
+namespace b200 {
+namespace {
+
+using bf16 = __nv_bfloat16;
+
+// A peer rank can lag by a whole step (data loading, host jitter): allow far more than an on-chip wait.
+constexpr unsigned long long kPeerWaitNs = 5000000000ull;
+
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.b32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.b32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// All threads of the block return once every rank's flag of `channel` has reached `epoch` (or the wait expired,
+// which is recorded in *status and reported through the return value).
+__device__ bool block_wait_flags(const int* flags, int world, int channel, int epoch, int* status) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+  if (threadIdx.x < world) {
+    const int* f = flags + channel * kMaxWorld + threadIdx.x;
+    if (ld_acquire_sys(f) < epoch) {
+      const uint64_t t0 = globaltimer_ns();
+      for (;;) {
+        if (ld_acquire_sys(f) >= epoch) break;
+        if (status_poisoned(status)) { s_fail = 1; break; }
+        if (globaltimer_ns() - t0 > kPeerWaitNs) {
+          if (status) atomicCAS(status, 0, ERR_WAIT_PEER_FLAG);
+          s_fail = 1;
+          break;
+        }
+        __nanosleep(200);
+      }
+    }
+  }
+  __syncthreads();
+  return s_fail == 0;
+}
+
+__global__ void signal_kernel(PeerPtrs peer_flags, int world, int rank, int channel, int epoch) {
+  if (threadIdx.x < world) {
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<int*>(peer_flags.p[threadIdx.x]) + channel * kMaxWorld + rank, epoch);
+  }
+}
+
+__global__ void wait_kernel(const int* flags, int world, int channel, int epoch, int* status) {
+  block_wait_flags(flags, world, channel, epoch, status);
+}
+
+// The last block to finish (device-scope counter after a system-scope fence) announces completion to every peer.
+__device__ void block_done_then_signal(int* counter, const PeerPtrs& peer_flags, int world, int rank, int channel,
+                                       int epoch) {
+  __shared__ int s_last;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int done = atomicAdd(counter, 1) + 1;
+    s_last = (done == (int)(gridDim.x * gridDim.y));
+    if (s_last) *counter = 0;
+  }
+  __syncthreads();
+  if (s_last && threadIdx.x < world) {
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<int*>(peer_flags.p[threadIdx.x]) + channel * kMaxWorld + rank, epoch);
+  }
+}
+
+// grid (blocks per matrix, nmat)
+__global__ void __launch_bounds__(256)
+rs_momentum_kernel(PeerPtrs grads, int world, long long elem_off, long long mat_elems, float* __restrict__ mom,
+                   bf16* __restrict__ u_out, float* __restrict__ sumsq, float mu, int nesterov, const int* flags,
+                   int channel, int epoch, int* status) {
+  __shared__ float red[8];
+  if (status_poisoned(status)) return;
+  if (!block_wait_flags(flags, world, channel, epoch, status)) return;
+  const int m = blockIdx.y;
+  const long long base = (long long)m * mat_elems;
+  const float inv_w = 1.f / world;
+  float acc = 0.f;
+  for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < mat_elems;
+       i += (long long)gridDim.x * blockDim.x * 4) {
+    float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < world; ++r) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[r]) + elem_off + base + i));
+      g.x += v.x; g.y += v.y; g.z += v.z; g.w += v.w;
+    }
+    float4 b = *reinterpret_cast<float4*>(mom + base + i);
+    float gi[4] = {g.x * inv_w, g.y * inv_w, g.z * inv_w, g.w * inv_w};
+    float bi[4] = {b.x, b.y, b.z, b.w};
+    float u[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      bi[k] = mu * bi[k] + (1.f - mu) * gi[k];
+      u[k] = nesterov ? (1.f - mu) * gi[k] + mu * bi[k] : bi[k];
+    }
+    *reinterpret_cast<float4*>(mom + base + i) = make_float4(bi[0], bi[1], bi[2], bi[3]);
+    __nv_bfloat162 lo = __floats2bfloat162_rn(u[0], u[1]), hi = __floats2bfloat162_rn(u[2], u[3]);
+    uint2 packed = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    *reinterpret_cast<uint2*>(u_out + base + i) = packed;
+    const float2 l2 = __bfloat1622float2(lo), h2 = __bfloat1622float2(hi);
+    acc += l2.x * l2.x + l2.y * l2.y + h2.x * h2.x + h2.y * h2.y;
+  }
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) t += red[i];
+    atomicAdd(&sumsq[m], t);
+  }
+}
+
+__global__ void stack_scale_kernel(bf16* __restrict__ x, const float* __restrict__ sumsq, long long mat_elems,
+                                   float eps) {
+  const int m = blockIdx.y;
+  const float s = 1.f / (sqrtf(sumsq[m]) + eps);
+  bf16* xm = x + (long long)m * mat_elems;
+  for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 2; i < mat_elems;
+       i += (long long)gridDim.x * blockDim.x * 2) {
+    float2 v = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(xm + i));
+    *reinterpret_cast<__nv_bfloat162*>(xm + i) = __floats2bfloat162_rn(v.x * s, v.y * s);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+ag_push_kernel(const bf16* __restrict__ src, PeerPtrs u_full, int world, int rank, long long dst_off, long long n,
+               PeerPtrs peer_flags, int channel, int epoch, int* counter) {
+  for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < n;
+       i += (long long)gridDim.x * blockDim.x * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(src + i);
+    for (int r = 0; r < world; ++r)
+      *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(u_full.p[r]) + dst_off + i) = v;
+  }
+  block_done_then_signal(counter, peer_flags, world, rank, channel, epoch);
+}
+
+__global__ void __launch_bounds__(256)
+ag_wait_apply_kernel(float* __restrict__ p, const bf16* __restrict__ u, bf16* __restrict__ p_bf16, long long n,
+                     float alpha, int world, const int* flags, int channel, int epoch, int* status) {
+  if (status_poisoned(status)) return;
+  if (!block_wait_flags(flags, world, channel, epoch, status)) return;
+  for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n;
+       i += (long long)gridDim.x * blockDim.x * 4) {
+    const uint2 raw = __ldcg(reinterpret_cast<const uint2*>(u + i));
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    float4 v = *reinterpret_cast<float4*>(p + i);
+    v.x = fmaf(alpha, a.x, v.x); v.y = fmaf(alpha, a.y, v.y); v.z = fmaf(alpha, b.x, v.z); v.w = fmaf(alpha, b.y, v.w);
+    *reinterpret_cast<float4*>(p + i) = v;
+    if (p_bf16) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+      *reinterpret_cast<uint2*>(p_bf16 + i) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    }
+  }
+}
+
+template <int DT>  // 0: fp32 (4 per thread-iteration), 1: bf16 (8 per thread-iteration)
+__global__ void __launch_bounds__(256)
+allreduce_kernel(PeerPtrs bufs, int world, int rank, long long lo, long long hi, const int* flags, PeerPtrs peer_flags,
+                 int channel, int epoch, int* status, int* counter) {
+  if (status_poisoned(status)) return;
+  const bool ok = block_wait_flags(flags, world, channel, epoch, status);
+  constexpr int VEC = DT == 0 ? 4 : 8;
+  const float inv_w = 1.f / world;
+  if (ok) {
+    for (long long i = lo + ((long long)blockIdx.x * blockDim.x + threadIdx.x) * VEC; i < hi;
+         i += (long long)gridDim.x * blockDim.x * VEC) {
+      if (DT == 0) {
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r = 0; r < world; ++r) {
+          const float4 v = __ldcg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(bufs.p[r]) + i));
+          a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+        }
+        a.x *= inv_w; a.y *= inv_w; a.z *= inv_w; a.w *= inv_w;
+        for (int r = 0; r < world; ++r) *reinterpret_cast<float4*>(reinterpret_cast<float*>(bufs.p[r]) + i) = a;
+      } else {
+        float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int r = 0; r < world; ++r) {
+          const uint4 v = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(bufs.p[r]) + i));
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float2 x = __bfloat1622float2(h[k]);
+            a[2 * k] += x.x;
+            a[2 * k + 1] += x.y;
+          }
+        }
+        uint4 o;
+        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) oh[k] = __floats2bfloat162_rn(a[2 * k] * inv_w, a[2 * k + 1] * inv_w);
+        for (int r = 0; r < world; ++r) *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(bufs.p[r]) + i) = o;
+      }
+    }
+  }
+  block_done_then_signal(counter, peer_flags, world, rank, channel + 1, epoch);
+}
+
+void check(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+int* device_counter() {
+  // one zero-initialised completion counter per device, shared by the kernels of this file (stream-ordered use)
+  static int* ctr[64] = {nullptr};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!ctr[dev]) {
+    cudaMalloc(&ctr[dev], 64 * sizeof(int));
+    cudaMemset(ctr[dev], 0, 64 * sizeof(int));
+  }
+  return ctr[dev];
+}
+
+}  // namespace
+
+void comm_signal(const PeerPtrs& peer_flags, int world, int rank, int channel, int epoch, cudaStream_t s) {
+  signal_kernel<<<1, 32, 0, s>>>(peer_flags, world, rank, channel, epoch);
+  check("comm_signal");
+}
+
+void comm_wait(const int* flags, int world, int channel, int epoch, int* status, cudaStream_t s) {
+  wait_kernel<<<1, 32, 0, s>>>(flags, world, channel, epoch, status);
+  check("comm_wait");
+}
+
+void muon_rs_momentum(const PeerPtrs& grads, int world, long long elem_off, int nmat, long long mat_elems, float* mom,
+                      void* u_out_bf16, float* sumsq, float mu, int nesterov, const int* flags, int channel, int epoch,
+                      int* status, cudaStream_t s) {
+  if (mat_elems % 4 != 0 || elem_off % 4 != 0) throw std::runtime_error("muon_rs_momentum: sizes must be multiples of 4");
+  if (nmat <= 0) return;
+  int bx = (int)((mat_elems / 4 + 255) / 256);
+  const int cap = (148 * 8 + nmat - 1) / nmat;
+  if (bx > cap) bx = cap;
+  if (bx < 1) bx = 1;
+  rs_momentum_kernel<<<dim3(bx, nmat), 256, 0, s>>>(grads, world, elem_off, mat_elems, mom, (bf16*)u_out_bf16, sumsq, mu,
+                                                     nesterov, flags, channel, epoch, status);
+  check("muon_rs_momentum");
+}
+
+void stack_scale_by_inv_norm(void* x_bf16, const float* sumsq, int nmat, long long mat_elems, float eps,
+                             cudaStream_t s) {
+  if (nmat <= 0) return;
+  int bx = (int)((mat_elems / 2 + 255) / 256);
+  const int cap = (148 * 8 + nmat - 1) / nmat;
+  if (bx > cap) bx = cap;
+  stack_scale_kernel<<<dim3(bx, nmat), 256, 0, s>>>((bf16*)x_bf16, sumsq, mat_elems, eps);
+  check("stack_scale_by_inv_norm");
+}
+
+void ag_push(const void* src_bf16, const PeerPtrs& u_full, int world, int rank, long long dst_off, long long n,
+             const PeerPtrs& peer_flags, int channel, int epoch, cudaStream_t s) {
+  if (n % 8 != 0 || dst_off % 8 != 0) throw std::runtime_error("ag_push: sizes must be multiples of 8");
+  int blocks = (int)((n / 8 + 255) / 256);
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  if (blocks < 1) blocks = 1;
+  ag_push_kernel<<<blocks, 256, 0, s>>>((const bf16*)src_bf16, u_full, world, rank, dst_off, n, peer_flags, channel, epoch,
+                                        device_counter());
+  check("ag_push");
+}
+
+void ag_wait_apply(float* p, const void* u_bf16, void* p_bf16, long long n, float alpha, int world, const int* flags,
+                   int channel, int epoch, int* status, cudaStream_t s) {
+  if (n % 4 != 0) throw std::runtime_error("ag_wait_apply: size must be a multiple of 4");
+  int blocks = (int)((n / 4 + 255) / 256);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks < 1) blocks = 1;
+  ag_wait_apply_kernel<<<blocks, 256, 0, s>>>(p, (const bf16*)u_bf16, (bf16*)p_bf16, n, alpha, world, flags, channel, epoch,
+                                              status);
+  check("ag_wait_apply");
+}
+
+void allreduce_mean(const PeerPtrs& bufs, int world, int rank, long long n, int dtype, const int* flags,
+                    const PeerPtrs& peer_flags, int channel, int epoch, int* status, cudaStream_t s) {
+  const int vec = dtype == 0 ? 4 : 8;
+  if (n % vec != 0) throw std::runtime_error("allreduce_mean: element count must be a multiple of the 16-byte vector");
+  const long long chunks = n / vec;
+  const long long lo = (chunks * rank / world) * vec, hi = (chunks * (rank + 1) / world) * vec;
+  int blocks = (int)(((hi - lo) / vec + 255) / 256);
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  if (blocks < 1) blocks = 1;
+  int* ctr = device_counter() + 1;
+  if (dtype == 0)
+    allreduce_kernel<0><<<blocks, 256, 0, s>>>(bufs, world, rank, lo, hi, flags, peer_flags, channel, epoch, status, ctr);
+  else
+    allreduce_kernel<1><<<blocks, 256, 0, s>>>(bufs, world, rank, lo, hi, flags, peer_flags, channel, epoch, status, ctr);
+  check("allreduce_mean");
+}
+
+}  // namespace b200

@@ -46,13 +46,13 @@ struct SmemLayout {
   static constexpr int kBBytes = BN * 128;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kBarOffset = STAGES * kStageBytes + kStagingBytes;
-  static constexpr int kTotal = kBarOffset + (2 * STAGES + 4) * 8 + 16 + 1024;  // + alignment slack
+  static constexpr int kTotal = kBarOffset + (2 * STAGES + 4 + 8) * 8 + 16 + 1024;  // + alignment slack
 };
 
 template <int BN, int STAGES, int AMN, int BMN, int ESZ>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-            const __grid_constant__ CUtensorMap tmC, const KParams p) {
+            const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmAux, const KParams p) {
   using L = SmemLayout<BN, STAGES>;
   constexpr int BK = 128 / ESZ;         // elements along K per stage (one 128-byte swizzle span)
   constexpr int UMMA_K = 32 / ESZ;      // elements along K per tcgen05.mma
@@ -68,7 +68,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* tfull_bar = empty_bar + STAGES;
   uint64_t* tempty_bar = tfull_bar + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  uint64_t* aux_bar = tempty_bar + 2;  // [4 epilogue warps][2 staging buffers]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux_bar + 8);
 
   if (status_poisoned(p.status)) return;
   const int warp = threadIdx.x >> 5;
@@ -83,10 +84,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       mbar_init(&tfull_bar[a], 1);
       mbar_init(&tempty_bar[a], 4);
     }
+    for (int a = 0; a < 8; ++a) mbar_init(&aux_bar[a], 1);
     fence_mbar_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
     tma_prefetch_desc(&tmC);
+    tma_prefetch_desc(&tmAux);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, TMEM_COLS);
@@ -191,6 +194,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     uint32_t acc_phase = 0;
     bool ok = true;
     const int out_cols_per_buf = p.out_f32 ? 32 : 64;
+    // bf16 output with an aux operand: the aux tile is brought by TMA into the (swizzled) staging buffer, combined in
+    // place by the thread that owns the row, and the same buffer is then stored - no uncoalesced per-row global loads.
+    const bool aux_tma = (p.epi == EPI_AXPBY || p.epi == EPI_RELU2_BWD) && !p.out_f32 && !p.reduce_add;
+    uint64_t* my_aux_bar = aux_bar + (warp - 2) * 2;
+    uint32_t aux_phase0 = 0, aux_phase1 = 0;
     for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
       int r = t;
       const int nt = r % p.tiles_n; r /= p.tiles_n;
@@ -200,6 +208,55 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const int row = m0 + q * 32 + lane;
       if (!mbar_wait(&tfull_bar[acc], acc_phase, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after_sync();
+      if (aux_tma) {
+        const int ngroups = min(BN / 64, (p.N - n0 + 63) / 64);
+        auto issue_aux = [&](int g, int bsel) {
+          if (lane == 0) {
+            tma_store_wait_read<0>();  // the store that last used this buffer has drained it
+            mbar_arrive_expect_tx(&my_aux_bar[bsel], 4096);
+            tma_load_3d(my_staging + bsel * 4096, &tmAux, &my_aux_bar[bsel], n0 + g * 64, m0 + q * 32, b);
+          }
+        };
+        issue_aux(0, buf);
+        for (int g = 0; g < ngroups && ok; ++g) {
+          if (g + 1 < ngroups) issue_aux(g + 1, buf ^ 1);
+          uint32_t v0[32], v1[32];
+          tmem_ld_32x32b_x32(tmem_base + (uint32_t(q * 32) << 16) + acc * BN + g * 64, v0);
+          tmem_ld_32x32b_x32(tmem_base + (uint32_t(q * 32) << 16) + acc * BN + g * 64 + 32, v1);
+          tmem_ld_wait();
+          const uint32_t ph = buf ? aux_phase1 : aux_phase0;
+          if (!mbar_wait(&my_aux_bar[buf], ph, p.status, ERR_WAIT_SMEM_FULL)) { ok = false; break; }
+          if (buf) aux_phase1 ^= 1; else aux_phase0 ^= 1;
+          uint8_t* rowp = my_staging + buf * 4096 + lane * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint4* cell = reinterpret_cast<uint4*>(rowp + ((j ^ (lane & 7)) << 4));
+            const uint4 u = *cell;
+            float a[8], f[8];
+            float2 x0 = unpack_bf16x2(u.x), x1 = unpack_bf16x2(u.y), x2 = unpack_bf16x2(u.z), x3 = unpack_bf16x2(u.w);
+            a[0] = x0.x; a[1] = x0.y; a[2] = x1.x; a[3] = x1.y; a[4] = x2.x; a[5] = x2.y; a[6] = x3.x; a[7] = x3.y;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float accv = __uint_as_float(j < 4 ? v0[8 * j + i] : v1[8 * (j - 4) + i]) * p.alpha;
+              f[i] = (p.epi == EPI_AXPBY) ? fmaf(p.beta, a[i], accv) : accv * 2.f * sqrtf(a[i]);
+            }
+            *cell = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_3d(&tmC, my_staging + buf * 4096, n0 + g * 64, m0 + q * 32, b);
+            tma_store_commit();
+          }
+          buf ^= 1;
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+        continue;
+      }
       const __nv_bfloat16* aux_row =
           p.aux ? p.aux + (long long)b * p.stride_aux + (long long)row * p.ld_aux : nullptr;
       int filled = 0;      // columns written into the current staging buffer
@@ -319,7 +376,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
 template <int BN, int STAGES, int AMN, int BMN, int ESZ>
 void launch(const GemmArgs& a, const KParams& kp, const CUtensorMap& tA, const CUtensorMap& tB,
-            const CUtensorMap& tC, int grid) {
+            const CUtensorMap& tC, const CUtensorMap& tX, int grid) {
   using L = SmemLayout<BN, STAGES>;
   auto kern = gemm_kernel<BN, STAGES, AMN, BMN, ESZ>;
   static bool configured = false;
@@ -328,18 +385,18 @@ void launch(const GemmArgs& a, const KParams& kp, const CUtensorMap& tA, const C
     if (e != cudaSuccess) throw std::runtime_error(std::string("gemm: cudaFuncSetAttribute: ") + cudaGetErrorString(e));
     configured = true;
   }
-  kern<<<grid, kThreads, L::kTotal, a.stream>>>(tA, tB, tC, kp);
+  kern<<<grid, kThreads, L::kTotal, a.stream>>>(tA, tB, tC, tX, kp);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) throw std::runtime_error(std::string("gemm launch: ") + cudaGetErrorString(e));
 }
 
 template <int BN, int STAGES, int ESZ>
 void dispatch_major(const GemmArgs& a, const KParams& kp, const CUtensorMap& tA, const CUtensorMap& tB,
-                    const CUtensorMap& tC, int grid) {
-  if (!a.a_mn && !a.b_mn) launch<BN, STAGES, 0, 0, ESZ>(a, kp, tA, tB, tC, grid);
-  else if (!a.a_mn && a.b_mn) launch<BN, STAGES, 0, 1, ESZ>(a, kp, tA, tB, tC, grid);
-  else if (a.a_mn && !a.b_mn) launch<BN, STAGES, 1, 0, ESZ>(a, kp, tA, tB, tC, grid);
-  else launch<BN, STAGES, 1, 1, ESZ>(a, kp, tA, tB, tC, grid);
+                    const CUtensorMap& tC, const CUtensorMap& tX, int grid) {
+  if (!a.a_mn && !a.b_mn) launch<BN, STAGES, 0, 0, ESZ>(a, kp, tA, tB, tC, tX, grid);
+  else if (!a.a_mn && a.b_mn) launch<BN, STAGES, 0, 1, ESZ>(a, kp, tA, tB, tC, tX, grid);
+  else if (a.a_mn && !a.b_mn) launch<BN, STAGES, 1, 0, ESZ>(a, kp, tA, tB, tC, tX, grid);
+  else launch<BN, STAGES, 1, 1, ESZ>(a, kp, tA, tB, tC, tX, grid);
 }
 
 int num_sms() {
@@ -383,6 +440,12 @@ void gemm_sm100(const GemmArgs& a) {
   tC = make_tmap_3d(a.C, a.c_dtype == GEMM_F32 ? TmapDtype::F32 : TmapDtype::BF16, a.N, a.M, nb, a.ldc * osz,
                     a.stride_c * osz, 128 / osz, 32, true);
 
+  CUtensorMap tX = tC;  // aux tile map (bf16 [batch][M][N]); only dereferenced by the aux epilogues
+  if (a.aux != nullptr && (a.ldaux % 8) == 0)
+    tX = make_tmap_3d(a.aux, TmapDtype::BF16, a.N, a.M, nb, a.ldaux * 2, a.stride_aux * 2, 64, 32, true);
+  else if (a.aux != nullptr)
+    throw std::runtime_error("gemm: aux row pitch must be a multiple of 8 elements");
+
   KParams kp;
   kp.M = a.M; kp.N = a.N; kp.K = a.K;
   kp.batch = a.batch; kp.splits = splits;
@@ -418,11 +481,11 @@ void gemm_sm100(const GemmArgs& a) {
   if (grid > kp.total_tiles) grid = kp.total_tiles;
 
   if (esz == 2) {
-    if (BN == 256) dispatch_major<256, 4, 2>(a, kp, tA, tB, tC, grid);
-    else           dispatch_major<128, 6, 2>(a, kp, tA, tB, tC, grid);
+    if (BN == 256) dispatch_major<256, 4, 2>(a, kp, tA, tB, tC, tX, grid);
+    else           dispatch_major<128, 6, 2>(a, kp, tA, tB, tC, tX, grid);
   } else {
-    if (BN == 256) dispatch_major<256, 4, 1>(a, kp, tA, tB, tC, grid);
-    else           dispatch_major<128, 6, 1>(a, kp, tA, tB, tC, grid);
+    if (BN == 256) dispatch_major<256, 4, 1>(a, kp, tA, tB, tC, tX, grid);
+    else           dispatch_major<128, 6, 1>(a, kp, tA, tB, tC, tX, grid);
   }
 }
 
