@@ -156,7 +156,7 @@ def run_ours(args, rank, local, world):
             "impl": "ours",
             "config": {"model": "modded-nanogpt GPT-2 124M (12L, d768, 6x128, vocab 50304, fp8 lm_head, Muon+Adam)",
                        "global_batch": SEQ_LEN * world, "seq_len": 1024, "tokens_per_rank_per_step": SEQ_LEN,
-                       "parallelism": f"dp{world}", "window_blocks": WINDOW_BLOCKS,
+                       "parallelism": f"dp{world}", "comm": trainer.comm_mode, "window_blocks": WINDOW_BLOCKS,
                        "l2": "inputs larger than L2: every step streams >20 GB of activations"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,

@@ -6,6 +6,7 @@
 #include <torch/types.h>
 
 #include "attn/attn.h"
+#include "comm/comm.h"
 #include "fused/fused.h"
 #include "gemm/gemm.h"
 
@@ -261,6 +262,69 @@ void axpy_bf16_to_f32(Tensor p, const Tensor& u, const c10::optional<Tensor>& p_
                          (float)alpha, cur_stream());
 }
 
+
+// ---------------------------------------------------------------------------------------------- peer-memory collectives
+b200::PeerPtrs to_peers(at::IntArrayRef ptrs) {
+  TORCH_CHECK(ptrs.size() >= 1 && (int)ptrs.size() <= b200::kMaxWorld, "peer pointer list: 1..", b200::kMaxWorld, " entries");
+  b200::PeerPtrs pp;
+  for (int i = 0; i < b200::kMaxWorld; ++i) pp.p[i] = nullptr;
+  for (size_t i = 0; i < ptrs.size(); ++i) pp.p[i] = reinterpret_cast<void*>(static_cast<uintptr_t>(ptrs[i]));
+  return pp;
+}
+
+void comm_signal(at::IntArrayRef peer_flags, int64_t rank, int64_t channel, int64_t epoch, const Tensor& like) {
+  const c10::cuda::CUDAGuard guard(like.device());
+  b200::comm_signal(to_peers(peer_flags), (int)peer_flags.size(), (int)rank, (int)channel, (int)epoch, cur_stream());
+}
+
+void comm_wait(const Tensor& flags, int64_t world, int64_t channel, int64_t epoch, Tensor status) {
+  const c10::cuda::CUDAGuard guard(flags.device());
+  b200::comm_wait(flags.data_ptr<int>(), (int)world, (int)channel, (int)epoch, status.data_ptr<int>(), cur_stream());
+}
+
+void muon_rs_momentum(at::IntArrayRef grad_ptrs, int64_t elem_off, int64_t nmat, int64_t mat_elems, Tensor mom,
+                      Tensor u_out, Tensor sumsq, double mu, bool nesterov, const Tensor& flags, int64_t channel,
+                      int64_t epoch, Tensor status) {
+  const c10::cuda::CUDAGuard guard(mom.device());
+  TORCH_CHECK(mom.scalar_type() == at::kFloat && mom.is_contiguous() && mom.numel() >= nmat * mat_elems, "mom: fp32 shard");
+  TORCH_CHECK(u_out.scalar_type() == at::kBFloat16 && u_out.is_contiguous() && u_out.numel() >= nmat * mat_elems, "u_out: bf16 shard");
+  TORCH_CHECK(sumsq.scalar_type() == at::kFloat && sumsq.numel() >= nmat, "sumsq: fp32 [nmat]");
+  b200::muon_rs_momentum(to_peers(grad_ptrs), (int)grad_ptrs.size(), elem_off, (int)nmat, mat_elems, mom.data_ptr<float>(),
+                         u_out.data_ptr(), sumsq.data_ptr<float>(), (float)mu, nesterov, flags.data_ptr<int>(), (int)channel,
+                         (int)epoch, status.data_ptr<int>(), cur_stream());
+}
+
+void stack_scale_by_inv_norm(Tensor x, const Tensor& sumsq, int64_t nmat, int64_t mat_elems, double eps) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  chk_bf16c(x, "x");
+  b200::stack_scale_by_inv_norm(x.data_ptr(), sumsq.data_ptr<float>(), (int)nmat, mat_elems, (float)eps, cur_stream());
+}
+
+void ag_push(const Tensor& src, at::IntArrayRef u_full_ptrs, int64_t rank, int64_t dst_off, at::IntArrayRef peer_flags,
+             int64_t channel, int64_t epoch) {
+  const c10::cuda::CUDAGuard guard(src.device());
+  chk_bf16c(src, "src");
+  b200::ag_push(src.data_ptr(), to_peers(u_full_ptrs), (int)u_full_ptrs.size(), (int)rank, dst_off, src.numel(),
+                to_peers(peer_flags), (int)channel, (int)epoch, cur_stream());
+}
+
+void ag_wait_apply(Tensor p, const Tensor& u, const c10::optional<Tensor>& p_bf16, double alpha, int64_t world,
+                   const Tensor& flags, int64_t channel, int64_t epoch, Tensor status) {
+  const c10::cuda::CUDAGuard guard(p.device());
+  TORCH_CHECK(p.scalar_type() == at::kFloat && p.is_contiguous() && u.scalar_type() == at::kBFloat16 && u.is_contiguous() &&
+              u.numel() >= p.numel(), "ag_wait_apply: p fp32, u bf16");
+  b200::ag_wait_apply(p.data_ptr<float>(), u.data_ptr(), p_bf16.has_value() ? p_bf16->data_ptr() : nullptr, p.numel(),
+                      (float)alpha, (int)world, flags.data_ptr<int>(), (int)channel, (int)epoch, status.data_ptr<int>(),
+                      cur_stream());
+}
+
+void allreduce_mean(at::IntArrayRef buf_ptrs, int64_t rank, int64_t n, int64_t dtype, const Tensor& flags,
+                    at::IntArrayRef peer_flags, int64_t channel, int64_t epoch, Tensor status) {
+  const c10::cuda::CUDAGuard guard(flags.device());
+  b200::allreduce_mean(to_peers(buf_ptrs), (int)buf_ptrs.size(), (int)rank, n, (int)dtype, flags.data_ptr<int>(),
+                       to_peers(peer_flags), (int)channel, (int)epoch, status.data_ptr<int>(), cur_stream());
+}
+
 }  // namespace
 
 TORCH_LIBRARY(b200, m) {
@@ -282,6 +346,13 @@ TORCH_LIBRARY(b200, m) {
   m.def("muon_momentum(Tensor g, Tensor(a!) buf, Tensor(b!) out, Tensor(c!) sumsq, float mu, bool nesterov, float grad_scale) -> ()");
   m.def("scale_by_inv_norm(Tensor(a!) x, Tensor sumsq, float eps) -> ()");
   m.def("axpy_bf16_to_f32(Tensor(a!) p, Tensor u, Tensor(b!)? p_bf16, float alpha) -> ()");
+  m.def("comm_signal(int[] peer_flags, int rank, int channel, int epoch, Tensor like) -> ()");
+  m.def("comm_wait(Tensor flags, int world, int channel, int epoch, Tensor(a!) status) -> ()");
+  m.def("muon_rs_momentum(int[] grad_ptrs, int elem_off, int nmat, int mat_elems, Tensor(a!) mom, Tensor(b!) u_out, Tensor(c!) sumsq, float mu, bool nesterov, Tensor flags, int channel, int epoch, Tensor(d!) status) -> ()");
+  m.def("stack_scale_by_inv_norm(Tensor(a!) x, Tensor sumsq, int nmat, int mat_elems, float eps) -> ()");
+  m.def("ag_push(Tensor src, int[] u_full_ptrs, int rank, int dst_off, int[] peer_flags, int channel, int epoch) -> ()");
+  m.def("ag_wait_apply(Tensor(a!) p, Tensor u, Tensor(b!)? p_bf16, float alpha, int world, Tensor flags, int channel, int epoch, Tensor(c!) status) -> ()");
+  m.def("allreduce_mean(int[] buf_ptrs, int rank, int n, int dtype, Tensor flags, int[] peer_flags, int channel, int epoch, Tensor(a!) status) -> ()");
   // <<DEFS>>
 }
 
@@ -302,5 +373,12 @@ TORCH_LIBRARY_IMPL(b200, CUDA, m) {
   m.impl("muon_momentum", &muon_momentum);
   m.impl("scale_by_inv_norm", &scale_by_inv_norm);
   m.impl("axpy_bf16_to_f32", &axpy_bf16_to_f32);
+  m.impl("comm_signal", &comm_signal);
+  m.impl("comm_wait", &comm_wait);
+  m.impl("muon_rs_momentum", &muon_rs_momentum);
+  m.impl("stack_scale_by_inv_norm", &stack_scale_by_inv_norm);
+  m.impl("ag_push", &ag_push);
+  m.impl("ag_wait_apply", &ag_wait_apply);
+  m.impl("allreduce_mean", &allreduce_mean);
   // <<IMPLS>>
 }

@@ -133,3 +133,205 @@ class DistMuon(torch.optim.Optimizer):
                 set_shadow(p, sh)
                 slot += nmat
         return None
+
+
+# ======================================================================================================================
+# Fused path: the same work split, with both collectives done by this package's kernels over peer memory
+# ======================================================================================================================
+CH_GRADS, CH_AG, CH_B16_IN, CH_B16_OUT, CH_F32_IN, CH_F32_OUT = 0, 1, 2, 3, 4, 5
+
+
+class MuonShardEngine:
+    """Banked Muon state of one rank plus the three phases of a fused step.
+
+    * ``publish_grads``   : gradients -> this rank's symmetric fp32 stack, then "ready" flag to every peer;
+    * ``reduce_ns_push``  : per shape group, one kernel reduce-scatters the owned slice straight out of the peers'
+      stacks into the momentum update / bf16 cast, Newton-Schulz runs on the slice, one kernel stores the
+      result into every peer's update buffer and raises the "pushed" flag;
+    * ``apply``           : waits for every rank's push, then ``p += alpha * U`` on the banked fp32 masters and
+      refreshes the banked bf16 copies in the same kernel.
+
+    Master weights and their bf16 copies live in per-shape banks; the ``nn.Parameter`` objects are views into them.
+    """
+
+    def __init__(self, params, world, alloc=None):
+        from ..utils.shadow import set_shadow as _set
+
+        self.w = world
+        self.params = [*params]
+        alloc = alloc or world.alloc
+        W = world.world
+        by_shape = defaultdict(list)
+        for p in self.params:
+            r, c = p.shape[-2], p.shape[-1]
+            by_shape[(r, c)].append((p, p.numel() // (r * c)))
+        self.groups = []
+        dev = self.params[0].device
+        for (r, c), plist in by_shape.items():
+            total = sum(n for _, n in plist)
+            padded = (total + W - 1) // W * W
+            per = padded // W
+            g = dict(r=r, c=c, plist=plist, total=total, per=per, padded=padded, mat=r * c)
+            g["g_full"] = alloc(padded * r * c, torch.float32)
+            g["u_full"] = alloc(padded * r * c, torch.bfloat16)
+            g["g_full"].local.zero_()
+            g["p_stack"] = torch.zeros(padded, r, c, dtype=torch.float32, device=dev)
+            slot = 0
+            with torch.no_grad():
+                for p, nmat in plist:
+                    view = g["p_stack"][slot:slot + nmat].view(p.shape)
+                    view.copy_(p.detach())
+                    p.data = view
+                    slot += nmat
+            g["sh_stack"] = g["p_stack"].to(torch.bfloat16)
+            slot = 0
+            for p, nmat in plist:
+                _set(p, g["sh_stack"][slot:slot + nmat].view(p.shape))
+                slot += nmat
+            g["mom"] = torch.zeros(per, r, c, dtype=torch.float32, device=dev)
+            g["u_shard"] = torch.empty(per, r, c, dtype=torch.bfloat16, device=dev)
+            g["sumsq"] = torch.zeros(per, dtype=torch.float32, device=dev)
+            self.groups.append(g)
+        self._work: dict = {}
+        self._step = 0
+
+    @torch.no_grad()
+    def publish_grads(self):
+        from ..ops.runtime import status
+
+        o = ops()
+        for g in self.groups:
+            views, srcs, slot = [], [], 0
+            flat = g["g_full"].local.view(g["padded"], g["r"], g["c"])
+            for p, nmat in g["plist"]:
+                if p.grad is not None:
+                    views.append(flat[slot:slot + nmat].view(p.shape))
+                    srcs.append(p.grad if p.grad.dtype == torch.float32 else p.grad.float())
+                slot += nmat
+            if views:
+                torch._foreach_copy_(views, srcs)
+        self._step += 1
+        o.comm_signal(self.w.flags.ptrs, self.w.rank, CH_GRADS, self._step, self.w.flags.local)
+        self._status = status(self.params[0].device)
+
+    @torch.no_grad()
+    def reduce_ns_push(self, mu: float, nesterov: bool, coeffs):
+        o = ops()
+        w = self.w
+        ng = len(self.groups)
+        for gi, g in enumerate(self.groups):
+            per, mat = g["per"], g["mat"]
+            g["sumsq"].zero_()
+            o.muon_rs_momentum(g["g_full"].ptrs, w.rank * per * mat, per, mat, g["mom"], g["u_shard"], g["sumsq"], mu,
+                               nesterov, w.flags.local, CH_GRADS, self._step, self._status)
+            o.stack_scale_by_inv_norm(g["u_shard"], g["sumsq"], per, mat, 1e-7)
+            u = newton_schulz_(g["u_shard"], coeffs, self._work)
+            o.ag_push(u.contiguous(), g["u_full"].ptrs, w.rank, w.rank * per * mat, w.flags.ptrs, CH_AG,
+                      (self._step - 1) * ng + gi + 1)
+
+    @torch.no_grad()
+    def apply(self, lr: float):
+        o = ops()
+        w = self.w
+        ng = len(self.groups)
+        for gi, g in enumerate(self.groups):
+            alpha = -lr * max(1.0, g["r"] / g["c"]) ** 0.5
+            o.ag_wait_apply(g["p_stack"], g["u_full"].local, g["sh_stack"], alpha, w.world, w.flags.local, CH_AG,
+                            (self._step - 1) * ng + gi + 1, self._status)
+            slot = 0
+            for p, nmat in g["plist"]:
+                set_shadow(p, g["sh_stack"][slot:slot + nmat].view(p.shape))
+                slot += nmat
+
+
+class FusedDistMuon(torch.optim.Optimizer):
+    """Muon whose reduce-scatter and all-gather are fused into its own kernels over NVLink peer memory."""
+
+    def __init__(self, params, world, lr: float = 0.02, momentum: float = 0.95, nesterov: bool = True, ns_steps: int = 5):
+        params = [*params]
+        super().__init__(params, dict(lr=lr, momentum=momentum, nesterov=nesterov, ns_steps=ns_steps))
+        self.engine = MuonShardEngine(params, world)
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        g = self.param_groups[0]
+        self.engine.publish_grads()
+        self.engine.reduce_ns_push(float(g["momentum"]), bool(g["nesterov"]), [NS5_COEFFS[0]] * g["ns_steps"])
+        self.engine.apply(float(g["lr"]))
+        return None
+
+
+class FusedGradSync:
+    """Mean all-reduce of the non-Muon gradients (embeddings, head, scalars) by the two-shot peer-memory kernel.
+
+    Gradients are packed into one bf16 and one fp32 symmetric bucket, reduced in place (each rank reduces 1/W of the
+    bucket out of all peers and stores the scaled result into every peer), and ``p.grad`` is re-pointed at the bucket
+    views, so nothing is copied back."""
+
+    def __init__(self, model, muon_params, world, alloc=None):
+        self.w = world
+        alloc = alloc or world.alloc
+        muon_ids = {id(p) for p in muon_params}
+        self.params = [p for p in model.parameters() if id(p) not in muon_ids]
+        self.p16 = [p for p in self.params if p.dtype == torch.bfloat16]
+        self.p32 = [p for p in self.params if p.dtype != torch.bfloat16]
+
+        def pad(n, m):
+            return (n + m - 1) // m * m
+
+        self.n16 = pad(sum(pad(p.numel(), 8) for p in self.p16), 8 * world.world) if self.p16 else 0
+        self.n32 = pad(sum(pad(p.numel(), 4) for p in self.p32), 4 * world.world) if self.p32 else 0
+        self.b16 = alloc(max(self.n16, 8), torch.bfloat16)
+        self.b32 = alloc(max(self.n32, 4), torch.float32)
+        self.b16.local.zero_()
+        self.b32.local.zero_()
+        self.views16, off = [], 0
+        for p in self.p16:
+            self.views16.append(self.b16.local[off:off + p.numel()].view(p.shape))
+            off += pad(p.numel(), 8)
+        self.views32, off = [], 0
+        for p in self.p32:
+            self.views32.append(self.b32.local[off:off + p.numel()].view(p.shape))
+            off += pad(p.numel(), 4)
+        self._step = 0
+
+    @torch.no_grad()
+    def publish(self):
+        from ..ops.runtime import status
+
+        o = ops()
+        for plist, views in ((self.p16, self.views16), (self.p32, self.views32)):
+            pairs = [(v, p.grad) for p, v in zip(plist, views) if p.grad is not None]
+            if pairs:
+                torch._foreach_copy_([a for a, _ in pairs], [b if b.dtype == a.dtype else b.to(a.dtype) for a, b in pairs])
+        self._step += 1
+        self._status = status(self.w.flags.local.device)
+        o.comm_signal(self.w.flags.ptrs, self.w.rank, CH_B16_IN, self._step, self.w.flags.local)
+        o.comm_signal(self.w.flags.ptrs, self.w.rank, CH_F32_IN, self._step, self.w.flags.local)
+
+    @torch.no_grad()
+    def reduce(self):
+        o = ops()
+        w = self.w
+        if self.n16:
+            o.allreduce_mean(self.b16.ptrs, w.rank, self.n16, 1, w.flags.local, w.flags.ptrs, CH_B16_IN, self._step, self._status)
+        if self.n32:
+            o.allreduce_mean(self.b32.ptrs, w.rank, self.n32, 0, w.flags.local, w.flags.ptrs, CH_F32_IN, self._step, self._status)
+
+    @torch.no_grad()
+    def finish(self):
+        o = ops()
+        w = self.w
+        if self.n16:
+            o.comm_wait(w.flags.local, w.world, CH_B16_OUT, self._step, self._status)
+        if self.n32:
+            o.comm_wait(w.flags.local, w.world, CH_F32_OUT, self._step, self._status)
+        for plist, views in ((self.p16, self.views16), (self.p32, self.views32)):
+            for p, v in zip(plist, views):
+                if p.grad is not None:
+                    p.grad = v
+
+    def sync_non_muon_grads(self):
+        self.publish()
+        self.reduce()
+        self.finish()

@@ -71,11 +71,28 @@ class GPTTrainer:
         self.optimizer1 = FusedAdam(adam_groups, betas=(0.8, 0.95), eps=1e-10)
         self.grad_sync = grad_sync
         self.comm = None
-        if world_size > 1 and grad_sync in ("auto", "fused") and self.device.type == "cuda":
-            from ..parallel.muon_dist import DistMuon, GradSync
+        self.comm_mode = "single"
+        if world_size > 1 and self.device.type == "cuda":
+            from ..parallel import muon_dist as md
 
-            self.comm = GradSync(model, hidden, rank, world_size)
-            self.optimizer2 = DistMuon(hidden, self.comm, lr=hp_.muon_lr, momentum=hp_.muon_momentum)
+            if grad_sync in ("auto", "fused"):
+                try:
+                    from ..parallel.symm import SymmWorld
+
+                    sw = SymmWorld.create(rank, world_size, self.device)
+                    self.comm = md.FusedGradSync(model, hidden, sw)
+                    self.optimizer2 = md.FusedDistMuon(hidden, sw, lr=hp_.muon_lr, momentum=hp_.muon_momentum)
+                    self.comm_mode = "fused-p2p"
+                except Exception as e:  # symmetric memory unavailable: NCCL plumbing with the same work split
+                    if grad_sync == "fused":
+                        raise
+                    if rank == 0:
+                        print(f"[gpt_trainer] fused peer-memory path unavailable ({type(e).__name__}: {e}); using NCCL")
+                    self.comm = None
+            if self.comm is None:
+                self.comm = md.GradSync(model, hidden, rank, world_size)
+                self.optimizer2 = md.DistMuon(hidden, self.comm, lr=hp_.muon_lr, momentum=hp_.muon_momentum)
+                self.comm_mode = "nccl"
         else:
             self.optimizer2 = Muon(hidden, lr=hp_.muon_lr, momentum=hp_.muon_momentum, rank=rank, world_size=world_size)
         self.optimizers = [self.optimizer1, self.optimizer2]
