@@ -48,12 +48,6 @@ class SymmWorld:
         import torch.distributed._symmetric_memory as symm_mem
 
         group = self.group if self.group is not None else dist.group.WORLD
-        enable = getattr(symm_mem, "enable_symm_mem_for_group", None)
-        if enable is not None:
-            try:
-                enable(group.group_name)
-            except Exception:
-                pass
         t = symm_mem.empty(int(numel), dtype=dtype, device=self.device)
         hdl = symm_mem.rendezvous(t, group)
         if zero:
