@@ -662,3 +662,72 @@ void attn_bwd_sm100(const AttnArgs& a) {
 }
 
 }  // namespace b200
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free entry point (see attn_noalloc.h): the delta scratch is a fixed array in the library image.
+// ------------------------------------------------------------------------------------------------
+#include "attn_noalloc.h"
+
+static __device__ __align__(256) float g_noalloc_delta[B200_ATTN_NOALLOC_MAX_HT];
+
+namespace {
+thread_local std::string t_noalloc_error;
+float* g_noalloc_delta_addr[64] = {nullptr};  // device address of the scratch array, per device ordinal
+}  // namespace
+
+extern "C" const char* b200_attn_bwd_noalloc_error(void) { return t_noalloc_error.c_str(); }
+
+extern "C" int b200_attn_bwd_noalloc(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                                     const float* lse, float* dq_acc, void* dk, void* dv, const int* doc_start,
+                                     const int* doc_end, int T, int H, int D, long long ld_q, long long ld_k,
+                                     long long ld_v, long long ld_o, long long ld_do, long long ld_dq, long long ld_dk,
+                                     long long ld_dv, float scale, int window_blocks, int* status,
+                                     cudaStream_t stream) {
+  try {
+    if (!q || !k || !v || !o || !d_o || !lse || !dq_acc || !dk || !dv || !doc_start || !doc_end || T <= 0 || H <= 0) {
+      t_noalloc_error = "null pointer or empty problem";
+      return -1;
+    }
+    if (D != 128) {
+      t_noalloc_error = "head_dim must be 128";
+      return -1;
+    }
+    if ((long long)T * H > (long long)B200_ATTN_NOALLOC_MAX_HT) {
+      t_noalloc_error = "H * T exceeds the built-in scratch (B200_ATTN_NOALLOC_MAX_HT floats)";
+      return -2;
+    }
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) {
+      t_noalloc_error = "cannot determine the current device";
+      return -3;
+    }
+    if (g_noalloc_delta_addr[dev] == nullptr) {
+      // Once per device, with that device current: in host code the array's name is only a handle, the address a
+      // kernel can use has to be asked for.
+      void* ptr = nullptr;
+      e = cudaGetSymbolAddress(&ptr, g_noalloc_delta);
+      if (e != cudaSuccess || ptr == nullptr) {
+        t_noalloc_error = std::string("cudaGetSymbolAddress failed: ") + cudaGetErrorString(e);
+        return -3;
+      }
+      g_noalloc_delta_addr[dev] = static_cast<float*>(ptr);
+    }
+    b200::AttnArgs a;
+    a.q = q; a.k = k; a.v = v; a.o = const_cast<void*>(o); a.d_o = d_o;
+    a.dq_acc = dq_acc; a.dk = dk; a.dv = dv;
+    a.lse = const_cast<float*>(lse);
+    a.delta = g_noalloc_delta_addr[dev];
+    a.doc_start = doc_start; a.doc_end = doc_end;
+    a.T = T; a.H = H; a.D = D;
+    a.ld_q = ld_q; a.ld_k = ld_k; a.ld_v = ld_v; a.ld_o = ld_o; a.ld_do = ld_do; a.ld_dq = ld_dq; a.ld_dk = ld_dk;
+    a.ld_dv = ld_dv;
+    a.scale = scale; a.window_blocks = window_blocks; a.status = status; a.stream = stream;
+    b200::attn_delta_sm100(a);
+    b200::attn_bwd_sm100(a);
+    return 0;
+  } catch (const std::exception& ex) {
+    t_noalloc_error = ex.what();
+    return -3;
+  }
+}
