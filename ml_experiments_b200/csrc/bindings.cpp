@@ -9,6 +9,7 @@
 #include "comm/comm.h"
 #include "fused/fused.h"
 #include "gemm/gemm.h"
+#include "scan/s6_scan.h"
 
 namespace {
 
@@ -325,6 +326,41 @@ void allreduce_mean(at::IntArrayRef buf_ptrs, int64_t rank, int64_t n, int64_t d
                        to_peers(peer_flags), (int)channel, (int)epoch, status.data_ptr<int>(), cur_stream());
 }
 
+
+// ---------------------------------------------------------------------------------------------- S6 selective scan
+void s6_scan_fwd(const Tensor& u, const Tensor& delta, const Tensor& A, const Tensor& Bm, const Tensor& Cm,
+                 const c10::optional<Tensor>& Dv, const c10::optional<Tensor>& z, const c10::optional<Tensor>& y_pre,
+                 Tensor out, const c10::optional<Tensor>& chunk_state) {
+  const c10::cuda::CUDAGuard guard(u.device());
+  chk_bf16c(u, "u"); chk_bf16c(out, "out");
+  TORCH_CHECK(u.dim() == 3 && delta.scalar_type() == at::kFloat && delta.is_contiguous() && delta.sizes() == u.sizes(), "delta: fp32 [B, L, Din]");
+  const int B = (int)u.size(0), L = (int)u.size(1), Din = (int)u.size(2), N = (int)A.size(1);
+  TORCH_CHECK(A.scalar_type() == at::kFloat && A.is_contiguous() && A.size(0) == Din, "A: fp32 [Din, N]");
+  TORCH_CHECK(Bm.scalar_type() == at::kFloat && Bm.is_contiguous() && Bm.size(0) == B && Bm.size(1) == L && Bm.size(2) == N, "B: fp32 [B, L, N]");
+  TORCH_CHECK(Cm.scalar_type() == at::kFloat && Cm.is_contiguous() && Cm.sizes() == Bm.sizes(), "C: fp32 [B, L, N]");
+  if (z.has_value()) chk_bf16c(*z, "z");
+  if (y_pre.has_value()) chk_bf16c(*y_pre, "y_pre");
+  b200::s6_scan_fwd(u.data_ptr(), delta.data_ptr<float>(), A.data_ptr<float>(), Bm.data_ptr<float>(), Cm.data_ptr<float>(),
+                    optf(Dv), optp(z), y_pre.has_value() ? y_pre->data_ptr() : nullptr, out.data_ptr(),
+                    chunk_state.has_value() ? chunk_state->data_ptr<float>() : nullptr, B, L, Din, N, cur_stream());
+}
+
+void s6_scan_bwd(const Tensor& u, const Tensor& delta, const Tensor& A, const Tensor& Bm, const Tensor& Cm,
+                 const c10::optional<Tensor>& Dv, const Tensor& dy, const Tensor& chunk_state, Tensor du, Tensor ddelta,
+                 Tensor dA, Tensor dB_part, Tensor dC_part, const c10::optional<Tensor>& dD) {
+  const c10::cuda::CUDAGuard guard(u.device());
+  chk_bf16c(u, "u"); chk_bf16c(dy, "dy"); chk_bf16c(du, "du");
+  const int B = (int)u.size(0), L = (int)u.size(1), Din = (int)u.size(2), N = (int)A.size(1);
+  TORCH_CHECK(ddelta.scalar_type() == at::kFloat && ddelta.is_contiguous() && dA.scalar_type() == at::kFloat &&
+              dB_part.scalar_type() == at::kFloat && dC_part.scalar_type() == at::kFloat, "s6_scan_bwd: fp32 gradient buffers");
+  TORCH_CHECK(dB_part.numel() == (int64_t)B * b200::s6_channel_blocks(Din) * L * N && dC_part.numel() == dB_part.numel(), "partial buffers: [B, ceil(Din/64), L, N]");
+  TORCH_CHECK(chunk_state.numel() == (int64_t)B * b200::s6_num_chunks(L) * Din * N, "chunk_state: [B, ceil(L/64), Din, N]");
+  b200::s6_scan_bwd(u.data_ptr(), delta.data_ptr<float>(), A.data_ptr<float>(), Bm.data_ptr<float>(), Cm.data_ptr<float>(),
+                    optf(Dv), dy.data_ptr(), chunk_state.data_ptr<float>(), du.data_ptr(), ddelta.data_ptr<float>(),
+                    dA.data_ptr<float>(), dB_part.data_ptr<float>(), dC_part.data_ptr<float>(),
+                    dD.has_value() ? dD->data_ptr<float>() : nullptr, B, L, Din, N, cur_stream());
+}
+
 }  // namespace
 
 TORCH_LIBRARY(b200, m) {
@@ -353,6 +389,8 @@ TORCH_LIBRARY(b200, m) {
   m.def("ag_push(Tensor src, int[] u_full_ptrs, int rank, int dst_off, int[] peer_flags, int channel, int epoch) -> ()");
   m.def("ag_wait_apply(Tensor(a!) p, Tensor u, Tensor(b!)? p_bf16, float alpha, int world, Tensor flags, int channel, int epoch, Tensor(c!) status) -> ()");
   m.def("allreduce_mean(int[] buf_ptrs, int rank, int n, int dtype, Tensor flags, int[] peer_flags, int channel, int epoch, Tensor(a!) status) -> ()");
+  m.def("s6_scan_fwd(Tensor u, Tensor delta, Tensor A, Tensor Bm, Tensor Cm, Tensor? Dv, Tensor? z, Tensor(a!)? y_pre, Tensor(b!) out, Tensor(c!)? chunk_state) -> ()");
+  m.def("s6_scan_bwd(Tensor u, Tensor delta, Tensor A, Tensor Bm, Tensor Cm, Tensor? Dv, Tensor dy, Tensor chunk_state, Tensor(a!) du, Tensor(b!) ddelta, Tensor(c!) dA, Tensor(d!) dB_part, Tensor(e!) dC_part, Tensor(f!)? dD) -> ()");
   // <<DEFS>>
 }
 
@@ -380,5 +418,7 @@ TORCH_LIBRARY_IMPL(b200, CUDA, m) {
   m.impl("ag_push", &ag_push);
   m.impl("ag_wait_apply", &ag_wait_apply);
   m.impl("allreduce_mean", &allreduce_mean);
+  m.impl("s6_scan_fwd", &s6_scan_fwd);
+  m.impl("s6_scan_bwd", &s6_scan_bwd);
   // <<IMPLS>>
 }

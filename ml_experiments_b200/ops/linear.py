@@ -1,0 +1,56 @@
+"""``y = x @ W.T`` as an autograd function on the tcgen05 GEMM (forward, data gradient and weight gradient).
+
+Used by every model of the package whose projections should not go through a library GEMM; falls back to
+``torch.nn.functional.linear`` for CPU tensors or shapes the TMA descriptors cannot express (row pitch not a multiple
+of 16 bytes).
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from . import gemm as G
+
+
+def _ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return x.is_cuda and x.shape[-1] % 8 == 0 and w.shape[0] % 8 == 0 and x.numel() > 0
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, epilogue):
+        x2 = x.reshape(-1, x.shape[-1])
+        x16 = x2 if x2.dtype == torch.bfloat16 else x2.to(torch.bfloat16)
+        w16 = w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)
+        x16, w16 = x16.contiguous(), w16.contiguous()
+        y = G.gemm(x16, w16, epilogue=epilogue)
+        ctx.save_for_backward(x16, w16, y if epilogue == G.EPI_RELU2 else None)
+        ctx.epilogue, ctx.x_shape, ctx.x_dtype, ctx.w_dtype = epilogue, x.shape, x.dtype, w.dtype
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x16, w16, h = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1]).to(torch.bfloat16).contiguous()
+        if ctx.epilogue == G.EPI_RELU2:  # d relu(z)^2 / dz = 2 relu(z) = 2 sqrt(h)
+            dy2 = (dy2.float() * 2 * h.float().sqrt()).to(torch.bfloat16)
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = G.gemm(dy2, w16, b_mn=True).view(ctx.x_shape).to(ctx.x_dtype)
+        if ctx.needs_input_grad[1]:
+            sk = G.auto_split_k(w16.shape[0], w16.shape[1], x16.shape[0])
+            dw = G.gemm(dy2, x16, a_mn=True, b_mn=True, split_k=sk, out_dtype=torch.float32).to(ctx.w_dtype)
+        return dx, dw, None
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, relu2: bool = False) -> torch.Tensor:
+    """bf16 tensor-core linear layer; ``relu2=True`` fuses ``relu(.)**2`` into the GEMM epilogue (no bias then)."""
+    if not _ok(x, w):
+        y = F.linear(x, w.to(x.dtype), None if bias is None else bias.to(x.dtype))
+        return F.relu(y).square() if relu2 else y
+    y = _Linear.apply(x, w, G.EPI_RELU2 if (relu2 and bias is None) else G.EPI_NONE)
+    if bias is not None:
+        y = y + bias.to(y.dtype)
+        if relu2:
+            y = F.relu(y).square()
+    return y
