@@ -353,12 +353,33 @@ void s6_scan_bwd(const Tensor& u, const Tensor& delta, const Tensor& A, const Te
   const int B = (int)u.size(0), L = (int)u.size(1), Din = (int)u.size(2), N = (int)A.size(1);
   TORCH_CHECK(ddelta.scalar_type() == at::kFloat && ddelta.is_contiguous() && dA.scalar_type() == at::kFloat &&
               dB_part.scalar_type() == at::kFloat && dC_part.scalar_type() == at::kFloat, "s6_scan_bwd: fp32 gradient buffers");
-  TORCH_CHECK(dB_part.numel() == (int64_t)B * b200::s6_channel_blocks(Din) * L * N && dC_part.numel() == dB_part.numel(), "partial buffers: [B, ceil(Din/64), L, N]");
+  TORCH_CHECK(dB_part.numel() == (int64_t)B * b200::s6_channel_blocks(Din) * L * N && dC_part.numel() == dB_part.numel(), "partial buffers: [B, ceil(Din/16), L, N]");
   TORCH_CHECK(chunk_state.numel() == (int64_t)B * b200::s6_num_chunks(L) * Din * N, "chunk_state: [B, ceil(L/64), Din, N]");
   b200::s6_scan_bwd(u.data_ptr(), delta.data_ptr<float>(), A.data_ptr<float>(), Bm.data_ptr<float>(), Cm.data_ptr<float>(),
                     optf(Dv), dy.data_ptr(), chunk_state.data_ptr<float>(), du.data_ptr(), ddelta.data_ptr<float>(),
                     dA.data_ptr<float>(), dB_part.data_ptr<float>(), dC_part.data_ptr<float>(),
                     dD.has_value() ? dD->data_ptr<float>() : nullptr, B, L, Din, N, cur_stream());
+}
+
+
+void causal_conv1d_silu_fwd(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& bias, Tensor y) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 3 && x.scalar_type() == at::kBFloat16 && x.stride(2) == 1 && x.stride(0) == x.size(1) * x.stride(1), "x: bf16 [B, L, C] (channel slice allowed)");
+  chk_bf16c(y, "y");
+  const int B = (int)x.size(0), L = (int)x.size(1), C = (int)x.size(2);
+  TORCH_CHECK(w.scalar_type() == at::kFloat && w.is_contiguous() && w.numel() == (int64_t)C * 4, "w: fp32 [C, 4]");
+  b200::causal_conv1d_silu_fwd(x.data_ptr(), x.stride(1), w.data_ptr<float>(), optf(bias), y.data_ptr(), B, L, C, cur_stream());
+}
+
+void causal_conv1d_silu_bwd(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& bias, const Tensor& dy, Tensor dx,
+                            Tensor dw, const c10::optional<Tensor>& dbias) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  chk_bf16c(dy, "dy");
+  TORCH_CHECK(dx.scalar_type() == at::kBFloat16 && dx.stride(2) == 1 && dx.stride(0) == dx.size(1) * dx.stride(1), "dx: bf16 [B, L, C]");
+  const int B = (int)x.size(0), L = (int)x.size(1), C = (int)x.size(2);
+  b200::causal_conv1d_silu_bwd(x.data_ptr(), x.stride(1), w.data_ptr<float>(), optf(bias), dy.data_ptr(), dx.data_ptr(),
+                               dx.stride(1), dw.data_ptr<float>(), dbias.has_value() ? dbias->data_ptr<float>() : nullptr, B, L, C,
+                               cur_stream());
 }
 
 }  // namespace
@@ -391,6 +412,8 @@ TORCH_LIBRARY(b200, m) {
   m.def("allreduce_mean(int[] buf_ptrs, int rank, int n, int dtype, Tensor flags, int[] peer_flags, int channel, int epoch, Tensor(a!) status) -> ()");
   m.def("s6_scan_fwd(Tensor u, Tensor delta, Tensor A, Tensor Bm, Tensor Cm, Tensor? Dv, Tensor? z, Tensor(a!)? y_pre, Tensor(b!) out, Tensor(c!)? chunk_state) -> ()");
   m.def("s6_scan_bwd(Tensor u, Tensor delta, Tensor A, Tensor Bm, Tensor Cm, Tensor? Dv, Tensor dy, Tensor chunk_state, Tensor(a!) du, Tensor(b!) ddelta, Tensor(c!) dA, Tensor(d!) dB_part, Tensor(e!) dC_part, Tensor(f!)? dD) -> ()");
+  m.def("causal_conv1d_silu_fwd(Tensor x, Tensor w, Tensor? bias, Tensor(a!) y) -> ()");
+  m.def("causal_conv1d_silu_bwd(Tensor x, Tensor w, Tensor? bias, Tensor dy, Tensor(a!) dx, Tensor(b!) dw, Tensor(c!)? dbias) -> ()");
   // <<DEFS>>
 }
 
@@ -420,5 +443,7 @@ TORCH_LIBRARY_IMPL(b200, CUDA, m) {
   m.impl("allreduce_mean", &allreduce_mean);
   m.impl("s6_scan_fwd", &s6_scan_fwd);
   m.impl("s6_scan_bwd", &s6_scan_bwd);
+  m.impl("causal_conv1d_silu_fwd", &causal_conv1d_silu_fwd);
+  m.impl("causal_conv1d_silu_bwd", &causal_conv1d_silu_bwd);
   // <<IMPLS>>
 }

@@ -8,8 +8,8 @@
 // The sequence is processed in chunks of 64 steps: the chunk's u / dt / B / C (and dy in the backward) are staged in
 // shared memory with coalesced loads, the forward stores the state at every chunk boundary, and the backward walks
 // the chunks in reverse, recomputing the 64 states of a chunk into registers from its stored boundary state.
-// A block owns 64 channels (8 groups of 8, looped) so that dB / dC are reduced over 64 channels on chip and written
-// as deterministic partial sums [B][Din/64][L][N] that the caller adds up.
+// A backward block owns 16 channels (2 groups of 8, looped) so that dB / dC are reduced over them on chip and written
+// as deterministic partial sums [B][Din/16][L][N] that the caller adds up; a forward block owns one group of 8.
 //
 // Semantics follow selective_scan_ref of the reference (zoology/mixers/mamba_ssm/ops/selective_scan_interface.py:91-157)
 // with real A, input-dependent B and C shared across channels, delta already soft-plussed.
@@ -28,7 +28,8 @@ namespace {
 using bf16 = __nv_bfloat16;
 constexpr int NS = 16;      // states per channel
 constexpr int CG = 8;       // channels per thread group
-constexpr int CB = 64;      // channels per block
+constexpr int CB_FWD = 8;   // channels per block, forward (one thread group: maximum parallelism)
+constexpr int CB_BWD = 16;  // channels per block, backward (dB / dC are reduced over these on chip)
 constexpr int CHUNK = 64;   // time steps staged per iteration
 constexpr float LOG2E = 1.4426950408889634f;
 
@@ -41,6 +42,7 @@ __device__ __forceinline__ float sum16(float v) {
 }
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
 
+template <int CB>
 struct FwdSmem {
   float dt[CHUNK][CB];
   float u[CHUNK][CB];
@@ -49,14 +51,15 @@ struct FwdSmem {
   float C[CHUNK][NS];
 };
 
-// grid (Din / 64, batch), 128 threads
+// grid (Din / CB, batch), 128 threads
+template <int CB>
 __global__ void __launch_bounds__(128)
 s6_fwd_kernel(const bf16* __restrict__ u, const float* __restrict__ delta, const float* __restrict__ A,
               const float* __restrict__ Bm, const float* __restrict__ Cm, const float* __restrict__ Dv,
               const bf16* __restrict__ z, bf16* __restrict__ y_pre, bf16* __restrict__ out,
               float* __restrict__ chunk_state, int L, int Din) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
-  FwdSmem& s = *reinterpret_cast<FwdSmem*>(smem_raw);
+  FwdSmem<CB>& s = *reinterpret_cast<FwdSmem<CB>*>(smem_raw);
   const int tid = threadIdx.x;
   const int n = tid & (NS - 1);
   const int cg = tid >> 4;  // 0..7 channel within group
@@ -119,6 +122,7 @@ s6_fwd_kernel(const bf16* __restrict__ u, const float* __restrict__ delta, const
   }
 }
 
+template <int CB>
 struct BwdSmem {
   float dt[CHUNK][CB];
   float u[CHUNK][CB];
@@ -131,7 +135,8 @@ struct BwdSmem {
   float dC[CHUNK][NS];
 };
 
-// grid (Din / 64, batch), 128 threads. dy is the gradient with respect to y (before the gate).
+// grid (Din / CB, batch), 128 threads. dy is the gradient with respect to y (before the gate).
+template <int CB>
 __global__ void __launch_bounds__(128)
 s6_bwd_kernel(const bf16* __restrict__ u, const float* __restrict__ delta, const float* __restrict__ A,
               const float* __restrict__ Bm, const float* __restrict__ Cm, const float* __restrict__ Dv,
@@ -139,7 +144,7 @@ s6_bwd_kernel(const bf16* __restrict__ u, const float* __restrict__ delta, const
               float* __restrict__ ddelta, float* __restrict__ dA, float* __restrict__ dB_part,
               float* __restrict__ dC_part, float* __restrict__ dD, int L, int Din) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
-  BwdSmem& s = *reinterpret_cast<BwdSmem*>(smem_raw);
+  BwdSmem<CB>& s = *reinterpret_cast<BwdSmem<CB>*>(smem_raw);
   const int tid = threadIdx.x;
   const int n = tid & (NS - 1);
   const int cg = tid >> 4;
@@ -261,7 +266,7 @@ void check(const char* what) {
 
 }  // namespace
 
-int s6_channel_blocks(int Din) { return (Din + CB - 1) / CB; }
+int s6_channel_blocks(int Din) { return (Din + CB_BWD - 1) / CB_BWD; }
 int s6_num_chunks(int L) { return (L + CHUNK - 1) / CHUNK; }
 
 void s6_scan_fwd(const void* u, const float* delta, const float* A, const float* Bm, const float* Cm, const float* Dv,
@@ -270,11 +275,11 @@ void s6_scan_fwd(const void* u, const float* delta, const float* A, const float*
   if (N != NS) throw std::runtime_error("s6_scan: state dimension must be 16");
   static bool cfg = false;
   if (!cfg) {
-    cudaFuncSetAttribute(s6_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(FwdSmem));
+    cudaFuncSetAttribute(s6_fwd_kernel<CB_FWD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(FwdSmem<CB_FWD>));
     cfg = true;
   }
-  dim3 grid(s6_channel_blocks(Din), batch);
-  s6_fwd_kernel<<<grid, 128, sizeof(FwdSmem), s>>>((const bf16*)u, delta, A, Bm, Cm, Dv, (const bf16*)z, (bf16*)y_pre,
+  dim3 grid((Din + CB_FWD - 1) / CB_FWD, batch);
+  s6_fwd_kernel<CB_FWD><<<grid, 128, sizeof(FwdSmem<CB_FWD>), s>>>((const bf16*)u, delta, A, Bm, Cm, Dv, (const bf16*)z, (bf16*)y_pre,
                                                    (bf16*)out, chunk_state, L, Din);
   check("s6_scan_fwd");
 }
@@ -285,11 +290,11 @@ void s6_scan_bwd(const void* u, const float* delta, const float* A, const float*
   if (N != NS) throw std::runtime_error("s6_scan: state dimension must be 16");
   static bool cfg = false;
   if (!cfg) {
-    cudaFuncSetAttribute(s6_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(BwdSmem));
+    cudaFuncSetAttribute(s6_bwd_kernel<CB_BWD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(BwdSmem<CB_BWD>));
     cfg = true;
   }
   dim3 grid(s6_channel_blocks(Din), batch);
-  s6_bwd_kernel<<<grid, 128, sizeof(BwdSmem), s>>>((const bf16*)u, delta, A, Bm, Cm, Dv, (const bf16*)dy, chunk_state,
+  s6_bwd_kernel<CB_BWD><<<grid, 128, sizeof(BwdSmem<CB_BWD>), s>>>((const bf16*)u, delta, A, Bm, Cm, Dv, (const bf16*)dy, chunk_state,
                                                    (bf16*)du, ddelta, dA, dB_part, dC_part, dD, L, Din);
   check("s6_scan_bwd");
 }

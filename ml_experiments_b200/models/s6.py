@@ -18,6 +18,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from ..ops.causal_conv import causal_conv1d_silu
 from ..ops.linear import linear
 from ..ops.selective_scan import selective_scan
 
@@ -79,7 +80,7 @@ class S6Mixer(nn.Module):
         L = x.shape[1]
         xz = linear(x, self.in_proj.weight)
         xi, z = xz.chunk(2, dim=-1)
-        xi = F.silu(self.conv1d(xi.transpose(1, 2))[..., :L].transpose(1, 2))
+        xi = causal_conv1d_silu(xi, self.conv1d.weight, self.conv1d.bias)
         dbc = linear(xi, self.x_proj.weight)
         dt, Bm, Cm = torch.split(dbc, [cfg.rank, cfg.d_state, cfg.d_state], dim=-1)
         delta = F.softplus(linear(dt, self.dt_proj.weight).float() + self.dt_proj.bias.float())

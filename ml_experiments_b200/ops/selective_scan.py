@@ -73,7 +73,7 @@ class _S6Scan(torch.autograd.Function):
             dy = (dout * zf * sig).to(torch.bfloat16).contiguous()
         else:
             dy = dout.to(torch.bfloat16).contiguous()
-        nblk = (din + 63) // 64
+        nblk = (din + 15) // 16
         du = torch.empty_like(u16)
         ddelta = torch.empty_like(d32)
         dA = torch.zeros_like(A32)

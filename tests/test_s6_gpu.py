@@ -49,3 +49,25 @@ def test_s6_lm_trains():
         opt.step()
         first = first if first is not None else loss.item()
     assert loss.item() < 0.8 * first
+
+
+def test_causal_conv1d_silu():
+    from ml_experiments_b200.ops.causal_conv import causal_conv1d_silu, causal_conv1d_silu_ref
+
+    torch.manual_seed(1)
+    B, L, C = 2, 150, 264
+    wide = torch.randn(B, L, 2 * C, device="cuda").bfloat16()
+    x = wide[..., :C].detach().requires_grad_(True)           # channel slice of a wider tensor
+    w = (torch.randn(C, 1, 4, device="cuda") * 0.5).requires_grad_(True)
+    b = torch.randn(C, device="cuda").requires_grad_(True)
+    g = torch.randn(B, L, C, device="cuda").bfloat16()
+    xr = x.detach().float().requires_grad_(True)
+    wr, br = w.detach().clone().requires_grad_(True), b.detach().clone().requires_grad_(True)
+    ref = causal_conv1d_silu_ref(xr, wr, br)
+    ref.backward(g.float())
+    y = causal_conv1d_silu(x, w, b)
+    assert ((y.float() - ref).abs().max() / ref.abs().max()).item() < 2e-2
+    y.backward(g)
+    for name, got, want in (("dx", x.grad, xr.grad), ("dw", w.grad, wr.grad), ("db", b.grad, br.grad)):
+        rel = ((got.float() - want).norm() / want.norm()).item()
+        assert rel < 2e-2, (name, rel)
