@@ -1,0 +1,22 @@
+"""Validator training (reference: src/heuristic_secrets/validator/train.py). Batches are
+``(features, byte_ids, lengths, labels)`` tuples."""
+from __future__ import annotations
+
+import torch
+
+from ..training import BinaryTaskTrainer, TrainMetrics, get_device, set_seed  # noqa: F401
+from .model import ValidatorConfig, ValidatorModel
+
+
+class ValidatorTrainer(BinaryTaskTrainer):
+    def _forward(self, batch):
+        feats, ids, lengths, labels = (t.to(self.device) for t in batch)
+        return self.model(feats, ids, lengths).squeeze(-1), labels.float(), None
+
+
+def load_checkpoint(path, device: torch.device | None = None) -> ValidatorModel:
+    device = device or get_device()
+    ck = torch.load(path, map_location=device, weights_only=False)
+    model = ValidatorModel(ValidatorConfig.from_dict(ck["config"]))
+    model.load_state_dict(ck.get("best_state") or ck["state_dict"])
+    return model.to(device)
