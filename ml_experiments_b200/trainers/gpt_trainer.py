@@ -52,7 +52,7 @@ class GPTTrainer:
     """Owns model, optimizers and (optionally) the process group; ``train_step`` runs one optimizer step."""
 
     def __init__(self, config: GPTConfig | None = None, hp: Hyperparameters | None = None, device="cuda",
-                 rank: int = 0, world_size: int = 1, seed: int = 0, grad_sync: str = "auto"):
+                 rank: int = 0, world_size: int = 1, seed: int = 0, grad_sync: str = "auto", matrix_optimizer: str = "muon"):
         self.hp = hp or Hyperparameters()
         self.config = config or GPTConfig(max_seq_len=max(self.hp.seq_len, 65536))
         self.rank, self.world_size = rank, world_size
@@ -72,7 +72,23 @@ class GPTTrainer:
         self.grad_sync = grad_sync
         self.comm = None
         self.comm_mode = "single"
-        if world_size > 1 and self.device.type == "cuda":
+        if matrix_optimizer == "dion":
+            from ..optim.dion import Dion
+
+            sw = None
+            if world_size > 1 and self.device.type == "cuda":
+                from ..parallel import muon_dist as md
+                from ..parallel.symm import SymmWorld
+
+                try:
+                    sw = SymmWorld.create(rank, world_size, self.device)
+                    self.comm = md.FusedGradSync(model, hidden, sw)
+                    self.comm_mode = "fused-p2p"
+                except Exception:
+                    self.comm = md.GradSync(model, hidden, rank, world_size)
+                    self.comm_mode = "nccl"
+            self.optimizer2 = Dion(hidden, lr=hp_.muon_lr * 0.2, mu=hp_.muon_momentum, rank_fraction=0.25, world=sw)
+        elif world_size > 1 and self.device.type == "cuda":
             from ..parallel import muon_dist as md
 
             if grad_sync in ("auto", "fused"):
