@@ -1,0 +1,122 @@
+"""Chunk-parallel scan for state-space layers with a scalar decay per head (the "SSD" form).
+
+Recurrence, per batch ``b`` and head ``h`` with state ``S [N, P]``::
+
+    S_t = alpha_t * S_{t-1} + gamma_t * B_t (x) x_t + beta_t * B_{t-1} (x) x_{t-1}        y_t = C_t . S_t
+
+``beta`` (the look-back term of the trapezoidal discretisation) is optional. This is the recurrence of the reference's
+``SSMMixer3._ssm_scan`` (src/heuristic_secrets/models/backbone.py:1516-1595), which walks the chunks in a Python loop
+and materialises the ``[B, L, H, N, P]`` outer products, and of the vendored Mamba-2 ``ssd_combined`` pipeline
+(zoology/mixers/mamba_ssm/ops/triton/ssd_combined.py). Here every chunk is processed at once as batched matrix
+products that land on the tensor cores -- intra-chunk ``(C B^T o decay) U``, per-chunk end states, a logarithmic-depth
+inter-chunk state pass, and the carried-state contribution -- and nothing of size ``L*N*P`` is ever formed.
+Differentiable through autograd. ``ssd_scan_ref`` is the sequential fp32 oracle.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+
+def ssd_scan_ref(x, B, C, log_alpha, gamma, beta=None, init_state=None):
+    """Sequential oracle. ``x [b,L,H,P]``, ``B,C [b,L,H,N]``, ``log_alpha, gamma, beta [b,L,H]`` -> ``(y, final_state)``."""
+    b, L, H, P = x.shape
+    N = B.shape[-1]
+    xf, Bf, Cf = x.float(), B.float().expand(b, L, H, N), C.float().expand(b, L, H, N)
+    S = xf.new_zeros(b, H, N, P) if init_state is None else init_state.float().clone()
+    ys = []
+    for t in range(L):
+        u = gamma[:, t, :, None, None].float() * Bf[:, t, :, :, None] * xf[:, t, :, None, :]
+        if beta is not None and t > 0:
+            u = u + beta[:, t, :, None, None].float() * Bf[:, t - 1, :, :, None] * xf[:, t - 1, :, None, :]
+        S = torch.exp(log_alpha[:, t].float())[:, :, None, None] * S + u
+        ys.append(torch.einsum("bhnp,bhn->bhp", S, Cf[:, t]))
+    return torch.stack(ys, 1).to(x.dtype), S
+
+
+def _decay_matrix(cs):
+    """``cs [..., Q]`` inclusive cumulative log-decay -> ``exp(cs_i - cs_j)`` for ``i >= j`` else 0, ``[..., Q, Q]``."""
+    Q = cs.shape[-1]
+    d = cs.unsqueeze(-1) - cs.unsqueeze(-2)
+    keep = torch.ones(Q, Q, dtype=torch.bool, device=cs.device).tril()
+    return torch.exp(d.masked_fill(~keep, float("-inf")))
+
+
+def _exclusive_state_pass(log_a, s, s0=None, block: int = 64):
+    """Linear recurrence over dim 1: ``S_in[c+1] = exp(log_a[c]) * S_in[c] + s[c]`` with ``S_in[0] = s0``.
+
+    ``log_a [b, n, H]``, ``s [b, n, H, D]`` -> ``(S_in [b, n, H, D], S_final [b, H, D])``. Blocks of ``block`` steps are
+    solved with a decay matrix; block totals recurse, so the depth is ``log_block(n)``.
+    """
+    b, n, H, D = s.shape
+    if n <= block:
+        cs = torch.cumsum(log_a.float(), dim=1)  # inclusive
+        M = _decay_matrix(cs.transpose(1, 2))  # [b, H, n, n]: exp(cs_i - cs_j), i >= j
+        # state after step i (inclusive) = sum_{j<=i} exp(cs_i - cs_j) s_j  (+ exp(cs_i) s0)
+        incl = torch.einsum("bhij,bjhd->bihd", M.to(s.dtype), s)
+        if s0 is not None:
+            incl = incl + torch.exp(cs).to(s.dtype).unsqueeze(-1) * s0.unsqueeze(1)
+        first = torch.zeros_like(s[:, :1]) if s0 is None else s0.unsqueeze(1)
+        return torch.cat([first, incl[:, :-1]], dim=1), incl[:, -1]
+    pad = (-n) % block
+    if pad:
+        log_a = F.pad(log_a, (0, 0, 0, pad))
+        s = F.pad(s, (0, 0, 0, 0, 0, pad))
+    nb = (n + pad) // block
+    la = log_a.view(b, nb, block, H)
+    sb = s.view(b, nb, block, H, D)
+    # within-block inclusive states from a zero start, all blocks at once
+    cs = torch.cumsum(la.float(), dim=2)
+    M = _decay_matrix(cs.permute(0, 1, 3, 2))  # [b, nb, H, blk, blk]
+    incl = torch.einsum("bchij,bcjhd->bcihd", M.to(s.dtype), sb)
+    tot_log = cs[:, :, -1]  # [b, nb, H]
+    carry_in, final = _exclusive_state_pass(tot_log, incl[:, :, -1], s0, block)  # state entering each block
+    incl = incl + torch.exp(cs).to(s.dtype).unsqueeze(-1) * carry_in.unsqueeze(2)
+    first = carry_in.unsqueeze(2)
+    excl = torch.cat([first, incl[:, :, :-1]], dim=2).reshape(b, nb * block, H, D)[:, :n]
+    if pad:  # padded steps have log_a = 0, s = 0: the state is unchanged, `final` is already right
+        pass
+    return excl, final
+
+
+def ssd_chunk_scan(x, B, C, log_alpha, gamma, beta=None, chunk: int = 64, init_state=None, return_state: bool = False):
+    """Chunk-parallel evaluation of the recurrence in the module docstring.
+
+    ``x [b,L,H,P]``; ``B, C [b,L,H,N]`` (a size-1 head dim broadcasts: grouped B/C); ``log_alpha, gamma, beta [b,L,H]``.
+    Returns ``y [b,L,H,P]`` (and the final state ``[b,H,N,P]`` if ``return_state``).
+    """
+    b, L, H, P = x.shape
+    N = B.shape[-1]
+    B = B.expand(b, L, H, N)
+    C = C.expand(b, L, H, N)
+    dt = x.dtype
+    u1 = gamma.to(dt).unsqueeze(-1) * x
+    if beta is not None:
+        u2 = beta.to(dt).unsqueeze(-1) * F.pad(x[:, :-1], (0, 0, 0, 0, 1, 0))
+        Bp = F.pad(B[:, :-1], (0, 0, 0, 0, 1, 0))
+    pad = (-L) % chunk
+    if pad:
+        padl = lambda t: F.pad(t, (0, 0) * (t.dim() - 2) + (0, pad))
+        u1, B, C, log_alpha = padl(u1), padl(B), padl(C), padl(log_alpha)
+        if beta is not None:
+            u2, Bp = padl(u2), padl(Bp)
+    nc, Q = (L + pad) // chunk, chunk
+    c5 = lambda t: t.reshape(b, nc, Q, H, t.shape[-1]).permute(0, 1, 3, 2, 4)  # [b, nc, H, Q, *]
+    Cc, Bc, U1 = c5(C), c5(B), c5(u1)
+    cs = torch.cumsum(log_alpha.float().view(b, nc, Q, H).permute(0, 1, 3, 2), dim=-1)  # [b, nc, H, Q]
+    dec = _decay_matrix(cs).to(dt)
+    to_end = torch.exp(cs[..., -1:] - cs).to(dt).unsqueeze(-1)  # decay from step j to the chunk end
+    y = torch.matmul(torch.matmul(Cc, Bc.transpose(-1, -2)) * dec, U1)
+    S = torch.matmul((Bc * to_end).transpose(-1, -2), U1)  # [b, nc, H, N, P]
+    if beta is not None:
+        Bpc, U2 = c5(Bp), c5(u2)
+        y = y + torch.matmul(torch.matmul(Cc, Bpc.transpose(-1, -2)) * dec, U2)
+        S = S + torch.matmul((Bpc * to_end).transpose(-1, -2), U2)
+    s0 = None if init_state is None else init_state.to(dt).reshape(b, H, N * P)
+    S_in, S_fin = _exclusive_state_pass(cs[..., -1], S.reshape(b, nc, H, N * P), s0)
+    S_in = S_in.view(b, nc, H, N, P)
+    y = y + torch.exp(cs).to(dt).unsqueeze(-1) * torch.matmul(Cc, S_in)
+    y = y.permute(0, 1, 3, 2, 4).reshape(b, nc * Q, H, P)[:, :L]
+    if return_state:
+        return y, S_fin.view(b, H, N, P)
+    return y
