@@ -11,6 +11,7 @@
 #include "gather/gather_conv.h"
 #include "gemm/gemm.h"
 #include "scan/s6_scan.h"
+#include "wkv/wkv.h"
 
 namespace {
 
@@ -329,37 +330,45 @@ void allreduce_mean(at::IntArrayRef buf_ptrs, int64_t rank, int64_t n, int64_t d
 
 
 // ---------------------------------------------------------------------------------------------- S6 selective scan
-void s6_scan_fwd(const Tensor& u, const Tensor& delta, const Tensor& A, const Tensor& Bm, const Tensor& Cm,
-                 const c10::optional<Tensor>& Dv, const c10::optional<Tensor>& z, const c10::optional<Tensor>& y_pre,
-                 Tensor out, const c10::optional<Tensor>& chunk_state) {
+void s6_scan_fwd(const Tensor& u, const Tensor& delta, const c10::optional<Tensor>& delta_bias, bool softplus, const Tensor& A,
+                 const Tensor& Bm, const Tensor& Cm, const c10::optional<Tensor>& Dv, const c10::optional<Tensor>& z,
+                 const c10::optional<Tensor>& y_pre, Tensor out, const c10::optional<Tensor>& state) {
   const c10::cuda::CUDAGuard guard(u.device());
   chk_bf16c(u, "u"); chk_bf16c(out, "out");
-  TORCH_CHECK(u.dim() == 3 && delta.scalar_type() == at::kFloat && delta.is_contiguous() && delta.sizes() == u.sizes(), "delta: fp32 [B, L, Din]");
+  TORCH_CHECK(u.dim() == 3 && (delta.scalar_type() == at::kFloat || delta.scalar_type() == at::kBFloat16) && delta.is_contiguous() && delta.sizes() == u.sizes(), "delta: fp32 or bf16 [B, L, Din]");
   const int B = (int)u.size(0), L = (int)u.size(1), Din = (int)u.size(2), N = (int)A.size(1);
   TORCH_CHECK(A.scalar_type() == at::kFloat && A.is_contiguous() && A.size(0) == Din, "A: fp32 [Din, N]");
   TORCH_CHECK(Bm.scalar_type() == at::kFloat && Bm.is_contiguous() && Bm.size(0) == B && Bm.size(1) == L && Bm.size(2) == N, "B: fp32 [B, L, N]");
   TORCH_CHECK(Cm.scalar_type() == at::kFloat && Cm.is_contiguous() && Cm.sizes() == Bm.sizes(), "C: fp32 [B, L, N]");
   if (z.has_value()) chk_bf16c(*z, "z");
   if (y_pre.has_value()) chk_bf16c(*y_pre, "y_pre");
-  b200::s6_scan_fwd(u.data_ptr(), delta.data_ptr<float>(), A.data_ptr<float>(), Bm.data_ptr<float>(), Cm.data_ptr<float>(),
-                    optf(Dv), optp(z), y_pre.has_value() ? y_pre->data_ptr() : nullptr, out.data_ptr(),
-                    chunk_state.has_value() ? chunk_state->data_ptr<float>() : nullptr, B, L, Din, N, cur_stream());
+  if (state.has_value())
+    TORCH_CHECK(state->scalar_type() == at::kFloat && state->is_contiguous() &&
+                state->numel() == (int64_t)B * b200::s6_num_chunks(L) * Din * N, "state: fp32 [B, ceil(L/16), 4, Din, 4]");
+  b200::s6_scan_fwd(u.data_ptr(), delta.data_ptr(), delta.scalar_type() == at::kBFloat16, optf(delta_bias), softplus, A.data_ptr<float>(), Bm.data_ptr<float>(),
+                    Cm.data_ptr<float>(), optf(Dv), optp(z), y_pre.has_value() ? y_pre->data_ptr() : nullptr, out.data_ptr(),
+                    state.has_value() ? state->data_ptr<float>() : nullptr, B, L, Din, N, cur_stream());
 }
 
-void s6_scan_bwd(const Tensor& u, const Tensor& delta, const Tensor& A, const Tensor& Bm, const Tensor& Cm,
-                 const c10::optional<Tensor>& Dv, const Tensor& dy, const Tensor& chunk_state, Tensor du, Tensor ddelta,
-                 Tensor dA, Tensor dB_part, Tensor dC_part, const c10::optional<Tensor>& dD) {
+void s6_scan_bwd(const Tensor& u, const Tensor& delta, const c10::optional<Tensor>& delta_bias, bool softplus, const Tensor& A,
+                 const Tensor& Bm, const Tensor& Cm, const c10::optional<Tensor>& Dv, const c10::optional<Tensor>& z,
+                 const c10::optional<Tensor>& y_pre, const Tensor& dout, const Tensor& state, Tensor du, Tensor ddelta, Tensor dA,
+                 Tensor dB_part, Tensor dC_part, const c10::optional<Tensor>& dD, const c10::optional<Tensor>& dz,
+                 const c10::optional<Tensor>& ddelta_bias) {
   const c10::cuda::CUDAGuard guard(u.device());
-  chk_bf16c(u, "u"); chk_bf16c(dy, "dy"); chk_bf16c(du, "du");
+  chk_bf16c(u, "u"); chk_bf16c(dout, "dout"); chk_bf16c(du, "du");
+  if (z.has_value()) { chk_bf16c(*z, "z"); TORCH_CHECK(y_pre.has_value(), "s6_scan_bwd: z needs y_pre"); chk_bf16c(*y_pre, "y_pre"); }
+  if (dz.has_value()) chk_bf16c(*dz, "dz");
   const int B = (int)u.size(0), L = (int)u.size(1), Din = (int)u.size(2), N = (int)A.size(1);
-  TORCH_CHECK(ddelta.scalar_type() == at::kFloat && ddelta.is_contiguous() && dA.scalar_type() == at::kFloat &&
+  TORCH_CHECK(ddelta.scalar_type() == delta.scalar_type() && ddelta.is_contiguous() && delta.is_contiguous() && ddelta.sizes() == u.sizes() && dA.scalar_type() == at::kFloat &&
               dB_part.scalar_type() == at::kFloat && dC_part.scalar_type() == at::kFloat, "s6_scan_bwd: fp32 gradient buffers");
-  TORCH_CHECK(dB_part.numel() == (int64_t)B * b200::s6_channel_blocks(Din) * L * N && dC_part.numel() == dB_part.numel(), "partial buffers: [B, ceil(Din/16), L, N]");
-  TORCH_CHECK(chunk_state.numel() == (int64_t)B * b200::s6_num_chunks(L) * Din * N, "chunk_state: [B, ceil(L/64), Din, N]");
-  b200::s6_scan_bwd(u.data_ptr(), delta.data_ptr<float>(), A.data_ptr<float>(), Bm.data_ptr<float>(), Cm.data_ptr<float>(),
-                    optf(Dv), dy.data_ptr(), chunk_state.data_ptr<float>(), du.data_ptr(), ddelta.data_ptr<float>(),
-                    dA.data_ptr<float>(), dB_part.data_ptr<float>(), dC_part.data_ptr<float>(),
-                    dD.has_value() ? dD->data_ptr<float>() : nullptr, B, L, Din, N, cur_stream());
+  TORCH_CHECK(dB_part.numel() == (int64_t)B * b200::s6_channel_blocks(Din) * L * N && dC_part.numel() == dB_part.numel(), "partial buffers: [B, ceil(Din/32), L, N]");
+  TORCH_CHECK(state.scalar_type() == at::kFloat && state.numel() == (int64_t)B * b200::s6_num_chunks(L) * Din * N, "state: [B, ceil(L/16), 4, Din, 4]");
+  b200::s6_scan_bwd(u.data_ptr(), delta.data_ptr(), delta.scalar_type() == at::kBFloat16, optf(delta_bias), softplus, A.data_ptr<float>(), Bm.data_ptr<float>(),
+                    Cm.data_ptr<float>(), optf(Dv), optp(z), optp(y_pre), dout.data_ptr(), state.data_ptr<float>(), du.data_ptr(),
+                    ddelta.data_ptr(), dA.data_ptr<float>(), dB_part.data_ptr<float>(), dC_part.data_ptr<float>(),
+                    dD.has_value() ? dD->data_ptr<float>() : nullptr, dz.has_value() ? dz->data_ptr() : nullptr,
+                    ddelta_bias.has_value() ? ddelta_bias->data_ptr<float>() : nullptr, B, L, Din, N, cur_stream());
 }
 
 
@@ -407,6 +416,58 @@ void gather_conv_bwd(const Tensor& x, const Tensor& pos, const Tensor& wgt, cons
                         dpos.data_ptr<float>(), dwgt.data_ptr<float>(), B, L, (int)pos.size(1), (int)H, C / (int)H, S, cur_stream());
 }
 
+
+// ---------------------------------------------------------------------------------------------- RWKV time mixing
+bool wkv_io(const Tensor& t, const char* n) {
+  TORCH_CHECK(t.is_cuda() && t.is_contiguous() && (t.scalar_type() == at::kFloat || t.scalar_type() == at::kBFloat16), n, ": contiguous fp32 or bf16 CUDA tensor");
+  return t.scalar_type() == at::kBFloat16;
+}
+void chk_f32c(const Tensor& t, const char* n) { TORCH_CHECK(t.is_cuda() && t.is_contiguous() && t.scalar_type() == at::kFloat, n, ": contiguous fp32 CUDA tensor"); }
+
+void wkv4_fwd(const Tensor& k, const Tensor& v, const Tensor& w, const Tensor& u, Tensor y) {
+  const c10::cuda::CUDAGuard guard(k.device());
+  const bool bf = wkv_io(k, "k");
+  TORCH_CHECK(k.dim() == 3 && v.sizes() == k.sizes() && y.sizes() == k.sizes() && wkv_io(v, "v") == bf && wkv_io(y, "y") == bf, "wkv4: k, v, y [B, T, C] of one dtype");
+  chk_f32c(w, "w"); chk_f32c(u, "u");
+  TORCH_CHECK(w.numel() == k.size(2) && u.numel() == k.size(2), "wkv4: w, u [C]");
+  b200::wkv4_fwd(k.data_ptr(), v.data_ptr(), w.data_ptr<float>(), u.data_ptr<float>(), y.data_ptr(), bf, (int)k.size(0), (int)k.size(1), (int)k.size(2), cur_stream());
+}
+
+void wkv4_bwd(const Tensor& k, const Tensor& v, const Tensor& w, const Tensor& u, const Tensor& gy, Tensor gk, Tensor gv, Tensor gw, Tensor gu, Tensor scratch) {
+  const c10::cuda::CUDAGuard guard(k.device());
+  const bool bf = wkv_io(k, "k");
+  TORCH_CHECK(wkv_io(v, "v") == bf && wkv_io(gy, "gy") == bf && wkv_io(gk, "gk") == bf && wkv_io(gv, "gv") == bf, "wkv4_bwd: one I/O dtype");
+  TORCH_CHECK(v.sizes() == k.sizes() && gy.sizes() == k.sizes() && gk.sizes() == k.sizes() && gv.sizes() == k.sizes(), "wkv4_bwd: [B, T, C] tensors");
+  chk_f32c(w, "w"); chk_f32c(u, "u"); chk_f32c(gw, "gw"); chk_f32c(gu, "gu"); chk_f32c(scratch, "scratch");
+  const int64_t B = k.size(0), T = k.size(1), C = k.size(2);
+  TORCH_CHECK(gw.numel() == B * C && gu.numel() == B * C && scratch.numel() == 3 * B * T * C, "wkv4_bwd: gw, gu [B, C]; scratch [3, B, T, C]");
+  b200::wkv4_bwd(k.data_ptr(), v.data_ptr(), w.data_ptr<float>(), u.data_ptr<float>(), gy.data_ptr(), gk.data_ptr(), gv.data_ptr(),
+                 gw.data_ptr<float>(), gu.data_ptr<float>(), scratch.data_ptr<float>(), bf, (int)B, (int)T, (int)C, cur_stream());
+}
+
+void wkv5_fwd(const Tensor& r, const Tensor& k, const Tensor& v, const Tensor& w, const Tensor& u, Tensor y) {
+  const c10::cuda::CUDAGuard guard(r.device());
+  const bool bf = wkv_io(r, "r");
+  TORCH_CHECK(r.dim() == 3 && k.sizes() == r.sizes() && v.sizes() == r.sizes() && y.sizes() == r.sizes(), "wkv5: r, k, v, y [B, T, C]");
+  TORCH_CHECK(wkv_io(k, "k") == bf && wkv_io(v, "v") == bf && wkv_io(y, "y") == bf, "wkv5: one I/O dtype");
+  chk_f32c(w, "w"); chk_f32c(u, "u");
+  TORCH_CHECK(w.dim() == 2 && u.sizes() == w.sizes() && w.numel() == r.size(2), "wkv5: w, u [H, N] with H * N == C");
+  b200::wkv5_fwd(r.data_ptr(), k.data_ptr(), v.data_ptr(), w.data_ptr<float>(), u.data_ptr<float>(), y.data_ptr(), bf, (int)r.size(0),
+                 (int)r.size(1), (int)w.size(0), (int)w.size(1), cur_stream());
+}
+
+void wkv5_bwd(const Tensor& r, const Tensor& k, const Tensor& v, const Tensor& w, const Tensor& u, const Tensor& gy, Tensor gr, Tensor gk,
+              Tensor gv, Tensor gw, Tensor gu) {
+  const c10::cuda::CUDAGuard guard(r.device());
+  const bool bf = wkv_io(r, "r");
+  for (const Tensor* t : std::initializer_list<const Tensor*>{&k, &v, &gy, &gr, &gk, &gv})
+    TORCH_CHECK(wkv_io(*t, "wkv5_bwd tensor") == bf && t->sizes() == r.sizes(), "wkv5_bwd: [B, T, C] tensors of one dtype");
+  chk_f32c(w, "w"); chk_f32c(u, "u"); chk_f32c(gw, "gw"); chk_f32c(gu, "gu");
+  TORCH_CHECK(w.dim() == 2 && w.numel() == r.size(2) && gw.numel() == r.size(0) * r.size(2) && gu.numel() == gw.numel(), "wkv5_bwd: w [H, N]; gw, gu [B, C]");
+  b200::wkv5_bwd(r.data_ptr(), k.data_ptr(), v.data_ptr(), w.data_ptr<float>(), u.data_ptr<float>(), gy.data_ptr(), gr.data_ptr(),
+                 gk.data_ptr(), gv.data_ptr(), gw.data_ptr<float>(), gu.data_ptr<float>(), bf, (int)r.size(0), (int)r.size(1),
+                 (int)w.size(0), (int)w.size(1), cur_stream());
+}
 }  // namespace
 
 TORCH_LIBRARY(b200, m) {
@@ -435,12 +496,16 @@ TORCH_LIBRARY(b200, m) {
   m.def("ag_push(Tensor src, int[] u_full_ptrs, int rank, int dst_off, int[] peer_flags, int channel, int epoch) -> ()");
   m.def("ag_wait_apply(Tensor(a!) p, Tensor u, Tensor(b!)? p_bf16, float alpha, int world, Tensor flags, int channel, int epoch, Tensor(c!) status) -> ()");
   m.def("allreduce_mean(int[] buf_ptrs, int rank, int n, int dtype, Tensor flags, int[] peer_flags, int channel, int epoch, Tensor(a!) status) -> ()");
-  m.def("s6_scan_fwd(Tensor u, Tensor delta, Tensor A, Tensor Bm, Tensor Cm, Tensor? Dv, Tensor? z, Tensor(a!)? y_pre, Tensor(b!) out, Tensor(c!)? chunk_state) -> ()");
-  m.def("s6_scan_bwd(Tensor u, Tensor delta, Tensor A, Tensor Bm, Tensor Cm, Tensor? Dv, Tensor dy, Tensor chunk_state, Tensor(a!) du, Tensor(b!) ddelta, Tensor(c!) dA, Tensor(d!) dB_part, Tensor(e!) dC_part, Tensor(f!)? dD) -> ()");
+  m.def("s6_scan_fwd(Tensor u, Tensor delta, Tensor? delta_bias, bool softplus, Tensor A, Tensor Bm, Tensor Cm, Tensor? Dv, Tensor? z, Tensor(a!)? y_pre, Tensor(b!) out, Tensor(c!)? state) -> ()");
+  m.def("s6_scan_bwd(Tensor u, Tensor delta, Tensor? delta_bias, bool softplus, Tensor A, Tensor Bm, Tensor Cm, Tensor? Dv, Tensor? z, Tensor? y_pre, Tensor dout, Tensor state, Tensor(a!) du, Tensor(b!) ddelta, Tensor(c!) dA, Tensor(d!) dB_part, Tensor(e!) dC_part, Tensor(f!)? dD, Tensor(g!)? dz, Tensor(h!)? ddelta_bias) -> ()");
   m.def("causal_conv1d_silu_fwd(Tensor x, Tensor w, Tensor? bias, Tensor(a!) y) -> ()");
   m.def("causal_conv1d_silu_bwd(Tensor x, Tensor w, Tensor? bias, Tensor dy, Tensor(a!) dx, Tensor(b!) dw, Tensor(c!)? dbias) -> ()");
   m.def("gather_conv_fwd(Tensor x, Tensor pos, Tensor wgt, Tensor(a!) out, int H) -> ()");
   m.def("gather_conv_bwd(Tensor x, Tensor pos, Tensor wgt, Tensor dout, Tensor(a!) dx, Tensor(b!) dpos, Tensor(c!) dwgt, int H) -> ()");
+  m.def("wkv4_fwd(Tensor k, Tensor v, Tensor w, Tensor u, Tensor(a!) y) -> ()");
+  m.def("wkv4_bwd(Tensor k, Tensor v, Tensor w, Tensor u, Tensor gy, Tensor(a!) gk, Tensor(b!) gv, Tensor(c!) gw, Tensor(d!) gu, Tensor(e!) scratch) -> ()");
+  m.def("wkv5_fwd(Tensor r, Tensor k, Tensor v, Tensor w, Tensor u, Tensor(a!) y) -> ()");
+  m.def("wkv5_bwd(Tensor r, Tensor k, Tensor v, Tensor w, Tensor u, Tensor gy, Tensor(a!) gr, Tensor(b!) gk, Tensor(c!) gv, Tensor(d!) gw, Tensor(e!) gu) -> ()");
   // <<DEFS>>
 }
 
@@ -474,5 +539,9 @@ TORCH_LIBRARY_IMPL(b200, CUDA, m) {
   m.impl("causal_conv1d_silu_bwd", &causal_conv1d_silu_bwd);
   m.impl("gather_conv_fwd", &gather_conv_fwd);
   m.impl("gather_conv_bwd", &gather_conv_bwd);
+  m.impl("wkv4_fwd", &wkv4_fwd);
+  m.impl("wkv4_bwd", &wkv4_bwd);
+  m.impl("wkv5_fwd", &wkv5_fwd);
+  m.impl("wkv5_bwd", &wkv5_bwd);
   // <<IMPLS>>
 }

@@ -1,24 +1,28 @@
 // S6 selective scan (torch-free interface). Tensors are channel-last:
-//   u, z, y_pre, out, dy, du : bf16 [B][L][Din]      delta, ddelta : fp32 [B][L][Din]
-//   Bm, Cm : fp32 [B][L][N]    A, dA : fp32 [Din][N]    Dv, dD : fp32 [Din]     N must be 16
-//   chunk_state : fp32 [B][ceil(L/64)][Din][N], state at the start of every 64-step chunk (forward writes it)
-//   dB_part, dC_part : fp32 [B][ceil(Din/16)][L][N] partial sums over 16-channel blocks (the caller sums dim 1)
+//   u, z, y_pre, out, dout, du, dz : bf16 [B][L][Din]      delta, ddelta : fp32 or bf16 [B][L][Din] (delta_bf16)
+//   Bm, Cm : fp32 [B][L][N]    A, dA : fp32 [Din][N]    Dv, dD, delta_bias, ddelta_bias : fp32 [Din]     N must be 16
+//   With `softplus` the step is softplus(delta + delta_bias) and ddelta / ddelta_bias are gradients of the raw values.
+//   state : fp32 [B][ceil(L/16)][4][Din][4], the state at the start of every 16-step tile, states grouped in fours
+//           (the forward writes it, the backward reads it)
+//   dB_part, dC_part : fp32 [B][ceil(Din/32)][L][N] partial sums over 32-channel blocks (the caller sums dim 1)
 #pragma once
 #include <cuda_runtime.h>
 
 namespace b200 {
 
-int s6_channel_blocks(int Din);
-int s6_num_chunks(int L);
+int s6_channel_blocks(int Din);  // ceil(Din / 32)
+int s6_num_chunks(int L);        // ceil(L / 16)
 
-void s6_scan_fwd(const void* u, const float* delta, const float* A, const float* Bm, const float* Cm, const float* Dv,
-                 const void* z, void* y_pre, void* out, float* chunk_state, int batch, int L, int Din, int N,
-                 cudaStream_t s);
+void s6_scan_fwd(const void* u, const void* delta, bool delta_bf16, const float* delta_bias, bool softplus, const float* A,
+                 const float* Bm, const float* Cm, const float* Dv, const void* z, void* y_pre, void* out,
+                 float* state, int batch, int L, int Din, int N, cudaStream_t s);
 
-// dy: gradient with respect to y_pre (before the silu(z) gate). dA and dD are accumulated into (zero them first).
-void s6_scan_bwd(const void* u, const float* delta, const float* A, const float* Bm, const float* Cm, const float* Dv,
-                 const void* dy, const float* chunk_state, void* du, float* ddelta, float* dA, float* dB_part,
-                 float* dC_part, float* dD, int batch, int L, int Din, int N, cudaStream_t s);
+// dout: gradient of `out`. With z the gate's backward runs inside (needs y_pre; dz is written when non-null).
+// dA, dD and ddelta_bias are accumulated into (zero them first).
+void s6_scan_bwd(const void* u, const void* delta, bool delta_bf16, const float* delta_bias, bool softplus, const float* A,
+                 const float* Bm, const float* Cm, const float* Dv, const void* z, const void* y_pre, const void* dout,
+                 const float* state, void* du, void* ddelta, float* dA, float* dB_part, float* dC_part, float* dD,
+                 void* dz, float* ddelta_bias, int batch, int L, int Din, int N, cudaStream_t s);
 
 }  // namespace b200
 

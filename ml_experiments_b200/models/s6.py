@@ -83,8 +83,8 @@ class S6Mixer(nn.Module):
         xi = causal_conv1d_silu(xi, self.conv1d.weight, self.conv1d.bias)
         dbc = linear(xi, self.x_proj.weight)
         dt, Bm, Cm = torch.split(dbc, [cfg.rank, cfg.d_state, cfg.d_state], dim=-1)
-        delta = F.softplus(linear(dt, self.dt_proj.weight).float() + self.dt_proj.bias.float())
-        y = selective_scan(xi.contiguous(), delta, -torch.exp(self.A_log.float()), Bm, Cm, self.D, z.contiguous())
+        y = selective_scan(xi.contiguous(), linear(dt, self.dt_proj.weight), -torch.exp(self.A_log.float()), Bm, Cm, self.D,
+                           z.contiguous(), delta_bias=self.dt_proj.bias, delta_softplus=True)
         return linear(y, self.out_proj.weight)
 
 

@@ -1,0 +1,175 @@
+"""Single-operator benchmark: ``python -m ml_experiments_b200.ops.microbench <op> [sizes]`` prints one JSON line.
+
+Times one of the hand-written kernels (CUDA events on the launching stream, warm-up, L2 flushed between iterations by
+writing a 256 MB buffer) and reports achieved FLOP/s or bytes/s against the measured peaks in ``MEASURED_PEAKS.json`` at
+the repository root when present (6.65 TB/s and 1.59 PFLOP/s otherwise). The same command line with ``--iters 1
+--warmup 0`` is what the profiler captures are taken on. The reference ships comparable sweep scripts for its own
+operators (scripts/bench_crossover.py, scripts/benchmark_scatter_attention.py).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+from pathlib import Path
+
+import torch
+
+
+def _peaks() -> dict:
+    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def _time(fn, iters: int, warmup: int, flush: bool = True) -> float:
+    scratch = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        if flush:
+            scratch.fill_(1)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        total += s.elapsed_time(e)
+    return total / iters
+
+
+def _doc_bounds(t: int, doc_len: int):
+    idx = torch.arange(t, device="cuda", dtype=torch.int32)
+    if doc_len <= 0:
+        return torch.zeros_like(idx), torch.full_like(idx, t)
+    start = idx // doc_len * doc_len
+    return start, (start + doc_len).clamp(max=t)
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("op", choices=["gemm", "attn_fwd", "attn_bwd", "softcap_ce", "s6_fwd", "s6_bwd", "gather_fwd", "gather_bwd",
+                                   "newton_schulz", "ssd"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--tokens", type=int, default=16384)
+    ap.add_argument("--heads", type=int, default=6)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--window-blocks", type=int, default=0)
+    ap.add_argument("--doc-len", type=int, default=0)
+    ap.add_argument("--vocab", type=int, default=50304)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--seq", type=int, default=4096)
+    ap.add_argument("--channels", type=int, default=2048)
+    ap.add_argument("--taps", type=int, default=16)
+    ap.add_argument("--epilogue", default="none", choices=["none", "relu2", "axpby"])
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    a = ap.parse_args(argv)
+    from . import gemm as G
+    from .runtime import check_status
+    dev, bf = "cuda", torch.bfloat16
+    flops = bytes_ = 0.0
+    if a.op == "gemm":
+        x = torch.randn(a.m, a.k, device=dev, dtype=bf)
+        w = torch.randn(a.n, a.k, device=dev, dtype=bf)
+        out = torch.empty(a.m, a.n, device=dev, dtype=bf)
+        aux = torch.randn(a.m, a.n, device=dev, dtype=bf) if a.epilogue == "axpby" else None
+        epi = {"none": G.EPI_NONE, "relu2": G.EPI_RELU2, "axpby": G.EPI_AXPBY}[a.epilogue]
+        fn = lambda: G.gemm(x, w, out=out, epilogue=epi, aux=aux, beta=1.0 if aux is not None else 0.0)
+        flops = 2.0 * a.m * a.n * a.k
+        bytes_ = 2.0 * (a.m * a.k + a.n * a.k + a.m * a.n * (2 if aux is not None else 1))
+    elif a.op in ("attn_fwd", "attn_bwd"):
+        from . import attention as A
+        t, h, d = a.tokens, a.heads, a.head_dim
+        q, k, v = (torch.randn(t, h, d, device=dev, dtype=bf) for _ in range(3))
+        ds, de = _doc_bounds(t, a.doc_len)
+        scale = d ** -0.5
+        o, lse = A.flash_attention_forward(q, k, v, ds, de, scale, a.window_blocks)
+        span = t if a.window_blocks <= 0 else min(t, a.window_blocks * 128)
+        if a.doc_len > 0:
+            span = min(span, a.doc_len)
+        pairs = t * span / (2.0 if span == t else 1.0)  # causal: half the square, or a band
+        if a.op == "attn_fwd":
+            fn = lambda: A.flash_attention_forward(q, k, v, ds, de, scale, a.window_blocks)
+            flops = 4.0 * pairs * h * d
+        else:
+            do = torch.randn_like(o)
+            dq = torch.zeros(t, h, d, device=dev, dtype=torch.float32)
+            fn = lambda: A.flash_attention_backward(q, k, v, o, do, lse, ds, de, scale, a.window_blocks, dq_acc=dq)
+            flops = 10.0 * pairs * h * d
+        bytes_ = 2.0 * 4 * t * h * d
+    elif a.op == "softcap_ce":
+        from . import fused as Fz
+        logits = torch.randn(a.tokens, a.vocab, device=dev, dtype=bf)
+        tgt = torch.randint(0, a.vocab, (a.tokens,), device=dev, dtype=torch.int64)
+        grad = torch.empty_like(logits)
+        fn = lambda: Fz.softcap_ce(logits, tgt, grad_out=grad)
+        bytes_ = 2.0 * 2 * a.tokens * a.vocab
+    elif a.op in ("s6_fwd", "s6_bwd"):
+        from .selective_scan import selective_scan
+        b, L, d, n = a.batch, a.seq, a.channels, 16
+        u = torch.randn(b, L, d, device=dev, dtype=bf, requires_grad=True)
+        delta = (torch.rand(b, L, d, device=dev) * 0.1).requires_grad_(True)
+        A_ = -torch.rand(d, n, device=dev).requires_grad_(True)
+        Bm, Cm = (torch.randn(b, L, n, device=dev, requires_grad=True) for _ in range(2))
+        D = torch.ones(d, device=dev, requires_grad=True)
+        z = torch.randn(b, L, d, device=dev, dtype=bf, requires_grad=True)
+        if a.op == "s6_fwd":
+            fn = lambda: selective_scan(u.detach(), delta.detach(), A_.detach(), Bm.detach(), Cm.detach(), D.detach(), z.detach())
+            bytes_ = b * L * d * (2 + 4 + 2 + 2 + 2.0)
+        else:
+            y = selective_scan(u, delta, A_, Bm, Cm, D, z)
+            g = torch.randn_like(y)
+            fn = lambda: torch.autograd.grad(y, (u, delta, A_, Bm, Cm, D, z), g, retain_graph=True)
+            bytes_ = b * L * d * (2 + 4 + 2 + 2 + 2 + 2 + 4 + 2.0)
+        flops = 9.0 * b * L * d * n
+    elif a.op in ("gather_fwd", "gather_bwd"):
+        from .gather_conv import gather_conv
+        b, L, c, h, s = a.batch, a.seq, a.channels, a.heads, a.taps
+        x = torch.randn(b, L, c, device=dev, dtype=bf, requires_grad=True)
+        pos = (torch.rand(b, L, h, s, device=dev) * (L - 1)).requires_grad_(True)
+        wgt = torch.rand(b, L, h, s, device=dev, requires_grad=True)
+        if a.op == "gather_fwd":
+            fn = lambda: gather_conv(x.detach(), pos.detach(), wgt.detach(), h)
+        else:
+            y = gather_conv(x, pos, wgt, h)
+            g = torch.randn_like(y)
+            fn = lambda: torch.autograd.grad(y, (x, pos, wgt), g, retain_graph=True)
+        bytes_ = b * L * (2.0 * c * (1 + 2 * s) + 8.0 * h * s)  # every tap reads two rows of its head
+    elif a.op == "newton_schulz":
+        from .newton_schulz import newton_schulz_
+        X = torch.randn(a.batch, a.m, a.n, device=dev, dtype=bf)
+        X /= X.norm(dim=(1, 2), keepdim=True)
+        work: dict = {}
+        fn = lambda: newton_schulz_(X.clone(), work=work)
+        small, big = min(a.m, a.n), max(a.m, a.n)
+        flops = 5 * a.batch * (2.0 * small * small * big * 2 + 2.0 * small ** 3)
+    else:  # ssd
+        from .ssd_scan import ssd_chunk_scan
+        b, L, h, p, n = a.batch, a.seq, a.heads, a.head_dim, 64
+        x = torch.randn(b, L, h, p, device=dev, dtype=bf)
+        Bm, Cm = (torch.randn(b, L, h, n, device=dev, dtype=bf) for _ in range(2))
+        la = -torch.rand(b, L, h, device=dev) * 0.1
+        gm = torch.rand(b, L, h, device=dev)
+        fn = lambda: ssd_chunk_scan(x, Bm, Cm, la, gm)
+        flops = 2.0 * b * L * h * (64 * n + 64 * p + 2 * n * p)
+    ms = _time(fn, a.iters, a.warmup)
+    check_status()
+    pk = _peaks()
+    out = {"op": a.op, "ms": round(ms, 4), "args": {k: v for k, v in vars(a).items() if k != "op"}, "peaks": pk["source"]}
+    if flops:
+        out["tflops"] = round(flops / ms / 1e9, 1)
+        out["frac_of_bf16_peak"] = round(flops / ms / 1e9 / pk["bf16_tflops"], 3)
+    if bytes_:
+        out["gbs"] = round(bytes_ / ms / 1e6, 1)
+        out["frac_of_hbm_peak"] = round(bytes_ / ms / 1e6 / pk["hbm_gbs"], 3)
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,4 +1,4 @@
-"""S6 selective scan: CUDA kernels (chunk 64, state 16) with autograd, plus the plain-torch restatement.
+"""S6 selective scan: CUDA kernels (tiles of 16 steps, state 16) with autograd, plus the plain-torch restatement.
 
 Interface mirrors ``selective_scan_fn`` / ``selective_scan_ref`` of the reference
 (zoology/mixers/mamba_ssm/ops/selective_scan_interface.py:19-157) but channel-last: ``u, delta, z`` are ``[B, L, Din]``,
@@ -38,60 +38,55 @@ def selective_scan_ref(u, delta, A, B, C, D=None, z=None, delta_bias=None, delta
 
 
 class _S6Scan(torch.autograd.Function):
+    """CUDA path: softplus / bias / gate and their backward all run inside the two kernels."""
+
     @staticmethod
-    def forward(ctx, u, delta, A, B, C, D, z):
+    def forward(ctx, u, delta, A, B, C, D, z, delta_bias, delta_softplus):
         o = ops()
         bsz, L, din = u.shape
         n = A.shape[1]
         u16 = u.to(torch.bfloat16).contiguous()
         z16 = None if z is None else z.to(torch.bfloat16).contiguous()
-        d32, A32 = delta.float().contiguous(), A.float().contiguous()
+        d32 = (delta if delta.dtype == torch.bfloat16 else delta.float()).contiguous()  # raw step, bf16 or fp32
+        A32 = A.float().contiguous()
         B32, C32 = B.float().contiguous(), C.float().contiguous()
         D32 = None if D is None else D.float().contiguous()
-        nch = (L + 63) // 64
-        state = torch.empty(bsz, nch, din, n, dtype=torch.float32, device=u.device)
-        y_pre = torch.empty_like(u16)
+        b32 = None if delta_bias is None else delta_bias.float().contiguous()
+        need_grad = any(t is not None and t.requires_grad for t in (u, delta, A, B, C, D, z, delta_bias))
+        state = torch.empty(bsz, (L + 15) // 16, 4, din, 4, dtype=torch.float32, device=u.device) if need_grad else None
+        y_pre = torch.empty_like(u16) if (need_grad and z16 is not None) else None
         out = torch.empty_like(u16)
-        o.s6_scan_fwd(u16, d32, A32, B32, C32, D32, z16, y_pre, out, state)
-        ctx.save_for_backward(u16, d32, A32, B32, C32, D32, z16, y_pre, state)
-        ctx.dtypes = (u.dtype, delta.dtype, A.dtype, B.dtype, C.dtype, None if D is None else D.dtype,
-                      None if z is None else z.dtype)
+        o.s6_scan_fwd(u16, d32, b32, bool(delta_softplus), A32, B32, C32, D32, z16, y_pre, out, state)
+        ctx.save_for_backward(u16, d32, b32, A32, B32, C32, D32, z16, y_pre, state)
+        ctx.softplus = bool(delta_softplus)
+        ctx.dtypes = tuple(None if t is None else t.dtype for t in (u, delta, A, B, C, D, z, delta_bias))
         return out.to(u.dtype)
 
     @staticmethod
     def backward(ctx, dout):
         o = ops()
-        u16, d32, A32, B32, C32, D32, z16, y_pre, state = ctx.saved_tensors
+        u16, d32, b32, A32, B32, C32, D32, z16, y_pre, state = ctx.saved_tensors
         bsz, L, din = u16.shape
         n = A32.shape[1]
-        dout = dout.float()
-        dz = None
-        if z16 is not None:
-            zf = z16.float()
-            sig = torch.sigmoid(zf)
-            dz = dout * y_pre.float() * (sig * (1 + zf * (1 - sig)))
-            dy = (dout * zf * sig).to(torch.bfloat16).contiguous()
-        else:
-            dy = dout.to(torch.bfloat16).contiguous()
-        nblk = (din + 15) // 16
+        dev = u16.device
         du = torch.empty_like(u16)
         ddelta = torch.empty_like(d32)
         dA = torch.zeros_like(A32)
-        dBp = torch.empty(bsz, nblk, L, n, dtype=torch.float32, device=u16.device)
+        dBp = torch.empty(bsz, (din + 31) // 32, L, n, dtype=torch.float32, device=dev)
         dCp = torch.empty_like(dBp)
         dD = None if D32 is None else torch.zeros_like(D32)
-        o.s6_scan_bwd(u16, d32, A32, B32, C32, D32, dy, state, du, ddelta, dA, dBp, dCp, dD)
+        dz = None if z16 is None else torch.empty_like(z16)
+        dbias = None if b32 is None else torch.zeros_like(b32)
+        o.s6_scan_bwd(u16, d32, b32, ctx.softplus, A32, B32, C32, D32, z16, y_pre, dout.to(torch.bfloat16).contiguous(), state,
+                      du, ddelta, dA, dBp, dCp, dD, dz, dbias)
         t = ctx.dtypes
-        return (du.to(t[0]), ddelta.to(t[1]), dA.to(t[2]), dBp.sum(1).to(t[3]), dCp.sum(1).to(t[4]),
-                None if dD is None else dD.to(t[5]), None if dz is None else dz.to(t[6]))
+        cast = lambda g, dt: None if g is None else g.to(dt)
+        return (cast(du, t[0]), cast(ddelta, t[1]), cast(dA, t[2]), cast(dBp.sum(1), t[3]), cast(dCp.sum(1), t[4]), cast(dD, t[5]),
+                cast(dz, t[6]), cast(dbias, t[7]), None)
 
 
 def selective_scan(u, delta, A, B, C, D=None, z=None, delta_bias=None, delta_softplus=False):
     """Differentiable S6 scan; CUDA kernels when ``u`` is on a GPU and ``N == 16``, the oracle otherwise."""
     if not u.is_cuda or A.shape[1] != 16:
         return selective_scan_ref(u, delta, A, B, C, D, z, delta_bias, delta_softplus)
-    if delta_bias is not None:
-        delta = delta + delta_bias
-    if delta_softplus:
-        delta = F.softplus(delta.float())
-    return _S6Scan.apply(u, delta, A, B, C, D, z)
+    return _S6Scan.apply(u, delta, A, B, C, D, z, delta_bias, delta_softplus)

@@ -1,0 +1,74 @@
+"""Small helpers: import-by-string, seeding, flatten / unflatten of nested dictionaries (zoology/utils.py:8-36 and the
+wandb table helpers of the reference)."""
+from __future__ import annotations
+
+import importlib
+import random
+from typing import Callable, Union
+
+import numpy as np
+import torch
+
+# reference module paths keep working in configs written for the vendored package
+_ALIASES = {"zoology.": "ml_experiments_b200.zoology."}
+
+
+def import_from_str(path: str) -> Union[type, Callable]:
+    """``"pkg.module.Name"`` -> the object; paths starting with ``zoology.`` resolve inside this package."""
+    for old, new in _ALIASES.items():
+        if path.startswith(old):
+            path = new + path[len(old):]
+    module_name, obj_name = path.rsplit(".", 1)
+    try:
+        module = importlib.import_module(module_name)
+    except ImportError as e:
+        raise ImportError(f"Module '{module_name}' not found.") from e
+    try:
+        return getattr(module, obj_name)
+    except AttributeError as e:
+        raise AttributeError(f"Class '{obj_name}' not found in module '{module_name}'.") from e
+
+
+def set_determinism(seed: int) -> None:
+    random.seed(seed)
+    np.random.seed(seed)
+    torch.manual_seed(seed)
+    if torch.cuda.is_available():
+        torch.cuda.manual_seed(seed)
+
+
+def flatten(data, parent_key: str | None = None, sep: str = ".") -> dict:
+    """``{"a": {"b": 1}, "f": [4, 5]}`` -> ``{"a.b": 1, "f.0": 4, "f.1": 5}``."""
+    items = {}
+    if isinstance(data, (list, tuple)):
+        pairs = ((str(i), v) for i, v in enumerate(data))
+    elif isinstance(data, dict):
+        pairs = data.items()
+    else:
+        return {parent_key: data}
+    for k, v in pairs:
+        items.update(flatten(v, k if parent_key is None else f"{parent_key}{sep}{k}", sep))
+    return items
+
+
+def unflatten(d: dict, sep: str = ".") -> dict:
+    """Inverse of ``flatten``; dictionaries whose keys are ``0..n-1`` become lists; NaN values are dropped."""
+    root: dict = {}
+    for key, value in d.items():
+        if isinstance(value, float) and np.isnan(value):
+            continue
+        node = root
+        parts = key.split(sep)
+        for part in parts[:-1]:
+            node = node.setdefault(part, {})
+        node[parts[-1]] = value
+
+    def listify(node):
+        if not isinstance(node, dict):
+            return node
+        node = {k: listify(v) for k, v in node.items()}
+        if node and all(k.isdigit() for k in node) and sorted(int(k) for k in node) == list(range(len(node))):
+            return [node[str(i)] for i in range(len(node))]
+        return node
+
+    return listify(root)

@@ -33,6 +33,38 @@ def test_scan_forward_backward(bsz, L, din):
         assert rel < 3e-2, (name, rel)
 
 
+@pytest.mark.parametrize("delta_dtype", [torch.float32, torch.bfloat16])
+def test_scan_fused_softplus_bias_gate(delta_dtype):
+    """Raw step + bias + softplus and the silu(z) gate run inside the kernels; gradients reach the raw step and the bias."""
+    from ml_experiments_b200.ops.selective_scan import selective_scan, selective_scan_ref
+
+    torch.manual_seed(1)
+    bsz, L, din, n, dev = 2, 150, 100, 16, "cuda"
+    u = torch.randn(bsz, L, din, device=dev).bfloat16().float().requires_grad_(True)
+    raw = (torch.randn(bsz, L, din, device=dev) - 3).to(delta_dtype).float().requires_grad_(True)
+    bias = torch.randn(din, device=dev).requires_grad_(True)
+    A = (-torch.rand(din, n, device=dev) * 4 - 0.2).requires_grad_(True)
+    B = torch.randn(bsz, L, n, device=dev).requires_grad_(True)
+    C = torch.randn(bsz, L, n, device=dev).requires_grad_(True)
+    z = torch.randn(bsz, L, din, device=dev).bfloat16().float().requires_grad_(True)
+    g = torch.randn(bsz, L, din, device=dev)
+    leaves = (u, raw, bias, A, B, C, z)
+    ref = selective_scan_ref(u, raw, A, B, C, None, z, delta_bias=bias, delta_softplus=True)
+    ref.backward(g)
+    want = [t.grad.clone() for t in leaves]
+    for t in leaves:
+        t.grad = None
+    raw_in = raw.to(delta_dtype)
+    raw_in.retain_grad()
+    out = selective_scan(u, raw_in, A, B, C, None, z, delta_bias=bias, delta_softplus=True)
+    assert ((out - ref).abs().max() / ref.abs().max()).item() < 2e-2
+    out.backward(g)
+    tol = 3e-2 if delta_dtype == torch.float32 else 5e-2
+    for name, t, w in zip("u raw bias A B C z".split(), leaves, want):
+        rel = ((t.grad.float() - w).norm() / (w.norm() + 1e-9)).item()
+        assert rel < tol, (name, rel)
+
+
 def test_s6_lm_trains():
     from ml_experiments_b200.models.s6 import S6Config, S6LM
 
