@@ -11,6 +11,7 @@
 #include "gather/gather_conv.h"
 #include "gemm/gemm.h"
 #include "scan/s6_scan.h"
+#include "window/window_attn.h"
 #include "wkv/wkv.h"
 
 namespace {
@@ -468,6 +469,30 @@ void wkv5_bwd(const Tensor& r, const Tensor& k, const Tensor& v, const Tensor& w
                  gk.data_ptr(), gv.data_ptr(), gw.data_ptr<float>(), gu.data_ptr<float>(), bf, (int)r.size(0), (int)r.size(1),
                  (int)w.size(0), (int)w.size(1), cur_stream());
 }
+
+// ---------------------------------------------------------------------------------------------- local window attention
+void window_attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& bias, Tensor out, Tensor P, double scale) {
+  const c10::cuda::CUDAGuard guard(q.device());
+  chk_bf16c(q, "q"); chk_bf16c(k, "k"); chk_bf16c(v, "v"); chk_bf16c(out, "out"); chk_f32c(bias, "bias"); chk_f32c(P, "P");
+  TORCH_CHECK(q.dim() == 4 && k.sizes() == q.sizes() && v.sizes() == q.sizes() && out.sizes() == q.sizes(), "window_attn: q, k, v, out [B, L, H, D]");
+  TORCH_CHECK(bias.dim() == 4 && bias.size(0) == q.size(0) && bias.size(1) == q.size(1) && bias.size(2) == q.size(2) && P.sizes() == bias.sizes(), "window_attn: bias, P [B, L, H, K]");
+  b200::window_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), bias.data_ptr<float>(), out.data_ptr(), P.data_ptr<float>(), (float)scale,
+                        (int)q.size(0), (int)q.size(1), (int)q.size(2), (int)q.size(3), (int)bias.size(3), cur_stream());
+}
+
+void window_attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& P, const Tensor& dout, Tensor dq, Tensor dk, Tensor dv,
+                     Tensor dbias, double scale) {
+  const c10::cuda::CUDAGuard guard(q.device());
+  for (const Tensor* t : std::initializer_list<const Tensor*>{&q, &k, &v, &dout, &dq, &dk, &dv}) {
+    chk_bf16c(*t, "window_attn_bwd tensor");
+    TORCH_CHECK(t->sizes() == q.sizes(), "window_attn_bwd: [B, L, H, D] tensors");
+  }
+  chk_f32c(P, "P"); chk_f32c(dbias, "dbias");
+  TORCH_CHECK(P.dim() == 4 && dbias.sizes() == P.sizes(), "window_attn_bwd: P, dbias [B, L, H, K]");
+  b200::window_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), P.data_ptr<float>(), dout.data_ptr(), dq.data_ptr(), dk.data_ptr(),
+                        dv.data_ptr(), dbias.data_ptr<float>(), (float)scale, (int)q.size(0), (int)q.size(1), (int)q.size(2), (int)q.size(3),
+                        (int)P.size(3), cur_stream());
+}
 }  // namespace
 
 TORCH_LIBRARY(b200, m) {
@@ -506,6 +531,8 @@ TORCH_LIBRARY(b200, m) {
   m.def("wkv4_bwd(Tensor k, Tensor v, Tensor w, Tensor u, Tensor gy, Tensor(a!) gk, Tensor(b!) gv, Tensor(c!) gw, Tensor(d!) gu, Tensor(e!) scratch) -> ()");
   m.def("wkv5_fwd(Tensor r, Tensor k, Tensor v, Tensor w, Tensor u, Tensor(a!) y) -> ()");
   m.def("wkv5_bwd(Tensor r, Tensor k, Tensor v, Tensor w, Tensor u, Tensor gy, Tensor(a!) gr, Tensor(b!) gk, Tensor(c!) gv, Tensor(d!) gw, Tensor(e!) gu) -> ()");
+  m.def("window_attn_fwd(Tensor q, Tensor k, Tensor v, Tensor bias, Tensor(a!) out, Tensor(b!) P, float scale) -> ()");
+  m.def("window_attn_bwd(Tensor q, Tensor k, Tensor v, Tensor P, Tensor dout, Tensor(a!) dq, Tensor(b!) dk, Tensor(c!) dv, Tensor(d!) dbias, float scale) -> ()");
   // <<DEFS>>
 }
 
@@ -543,5 +570,7 @@ TORCH_LIBRARY_IMPL(b200, CUDA, m) {
   m.impl("wkv4_bwd", &wkv4_bwd);
   m.impl("wkv5_fwd", &wkv5_fwd);
   m.impl("wkv5_bwd", &wkv5_bwd);
+  m.impl("window_attn_fwd", &window_attn_fwd);
+  m.impl("window_attn_bwd", &window_attn_bwd);
   // <<IMPLS>>
 }

@@ -46,13 +46,13 @@ gather_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ pos, con
   const bf16* xb = x + (long long)b * L * H * D + h * D + sub * 4;
   const float* pr = pos + row * S;
   const float* wr = wgt + row * S;
-  const float hi = (float)L - 1.001f;
+  const float hi = (float)(L - 1);  // positions clamp into [0, L-1]; the floor row is capped at L-2 so that p = L-1 reads row L-1 exactly
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int s = 0; s < S; ++s) {
     const float w = wr[s];
     if (w == 0.f) continue;
     const float pc = fminf(fmaxf(pr[s], 0.f), hi);
-    const int fl = (int)pc;
+    const int fl = min((int)pc, max(L - 2, 0));
     const int ce = min(fl + 1, L - 1);
     const float fr = pc - (float)fl;
     const float4 a = ld4(xb + (long long)fl * H * D), c = ld4(xb + (long long)ce * H * D);
@@ -81,13 +81,13 @@ gather_bwd_kernel(const bf16* __restrict__ x, const float* __restrict__ pos, con
   float* dxb = dx + (long long)b * L * H * D + h * D + sub * 4;
   const float* pr = pos + rr * S;
   const float* wr = wgt + rr * S;
-  const float hi = (float)L - 1.001f;
+  const float hi = (float)(L - 1);  // positions clamp into [0, L-1]; the floor row is capped at L-2 so that p = L-1 reads row L-1 exactly
   const float4 g = ld4(dout + rr * D + sub * 4);
   for (int s = 0; s < S; ++s) {
     const float w = wr[s];
     const float p = pr[s];
     const float pc = fminf(fmaxf(p, 0.f), hi);
-    const int fl = (int)pc;
+    const int fl = min((int)pc, max(L - 2, 0));
     const int ce = min(fl + 1, L - 1);
     const float fr = pc - (float)fl;
     const float4 a = ld4(xb + (long long)fl * H * D), c = ld4(xb + (long long)ce * H * D);

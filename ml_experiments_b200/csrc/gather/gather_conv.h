@@ -3,7 +3,7 @@
 // x : bf16 [B][L][H*D] (source)   out : bf16 [B][Lq][H*D]   pos, wgt : fp32 [B][Lq][H][S]   (Lq query rows gather from
 // the L source rows; Lq = L for a whole-sequence call, smaller for a chunk)   D in {8,16,32,64,128}
 // Backward: dwgt, dpos (fp32, same shape as wgt) and dx accumulated with vector atomics into fp32 [B][L][H*D]
-// (zero it first). Positions are clamped to [0, L - 1.001] exactly as the PyTorch modules do; a clamped tap gets no
+// (zero it first). Positions are clamped to [0, L - 1] (floor row capped at L - 2, so integer positions read exactly); a clamped tap gets no
 // position gradient.
 #pragma once
 #include <cuda_runtime.h>

@@ -41,6 +41,7 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 __device__ __forceinline__ float ld(const float* p, long long i) { return p[i]; }
 __device__ __forceinline__ float ld(const bf16* p, long long i) { return __bfloat162float(p[i]); }
 __device__ __forceinline__ void st(float* p, long long i, float v) { p[i] = v; }
@@ -77,7 +78,7 @@ s6_fwd_kernel(const bf16* __restrict__ u, const DT* __restrict__ delta, const fl
   const float bias = (dok && delta_bias) ? delta_bias[d] : 0.f;
   const float dsk = (dok && Dv) ? Dv[d] : 0.f;
   // staging registers for the next tile: the thread covers rows w + 4j of the [16][32] tiles and two B / C elements
-  float pdt[SUB / 4], pu[SUB / 4], pB[2], pC[2];
+  float pdt[SUB / 4], pu[SUB / 4], pz[SUB / 4], pB[2], pC[2];
   auto fetch = [&](int tile) {
     const int t0 = tile * SUB;
 #pragma unroll
@@ -87,6 +88,7 @@ s6_fwd_kernel(const bf16* __restrict__ u, const DT* __restrict__ delta, const fl
       const long long off = ((long long)b * L + t) * Din + d;
       pdt[j] = ok ? ld(delta, off) : 0.f;
       pu[j] = ok ? __bfloat162float(u[off]) : 0.f;
+      pz[j] = (ok && z) ? __bfloat162float(z[off]) : 0.f;
     }
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
@@ -113,6 +115,9 @@ s6_fwd_kernel(const bf16* __restrict__ u, const DT* __restrict__ delta, const fl
       s.B[i / NS][i % NS] = pB[j];
       s.C[i / NS][i % NS] = pC[j];
     }
+    float zc[SUB / 4];  // this tile's gate inputs (the staging registers are about to be refilled)
+#pragma unroll
+    for (int j = 0; j < SUB / 4; ++j) zc[j] = pz[j];
     __syncthreads();
     if (tile + 1 < nsub) fetch(tile + 1);
     if (state && dok)
@@ -141,10 +146,7 @@ s6_fwd_kernel(const bf16* __restrict__ u, const DT* __restrict__ delta, const fl
         const float yv = s.yp[0][t][lane] + s.yp[1][t][lane] + s.yp[2][t][lane] + s.yp[3][t][lane] + dsk * s.u[t][lane];
         if (y_pre) y_pre[off] = __float2bfloat16_rn(yv);
         float o = yv;
-        if (z) {
-          const float zv = __bfloat162float(z[off]);
-          o = yv * zv * sigmoidf(zv);
-        }
+        if (z) o = yv * zc[j] * sigmoidf(zc[j]);
         out[off] = __float2bfloat16_rn(o);
       }
     }
@@ -250,6 +252,26 @@ s6_bwd_kernel(const bf16* __restrict__ u, const DT* __restrict__ delta, const fl
       h04 = *reinterpret_cast<const float4*>(&state[((((long long)b * nsub + tile) * (NS / QS) + w) * Din + d) * QS]);
     const float h0[QS] = {h04.x, h04.y, h04.z, h04.w};
     __syncthreads();
+    if (tile > 0) {  // warm L2 with the rows of the tile processed next (one tile earlier in time)
+#pragma unroll
+      for (int j = 0; j < SUB / 4; ++j) {
+        const long long off = ((long long)b * L + t0 - SUB + w + 4 * j) * Din + d;
+        if (dok) {
+          prefetch_l2(delta + off);
+          prefetch_l2(u + off);
+          prefetch_l2(dout + off);
+          if (z) {
+            prefetch_l2(z + off);
+            prefetch_l2(y_pre + off);
+          }
+        }
+      }
+      if (dok) prefetch_l2(&state[((((long long)b * nsub + tile - 1) * (NS / QS) + w) * Din + d) * QS]);
+      if (tid < 2 * SUB) {
+        const long long off = ((long long)b * L + t0 - SUB + (tid >> 1)) * NS;
+        prefetch_l2((tid & 1) ? Cm + off : Bm + off);
+      }
+    }
     float hs[SUB][QS];
     {
       float hh[QS] = {h0[0], h0[1], h0[2], h0[3]};
