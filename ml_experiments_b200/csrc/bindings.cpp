@@ -395,7 +395,7 @@ void causal_conv1d_silu_bwd(const Tensor& x, const Tensor& w, const c10::optiona
 
 
 // ---------------------------------------------------------------------------------------------- gather convolution
-void gather_conv_fwd(const Tensor& x, const Tensor& pos, const Tensor& wgt, Tensor out, int64_t H) {
+void gather_conv_fwd(const Tensor& x, const Tensor& pos, const Tensor& wgt, Tensor out, int64_t H, double pos_max) {
   const c10::cuda::CUDAGuard guard(x.device());
   chk_bf16c(x, "x"); chk_bf16c(out, "out");
   TORCH_CHECK(x.dim() == 3 && pos.scalar_type() == at::kFloat && wgt.scalar_type() == at::kFloat && pos.is_contiguous() &&
@@ -403,18 +403,18 @@ void gather_conv_fwd(const Tensor& x, const Tensor& pos, const Tensor& wgt, Tens
   const int B = (int)x.size(0), L = (int)x.size(1), C = (int)x.size(2), S = (int)pos.size(3);
   const int Lq = (int)pos.size(1);
   TORCH_CHECK(pos.size(0) == B && pos.size(2) == H && C % H == 0 && out.numel() == (int64_t)B * Lq * C, "gather_conv: shape mismatch");
-  b200::gather_conv_fwd(x.data_ptr(), pos.data_ptr<float>(), wgt.data_ptr<float>(), out.data_ptr(), B, L, Lq, (int)H, C / (int)H, S, cur_stream());
+  b200::gather_conv_fwd(x.data_ptr(), pos.data_ptr<float>(), wgt.data_ptr<float>(), out.data_ptr(), B, L, Lq, (int)H, C / (int)H, S, (float)pos_max, cur_stream());
 }
 
 void gather_conv_bwd(const Tensor& x, const Tensor& pos, const Tensor& wgt, const Tensor& dout, Tensor dx, Tensor dpos,
-                     Tensor dwgt, int64_t H) {
+                     Tensor dwgt, int64_t H, double pos_max) {
   const c10::cuda::CUDAGuard guard(x.device());
   chk_bf16c(x, "x"); chk_bf16c(dout, "dout");
   TORCH_CHECK(dx.scalar_type() == at::kFloat && dx.is_contiguous() && dx.numel() == x.numel(), "dx: fp32, zeroed, x's shape");
   TORCH_CHECK(dpos.scalar_type() == at::kFloat && dwgt.scalar_type() == at::kFloat && dpos.is_contiguous() && dwgt.is_contiguous(), "dpos/dwgt: fp32");
   const int B = (int)x.size(0), L = (int)x.size(1), C = (int)x.size(2), S = (int)pos.size(3);
   b200::gather_conv_bwd(x.data_ptr(), pos.data_ptr<float>(), wgt.data_ptr<float>(), dout.data_ptr(), dx.data_ptr<float>(),
-                        dpos.data_ptr<float>(), dwgt.data_ptr<float>(), B, L, (int)pos.size(1), (int)H, C / (int)H, S, cur_stream());
+                        dpos.data_ptr<float>(), dwgt.data_ptr<float>(), B, L, (int)pos.size(1), (int)H, C / (int)H, S, (float)pos_max, cur_stream());
 }
 
 
@@ -525,8 +525,8 @@ TORCH_LIBRARY(b200, m) {
   m.def("s6_scan_bwd(Tensor u, Tensor delta, Tensor? delta_bias, bool softplus, Tensor A, Tensor Bm, Tensor Cm, Tensor? Dv, Tensor? z, Tensor? y_pre, Tensor dout, Tensor state, Tensor(a!) du, Tensor(b!) ddelta, Tensor(c!) dA, Tensor(d!) dB_part, Tensor(e!) dC_part, Tensor(f!)? dD, Tensor(g!)? dz, Tensor(h!)? ddelta_bias) -> ()");
   m.def("causal_conv1d_silu_fwd(Tensor x, Tensor w, Tensor? bias, Tensor(a!) y) -> ()");
   m.def("causal_conv1d_silu_bwd(Tensor x, Tensor w, Tensor? bias, Tensor dy, Tensor(a!) dx, Tensor(b!) dw, Tensor(c!)? dbias) -> ()");
-  m.def("gather_conv_fwd(Tensor x, Tensor pos, Tensor wgt, Tensor(a!) out, int H) -> ()");
-  m.def("gather_conv_bwd(Tensor x, Tensor pos, Tensor wgt, Tensor dout, Tensor(a!) dx, Tensor(b!) dpos, Tensor(c!) dwgt, int H) -> ()");
+  m.def("gather_conv_fwd(Tensor x, Tensor pos, Tensor wgt, Tensor(a!) out, int H, float pos_max) -> ()");
+  m.def("gather_conv_bwd(Tensor x, Tensor pos, Tensor wgt, Tensor dout, Tensor(a!) dx, Tensor(b!) dpos, Tensor(c!) dwgt, int H, float pos_max) -> ()");
   m.def("wkv4_fwd(Tensor k, Tensor v, Tensor w, Tensor u, Tensor(a!) y) -> ()");
   m.def("wkv4_bwd(Tensor k, Tensor v, Tensor w, Tensor u, Tensor gy, Tensor(a!) gk, Tensor(b!) gv, Tensor(c!) gw, Tensor(d!) gu, Tensor(e!) scratch) -> ()");
   m.def("wkv5_fwd(Tensor r, Tensor k, Tensor v, Tensor w, Tensor u, Tensor(a!) y) -> ()");

@@ -35,7 +35,7 @@ __device__ __forceinline__ float group_sum(float v) {
 template <int LPR>
 __global__ void __launch_bounds__(256)
 gather_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ pos, const float* __restrict__ wgt,
-                  bf16* __restrict__ out, int B, int L, int Lq, int H, int S) {
+                  bf16* __restrict__ out, int B, int L, int Lq, int H, int S, float pos_max) {
   constexpr int D = LPR * 4;
   const long long row = ((long long)blockIdx.x * 256 + threadIdx.x) / LPR;
   const int sub = threadIdx.x % LPR;
@@ -46,7 +46,7 @@ gather_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ pos, con
   const bf16* xb = x + (long long)b * L * H * D + h * D + sub * 4;
   const float* pr = pos + row * S;
   const float* wr = wgt + row * S;
-  const float hi = (float)(L - 1);  // positions clamp into [0, L-1]; the floor row is capped at L-2 so that p = L-1 reads row L-1 exactly
+  const float hi = pos_max;  // positions clamp into [0, pos_max]; the floor row is capped at L-2 so that p = L-1 reads row L-1 exactly
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int s = 0; s < S; ++s) {
     const float w = wr[s];
@@ -68,7 +68,7 @@ template <int LPR>
 __global__ void __launch_bounds__(256)
 gather_bwd_kernel(const bf16* __restrict__ x, const float* __restrict__ pos, const float* __restrict__ wgt,
                   const bf16* __restrict__ dout, float* __restrict__ dx, float* __restrict__ dpos,
-                  float* __restrict__ dwgt, int B, int L, int Lq, int H, int S) {
+                  float* __restrict__ dwgt, int B, int L, int Lq, int H, int S, float pos_max) {
   constexpr int D = LPR * 4;
   const long long row = ((long long)blockIdx.x * 256 + threadIdx.x) / LPR;
   const int sub = threadIdx.x % LPR;
@@ -81,7 +81,7 @@ gather_bwd_kernel(const bf16* __restrict__ x, const float* __restrict__ pos, con
   float* dxb = dx + (long long)b * L * H * D + h * D + sub * 4;
   const float* pr = pos + rr * S;
   const float* wr = wgt + rr * S;
-  const float hi = (float)(L - 1);  // positions clamp into [0, L-1]; the floor row is capped at L-2 so that p = L-1 reads row L-1 exactly
+  const float hi = pos_max;  // positions clamp into [0, pos_max]; the floor row is capped at L-2 so that p = L-1 reads row L-1 exactly
   const float4 g = ld4(dout + rr * D + sub * 4);
   for (int s = 0; s < S; ++s) {
     const float w = wr[s];
@@ -124,22 +124,22 @@ void chk(const char* what) {
 }  // namespace
 
 void gather_conv_fwd(const void* x, const float* pos, const float* wgt, void* out, int B, int L, int Lq, int H, int D,
-                     int S, cudaStream_t s) {
+                     int S, float pos_max, cudaStream_t s) {
   const long long rows = (long long)B * Lq * H;
   DISPATCH_LPR(D, {
     const int rpb = 256 / LPR_;
-    gather_fwd_kernel<LPR_><<<(unsigned)((rows + rpb - 1) / rpb), 256, 0, s>>>((const bf16*)x, pos, wgt, (bf16*)out, B, L, Lq, H, S);
+    gather_fwd_kernel<LPR_><<<(unsigned)((rows + rpb - 1) / rpb), 256, 0, s>>>((const bf16*)x, pos, wgt, (bf16*)out, B, L, Lq, H, S, pos_max);
   });
   chk("gather_conv_fwd");
 }
 
 void gather_conv_bwd(const void* x, const float* pos, const float* wgt, const void* dout, float* dx, float* dpos,
-                     float* dwgt, int B, int L, int Lq, int H, int D, int S, cudaStream_t s) {
+                     float* dwgt, int B, int L, int Lq, int H, int D, int S, float pos_max, cudaStream_t s) {
   const long long rows = (long long)B * Lq * H;
   DISPATCH_LPR(D, {
     const int rpb = 256 / LPR_;
     gather_bwd_kernel<LPR_><<<(unsigned)((rows + rpb - 1) / rpb), 256, 0, s>>>((const bf16*)x, pos, wgt, (const bf16*)dout, dx,
-                                                                              dpos, dwgt, B, L, Lq, H, S);
+                                                                              dpos, dwgt, B, L, Lq, H, S, pos_max);
   });
   chk("gather_conv_bwd");
 }

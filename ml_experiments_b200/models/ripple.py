@@ -76,6 +76,9 @@ class RippleAttention(nn.Module):
             if plain_conv_size > 0:
                 self.conv = nn.Conv1d(channels, channels, plain_conv_size, padding=plain_conv_size // 2, groups=channels)
                 self._plain_conv = True
+            elif siren_conv:
+                from .scatter import AdaptiveConvND
+                self.conv = AdaptiveConvND(channels, ndim=1, max_samples=int(max_seq_len ** 0.5), num_channels=num_heads)
             else:
                 self.conv = AdaptiveLocalConv(channels, num_heads=num_heads, max_kernel_size=max_kernel_size,
                                               scale_power=conv_power)
@@ -116,25 +119,85 @@ class RippleAttention(nn.Module):
         return (x + h, info) if self.embed_residual else (h, info)
 
 
+class LayerHistoryAccumulator(nn.Module):
+    """SIREN-downsample a layer's output to ``L**reduction_power`` tokens and normalise it: one entry of the cross-layer
+    history (src/heuristic_secrets/models/ripple_attention.py:87-118)."""
+
+    def __init__(self, channels: int, reduction_power: float = 0.75, eps: float = 1e-6):
+        super().__init__()
+        from .scatter import SIRENDownsampleND
+        self.channels, self.reduction_power = channels, reduction_power
+        self.downsample = SIRENDownsampleND(channels, ndim=1)
+        self.norm = RMSNorm(channels, eps)
+
+    def forward(self, x):
+        return self.norm(self.downsample(x, (max(1, int(x.shape[1] ** self.reduction_power)),)))
+
+
+class CrossLayerAttention(nn.Module):
+    """Attention over the history of earlier layers' summaries: queries from the newest entry, keys / values from all
+    older ones, a rotary rotation by layer depth, SIREN-upsampled back to the sequence and added as a residual
+    (ripple_attention.py:213-305)."""
+
+    def __init__(self, channels: int, num_heads: int = 8, eps: float = 1e-6):
+        super().__init__()
+        from .scatter import SIRENUpsampleND
+        self.channels, self.num_heads, self.head_dim = channels, num_heads, channels // num_heads
+        self.q_proj = nn.Linear(channels, channels, bias=False)
+        self.k_proj = nn.Linear(channels, channels, bias=False)
+        self.v_proj = nn.Linear(channels, channels, bias=False)
+        self.q_norm, self.k_norm = RMSNorm(self.head_dim, eps), RMSNorm(self.head_dim, eps)
+        self.out_proj = nn.Linear(channels, channels, bias=False)
+        self.out_norm = RMSNorm(channels, eps)
+        self.upsample = SIRENUpsampleND(channels, ndim=1)
+
+    @staticmethod
+    def _depth_rope(x, depth: int, base: float = 10000.0):
+        half = x.shape[-1] // 2
+        ang = depth / (base ** (torch.arange(half, device=x.device, dtype=x.dtype) / half))
+        x1, x2 = x[..., :half], x[..., half:2 * half]
+        return torch.cat([x1 * ang.cos() - x2 * ang.sin(), x1 * ang.sin() + x2 * ang.cos()], dim=-1)
+
+    def forward(self, x, history):
+        if len(history) < 2:
+            return x
+        B, L, C = x.shape
+        H, D = self.num_heads, self.head_dim
+        q = self._depth_rope(self.q_norm(self.q_proj(history[-1]).view(B, -1, H, D)), len(history) - 1)
+        ks = [self._depth_rope(self.k_norm(self.k_proj(kv).view(B, -1, H, D)), d) for d, kv in enumerate(history[:-1])]
+        vs = [self.v_proj(kv).view(B, -1, H, D) for kv in history[:-1]]
+        out = F.scaled_dot_product_attention(q.transpose(1, 2), torch.cat(ks, 1).transpose(1, 2), torch.cat(vs, 1).transpose(1, 2))
+        out = self.out_proj(out.transpose(1, 2).reshape(B, -1, C))
+        return x + self.out_norm(self.upsample(out, (L,)))
+
+
 class RippleBlock(nn.Module):
     def __init__(self, channels: int, num_heads: int = 8, max_kernel_size: int = 64, mlp_ratio: float = 4.0,
                  use_triton: bool = True, eps: float = 1e-6, order: str = "tele,conv,lowrank", lowrank_power: float = 0.75,
                  telephone_power: float = 0.5625, conv_power: float = 0.421875, max_seq_len: int = 8192,
                  cross_layer: bool = False, jacobi_iters: int = 12, siren_conv: bool = False):
         super().__init__()
-        if cross_layer:
-            raise NotImplementedError("cross-layer history attention is not available in this build")
-        self.cross_layer = False
+        self.cross_layer = cross_layer
         self.attn = RippleAttention(channels, num_heads=num_heads, max_kernel_size=max_kernel_size, eps=eps, order=order,
                                     lowrank_power=lowrank_power, telephone_power=telephone_power, conv_power=conv_power,
                                     max_seq_len=max_seq_len, jacobi_iters=jacobi_iters, siren_conv=siren_conv)
         hidden = int(channels * mlp_ratio)
         self.mlp = nn.Sequential(nn.Linear(channels, hidden), nn.SiLU(), nn.Linear(hidden, channels))
+        if cross_layer:
+            self.cross_layer_attn = CrossLayerAttention(channels, num_heads, eps)
+            self.history_accum = LayerHistoryAccumulator(channels, lowrank_power, eps)
+            self.decay_head = nn.Sequential(nn.Linear(channels, channels // 4), nn.SiLU(), nn.Linear(channels // 4, 1))
 
     def forward(self, x: torch.Tensor, history=None):
+        if self.cross_layer and history is not None:
+            x = self.cross_layer_attn(x, history)
         a, info = self.attn(x)
         x = x + a
-        return x + self.mlp(x), info
+        x = x + self.mlp(x)
+        if self.cross_layer:
+            decay = 0.5 + 0.5 * torch.sigmoid(self.decay_head(x.mean(dim=1))).unsqueeze(-1)
+            return x, info, self.history_accum(x), decay
+        return x, info
 
 
 class RippleClassifier(nn.Module):
@@ -163,6 +226,9 @@ class RippleClassifier(nn.Module):
             for _ in range(n_layers)])
         self.norm = RMSNorm(width, eps)
         self.head = nn.Linear(width, n_classes)
+        if cross_layer:
+            self.embed_accum = LayerHistoryAccumulator(width, lowrank_power, eps)
+            self.head_cross_attn = CrossLayerAttention(width, num_heads, eps)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self.embed_2d is not None:
@@ -172,7 +238,14 @@ class RippleClassifier(nn.Module):
             x = self.embed_norm(self.embed(xl) + self.pos_embed[:, : xl.shape[1]])
         else:
             x = self.embed_norm(F.silu(self.embed(x.unsqueeze(-1)))) + self.pos_norm(F.silu(self.pos_embed))
-        for layer in self.layers:
-            x, _ = layer(x)
+        if self.cross_layer:
+            history = [self.embed_accum(x)]
+            for layer in self.layers:
+                x, _, summary, decay = layer(x, history)
+                history = [h * decay for h in history] + [summary]  # older summaries fade with a learned per-sample decay
+            x = self.head_cross_attn(x, history)
+        else:
+            for layer in self.layers:
+                x, _ = layer(x)
         x = self.norm(x)
         return self.head(x) if self.vocab_size is not None else self.head(x.mean(dim=1))

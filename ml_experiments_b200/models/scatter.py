@@ -240,7 +240,7 @@ class AdaptiveConvND(nn.Module):
         idx, w = self._taps(x_flat[:, start:end], start, spatial)
         if x_flat.is_cuda and D in _GATHER_DIMS:
             pos = idx.to(torch.float32).unsqueeze(2).expand(B, end - start, H, S)
-            out = gather_conv(x_flat, pos, w, H)
+            out = gather_conv(x_flat, pos, w, H, pos_max=L - 1)
         else:
             b_idx = torch.arange(B, device=x_flat.device).view(B, 1, 1)
             vals = x_flat[b_idx, idx].view(B, end - start, S, H, D)

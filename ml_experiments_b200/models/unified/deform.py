@@ -41,7 +41,7 @@ def deform_sample(x: torch.Tensor, abs_pos: torch.Tensor, tap_w: torch.Tensor, g
     if channel_kernel is None and x.is_cuda and gc in _GATHER_DIMS:
         from ...ops.gather_conv import gather_conv
         inside = ((abs_pos >= 0) & (abs_pos <= L - 1)).to(tap_w.dtype)
-        return gather_conv(x, abs_pos, tap_w * inside, G)
+        return gather_conv(x, abs_pos, tap_w * inside, G, pos_max=L - 1)
     lo, hi, w_lo, w_hi, _ = _taps(abs_pos, L)
     xg = x.view(N, L, G, gc)
     n_idx = torch.arange(N, device=x.device).view(N, 1, 1, 1)

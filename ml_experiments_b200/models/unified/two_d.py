@@ -193,7 +193,7 @@ def deform_sample_2d(x, pos_h, pos_w, tap_w, groups: int, channel_kernel=None, z
         # rows floor(h) and ceil(h) of the flattened map; the column interpolation is the kernel's own 1-D lerp
         pos = torch.cat([h_lo * W + pw, h_hi * W + pw], dim=-1).view(B, H * W, G, 2 * K)
         wgt = torch.cat([tap_w * (1 - fh), tap_w * fh], dim=-1).view(B, H * W, G, 2 * K)
-        return gather_conv(x.reshape(B, H * W, C), pos, wgt, G).view(B, H, W, C)
+        return gather_conv(x.reshape(B, H * W, C), pos, wgt, G, pos_max=H * W - 1).view(B, H, W, C)
     w_lo = pw.detach().floor().clamp(0, W - 1)
     w_hi = (w_lo + 1).clamp(max=W - 1)
     fw = pw - w_lo

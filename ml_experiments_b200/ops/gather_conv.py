@@ -3,9 +3,9 @@ adaptive-local-conv and scatter attention operators.
 
 ``x`` is ``[B, L, C]`` (source rows), ``pos`` / ``wgt`` are ``[B, Lq, H, S]`` (``Lq`` query rows, ``Lq == L`` for a whole sequence):
 ``out[b, l, h] = sum_s wgt[b, l, h, s] * lerp(x[b, floor(p)], x[b, floor(p) + 1], frac(p))`` with ``p = pos[b, l, h, s]``
-clamped to ``[0, L - 1]`` (the reference's PyTorch modules clamp to ``L - 1.001``,
-src/heuristic_secrets/models/telephone_attention.py:150-156; the results differ by at most 0.1 % of a row difference and
-integer positions, which the scatter operator uses, are read exactly). Gradients flow to ``x``, ``pos`` and ``wgt``.
+clamped to ``[0, pos_max]``. The default ``pos_max = L - 1.001`` is the rule of the reference's PyTorch modules
+(src/heuristic_secrets/models/telephone_attention.py:150-156); ``pos_max = L - 1`` reads integer positions, the last row
+included, exactly (the scatter operator uses it). Gradients flow to ``x``, ``pos`` and ``wgt``.
 """
 from __future__ import annotations
 
@@ -14,13 +14,13 @@ import torch
 from .runtime import ops
 
 
-def gather_conv_ref(x: torch.Tensor, pos: torch.Tensor, wgt: torch.Tensor, num_heads: int) -> torch.Tensor:
+def gather_conv_ref(x: torch.Tensor, pos: torch.Tensor, wgt: torch.Tensor, num_heads: int, pos_max: float | None = None) -> torch.Tensor:
     """Plain-torch restatement (differentiable)."""
     B, L, C = x.shape
     H, S, Lq = num_heads, pos.shape[-1], pos.shape[1]
     D = C // H
     xh = x.view(B, L, H, D)
-    pc = pos.clamp(0, L - 1)
+    pc = pos.clamp(0, L - 1.001 if pos_max is None else pos_max)
     fl = pc.detach().floor().long().clamp(0, max(L - 2, 0))
     ce = (fl + 1).clamp(0, L - 1)
     fr = (pc - fl.to(pc.dtype)).unsqueeze(-1)
@@ -33,13 +33,13 @@ def gather_conv_ref(x: torch.Tensor, pos: torch.Tensor, wgt: torch.Tensor, num_h
 
 class _GatherConv(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, pos, wgt, num_heads):
+    def forward(ctx, x, pos, wgt, num_heads, pos_max):
         x16 = x.to(torch.bfloat16).contiguous()
         p32, w32 = pos.float().contiguous(), wgt.float().contiguous()
         out = torch.empty(x16.shape[0], pos.shape[1], x16.shape[2], dtype=torch.bfloat16, device=x16.device)
-        ops().gather_conv_fwd(x16, p32, w32, out, num_heads)
+        ops().gather_conv_fwd(x16, p32, w32, out, num_heads, pos_max)
         ctx.save_for_backward(x16, p32, w32)
-        ctx.h, ctx.dt = num_heads, (x.dtype, pos.dtype, wgt.dtype)
+        ctx.h, ctx.pos_max, ctx.dt = num_heads, pos_max, (x.dtype, pos.dtype, wgt.dtype)
         return out.to(x.dtype)
 
     @staticmethod
@@ -47,12 +47,13 @@ class _GatherConv(torch.autograd.Function):
         x16, p32, w32 = ctx.saved_tensors
         dx = torch.zeros(x16.shape, dtype=torch.float32, device=x16.device)
         dpos, dwgt = torch.empty_like(p32), torch.empty_like(w32)
-        ops().gather_conv_bwd(x16, p32, w32, dout.to(torch.bfloat16).contiguous(), dx, dpos, dwgt, ctx.h)
-        return dx.to(ctx.dt[0]), dpos.to(ctx.dt[1]), dwgt.to(ctx.dt[2]), None
+        ops().gather_conv_bwd(x16, p32, w32, dout.to(torch.bfloat16).contiguous(), dx, dpos, dwgt, ctx.h, ctx.pos_max)
+        return dx.to(ctx.dt[0]), dpos.to(ctx.dt[1]), dwgt.to(ctx.dt[2]), None, None
 
 
-def gather_conv(x: torch.Tensor, pos: torch.Tensor, wgt: torch.Tensor, num_heads: int) -> torch.Tensor:
+def gather_conv(x: torch.Tensor, pos: torch.Tensor, wgt: torch.Tensor, num_heads: int, pos_max: float | None = None) -> torch.Tensor:
     d = x.shape[-1] // num_heads
+    pos_max = float(x.shape[1] - 1.001 if pos_max is None else pos_max)
     if x.is_cuda and d in (8, 16, 32, 64, 128):
-        return _GatherConv.apply(x, pos, wgt, num_heads)
-    return gather_conv_ref(x, pos, wgt, num_heads)
+        return _GatherConv.apply(x, pos, wgt, num_heads, pos_max)
+    return gather_conv_ref(x, pos, wgt, num_heads, pos_max)

@@ -92,3 +92,28 @@ def test_layerwise_ripple_models_run_and_train():
     for i in range(4):
         state, out_step = ssm.step(x, state, i)
     assert torch.allclose(out_step, ssm(x), atol=1e-6)  # stepping with a fixed input is the iterated forward
+
+
+@needs_ref
+def test_cross_layer_and_channel_classifiers_match_reference():
+    sys.path.insert(0, REF_SRC)
+    try:
+        from heuristic_secrets.models import ripple_attention as RA
+    finally:
+        sys.path.remove(REF_SRC)
+    from ml_experiments_b200.models import ripple as M
+    from ml_experiments_b200.models import ripple_channel as MC
+
+    torch.manual_seed(0)
+    x = torch.rand(2, 40)
+    kw = dict(num_heads=4, max_kernel_size=8, cross_layer=True, max_seq_len=64)
+    _same(*_pair(RA.RippleClassifier(32, 3, 4, 40, use_triton=False, **kw), M.RippleClassifier(32, 3, 4, 40, **kw)), x, atol=2e-4)
+    kw = dict(topology="tele,conv,se,lowrank,se", num_heads=2, max_kernel_size=8, max_seq_len=64, router_top_k=2)
+    _same(*_pair(RA.RippleChannelClassifier(32, 4, 3, 40, use_triton=False, **kw), MC.RippleChannelClassifier(32, 4, 3, 40, **kw)), x, atol=2e-4)
+    kw = dict(topology="tele,conv,lowrank,se,attn", num_heads=2, max_kernel_size=8, max_seq_len=64, vocab_size=50)
+    _same(*_pair(RA.RippleChannelClassifier(32, 4, 3, 40, use_triton=False, **kw), MC.RippleChannelClassifier(32, 4, 3, 40, **kw)),
+          torch.randint(0, 50, (2, 40)), atol=2e-4)
+    # a Jacobi op inside a channel: the reference unpacks its (tuple-less) output along the batch axis; here it just runs
+    m = MC.RippleChannelClassifier(32, 4, 3, 40, topology="jacobi,se,conv", num_heads=2, max_kernel_size=8, max_seq_len=64, jacobi_iters=2,
+                                   siren_conv=True)
+    assert m(x).shape == (2, 3)
