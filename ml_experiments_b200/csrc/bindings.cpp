@@ -212,8 +212,9 @@ void cast_fp8(const Tensor& x, Tensor out, double scale) {
 }
 
 void softcap_ce(const Tensor& logits, const Tensor& targets, Tensor loss_rows, const c10::optional<Tensor>& grad,
-                double cap, double div, double loss_scale, double grad_scale) {
+                double cap, double div, double loss_scale, double grad_scale, double shift, const c10::optional<Tensor>& mtp_w) {
   const c10::cuda::CUDAGuard guard(logits.device());
+  if (mtp_w.has_value()) TORCH_CHECK(mtp_w->is_cuda() && mtp_w->scalar_type() == at::kFloat && mtp_w->is_contiguous() && mtp_w->numel() >= 1 && mtp_w->numel() <= 4, "mtp_w: fp32 [1..4]");
   TORCH_CHECK(logits.dim() == 2 && logits.scalar_type() == at::kBFloat16 && logits.stride(1) == 1, "logits: bf16 [T, V]");
   TORCH_CHECK(targets.scalar_type() == at::kLong && targets.is_contiguous(), "targets: int64");
   TORCH_CHECK(loss_rows.scalar_type() == at::kFloat && loss_rows.numel() == logits.size(0), "loss_rows: fp32 [T]");
@@ -225,8 +226,9 @@ void softcap_ce(const Tensor& logits, const Tensor& targets, Tensor loss_rows, c
   }
   b200::softcap_ce(logits.data_ptr(), targets.data_ptr<int64_t>() ? (const long long*)targets.data_ptr<int64_t>() : nullptr,
                    loss_rows.data_ptr<float>(), grad.has_value() ? grad->data_ptr() : nullptr, grad_bf16,
-                   (int)logits.size(0), (int)logits.size(1), logits.stride(0), (float)cap, (float)div, (float)loss_scale,
-                   (float)grad_scale, cur_stream());
+                   (int)logits.size(0), (int)logits.size(1), logits.stride(0), (float)cap, (float)div, (float)shift, (float)loss_scale,
+                   (float)grad_scale, mtp_w.has_value() ? mtp_w->data_ptr<float>() : nullptr, mtp_w.has_value() ? (int)mtp_w->numel() : 1,
+                   cur_stream());
 }
 
 void adam_step(Tensor p, const Tensor& g, Tensor m, Tensor v, double lr, double beta1, double beta2, double eps,
@@ -509,7 +511,7 @@ TORCH_LIBRARY(b200, m) {
   m.def("embed_gather(Tensor idx, Tensor table, Tensor(a!) out, bool normalize, float eps) -> ()");
   m.def("embed_scatter_add(Tensor idx, Tensor src, Tensor(a!) grad_table) -> ()");
   m.def("cast_fp8(Tensor x, Tensor(a!) out, float scale) -> ()");
-  m.def("softcap_ce(Tensor logits, Tensor targets, Tensor(a!) loss_rows, Tensor(b!)? grad, float cap, float div, float loss_scale, float grad_scale) -> ()");
+  m.def("softcap_ce(Tensor logits, Tensor targets, Tensor(a!) loss_rows, Tensor(b!)? grad, float cap, float div, float loss_scale, float grad_scale, float shift=0.0, Tensor? mtp_w=None) -> ()");
   m.def("adam_step(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, float lr, float beta1, float beta2, float eps, float wd, float bias1, float bias2, float grad_scale) -> ()");
   m.def("muon_momentum(Tensor g, Tensor(a!) buf, Tensor(b!) out, Tensor(c!) sumsq, float mu, bool nesterov, float grad_scale) -> ()");
   m.def("scale_by_inv_norm(Tensor(a!) x, Tensor sumsq, float eps) -> ()");

@@ -439,13 +439,30 @@ __global__ void cast_fp8_kernel(const TI* __restrict__ x, uint8_t* __restrict__ 
 // One block per row. z = cap * sigmoid(x / div) is bounded by cap (30), so exp(z) needs no running maximum.
 __global__ void __launch_bounds__(512)
 softcap_ce_kernel(const bf16* __restrict__ logits, const long long* __restrict__ targets,
-                  float* __restrict__ loss_rows, uint8_t* __restrict__ grad, int grad_is_bf16, int V, long long ld,
-                  float cap, float inv_div, float loss_scale, float grad_scale) {
+                  float* __restrict__ loss_rows, uint8_t* __restrict__ grad, int grad_is_bf16, int T, int V, long long ld,
+                  float cap, float inv_div, float shift, float loss_scale, float grad_scale,
+                  const float* __restrict__ mtp_w, int n_predict) {
+  // z = cap * sigmoid((x + shift) / div); loss_row = sum_k w_k (lse - z[target[row + k]]) over the rows that exist
+  // (multi-token prediction: row r also predicts the targets of the next n_predict - 1 rows), w = {1} by default.
+  constexpr int MAXP = 4;
   __shared__ float red[16];
   __shared__ float s_total;
   const int row = blockIdx.x;
   const bf16* x = logits + (long long)row * ld;
-  const int tgt = (int)targets[row];
+  int tg[MAXP];
+  float wk[MAXP], wsum = 0.f;
+#pragma unroll
+  for (int k = 0; k < MAXP; ++k) {
+    const bool on = k < n_predict && row + k < T;
+    const int t = on ? (int)targets[row + k] : -1;
+    const float w = on ? (mtp_w ? mtp_w[k] : 1.f) : 0.f;
+    wsum += w;                                    // the probability term counts every existing row's weight
+    const bool valid = t >= 0 && t < V && w > 0.f;
+    tg[k] = valid ? t : -1;
+    wk[k] = valid ? w : 0.f;
+  }
+  const bool single_ignored = (n_predict == 1 && tg[0] < 0);  // an ignored position contributes nothing at all
+  if (single_ignored) wsum = 0.f;
   const int nch = V / 8;
   const float L2E = 1.4426950408889634f;
   float sum = 0.f;
@@ -454,7 +471,7 @@ softcap_ce_kernel(const bf16* __restrict__ logits, const long long* __restrict__
     load8(x + ci * 8, f);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const float sg = 0.5f * tanhf(0.5f * f[i] * inv_div) + 0.5f;  // sigmoid, one MUFU under fast-math
+      const float sg = 0.5f * tanhf(0.5f * (f[i] + shift) * inv_div) + 0.5f;  // sigmoid, one MUFU under fast-math
       sum += exp2f(cap * sg * L2E);
     }
   }
@@ -470,28 +487,31 @@ softcap_ce_kernel(const bf16* __restrict__ logits, const long long* __restrict__
   const float total = s_total;
   const float lse = logf(total);
   if (threadIdx.x == 0) {
-    float zt = 0.f;
-    if (tgt >= 0 && tgt < V) {
-      const float sg = 0.5f * tanhf(0.5f * __bfloat162float(x[tgt]) * inv_div) + 0.5f;
-      zt = cap * sg;
-      loss_rows[row] = (lse - zt) * loss_scale;
-    } else {
-      loss_rows[row] = 0.f;  // ignored position
+    float loss = 0.f;
+#pragma unroll
+    for (int k = 0; k < MAXP; ++k) {
+      if (tg[k] >= 0) {
+        const float sg = 0.5f * tanhf(0.5f * (__bfloat162float(x[tg[k]]) + shift) * inv_div) + 0.5f;
+        loss += wk[k] * (lse - cap * sg);
+      }
     }
+    loss_rows[row] = loss * loss_scale;
   }
   if (!grad) return;
-  const bool ignore = !(tgt >= 0 && tgt < V);
   const float inv_total = 1.f / total;
-  const float gs = ignore ? 0.f : grad_scale * cap * inv_div;
+  const float gs = grad_scale * cap * inv_div;
   for (int ci = threadIdx.x; ci < nch; ci += blockDim.x) {
     float f[8], g[8];
     load8(x + ci * 8, f);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const float sg = 0.5f * tanhf(0.5f * f[i] * inv_div) + 0.5f;
+      const float sg = 0.5f * tanhf(0.5f * (f[i] + shift) * inv_div) + 0.5f;
       const float pr = exp2f(cap * sg * L2E) * inv_total;
-      const float onehot = (ci * 8 + i == tgt) ? 1.f : 0.f;
-      g[i] = (pr - onehot) * sg * (1.f - sg) * gs;
+      const int col = ci * 8 + i;
+      float hot = 0.f;
+#pragma unroll
+      for (int k = 0; k < MAXP; ++k) hot += (col == tg[k]) ? wk[k] : 0.f;
+      g[i] = (wsum * pr - hot) * sg * (1.f - sg) * gs;
     }
     if (grad_is_bf16) {
       store8(reinterpret_cast<bf16*>(grad) + (long long)row * ld + ci * 8, g);
@@ -662,10 +682,12 @@ void cast_fp8(const void* x, void* out, float scale, long long n, int in_kind, i
 }
 
 void softcap_ce(const void* logits, const long long* targets, float* loss_rows, void* grad, int grad_is_bf16, int T,
-                int V, long long ld, float cap, float div, float loss_scale, float grad_scale, cudaStream_t s) {
+                int V, long long ld, float cap, float div, float shift, float loss_scale, float grad_scale,
+                const float* mtp_w, int n_predict, cudaStream_t s) {
   if (V % 8 != 0 || ld % 8 != 0) throw std::runtime_error("softcap_ce: vocabulary and row pitch must be multiples of 8");
-  softcap_ce_kernel<<<T, 512, 0, s>>>((const bf16*)logits, targets, loss_rows, (uint8_t*)grad, grad_is_bf16, V, ld, cap,
-                                      1.f / div, loss_scale, grad_scale);
+  if (n_predict < 1 || n_predict > 4) throw std::runtime_error("softcap_ce: 1 to 4 prediction offsets");
+  softcap_ce_kernel<<<T, 512, 0, s>>>((const bf16*)logits, targets, loss_rows, (uint8_t*)grad, grad_is_bf16, T, V, ld, cap,
+                                      1.f / div, shift, loss_scale, grad_scale, mtp_w, n_predict);
   check("softcap_ce");
 }
 

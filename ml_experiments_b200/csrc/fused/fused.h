@@ -47,11 +47,14 @@ void embed_scatter_add(const int* idx, const void* src, int src_is_f32, float* g
 void cast_fp8(const void* x, void* out, float scale, long long n, int in_kind, int out_kind, cudaStream_t s);
 
 // Soft-capped cross entropy over bf16 logits [T][V]:  z = cap * sigmoid(logit / div),
-// loss_rows[t] = (logsumexp(z_t) - z_t[target_t]) * loss_scale ; grad (e5m2) = dL/dlogit * grad_scale.
-// Targets outside [0, V) are ignored (zero loss and gradient). grad may be null (evaluation).
+// z = cap * sigmoid((logit + shift) / div).
+// loss_rows[t] = sum_k w_k (logsumexp(z_t) - z_t[target_{t+k}]) * loss_scale over k < n_predict with t + k < T (w = mtp_w,
+// {1} when null: plain next-token loss); grad (e5m2) = dL/dlogit * grad_scale.
+// Targets outside [0, V) are ignored (with n_predict = 1: zero loss and gradient). grad may be null (evaluation).
 // grad_is_bf16 selects a bf16 gradient buffer instead of e5m2.
 void softcap_ce(const void* logits, const long long* targets, float* loss_rows, void* grad, int grad_is_bf16, int T,
-                int V, long long ld, float cap, float div, float loss_scale, float grad_scale, cudaStream_t s);
+                int V, long long ld, float cap, float div, float shift, float loss_scale, float grad_scale,
+                const float* mtp_w, int n_predict, cudaStream_t s);
 
 // ---- optimizer pieces -------------------------------------------------------------------------
 // Adam (bias-corrected, decoupled weight decay wd*lr) over n elements. p : fp32 or bf16 (p_is_bf16);

@@ -54,3 +54,34 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, r
         if relu2:
             y = F.relu(y).square()
     return y
+
+
+class _LinearT(torch.autograd.Function):
+    """``y = x @ W`` for a weight stored ``(in_features, out_features)``: all three GEMMs read it as stored."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        x16 = x.reshape(-1, x.shape[-1]).to(torch.bfloat16).contiguous()
+        w16 = w.to(torch.bfloat16).contiguous()
+        ctx.save_for_backward(x16, w16)
+        ctx.x_shape, ctx.x_dtype, ctx.w_dtype = x.shape, x.dtype, w.dtype
+        return G.gemm(x16, w16, b_mn=True).view(*x.shape[:-1], w.shape[1])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x16, w16 = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1]).to(torch.bfloat16).contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = G.gemm(dy2, w16).view(ctx.x_shape).to(ctx.x_dtype)
+        if ctx.needs_input_grad[1]:
+            sk = G.auto_split_k(w16.shape[0], w16.shape[1], x16.shape[0])
+            dw = G.gemm(x16, dy2, a_mn=True, b_mn=True, split_k=sk, out_dtype=torch.float32).to(ctx.w_dtype)
+        return dx, dw
+
+
+def linear_t(x: torch.Tensor, w_t: torch.Tensor) -> torch.Tensor:
+    """``x @ w_t`` with ``w_t`` of shape ``(in_features, out_features)``."""
+    if not (x.is_cuda and w_t.shape[0] % 8 == 0 and w_t.shape[1] % 8 == 0 and x.numel() > 0):
+        return x @ w_t.to(x.dtype)
+    return _LinearT.apply(x, w_t)
