@@ -10,6 +10,7 @@
 #include "fused/fused.h"
 #include "gather/gather_conv.h"
 #include "gemm/gemm.h"
+#include "mra/mra.h"
 #include "scan/s6_scan.h"
 #include "window/window_attn.h"
 #include "wkv/wkv.h"
@@ -495,6 +496,34 @@ void window_attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Te
                         dv.data_ptr(), dbias.data_ptr<float>(), (float)scale, (int)q.size(0), (int)q.size(1), (int)q.size(2), (int)q.size(3),
                         (int)P.size(3), cur_stream());
 }
+
+// ---------------------------------------------------------------------------------------------- MRA block-sparse ops
+void chk_i32c(const Tensor& t, const char* n) { TORCH_CHECK(t.is_cuda() && t.is_contiguous() && t.scalar_type() == at::kInt, n, ": contiguous int32 CUDA tensor"); }
+
+void mra_sddmm(const Tensor& Q, const Tensor& K, const Tensor& indices, Tensor S) {
+  const c10::cuda::CUDAGuard guard(Q.device());
+  chk_f32c(Q, "Q"); chk_f32c(K, "K"); chk_f32c(S, "S"); chk_i32c(indices, "indices");
+  TORCH_CHECK(Q.dim() == 3 && K.dim() == 3 && Q.size(0) == K.size(0) && Q.size(2) == K.size(2) && Q.size(1) % 32 == 0 && K.size(1) % 32 == 0, "mra_sddmm: Q [B, Lq, D], K [B, Lk, D], lengths multiples of 32");
+  TORCH_CHECK(indices.dim() == 2 && indices.size(0) == Q.size(0) && S.numel() == indices.numel() * 1024, "mra_sddmm: indices [B, n], S [B, n, 32, 32]");
+  b200::mra_sddmm(Q.data_ptr<float>(), K.data_ptr<float>(), indices.data_ptr<int>(), S.data_ptr<float>(), (int)Q.size(0), (int)Q.size(1),
+                  (int)K.size(1), (int)Q.size(2), (int)indices.size(1), cur_stream());
+}
+
+void mra_spmm(const Tensor& P, const Tensor& indices, const Tensor& V, Tensor out, int64_t Lq, int64_t Lk, bool transposed) {
+  const c10::cuda::CUDAGuard guard(P.device());
+  chk_f32c(P, "P"); chk_f32c(V, "V"); chk_f32c(out, "out"); chk_i32c(indices, "indices");
+  TORCH_CHECK(V.dim() == 3 && out.dim() == 3 && V.size(1) == (transposed ? Lq : Lk) && out.size(1) == (transposed ? Lk : Lq) && V.size(2) == out.size(2), "mra_spmm: operand lengths do not match the block grid");
+  TORCH_CHECK(P.numel() == indices.numel() * 1024 && Lq % 32 == 0 && Lk % 32 == 0, "mra_spmm: P [B, n, 32, 32]");
+  b200::mra_spmm(P.data_ptr<float>(), indices.data_ptr<int>(), V.data_ptr<float>(), out.data_ptr<float>(), (int)V.size(0), (int)Lq, (int)Lk,
+                 (int)V.size(2), (int)indices.size(1), transposed, cur_stream());
+}
+
+void mra_rowmax(const Tensor& S, const Tensor& indices, Tensor m, int64_t Lk) {
+  const c10::cuda::CUDAGuard guard(S.device());
+  chk_f32c(S, "S"); chk_f32c(m, "m"); chk_i32c(indices, "indices");
+  TORCH_CHECK(m.dim() == 2 && S.numel() == indices.numel() * 1024 && m.size(0) == indices.size(0), "mra_rowmax: S [B, n, 32, 32], m [B, Lq]");
+  b200::mra_rowmax(S.data_ptr<float>(), indices.data_ptr<int>(), m.data_ptr<float>(), (int)m.size(0), (int)m.size(1), (int)Lk, (int)indices.size(1), cur_stream());
+}
 }  // namespace
 
 TORCH_LIBRARY(b200, m) {
@@ -535,6 +564,9 @@ TORCH_LIBRARY(b200, m) {
   m.def("wkv5_bwd(Tensor r, Tensor k, Tensor v, Tensor w, Tensor u, Tensor gy, Tensor(a!) gr, Tensor(b!) gk, Tensor(c!) gv, Tensor(d!) gw, Tensor(e!) gu) -> ()");
   m.def("window_attn_fwd(Tensor q, Tensor k, Tensor v, Tensor bias, Tensor(a!) out, Tensor(b!) P, float scale) -> ()");
   m.def("window_attn_bwd(Tensor q, Tensor k, Tensor v, Tensor P, Tensor dout, Tensor(a!) dq, Tensor(b!) dk, Tensor(c!) dv, Tensor(d!) dbias, float scale) -> ()");
+  m.def("mra_sddmm(Tensor Q, Tensor K, Tensor indices, Tensor(a!) S) -> ()");
+  m.def("mra_spmm(Tensor P, Tensor indices, Tensor V, Tensor(a!) out, int Lq, int Lk, bool transposed) -> ()");
+  m.def("mra_rowmax(Tensor S, Tensor indices, Tensor(a!) m, int Lk) -> ()");
   // <<DEFS>>
 }
 
@@ -574,5 +606,8 @@ TORCH_LIBRARY_IMPL(b200, CUDA, m) {
   m.impl("wkv5_bwd", &wkv5_bwd);
   m.impl("window_attn_fwd", &window_attn_fwd);
   m.impl("window_attn_bwd", &window_attn_bwd);
+  m.impl("mra_sddmm", &mra_sddmm);
+  m.impl("mra_spmm", &mra_spmm);
+  m.impl("mra_rowmax", &mra_rowmax);
   // <<IMPLS>>
 }
