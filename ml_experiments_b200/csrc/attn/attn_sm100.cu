@@ -656,9 +656,9 @@ void attn_delta_sm100(const AttnArgs& a) {
 
 void attn_bwd_sm100(const AttnArgs& a) {
   check_common(a);
-  // dQᵀ = Kᵀ·dSᵀ puts the head dimension on the MMA M axis, which this kernel issues at M = 128 only.
-  if (a.D != 128) throw std::runtime_error("attention backward: head_dim must be 128");
-  bwd_impl<128>(a);
+  // dQᵀ = Kᵀ·dSᵀ puts the head dimension on the MMA M axis, always issued at M = 128. With head_dim 64 the upper 64
+  // rows of the A operand fall on the V tile that follows K in shared memory; their accumulator rows are never read.
+  if (a.D == 128) bwd_impl<128>(a); else bwd_impl<64>(a);
 }
 
 }  // namespace b200

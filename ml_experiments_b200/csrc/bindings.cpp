@@ -9,6 +9,7 @@
 #include "comm/comm.h"
 #include "fused/fused.h"
 #include "gather/gather_conv.h"
+#include "gather/fused_taps.h"
 #include "gemm/gemm.h"
 #include "mra/mra.h"
 #include "scan/s6_scan.h"
@@ -524,6 +525,63 @@ void mra_rowmax(const Tensor& S, const Tensor& indices, Tensor m, int64_t Lk) {
   TORCH_CHECK(m.dim() == 2 && S.numel() == indices.numel() * 1024 && m.size(0) == indices.size(0), "mra_rowmax: S [B, n, 32, 32], m [B, Lq]");
   b200::mra_rowmax(S.data_ptr<float>(), indices.data_ptr<int>(), m.data_ptr<float>(), (int)m.size(0), (int)m.size(1), (int)Lk, (int)indices.size(1), cur_stream());
 }
+// ---------------------------------------------------------------------------------------------- fused tap kernels
+void chk_rows_f32(const Tensor& t, int64_t n, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kFloat && t.is_contiguous() && t.numel() == n, name, ": contiguous fp32 CUDA tensor of ", n, " elements");
+}
+
+void tele_fused_fwd(const Tensor& x, const Tensor& freq, const Tensor& phase, const Tensor& kern, const Tensor& expo, Tensor out,
+                    int64_t H, int64_t half, double max_rec) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  chk_bf16c(x, "x"); chk_bf16c(out, "out");
+  TORCH_CHECK(x.dim() == 3 && out.sizes() == x.sizes() && kern.dim() == 4, "tele_fused: x/out [B,L,C], kern [B,L,H,K]");
+  const int B = (int)x.size(0), L = (int)x.size(1), C = (int)x.size(2), K = (int)kern.size(3);
+  const int64_t rows = (int64_t)B * L * H;
+  chk_rows_f32(freq, rows, "freq"); chk_rows_f32(phase, rows, "phase"); chk_rows_f32(kern, rows * K, "kern"); chk_rows_f32(expo, (int64_t)B * L, "expo");
+  b200::tele_fused_fwd(x.data_ptr(), freq.data_ptr<float>(), phase.data_ptr<float>(), kern.data_ptr<float>(), expo.data_ptr<float>(),
+                       out.data_ptr(), B, L, (int)H, C / (int)H, K, (int)half, (float)max_rec, cur_stream());
+}
+
+void tele_fused_bwd(const Tensor& x, const Tensor& freq, const Tensor& phase, const Tensor& kern, const Tensor& expo, const Tensor& dout,
+                    Tensor dx, Tensor dfreq, Tensor dphase, Tensor dkern, Tensor dexpo_h, int64_t H, int64_t half, double max_rec) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  chk_bf16c(x, "x"); chk_bf16c(dout, "dout");
+  TORCH_CHECK(x.dim() == 3 && dout.sizes() == x.sizes() && kern.dim() == 4, "tele_fused: x/dout [B,L,C], kern [B,L,H,K]");
+  const int B = (int)x.size(0), L = (int)x.size(1), C = (int)x.size(2), K = (int)kern.size(3);
+  const int64_t rows = (int64_t)B * L * H;
+  chk_rows_f32(freq, rows, "freq"); chk_rows_f32(phase, rows, "phase"); chk_rows_f32(kern, rows * K, "kern"); chk_rows_f32(expo, (int64_t)B * L, "expo");
+  chk_rows_f32(dx, x.numel(), "dx"); chk_rows_f32(dfreq, rows, "dfreq"); chk_rows_f32(dphase, rows, "dphase");
+  chk_rows_f32(dkern, rows * K, "dkern"); chk_rows_f32(dexpo_h, rows, "dexpo_h");
+  b200::tele_fused_bwd(x.data_ptr(), freq.data_ptr<float>(), phase.data_ptr<float>(), kern.data_ptr<float>(), expo.data_ptr<float>(),
+                       dout.data_ptr(), dx.data_ptr<float>(), dfreq.data_ptr<float>(), dphase.data_ptr<float>(), dkern.data_ptr<float>(),
+                       dexpo_h.data_ptr<float>(), B, L, (int)H, C / (int)H, K, (int)half, (float)max_rec, cur_stream());
+}
+
+void alc_fused_fwd(const Tensor& x, const Tensor& half_w, const Tensor& center, const Tensor& kern, Tensor out, int64_t H, int64_t half) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  chk_bf16c(x, "x"); chk_bf16c(out, "out");
+  TORCH_CHECK(x.dim() == 3 && out.sizes() == x.sizes() && kern.dim() == 4, "alc_fused: x/out [B,L,C], kern [B,L,H,K]");
+  const int B = (int)x.size(0), L = (int)x.size(1), C = (int)x.size(2), K = (int)kern.size(3);
+  const int64_t rows = (int64_t)B * L * H;
+  chk_rows_f32(half_w, rows, "half_w"); chk_rows_f32(center, rows, "center"); chk_rows_f32(kern, rows * K, "kern");
+  b200::alc_fused_fwd(x.data_ptr(), half_w.data_ptr<float>(), center.data_ptr<float>(), kern.data_ptr<float>(), out.data_ptr(), B, L,
+                      (int)H, C / (int)H, K, (int)half, cur_stream());
+}
+
+void alc_fused_bwd(const Tensor& x, const Tensor& half_w, const Tensor& center, const Tensor& kern, const Tensor& dout, Tensor dx,
+                   Tensor dhalf_w, Tensor dcenter, Tensor dkern, int64_t H, int64_t half) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  chk_bf16c(x, "x"); chk_bf16c(dout, "dout");
+  TORCH_CHECK(x.dim() == 3 && dout.sizes() == x.sizes() && kern.dim() == 4, "alc_fused: x/dout [B,L,C], kern [B,L,H,K]");
+  const int B = (int)x.size(0), L = (int)x.size(1), C = (int)x.size(2), K = (int)kern.size(3);
+  const int64_t rows = (int64_t)B * L * H;
+  chk_rows_f32(half_w, rows, "half_w"); chk_rows_f32(center, rows, "center"); chk_rows_f32(kern, rows * K, "kern");
+  chk_rows_f32(dx, x.numel(), "dx"); chk_rows_f32(dhalf_w, rows, "dhalf_w"); chk_rows_f32(dcenter, rows, "dcenter"); chk_rows_f32(dkern, rows * K, "dkern");
+  b200::alc_fused_bwd(x.data_ptr(), half_w.data_ptr<float>(), center.data_ptr<float>(), kern.data_ptr<float>(), dout.data_ptr(),
+                      dx.data_ptr<float>(), dhalf_w.data_ptr<float>(), dcenter.data_ptr<float>(), dkern.data_ptr<float>(), B, L, (int)H,
+                      C / (int)H, K, (int)half, cur_stream());
+}
+
 }  // namespace
 
 TORCH_LIBRARY(b200, m) {
@@ -556,6 +614,10 @@ TORCH_LIBRARY(b200, m) {
   m.def("s6_scan_bwd(Tensor u, Tensor delta, Tensor? delta_bias, bool softplus, Tensor A, Tensor Bm, Tensor Cm, Tensor? Dv, Tensor? z, Tensor? y_pre, Tensor dout, Tensor state, Tensor(a!) du, Tensor(b!) ddelta, Tensor(c!) dA, Tensor(d!) dB_part, Tensor(e!) dC_part, Tensor(f!)? dD, Tensor(g!)? dz, Tensor(h!)? ddelta_bias) -> ()");
   m.def("causal_conv1d_silu_fwd(Tensor x, Tensor w, Tensor? bias, Tensor(a!) y) -> ()");
   m.def("causal_conv1d_silu_bwd(Tensor x, Tensor w, Tensor? bias, Tensor dy, Tensor(a!) dx, Tensor(b!) dw, Tensor(c!)? dbias) -> ()");
+  m.def("tele_fused_fwd(Tensor x, Tensor freq, Tensor phase, Tensor kern, Tensor expo, Tensor(a!) out, int H, int half, float max_rec) -> ()");
+  m.def("tele_fused_bwd(Tensor x, Tensor freq, Tensor phase, Tensor kern, Tensor expo, Tensor dout, Tensor(a!) dx, Tensor(b!) dfreq, Tensor(c!) dphase, Tensor(d!) dkern, Tensor(e!) dexpo_h, int H, int half, float max_rec) -> ()");
+  m.def("alc_fused_fwd(Tensor x, Tensor half_w, Tensor center, Tensor kern, Tensor(a!) out, int H, int half) -> ()");
+  m.def("alc_fused_bwd(Tensor x, Tensor half_w, Tensor center, Tensor kern, Tensor dout, Tensor(a!) dx, Tensor(b!) dhalf_w, Tensor(c!) dcenter, Tensor(d!) dkern, int H, int half) -> ()");
   m.def("gather_conv_fwd(Tensor x, Tensor pos, Tensor wgt, Tensor(a!) out, int H, float pos_max) -> ()");
   m.def("gather_conv_bwd(Tensor x, Tensor pos, Tensor wgt, Tensor dout, Tensor(a!) dx, Tensor(b!) dpos, Tensor(c!) dwgt, int H, float pos_max) -> ()");
   m.def("wkv4_fwd(Tensor k, Tensor v, Tensor w, Tensor u, Tensor(a!) y) -> ()");
@@ -598,6 +660,10 @@ TORCH_LIBRARY_IMPL(b200, CUDA, m) {
   m.impl("s6_scan_bwd", &s6_scan_bwd);
   m.impl("causal_conv1d_silu_fwd", &causal_conv1d_silu_fwd);
   m.impl("causal_conv1d_silu_bwd", &causal_conv1d_silu_bwd);
+  m.impl("tele_fused_fwd", &tele_fused_fwd);
+  m.impl("tele_fused_bwd", &tele_fused_bwd);
+  m.impl("alc_fused_fwd", &alc_fused_fwd);
+  m.impl("alc_fused_bwd", &alc_fused_bwd);
   m.impl("gather_conv_fwd", &gather_conv_fwd);
   m.impl("gather_conv_bwd", &gather_conv_bwd);
   m.impl("wkv4_fwd", &wkv4_fwd);

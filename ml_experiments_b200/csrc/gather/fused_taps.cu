@@ -1,0 +1,444 @@
+// See fused_taps.h. Thread layout as in gather_conv.cu: a group of LPR = D/4 adjacent lanes owns one (b, l, h) row and
+// each lane keeps 4 channels. Taps are processed LPR at a time: lane j of the group evaluates the tap formula of tap
+// s0 + j (so the transcendental work is done once per tap, not once per lane), then the group walks the LPR taps,
+// broadcasting (weight, position) by shuffle and gathering the two value rows. In the backward the owner lane of a tap
+// turns the two reduced dot products into the gradients of the row's scalars; kernel-table gradients accumulate in
+// shared memory and leave the block coalesced.
+#include "fused_taps.h"
+
+#include <cuda_bf16.h>
+
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+
+namespace b200 {
+namespace {
+using bf16 = __nv_bfloat16;
+constexpr int KMAX = 64;
+
+__device__ __forceinline__ float4 ld4(const bf16* p) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void st4(bf16* p, float4 v) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+}
+template <int LPR>
+__device__ __forceinline__ unsigned group_mask() {
+  const unsigned lane = threadIdx.x & 31u;
+  return (LPR == 32 ? 0xffffffffu : ((1u << LPR) - 1u)) << (lane & ~unsigned(LPR - 1));
+}
+template <int LPR>
+__device__ __forceinline__ float group_sum(float v) {
+  const unsigned mask = group_mask<LPR>();
+#pragma unroll
+  for (int s = LPR / 2; s > 0; s >>= 1) v += __shfl_xor_sync(mask, v, s);
+  return v;
+}
+template <int LPR>
+__device__ __forceinline__ float group_bcast(float v, int j) {
+  return __shfl_sync(group_mask<LPR>(), v, j, LPR);
+}
+__device__ __forceinline__ float dot4(float4 a, float4 b) { return a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w; }
+
+struct Lerp {
+  int lo;
+  float wh, v, slope;
+};
+// table value at t in [0, 1] (K entries), with the slope d v / d t
+__device__ __forceinline__ Lerp lerp_table(const float* kr, int K, float t) {
+  Lerp r;
+  const float idx = fminf(fmaxf(t, 0.f), 1.f) * (float)(K - 1);
+  r.lo = min((int)idx, K - 2);
+  r.wh = idx - (float)r.lo;
+  const float a = kr[r.lo], b = kr[r.lo + 1];
+  r.v = a * (1.f - r.wh) + b * r.wh;
+  r.slope = (t >= 0.f && t <= 1.f) ? (b - a) * (float)(K - 1) : 0.f;
+  return r;
+}
+
+struct Row {
+  long long row, bl;
+  int b, l, h, sub;
+  bool active;
+};
+template <int LPR>
+__device__ __forceinline__ Row locate(int B, int L, int H) {
+  Row r;
+  r.row = ((long long)blockIdx.x * 256 + threadIdx.x) / LPR;
+  r.sub = threadIdx.x % LPR;
+  r.active = r.row < (long long)B * L * H;
+  const long long rr = r.active ? r.row : 0;
+  r.row = rr;
+  r.h = (int)(rr % H);
+  r.bl = rr / H;
+  r.b = (int)(r.bl / L);
+  r.l = (int)(r.bl % L);
+  return r;
+}
+
+struct Bil {
+  int fl, ce;
+  float fr;
+};
+__device__ __forceinline__ Bil bilinear(float p, int L) {
+  Bil r;
+  const float pc = fminf(fmaxf(p, 0.f), (float)L - 1.001f);
+  r.fl = min((int)pc, max(L - 2, 0));
+  r.ce = min(r.fl + 1, L - 1);
+  r.fr = pc - (float)r.fl;
+  return r;
+}
+
+// ------------------------------------------------------------------------------------------------ telephone
+template <int LPR>
+__global__ void __launch_bounds__(256)
+tele_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ freq, const float* __restrict__ phase,
+                const float* __restrict__ kern, const float* __restrict__ expo, bf16* __restrict__ out, int B, int L, int H,
+                int K, int half, float max_rec) {
+  constexpr int D = LPR * 4;
+  const Row r = locate<LPR>(B, L, H);
+  const float f = freq[r.row], ph = phase[r.row], e = expo[r.bl];
+  const float* kr = kern + r.row * K;
+  const bf16* xb = x + (long long)r.b * L * H * D + r.h * D + r.sub * 4;
+  const float invL = 1.f / (float)L, inv_rec = 1.f / max_rec;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int s0 = -half; s0 <= half; s0 += LPR) {
+    const int s = s0 + r.sub;
+    float w = 0.f, p = 0.f;
+    if (s <= half) {
+      const float rel = (float)s * f, ar = fabsf(rel);
+      p = (float)r.l + rel + ph;
+      if (p >= 0.f && p < (float)L) w = lerp_table(kr, K, ar * inv_rec).v * exp2f(-e * log2f(1.f + ar * invL));
+    }
+    const int n = min(LPR, half - s0 + 1);
+    for (int j = 0; j < n; ++j) {
+      const float wj = group_bcast<LPR>(w, j), pj = group_bcast<LPR>(p, j);
+      if (wj == 0.f) continue;
+      const Bil bi = bilinear(pj, L);
+      const float4 a = ld4(xb + (long long)bi.fl * H * D), c = ld4(xb + (long long)bi.ce * H * D);
+      const float wa = wj * (1.f - bi.fr), wc = wj * bi.fr;
+      acc.x += wa * a.x + wc * c.x; acc.y += wa * a.y + wc * c.y;
+      acc.z += wa * a.z + wc * c.z; acc.w += wa * a.w + wc * c.w;
+    }
+  }
+  if (r.active) st4(out + r.row * D + r.sub * 4, acc);
+}
+
+template <int LPR>
+__global__ void __launch_bounds__(256)
+tele_bwd_kernel(const bf16* __restrict__ x, const float* __restrict__ freq, const float* __restrict__ phase,
+                const float* __restrict__ kern, const float* __restrict__ expo, const bf16* __restrict__ dout,
+                float* __restrict__ dx, float* __restrict__ dfreq, float* __restrict__ dphase, float* __restrict__ dkern,
+                float* __restrict__ dexpo_h, int B, int L, int H, int K, int half, float max_rec) {
+  constexpr int D = LPR * 4;
+  constexpr int RPB = 256 / LPR;
+  extern __shared__ float s_dk[];  // [RPB][K]
+  for (int i = threadIdx.x; i < RPB * K; i += 256) s_dk[i] = 0.f;
+  __syncthreads();
+  const Row r = locate<LPR>(B, L, H);
+  const float f = freq[r.row], ph = phase[r.row], e = expo[r.bl];
+  const float* kr = kern + r.row * K;
+  float* dk = s_dk + (threadIdx.x / LPR) * K;
+  const bf16* xb = x + (long long)r.b * L * H * D + r.h * D + r.sub * 4;
+  float* dxb = dx + (long long)r.b * L * H * D + r.h * D + r.sub * 4;
+  const float invL = 1.f / (float)L, inv_rec = 1.f / max_rec, hi = (float)L - 1.001f;
+  const float4 g = ld4(dout + r.row * D + r.sub * 4);
+  float df = 0.f, dph = 0.f, de = 0.f;
+  for (int s0 = -half; s0 <= half; s0 += LPR) {
+    const int s = s0 + r.sub;
+    float w = 0.f, p = 0.f, kv = 0.f, pw = 0.f, rel = 0.f, base = 1.f;
+    Lerp lt;
+    lt.lo = 0; lt.wh = 0.f; lt.v = 0.f; lt.slope = 0.f;
+    bool valid = false;
+    if (s <= half) {
+      rel = (float)s * f;
+      const float ar = fabsf(rel);
+      p = (float)r.l + rel + ph;
+      valid = p >= 0.f && p < (float)L;
+      if (valid) {
+        lt = lerp_table(kr, K, ar * inv_rec);
+        kv = lt.v;
+        base = 1.f + ar * invL;
+        pw = exp2f(-e * log2f(base));
+        w = kv * pw;
+      }
+    }
+    const int n = min(LPR, half - s0 + 1);
+    float my_sa = 0.f, my_sc = 0.f, my_fr = 0.f;
+    for (int j = 0; j < n; ++j) {
+      const float vj = group_bcast<LPR>(valid ? 1.f : 0.f, j);
+      if (vj == 0.f) continue;
+      const float wj = group_bcast<LPR>(w, j), pj = group_bcast<LPR>(p, j);
+      const Bil bi = bilinear(pj, L);
+      const float4 a = ld4(xb + (long long)bi.fl * H * D), c = ld4(xb + (long long)bi.ce * H * D);
+      const float sa = group_sum<LPR>(dot4(g, a)), sc = group_sum<LPR>(dot4(g, c));
+      if (r.sub == j) { my_sa = sa; my_sc = sc; my_fr = bi.fr; }
+      if (r.active && wj != 0.f) {
+        const float wa = wj * (1.f - bi.fr), wc = wj * bi.fr;
+        atomicAdd(reinterpret_cast<float4*>(dxb + (long long)bi.fl * H * D), make_float4(wa * g.x, wa * g.y, wa * g.z, wa * g.w));
+        if (wc != 0.f)
+          atomicAdd(reinterpret_cast<float4*>(dxb + (long long)bi.ce * H * D), make_float4(wc * g.x, wc * g.y, wc * g.z, wc * g.w));
+      }
+    }
+    if (valid && r.active) {  // scalar gradients of this lane's own tap
+      const float dW = my_sa * (1.f - my_fr) + my_sc * my_fr;
+      const float dP = (p >= 0.f && p <= hi) ? w * (my_sc - my_sa) : 0.f;
+      const float dkv = dW * pw;
+      atomicAdd(&dk[lt.lo], dkv * (1.f - lt.wh));
+      atomicAdd(&dk[lt.lo + 1], dkv * lt.wh);
+      const float dpw = dW * kv;
+      de += dpw * pw * (-logf(base));
+      float dar = dkv * lt.slope * inv_rec + dpw * pw * (-e) * invL / base;
+      const float sgn = rel > 0.f ? 1.f : (rel < 0.f ? -1.f : 0.f);
+      const float drel = dar * sgn + dP;
+      df += drel * (float)s;
+      dph += dP;
+    }
+  }
+  df = group_sum<LPR>(df);
+  dph = group_sum<LPR>(dph);
+  de = group_sum<LPR>(de);
+  if (r.active && r.sub == 0) {
+    dfreq[r.row] = df;
+    dphase[r.row] = dph;
+    dexpo_h[r.row] = de;
+  }
+  __syncthreads();
+  const long long row0 = (long long)blockIdx.x * RPB;
+  const long long nrows = (long long)B * L * H;
+  for (int i = threadIdx.x; i < RPB * K; i += 256) {
+    const long long rr = row0 + i / K;
+    if (rr < nrows) dkern[rr * K + i % K] = s_dk[i];
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ adaptive local conv
+struct AlcTap {
+  float base, rk, ex, r, p;
+  Lerp lt;
+  bool valid;
+};
+__device__ __forceinline__ AlcTap alc_tap(const float* kr, int K, int s, float inv_hw, float pc0, int L) {
+  AlcTap t;
+  t.r = fabsf((float)s) * inv_hw;
+  t.p = pc0 + (float)s;
+  t.valid = t.p >= 0.f && t.p < (float)L;
+  t.lt = lerp_table(kr, K, t.r);
+  t.rk = fmaxf(t.lt.v, 0.f) + 1.f;
+  t.ex = __expf(-t.r * t.r);
+  t.base = t.valid ? t.rk * t.ex : 0.f;
+  return t;
+}
+
+template <int LPR>
+__global__ void __launch_bounds__(256)
+alc_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ half_w, const float* __restrict__ center,
+               const float* __restrict__ kern, bf16* __restrict__ out, int B, int L, int H, int K, int half) {
+  constexpr int D = LPR * 4;
+  const Row r = locate<LPR>(B, L, H);
+  const float inv_hw = 1.f / half_w[r.row], pc0 = (float)r.l + center[r.row];
+  const float* kr = kern + r.row * K;
+  const bf16* xb = x + (long long)r.b * L * H * D + r.h * D + r.sub * 4;
+  float sum = 0.f;
+  for (int s = -half + r.sub; s <= half; s += LPR) sum += alc_tap(kr, K, s, inv_hw, pc0, L).base;
+  const float inv_norm = 1.f / fmaxf(group_sum<LPR>(sum), 1.f);
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int s0 = -half; s0 <= half; s0 += LPR) {
+    const int s = s0 + r.sub;
+    float w = 0.f, p = 0.f;
+    if (s <= half) {
+      const AlcTap t = alc_tap(kr, K, s, inv_hw, pc0, L);
+      w = t.base * inv_norm;
+      p = t.p;
+    }
+    const int n = min(LPR, half - s0 + 1);
+    for (int j = 0; j < n; ++j) {
+      const float wj = group_bcast<LPR>(w, j), pj = group_bcast<LPR>(p, j);
+      if (wj == 0.f) continue;
+      const Bil bi = bilinear(pj, L);
+      const float4 a = ld4(xb + (long long)bi.fl * H * D), c = ld4(xb + (long long)bi.ce * H * D);
+      const float wa = wj * (1.f - bi.fr), wc = wj * bi.fr;
+      acc.x += wa * a.x + wc * c.x; acc.y += wa * a.y + wc * c.y;
+      acc.z += wa * a.z + wc * c.z; acc.w += wa * a.w + wc * c.w;
+    }
+  }
+  if (r.active) st4(out + r.row * D + r.sub * 4, acc);
+}
+
+// shared memory: [RPB][K] kernel gradients, then [RPB][SP] per-tap dW (SP = 2*half+1)
+template <int LPR>
+__global__ void __launch_bounds__(256)
+alc_bwd_kernel(const bf16* __restrict__ x, const float* __restrict__ half_w, const float* __restrict__ center,
+               const float* __restrict__ kern, const bf16* __restrict__ dout, float* __restrict__ dx,
+               float* __restrict__ dhalf_w, float* __restrict__ dcenter, float* __restrict__ dkern, int B, int L, int H,
+               int K, int half) {
+  constexpr int D = LPR * 4;
+  constexpr int RPB = 256 / LPR;
+  extern __shared__ float s_mem[];
+  const int SP = 2 * half + 1;
+  float* s_dk = s_mem;
+  float* s_dw = s_mem + RPB * K;
+  for (int i = threadIdx.x; i < RPB * K; i += 256) s_dk[i] = 0.f;
+  __syncthreads();
+  const Row r = locate<LPR>(B, L, H);
+  const float hw = half_w[r.row], inv_hw = 1.f / hw, pc0 = (float)r.l + center[r.row];
+  const float* kr = kern + r.row * K;
+  float* dk = s_dk + (threadIdx.x / LPR) * K;
+  float* dw = s_dw + (threadIdx.x / LPR) * SP;
+  const bf16* xb = x + (long long)r.b * L * H * D + r.h * D + r.sub * 4;
+  float* dxb = dx + (long long)r.b * L * H * D + r.h * D + r.sub * 4;
+  const float hi = (float)L - 1.001f;
+  const float4 g = ld4(dout + r.row * D + r.sub * 4);
+  float sum = 0.f;
+  for (int s = -half + r.sub; s <= half; s += LPR) sum += alc_tap(kr, K, s, inv_hw, pc0, L).base;
+  sum = group_sum<LPR>(sum);
+  const float inv_norm = 1.f / fmaxf(sum, 1.f);
+  float dc = 0.f, G = 0.f;
+  // pass 1: gathers -> per-tap dW (shared), dx atomics, centre gradient, G = sum_j dW_j w_j
+  for (int s0 = -half; s0 <= half; s0 += LPR) {
+    const int s = s0 + r.sub;
+    float w = 0.f, p = 0.f;
+    if (s <= half) {
+      const AlcTap t = alc_tap(kr, K, s, inv_hw, pc0, L);
+      w = t.base * inv_norm;
+      p = t.p;
+    }
+    const int n = min(LPR, half - s0 + 1);
+    for (int j = 0; j < n; ++j) {
+      const float wj = group_bcast<LPR>(w, j), pj = group_bcast<LPR>(p, j);
+      float dWj = 0.f;
+      if (pj >= 0.f && pj < (float)L) {
+        const Bil bi = bilinear(pj, L);
+        const float4 a = ld4(xb + (long long)bi.fl * H * D), c = ld4(xb + (long long)bi.ce * H * D);
+        const float sa = group_sum<LPR>(dot4(g, a)), sc = group_sum<LPR>(dot4(g, c));
+        dWj = sa * (1.f - bi.fr) + sc * bi.fr;
+        if (r.sub == j) {
+          G += dWj * wj;
+          if (pj <= hi) dc += wj * (sc - sa);
+        }
+        if (r.active && wj != 0.f) {
+          const float wa = wj * (1.f - bi.fr), wc = wj * bi.fr;
+          atomicAdd(reinterpret_cast<float4*>(dxb + (long long)bi.fl * H * D), make_float4(wa * g.x, wa * g.y, wa * g.z, wa * g.w));
+          if (wc != 0.f)
+            atomicAdd(reinterpret_cast<float4*>(dxb + (long long)bi.ce * H * D), make_float4(wc * g.x, wc * g.y, wc * g.z, wc * g.w));
+        }
+      }
+      if (r.sub == j) dw[s0 + j + half] = dWj;
+    }
+  }
+  G = group_sum<LPR>(G);
+  dc = group_sum<LPR>(dc);
+  __syncwarp(group_mask<LPR>());
+  // pass 2: per-tap gradients of the kernel table and of the half window
+  const float corr = sum > 1.f ? G : 0.f;
+  float dhw = 0.f;
+  for (int s = -half + r.sub; s <= half; s += LPR) {
+    const AlcTap t = alc_tap(kr, K, s, inv_hw, pc0, L);
+    if (!t.valid) continue;
+    const float dbase = (dw[s + half] - corr) * inv_norm;
+    const float dkv = t.lt.v > 0.f ? dbase * t.ex : 0.f;
+    atomicAdd(&dk[t.lt.lo], dkv * (1.f - t.lt.wh));
+    atomicAdd(&dk[t.lt.lo + 1], dkv * t.lt.wh);
+    const float dr = dbase * t.rk * t.ex * (-2.f * t.r) + dkv * t.lt.slope;
+    dhw += dr * (-t.r * inv_hw);
+  }
+  dhw = group_sum<LPR>(dhw);
+  if (r.active && r.sub == 0) {
+    dhalf_w[r.row] = dhw;
+    dcenter[r.row] = dc;
+  }
+  __syncthreads();
+  const long long row0 = (long long)blockIdx.x * RPB;
+  const long long nrows = (long long)B * L * H;
+  for (int i = threadIdx.x; i < RPB * K; i += 256) {
+    const long long rr = row0 + i / K;
+    if (rr < nrows) dkern[rr * K + i % K] = s_dk[i];
+  }
+}
+
+void chk(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+}
+void check_dims(int D, int K, int half) {
+  if (K < 2 || K > KMAX) throw std::runtime_error("fused taps: kernel table size must be in [2, 64]");
+  if (half < 0 || half > 4096) throw std::runtime_error("fused taps: half tap count out of range");
+  (void)D;
+}
+
+#define DISPATCH_LPR(D, ...)                                    \
+  switch ((D) / 4) {                                            \
+    case 2: { constexpr int LPR_ = 2; __VA_ARGS__; break; }            \
+    case 4: { constexpr int LPR_ = 4; __VA_ARGS__; break; }            \
+    case 8: { constexpr int LPR_ = 8; __VA_ARGS__; break; }            \
+    case 16: { constexpr int LPR_ = 16; __VA_ARGS__; break; }          \
+    case 32: { constexpr int LPR_ = 32; __VA_ARGS__; break; }          \
+    default: throw std::runtime_error("fused taps: head_dim must be 8, 16, 32, 64 or 128"); \
+  }
+template <typename Kern>
+void opt_in_smem(Kern k, size_t bytes) {
+  if (bytes > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) throw std::runtime_error(std::string("fused taps: shared memory opt-in: ") + cudaGetErrorString(e));
+  }
+}
+}  // namespace
+
+void tele_fused_fwd(const void* x, const float* freq, const float* phase, const float* kern, const float* expo, void* out,
+                    int B, int L, int H, int D, int K, int half, float max_rec, cudaStream_t s) {
+  check_dims(D, K, half);
+  const long long rows = (long long)B * L * H;
+  DISPATCH_LPR(D, {
+    const int rpb = 256 / LPR_;
+    tele_fwd_kernel<LPR_><<<(unsigned)((rows + rpb - 1) / rpb), 256, 0, s>>>((const bf16*)x, freq, phase, kern, expo, (bf16*)out, B, L, H, K, half, max_rec);
+  });
+  chk("tele_fused_fwd");
+}
+
+void tele_fused_bwd(const void* x, const float* freq, const float* phase, const float* kern, const float* expo,
+                    const void* dout, float* dx, float* dfreq, float* dphase, float* dkern, float* dexpo_h, int B, int L,
+                    int H, int D, int K, int half, float max_rec, cudaStream_t s) {
+  check_dims(D, K, half);
+  const long long rows = (long long)B * L * H;
+  DISPATCH_LPR(D, {
+    const int rpb = 256 / LPR_;
+    const size_t smem = (size_t)rpb * K * sizeof(float);
+    tele_bwd_kernel<LPR_><<<(unsigned)((rows + rpb - 1) / rpb), 256, smem, s>>>((const bf16*)x, freq, phase, kern, expo, (const bf16*)dout, dx,
+                                                                               dfreq, dphase, dkern, dexpo_h, B, L, H, K, half, max_rec);
+  });
+  chk("tele_fused_bwd");
+}
+
+void alc_fused_fwd(const void* x, const float* half_w, const float* center, const float* kern, void* out, int B, int L,
+                   int H, int D, int K, int half, cudaStream_t s) {
+  check_dims(D, K, half);
+  const long long rows = (long long)B * L * H;
+  DISPATCH_LPR(D, {
+    const int rpb = 256 / LPR_;
+    alc_fwd_kernel<LPR_><<<(unsigned)((rows + rpb - 1) / rpb), 256, 0, s>>>((const bf16*)x, half_w, center, kern, (bf16*)out, B, L, H, K, half);
+  });
+  chk("alc_fused_fwd");
+}
+
+void alc_fused_bwd(const void* x, const float* half_w, const float* center, const float* kern, const void* dout, float* dx,
+                   float* dhalf_w, float* dcenter, float* dkern, int B, int L, int H, int D, int K, int half, cudaStream_t s) {
+  check_dims(D, K, half);
+  if (half > 64) throw std::runtime_error("adaptive local conv: at most 129 taps");
+  const long long rows = (long long)B * L * H;
+  DISPATCH_LPR(D, {
+    const int rpb = 256 / LPR_;
+    const size_t smem = (size_t)rpb * (K + 2 * half + 1) * sizeof(float);
+    auto kernel = alc_bwd_kernel<LPR_>;
+    opt_in_smem(kernel, smem);
+    kernel<<<(unsigned)((rows + rpb - 1) / rpb), 256, smem, s>>>((const bf16*)x, half_w, center, kern, (const bf16*)dout, dx, dhalf_w, dcenter,
+                                                                dkern, B, L, H, K, half);
+  });
+  chk("alc_fused_bwd");
+}
+
+}  // namespace b200

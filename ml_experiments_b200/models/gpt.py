@@ -55,7 +55,7 @@ class GPTConfig:
     x_s: float = 2.0
     w_s: float = 2.0 ** 9
     grad_s: float = 2.0 ** 19
-    uniform_doc_len: int | None = None   # set when every document has this length (lets head_dim 64 use batched SDPA)
+    uniform_doc_len: int | None = None   # set when every document has this length (documents then start every N tokens)
 
     def to_dict(self):
         return asdict(self)

@@ -23,24 +23,7 @@ EPS = Fz.BF16_EPS
 
 
 class _Saved:
-    __slots__ = ("x_in", "x_mix", "xn", "qkv", "qkvp", "y", "lse", "x_a", "xn2", "h", "skip", "skip_idx", "sdpa")
-
-
-def _sdpa_docs(q4, doc_len: int, scale: float, window_blocks: int):
-    """Library attention for head dims the tcgen05 backward does not cover: equal-length documents as a batch.
-
-    Returns ``(y [T, H, D], leaves)``; ``leaves`` are the q / k / v tensors to differentiate with respect to."""
-    T, _, H, D = q4.shape
-    n = T // doc_len
-    leaves = [q4[:, i].reshape(n, doc_len, H, D).transpose(1, 2).detach().requires_grad_(True) for i in range(3)]
-    mask = None
-    if 0 < window_blocks * 128 < doc_len:
-        i = torch.arange(doc_len, device=q4.device)
-        mask = (i[:, None] >= i[None, :]) & ((i[None, :] // 128) > (i[:, None] // 128 - window_blocks))
-    with torch.enable_grad():
-        y = torch.nn.functional.scaled_dot_product_attention(leaves[0], leaves[1], leaves[2], attn_mask=mask,
-                                                             is_causal=mask is None, scale=scale)
-    return y, leaves
+    __slots__ = ("x_in", "x_mix", "xn", "qkv", "qkvp", "y", "lse", "x_a", "xn2", "h", "skip", "skip_idx")
 
 
 def _wgrad(dy: Tensor, x: Tensor, out_shape) -> Tensor:
@@ -93,17 +76,10 @@ def _forward_backward(model, input_seq: Tensor, target_seq: Tensor, swb: int, ne
             ve = ves[ve_map[i]] if ve_map[i] is not None else None
             o.qkv_post_fwd(s.qkv, ve, a.lambdas, cos, sin, s.qkvp, H, D, EPS)
             q4 = s.qkvp.view(T, 3, H, D)
-            if D == 128:
-                s.y, s.lse = flash_attention_forward(q4[:, 0], q4[:, 1], q4[:, 2], doc_start, doc_end, a.attn_scale, windows[i])
-                s.sdpa = None
-            else:
-                if not c.uniform_doc_len or T % c.uniform_doc_len:
-                    raise RuntimeError("head_dim != 128 needs GPTConfig.uniform_doc_len (equal-length documents)")
-                yb, leaves = _sdpa_docs(q4, c.uniform_doc_len, a.attn_scale, windows[i])
-                s.y, s.lse, s.sdpa = yb.detach().transpose(1, 2).reshape(T, H, D).contiguous(), None, (yb, leaves)
+            s.y, s.lse = flash_attention_forward(q4[:, 0], q4[:, 1], q4[:, 2], doc_start, doc_end, a.attn_scale, windows[i])
             s.x_a = G.gemm(s.y.view(T, HD), w16(a.c_proj.weight), epilogue=G.EPI_AXPBY, aux=s.x_mix, beta=1.0)
         else:
-            s.qkv = s.qkvp = s.y = s.lse = s.sdpa = None
+            s.qkv = s.qkvp = s.y = s.lse = None
             s.x_a = s.x_mix
         s.xn2 = Fz.rmsnorm(s.x_a, EPS)
         s.h = G.gemm(s.xn2, w16(blk.mlp.c_fc.weight), epilogue=G.EPI_RELU2)
@@ -172,15 +148,8 @@ def _forward_backward(model, input_seq: Tensor, target_seq: Tensor, swb: int, ne
                 dq_acc = torch.zeros(T, H, D, dtype=torch.float32, device=dev)
             else:
                 dq_acc.zero_()
-            if s.sdpa is None:
-                dq, dk, dv = flash_attention_backward(q4[:, 0], q4[:, 1], q4[:, 2], s.y, dy.view(T, H, D), s.lse, doc_start,
-                                                      doc_end, a.attn_scale, windows[i], dq_acc)
-            else:
-                yb, leaves = s.sdpa
-                n_docs = yb.shape[0]
-                gq, gk, gv = torch.autograd.grad(yb, leaves, dy.view(n_docs, -1, H, D).transpose(1, 2))
-                back = lambda t: t.transpose(1, 2).reshape(T, H, D).contiguous()
-                dq, dk, dv = back(gq).float(), back(gk), back(gv)
+            dq, dk, dv = flash_attention_backward(q4[:, 0], q4[:, 1], q4[:, 2], s.y, dy.view(T, H, D), s.lse, doc_start,
+                                                  doc_end, a.attn_scale, windows[i], dq_acc)
             dqkv = torch.empty_like(s.qkv)
             vi = ve_map[i]
             ve = ves[vi] if vi is not None else None

@@ -21,6 +21,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 from torch.utils.checkpoint import checkpoint as grad_checkpoint
 
+from ..ops.fused_taps import adaptive_local_gather, telephone_gather
 from ..ops.gather_conv import gather_conv
 
 
@@ -125,6 +126,17 @@ class TelephoneAttentionND(nn.Module):
         wgt = _lerp_table(kern, rel.abs() / max_receptive) * power * valid
         return pos, wgt
 
+    def _fused(self, xf: torch.Tensor, L: int) -> torch.Tensor:
+        """Whole sequence in one launch: the per-position scalars go to the kernel, which evaluates the taps itself."""
+        B, H, K = xf.shape[0], self.num_heads, self.max_kernel_size
+        half = min(self.max_samples, max(3, int(L ** self.scale_power))) // 2
+        wave = F.silu(llama_rmsnorm(self.wave_proj(xf), self.wave_gamma)).view(B, L, 2, H).float()
+        freq = torch.sigmoid(wave[:, :, 0]) * (self.max_freq - self.min_freq) + self.min_freq
+        phase = torch.tanh(wave[:, :, 1]) * self.max_freq
+        kern = F.silu(llama_rmsnorm(self.kernel_proj(xf), self.kernel_gamma)).view(B, L, H, K).float()
+        expo = torch.sigmoid(llama_rmsnorm(self.exponent_proj(xf), self.exponent_gamma)).float() * 3.5 + 0.5
+        return telephone_gather(xf, freq, phase, kern, expo, H, half, half * self.max_freq)
+
     def _chunk(self, x_flat: torch.Tensor, start: int, end: int, L: int) -> torch.Tensor:
         pos, wgt = self._taps(x_flat[:, start:end], start, L)
         # the gather reads the whole sequence but only produces rows [start, end): place the chunk's taps in a full-length
@@ -138,6 +150,8 @@ class TelephoneAttentionND(nn.Module):
         if self.ndim != 1:
             return _telephone_nd(self, x)
         xf = x.reshape(B, L, C)
+        if xf.is_cuda and self.head_dim in (8, 16, 32, 64, 128) and self.max_kernel_size <= 64:
+            return F.silu(self.out_proj(self._fused(xf, L))).reshape(B, *spatial, C), {}
         outs = []
         for start in range(0, L, self.chunk_size):
             end = min(start + self.chunk_size, L)
@@ -239,14 +253,7 @@ class AdaptiveLocalConv(nn.Module):
         center = torch.tanh(llama_rmsnorm(self.offset_proj(x), self.offset_gamma)).float() * max_offset
         kern = F.silu(llama_rmsnorm(self.kernel_proj(x), self.kernel_gamma)).view(B, L, H, K).float()
         v = self.v_proj(x)
-        s_off = torch.arange(-half_max, half_max + 1, device=x.device, dtype=torch.float32)
-        half_w = (window / 2).clamp(min=0.5).unsqueeze(-1)                       # [B, L, H, 1]
-        rel = s_off.abs().view(1, 1, 1, -1) / half_w                             # [B, L, H, S]
-        pos = torch.arange(L, device=x.device, dtype=torch.float32).view(1, L, 1, 1) + center.unsqueeze(-1) + s_off.view(1, 1, 1, -1)
-        valid = ((pos >= 0) & (pos < L)).float()
-        wgt = (_lerp_table(kern, rel).clamp(min=0) + 1.0) * torch.exp(-rel * rel) * valid
-        wgt = wgt / wgt.sum(-1, keepdim=True).clamp(min=1.0)
-        out = gather_conv(v, pos, wgt, H)
+        out = adaptive_local_gather(v, (window / 2).clamp(min=0.5), center, kern, H, half_max)
         out = F.silu(self.out_proj(self.se(out)))
         return out, {"window_sizes": window.detach(), "center_offsets": center.detach(),
                      "max_window": torch.tensor(max_window), "max_offset": torch.tensor(max_offset)}

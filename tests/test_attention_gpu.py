@@ -30,11 +30,12 @@ def test_attention_forward(t, doc_len, window, d):
 
 
 @pytest.mark.parametrize("t,doc_len,window", [(256, 256, 0), (1024, 1024, 0), (1024, 384, 0), (2048, 1000, 3)])
-def test_attention_backward(t, doc_len, window):
+@pytest.mark.parametrize("d", [128, 64])
+def test_attention_backward(t, doc_len, window, d):
     from ml_experiments_b200.ops import attention as A
 
-    q, k, v, ds, de = _setup(t, 2, 128, doc_len, seed=1)
-    d_o = torch.randn(t, 2, 128, device="cuda", dtype=torch.bfloat16)
+    q, k, v, ds, de = _setup(t, 2, d, doc_len, seed=1)
+    d_o = torch.randn(t, 2, d, device="cuda", dtype=torch.bfloat16)
     qf, kf, vf = (x.float().detach().requires_grad_(True) for x in (q, k, v))
     ref = A.attention_reference(qf, kf, vf, ds, 0.12, window)
     ref.backward(d_o.float())

@@ -22,6 +22,15 @@ MIXERS = [
     ("zoology.mixers.mamba2.Mamba2", dict(d_state=8, headdim=8, chunk_size=8)),
     ("zoology.mixers.rwkv.RWKVTimeMixer", dict(l_max=32, n_layer=2)),
     ("zoology.mixers.rwkv.RWKV5TimeMixer", dict(l_max=32, n_layer=2, head_size=16)),
+    ("zoology.mixers.mra.MRAAttention", dict(max_position_embeddings=32, num_heads=2, num_block_per_row=1)),
+    ("zoology.mixers.linear_attn.GatedLinearAttention", dict(num_heads=2)),
+    ("zoology.mixers.linear_attn.GatedLinearAttention", dict(num_heads=4, num_kv_heads=2, use_short_conv=True)),
+    ("zoology.mixers.linear_attn.DeltaNet", dict(num_heads=2)),
+    ("zoology.mixers.linear_attn.DeltaNet", dict(num_heads=2, use_gate=True, allow_neg_eigval=True, qk_activation="relu")),
+    ("zoology.mixers.linear_attn.GatedDeltaNet", dict(num_heads=2)),
+    ("zoology.mixers.linear_attn.RWKV7Attention", dict(head_dim=16)),
+    ("zoology.mixers.hyena.Hyena", dict(l_max=32, filter_order=8, num_heads=2)),
+    ("zoology.mixers.h3.H3", dict(l_max=32, d_state=8, head_dim=2)),
     ("zoology.mixers.hybrid.Hybrid", dict(configs=[dict(name="zoology.mixers.attention.MHA", kwargs=dict(num_heads=1)),
                                                    dict(name="zoology.mixers.base_conv.BaseConv", kwargs=dict(l_max=32))])),
 ]
@@ -138,3 +147,32 @@ def test_sweep_launcher_runs_every_config(tmp_path, monkeypatch):
     out = run_sweep(str(sweep), name="t")
     assert [o[0] for o in out] == ["a", "b", "c"]
     assert out[0][2] is None and out[2][2] is None and "not found" in out[1][2]
+
+
+def test_chunked_recurrences_match_step_by_step():
+    from ml_experiments_b200.ops import linear_recurrence as R
+    torch.manual_seed(0)
+    B, T, H, dk, dv = 2, 150, 2, 16, 24
+    q, k, v = torch.randn(B, T, H, dk), torch.randn(B, T, H, dk), torch.randn(B, T, H, dv)
+    g = torch.nn.functional.logsigmoid(torch.randn(B, T, H, dk) * 3)
+    o1, s1 = R.gla_recurrent(q, k, v, g)
+    o2, s2 = R.chunk_gla(q, k, v, g)
+    assert torch.allclose(o1, o2, atol=1e-4) and torch.allclose(s1, s2, atol=1e-4)
+    kn, beta = torch.nn.functional.normalize(k, dim=-1), torch.rand(B, T, H)
+    for gate in (None, torch.nn.functional.logsigmoid(torch.randn(B, T, H) + 2)):
+        o1, s1 = R.delta_rule_recurrent(q, kn, v, beta, gate)
+        o2, s2 = R.chunk_delta_rule(q, kn, v, beta, gate)
+        assert torch.allclose(o1, o2, atol=1e-4) and torch.allclose(s1, s2, atol=1e-4)
+
+
+def test_state_space_kernels_match_their_recurrences():
+    from ml_experiments_b200.zoology.mixers.h3 import SSKernel
+    torch.manual_seed(0)
+    for mode, extra in (("diag", dict(disc="bilinear")), ("diag", dict(disc="zoh")), ("diag", dict(measure="diag")), ("shift", {})):
+        k = SSKernel(4, N=8, L=20, mode=mode, **extra)
+        K = k(L=20)[0][0]
+        state, ys = k.default_state(1), []
+        for t in range(20):
+            y, state = k.step(torch.ones(1, 4) * (t == 0), state)
+            ys.append(y[0, 0])
+        assert torch.allclose(torch.stack(ys, -1), K, atol=1e-5)
