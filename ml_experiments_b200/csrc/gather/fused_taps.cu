@@ -66,19 +66,33 @@ struct Row {
   int b, l, h, sub;
   bool active;
 };
+// A block owns 256 / LPR consecutive positions of ONE (batch, head): neighbouring positions sample neighbouring rows, so
+// the floor row of one is the ceil row of the next and the pair of loads hits L1 instead of L2.
 template <int LPR>
 __device__ __forceinline__ Row locate(int B, int L, int H) {
+  constexpr int RPB = 256 / LPR;
+  const int nt = (L + RPB - 1) / RPB;
   Row r;
-  r.row = ((long long)blockIdx.x * 256 + threadIdx.x) / LPR;
+  const int tile = blockIdx.x % nt;
+  r.h = (blockIdx.x / nt) % H;
+  r.b = blockIdx.x / (nt * H);
   r.sub = threadIdx.x % LPR;
-  r.active = r.row < (long long)B * L * H;
-  const long long rr = r.active ? r.row : 0;
-  r.row = rr;
-  r.h = (int)(rr % H);
-  r.bl = rr / H;
-  r.b = (int)(r.bl / L);
-  r.l = (int)(r.bl % L);
+  const int l = tile * RPB + threadIdx.x / LPR;
+  r.active = l < L;
+  r.l = r.active ? l : L - 1;
+  r.bl = (long long)r.b * L + r.l;
+  r.row = r.bl * H + r.h;
   return r;
+}
+template <int LPR>
+__device__ __forceinline__ void store_dkern(float* __restrict__ dkern, const float* s_dk, int L, int H, int K) {
+  constexpr int RPB = 256 / LPR;
+  const int nt = (L + RPB - 1) / RPB;
+  const int tile = blockIdx.x % nt, h = (blockIdx.x / nt) % H, b = blockIdx.x / (nt * H);
+  for (int i = threadIdx.x; i < RPB * K; i += 256) {
+    const int l = tile * RPB + i / K;
+    if (l < L) dkern[(((long long)b * L + l) * H + h) * K + i % K] = s_dk[i];
+  }
 }
 
 struct Bil {
@@ -209,12 +223,7 @@ tele_bwd_kernel(const bf16* __restrict__ x, const float* __restrict__ freq, cons
     dexpo_h[r.row] = de;
   }
   __syncthreads();
-  const long long row0 = (long long)blockIdx.x * RPB;
-  const long long nrows = (long long)B * L * H;
-  for (int i = threadIdx.x; i < RPB * K; i += 256) {
-    const long long rr = row0 + i / K;
-    if (rr < nrows) dkern[rr * K + i % K] = s_dk[i];
-  }
+  store_dkern<LPR>(dkern, s_dk, L, H, K);
 }
 
 // ------------------------------------------------------------------------------------------------ adaptive local conv
@@ -353,12 +362,7 @@ alc_bwd_kernel(const bf16* __restrict__ x, const float* __restrict__ half_w, con
     dcenter[r.row] = dc;
   }
   __syncthreads();
-  const long long row0 = (long long)blockIdx.x * RPB;
-  const long long nrows = (long long)B * L * H;
-  for (int i = threadIdx.x; i < RPB * K; i += 256) {
-    const long long rr = row0 + i / K;
-    if (rr < nrows) dkern[rr * K + i % K] = s_dk[i];
-  }
+  store_dkern<LPR>(dkern, s_dk, L, H, K);
 }
 
 void chk(const char* what) {
@@ -392,10 +396,10 @@ void opt_in_smem(Kern k, size_t bytes) {
 void tele_fused_fwd(const void* x, const float* freq, const float* phase, const float* kern, const float* expo, void* out,
                     int B, int L, int H, int D, int K, int half, float max_rec, cudaStream_t s) {
   check_dims(D, K, half);
-  const long long rows = (long long)B * L * H;
   DISPATCH_LPR(D, {
     const int rpb = 256 / LPR_;
-    tele_fwd_kernel<LPR_><<<(unsigned)((rows + rpb - 1) / rpb), 256, 0, s>>>((const bf16*)x, freq, phase, kern, expo, (bf16*)out, B, L, H, K, half, max_rec);
+    const long long nblk = (long long)B * H * ((L + rpb - 1) / rpb);
+    tele_fwd_kernel<LPR_><<<(unsigned)nblk, 256, 0, s>>>((const bf16*)x, freq, phase, kern, expo, (bf16*)out, B, L, H, K, half, max_rec);
   });
   chk("tele_fused_fwd");
 }
@@ -404,11 +408,11 @@ void tele_fused_bwd(const void* x, const float* freq, const float* phase, const 
                     const void* dout, float* dx, float* dfreq, float* dphase, float* dkern, float* dexpo_h, int B, int L,
                     int H, int D, int K, int half, float max_rec, cudaStream_t s) {
   check_dims(D, K, half);
-  const long long rows = (long long)B * L * H;
   DISPATCH_LPR(D, {
     const int rpb = 256 / LPR_;
+    const long long nblk = (long long)B * H * ((L + rpb - 1) / rpb);
     const size_t smem = (size_t)rpb * K * sizeof(float);
-    tele_bwd_kernel<LPR_><<<(unsigned)((rows + rpb - 1) / rpb), 256, smem, s>>>((const bf16*)x, freq, phase, kern, expo, (const bf16*)dout, dx,
+    tele_bwd_kernel<LPR_><<<(unsigned)nblk, 256, smem, s>>>((const bf16*)x, freq, phase, kern, expo, (const bf16*)dout, dx,
                                                                                dfreq, dphase, dkern, dexpo_h, B, L, H, K, half, max_rec);
   });
   chk("tele_fused_bwd");
@@ -417,10 +421,10 @@ void tele_fused_bwd(const void* x, const float* freq, const float* phase, const 
 void alc_fused_fwd(const void* x, const float* half_w, const float* center, const float* kern, void* out, int B, int L,
                    int H, int D, int K, int half, cudaStream_t s) {
   check_dims(D, K, half);
-  const long long rows = (long long)B * L * H;
   DISPATCH_LPR(D, {
     const int rpb = 256 / LPR_;
-    alc_fwd_kernel<LPR_><<<(unsigned)((rows + rpb - 1) / rpb), 256, 0, s>>>((const bf16*)x, half_w, center, kern, (bf16*)out, B, L, H, K, half);
+    const long long nblk = (long long)B * H * ((L + rpb - 1) / rpb);
+    alc_fwd_kernel<LPR_><<<(unsigned)nblk, 256, 0, s>>>((const bf16*)x, half_w, center, kern, (bf16*)out, B, L, H, K, half);
   });
   chk("alc_fused_fwd");
 }
@@ -429,13 +433,13 @@ void alc_fused_bwd(const void* x, const float* half_w, const float* center, cons
                    float* dhalf_w, float* dcenter, float* dkern, int B, int L, int H, int D, int K, int half, cudaStream_t s) {
   check_dims(D, K, half);
   if (half > 64) throw std::runtime_error("adaptive local conv: at most 129 taps");
-  const long long rows = (long long)B * L * H;
   DISPATCH_LPR(D, {
     const int rpb = 256 / LPR_;
+    const long long nblk = (long long)B * H * ((L + rpb - 1) / rpb);
     const size_t smem = (size_t)rpb * (K + 2 * half + 1) * sizeof(float);
     auto kernel = alc_bwd_kernel<LPR_>;
     opt_in_smem(kernel, smem);
-    kernel<<<(unsigned)((rows + rpb - 1) / rpb), 256, smem, s>>>((const bf16*)x, half_w, center, kern, (const bf16*)dout, dx, dhalf_w, dcenter,
+    kernel<<<(unsigned)nblk, 256, smem, s>>>((const bf16*)x, half_w, center, kern, (const bf16*)dout, dx, dhalf_w, dcenter,
                                                                 dkern, B, L, H, K, half);
   });
   chk("alc_fused_bwd");

@@ -31,6 +31,17 @@ MIXERS = [
     ("zoology.mixers.linear_attn.RWKV7Attention", dict(head_dim=16)),
     ("zoology.mixers.hyena.Hyena", dict(l_max=32, filter_order=8, num_heads=2)),
     ("zoology.mixers.h3.H3", dict(l_max=32, d_state=8, head_dim=2)),
+    ("zoology.mixers.scatterbrain.SBLocalAttention", dict(num_heads=2, window_size=4, feature_dim=8, dropout=0.0)),
+    ("zoology.mixers.scatterbrain.ScatterBrain", dict(feature_dim=4, num_heads=4, num_key_value_heads=2)),
+    ("zoology.mixers.selective.SigmoidLookups", dict(num_heads=2)),
+    ("zoology.mixers.selective.SMA", dict(num_heads=2)),
+    ("zoology.mixers.nsa.SparseAttention", dict(num_heads=2, sliding_window_size=4, compress_block_size=4, selection_block_size=4, num_selected_blocks=2)),
+    ("zoology.mixers.nsa.SparseAttention", dict(num_heads=2, kv_heads=1, sliding_window_size=4, compress_block_size=4, selection_block_size=4, num_selected_blocks=2, query_heads_share_selected_kv=False)),
+    ("zoology.mixers.bigbird.BigBIRDAttention", dict(block_size=2)),
+    ("zoology.mixers.nystrom.NystromAttention", dict(num_heads=2, num_landmarks=64)),
+    ("zoology.mixers.ttt.TTT", dict(num_heads=2)),
+    ("zoology.mixers.ttt.TTT", dict(num_heads=2, ttt_layer_type="mlp", use_gate=True, mini_batch_size=8)),
+    ("zoology.mixers.ttt.TTT", dict(num_heads=2, share_qk=True)),
     ("zoology.mixers.hybrid.Hybrid", dict(configs=[dict(name="zoology.mixers.attention.MHA", kwargs=dict(num_heads=1)),
                                                    dict(name="zoology.mixers.base_conv.BaseConv", kwargs=dict(l_max=32))])),
 ]
@@ -39,7 +50,7 @@ MIXERS = [
 @pytest.mark.parametrize("name,kwargs", MIXERS)
 def test_mixer_is_causal_and_differentiable(name, kwargs):
     torch.manual_seed(0)
-    mixer = import_from_str(name)(d_model=32, layer_idx=1, **kwargs).eval()
+    mixer = import_from_str(name)(d_model=32, layer_idx=1, **kwargs).train()
     x = torch.randn(2, 24, 32, requires_grad=True)
     y = mixer(x)
     assert y.shape == x.shape
@@ -176,3 +187,26 @@ def test_state_space_kernels_match_their_recurrences():
             y, state = k.step(torch.ones(1, 4) * (t == 0), state)
             ys.append(y[0, 0])
         assert torch.allclose(torch.stack(ys, -1), K, atol=1e-5)
+
+
+def test_mixers_that_look_ahead_by_design():
+    """The landmark Nystrom approximation and the eval-mode top-k of the selective look-ups see the whole sequence, as
+    in the reference; they are checked for shape, gradients and their exact special cases only."""
+    from ml_experiments_b200.zoology.mixers.nystrom import NystromAttention, iterative_pinv
+    from ml_experiments_b200.zoology.mixers.selective import SelectiveLookups
+    from ml_experiments_b200.zoology.mixers.scatterbrain import SBLocalAttention
+    torch.manual_seed(0)
+    x = torch.randn(2, 24, 32, requires_grad=True)
+    for m in (NystromAttention(32, num_heads=2, num_landmarks=8), NystromAttention(32, num_heads=2, num_landmarks=8, split_heads=True, conv_kernel_size=3),
+              SelectiveLookups(32, 2).eval(), SelectiveLookups(32, 2).train()):
+        y = m(x)
+        assert y.shape == x.shape
+        y.sum().backward()
+        assert torch.isfinite(x.grad).all()
+    a = torch.softmax(torch.randn(3, 8, 8), dim=-1)
+    assert torch.allclose(iterative_pinv(a, 20) @ a, torch.eye(8).expand(3, 8, 8), atol=1e-2)
+    # a window covering the whole sequence makes the sparse + low-rank decomposition exact softmax attention
+    m = SBLocalAttention(32, 2, window_size=64, feature_dim=8, dropout=0.0)
+    q, k, v = m.Wqkv(x).view(2, 24, 3, 2, 16).permute(2, 0, 3, 1, 4)
+    ref = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(2, 24, 32)
+    assert torch.allclose(m(x), m.out_proj(ref), atol=1e-5)
