@@ -10,6 +10,7 @@
 #include "fused/fused.h"
 #include "gather/gather_conv.h"
 #include "gather/fused_taps.h"
+#include "fused/norm_act.h"
 #include "gemm/gemm.h"
 #include "mra/mra.h"
 #include "scan/s6_scan.h"
@@ -582,6 +583,33 @@ void alc_fused_bwd(const Tensor& x, const Tensor& half_w, const Tensor& center, 
                       C / (int)H, K, (int)half, cur_stream());
 }
 
+// ---------------------------------------------------------------------------------------------- RMSNorm + activation
+bool norm_io_bf16(const Tensor& t, const char* n) {
+  TORCH_CHECK(t.is_cuda() && t.is_contiguous() && (t.scalar_type() == at::kBFloat16 || t.scalar_type() == at::kFloat), n, ": contiguous bf16 or fp32 CUDA tensor");
+  return t.scalar_type() == at::kBFloat16;
+}
+
+void rms_act_fwd(const Tensor& x, const Tensor& w, Tensor y, Tensor rstd, double eps, int64_t act) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  const bool xb = norm_io_bf16(x, "x"), yb = norm_io_bf16(y, "y");
+  const int C = (int)x.size(-1);
+  const int64_t R = x.numel() / C;
+  TORCH_CHECK(y.numel() == x.numel(), "y: x's shape");
+  chk_rows_f32(w, C, "weight"); chk_rows_f32(rstd, R, "rstd");
+  b200::rms_act_fwd(x.data_ptr(), xb, w.data_ptr<float>(), y.data_ptr(), yb, rstd.data_ptr<float>(), R, C, (float)eps, (int)act, cur_stream());
+}
+
+void rms_act_bwd(const Tensor& x, const Tensor& w, const Tensor& rstd, const Tensor& dy, Tensor dx, Tensor dw, int64_t act) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  const bool xb = norm_io_bf16(x, "x"), gb = norm_io_bf16(dy, "dy");
+  TORCH_CHECK(norm_io_bf16(dx, "dx") == xb && dx.numel() == x.numel() && dy.numel() == x.numel(), "dx: x's dtype and shape; dy: x's shape");
+  const int C = (int)x.size(-1);
+  const int64_t R = x.numel() / C;
+  chk_rows_f32(w, C, "weight"); chk_rows_f32(rstd, R, "rstd"); chk_rows_f32(dw, C, "dw");
+  b200::rms_act_bwd(x.data_ptr(), xb, w.data_ptr<float>(), rstd.data_ptr<float>(), dy.data_ptr(), gb, dx.data_ptr(), dw.data_ptr<float>(), R, C,
+                    (int)act, cur_stream());
+}
+
 }  // namespace
 
 TORCH_LIBRARY(b200, m) {
@@ -614,6 +642,8 @@ TORCH_LIBRARY(b200, m) {
   m.def("s6_scan_bwd(Tensor u, Tensor delta, Tensor? delta_bias, bool softplus, Tensor A, Tensor Bm, Tensor Cm, Tensor? Dv, Tensor? z, Tensor? y_pre, Tensor dout, Tensor state, Tensor(a!) du, Tensor(b!) ddelta, Tensor(c!) dA, Tensor(d!) dB_part, Tensor(e!) dC_part, Tensor(f!)? dD, Tensor(g!)? dz, Tensor(h!)? ddelta_bias) -> ()");
   m.def("causal_conv1d_silu_fwd(Tensor x, Tensor w, Tensor? bias, Tensor(a!) y) -> ()");
   m.def("causal_conv1d_silu_bwd(Tensor x, Tensor w, Tensor? bias, Tensor dy, Tensor(a!) dx, Tensor(b!) dw, Tensor(c!)? dbias) -> ()");
+  m.def("rms_act_fwd(Tensor x, Tensor w, Tensor(a!) y, Tensor(b!) rstd, float eps, int act) -> ()");
+  m.def("rms_act_bwd(Tensor x, Tensor w, Tensor rstd, Tensor dy, Tensor(a!) dx, Tensor(b!) dw, int act) -> ()");
   m.def("tele_fused_fwd(Tensor x, Tensor freq, Tensor phase, Tensor kern, Tensor expo, Tensor(a!) out, int H, int half, float max_rec) -> ()");
   m.def("tele_fused_bwd(Tensor x, Tensor freq, Tensor phase, Tensor kern, Tensor expo, Tensor dout, Tensor(a!) dx, Tensor(b!) dfreq, Tensor(c!) dphase, Tensor(d!) dkern, Tensor(e!) dexpo_h, int H, int half, float max_rec) -> ()");
   m.def("alc_fused_fwd(Tensor x, Tensor half_w, Tensor center, Tensor kern, Tensor(a!) out, int H, int half) -> ()");
@@ -660,6 +690,8 @@ TORCH_LIBRARY_IMPL(b200, CUDA, m) {
   m.impl("s6_scan_bwd", &s6_scan_bwd);
   m.impl("causal_conv1d_silu_fwd", &causal_conv1d_silu_fwd);
   m.impl("causal_conv1d_silu_bwd", &causal_conv1d_silu_bwd);
+  m.impl("rms_act_fwd", &rms_act_fwd);
+  m.impl("rms_act_bwd", &rms_act_bwd);
   m.impl("tele_fused_fwd", &tele_fused_fwd);
   m.impl("tele_fused_bwd", &tele_fused_bwd);
   m.impl("alc_fused_fwd", &alc_fused_fwd);

@@ -22,12 +22,13 @@ import torch.nn.functional as F
 from torch.utils.checkpoint import checkpoint as grad_checkpoint
 
 from ..ops.fused_taps import adaptive_local_gather, telephone_gather
-from ..ops.gather_conv import gather_conv
+from ..ops.gather_conv import gather_conv, linear_resample
+from ..ops.norm_act import rms_norm_act
 
 
-def llama_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
-    xf = x.float()
-    return (weight * (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps))).to(x.dtype)
+def llama_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, act: str = "none", out_dtype=None) -> torch.Tensor:
+    """``act(weight * x / rms(x))`` in one kernel on CUDA (``act`` in none / silu / sigmoid / tanh)."""
+    return rms_norm_act(x, weight, eps, act, out_dtype)
 
 
 class RMSNorm(nn.Module):
@@ -113,15 +114,15 @@ class TelephoneAttentionND(nn.Module):
         c = self.max_samples // 2
         s_off = self.stride_grid[c - half:c + half + 1, 0].to(torch.float32)
         max_receptive = half * self.max_freq
-        wave = F.silu(llama_rmsnorm(self.wave_proj(x_chunk), self.wave_gamma)).view(B, n, 2, H).float()
+        wave = llama_rmsnorm(self.wave_proj(x_chunk), self.wave_gamma, act="silu", out_dtype=torch.float32).view(B, n, 2, H)
         freq = torch.sigmoid(wave[:, :, 0]) * (self.max_freq - self.min_freq) + self.min_freq
         phase = torch.tanh(wave[:, :, 1]) * self.max_freq
         centers = torch.arange(start, start + n, device=x_chunk.device, dtype=torch.float32).view(1, n, 1, 1)
         rel = s_off.view(1, 1, 1, -1) * freq.unsqueeze(-1)
         pos = centers + rel + phase.unsqueeze(-1)
         valid = ((pos >= 0) & (pos < L)).float()
-        kern = F.silu(llama_rmsnorm(self.kernel_proj(x_chunk), self.kernel_gamma)).view(B, n, H, K).float()
-        expo = torch.sigmoid(llama_rmsnorm(self.exponent_proj(x_chunk), self.exponent_gamma)).float() * 3.5 + 0.5
+        kern = llama_rmsnorm(self.kernel_proj(x_chunk), self.kernel_gamma, act="silu", out_dtype=torch.float32).view(B, n, H, K)
+        expo = llama_rmsnorm(self.exponent_proj(x_chunk), self.exponent_gamma, act="sigmoid", out_dtype=torch.float32) * 3.5 + 0.5
         power = (1.0 + rel.abs() / L).pow(-expo.unsqueeze(-1))
         wgt = _lerp_table(kern, rel.abs() / max_receptive) * power * valid
         return pos, wgt
@@ -130,11 +131,11 @@ class TelephoneAttentionND(nn.Module):
         """Whole sequence in one launch: the per-position scalars go to the kernel, which evaluates the taps itself."""
         B, H, K = xf.shape[0], self.num_heads, self.max_kernel_size
         half = min(self.max_samples, max(3, int(L ** self.scale_power))) // 2
-        wave = F.silu(llama_rmsnorm(self.wave_proj(xf), self.wave_gamma)).view(B, L, 2, H).float()
+        wave = llama_rmsnorm(self.wave_proj(xf), self.wave_gamma, act="silu", out_dtype=torch.float32).view(B, L, 2, H)
         freq = torch.sigmoid(wave[:, :, 0]) * (self.max_freq - self.min_freq) + self.min_freq
         phase = torch.tanh(wave[:, :, 1]) * self.max_freq
-        kern = F.silu(llama_rmsnorm(self.kernel_proj(xf), self.kernel_gamma)).view(B, L, H, K).float()
-        expo = torch.sigmoid(llama_rmsnorm(self.exponent_proj(xf), self.exponent_gamma)).float() * 3.5 + 0.5
+        kern = llama_rmsnorm(self.kernel_proj(xf), self.kernel_gamma, act="silu", out_dtype=torch.float32).view(B, L, H, K)
+        expo = llama_rmsnorm(self.exponent_proj(xf), self.exponent_gamma, act="sigmoid", out_dtype=torch.float32) * 3.5 + 0.5
         return telephone_gather(xf, freq, phase, kern, expo, H, half, half * self.max_freq)
 
     def _chunk(self, x_flat: torch.Tensor, start: int, end: int, L: int) -> torch.Tensor:
@@ -178,7 +179,7 @@ def _telephone_nd(mod: TelephoneAttentionND, x: torch.Tensor):
     grid = mod.stride_grid.to(torch.float32)
     S = grid.shape[0]
     half = mod.max_offset
-    wave = F.silu(llama_rmsnorm(mod.wave_proj(xf), mod.wave_gamma)).view(B, L, 2, H).float()
+    wave = llama_rmsnorm(mod.wave_proj(xf), mod.wave_gamma, act="silu", out_dtype=torch.float32).view(B, L, 2, H)
     freq = torch.sigmoid(wave[:, :, 0]) * (mod.max_freq - mod.min_freq) + mod.min_freq
     phase = torch.tanh(wave[:, :, 1]) * mod.max_freq
     coords = torch.stack([m.flatten() for m in torch.meshgrid(*[torch.arange(s, device=x.device, dtype=torch.float32)
@@ -192,8 +193,8 @@ def _telephone_nd(mod: TelephoneAttentionND, x: torch.Tensor):
         idx += pos[..., d].long().clamp(0, spatial[d] - 1) * stride
         stride *= spatial[d]
     rel = (grid.view(1, 1, 1, S, -1) * freq.view(B, L, H, 1, 1)).norm(dim=-1)
-    kern = F.silu(llama_rmsnorm(mod.kernel_proj(xf), mod.kernel_gamma)).view(B, L, H, K).float()
-    expo = torch.sigmoid(llama_rmsnorm(mod.exponent_proj(xf), mod.exponent_gamma)).float() * 3.5 + 0.5
+    kern = llama_rmsnorm(mod.kernel_proj(xf), mod.kernel_gamma, act="silu", out_dtype=torch.float32).view(B, L, H, K)
+    expo = llama_rmsnorm(mod.exponent_proj(xf), mod.exponent_gamma, act="sigmoid", out_dtype=torch.float32) * 3.5 + 0.5
     wgt = _lerp_table(kern, rel / (half * mod.max_freq)) * (1.0 + rel / L).pow(-expo.unsqueeze(-1)) * valid.float()
     xh = xf.view(B, L, H, D)
     bidx = torch.arange(B, device=x.device).view(B, 1, 1, 1).expand_as(idx)
@@ -249,9 +250,9 @@ class AdaptiveLocalConv(nn.Module):
         max_window = min(int(L ** self.scale_power), K)
         half_max = max_window // 2
         max_offset = int(L ** self.scale_power)
-        window = self.min_window + torch.sigmoid(llama_rmsnorm(self.window_proj(x), self.window_gamma)).float() * (max_window - self.min_window)
-        center = torch.tanh(llama_rmsnorm(self.offset_proj(x), self.offset_gamma)).float() * max_offset
-        kern = F.silu(llama_rmsnorm(self.kernel_proj(x), self.kernel_gamma)).view(B, L, H, K).float()
+        window = self.min_window + llama_rmsnorm(self.window_proj(x), self.window_gamma, act="sigmoid", out_dtype=torch.float32) * (max_window - self.min_window)
+        center = llama_rmsnorm(self.offset_proj(x), self.offset_gamma, act="tanh", out_dtype=torch.float32) * max_offset
+        kern = llama_rmsnorm(self.kernel_proj(x), self.kernel_gamma, act="silu", out_dtype=torch.float32).view(B, L, H, K)
         v = self.v_proj(x)
         out = adaptive_local_gather(v, (window / 2).clamp(min=0.5), center, kern, H, half_max)
         out = F.silu(self.out_proj(self.se(out)))
@@ -304,7 +305,7 @@ class LowRankAttention(nn.Module):
         B, L, C = x.shape
         H, d = self.num_heads, self.head_dim
         r = max(1, int(L ** self.reduction_power))
-        xd = F.interpolate(x.transpose(1, 2), size=r, mode="linear", align_corners=False).transpose(1, 2)
+        xd = linear_resample(x, r)
         q = self.q_proj(xd).reshape(B, r, H, 2, d)
         k = self.k_proj(xd).reshape(B, r, H, 2, d)
         v = self.v_proj(xd).reshape(B, r, H, 2 * d).transpose(1, 2)
@@ -317,7 +318,7 @@ class LowRankAttention(nn.Module):
         o2 = F.scaled_dot_product_attention(qs[1].transpose(1, 2), ks[1].transpose(1, 2), v.to(qs[1].dtype), scale=self.scale)
         diff = self.head_norm((o1 - lam * o2).transpose(1, 2)) * (1 - self.lambda_init)
         low = F.silu(self.out_proj(diff.reshape(B, r, C)))
-        full = F.interpolate(low.transpose(1, 2), size=L, mode="linear", align_corners=False).transpose(1, 2)
+        full = linear_resample(low, L)
         return full, low
 
 

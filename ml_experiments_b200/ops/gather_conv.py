@@ -57,3 +57,16 @@ def gather_conv(x: torch.Tensor, pos: torch.Tensor, wgt: torch.Tensor, num_heads
     if x.is_cuda and d in (8, 16, 32, 64, 128):
         return _GatherConv.apply(x, pos, wgt, num_heads, pos_max)
     return gather_conv_ref(x, pos, wgt, num_heads, pos_max)
+
+
+def linear_resample(x: torch.Tensor, size: int) -> torch.Tensor:
+    """``[B, L, C] -> [B, size, C]`` with the sample positions of ``F.interpolate(mode="linear", align_corners=False)``:
+    one fractional tap per output row on the gather kernel (channel-last, no transposes, fp32 atomics backward)."""
+    B, L, C = x.shape
+    d = next((d for d in (128, 64, 32, 16, 8) if C % d == 0), None)
+    if not x.is_cuda or d is None:
+        return torch.nn.functional.interpolate(x.transpose(1, 2), size=size, mode="linear", align_corners=False).transpose(1, 2)
+    H = C // d
+    src = ((torch.arange(size, device=x.device, dtype=torch.float32) + 0.5) * (L / size) - 0.5).clamp(min=0)
+    pos = src.view(1, size, 1, 1).expand(B, size, H, 1).contiguous()
+    return gather_conv(x, pos, torch.ones_like(pos), H, pos_max=float(L - 1))

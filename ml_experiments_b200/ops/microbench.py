@@ -52,7 +52,7 @@ def _doc_bounds(t: int, doc_len: int):
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("op", choices=["gemm", "attn_fwd", "attn_bwd", "softcap_ce", "s6_fwd", "s6_bwd", "gather_fwd", "gather_bwd",
-                                   "newton_schulz", "ssd"])
+                                   "newton_schulz", "ssd", "tele_fwd", "tele_bwd", "alc_fwd", "alc_bwd", "rms_act"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -141,6 +141,38 @@ def main(argv=None):
             g = torch.randn_like(y)
             fn = lambda: torch.autograd.grad(y, (x, pos, wgt), g, retain_graph=True)
         bytes_ = b * L * (2.0 * c * (1 + 2 * s) + 8.0 * h * s)  # every tap reads two rows of its head
+    elif a.op in ("tele_fwd", "tele_bwd", "alc_fwd", "alc_bwd"):
+        from . import fused_taps as T
+        b, L, c, h, s = a.batch, a.seq, a.channels, a.heads, a.taps
+        half, K = s // 2, 64
+        x = torch.randn(b, L, c, device=dev, dtype=bf, requires_grad=True)
+        kern = torch.randn(b, L, h, K, device=dev, requires_grad=True)
+        if a.op.startswith("tele"):
+            p1 = (torch.rand(b, L, h, device=dev) * 15 + 1).requires_grad_(True)          # stride per sample
+            p2 = ((torch.rand(b, L, h, device=dev) * 2 - 1) * 16).requires_grad_(True)    # phase
+            expo = (torch.rand(b, L, 1, device=dev) * 3.5 + 0.5).requires_grad_(True)
+            call = lambda xx, *ps: T.telephone_gather(xx, *ps, h, half, half * 16.0)
+            leaves = (x, p1, p2, kern, expo)
+        else:
+            p1 = (torch.rand(b, L, h, device=dev) * half + 0.5).requires_grad_(True)      # half window
+            p2 = ((torch.rand(b, L, h, device=dev) * 2 - 1) * half).requires_grad_(True)  # centre offset
+            call = lambda xx, *ps: T.adaptive_local_gather(xx, *ps, h, half)
+            leaves = (x, p1, p2, kern)
+        if a.op.endswith("fwd"):
+            det = tuple(t.detach() for t in leaves)
+            fn = lambda: call(*det)
+        else:
+            y = call(*leaves)
+            g = torch.randn_like(y)
+            fn = lambda: torch.autograd.grad(y, leaves, g, retain_graph=True)
+        taps = 2 * half + 1
+        bytes_ = b * L * (2.0 * c * (1 + 2 * taps) + 4.0 * h * (K + 3))  # every tap reads two bf16 rows of its head (mostly from L2)
+    elif a.op == "rms_act":
+        from .norm_act import rms_norm_act
+        x = torch.randn(a.batch * a.seq, a.channels, device=dev, dtype=bf)
+        w = torch.ones(a.channels, device=dev)
+        fn = lambda: rms_norm_act(x, w, 1e-6, "silu", torch.float32)
+        bytes_ = x.numel() * 6.0
     elif a.op == "newton_schulz":
         from .newton_schulz import newton_schulz_
         X = torch.randn(a.batch, a.m, a.n, device=dev, dtype=bf)

@@ -1,0 +1,53 @@
+"""Weighted RMSNorm with a fused activation (one kernel forward, one backward): ``act(w * x * rsqrt(mean(x^2) + eps))``.
+
+The Ripple-family operators normalise every small projection this way (telephone / adaptive-conv wave, kernel, window
+and exponent heads: src/heuristic_secrets/models/telephone_attention.py:17-30,124-140 of the reference) and the
+unfused PyTorch form costs about eight elementwise kernels forward and twice that backward per call.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from .runtime import ops
+
+_ACTS = {"none": 0, "silu": 1, "sigmoid": 2, "tanh": 3}
+_ACT_FN = {"none": lambda t: t, "silu": F.silu, "sigmoid": torch.sigmoid, "tanh": torch.tanh}
+
+
+def rms_norm_act_ref(x, weight, eps: float = 1e-6, act: str = "none", out_dtype=None):
+    xf = x.float()
+    y = _ACT_FN[act](weight.float() * (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)))
+    return y.to(out_dtype or x.dtype)
+
+
+class _RmsAct(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, eps, act, out_dtype):
+        xc = x.contiguous()
+        w32 = weight.detach().float().contiguous()
+        y = torch.empty(xc.shape, dtype=out_dtype, device=x.device)
+        rstd = torch.empty(xc.numel() // xc.shape[-1], dtype=torch.float32, device=x.device)
+        ops().rms_act_fwd(xc, w32, y, rstd, eps, act)
+        ctx.save_for_backward(xc, w32, rstd)
+        ctx.act, ctx.wdtype = act, weight.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xc, w32, rstd = ctx.saved_tensors
+        if dy.dtype not in (torch.bfloat16, torch.float32):
+            dy = dy.float()
+        dx = torch.empty_like(xc)
+        dw = torch.zeros_like(w32)
+        ops().rms_act_bwd(xc, w32, rstd, dy.contiguous(), dx, dw, ctx.act)
+        return dx, dw.to(ctx.wdtype), None, None, None
+
+
+def rms_norm_act(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, act: str = "none", out_dtype=None) -> torch.Tensor:
+    out_dtype = out_dtype or x.dtype
+    ok = (x.is_cuda and x.dtype in (torch.bfloat16, torch.float32) and out_dtype in (torch.bfloat16, torch.float32)
+          and 1 <= x.shape[-1] <= 4096 and weight.numel() == x.shape[-1])
+    if not ok:
+        return rms_norm_act_ref(x, weight, eps, act, out_dtype)
+    return _RmsAct.apply(x, weight, float(eps), _ACTS[act], out_dtype)

@@ -54,3 +54,25 @@ def test_adaptive_local_fused(B, L, H, D, K, half):
     ref.backward(dout)
     for name, a, b in zip(("dx", "dhalf_w", "dcenter", "dkern"), leaves, ref_leaves):
         assert _rel(a.grad, b.grad) < 2e-2, (name, _rel(a.grad, b.grad))
+
+
+@pytest.mark.parametrize("C", [1, 4, 8, 64, 256, 300, 1024])
+@pytest.mark.parametrize("act", ["none", "silu", "sigmoid", "tanh"])
+@pytest.mark.parametrize("dtypes", [(torch.bfloat16, torch.float32), (torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16)])
+def test_rms_norm_act(C, act, dtypes):
+    from ml_experiments_b200.ops.norm_act import rms_norm_act, rms_norm_act_ref
+
+    din, dout = dtypes
+    g = torch.Generator().manual_seed(C)
+    x = torch.randn(3, 37, C, generator=g).to("cuda", din)
+    w = (torch.rand(C, generator=g) + 0.5).to("cuda")
+    xa, wa = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    xb, wb = x.float().clone().requires_grad_(True), w.clone().requires_grad_(True)
+    ya = rms_norm_act(xa, wa, 1e-6, act, dout)
+    yb = rms_norm_act_ref(xb, wb, 1e-6, act, torch.float32)
+    assert ya.dtype == dout and _rel(ya, yb) < (1e-2 if dout == torch.bfloat16 else 1e-5)
+    gy = torch.randn(3, 37, C, generator=g).to("cuda")
+    ya.backward(gy.to(dout))
+    yb.backward(gy.to(dout).float())
+    tol = 2e-2 if torch.bfloat16 in dtypes else 1e-4
+    assert _rel(xa.grad, xb.grad) < tol and _rel(wa.grad, wb.grad) < tol

@@ -39,3 +39,19 @@ def test_gather_conv_chunk_of_queries():
     wgt = torch.randn(B, Lq, H, S, device="cuda")
     out, ref = gather_conv(x, pos, wgt, H), gather_conv_ref(x, pos, wgt, H)
     assert out.shape == (B, Lq, H * D) and ((out - ref).abs().max() / ref.abs().max()).item() < 2e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("L,size", [(1000, 177), (177, 1000), (64, 64), (5, 300)])
+def test_linear_resample_matches_interpolate(L, size):
+    from ml_experiments_b200.ops.gather_conv import linear_resample
+
+    x = torch.randn(2, L, 96, device="cuda").bfloat16().float()
+    a, b = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+    ya = linear_resample(a, size)
+    yb = torch.nn.functional.interpolate(b.transpose(1, 2), size=size, mode="linear", align_corners=False).transpose(1, 2)
+    assert torch.allclose(ya, yb, atol=2e-2, rtol=2e-2)
+    g = torch.randn_like(yb).bfloat16().float()
+    ya.backward(g)
+    yb.backward(g)
+    assert ((a.grad - b.grad).norm() / b.grad.norm()).item() < 1e-2
