@@ -108,6 +108,43 @@ __device__ __forceinline__ Bil bilinear(float p, int L) {
   return r;
 }
 
+// Walks the n <= LPR taps held one per lane (weight w, position p), UNR at a time so that the row loads of several taps
+// are in flight together; taps of weight zero are not loaded.
+constexpr int UNR = 4;
+template <int LPR>
+__device__ __forceinline__ void gather_taps(float4& acc, float w, float p, int n, const bf16* xb, int L, long long rs) {
+  for (int j0 = 0; j0 < n; j0 += UNR) {
+    float wj[UNR];
+    Bil bi[UNR];
+    float4 a[UNR], c[UNR];
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      const int j = j0 + u;
+      const float wb = group_bcast<LPR>(w, j & (LPR - 1)), pb = group_bcast<LPR>(p, j & (LPR - 1));
+      wj[u] = j < n ? wb : 0.f;
+      bi[u] = bilinear(pb, L);
+    }
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      a[u] = c[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (wj[u] != 0.f) {
+        a[u] = ld4(xb + bi[u].fl * rs);
+        c[u] = ld4(xb + bi[u].ce * rs);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      const float wa = wj[u] * (1.f - bi[u].fr), wc = wj[u] * bi[u].fr;
+      acc.x += wa * a[u].x + wc * c[u].x; acc.y += wa * a[u].y + wc * c[u].y;
+      acc.z += wa * a[u].z + wc * c[u].z; acc.w += wa * a[u].w + wc * c[u].w;
+    }
+  }
+}
+
+__device__ __forceinline__ void scatter_row(float* dst, float wgt, float4 g) {
+  atomicAdd(reinterpret_cast<float4*>(dst), make_float4(wgt * g.x, wgt * g.y, wgt * g.z, wgt * g.w));
+}
+
 // ------------------------------------------------------------------------------------------------ telephone
 template <int LPR>
 __global__ void __launch_bounds__(256)
@@ -130,15 +167,7 @@ tele_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ freq, cons
       if (p >= 0.f && p < (float)L) w = lerp_table(kr, K, ar * inv_rec).v * exp2f(-e * log2f(1.f + ar * invL));
     }
     const int n = min(LPR, half - s0 + 1);
-    for (int j = 0; j < n; ++j) {
-      const float wj = group_bcast<LPR>(w, j), pj = group_bcast<LPR>(p, j);
-      if (wj == 0.f) continue;
-      const Bil bi = bilinear(pj, L);
-      const float4 a = ld4(xb + (long long)bi.fl * H * D), c = ld4(xb + (long long)bi.ce * H * D);
-      const float wa = wj * (1.f - bi.fr), wc = wj * bi.fr;
-      acc.x += wa * a.x + wc * c.x; acc.y += wa * a.y + wc * c.y;
-      acc.z += wa * a.z + wc * c.z; acc.w += wa * a.w + wc * c.w;
-    }
+    gather_taps<LPR>(acc, w, p, n, xb, L, (long long)H * D);
   }
   if (r.active) st4(out + r.row * D + r.sub * 4, acc);
 }
@@ -184,19 +213,36 @@ tele_bwd_kernel(const bf16* __restrict__ x, const float* __restrict__ freq, cons
     }
     const int n = min(LPR, half - s0 + 1);
     float my_sa = 0.f, my_sc = 0.f, my_fr = 0.f;
-    for (int j = 0; j < n; ++j) {
-      const float vj = group_bcast<LPR>(valid ? 1.f : 0.f, j);
-      if (vj == 0.f) continue;
-      const float wj = group_bcast<LPR>(w, j), pj = group_bcast<LPR>(p, j);
-      const Bil bi = bilinear(pj, L);
-      const float4 a = ld4(xb + (long long)bi.fl * H * D), c = ld4(xb + (long long)bi.ce * H * D);
-      const float sa = group_sum<LPR>(dot4(g, a)), sc = group_sum<LPR>(dot4(g, c));
-      if (r.sub == j) { my_sa = sa; my_sc = sc; my_fr = bi.fr; }
-      if (r.active && wj != 0.f) {
-        const float wa = wj * (1.f - bi.fr), wc = wj * bi.fr;
-        atomicAdd(reinterpret_cast<float4*>(dxb + (long long)bi.fl * H * D), make_float4(wa * g.x, wa * g.y, wa * g.z, wa * g.w));
-        if (wc != 0.f)
-          atomicAdd(reinterpret_cast<float4*>(dxb + (long long)bi.ce * H * D), make_float4(wc * g.x, wc * g.y, wc * g.z, wc * g.w));
+    const long long rs = (long long)H * D;
+    for (int j0 = 0; j0 < n; j0 += UNR) {
+      float wj[UNR];
+      bool vj[UNR];
+      Bil bi[UNR];
+      float4 a[UNR], c[UNR];
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const int j = j0 + u, src = j & (LPR - 1);
+        const float vb = group_bcast<LPR>(valid ? 1.f : 0.f, src), wb = group_bcast<LPR>(w, src), pb = group_bcast<LPR>(p, src);
+        vj[u] = j < n && vb != 0.f;
+        wj[u] = wb;
+        bi[u] = bilinear(pb, L);
+      }
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        a[u] = c[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (vj[u]) {
+          a[u] = ld4(xb + bi[u].fl * rs);
+          c[u] = ld4(xb + bi[u].ce * rs);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const float sa = group_sum<LPR>(dot4(g, a[u])), sc = group_sum<LPR>(dot4(g, c[u]));
+        if (r.sub == j0 + u) { my_sa = sa; my_sc = sc; my_fr = bi[u].fr; }
+        if (r.active && vj[u] && wj[u] != 0.f) {
+          scatter_row(dxb + bi[u].fl * rs, wj[u] * (1.f - bi[u].fr), g);
+          if (bi[u].fr != 0.f) scatter_row(dxb + bi[u].ce * rs, wj[u] * bi[u].fr, g);
+        }
       }
     }
     if (valid && r.active) {  // scalar gradients of this lane's own tap
@@ -266,15 +312,7 @@ alc_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ half_w, con
       p = t.p;
     }
     const int n = min(LPR, half - s0 + 1);
-    for (int j = 0; j < n; ++j) {
-      const float wj = group_bcast<LPR>(w, j), pj = group_bcast<LPR>(p, j);
-      if (wj == 0.f) continue;
-      const Bil bi = bilinear(pj, L);
-      const float4 a = ld4(xb + (long long)bi.fl * H * D), c = ld4(xb + (long long)bi.ce * H * D);
-      const float wa = wj * (1.f - bi.fr), wc = wj * bi.fr;
-      acc.x += wa * a.x + wc * c.x; acc.y += wa * a.y + wc * c.y;
-      acc.z += wa * a.z + wc * c.z; acc.w += wa * a.w + wc * c.w;
-    }
+    gather_taps<LPR>(acc, w, p, n, xb, L, (long long)H * D);
   }
   if (r.active) st4(out + r.row * D + r.sub * 4, acc);
 }
@@ -318,26 +356,42 @@ alc_bwd_kernel(const bf16* __restrict__ x, const float* __restrict__ half_w, con
       p = t.p;
     }
     const int n = min(LPR, half - s0 + 1);
-    for (int j = 0; j < n; ++j) {
-      const float wj = group_bcast<LPR>(w, j), pj = group_bcast<LPR>(p, j);
-      float dWj = 0.f;
-      if (pj >= 0.f && pj < (float)L) {
-        const Bil bi = bilinear(pj, L);
-        const float4 a = ld4(xb + (long long)bi.fl * H * D), c = ld4(xb + (long long)bi.ce * H * D);
-        const float sa = group_sum<LPR>(dot4(g, a)), sc = group_sum<LPR>(dot4(g, c));
-        dWj = sa * (1.f - bi.fr) + sc * bi.fr;
-        if (r.sub == j) {
-          G += dWj * wj;
-          if (pj <= hi) dc += wj * (sc - sa);
-        }
-        if (r.active && wj != 0.f) {
-          const float wa = wj * (1.f - bi.fr), wc = wj * bi.fr;
-          atomicAdd(reinterpret_cast<float4*>(dxb + (long long)bi.fl * H * D), make_float4(wa * g.x, wa * g.y, wa * g.z, wa * g.w));
-          if (wc != 0.f)
-            atomicAdd(reinterpret_cast<float4*>(dxb + (long long)bi.ce * H * D), make_float4(wc * g.x, wc * g.y, wc * g.z, wc * g.w));
+    const long long rs = (long long)H * D;
+    for (int j0 = 0; j0 < n; j0 += UNR) {
+      float wj[UNR], pj[UNR];
+      bool vj[UNR];
+      Bil bi[UNR];
+      float4 a[UNR], c[UNR];
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const int j = j0 + u, src = j & (LPR - 1);
+        wj[u] = group_bcast<LPR>(w, src);
+        pj[u] = group_bcast<LPR>(p, src);
+        vj[u] = j < n && pj[u] >= 0.f && pj[u] < (float)L;
+        bi[u] = bilinear(pj[u], L);
+      }
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        a[u] = c[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (vj[u]) {
+          a[u] = ld4(xb + bi[u].fl * rs);
+          c[u] = ld4(xb + bi[u].ce * rs);
         }
       }
-      if (r.sub == j) dw[s0 + j + half] = dWj;
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const float sa = group_sum<LPR>(dot4(g, a[u])), sc = group_sum<LPR>(dot4(g, c[u]));
+        const float dWj = sa * (1.f - bi[u].fr) + sc * bi[u].fr;  // zero for a tap outside the sequence
+        if (r.sub == j0 + u && j0 + u < n) {
+          G += dWj * wj[u];
+          if (vj[u] && pj[u] <= hi) dc += wj[u] * (sc - sa);
+          dw[s0 + j0 + u + half] = dWj;
+        }
+        if (r.active && vj[u] && wj[u] != 0.f) {
+          scatter_row(dxb + bi[u].fl * rs, wj[u] * (1.f - bi[u].fr), g);
+          if (bi[u].fr != 0.f) scatter_row(dxb + bi[u].ce * rs, wj[u] * bi[u].fr, g);
+        }
+      }
     }
   }
   G = group_sum<LPR>(G);

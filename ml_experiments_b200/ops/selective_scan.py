@@ -90,3 +90,35 @@ def selective_scan(u, delta, A, B, C, D=None, z=None, delta_bias=None, delta_sof
     if not u.is_cuda or A.shape[1] != 16:
         return selective_scan_ref(u, delta, A, B, C, D, z, delta_bias, delta_softplus)
     return _S6Scan.apply(u, delta, A, B, C, D, z, delta_bias, delta_softplus)
+
+
+def selective_state_update(state, x, dt, A, B, C, D=None, z=None, dt_bias=None, dt_softplus: bool = False):
+    """One decode step of the S6 recurrence, in place on ``state [B, Din, N]`` (the ``selective_state_update`` Triton
+    kernel of the reference, zoology/mixers/mamba_ssm/ops/triton/selective_state_update.py): ``x, dt, z [B, Din]``,
+    ``A [Din, N]``, ``B, C [B, N]``, ``D, dt_bias [Din]``. Returns ``y [B, Din]``. A handful of fused elementwise
+    kernels; one token per sequence is launch-bound, not bandwidth-bound."""
+    dt = dt.float()
+    if dt_bias is not None:
+        dt = dt + dt_bias.float()
+    if dt_softplus:
+        dt = F.softplus(dt)
+    dA = torch.exp(dt.unsqueeze(-1) * A.float())
+    dBx = (dt * x.float()).unsqueeze(-1) * B.float().unsqueeze(1)
+    state.copy_(state.float() * dA + dBx)
+    y = (state.float() * C.float().unsqueeze(1)).sum(-1)
+    if D is not None:
+        y = y + x.float() * D.float()
+    if z is not None:
+        y = y * F.silu(z.float())
+    return y.to(x.dtype)
+
+
+def causal_conv1d_update(x, conv_state, weight, bias=None, activation: str | None = None):
+    """One decode step of a causal depthwise conv: ``x [B, C]``, ``conv_state [B, C, K]`` (shifted in place),
+    ``weight [C, K]``."""
+    conv_state.copy_(torch.roll(conv_state, shifts=-1, dims=-1))
+    conv_state[:, :, -1] = x
+    y = (conv_state.float() * weight.float()).sum(-1)
+    if bias is not None:
+        y = y + bias.float()
+    return (F.silu(y) if activation in ("silu", "swish") else y).to(x.dtype)

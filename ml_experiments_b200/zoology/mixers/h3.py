@@ -149,6 +149,7 @@ class H3(nn.Module):
                  dropout: float = 0.0, layer_idx: int = None, device=None, dtype=None, kernel_args: dict = {}, **kwargs):
         super().__init__()
         assert d_model % head_dim == 0
+        d_state = int(d_state)
         self.d_model, self.head_dim, self.H, self.N, self.L, self.layer_idx = d_model, head_dim, d_model // head_dim, d_state, l_max, layer_idx
         self.q_proj, self.k_proj, self.v_proj = (nn.Linear(d_model, d_model) for _ in range(3))
         self.ssm_k_kernel = SSKernel(d_model, N=d_state, L=l_max, mode="shift", lr=kernel_args.get("lr", None))

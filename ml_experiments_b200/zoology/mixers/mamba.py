@@ -15,7 +15,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ...ops.causal_conv import causal_conv1d_silu
-from ...ops.selective_scan import selective_scan
+from ...ops.selective_scan import causal_conv1d_update, selective_scan, selective_state_update
 from .norms import RMSNorm, layer_norm_fn, rms_norm_fn
 
 
@@ -64,6 +64,21 @@ class Mamba(nn.Module):
         y = selective_scan(x.contiguous(), F.linear(dt, self.dt_proj.weight), -torch.exp(self.A_log.float()), B, C, self.D.float(),
                            z=z.contiguous(), delta_bias=self.dt_proj.bias.float(), delta_softplus=True)
         return self.out_proj(y)
+
+    def allocate_inference_cache(self, batch_size: int, max_seqlen: int = 0, dtype=None):
+        """``(conv_state [B, Din, K], ssm_state [B, Din, N])`` for token-by-token decoding with :meth:`step`."""
+        w = self.conv1d.weight
+        return (torch.zeros(batch_size, self.d_inner, self.d_conv, device=w.device, dtype=dtype or w.dtype),
+                torch.zeros(batch_size, self.d_inner, self.d_state, device=w.device, dtype=torch.float32))
+
+    def step(self, hidden_states, conv_state, ssm_state):
+        """One token ``[B, 1, d_model]`` through the layer, updating both states in place (mamba.py:199-249 of the reference)."""
+        x, z = self.in_proj(hidden_states.squeeze(1)).chunk(2, dim=-1)
+        x = causal_conv1d_update(x, conv_state, self.conv1d.weight.squeeze(1), self.conv1d.bias, "silu")
+        dt, B, C = self.x_proj(x).split([self.dt_rank, self.d_state, self.d_state], dim=-1)
+        y = selective_state_update(ssm_state, x, F.linear(dt, self.dt_proj.weight), -torch.exp(self.A_log.float()), B, C, self.D.float(),
+                                   z=z, dt_bias=self.dt_proj.bias.float(), dt_softplus=True)
+        return self.out_proj(y).unsqueeze(1), conv_state, ssm_state
 
     def state_size(self, sequence_length: int = 2048):
         return 2 * self.d_model * self.d_state

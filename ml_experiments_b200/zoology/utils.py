@@ -11,6 +11,21 @@ import torch
 
 # reference module paths keep working in configs written for the vendored package
 _ALIASES = {"zoology.": "ml_experiments_b200.zoology."}
+# modules of the reference's mixer zoo that live under another file name here
+_MODULE_ALIASES = {
+    "ml_experiments_b200.zoology.mixers.delta_net": "ml_experiments_b200.zoology.mixers.linear_attn",
+    "ml_experiments_b200.zoology.mixers.gated_delta_net": "ml_experiments_b200.zoology.mixers.linear_attn",
+    "ml_experiments_b200.zoology.mixers.gla": "ml_experiments_b200.zoology.mixers.linear_attn",
+    "ml_experiments_b200.zoology.mixers.rwkv7": "ml_experiments_b200.zoology.mixers.linear_attn",
+    "ml_experiments_b200.zoology.mixers.deepseek_nsa": "ml_experiments_b200.zoology.mixers.nsa",
+    "ml_experiments_b200.zoology.mixers.slide_attn": "ml_experiments_b200.zoology.mixers.attention",
+    "ml_experiments_b200.zoology.mixers.scatterbrain_new": "ml_experiments_b200.zoology.mixers.scatterbrain",
+    "ml_experiments_b200.zoology.mixers.scatterbrain.attn": "ml_experiments_b200.zoology.mixers.scatterbrain",
+    "ml_experiments_b200.zoology.mixers.nystromformer.nystromformer": "ml_experiments_b200.zoology.mixers.nystrom",
+    "ml_experiments_b200.zoology.mixers.mra.mra": "ml_experiments_b200.zoology.mixers.mra",
+    "ml_experiments_b200.zoology.mixers.h3.h3": "ml_experiments_b200.zoology.mixers.h3",
+    "ml_experiments_b200.zoology.mixers.rwkv5": "ml_experiments_b200.zoology.mixers.rwkv",
+}
 
 
 def import_from_str(path: str) -> Union[type, Callable]:
@@ -19,6 +34,7 @@ def import_from_str(path: str) -> Union[type, Callable]:
         if path.startswith(old):
             path = new + path[len(old):]
     module_name, obj_name = path.rsplit(".", 1)
+    module_name = _MODULE_ALIASES.get(module_name, module_name)
     try:
         module = importlib.import_module(module_name)
     except ImportError as e:

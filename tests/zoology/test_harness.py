@@ -210,3 +210,35 @@ def test_mixers_that_look_ahead_by_design():
     q, k, v = m.Wqkv(x).view(2, 24, 3, 2, 16).permute(2, 0, 3, 1, 4)
     ref = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(2, 24, 32)
     assert torch.allclose(m(x), m.out_proj(ref), atol=1e-5)
+
+
+def test_mamba_decode_steps_match_the_parallel_forward():
+    from ml_experiments_b200.zoology.mixers.mamba import Mamba
+    torch.manual_seed(0)
+    m = Mamba(32, d_state=8).eval()
+    x = torch.randn(2, 12, 32)
+    full = m(x)
+    conv_state, ssm_state = m.allocate_inference_cache(2)
+    outs = [m.step(x[:, t:t + 1], conv_state, ssm_state)[0] for t in range(12)]
+    assert torch.allclose(torch.cat(outs, 1), full, atol=1e-5)
+
+
+def test_experiment_definitions_build_and_instantiate():
+    """The sweep files produce configs whose every mixer can be built and run (tiny widths, one per family)."""
+    from ml_experiments_b200.zoology.experiments import models_repo, ripple_mqar
+    cfgs = ripple_mqar.build_configs(seq_kv=[(64, 4)], d_models=[32], lrs=[1e-3], mixers=["attention", "mamba", *ripple_mqar.RIPPLE_VARIANTS],
+                                     num_train=8, num_test=8, vocab_size=64)
+    assert len(cfgs) == 2 + len(ripple_mqar.RIPPLE_VARIANTS)
+    assert len(ripple_mqar.configs) == 5 * 5 * 3 * len(ripple_mqar.DEFAULT_MIXERS)
+    x = torch.randint(0, 64, (2, 64))
+    for c in cfgs[:4] + cfgs[-2:]:
+        assert LanguageModel(c.model)(x).shape == (2, 64, 64)
+    seen = set()
+    for add in models_repo.ALL_FAMILIES:
+        models = add([], dict(name="zoology.mixers.base_conv.BaseConv", kwargs={"l_max": 64, "kernel_size": 3}), 64, dict(vocab_size=64))
+        assert models
+        m = min(models, key=lambda mc: mc.d_model)
+        if m.name in seen:
+            continue
+        seen.add(m.name)
+        assert LanguageModel(m)(x).shape == (2, 64, 64), m.name
