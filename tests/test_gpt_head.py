@@ -148,3 +148,39 @@ def test_head_gpt_gpu_matches_cpu():
     g.lm_head.use_fp8 = True
     loss8 = g(x.cuda(), y.cuda(), seqlens.cuda(), big.cuda(), cfg_g) / T
     assert abs(loss8.item() - want.item()) / want.item() < 6e-2
+
+
+def test_medium_track_model_trains_and_evaluates():
+    from ml_experiments_b200.models.gpt_head import ForwardScheduleConfig
+    from ml_experiments_b200.models.gpt_medium import GPTMedium
+
+    torch.manual_seed(0)
+    m = GPTMedium(vocab_size=300, num_heads=2, head_dim=16, model_dim=32, max_seq_len=256, world_size=8)
+    assert m.scalars.numel() % 8 == 0 and m.scalars.numel() >= 16 * 3 + 5
+    labels = {getattr(p, "label", None) for p in m.parameters()}
+    assert {"attn", "mlp", "attn_gate", "value_embed_gate", "smear_gate", "skip_gate", "value_embed", "lm_head", "embed", "embed2",
+            "x0_lambdas", "scalars"} <= labels
+    for p in m.parameters():
+        if p.ndim >= 2 and p.abs().sum() == 0:
+            torch.nn.init.normal_(p, std=0.02)
+    T = 128
+    ids, tg = torch.randint(0, 300, (T,)), torch.randint(0, 300, (T,))
+    seqlens = torch.tensor([0, 50, 128], dtype=torch.int32)
+    cfg = ForwardScheduleConfig(mtp_weights=torch.tensor([1.0, 0.5]), ws_short=1, ws_long=2)
+    loss = m(ids, tg, seqlens, cfg)
+    loss.backward()
+    missing = [n for n, p in m.named_parameters() if p.grad is None]
+    assert missing == ["embed.weight"]          # tied to lm_head until split_embed
+    m.eval()
+    ev = m(ids, tg, seqlens, cfg)
+    assert abs(ev.item() - loss.item() / T / 1.5) < 0.2
+    # a document boundary isolates the two documents: changing document 2 leaves document 1's logits alone
+    ids2 = ids.clone()
+    ids2[60:] = (ids2[60:] + 1) % 300
+    m.train()
+    cfg1 = ForwardScheduleConfig(mtp_weights=None, ws_short=1, ws_long=2)
+    l1 = m(ids[:50], tg[:50], torch.tensor([0, 50], dtype=torch.int32), cfg1)
+    tg_mask = tg.clone()
+    tg_mask[50:] = -1
+    l2 = m(ids2, tg_mask, seqlens, cfg1)
+    assert torch.allclose(l1, l2, rtol=1e-4)
