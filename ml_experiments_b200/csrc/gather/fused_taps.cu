@@ -108,9 +108,9 @@ __device__ __forceinline__ Bil bilinear(float p, int L) {
   return r;
 }
 
-// Walks the n <= LPR taps held one per lane (weight w, position p), UNR at a time so that the row loads of several taps
-// are in flight together; taps of weight zero are not loaded.
-constexpr int UNR = 2;
+// Walks the n <= LPR taps held one per lane (weight w, position p), UNR at a time (the row loads of UNR taps are issued
+// together); taps of weight zero are not loaded.
+constexpr int UNR = 1;  // measured: 2 and 4 lose more to the lower occupancy (64 / 99 registers) than the batched loads win
 template <int LPR>
 __device__ __forceinline__ void gather_taps(float4& acc, float w, float p, int n, const bf16* xb, int L, long long rs) {
   for (int j0 = 0; j0 < n; j0 += UNR) {
@@ -147,7 +147,7 @@ __device__ __forceinline__ void scatter_row(float* dst, float wgt, float4 g) {
 
 // ------------------------------------------------------------------------------------------------ telephone
 template <int LPR>
-__global__ void __launch_bounds__(256, 4)
+__global__ void __launch_bounds__(256)
 tele_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ freq, const float* __restrict__ phase,
                 const float* __restrict__ kern, const float* __restrict__ expo, bf16* __restrict__ out, int B, int L, int H,
                 int K, int half, float max_rec) {
@@ -173,7 +173,7 @@ tele_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ freq, cons
 }
 
 template <int LPR>
-__global__ void __launch_bounds__(256, 4)
+__global__ void __launch_bounds__(256)
 tele_bwd_kernel(const bf16* __restrict__ x, const float* __restrict__ freq, const float* __restrict__ phase,
                 const float* __restrict__ kern, const float* __restrict__ expo, const bf16* __restrict__ dout,
                 float* __restrict__ dx, float* __restrict__ dfreq, float* __restrict__ dphase, float* __restrict__ dkern,
@@ -291,7 +291,7 @@ __device__ __forceinline__ AlcTap alc_tap(const float* kr, int K, int s, float i
 }
 
 template <int LPR>
-__global__ void __launch_bounds__(256, 4)
+__global__ void __launch_bounds__(256)
 alc_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ half_w, const float* __restrict__ center,
                const float* __restrict__ kern, bf16* __restrict__ out, int B, int L, int H, int K, int half) {
   constexpr int D = LPR * 4;
@@ -319,7 +319,7 @@ alc_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ half_w, con
 
 // shared memory: [RPB][K] kernel gradients, then [RPB][SP] per-tap dW (SP = 2*half+1)
 template <int LPR>
-__global__ void __launch_bounds__(256, 4)
+__global__ void __launch_bounds__(256)
 alc_bwd_kernel(const bf16* __restrict__ x, const float* __restrict__ half_w, const float* __restrict__ center,
                const float* __restrict__ kern, const bf16* __restrict__ dout, float* __restrict__ dx,
                float* __restrict__ dhalf_w, float* __restrict__ dcenter, float* __restrict__ dkern, int B, int L, int H,

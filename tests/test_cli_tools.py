@@ -1,0 +1,42 @@
+"""Command-line tools: the scatter benchmark harness, the crossover sweep, the Ripple profiler and the SpanFinder trainer."""
+import json
+
+import torch
+
+
+def test_bench_scatter_builds_every_model_at_a_matched_budget_and_trains():
+    from ml_experiments_b200.cli import bench_scatter as B
+
+    for kind in B.MODEL_TYPES:
+        m = B.build_model(kind, layers=2, n_out=2, seq_len=64, num_channels=2, target_params=20_000, jacobi_iters=1)
+        n = B.count_params(m)
+        assert 5_000 < n < 80_000, (kind, n)
+        assert m(torch.rand(2, 64)).shape == (2, 2)
+    res = B.main(["--model", "conv,ripple", "--dataset", "mqar", "--seq-len", "32", "--epochs", "2", "--layers", "1", "--num-train", "32",
+                  "--num-test", "16", "--batch-size", "16", "--target-params", "8000", "--device", "cpu", "--swa", "--swa-start", "0.5",
+                  "--hard-mining", "--self-distill", "--distill-merge", "slerp", "--task-vocab-size", "32"])
+    assert set(res) == {"conv", "ripple"} and all(0.0 <= r["mean"] <= 1.0 for r in res.values())
+
+
+def test_schedule_and_weight_merges():
+    from ml_experiments_b200.cli.bench_scatter import lerp_weights, lr_lambda, slerp_weights
+
+    assert lr_lambda(0, 100, 10, 0.1) == 0.1 and lr_lambda(9, 100, 10, 0.1) == 1.0 and lr_lambda(15, 100, 10, 0.1) == 1.0
+    assert lr_lambda(99, 100, 10, 0.1) < 0.01
+    a, b = {"w": torch.tensor([1.0, 0.0])}, {"w": torch.tensor([0.0, 1.0])}
+    assert torch.allclose(lerp_weights(a, b, 0.25)["w"], torch.tensor([0.75, 0.25]))
+    s = slerp_weights(a, b, 0.5)["w"]
+    assert torch.allclose(s, torch.full((2,), 0.5 ** 0.5), atol=1e-6)   # stays on the unit circle
+
+
+def test_crossover_profile_and_spanfinder_tools(tmp_path, capsys):
+    from ml_experiments_b200.cli import bench_crossover, profile_ripple, train_spanfinder
+
+    rows = bench_crossover.main(["--lengths", "64", "--ops", "attention,conv,lowrank", "--width", "32", "--heads", "2", "--batch", "2", "--iters", "1",
+                                 "--warmup", "0", "--device", "cpu"])
+    assert [r["op"] for r in rows] == ["attention", "conv", "lowrank"] and all(r["fwd_ms"] > 0 for r in rows)
+    out = profile_ripple.main(["--seq-len", "64", "--width", "32", "--layers", "1", "--heads", "2", "--batch", "2", "--iters", "1", "--device", "cpu"])
+    assert {"telephone", "conv", "lowrank"} <= set(out["forward_by_operator"]) and out["forward_ms"] > 0
+    meta = train_spanfinder.main(["--preset", "tiny", "--synthetic", "32", "--batch-size", "16", "--epochs", "1", "--output", str(tmp_path / "sf"),
+                                  "--device", "cpu", "--chunk-size", "128"])
+    assert (tmp_path / "sf.safetensors").exists() and json.loads((tmp_path / "sf.meta.json").read_text())["parameters"] == meta["parameters"]
