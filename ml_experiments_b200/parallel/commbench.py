@@ -1,0 +1,171 @@
+"""Multi-rank benchmark of the fused peer-memory collectives against NCCL and against their rooflines.
+
+    python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 --master-port P -m ml_experiments_b200.parallel.commbench
+
+Every number is timed with CUDA events on the launching stream after warm-up, bracketed by barrier + synchronize, and
+reported as the maximum over ranks. Rank 0 prints one JSON line per measurement:
+
+* ``allreduce``: the two-shot peer-memory mean all-reduce (scale and dtype handling fused) and ``dist.all_reduce`` on
+  the same sizes. Each rank moves ``(W-1)/W * bytes`` in each direction, so the roofline time is that over the
+  per-direction link bandwidth (``--link-gbs``, 770 GB/s measured peer copy by default).
+* ``muon_step``: one fused Muon step (reduce-scatter + momentum + cast, Newton-Schulz on the owned slice, all-gather by
+  peer stores + weight update) on the hidden matrices of a GPT of the given shape, with the equivalent built from NCCL
+  ``reduce_scatter_tensor`` / ``all_gather_into_tensor`` around the same Newton-Schulz for comparison. Roofline = the
+  slower of the Newton-Schulz FLOPs at the measured GEMM peak and the bytes crossing NVLink at link bandwidth
+  (fp32 gradients in: ``(W-1)/W * 4`` bytes per element; bf16 updates out: ``(W-1)/W * 2`` bytes per element).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+from ..ops.newton_schulz import newton_schulz_
+from ..ops.runtime import check_status, ops, status
+from ..optim.muon import NS5_COEFFS
+from .ddp import CH_IN, CH_OUT
+from .muon_dist import MuonShardEngine
+from .symm import SymmWorld
+
+
+def _timed(fn, iters, warmup, dev):
+    for _ in range(warmup):
+        fn()
+    dist.barrier()
+    torch.cuda.synchronize(dev)
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(iters):
+        fn()
+    e.record()
+    dist.barrier()
+    torch.cuda.synchronize(dev)
+    t = torch.tensor([s.elapsed_time(e) / iters], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def _gemm_peak_tflops():
+    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    return (json.loads(p.read_text())["bf16_tflops"], "measured") if p.exists() else (1590.0, "fallback")
+
+
+def bench_allreduce(w: SymmWorld, sizes_mb, iters, warmup, link_gbs, emit):
+    o, dev, W = ops(), w.device, w.world
+    epoch = [0]
+    for dtype, code in ((torch.bfloat16, 1), (torch.float32, 0)):
+        esize = torch.tensor([], dtype=dtype).element_size()
+        for mb in sizes_mb:
+            vec = (8 if code else 4) * W
+            n = (mb * (1 << 20) // esize) // vec * vec
+            buf = w.alloc(n, dtype, zero=True)
+            buf.local.normal_()
+            ref = buf.local.clone()
+
+            def fused():
+                epoch[0] += 1
+                o.comm_signal(w.flags.ptrs, w.rank, CH_IN, 10_000_000 + epoch[0], w.flags.local)
+                o.allreduce_mean(buf.ptrs, w.rank, n, code, w.flags.local, w.flags.ptrs, CH_IN, 10_000_000 + epoch[0], status(dev))
+                o.comm_wait(w.flags.local, W, CH_OUT, 10_000_000 + epoch[0], status(dev))
+
+            def nccl():
+                dist.all_reduce(ref, op=dist.ReduceOp.AVG)
+
+            t_f, t_n = _timed(fused, iters, warmup, dev), _timed(nccl, iters, warmup, dev)
+            check_status()
+            per_dir = (W - 1) / W * n * esize
+            roof_ms = per_dir / (link_gbs * 1e6)
+            emit(dict(bench="allreduce", dtype=str(dtype).split(".")[-1], mbytes=round(n * esize / 2 ** 20, 1), world=W, fused_ms=round(t_f, 4),
+                      nccl_ms=round(t_n, 4), fused_busbw_gbs=round(2 * per_dir / t_f / 1e6, 1), nccl_busbw_gbs=round(2 * per_dir / t_n / 1e6, 1),
+                      roofline_ms=round(roof_ms, 4), fused_frac_of_roofline=round(roof_ms / t_f, 3), link_gbs=link_gbs))
+
+
+def hidden_matrices(layers: int, d: int, dev):
+    """Muon's parameter set of a classic GPT block stack: qkv (3 x d x d), attention out (d x d), MLP in / out (4d x d, d x 4d)."""
+    ps = []
+    for _ in range(layers):
+        ps += [torch.nn.Parameter(torch.randn(3, d, d, device=dev) * 0.02), torch.nn.Parameter(torch.randn(d, d, device=dev) * 0.02),
+               torch.nn.Parameter(torch.randn(4 * d, d, device=dev) * 0.02), torch.nn.Parameter(torch.randn(d, 4 * d, device=dev) * 0.02)]
+    return ps
+
+
+def bench_muon(w: SymmWorld, layers, d, iters, warmup, link_gbs, emit):
+    dev, W = w.device, w.world
+    params = hidden_matrices(layers, d, dev)
+    for p in params:
+        p.grad = torch.randn_like(p)
+    eng = MuonShardEngine(params, w)
+    coeffs = [NS5_COEFFS[0]] * 5
+
+    def fused():
+        eng.publish_grads()
+        eng.reduce_ns_push(0.95, True, coeffs)
+        eng.apply(0.02)
+
+    t_f = _timed(fused, iters, warmup, dev)
+    check_status()
+    # the same step from library collectives: reduce-scatter -> momentum -> Newton-Schulz -> all-gather -> update
+    state = []
+    for g in eng.groups:
+        state.append(dict(g=g, gin=torch.randn(g["padded"], g["r"], g["c"], device=dev), gout=torch.empty(g["per"], g["r"], g["c"], device=dev),
+                          mom=torch.zeros(g["per"], g["r"], g["c"], device=dev), ufull=torch.empty(g["padded"], g["r"], g["c"], device=dev, dtype=torch.bfloat16)))
+    work: dict = {}
+
+    def nccl():
+        for s in state:
+            dist.reduce_scatter_tensor(s["gout"], s["gin"], op=dist.ReduceOp.AVG)
+            s["mom"].lerp_(s["gout"], 0.05)
+            u = s["gout"].lerp(s["mom"], 0.95).to(torch.bfloat16)
+            u = u / (u.float().norm(dim=(1, 2), keepdim=True) + 1e-7).to(torch.bfloat16)
+            u = newton_schulz_(u, coeffs, work)
+            dist.all_gather_into_tensor(s["ufull"], u.contiguous())
+            s["g"]["p_stack"].add_(s["ufull"].float(), alpha=-0.02)
+
+    t_n = _timed(nccl, iters, warmup, dev)
+    elems = sum(g["padded"] * g["mat"] for g in eng.groups)
+    flops = 0.0
+    for g in eng.groups:
+        small, big = min(g["r"], g["c"]), max(g["r"], g["c"])
+        flops += g["per"] * 5 * (2.0 * small * small * big * 2 + 2.0 * small ** 3)
+    peak, src = _gemm_peak_tflops()
+    t_flops = flops / (peak * 1e9)
+    # per rank and direction: it pulls (W-1)/W of its 1/W slice in fp32 ( = inbound) and pushes its slice to W-1 peers in bf16 (outbound)
+    t_in = (W - 1) * (elems / W) * 4 / (link_gbs * 1e6) if W > 1 else 0.0
+    t_out = (W - 1) * (elems / W) * 2 / (link_gbs * 1e6) if W > 1 else 0.0
+    roof = max(t_flops, t_in, t_out)
+    emit(dict(bench="muon_step", world=W, layers=layers, d_model=d, matrices_melems=round(elems / 1e6, 1), fused_ms=round(t_f, 4), nccl_ms=round(t_n, 4),
+              ns_tflop=round(flops / 1e12, 3), roofline_ms=round(roof, 4), roofline_terms_ms=dict(ns_at_gemm_peak=round(t_flops, 4), nvlink_in=round(t_in, 4), nvlink_out=round(t_out, 4)),
+              fused_frac_of_roofline=round(roof / t_f, 3), gemm_peak=src, link_gbs=link_gbs))
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--sizes-mb", default="1,16,128,512")
+    ap.add_argument("--layers", type=int, default=12)
+    ap.add_argument("--d-model", type=int, default=768)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--link-gbs", type=float, default=770.0)
+    ap.add_argument("--skip", default="", help="comma list of benches to skip (allreduce, muon_step)")
+    a = ap.parse_args(argv)
+    rank, world, local = (int(os.environ.get(k, d)) for k, d in (("RANK", 0), ("WORLD_SIZE", 1), ("LOCAL_RANK", 0)))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    w = SymmWorld.create(rank, world, dev)
+    emit = lambda d: print(json.dumps(d), flush=True) if rank == 0 else None
+    skip = set(a.skip.split(","))
+    if "allreduce" not in skip:
+        bench_allreduce(w, [int(s) for s in a.sizes_mb.split(",")], a.iters, a.warmup, a.link_gbs, emit)
+    if "muon_step" not in skip:
+        bench_muon(w, a.layers, a.d_model, a.iters, a.warmup, a.link_gbs, emit)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
