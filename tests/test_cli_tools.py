@@ -40,3 +40,12 @@ def test_crossover_profile_and_spanfinder_tools(tmp_path, capsys):
     meta = train_spanfinder.main(["--preset", "tiny", "--synthetic", "32", "--batch-size", "16", "--epochs", "1", "--output", str(tmp_path / "sf"),
                                   "--device", "cpu", "--chunk-size", "128"])
     assert (tmp_path / "sf.safetensors").exists() and json.loads((tmp_path / "sf.meta.json").read_text())["parameters"] == meta["parameters"]
+
+
+def test_validator_trainer_tool(tmp_path):
+    from ml_experiments_b200.cli import train_validator
+
+    meta = train_validator.main(["--synthetic", "120", "--epochs", "2", "--output", str(tmp_path / "val"), "--device", "cpu"])
+    saved = json.loads((tmp_path / "val.meta.json").read_text())
+    assert (tmp_path / "val.safetensors").exists() and set(saved["frequencies"]) == {"text", "innocuous", "secret"}
+    assert saved["config"]["num_features"] == 6 and meta["parameters"] > 0
