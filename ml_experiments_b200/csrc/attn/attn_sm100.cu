@@ -383,6 +383,33 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t idesc_dv = make_idesc(FMT_BF16, FMT_BF16, 0, 1, 128, D);    // Pᵀ·dO, dSᵀ·Q   (B MN-major)
   const uint32_t idesc_dq = make_idesc(FMT_BF16, FMT_BF16, 1, 1, 128, BQ);   // Kᵀ·dSᵀ         (A, B MN-major)
 
+  // One thread issues every TMA load and MMA. The S / dP products of tile it+1 are issued as soon as every thread has
+  // copied tile it's S / dP out of TMEM, so they run on the tensor pipe while the CTA does the exponentials of tile it.
+  auto issue_s_dp = [&](int buf) {
+    const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
+    const uint32_t qa = smem_u32(sQ + buf * Q_BYTES), doa = smem_u32(sdO + buf * Q_BYTES);
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      const uint64_t ad = make_smem_desc_sw128(ka + (ks / 4) * (BKV * 128) + (ks % 4) * 32, 16, 1024);
+      const uint64_t bd = make_smem_desc_sw128(qa + (ks / 4) * (BQ * 128) + (ks % 4) * 32, 16, 1024);
+      tc_mma_f16(tmem_base + ST_COL, ad, bd, idesc_st, ks != 0);
+    }
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      const uint64_t ad = make_smem_desc_sw128(va + (ks / 4) * (BKV * 128) + (ks % 4) * 32, 16, 1024);
+      const uint64_t bd = make_smem_desc_sw128(doa + (ks / 4) * (BQ * 128) + (ks % 4) * 32, 16, 1024);
+      tc_mma_f16(tmem_base + DPT_COL, ad, bd, idesc_st, ks != 0);
+    }
+    tc_commit(bar_m1);
+  };
+  auto load_q_do = [&](int buf, int q0) {
+    mbar_arrive_expect_tx(&bar_q[buf], 2 * Q_BYTES);
+    for (int s = 0; s < NS; ++s) {
+      tma_load_3d(sQ + buf * Q_BYTES + s * BQ * 128, &tmQ, &bar_q[buf], s * 64, q0, h);
+      tma_load_3d(sdO + buf * Q_BYTES + s * BQ * 128, &tmdO, &bar_q[buf], s * 64, q0, h);
+    }
+  };
+
   if (tid == 0) {
     mbar_arrive_expect_tx(bar_kv, 2 * KV_BYTES);
     for (int s = 0; s < NS; ++s) {
@@ -390,11 +417,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tma_load_3d(sV + s * BKV * 128, &tmV, bar_kv, s * 64, kv0, h);
     }
     if (ntile > 0) {
-      mbar_arrive_expect_tx(&bar_q[0], 2 * Q_BYTES);
-      for (int s = 0; s < NS; ++s) {
-        tma_load_3d(sQ + s * BQ * 128, &tmQ, &bar_q[0], s * 64, q_lo, h);
-        tma_load_3d(sdO + s * BQ * 128, &tmdO, &bar_q[0], s * 64, q_lo, h);
-      }
+      load_q_do(0, q_lo);
+      if (ntile > 1) load_q_do(1, q_lo + BQ);
+      cta_wait(bar_kv, 0, abort_flag, p.status, ERR_WAIT_SMEM_FULL);
+      cta_wait(&bar_q[0], 0, abort_flag, p.status, ERR_WAIT_SMEM_FULL);
+      tc_fence_after_sync();
+      issue_s_dp(0);
     }
   }
 
@@ -407,45 +435,24 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       s_ld[tid] = make_float2(okq ? p.lse[(long long)h * p.T + qq] : INFINITY, okq ? p.delta[(long long)h * p.T + qq] : 0.f);
       s_ds[tid] = okq ? p.doc_start[qq] : 0x7fffffff;
     }
-    if (tid == 0) {
-      if (it + 1 < ntile) {  // prefetch next Q / dO tile; its buffer was released by bar_m2 of tile it-1
-        const int nb = buf ^ 1;
-        mbar_arrive_expect_tx(&bar_q[nb], 2 * Q_BYTES);
-        for (int s = 0; s < NS; ++s) {
-          tma_load_3d(sQ + nb * Q_BYTES + s * BQ * 128, &tmQ, &bar_q[nb], s * 64, qt0 + BQ, h);
-          tma_load_3d(sdO + nb * Q_BYTES + s * BQ * 128, &tmdO, &bar_q[nb], s * 64, qt0 + BQ, h);
-        }
-      }
-      if (it == 0) cta_wait(bar_kv, 0, abort_flag, p.status, ERR_WAIT_SMEM_FULL);
-      cta_wait(&bar_q[buf], (it >> 1) & 1, abort_flag, p.status, ERR_WAIT_SMEM_FULL);
-      tc_fence_after_sync();
-      const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
-      const uint32_t qa = smem_u32(sQ + buf * Q_BYTES), doa = smem_u32(sdO + buf * Q_BYTES);
-#pragma unroll
-      for (int ks = 0; ks < D / 16; ++ks) {
-        const uint64_t ad = make_smem_desc_sw128(ka + (ks / 4) * (BKV * 128) + (ks % 4) * 32, 16, 1024);
-        const uint64_t bd = make_smem_desc_sw128(qa + (ks / 4) * (BQ * 128) + (ks % 4) * 32, 16, 1024);
-        tc_mma_f16(tmem_base + ST_COL, ad, bd, idesc_st, ks != 0);
-      }
-#pragma unroll
-      for (int ks = 0; ks < D / 16; ++ks) {
-        const uint64_t ad = make_smem_desc_sw128(va + (ks / 4) * (BKV * 128) + (ks % 4) * 32, 16, 1024);
-        const uint64_t bd = make_smem_desc_sw128(doa + (ks / 4) * (BQ * 128) + (ks % 4) * 32, 16, 1024);
-        tc_mma_f16(tmem_base + DPT_COL, ad, bd, idesc_st, ks != 0);
-      }
-      tc_commit(bar_m1);
-    }
     __syncthreads();  // s_ld / s_ds visible
     cta_wait(bar_m1, it & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
     tc_fence_after_sync();
+    uint32_t sv[32], dv_[32];
+    tmem_ld_32x32b_x32(tmem_base + lane_off + ST_COL + half * 32, sv);
+    tmem_ld_32x32b_x32(tmem_base + lane_off + DPT_COL + half * 32, dv_);
+    tmem_ld_wait();
+    tc_fence_before_sync();
+    __syncthreads();  // every thread holds its S / dP values: the TMEM columns may be overwritten
+    if (tid == 0 && it + 1 < ntile) {
+      cta_wait(&bar_q[buf ^ 1], ((it + 1) >> 1) & 1, abort_flag, p.status, ERR_WAIT_SMEM_FULL);
+      tc_fence_after_sync();
+      issue_s_dp(buf ^ 1);
+    }
 
     // masks are needed only where the tile touches the causal diagonal, a document boundary or the sequence end
     const bool need_mask = (qt0 < kv0 + BKV) || (s_ds[BQ - 1] > kv0) || (kv0 + BKV > p.T) || (qt0 + BQ > p.T);
     {
-      uint32_t sv[32], dv_[32];
-      tmem_ld_32x32b_x32(tmem_base + lane_off + ST_COL + half * 32, sv);
-      tmem_ld_32x32b_x32(tmem_base + lane_off + DPT_COL + half * 32, dv_);
-      tmem_ld_wait();
       uint32_t pp[16], dd[16];
 #pragma unroll
       for (int i = 0; i < 32; i += 2) {
@@ -500,6 +507,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     __syncthreads();
     cta_wait(bar_m2, it & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
     tc_fence_after_sync();
+    if (tid == 0 && it + 2 < ntile) load_q_do(buf, qt0 + 2 * BQ);  // this tile's Q / dO buffer is free again
     // dQᵀ row (= head-dim index r), this warp's half of the query columns -> staging[q][r]
     if (r < D) {
       uint32_t v[32];

@@ -49,3 +49,16 @@ def test_validator_trainer_tool(tmp_path):
     saved = json.loads((tmp_path / "val.meta.json").read_text())
     assert (tmp_path / "val.safetensors").exists() and set(saved["frequencies"]) == {"text", "innocuous", "secret"}
     assert saved["config"]["num_features"] == 6 and meta["parameters"] > 0
+
+
+def test_line_filter_trainer_checkpoints_and_resumes(tmp_path):
+    from ml_experiments_b200.cli import train_line_filter as T
+
+    common = ["--synthetic", "96", "--arch", "conv", "--embed-width", "16", "--output", str(tmp_path), "--device", "cpu", "--batch-size", "32"]
+    T.main(common + ["--epochs", "2", "--neg-ratio", "1.0"])
+    assert (tmp_path / "epoch002.pt").exists() and (tmp_path / "final.pt").exists()
+    s = T.main(common + ["--epochs", "3", "--resume", str(tmp_path / "epoch002.pt")])
+    assert (tmp_path / "epoch003.pt").exists() and s["parameters"] > 0
+    assert abs(T.pos_weight_at(0, 10, 4.0, 1.0) - 4.0) < 1e-6 and abs(T.pos_weight_at(9, 10, 4.0, 1.0) - 1.0) < 1e-6
+    m = T.main(common + ["--epochs", "1", "--head", "classifier", "--no-swa"])
+    assert 0.0 <= float(m["best_metric"]) <= 1.0
