@@ -327,6 +327,13 @@ void ag_wait_apply(Tensor p, const Tensor& u, const c10::optional<Tensor>& p_bf1
                       cur_stream());
 }
 
+void allreduce_mean_multimem(int64_t mc_ptr, int64_t world, int64_t rank, int64_t n, int64_t dtype, const Tensor& flags,
+                             at::IntArrayRef peer_flags, int64_t channel, int64_t epoch, Tensor status) {
+  const c10::cuda::CUDAGuard guard(flags.device());
+  b200::allreduce_mean_multimem(reinterpret_cast<void*>(mc_ptr), (int)world, (int)rank, n, (int)dtype, flags.data_ptr<int>(),
+                                to_peers(peer_flags), (int)channel, (int)epoch, status.data_ptr<int>(), cur_stream());
+}
+
 void allreduce_mean(at::IntArrayRef buf_ptrs, int64_t rank, int64_t n, int64_t dtype, const Tensor& flags,
                     at::IntArrayRef peer_flags, int64_t channel, int64_t epoch, Tensor status) {
   const c10::cuda::CUDAGuard guard(flags.device());
@@ -637,6 +644,7 @@ TORCH_LIBRARY(b200, m) {
   m.def("stack_scale_by_inv_norm(Tensor(a!) x, Tensor sumsq, int nmat, int mat_elems, float eps) -> ()");
   m.def("ag_push(Tensor src, int[] u_full_ptrs, int rank, int dst_off, int[] peer_flags, int channel, int epoch) -> ()");
   m.def("ag_wait_apply(Tensor(a!) p, Tensor u, Tensor(b!)? p_bf16, float alpha, int world, Tensor flags, int channel, int epoch, Tensor(c!) status) -> ()");
+  m.def("allreduce_mean_multimem(int mc_ptr, int world, int rank, int n, int dtype, Tensor flags, int[] peer_flags, int channel, int epoch, Tensor(a!) status) -> ()");
   m.def("allreduce_mean(int[] buf_ptrs, int rank, int n, int dtype, Tensor flags, int[] peer_flags, int channel, int epoch, Tensor(a!) status) -> ()");
   m.def("s6_scan_fwd(Tensor u, Tensor delta, Tensor? delta_bias, bool softplus, Tensor A, Tensor Bm, Tensor Cm, Tensor? Dv, Tensor? z, Tensor(a!)? y_pre, Tensor(b!) out, Tensor(c!)? state) -> ()");
   m.def("s6_scan_bwd(Tensor u, Tensor delta, Tensor? delta_bias, bool softplus, Tensor A, Tensor Bm, Tensor Cm, Tensor? Dv, Tensor? z, Tensor? y_pre, Tensor dout, Tensor state, Tensor(a!) du, Tensor(b!) ddelta, Tensor(c!) dA, Tensor(d!) dB_part, Tensor(e!) dC_part, Tensor(f!)? dD, Tensor(g!)? dz, Tensor(h!)? ddelta_bias) -> ()");
@@ -685,6 +693,7 @@ TORCH_LIBRARY_IMPL(b200, CUDA, m) {
   m.impl("stack_scale_by_inv_norm", &stack_scale_by_inv_norm);
   m.impl("ag_push", &ag_push);
   m.impl("ag_wait_apply", &ag_wait_apply);
+  m.impl("allreduce_mean_multimem", &allreduce_mean_multimem);
   m.impl("allreduce_mean", &allreduce_mean);
   m.impl("s6_scan_fwd", &s6_scan_fwd);
   m.impl("s6_scan_bwd", &s6_scan_bwd);

@@ -213,6 +213,47 @@ allreduce_kernel(PeerPtrs bufs, int world, int rank, long long lo, long long hi,
   block_done_then_signal(counter, peer_flags, world, rank, channel + 1, epoch);
 }
 
+// In-switch variant: `mc` is the NVLink multicast address of the same symmetric buffer. One multimem.ld_reduce returns
+// the sum over all ranks of 16 bytes (reduced inside NVSwitch), one multimem.st writes the scaled result to every rank;
+// each rank handles its 1/world slice, so every byte crosses this GPU's links once in each direction.
+template <int DT>
+__global__ void __launch_bounds__(256)
+allreduce_multimem_kernel(void* mc, int world, int rank, long long lo, long long hi, const int* flags, PeerPtrs peer_flags,
+                          int channel, int epoch, int* status, int* counter) {
+  if (status_poisoned(status)) return;
+  const bool ok = block_wait_flags(flags, world, channel, epoch, status);
+  constexpr int VEC = DT == 0 ? 4 : 8;
+  const float inv_w = 1.f / world;
+  if (ok) {
+    for (long long i = lo + ((long long)blockIdx.x * blockDim.x + threadIdx.x) * VEC; i < hi;
+         i += (long long)gridDim.x * blockDim.x * VEC) {
+      if (DT == 0) {
+        float* addr = reinterpret_cast<float*>(mc) + i;
+        float4 a;
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w) : "l"(addr) : "memory");
+        a.x *= inv_w; a.y *= inv_w; a.z *= inv_w; a.w *= inv_w;
+        asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                     :: "l"(addr), "f"(a.x), "f"(a.y), "f"(a.z), "f"(a.w) : "memory");
+      } else {
+        bf16* addr = reinterpret_cast<bf16*>(mc) + i;
+        uint4 v;
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(addr) : "memory");
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 x = __bfloat1622float2(h[k]);
+          h[k] = __floats2bfloat162_rn(x.x * inv_w, x.y * inv_w);
+        }
+        asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};"
+                     :: "l"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+      }
+    }
+  }
+  block_done_then_signal(counter, peer_flags, world, rank, channel + 1, epoch);
+}
+
 void check(const char* what) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
@@ -303,6 +344,24 @@ void allreduce_mean(const PeerPtrs& bufs, int world, int rank, long long n, int 
   else
     allreduce_kernel<1><<<blocks, 256, 0, s>>>(bufs, world, rank, lo, hi, flags, peer_flags, channel, epoch, status, ctr);
   check("allreduce_mean");
+}
+
+void allreduce_mean_multimem(void* mc, int world, int rank, long long n, int dtype, const int* flags, const PeerPtrs& peer_flags,
+                             int channel, int epoch, int* status, cudaStream_t s) {
+  const int vec = dtype == 0 ? 4 : 8;
+  if (n % vec != 0) throw std::runtime_error("allreduce_mean_multimem: element count must be a multiple of the 16-byte vector");
+  if (!mc) throw std::runtime_error("allreduce_mean_multimem: no multicast address (NVLS not available for this buffer)");
+  const long long chunks = n / vec;
+  const long long lo = (chunks * rank / world) * vec, hi = (chunks * (rank + 1) / world) * vec;
+  int blocks = (int)(((hi - lo) / vec + 255) / 256);
+  if (blocks > 148 * 2) blocks = 148 * 2;
+  if (blocks < 1) blocks = 1;
+  int* ctr = device_counter() + 2;
+  if (dtype == 0)
+    allreduce_multimem_kernel<0><<<blocks, 256, 0, s>>>(mc, world, rank, lo, hi, flags, peer_flags, channel, epoch, status, ctr);
+  else
+    allreduce_multimem_kernel<1><<<blocks, 256, 0, s>>>(mc, world, rank, lo, hi, flags, peer_flags, channel, epoch, status, ctr);
+  check("allreduce_mean_multimem");
 }
 
 }  // namespace b200

@@ -50,6 +50,11 @@ void ag_wait_apply(float* p, const void* u_bf16, void* p_bf16, long long n, floa
 void allreduce_mean(const PeerPtrs& bufs, int world, int rank, long long n, int dtype, const int* flags,
                     const PeerPtrs& peer_flags, int channel, int epoch, int* status, cudaStream_t s);
 
+// The same all-reduce through NVSwitch multicast (NVLS): `mc` is the multicast address of the symmetric buffer; the sum
+// is formed inside the switch by multimem.ld_reduce and written to every rank by multimem.st. Same flag protocol.
+void allreduce_mean_multimem(void* mc, int world, int rank, long long n, int dtype, const int* flags,
+                             const PeerPtrs& peer_flags, int channel, int epoch, int* status, cudaStream_t s);
+
 // Blocks the stream (bounded) until flags[channel][r] >= epoch for every r.
 void comm_wait(const int* flags, int world, int channel, int epoch, int* status, cudaStream_t s);
 

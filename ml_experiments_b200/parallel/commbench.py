@@ -54,7 +54,7 @@ def _gemm_peak_tflops():
     return (json.loads(p.read_text())["bf16_tflops"], "measured") if p.exists() else (1590.0, "fallback")
 
 
-def bench_allreduce(w: SymmWorld, sizes_mb, iters, warmup, link_gbs, emit):
+def bench_allreduce(w: SymmWorld, sizes_mb, iters, warmup, link_gbs, emit, use_nvls=False):
     o, dev, W = ops(), w.device, w.world
     epoch = [0]
     for dtype, code in ((torch.bfloat16, 1), (torch.float32, 0)):
@@ -75,12 +75,20 @@ def bench_allreduce(w: SymmWorld, sizes_mb, iters, warmup, link_gbs, emit):
             def nccl():
                 dist.all_reduce(ref, op=dist.ReduceOp.AVG)
 
+            def nvls():
+                epoch[0] += 1
+                o.comm_signal(w.flags.ptrs, w.rank, CH_IN, 10_000_000 + epoch[0], w.flags.local)
+                o.allreduce_mean_multimem(buf.mc_ptr, W, w.rank, n, code, w.flags.local, w.flags.ptrs, CH_IN, 10_000_000 + epoch[0], status(dev))
+                o.comm_wait(w.flags.local, W, CH_OUT, 10_000_000 + epoch[0], status(dev))
+
             t_f, t_n = _timed(fused, iters, warmup, dev), _timed(nccl, iters, warmup, dev)
+            t_m = _timed(nvls, iters, warmup, dev) if (use_nvls and buf.mc_ptr) else None
             check_status()
             per_dir = (W - 1) / W * n * esize
             roof_ms = per_dir / (link_gbs * 1e6)
             emit(dict(bench="allreduce", dtype=str(dtype).split(".")[-1], mbytes=round(n * esize / 2 ** 20, 1), world=W, fused_ms=round(t_f, 4),
                       nccl_ms=round(t_n, 4), fused_busbw_gbs=round(2 * per_dir / t_f / 1e6, 1), nccl_busbw_gbs=round(2 * per_dir / t_n / 1e6, 1),
+                      multimem_ms=None if t_m is None else round(t_m, 4), multimem_frac_of_roofline=None if t_m is None else round(roof_ms / t_m, 3),
                       roofline_ms=round(roof_ms, 4), fused_frac_of_roofline=round(roof_ms / t_f, 3), link_gbs=link_gbs))
 
 
@@ -150,6 +158,7 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--link-gbs", type=float, default=770.0)
+    ap.add_argument("--nvls", action="store_true", help="also time the NVSwitch-multicast (multimem) all-reduce")
     ap.add_argument("--skip", default="", help="comma list of benches to skip (allreduce, muon_step)")
     a = ap.parse_args(argv)
     rank, world, local = (int(os.environ.get(k, d)) for k, d in (("RANK", 0), ("WORLD_SIZE", 1), ("LOCAL_RANK", 0)))
@@ -160,7 +169,7 @@ def main(argv=None):
     emit = lambda d: print(json.dumps(d), flush=True) if rank == 0 else None
     skip = set(a.skip.split(","))
     if "allreduce" not in skip:
-        bench_allreduce(w, [int(s) for s in a.sizes_mb.split(",")], a.iters, a.warmup, a.link_gbs, emit)
+        bench_allreduce(w, [int(s) for s in a.sizes_mb.split(",")], a.iters, a.warmup, a.link_gbs, emit, a.nvls)
     if "muon_step" not in skip:
         bench_muon(w, a.layers, a.d_model, a.iters, a.warmup, a.link_gbs, emit)
     dist.barrier()

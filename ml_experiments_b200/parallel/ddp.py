@@ -9,7 +9,8 @@ order, the order in which backward produces them). A ``post_accumulate_grad`` ho
 bucket; when a bucket is complete its all-reduce starts on a side stream while backward continues:
 
 * CUDA with symmetric memory: the bucket *is* a peer-mapped buffer and the mean all-reduce is this package's
-  two-shot peer-memory kernel (sum over peers, 1/W scale and dtype handling fused);
+  two-shot peer-memory kernel (sum over peers, 1/W scale and dtype handling fused), or with ``use_nvls`` its
+  NVSwitch-multicast variant (``multimem.ld_reduce`` / ``multimem.st``: the sum is formed inside the switch);
 * otherwise (CPU / gloo, or no peer access): ``dist.all_reduce`` on the flat bucket.
 
 ``finish()`` (called automatically by ``step`` hooks of optimizers created through :meth:`wrap_optimizer`, or by hand)
@@ -18,6 +19,7 @@ waits for all buckets and re-points every ``p.grad`` at its averaged bucket view
 from __future__ import annotations
 
 import contextlib
+import os
 
 import torch
 import torch.distributed as dist
@@ -48,8 +50,10 @@ class _Bucket:
 
 class DistributedDataParallel(nn.Module):
     def __init__(self, module: nn.Module, world=None, bucket_cap_mb: float = 64.0, process_group=None,
-                 broadcast_parameters: bool = True):
+                 broadcast_parameters: bool = True, use_nvls: bool | None = None):
         super().__init__()
+        # in-switch reduction (multimem) instead of peer loads; off unless asked for (argument or B200_NVLS=1)
+        self.use_nvls = (os.environ.get("B200_NVLS", "0") == "1") if use_nvls is None else use_nvls
         self.module = module
         self.group = process_group
         self.world_size = dist.get_world_size(process_group) if dist.is_initialized() else 1
@@ -122,8 +126,12 @@ class DistributedDataParallel(nn.Module):
             with torch.cuda.stream(self._comm_stream):
                 self._comm_stream.wait_event(ready)
                 o.comm_signal(w.flags.ptrs, w.rank, CH_IN, epoch, w.flags.local)
-                o.allreduce_mean(b.symm.ptrs, w.rank, b.numel, 1 if b.dtype == torch.bfloat16 else 0, w.flags.local,
-                                 w.flags.ptrs, CH_IN, epoch, status(self.device))
+                code = 1 if b.dtype == torch.bfloat16 else 0
+                if self.use_nvls and b.symm.mc_ptr:
+                    o.allreduce_mean_multimem(b.symm.mc_ptr, w.world, w.rank, b.numel, code, w.flags.local, w.flags.ptrs, CH_IN, epoch,
+                                              status(self.device))
+                else:
+                    o.allreduce_mean(b.symm.ptrs, w.rank, b.numel, code, w.flags.local, w.flags.ptrs, CH_IN, epoch, status(self.device))
                 o.comm_wait(w.flags.local, w.world, CH_OUT, epoch, status(self.device))
                 b.event = torch.cuda.Event()
                 b.event.record()

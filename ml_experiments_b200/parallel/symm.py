@@ -25,6 +25,7 @@ class SymmBuffer:
     local: torch.Tensor            # this rank's buffer
     ptrs: list[int]                # address of every rank's buffer as mapped on this device
     handle: object = None          # keeps the symmetric-memory mapping alive
+    mc_ptr: int = 0                # NVLink multicast (NVLS) address of the same buffer, 0 when the fabric offers none
 
 
 @dataclass
@@ -54,7 +55,11 @@ class SymmWorld:
             t.zero_()
             torch.cuda.synchronize(self.device)
             dist.barrier(group=group)
-        buf = SymmBuffer(local=t, ptrs=[int(p) for p in hdl.buffer_ptrs], handle=hdl)
+        try:
+            mc = int(getattr(hdl, "multicast_ptr", 0) or 0)
+        except Exception:
+            mc = 0
+        buf = SymmBuffer(local=t, ptrs=[int(p) for p in hdl.buffer_ptrs], handle=hdl, mc_ptr=mc)
         self._keep.append(buf)
         return buf
 
