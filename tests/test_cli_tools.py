@@ -62,3 +62,24 @@ def test_line_filter_trainer_checkpoints_and_resumes(tmp_path):
     assert abs(T.pos_weight_at(0, 10, 4.0, 1.0) - 4.0) < 1e-6 and abs(T.pos_weight_at(9, 10, 4.0, 1.0) - 1.0) < 1e-6
     m = T.main(common + ["--epochs", "1", "--head", "classifier", "--no-swa"])
     assert 0.0 <= float(m["best_metric"]) <= 1.0
+
+
+def test_pathfinder_generator_and_pathx_trainers(tmp_path):
+    import numpy as np
+
+    from ml_experiments_b200.cli import generate_pathx, train_pathx
+    from ml_experiments_b200.data import pathfinder
+
+    x, y = pathfinder.generate(12, 64, seed=3)
+    x2, y2 = pathfinder.generate(12, 64, seed=3)
+    assert x.shape == (12, 64, 64) and x.dtype == np.uint8 and (x == x2).all() and (y == y2).all() and y.sum() == 6
+    assert 0.005 < (x > 0).mean() < 0.5                       # sparse strokes on a dark canvas
+    generate_pathx.main(["--output-dir", str(tmp_path / "gen"), "--n-train", "8", "--n-val", "4", "--n-test", "0", "--size", "32"])
+    assert np.load(tmp_path / "gen" / "train.npz")["x"].shape == (8, 32, 32)
+    common = ["--size", "16", "--n-train", "32", "--n-val", "16", "--embed-width", "16", "--attn-window", "16", "--data-dir", str(tmp_path / "d"),
+              "--device", "cpu", "--batch-size", "16"]
+    s1 = train_pathx.main(common + ["--epochs", "2", "--mode", "1d", "--arch", "conv", "--output", str(tmp_path / "o1")])
+    assert s1["tokens"] == 256 and (tmp_path / "o1" / "epoch002.pt").exists()
+    train_pathx.main(common + ["--epochs", "2", "--mode", "2d", "--output", str(tmp_path / "o2")])
+    s2 = train_pathx.main(common + ["--epochs", "2", "--mode", "2d", "--output", str(tmp_path / "o2"), "--resume", str(tmp_path / "o2" / "epoch001.pt")])
+    assert len(s2["history"]) == 2 and s2["history"][0]["epoch"] == 1     # the second epoch was run again from the first one's checkpoint
