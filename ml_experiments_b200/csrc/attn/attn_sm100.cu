@@ -325,19 +325,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
   uint8_t* sV = sK + KV_BYTES;
-  uint8_t* sQ = sV + KV_BYTES;        // 2 buffers
-  uint8_t* sdO = sQ + 2 * Q_BYTES;    // 2 buffers
-  uint8_t* sPT = sdO + 2 * Q_BYTES;
+  constexpr int NQB = 3;              // Q / dO buffers
+  uint8_t* sQ = sV + KV_BYTES;
+  uint8_t* sdO = sQ + NQB * Q_BYTES;
+  uint8_t* sPT = sdO + NQB * Q_BYTES;
   uint8_t* sdST = sPT + PT_BYTES;
   float* sdQ = reinterpret_cast<float*>(sdST + PT_BYTES);
   float2* s_ld = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(sdQ) + DQ_BYTES);  // [64] {lse, delta}
   int* s_ds = reinterpret_cast<int*>(s_ld + BQ);                                          // [64]
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_ds + BQ);
   uint64_t* bar_kv = bars;
-  uint64_t* bar_q = bars + 1;  // [2]
-  uint64_t* bar_m1 = bars + 3;
-  uint64_t* bar_m2 = bars + 4;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+  uint64_t* bar_q = bars + 1;  // [3]
+  uint64_t* bar_m1 = bars + 4;   // S / dP of a tile are in TMEM
+  uint64_t* bar_m2 = bars + 5;   // dV / dK of a tile are accumulated: its P / dS staging and its Q / dO buffer are free
+  uint64_t* bar_dq = bars + 6;   // dQ of a tile is in TMEM
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   if (status_poisoned(p.status)) return;
@@ -356,8 +358,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     mbar_init(bar_kv, 1);
     mbar_init(&bar_q[0], 1);
     mbar_init(&bar_q[1], 1);
+    mbar_init(&bar_q[2], 1);
     mbar_init(bar_m1, 1);
     mbar_init(bar_m2, 1);
+    mbar_init(bar_dq, 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -383,8 +387,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t idesc_dv = make_idesc(FMT_BF16, FMT_BF16, 0, 1, 128, D);    // Pᵀ·dO, dSᵀ·Q   (B MN-major)
   const uint32_t idesc_dq = make_idesc(FMT_BF16, FMT_BF16, 1, 1, 128, BQ);   // Kᵀ·dSᵀ         (A, B MN-major)
 
-  // One thread issues every TMA load and MMA. The S / dP products of tile it+1 are issued as soon as every thread has
-  // copied tile it's S / dP out of TMEM, so they run on the tensor pipe while the CTA does the exponentials of tile it.
+  // One thread issues every TMA load and MMA; the tensor pipe runs them in issue order. Per query tile:
+  //   S, dP of tile it+1   issued as soon as every thread has copied tile it's S / dP out of TMEM: they run while the CTA
+  //                        does the exponentials of tile it;
+  //   dQ of tile it        issued right after the exponentials, on its own barrier: the CTA stages and reduces dQ while
+  //   dV, dK of tile it    are still accumulating; their barrier is only waited for in the next iteration, before the
+  //                        P / dS staging buffers are overwritten.
+  // Q / dO tiles are triple-buffered so that the load of tile it+2 never waits for a buffer.
   auto issue_s_dp = [&](int buf) {
     const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
     const uint32_t qa = smem_u32(sQ + buf * Q_BYTES), doa = smem_u32(sdO + buf * Q_BYTES);
@@ -419,6 +428,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (ntile > 0) {
       load_q_do(0, q_lo);
       if (ntile > 1) load_q_do(1, q_lo + BQ);
+      if (ntile > 2) load_q_do(2, q_lo + 2 * BQ);
       cta_wait(bar_kv, 0, abort_flag, p.status, ERR_WAIT_SMEM_FULL);
       cta_wait(&bar_q[0], 0, abort_flag, p.status, ERR_WAIT_SMEM_FULL);
       tc_fence_after_sync();
@@ -427,7 +437,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 
   for (int it = 0; it < ntile; ++it) {
-    const int buf = it & 1;
+    const int buf = it % NQB;
     const int qt0 = q_lo + it * BQ;
     if (tid < BQ) {
       const int qq = qt0 + tid;
@@ -445,9 +455,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     tc_fence_before_sync();
     __syncthreads();  // every thread holds its S / dP values: the TMEM columns may be overwritten
     if (tid == 0 && it + 1 < ntile) {
-      cta_wait(&bar_q[buf ^ 1], ((it + 1) >> 1) & 1, abort_flag, p.status, ERR_WAIT_SMEM_FULL);
+      cta_wait(&bar_q[(it + 1) % NQB], ((it + 1) / NQB) & 1, abort_flag, p.status, ERR_WAIT_SMEM_FULL);
       tc_fence_after_sync();
-      issue_s_dp(buf ^ 1);
+      issue_s_dp((it + 1) % NQB);
+    }
+    if (it > 0) {  // dV / dK of the previous tile: frees the P / dS staging and that tile's Q / dO buffer
+      cta_wait(bar_m2, (it - 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
+      tc_fence_after_sync();
+      if (tid == 0 && it + 2 < ntile) load_q_do((it + 2) % NQB, qt0 + 2 * BQ);
     }
 
     // masks are needed only where the tile touches the causal diagonal, a document boundary or the sequence end
@@ -483,6 +498,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_after_sync();
       const uint32_t pa = smem_u32(sPT), dsa = smem_u32(sdST), ka = smem_u32(sK);
       const uint32_t qa = smem_u32(sQ + buf * Q_BYTES), doa = smem_u32(sdO + buf * Q_BYTES);
+      tma_store_wait_read<0>();  // previous tile's reduce-add has drained the dQ staging buffer
+#pragma unroll
+      for (int ks = 0; ks < BKV / 16; ++ks) {  // dQᵀ = Kᵀ · dSᵀ
+        const uint64_t ad = make_smem_desc_sw128(ka + ks * 2048, BKV * 128, 1024);
+        const uint64_t bd = make_smem_desc_sw128(dsa + ks * 2048, BKV * 128, 1024);
+        tc_mma_f16(tmem_base + DQT_COL, ad, bd, idesc_dq, ks != 0);
+      }
+      tc_commit(bar_dq);
 #pragma unroll
       for (int ks = 0; ks < BQ / 16; ++ks) {  // dV += Pᵀ · dO
         const uint64_t ad = make_smem_desc_sw128(pa + ks * 32, 16, 1024);
@@ -495,19 +518,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const uint64_t bd = make_smem_desc_sw128(qa + ks * 2048, BQ * 128, 1024);
         tc_mma_f16(tmem_base + DK_COL, ad, bd, idesc_dv, (it | ks) != 0);
       }
-#pragma unroll
-      for (int ks = 0; ks < BKV / 16; ++ks) {  // dQᵀ = Kᵀ · dSᵀ
-        const uint64_t ad = make_smem_desc_sw128(ka + ks * 2048, BKV * 128, 1024);
-        const uint64_t bd = make_smem_desc_sw128(dsa + ks * 2048, BKV * 128, 1024);
-        tc_mma_f16(tmem_base + DQT_COL, ad, bd, idesc_dq, ks != 0);
-      }
       tc_commit(bar_m2);
-      tma_store_wait_read<0>();  // previous tile's reduce-add has drained the staging buffer
     }
-    __syncthreads();
-    cta_wait(bar_m2, it & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
+    cta_wait(bar_dq, it & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
     tc_fence_after_sync();
-    if (tid == 0 && it + 2 < ntile) load_q_do(buf, qt0 + 2 * BQ);  // this tile's Q / dO buffer is free again
     // dQᵀ row (= head-dim index r), this warp's half of the query columns -> staging[q][r]
     if (r < D) {
       uint32_t v[32];
@@ -526,6 +540,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 
   // final: dV, dK rows; each warp writes its half of the head dimension
+  if (ntile > 0) cta_wait(bar_m2, (ntile - 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
   tc_fence_after_sync();
   if (ntile > 0) {
     __nv_bfloat16* dvrow = p.dv + (long long)kv * p.ld_dv + h * D + half * (D / 2);
@@ -628,7 +643,7 @@ void fwd_impl(const AttnArgs& a) {
 template <int D>
 void bwd_impl(const AttnArgs& a) {
   constexpr int NS = D / 64;
-  const int smem = 2 * NS * 128 * 128 + 4 * NS * 64 * 128 + 2 * 128 * 128 + 64 * D * 4 + 3 * 64 * 4 + 64 + 1024;
+  const int smem = 2 * NS * 128 * 128 + 6 * NS * 64 * 128 + 2 * 128 * 128 + 64 * D * 4 + 3 * 64 * 4 + 96 + 1024;
   CUtensorMap tq = qkv_map(a.q, a.T, a.H, D, a.ld_q, 64);
   CUtensorMap tk = qkv_map(a.k, a.T, a.H, D, a.ld_k, 128);
   CUtensorMap tv = qkv_map(a.v, a.T, a.H, D, a.ld_v, 128);

@@ -1,5 +1,5 @@
-// See fused_taps.h. Thread layout as in gather_conv.cu: a group of LPR = D/4 adjacent lanes owns one (b, l, h) row and
-// each lane keeps 4 channels. Taps are processed LPR at a time: lane j of the group evaluates the tap formula of tap
+// See fused_taps.h. A group of LPR adjacent lanes owns one (b, l, h) row and each lane keeps CPL = D / LPR channels
+// (8 where the head dimension allows: 16-byte row loads, and the per-tap index arithmetic is shared by more channels). Taps are processed LPR at a time: lane j of the group evaluates the tap formula of tap
 // s0 + j (so the transcendental work is done once per tap, not once per lane), then the group walks the LPR taps,
 // broadcasting (weight, position) by shuffle and gathering the two value rows. In the backward the owner lane of a tap
 // turns the two reduced dot products into the gradients of the row's scalars; kernel-table gradients accumulate in
@@ -17,15 +17,69 @@ namespace {
 using bf16 = __nv_bfloat16;
 constexpr int KMAX = 64;
 
-__device__ __forceinline__ float4 ld4(const bf16* p) {
-  const uint2 u = *reinterpret_cast<const uint2*>(p);
-  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
-  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
-  return make_float4(a.x, a.y, b.x, b.y);
+template <int CPL>
+struct Vec {
+  float v[CPL];
+};
+template <int CPL>
+__device__ __forceinline__ Vec<CPL> vzero() {
+  Vec<CPL> r;
+#pragma unroll
+  for (int i = 0; i < CPL; ++i) r.v[i] = 0.f;
+  return r;
 }
-__device__ __forceinline__ void st4(bf16* p, float4 v) {
-  __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
-  *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+template <int CPL>
+__device__ __forceinline__ Vec<CPL> vload(const bf16* p) {
+  Vec<CPL> r;
+  if (CPL == 8) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(h[i]);
+      r.v[2 * i] = f.x;
+      r.v[2 * i + 1] = f.y;
+    }
+  } else {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const float2 f = __bfloat1622float2(h[i]);
+      r.v[2 * i] = f.x;
+      r.v[2 * i + 1] = f.y;
+    }
+  }
+  return r;
+}
+template <int CPL>
+__device__ __forceinline__ void vstore(bf16* p, const Vec<CPL>& a) {
+  uint32_t w[CPL / 2];
+#pragma unroll
+  for (int i = 0; i < CPL / 2; ++i) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a.v[2 * i], a.v[2 * i + 1]);
+    w[i] = *reinterpret_cast<uint32_t*>(&h);
+  }
+  if (CPL == 8) *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  else *reinterpret_cast<uint2*>(p) = make_uint2(w[0], w[1]);
+}
+template <int CPL>
+__device__ __forceinline__ float vdot(const Vec<CPL>& a, const Vec<CPL>& b) {
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < CPL; ++i) s += a.v[i] * b.v[i];
+  return s;
+}
+template <int CPL>
+__device__ __forceinline__ void vaxpy2(Vec<CPL>& acc, float wa, const Vec<CPL>& a, float wc, const Vec<CPL>& c) {
+#pragma unroll
+  for (int i = 0; i < CPL; ++i) acc.v[i] += wa * a.v[i] + wc * c.v[i];
+}
+template <int CPL>
+__device__ __forceinline__ void scatter_row(float* dst, float wgt, const Vec<CPL>& g) {
+#pragma unroll
+  for (int i = 0; i < CPL; i += 4)
+    atomicAdd(reinterpret_cast<float4*>(dst + i), make_float4(wgt * g.v[i], wgt * g.v[i + 1], wgt * g.v[i + 2], wgt * g.v[i + 3]));
 }
 template <int LPR>
 __device__ __forceinline__ unsigned group_mask() {
@@ -43,7 +97,6 @@ template <int LPR>
 __device__ __forceinline__ float group_bcast(float v, int j) {
   return __shfl_sync(group_mask<LPR>(), v, j, LPR);
 }
-__device__ __forceinline__ float dot4(float4 a, float4 b) { return a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w; }
 
 struct Lerp {
   int lo;
@@ -111,12 +164,12 @@ __device__ __forceinline__ Bil bilinear(float p, int L) {
 // Walks the n <= LPR taps held one per lane (weight w, position p), UNR at a time (the row loads of UNR taps are issued
 // together); taps of weight zero are not loaded.
 constexpr int UNR = 1;  // measured: 2 and 4 lose more to the lower occupancy (64 / 99 registers) than the batched loads win
-template <int LPR>
-__device__ __forceinline__ void gather_taps(float4& acc, float w, float p, int n, const bf16* xb, int L, long long rs) {
+template <int LPR, int CPL>
+__device__ __forceinline__ void gather_taps(Vec<CPL>& acc, float w, float p, int n, const bf16* xb, int L, long long rs) {
   for (int j0 = 0; j0 < n; j0 += UNR) {
     float wj[UNR];
     Bil bi[UNR];
-    float4 a[UNR], c[UNR];
+    Vec<CPL> a[UNR], c[UNR];
 #pragma unroll
     for (int u = 0; u < UNR; ++u) {
       const int j = j0 + u;
@@ -126,38 +179,31 @@ __device__ __forceinline__ void gather_taps(float4& acc, float w, float p, int n
     }
 #pragma unroll
     for (int u = 0; u < UNR; ++u) {
-      a[u] = c[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      a[u] = c[u] = vzero<CPL>();
       if (wj[u] != 0.f) {
-        a[u] = ld4(xb + bi[u].fl * rs);
-        c[u] = ld4(xb + bi[u].ce * rs);
+        a[u] = vload<CPL>(xb + bi[u].fl * rs);
+        c[u] = vload<CPL>(xb + bi[u].ce * rs);
       }
     }
 #pragma unroll
-    for (int u = 0; u < UNR; ++u) {
-      const float wa = wj[u] * (1.f - bi[u].fr), wc = wj[u] * bi[u].fr;
-      acc.x += wa * a[u].x + wc * c[u].x; acc.y += wa * a[u].y + wc * c[u].y;
-      acc.z += wa * a[u].z + wc * c[u].z; acc.w += wa * a[u].w + wc * c[u].w;
-    }
+    for (int u = 0; u < UNR; ++u) vaxpy2<CPL>(acc, wj[u] * (1.f - bi[u].fr), a[u], wj[u] * bi[u].fr, c[u]);
   }
 }
 
-__device__ __forceinline__ void scatter_row(float* dst, float wgt, float4 g) {
-  atomicAdd(reinterpret_cast<float4*>(dst), make_float4(wgt * g.x, wgt * g.y, wgt * g.z, wgt * g.w));
-}
 
 // ------------------------------------------------------------------------------------------------ telephone
-template <int LPR>
+template <int LPR, int CPL>
 __global__ void __launch_bounds__(256)
 tele_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ freq, const float* __restrict__ phase,
                 const float* __restrict__ kern, const float* __restrict__ expo, bf16* __restrict__ out, int B, int L, int H,
                 int K, int half, float max_rec) {
-  constexpr int D = LPR * 4;
+  constexpr int D = LPR * CPL;
   const Row r = locate<LPR>(B, L, H);
   const float f = freq[r.row], ph = phase[r.row], e = expo[r.bl];
   const float* kr = kern + r.row * K;
-  const bf16* xb = x + (long long)r.b * L * H * D + r.h * D + r.sub * 4;
+  const bf16* xb = x + (long long)r.b * L * H * D + r.h * D + r.sub * CPL;
   const float invL = 1.f / (float)L, inv_rec = 1.f / max_rec;
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  Vec<CPL> acc = vzero<CPL>();
   for (int s0 = -half; s0 <= half; s0 += LPR) {
     const int s = s0 + r.sub;
     float w = 0.f, p = 0.f;
@@ -167,18 +213,18 @@ tele_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ freq, cons
       if (p >= 0.f && p < (float)L) w = lerp_table(kr, K, ar * inv_rec).v * exp2f(-e * log2f(1.f + ar * invL));
     }
     const int n = min(LPR, half - s0 + 1);
-    gather_taps<LPR>(acc, w, p, n, xb, L, (long long)H * D);
+    gather_taps<LPR, CPL>(acc, w, p, n, xb, L, (long long)H * D);
   }
-  if (r.active) st4(out + r.row * D + r.sub * 4, acc);
+  if (r.active) vstore<CPL>(out + r.row * D + r.sub * CPL, acc);
 }
 
-template <int LPR>
+template <int LPR, int CPL>
 __global__ void __launch_bounds__(256)
 tele_bwd_kernel(const bf16* __restrict__ x, const float* __restrict__ freq, const float* __restrict__ phase,
                 const float* __restrict__ kern, const float* __restrict__ expo, const bf16* __restrict__ dout,
                 float* __restrict__ dx, float* __restrict__ dfreq, float* __restrict__ dphase, float* __restrict__ dkern,
                 float* __restrict__ dexpo_h, int B, int L, int H, int K, int half, float max_rec) {
-  constexpr int D = LPR * 4;
+  constexpr int D = LPR * CPL;
   constexpr int RPB = 256 / LPR;
   extern __shared__ float s_dk[];  // [RPB][K]
   for (int i = threadIdx.x; i < RPB * K; i += 256) s_dk[i] = 0.f;
@@ -187,10 +233,10 @@ tele_bwd_kernel(const bf16* __restrict__ x, const float* __restrict__ freq, cons
   const float f = freq[r.row], ph = phase[r.row], e = expo[r.bl];
   const float* kr = kern + r.row * K;
   float* dk = s_dk + (threadIdx.x / LPR) * K;
-  const bf16* xb = x + (long long)r.b * L * H * D + r.h * D + r.sub * 4;
-  float* dxb = dx + (long long)r.b * L * H * D + r.h * D + r.sub * 4;
+  const bf16* xb = x + (long long)r.b * L * H * D + r.h * D + r.sub * CPL;
+  float* dxb = dx + (long long)r.b * L * H * D + r.h * D + r.sub * CPL;
   const float invL = 1.f / (float)L, inv_rec = 1.f / max_rec, hi = (float)L - 1.001f;
-  const float4 g = ld4(dout + r.row * D + r.sub * 4);
+  const Vec<CPL> g = vload<CPL>(dout + r.row * D + r.sub * CPL);
   float df = 0.f, dph = 0.f, de = 0.f;
   for (int s0 = -half; s0 <= half; s0 += LPR) {
     const int s = s0 + r.sub;
@@ -218,7 +264,7 @@ tele_bwd_kernel(const bf16* __restrict__ x, const float* __restrict__ freq, cons
       float wj[UNR];
       bool vj[UNR];
       Bil bi[UNR];
-      float4 a[UNR], c[UNR];
+      Vec<CPL> a[UNR], c[UNR];
 #pragma unroll
       for (int u = 0; u < UNR; ++u) {
         const int j = j0 + u, src = j & (LPR - 1);
@@ -229,19 +275,19 @@ tele_bwd_kernel(const bf16* __restrict__ x, const float* __restrict__ freq, cons
       }
 #pragma unroll
       for (int u = 0; u < UNR; ++u) {
-        a[u] = c[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        a[u] = c[u] = vzero<CPL>();
         if (vj[u]) {
-          a[u] = ld4(xb + bi[u].fl * rs);
-          c[u] = ld4(xb + bi[u].ce * rs);
+          a[u] = vload<CPL>(xb + bi[u].fl * rs);
+          c[u] = vload<CPL>(xb + bi[u].ce * rs);
         }
       }
 #pragma unroll
       for (int u = 0; u < UNR; ++u) {
-        const float sa = group_sum<LPR>(dot4(g, a[u])), sc = group_sum<LPR>(dot4(g, c[u]));
+        const float sa = group_sum<LPR>(vdot<CPL>(g, a[u])), sc = group_sum<LPR>(vdot<CPL>(g, c[u]));
         if (r.sub == j0 + u) { my_sa = sa; my_sc = sc; my_fr = bi[u].fr; }
         if (r.active && vj[u] && wj[u] != 0.f) {
-          scatter_row(dxb + bi[u].fl * rs, wj[u] * (1.f - bi[u].fr), g);
-          if (bi[u].fr != 0.f) scatter_row(dxb + bi[u].ce * rs, wj[u] * bi[u].fr, g);
+          scatter_row<CPL>(dxb + bi[u].fl * rs, wj[u] * (1.f - bi[u].fr), g);
+          if (bi[u].fr != 0.f) scatter_row<CPL>(dxb + bi[u].ce * rs, wj[u] * bi[u].fr, g);
         }
       }
     }
@@ -290,19 +336,19 @@ __device__ __forceinline__ AlcTap alc_tap(const float* kr, int K, int s, float i
   return t;
 }
 
-template <int LPR>
+template <int LPR, int CPL>
 __global__ void __launch_bounds__(256)
 alc_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ half_w, const float* __restrict__ center,
                const float* __restrict__ kern, bf16* __restrict__ out, int B, int L, int H, int K, int half) {
-  constexpr int D = LPR * 4;
+  constexpr int D = LPR * CPL;
   const Row r = locate<LPR>(B, L, H);
   const float inv_hw = 1.f / half_w[r.row], pc0 = (float)r.l + center[r.row];
   const float* kr = kern + r.row * K;
-  const bf16* xb = x + (long long)r.b * L * H * D + r.h * D + r.sub * 4;
+  const bf16* xb = x + (long long)r.b * L * H * D + r.h * D + r.sub * CPL;
   float sum = 0.f;
   for (int s = -half + r.sub; s <= half; s += LPR) sum += alc_tap(kr, K, s, inv_hw, pc0, L).base;
   const float inv_norm = 1.f / fmaxf(group_sum<LPR>(sum), 1.f);
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  Vec<CPL> acc = vzero<CPL>();
   for (int s0 = -half; s0 <= half; s0 += LPR) {
     const int s = s0 + r.sub;
     float w = 0.f, p = 0.f;
@@ -312,19 +358,19 @@ alc_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ half_w, con
       p = t.p;
     }
     const int n = min(LPR, half - s0 + 1);
-    gather_taps<LPR>(acc, w, p, n, xb, L, (long long)H * D);
+    gather_taps<LPR, CPL>(acc, w, p, n, xb, L, (long long)H * D);
   }
-  if (r.active) st4(out + r.row * D + r.sub * 4, acc);
+  if (r.active) vstore<CPL>(out + r.row * D + r.sub * CPL, acc);
 }
 
 // shared memory: [RPB][K] kernel gradients, then [RPB][SP] per-tap dW (SP = 2*half+1)
-template <int LPR>
+template <int LPR, int CPL>
 __global__ void __launch_bounds__(256)
 alc_bwd_kernel(const bf16* __restrict__ x, const float* __restrict__ half_w, const float* __restrict__ center,
                const float* __restrict__ kern, const bf16* __restrict__ dout, float* __restrict__ dx,
                float* __restrict__ dhalf_w, float* __restrict__ dcenter, float* __restrict__ dkern, int B, int L, int H,
                int K, int half) {
-  constexpr int D = LPR * 4;
+  constexpr int D = LPR * CPL;
   constexpr int RPB = 256 / LPR;
   extern __shared__ float s_mem[];
   const int SP = 2 * half + 1;
@@ -337,10 +383,10 @@ alc_bwd_kernel(const bf16* __restrict__ x, const float* __restrict__ half_w, con
   const float* kr = kern + r.row * K;
   float* dk = s_dk + (threadIdx.x / LPR) * K;
   float* dw = s_dw + (threadIdx.x / LPR) * SP;
-  const bf16* xb = x + (long long)r.b * L * H * D + r.h * D + r.sub * 4;
-  float* dxb = dx + (long long)r.b * L * H * D + r.h * D + r.sub * 4;
+  const bf16* xb = x + (long long)r.b * L * H * D + r.h * D + r.sub * CPL;
+  float* dxb = dx + (long long)r.b * L * H * D + r.h * D + r.sub * CPL;
   const float hi = (float)L - 1.001f;
-  const float4 g = ld4(dout + r.row * D + r.sub * 4);
+  const Vec<CPL> g = vload<CPL>(dout + r.row * D + r.sub * CPL);
   float sum = 0.f;
   for (int s = -half + r.sub; s <= half; s += LPR) sum += alc_tap(kr, K, s, inv_hw, pc0, L).base;
   sum = group_sum<LPR>(sum);
@@ -361,7 +407,7 @@ alc_bwd_kernel(const bf16* __restrict__ x, const float* __restrict__ half_w, con
       float wj[UNR], pj[UNR];
       bool vj[UNR];
       Bil bi[UNR];
-      float4 a[UNR], c[UNR];
+      Vec<CPL> a[UNR], c[UNR];
 #pragma unroll
       for (int u = 0; u < UNR; ++u) {
         const int j = j0 + u, src = j & (LPR - 1);
@@ -372,15 +418,15 @@ alc_bwd_kernel(const bf16* __restrict__ x, const float* __restrict__ half_w, con
       }
 #pragma unroll
       for (int u = 0; u < UNR; ++u) {
-        a[u] = c[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        a[u] = c[u] = vzero<CPL>();
         if (vj[u]) {
-          a[u] = ld4(xb + bi[u].fl * rs);
-          c[u] = ld4(xb + bi[u].ce * rs);
+          a[u] = vload<CPL>(xb + bi[u].fl * rs);
+          c[u] = vload<CPL>(xb + bi[u].ce * rs);
         }
       }
 #pragma unroll
       for (int u = 0; u < UNR; ++u) {
-        const float sa = group_sum<LPR>(dot4(g, a[u])), sc = group_sum<LPR>(dot4(g, c[u]));
+        const float sa = group_sum<LPR>(vdot<CPL>(g, a[u])), sc = group_sum<LPR>(vdot<CPL>(g, c[u]));
         const float dWj = sa * (1.f - bi[u].fr) + sc * bi[u].fr;  // zero for a tap outside the sequence
         if (r.sub == j0 + u && j0 + u < n) {
           G += dWj * wj[u];
@@ -388,8 +434,8 @@ alc_bwd_kernel(const bf16* __restrict__ x, const float* __restrict__ half_w, con
           dw[s0 + j0 + u + half] = dWj;
         }
         if (r.active && vj[u] && wj[u] != 0.f) {
-          scatter_row(dxb + bi[u].fl * rs, wj[u] * (1.f - bi[u].fr), g);
-          if (bi[u].fr != 0.f) scatter_row(dxb + bi[u].ce * rs, wj[u] * bi[u].fr, g);
+          scatter_row<CPL>(dxb + bi[u].fl * rs, wj[u] * (1.f - bi[u].fr), g);
+          if (bi[u].fr != 0.f) scatter_row<CPL>(dxb + bi[u].ce * rs, wj[u] * bi[u].fr, g);
         }
       }
     }
@@ -429,13 +475,13 @@ void check_dims(int D, int K, int half) {
   (void)D;
 }
 
-#define DISPATCH_LPR(D, ...)                                    \
-  switch ((D) / 4) {                                            \
-    case 2: { constexpr int LPR_ = 2; __VA_ARGS__; break; }            \
-    case 4: { constexpr int LPR_ = 4; __VA_ARGS__; break; }            \
-    case 8: { constexpr int LPR_ = 8; __VA_ARGS__; break; }            \
-    case 16: { constexpr int LPR_ = 16; __VA_ARGS__; break; }          \
-    case 32: { constexpr int LPR_ = 32; __VA_ARGS__; break; }          \
+#define DISPATCH_LPR(D, ...)                                                              \
+  switch (D) {                                                                            \
+    case 8: { constexpr int LPR_ = 2, CPL_ = 4; __VA_ARGS__; break; }                          \
+    case 16: { constexpr int LPR_ = 2, CPL_ = 8; __VA_ARGS__; break; }                         \
+    case 32: { constexpr int LPR_ = 4, CPL_ = 8; __VA_ARGS__; break; }                         \
+    case 64: { constexpr int LPR_ = 8, CPL_ = 8; __VA_ARGS__; break; }                         \
+    case 128: { constexpr int LPR_ = 16, CPL_ = 8; __VA_ARGS__; break; }                       \
     default: throw std::runtime_error("fused taps: head_dim must be 8, 16, 32, 64 or 128"); \
   }
 template <typename Kern>
@@ -453,7 +499,7 @@ void tele_fused_fwd(const void* x, const float* freq, const float* phase, const 
   DISPATCH_LPR(D, {
     const int rpb = 256 / LPR_;
     const long long nblk = (long long)B * H * ((L + rpb - 1) / rpb);
-    tele_fwd_kernel<LPR_><<<(unsigned)nblk, 256, 0, s>>>((const bf16*)x, freq, phase, kern, expo, (bf16*)out, B, L, H, K, half, max_rec);
+    tele_fwd_kernel<LPR_, CPL_><<<(unsigned)nblk, 256, 0, s>>>((const bf16*)x, freq, phase, kern, expo, (bf16*)out, B, L, H, K, half, max_rec);
   });
   chk("tele_fused_fwd");
 }
@@ -466,7 +512,7 @@ void tele_fused_bwd(const void* x, const float* freq, const float* phase, const 
     const int rpb = 256 / LPR_;
     const long long nblk = (long long)B * H * ((L + rpb - 1) / rpb);
     const size_t smem = (size_t)rpb * K * sizeof(float);
-    tele_bwd_kernel<LPR_><<<(unsigned)nblk, 256, smem, s>>>((const bf16*)x, freq, phase, kern, expo, (const bf16*)dout, dx,
+    tele_bwd_kernel<LPR_, CPL_><<<(unsigned)nblk, 256, smem, s>>>((const bf16*)x, freq, phase, kern, expo, (const bf16*)dout, dx,
                                                                                dfreq, dphase, dkern, dexpo_h, B, L, H, K, half, max_rec);
   });
   chk("tele_fused_bwd");
@@ -478,7 +524,7 @@ void alc_fused_fwd(const void* x, const float* half_w, const float* center, cons
   DISPATCH_LPR(D, {
     const int rpb = 256 / LPR_;
     const long long nblk = (long long)B * H * ((L + rpb - 1) / rpb);
-    alc_fwd_kernel<LPR_><<<(unsigned)nblk, 256, 0, s>>>((const bf16*)x, half_w, center, kern, (bf16*)out, B, L, H, K, half);
+    alc_fwd_kernel<LPR_, CPL_><<<(unsigned)nblk, 256, 0, s>>>((const bf16*)x, half_w, center, kern, (bf16*)out, B, L, H, K, half);
   });
   chk("alc_fused_fwd");
 }
@@ -491,7 +537,7 @@ void alc_fused_bwd(const void* x, const float* half_w, const float* center, cons
     const int rpb = 256 / LPR_;
     const long long nblk = (long long)B * H * ((L + rpb - 1) / rpb);
     const size_t smem = (size_t)rpb * (K + 2 * half + 1) * sizeof(float);
-    auto kernel = alc_bwd_kernel<LPR_>;
+    auto kernel = alc_bwd_kernel<LPR_, CPL_>;
     opt_in_smem(kernel, smem);
     kernel<<<(unsigned)nblk, 256, smem, s>>>((const bf16*)x, half_w, center, kern, (const bf16*)dout, dx, dhalf_w, dcenter,
                                                                 dkern, B, L, H, K, half);
