@@ -72,8 +72,13 @@ class Heartbeat:
                 raise RankFailure(r, f"last heartbeat (step {st[1]}) is {st[2]:.1f}s old")
 
     def wait_all_at(self, step: int, poll: float = 0.05) -> None:
-        """Host-side rendezvous: return when every peer has published ``>= step``; raise on failure / timeout."""
+        """Host-side rendezvous: return when every peer has published ``>= step``; raise on failure / timeout.
+        A rank that waits here keeps refreshing its own heartbeat: waiting for a slow peer is not being dead."""
+        last = time.time()
         while True:
+            if time.time() - last > self.timeout / 4:
+                self.beat(step)
+                last = time.time()
             self.check()
             behind = [r for r in range(self.world_size) if r != self.rank and not (self.peer_state(r)[0] == "alive" and self.peer_state(r)[1] >= step)]
             if not behind:
