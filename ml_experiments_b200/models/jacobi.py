@@ -79,7 +79,9 @@ class MIMOJacobiSSM_ND(nn.Module):
         H = torch.zeros(x.shape[0], self.R, *x.shape[1:-1], self.N, device=x.device, dtype=x.dtype)
         return H, None
 
-    def _maps(self, x, it: int):
+    def _project(self, x):
+        """Everything ``_maps`` computes that does not depend on the iteration (the input does not change between
+        iterations, so the five projections are evaluated once per call instead of once per iteration)."""
         B, spatial = x.shape[0], tuple(x.shape[1:-1])
         nd = len(spatial)
         to_br = (0, nd + 2) + tuple(range(1, nd + 1)) + (nd + 1,)  # (B, *sp, N, R) -> (B, R, *sp, N)
@@ -87,16 +89,20 @@ class MIMOJacobiSSM_ND(nn.Module):
         Cm = self.act(self.to_C(x) + self.C_bias).view(B, *spatial, self.N, self.R).permute(*to_br)
         if self.bc_norm:
             Bm, Cm = self.b_norm(Bm), self.c_norm(Cm)
-        theta = (self.to_theta(x) * (it + 1)).unsqueeze(1)
-        Bm, Cm = _rotate_pairs(Bm, theta), _rotate_pairs(Cm, theta)
         xr = self.act(self.to_X(x)).movedim(-1, 1).unsqueeze(-1)  # (B, R, *sp, 1)
+        return Bm, Cm, self.to_theta(x).unsqueeze(1), xr, torch.sigmoid(self.to_decay(x)).unsqueeze(1), torch.sigmoid(self.to_lambda(x)).unsqueeze(1)
+
+    def _maps(self, x, it: int, proj=None):
+        Bm, Cm, theta, xr, alpha, gamma = self._project(x) if proj is None else proj
+        theta = theta * (it + 1)
+        Bm, Cm = _rotate_pairs(Bm, theta), _rotate_pairs(Cm, theta)
         if self.diff_inject:
             h = self.N // 2
             i1, i2 = Bm[..., :h] * xr, Bm[..., h:] * xr
             inject = torch.cat([i1 - self.inject_lambda * i2, i1 + self.inject_lambda * i2], dim=-1)
         else:
             inject = Bm * xr
-        return inject, torch.sigmoid(self.to_decay(x)).unsqueeze(1), torch.sigmoid(self.to_lambda(x)).unsqueeze(1), Cm
+        return inject, alpha, gamma, Cm
 
     def _diffuse_state(self, H):
         B, spatial = H.shape[0], tuple(H.shape[2:-1])
@@ -115,8 +121,8 @@ class MIMOJacobiSSM_ND(nn.Module):
             gated = Cm * H
         return self.act(self.out_proj(gated.movedim(1, -2).reshape(B, *spatial, self.R * self.N)))
 
-    def _iterate(self, x, H, prev, it: int):
-        inject, alpha, gamma, Cm = self._maps(x, it)
+    def _iterate(self, x, H, prev, it: int, proj=None):
+        inject, alpha, gamma, Cm = self._maps(x, it, proj)
         H = self._diffuse_state(H)
         H = alpha * H + inject if prev is None else alpha * H + (1.0 - gamma) * alpha * prev + gamma * inject
         return H, inject, Cm
@@ -129,9 +135,9 @@ class MIMOJacobiSSM_ND(nn.Module):
 
     def forward(self, x):
         H, prev = self.init_state(x)
-        Cm = None
+        Cm, proj = None, self._project(x)
         for it in range(self.n_iters):
-            H, prev, Cm = self._iterate(x, H, prev, it)
+            H, prev, Cm = self._iterate(x, H, prev, it, proj)
         return self._readout(H, Cm)
 
 
