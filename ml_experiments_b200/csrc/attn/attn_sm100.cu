@@ -330,9 +330,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint8_t* sdO = sQ + NQB * Q_BYTES;
   uint8_t* sPT = sdO + NQB * Q_BYTES;
   uint8_t* sdST = sPT + PT_BYTES;
-  float2* s_ld = reinterpret_cast<float2*>(sdST + PT_BYTES);  // [64] {lse, delta}
-  int* s_ds = reinterpret_cast<int*>(s_ld + BQ);                                          // [64]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_ds + BQ);
+  float2* s_ld_all = reinterpret_cast<float2*>(sdST + PT_BYTES);  // [2][64] {lse, delta}, double-buffered over query tiles
+  int* s_ds_all = reinterpret_cast<int*>(s_ld_all + 2 * BQ);      // [2][64] document start of each query
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_ds_all + 2 * BQ);
   uint64_t* bar_kv = bars;
   uint64_t* bar_q = bars + 1;  // [3]
   uint64_t* bar_m1 = bars + 4;   // S / dP of a tile are in TMEM
@@ -435,16 +435,28 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   }
 
+  // per-query scalars (lse, delta, document start) of the next tile are fetched one iteration ahead
+  float2 nxt_ld = make_float2(INFINITY, 0.f);
+  int nxt_ds = 0x7fffffff;
+  auto fetch_scalars = [&](int q0) {
+    const int qq = q0 + tid;
+    const bool okq = qq < p.T;
+    nxt_ld = make_float2(okq ? p.lse[(long long)h * p.T + qq] : INFINITY, okq ? p.delta[(long long)h * p.T + qq] : 0.f);
+    nxt_ds = okq ? p.doc_start[qq] : 0x7fffffff;
+  };
+  if (tid < BQ && ntile > 0) {
+    fetch_scalars(q_lo);
+    s_ld_all[tid] = nxt_ld;
+    s_ds_all[tid] = nxt_ds;
+  }
+
   for (int it = 0; it < ntile; ++it) {
     const int buf = it % NQB;
     const int qt0 = q_lo + it * BQ;
-    if (tid < BQ) {
-      const int qq = qt0 + tid;
-      const bool okq = qq < p.T;
-      s_ld[tid] = make_float2(okq ? p.lse[(long long)h * p.T + qq] : INFINITY, okq ? p.delta[(long long)h * p.T + qq] : 0.f);
-      s_ds[tid] = okq ? p.doc_start[qq] : 0x7fffffff;
-    }
-    __syncthreads();  // s_ld / s_ds visible
+    const float2* s_ld = s_ld_all + (it & 1) * BQ;
+    const int* s_ds = s_ds_all + (it & 1) * BQ;
+    if (tid < BQ && it + 1 < ntile) fetch_scalars(qt0 + BQ);  // loads stay in flight until the stores at the end of the iteration
+    __syncthreads();  // s_ld / s_ds of this tile visible (written in the prologue or at the end of the previous iteration)
     cta_wait(bar_m1, it & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
     tc_fence_after_sync();
     uint32_t sv[32], dv_[32];
@@ -531,6 +543,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
       for (int i = 0; i < 32; ++i)
         if (i < nq) atomicAdd(dst + (long long)i * p.ld_dq, __uint_as_float(v[i]) * p.scale);
+    }
+    if (tid < BQ && it + 1 < ntile) {
+      s_ld_all[((it + 1) & 1) * BQ + tid] = nxt_ld;
+      s_ds_all[((it + 1) & 1) * BQ + tid] = nxt_ds;
     }
     tc_fence_before_sync();
     __syncthreads();  // dQ columns of TMEM are free for the next tile
@@ -640,7 +656,7 @@ void fwd_impl(const AttnArgs& a) {
 template <int D>
 void bwd_impl(const AttnArgs& a) {
   constexpr int NS = D / 64;
-  const int smem = 2 * NS * 128 * 128 + 6 * NS * 64 * 128 + 2 * 128 * 128 + 3 * 64 * 4 + 96 + 1024;
+  const int smem = 2 * NS * 128 * 128 + 6 * NS * 64 * 128 + 2 * 128 * 128 + 6 * 64 * 4 + 96 + 1024;
   CUtensorMap tq = qkv_map(a.q, a.T, a.H, D, a.ld_q, 64);
   CUtensorMap tk = qkv_map(a.k, a.T, a.H, D, a.ld_k, 128);
   CUtensorMap tv = qkv_map(a.v, a.T, a.H, D, a.ld_v, 128);
