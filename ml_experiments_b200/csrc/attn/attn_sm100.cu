@@ -32,7 +32,6 @@ struct KP {
   __nv_bfloat16* o; long long ld_o;
   __nv_bfloat16* dk; long long ld_dk;
   __nv_bfloat16* dv; long long ld_dv;
-  float* dq; long long ld_dq;  // fp32 accumulator [T][ld_dq], head h at column h * D
   float* lse;
   const float* delta;
   int* status;
@@ -318,6 +317,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   constexpr int KV_BYTES = NS * BKV * 128;  // K or V tile
   constexpr int Q_BYTES = NS * BQ * 128;    // Q or dO tile
   constexpr int PT_BYTES = BKV * 128;       // Pᵀ or dSᵀ: 128 key rows x 64 queries
+  constexpr int DQ_BYTES = BQ * D * 4;      // fp32 staging of one dQ tile
   constexpr uint32_t ST_COL = 0, DPT_COL = 64, DV_COL = 128, DK_COL = 128 + D, DQT_COL = 128 + 2 * D;
   constexpr uint32_t TMEM_COLS = (128 + 2 * D + 64) <= 256 ? 256 : 512;
 
@@ -330,7 +330,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint8_t* sdO = sQ + NQB * Q_BYTES;
   uint8_t* sPT = sdO + NQB * Q_BYTES;
   uint8_t* sdST = sPT + PT_BYTES;
-  float2* s_ld_all = reinterpret_cast<float2*>(sdST + PT_BYTES);  // [2][64] {lse, delta}, double-buffered over query tiles
+  float* sdQ = reinterpret_cast<float*>(sdST + PT_BYTES);
+  float2* s_ld_all = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(sdQ) + DQ_BYTES);  // [2][64] {lse, delta}, double-buffered over query tiles
   int* s_ds_all = reinterpret_cast<int*>(s_ld_all + 2 * BQ);      // [2][64] document start of each query
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_ds_all + 2 * BQ);
   uint64_t* bar_kv = bars;
@@ -509,6 +510,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_after_sync();
       const uint32_t pa = smem_u32(sPT), dsa = smem_u32(sdST), ka = smem_u32(sK);
       const uint32_t qa = smem_u32(sQ + buf * Q_BYTES), doa = smem_u32(sdO + buf * Q_BYTES);
+      tma_store_wait_read<0>();  // previous tile's reduce-add has drained the dQ staging buffer
 #pragma unroll
       for (int ks = 0; ks < BKV / 16; ++ks) {  // dQᵀ = Kᵀ · dSᵀ
         const uint64_t ad = make_smem_desc_sw128(ka + ks * 2048, BKV * 128, 1024);
@@ -532,24 +534,26 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
     cta_wait(bar_dq, it & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
     tc_fence_after_sync();
-    // dQᵀ row (= head-dim index r), this warp's half of the query columns: one fire-and-forget reduction per element,
-    // a warp covering 32 consecutive floats (128 bytes) of one query row of the fp32 accumulator
+    // dQᵀ row (= head-dim index r), this warp's half of the query columns -> staging[q][r], then one bulk reduce-add
+    // into the fp32 accumulator (reductions issued element by element from registers measured 25 % slower)
     if (r < D) {
       uint32_t v[32];
       tmem_ld_32x32b_x32(tmem_base + lane_off + DQT_COL + half * 32, v);
       tmem_ld_wait();
-      float* dst = p.dq + (long long)(qt0 + half * 32) * p.ld_dq + h * D + r;
-      const int nq = min(32, p.T - (qt0 + half * 32));
 #pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (i < nq) atomicAdd(dst + (long long)i * p.ld_dq, __uint_as_float(v[i]) * p.scale);
+      for (int i = 0; i < 32; ++i) sdQ[(half * 32 + i) * D + r] = __uint_as_float(v[i]) * p.scale;
     }
+    fence_proxy_async_smem();
     if (tid < BQ && it + 1 < ntile) {
       s_ld_all[((it + 1) & 1) * BQ + tid] = nxt_ld;
       s_ds_all[((it + 1) & 1) * BQ + tid] = nxt_ds;
     }
     tc_fence_before_sync();
-    __syncthreads();  // dQ columns of TMEM are free for the next tile
+    __syncthreads();  // dQ columns of TMEM are free for the next tile; the staged dQ tile is complete
+    if (tid == 0) {
+      tma_reduce_add_3d(&tmdQ, sdQ, 0, qt0, h);
+      tma_store_commit();
+    }
   }
 
   // final: dV, dK rows; each warp writes its half of the head dimension
@@ -588,6 +592,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   }
   if (tid == 0) {
+    tma_store_wait_all<0>();
     if (*abort_flag) {
       const uint64_t t0 = globaltimer_ns();
       while (globaltimer_ns() - t0 < 1000000ull) __nanosleep(1000);
@@ -614,7 +619,6 @@ KP make_kp(const AttnArgs& a) {
   p.o = reinterpret_cast<__nv_bfloat16*>(a.o); p.ld_o = a.ld_o;
   p.dk = reinterpret_cast<__nv_bfloat16*>(a.dk); p.ld_dk = a.ld_dk;
   p.dv = reinterpret_cast<__nv_bfloat16*>(a.dv); p.ld_dv = a.ld_dv;
-  p.dq = reinterpret_cast<float*>(a.dq_acc); p.ld_dq = a.ld_dq;
   p.lse = a.lse; p.delta = a.delta;
   p.status = a.status;
   return p;
@@ -656,7 +660,7 @@ void fwd_impl(const AttnArgs& a) {
 template <int D>
 void bwd_impl(const AttnArgs& a) {
   constexpr int NS = D / 64;
-  const int smem = 2 * NS * 128 * 128 + 6 * NS * 64 * 128 + 2 * 128 * 128 + 6 * 64 * 4 + 96 + 1024;
+  const int smem = 2 * NS * 128 * 128 + 6 * NS * 64 * 128 + 2 * 128 * 128 + 64 * D * 4 + 6 * 64 * 4 + 96 + 1024;
   CUtensorMap tq = qkv_map(a.q, a.T, a.H, D, a.ld_q, 64);
   CUtensorMap tk = qkv_map(a.k, a.T, a.H, D, a.ld_k, 128);
   CUtensorMap tv = qkv_map(a.v, a.T, a.H, D, a.ld_v, 128);
