@@ -95,7 +95,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
     if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   for (;;) {
-    for (int i = 0; i < 128; ++i)
+    // the status word lives in global memory: polling it every few tries showed up as long-scoreboard and
+    // load/store-throttle stalls in every thread that waits (attention backward), so it is looked at rarely
+    for (int i = 0; i < 2048; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     // another CTA (or an earlier kernel) already gave up: do not spend a full time-out per CTA
     if (status && *reinterpret_cast<volatile int*>(status) != 0) return false;
