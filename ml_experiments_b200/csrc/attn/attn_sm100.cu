@@ -353,6 +353,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int h = blockIdx.y;
   const int kv0 = jb * BKV;
   const int kv = kv0 + r;
+  // The single-thread issue work is spread over four warps so that no warp carries all of it on top of its share of the
+  // exponentials: S / dP products, the products that follow the exponentials, the dQ bulk reductions, the Q / dO loads.
+  const bool issue_sdp = tid == 0, issue_grad = tid == 32, issue_red = tid == 64, issue_load = tid == 96;
 
   if (tid == 0) {
     mbar_init(bar_kv, 1);
@@ -466,7 +469,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     tmem_ld_wait();
     tc_fence_before_sync();
     __syncthreads();  // every thread holds its S / dP values: the TMEM columns may be overwritten
-    if (tid == 0 && it + 1 < ntile) {
+    if (issue_sdp && it + 1 < ntile) {
       cta_wait(&bar_q[(it + 1) % NQB], ((it + 1) / NQB) & 1, abort_flag, p.status, ERR_WAIT_SMEM_FULL);
       tc_fence_after_sync();
       issue_s_dp((it + 1) % NQB);
@@ -474,7 +477,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (it > 0) {  // dV / dK of the previous tile: frees the P / dS staging and that tile's Q / dO buffer
       cta_wait(bar_m2, (it - 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
       tc_fence_after_sync();
-      if (tid == 0 && it + 2 < ntile) load_q_do((it + 2) % NQB, qt0 + 2 * BQ);
+      if (issue_load && it + 2 < ntile) load_q_do((it + 2) % NQB, qt0 + 2 * BQ);
     }
 
     // masks are needed only where the tile touches the causal diagonal, a document boundary or the sequence end
@@ -503,14 +506,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         *reinterpret_cast<uint4*>(drow + (((half * 4 + j) ^ (r & 7)) << 4)) = make_uint4(dd[4 * j], dd[4 * j + 1], dd[4 * j + 2], dd[4 * j + 3]);
       }
     }
+    if (issue_red) tma_store_wait_read<0>();  // the previous tile's reduce-add has drained the dQ staging buffer; the barrier
+                                              // below orders this before every thread's staging stores of this tile
     fence_proxy_async_smem();
     tc_fence_before_sync();
     __syncthreads();
-    if (tid == 0) {
+    if (issue_grad) {
       tc_fence_after_sync();
       const uint32_t pa = smem_u32(sPT), dsa = smem_u32(sdST), ka = smem_u32(sK);
       const uint32_t qa = smem_u32(sQ + buf * Q_BYTES), doa = smem_u32(sdO + buf * Q_BYTES);
-      tma_store_wait_read<0>();  // previous tile's reduce-add has drained the dQ staging buffer
 #pragma unroll
       for (int ks = 0; ks < BKV / 16; ++ks) {  // dQᵀ = Kᵀ · dSᵀ
         const uint64_t ad = make_smem_desc_sw128(ka + ks * 2048, BKV * 128, 1024);
@@ -550,7 +554,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
     tc_fence_before_sync();
     __syncthreads();  // dQ columns of TMEM are free for the next tile; the staged dQ tile is complete
-    if (tid == 0) {
+    if (issue_red) {
       tma_reduce_add_3d(&tmdQ, sdQ, 0, qt0, h);
       tma_store_commit();
     }
@@ -591,8 +595,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
     }
   }
+  if (issue_red) tma_store_wait_all<0>();
   if (tid == 0) {
-    tma_store_wait_all<0>();
     if (*abort_flag) {
       const uint64_t t0 = globaltimer_ns();
       while (globaltimer_ns() - t0 < 1000000ull) __nanosleep(1000);
