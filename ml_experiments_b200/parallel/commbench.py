@@ -84,11 +84,25 @@ def bench_allreduce(w: SymmWorld, sizes_mb, iters, warmup, link_gbs, emit, use_n
             t_f, t_n = _timed(fused, iters, warmup, dev), _timed(nccl, iters, warmup, dev)
             t_m = _timed(nvls, iters, warmup, dev) if (use_nvls and buf.mc_ptr) else None
             check_status()
+
+            def max_err(fn):  # every rank contributes rank + 1 + i / n: the mean is known in closed form
+                ramp = torch.arange(n, device=dev, dtype=torch.float32) / n
+                buf.local.copy_((ramp + w.rank + 1).to(dtype))
+                dist.barrier()
+                fn()
+                torch.cuda.synchronize(dev)
+                err = (buf.local.float() - (ramp + (W + 1) / 2)).abs().max()
+                dist.all_reduce(err, op=dist.ReduceOp.MAX)
+                dist.barrier()
+                return round(float(err), 5)
+
+            err_f = max_err(fused)
+            err_m = max_err(nvls) if t_m is not None else None
             per_dir = (W - 1) / W * n * esize
             roof_ms = per_dir / (link_gbs * 1e6)
             emit(dict(bench="allreduce", dtype=str(dtype).split(".")[-1], mbytes=round(n * esize / 2 ** 20, 1), world=W, fused_ms=round(t_f, 4),
                       nccl_ms=round(t_n, 4), fused_busbw_gbs=round(2 * per_dir / t_f / 1e6, 1), nccl_busbw_gbs=round(2 * per_dir / t_n / 1e6, 1),
-                      multimem_ms=None if t_m is None else round(t_m, 4), multimem_frac_of_roofline=None if t_m is None else round(roof_ms / t_m, 3),
+                      fused_max_err=err_f, multimem_max_err=err_m, multimem_ms=None if t_m is None else round(t_m, 4), multimem_frac_of_roofline=None if t_m is None else round(roof_ms / t_m, 3),
                       roofline_ms=round(roof_ms, 4), fused_frac_of_roofline=round(roof_ms / t_f, 3), link_gbs=link_gbs))
 
 
