@@ -339,7 +339,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* bar_m1 = bars + 4;   // S / dP of a tile are in TMEM
   uint64_t* bar_m2 = bars + 5;   // dV / dK of a tile are accumulated: its P / dS staging and its Q / dO buffer are free
   uint64_t* bar_dq = bars + 6;   // dQ of a tile is in TMEM
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+  uint64_t* bar_sread = bars + 7;   // every warp has copied S / dP of a tile out of TMEM (one arrival per warp)
+  uint64_t* bar_pready = bars + 8;  // every warp has written its P / dS rows of a tile to shared memory
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   if (status_poisoned(p.status)) return;
@@ -365,6 +367,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     mbar_init(bar_m1, 1);
     mbar_init(bar_m2, 1);
     mbar_init(bar_dq, 1);
+    mbar_init(bar_sread, 8);
+    mbar_init(bar_pready, 8);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -454,13 +458,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     s_ds_all[tid] = nxt_ds;
   }
 
+  __syncthreads();  // first tile's scalars visible
+  // Warps meet at one CTA barrier per tile (after the dQ staging). "S / dP copied out" and "P / dS written" are mbarriers
+  // with one arrival per warp that only the issuing thread waits for, so the other warps run on.
   for (int it = 0; it < ntile; ++it) {
     const int buf = it % NQB;
     const int qt0 = q_lo + it * BQ;
     const float2* s_ld = s_ld_all + (it & 1) * BQ;
     const int* s_ds = s_ds_all + (it & 1) * BQ;
     if (tid < BQ && it + 1 < ntile) fetch_scalars(qt0 + BQ);  // loads stay in flight until the stores at the end of the iteration
-    __syncthreads();  // s_ld / s_ds of this tile visible (written in the prologue or at the end of the previous iteration)
     cta_wait(bar_m1, it & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
     tc_fence_after_sync();
     uint32_t sv[32], dv_[32];
@@ -468,8 +474,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     tmem_ld_32x32b_x32(tmem_base + lane_off + DPT_COL + half * 32, dv_);
     tmem_ld_wait();
     tc_fence_before_sync();
-    __syncthreads();  // every thread holds its S / dP values: the TMEM columns may be overwritten
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar_sread);
     if (issue_sdp && it + 1 < ntile) {
+      cta_wait(bar_sread, it & 1, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY);  // the TMEM columns may be overwritten
       cta_wait(&bar_q[(it + 1) % NQB], ((it + 1) / NQB) & 1, abort_flag, p.status, ERR_WAIT_SMEM_FULL);
       tc_fence_after_sync();
       issue_s_dp((it + 1) % NQB);
@@ -506,12 +514,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         *reinterpret_cast<uint4*>(drow + (((half * 4 + j) ^ (r & 7)) << 4)) = make_uint4(dd[4 * j], dd[4 * j + 1], dd[4 * j + 2], dd[4 * j + 3]);
       }
     }
-    if (issue_red) tma_store_wait_read<0>();  // the previous tile's reduce-add has drained the dQ staging buffer; the barrier
-                                              // below orders this before every thread's staging stores of this tile
+    if (issue_red) tma_store_wait_read<0>();  // the previous tile's reduce-add has drained the dQ staging buffer; this warp's
+                                              // arrival below -> the dQ product's commit -> every thread's dQ wait orders it
+                                              // before the staging stores of this tile
     fence_proxy_async_smem();
-    tc_fence_before_sync();
-    __syncthreads();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar_pready);
     if (issue_grad) {
+      cta_wait(bar_pready, it & 1, abort_flag, p.status, ERR_WAIT_SMEM_FULL);
       tc_fence_after_sync();
       const uint32_t pa = smem_u32(sPT), dsa = smem_u32(sdST), ka = smem_u32(sK);
       const uint32_t qa = smem_u32(sQ + buf * Q_BYTES), doa = smem_u32(sdO + buf * Q_BYTES);
