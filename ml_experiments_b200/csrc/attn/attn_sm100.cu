@@ -319,7 +319,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   constexpr int PT_BYTES = BKV * 128;       // Pᵀ or dSᵀ: 128 key rows x 64 queries
   constexpr int DQ_BYTES = BQ * D * 4;      // fp32 staging of one dQ tile
   constexpr uint32_t ST_COL = 0, DPT_COL = 64, DV_COL = 128, DK_COL = 128 + D, DQT_COL = 128 + 2 * D;
-  constexpr uint32_t TMEM_COLS = (128 + 2 * D + 64) <= 256 ? 256 : 512;
+  constexpr uint32_t TMEM_COLS = 512;  // S 64 + dP 64 + dV D + dK D + two dQ buffers of 64: 512 at D = 128
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -452,6 +452,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     nxt_ld = make_float2(okq ? p.lse[(long long)h * p.T + qq] : INFINITY, okq ? p.delta[(long long)h * p.T + qq] : 0.f);
     nxt_ds = okq ? p.doc_start[qq] : 0x7fffffff;
   };
+  // dQᵀ row (= head-dim index r), this warp's half of the query columns -> staging[q][r] for one bulk reduce-add into
+  // the fp32 accumulator (reductions issued element by element from registers measured 25 % slower)
+  auto stage_dq = [&](int which) {
+    if (r < D) {
+      uint32_t v[32];
+      tmem_ld_32x32b_x32(tmem_base + lane_off + DQT_COL + which * 64 + half * 32, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) sdQ[(half * 32 + i) * D + r] = __uint_as_float(v[i]) * p.scale;
+    }
+    fence_proxy_async_smem();
+  };
   if (tid < BQ && ntile > 0) {
     fetch_scalars(q_lo);
     s_ld_all[tid] = nxt_ld;
@@ -514,9 +526,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         *reinterpret_cast<uint4*>(drow + (((half * 4 + j) ^ (r & 7)) << 4)) = make_uint4(dd[4 * j], dd[4 * j + 1], dd[4 * j + 2], dd[4 * j + 3]);
       }
     }
-    if (issue_red) tma_store_wait_read<0>();  // the previous tile's reduce-add has drained the dQ staging buffer; this warp's
-                                              // arrival below -> the dQ product's commit -> every thread's dQ wait orders it
-                                              // before the staging stores of this tile
+    // dQ of the previous tile was issued one iteration ago: waiting for it here (before this warp's arrival below lets
+    // the next dQ product be issued) keeps every waiter inside the phase it waits for
+    if (it > 0) cta_wait(bar_dq, (it - 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
     fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0) mbar_arrive(bar_pready);
@@ -526,10 +538,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint32_t pa = smem_u32(sPT), dsa = smem_u32(sdST), ka = smem_u32(sK);
       const uint32_t qa = smem_u32(sQ + buf * Q_BYTES), doa = smem_u32(sdO + buf * Q_BYTES);
 #pragma unroll
-      for (int ks = 0; ks < BKV / 16; ++ks) {  // dQᵀ = Kᵀ · dSᵀ
+      for (int ks = 0; ks < BKV / 16; ++ks) {  // dQᵀ = Kᵀ · dSᵀ, into the dQ buffer of this tile's parity
         const uint64_t ad = make_smem_desc_sw128(ka + ks * 2048, BKV * 128, 1024);
         const uint64_t bd = make_smem_desc_sw128(dsa + ks * 2048, BKV * 128, 1024);
-        tc_mma_f16(tmem_base + DQT_COL, ad, bd, idesc_dq, ks != 0);
+        tc_mma_f16(tmem_base + DQT_COL + (it & 1) * 64, ad, bd, idesc_dq, ks != 0);
       }
       tc_commit(bar_dq);
 #pragma unroll
@@ -546,26 +558,32 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       tc_commit(bar_m2);
     }
-    cta_wait(bar_dq, it & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
+    // While this tile's dQ / dV / dK products run, dQ of the PREVIOUS tile leaves through the staging buffer.
+    if (issue_red) tma_store_wait_read<0>();  // the reduce-add issued one iteration ago has drained the staging buffer
     tc_fence_after_sync();
-    // dQᵀ row (= head-dim index r), this warp's half of the query columns -> staging[q][r], then one bulk reduce-add
-    // into the fp32 accumulator (reductions issued element by element from registers measured 25 % slower)
-    if (r < D) {
-      uint32_t v[32];
-      tmem_ld_32x32b_x32(tmem_base + lane_off + DQT_COL + half * 32, v);
-      tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 32; ++i) sdQ[(half * 32 + i) * D + r] = __uint_as_float(v[i]) * p.scale;
-    }
-    fence_proxy_async_smem();
+    __syncthreads();
+    if (it > 0) stage_dq((it - 1) & 1);
     if (tid < BQ && it + 1 < ntile) {
       s_ld_all[((it + 1) & 1) * BQ + tid] = nxt_ld;
       s_ds_all[((it + 1) & 1) * BQ + tid] = nxt_ds;
     }
     tc_fence_before_sync();
-    __syncthreads();  // dQ columns of TMEM are free for the next tile; the staged dQ tile is complete
+    __syncthreads();  // staged dQ tile complete; its TMEM buffer is free; next tile's scalars visible
+    if (issue_red && it > 0) {
+      tma_reduce_add_3d(&tmdQ, sdQ, 0, qt0 - BQ, h);
+      tma_store_commit();
+    }
+  }
+  if (ntile > 0) {  // dQ of the last tile
+    cta_wait(bar_dq, (ntile - 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
+    if (issue_red) tma_store_wait_read<0>();
+    tc_fence_after_sync();
+    __syncthreads();
+    stage_dq((ntile - 1) & 1);
+    tc_fence_before_sync();
+    __syncthreads();
     if (issue_red) {
-      tma_reduce_add_3d(&tmdQ, sdQ, 0, qt0, h);
+      tma_reduce_add_3d(&tmdQ, sdQ, 0, q_lo + (ntile - 1) * BQ, h);
       tma_store_commit();
     }
   }
