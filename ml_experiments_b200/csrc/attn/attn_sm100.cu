@@ -319,7 +319,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   constexpr int PT_BYTES = BKV * 128;       // Pᵀ or dSᵀ: 128 key rows x 64 queries
   constexpr int DQ_BYTES = BQ * D * 4;      // fp32 staging of one dQ tile
   constexpr uint32_t ST_COL = 0, DPT_COL = 64, DV_COL = 128, DK_COL = 128 + D, DQT_COL = 128 + 2 * D;
-  constexpr uint32_t TMEM_COLS = 512;  // S 64 + dP 64 + dV D + dK D + two dQ buffers of 64: 512 at D = 128
+  constexpr uint32_t TMEM_COLS = (128 + 2 * D + 64) <= 256 ? 256 : 512;
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -339,9 +339,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* bar_m1 = bars + 4;   // S / dP of a tile are in TMEM
   uint64_t* bar_m2 = bars + 5;   // dV / dK of a tile are accumulated: its P / dS staging and its Q / dO buffer are free
   uint64_t* bar_dq = bars + 6;   // dQ of a tile is in TMEM
-  uint64_t* bar_sread = bars + 7;   // every warp has copied S / dP of a tile out of TMEM (one arrival per warp)
-  uint64_t* bar_pready = bars + 8;  // every warp has written its P / dS rows of a tile to shared memory
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   if (status_poisoned(p.status)) return;
@@ -367,8 +365,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     mbar_init(bar_m1, 1);
     mbar_init(bar_m2, 1);
     mbar_init(bar_dq, 1);
-    mbar_init(bar_sread, 8);
-    mbar_init(bar_pready, 8);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -452,33 +448,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     nxt_ld = make_float2(okq ? p.lse[(long long)h * p.T + qq] : INFINITY, okq ? p.delta[(long long)h * p.T + qq] : 0.f);
     nxt_ds = okq ? p.doc_start[qq] : 0x7fffffff;
   };
-  // dQᵀ row (= head-dim index r), this warp's half of the query columns -> staging[q][r] for one bulk reduce-add into
-  // the fp32 accumulator (reductions issued element by element from registers measured 25 % slower)
-  auto stage_dq = [&](int which) {
-    if (r < D) {
-      uint32_t v[32];
-      tmem_ld_32x32b_x32(tmem_base + lane_off + DQT_COL + which * 64 + half * 32, v);
-      tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 32; ++i) sdQ[(half * 32 + i) * D + r] = __uint_as_float(v[i]) * p.scale;
-    }
-    fence_proxy_async_smem();
-  };
   if (tid < BQ && ntile > 0) {
     fetch_scalars(q_lo);
     s_ld_all[tid] = nxt_ld;
     s_ds_all[tid] = nxt_ds;
   }
 
-  __syncthreads();  // first tile's scalars visible
-  // Warps meet at one CTA barrier per tile (after the dQ staging). "S / dP copied out" and "P / dS written" are mbarriers
-  // with one arrival per warp that only the issuing thread waits for, so the other warps run on.
   for (int it = 0; it < ntile; ++it) {
     const int buf = it % NQB;
     const int qt0 = q_lo + it * BQ;
     const float2* s_ld = s_ld_all + (it & 1) * BQ;
     const int* s_ds = s_ds_all + (it & 1) * BQ;
     if (tid < BQ && it + 1 < ntile) fetch_scalars(qt0 + BQ);  // loads stay in flight until the stores at the end of the iteration
+    __syncthreads();  // s_ld / s_ds of this tile visible (written in the prologue or at the end of the previous iteration)
     cta_wait(bar_m1, it & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
     tc_fence_after_sync();
     uint32_t sv[32], dv_[32];
@@ -486,10 +468,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     tmem_ld_32x32b_x32(tmem_base + lane_off + DPT_COL + half * 32, dv_);
     tmem_ld_wait();
     tc_fence_before_sync();
-    __syncwarp();
-    if (lane == 0) mbar_arrive(bar_sread);
+    __syncthreads();  // every thread holds its S / dP values: the TMEM columns may be overwritten
     if (issue_sdp && it + 1 < ntile) {
-      cta_wait(bar_sread, it & 1, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY);  // the TMEM columns may be overwritten
       cta_wait(&bar_q[(it + 1) % NQB], ((it + 1) / NQB) & 1, abort_flag, p.status, ERR_WAIT_SMEM_FULL);
       tc_fence_after_sync();
       issue_s_dp((it + 1) % NQB);
@@ -526,22 +506,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         *reinterpret_cast<uint4*>(drow + (((half * 4 + j) ^ (r & 7)) << 4)) = make_uint4(dd[4 * j], dd[4 * j + 1], dd[4 * j + 2], dd[4 * j + 3]);
       }
     }
-    // dQ of the previous tile was issued one iteration ago: waiting for it here (before this warp's arrival below lets
-    // the next dQ product be issued) keeps every waiter inside the phase it waits for
-    if (it > 0) cta_wait(bar_dq, (it - 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
+    if (issue_red) tma_store_wait_read<0>();  // the previous tile's reduce-add has drained the dQ staging buffer; the barrier
+                                              // below orders this before every thread's staging stores of this tile
     fence_proxy_async_smem();
-    __syncwarp();
-    if (lane == 0) mbar_arrive(bar_pready);
+    tc_fence_before_sync();
+    __syncthreads();
     if (issue_grad) {
-      cta_wait(bar_pready, it & 1, abort_flag, p.status, ERR_WAIT_SMEM_FULL);
       tc_fence_after_sync();
       const uint32_t pa = smem_u32(sPT), dsa = smem_u32(sdST), ka = smem_u32(sK);
       const uint32_t qa = smem_u32(sQ + buf * Q_BYTES), doa = smem_u32(sdO + buf * Q_BYTES);
 #pragma unroll
-      for (int ks = 0; ks < BKV / 16; ++ks) {  // dQᵀ = Kᵀ · dSᵀ, into the dQ buffer of this tile's parity
+      for (int ks = 0; ks < BKV / 16; ++ks) {  // dQᵀ = Kᵀ · dSᵀ
         const uint64_t ad = make_smem_desc_sw128(ka + ks * 2048, BKV * 128, 1024);
         const uint64_t bd = make_smem_desc_sw128(dsa + ks * 2048, BKV * 128, 1024);
-        tc_mma_f16(tmem_base + DQT_COL + (it & 1) * 64, ad, bd, idesc_dq, ks != 0);
+        tc_mma_f16(tmem_base + DQT_COL, ad, bd, idesc_dq, ks != 0);
       }
       tc_commit(bar_dq);
 #pragma unroll
@@ -558,32 +536,26 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       tc_commit(bar_m2);
     }
-    // While this tile's dQ / dV / dK products run, dQ of the PREVIOUS tile leaves through the staging buffer.
-    if (issue_red) tma_store_wait_read<0>();  // the reduce-add issued one iteration ago has drained the staging buffer
+    cta_wait(bar_dq, it & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
     tc_fence_after_sync();
-    __syncthreads();
-    if (it > 0) stage_dq((it - 1) & 1);
+    // dQᵀ row (= head-dim index r), this warp's half of the query columns -> staging[q][r], then one bulk reduce-add
+    // into the fp32 accumulator (reductions issued element by element from registers measured 25 % slower)
+    if (r < D) {
+      uint32_t v[32];
+      tmem_ld_32x32b_x32(tmem_base + lane_off + DQT_COL + half * 32, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) sdQ[(half * 32 + i) * D + r] = __uint_as_float(v[i]) * p.scale;
+    }
+    fence_proxy_async_smem();
     if (tid < BQ && it + 1 < ntile) {
       s_ld_all[((it + 1) & 1) * BQ + tid] = nxt_ld;
       s_ds_all[((it + 1) & 1) * BQ + tid] = nxt_ds;
     }
     tc_fence_before_sync();
-    __syncthreads();  // staged dQ tile complete; its TMEM buffer is free; next tile's scalars visible
-    if (issue_red && it > 0) {
-      tma_reduce_add_3d(&tmdQ, sdQ, 0, qt0 - BQ, h);
-      tma_store_commit();
-    }
-  }
-  if (ntile > 0) {  // dQ of the last tile
-    cta_wait(bar_dq, (ntile - 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
-    if (issue_red) tma_store_wait_read<0>();
-    tc_fence_after_sync();
-    __syncthreads();
-    stage_dq((ntile - 1) & 1);
-    tc_fence_before_sync();
-    __syncthreads();
+    __syncthreads();  // dQ columns of TMEM are free for the next tile; the staged dQ tile is complete
     if (issue_red) {
-      tma_reduce_add_3d(&tmdQ, sdQ, 0, q_lo + (ntile - 1) * BQ, h);
+      tma_reduce_add_3d(&tmdQ, sdQ, 0, qt0, h);
       tma_store_commit();
     }
   }
