@@ -83,3 +83,21 @@ def test_pathfinder_generator_and_pathx_trainers(tmp_path):
     train_pathx.main(common + ["--epochs", "2", "--mode", "2d", "--output", str(tmp_path / "o2")])
     s2 = train_pathx.main(common + ["--epochs", "2", "--mode", "2d", "--output", str(tmp_path / "o2"), "--resume", str(tmp_path / "o2" / "epoch001.pt")])
     assert len(s2["history"]) == 2 and s2["history"][0]["epoch"] == 1     # the second epoch was run again from the first one's checkpoint
+
+
+def test_pipeline_evaluation_and_feature_subset_search(tmp_path):
+    from ml_experiments_b200.cli import evaluate_pipeline, heuristic_search
+    from ml_experiments_b200.heuristic_secrets.io import save_model_bundle
+    from ml_experiments_b200.heuristic_secrets.pipeline.detector import DetectorConfig
+    from ml_experiments_b200.heuristic_secrets.spanfinder.model import SpanFinderConfig, SpanFinderModel
+    from ml_experiments_b200.heuristic_secrets.validator.features import FrequencyTable
+    from ml_experiments_b200.heuristic_secrets.validator.model import ValidatorConfig, ValidatorModel
+
+    assert evaluate_pipeline.match_spans([(0, 10), (50, 60)], [(1, 10), (100, 120)]) == (1, 1, 1)
+    save_model_bundle(tmp_path / "b", SpanFinderModel(SpanFinderConfig.tiny()), ValidatorModel(ValidatorConfig()), DetectorConfig(),
+                      {k: FrequencyTable({65: 1.0}) for k in ("text", "innocuous", "secret")})
+    out = evaluate_pipeline.main(["--bundle", str(tmp_path / "b"), "--synthetic", "6"])
+    assert out["documents"] == 6 and 0.0 <= out["f1"] <= 1.0 and out["bytes_per_second"] > 0
+    assert len(list(heuristic_search.subsets(6))) == 63
+    res = heuristic_search.main(["--synthetic", "60", "--epochs", "1", "--max-size", "1", "--device", "cpu"])
+    assert len(res) == 6 and res[0]["f1"] >= res[-1]["f1"]
