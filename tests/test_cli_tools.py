@@ -101,3 +101,13 @@ def test_pipeline_evaluation_and_feature_subset_search(tmp_path):
     assert len(list(heuristic_search.subsets(6))) == 63
     res = heuristic_search.main(["--synthetic", "60", "--epochs", "1", "--max-size", "1", "--device", "cpu"])
     assert len(res) == 6 and res[0]["f1"] >= res[-1]["f1"]
+
+
+def test_checkpoint_ensemble_evaluation(tmp_path):
+    from ml_experiments_b200.cli import eval_checkpoints, train_line_filter
+
+    train_line_filter.main(["--synthetic", "96", "--arch", "conv", "--embed-width", "16", "--output", str(tmp_path), "--device", "cpu",
+                            "--batch-size", "32", "--epochs", "2", "--no-swa"])
+    rows, summary = eval_checkpoints.main(["--checkpoints", str(tmp_path / "epoch00*.pt"), "--synthetic", "48", "--device", "cpu"])
+    assert len(rows) == 2 and summary["ensemble"]["members"] == 2
+    assert summary["mean_disagreement"] == summary["mean_disagreement"] and 0.0 <= summary["ensemble"]["f1"] <= 1.0
