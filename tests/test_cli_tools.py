@@ -111,3 +111,13 @@ def test_checkpoint_ensemble_evaluation(tmp_path):
     rows, summary = eval_checkpoints.main(["--checkpoints", str(tmp_path / "epoch00*.pt"), "--synthetic", "48", "--device", "cpu"])
     assert len(rows) == 2 and summary["ensemble"]["members"] == 2
     assert summary["mean_disagreement"] == summary["mean_disagreement"] and 0.0 <= summary["ensemble"]["f1"] <= 1.0
+
+
+def test_bytemasker_and_joint_trainer_tool(tmp_path):
+    from ml_experiments_b200.cli import train_bytemasker
+
+    s = train_bytemasker.main(["--synthetic", "64", "--epochs", "1", "--width", "16", "--depth", "2", "--output", str(tmp_path / "bm.pt"), "--device", "cpu"])
+    assert s["kind"] == "bytemasker" and (tmp_path / "bm.pt").exists() and 0.0 <= s["clean_fp_rate"] <= 1.0
+    j = train_bytemasker.main(["--joint", "--synthetic", "64", "--epochs", "1", "--width", "16", "--depth", "2", "--output", str(tmp_path / "j.pt"),
+                               "--device", "cpu"])
+    assert j["kind"] == "joint" and (tmp_path / "j.pt").exists()
