@@ -21,6 +21,8 @@ class Ensemble(nn.Module):
         self.config, self.n_members = config, n_members
         self.models = nn.ModuleList([Model(config) for _ in range(n_members)])
         self._stacked = None
+        self._loop = False
+        self._streams = None
 
     def train(self, mode: bool = True):
         self._stacked = None
@@ -35,8 +37,29 @@ class Ensemble(nn.Module):
         def one(p, b, x, mask, precomputed):
             return functional_call(template, (p, b), (x, mask, precomputed))[0]
 
-        logits = torch.vmap(one, in_dims=(0, 0, None, None, None), randomness="different")(params, buffers, x, mask, precomputed)
-        return torch.sigmoid(logits)
+        if not self._loop:
+            try:
+                logits = torch.vmap(one, in_dims=(0, 0, None, None, None), randomness="different")(params, buffers, x, mask, precomputed)
+                return torch.sigmoid(logits)
+            except (RuntimeError, NotImplementedError):
+                # a hand-written CUDA op without a batching rule: run the members one after another on side streams
+                self._loop = True
+        return torch.sigmoid(self._member_logits_loop(x, mask, precomputed))
+
+    def _member_logits_loop(self, x, mask, precomputed):
+        if not x.is_cuda:
+            return torch.stack([m(x, mask, precomputed)[0] for m in self.models])
+        cur = torch.cuda.current_stream(x.device)
+        if self._streams is None or len(self._streams) != self.n_members:
+            self._streams = [torch.cuda.Stream(x.device) for _ in range(self.n_members)]
+        outs = []
+        for m, st in zip(self.models, self._streams):
+            st.wait_stream(cur)
+            with torch.cuda.stream(st):
+                outs.append(m(x, mask, precomputed)[0])
+        for st in self._streams:
+            cur.wait_stream(st)
+        return torch.stack(outs)
 
     def forward(self, x, mask=None, precomputed=None):
         return self._member_probs(x, mask, precomputed).mean(dim=0)
