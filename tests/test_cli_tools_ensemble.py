@@ -70,3 +70,23 @@ def test_inspect_kernels_reports_every_adaptive_branch(tmp_path, capsys):
     shares = [v["share"] for v in summary.values()]
     assert abs(sum(shares) - 1.0) < 1e-5 and all("sigma" in v for v in summary.values())
     assert "branch contribution" in capsys.readouterr().out
+
+
+def test_vision_2d_trainer_augments_on_device_and_resumes(tmp_path):
+    from ml_experiments_b200.cli import train_vision_2d as V
+
+    g = torch.Generator().manual_seed(0)
+    grey, colour = torch.rand(4, 1, 28, 28), torch.rand(4, 3, 32, 32)
+    assert V.augment(grey, g).shape == grey.shape and V.augment(colour, g).shape == colour.shape
+    # colour augmentation only moves pixels: every output value exists in the zero-padded input
+    out = V.augment(colour, g)
+    assert set(out[0, 0].flatten().tolist()) <= set(colour[0, 0].flatten().tolist()) | {0.0}
+    x, y = V.synthetic_images(V.DATASET_CONFIGS["mnist"], 32, 0)
+    assert x.shape == (32, 1, 28, 28) and x.dtype == torch.uint8 and int(y.max()) < 10
+    assert V.to_gray(torch.full((1, 3, 2, 2), 100, dtype=torch.uint8)).unique().tolist() == [100]
+    args = ["--dataset", "mnist", "--source", "synthetic", "--n-train", "64", "--n-val", "32", "--width", "8", "--n-layers", "1", "--batch-size", "32",
+            "--adaptive", "--n-branches", "2", "--output", str(tmp_path / "m.pt"), "--device", "cpu"]
+    s1 = V.main(args + ["--epochs", "1"])
+    assert (tmp_path / "m.last.pt").exists() and 0.0 <= s1["best_acc"] <= 1.0
+    ck = torch.load(tmp_path / "m.last.pt", weights_only=False)
+    assert ck["epoch"] == 1 and ck["model_config"]["layer"]["adaptive_conv"] is True
