@@ -77,6 +77,7 @@ class TelephoneAttentionND(nn.Module):
         self.channels, self.ndim, self.num_heads = channels, ndim, num_heads
         self.head_dim = channels // num_heads
         self.chunk_size, self.checkpoint = chunk_size, checkpoint
+        self.fused = True       # False forces the chunked (optionally checkpointed) composition on a GPU as well
         self.max_freq, self.min_freq, self.max_kernel_size = max_freq, min_freq, max_kernel_size
         self.scale_power, self.max_seq_len = scale_power, max_seq_len
         H = num_heads
@@ -151,7 +152,7 @@ class TelephoneAttentionND(nn.Module):
         if self.ndim != 1:
             return _telephone_nd(self, x)
         xf = x.reshape(B, L, C)
-        if xf.is_cuda and self.head_dim in (8, 16, 32, 64, 128) and self.max_kernel_size <= 64:
+        if self.fused and xf.is_cuda and self.head_dim in (8, 16, 32, 64, 128) and self.max_kernel_size <= 64:
             return F.silu(self.out_proj(self._fused(xf, L))).reshape(B, *spatial, C), {}
         outs = []
         for start in range(0, L, self.chunk_size):

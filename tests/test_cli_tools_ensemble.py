@@ -90,3 +90,32 @@ def test_vision_2d_trainer_augments_on_device_and_resumes(tmp_path):
     assert (tmp_path / "m.last.pt").exists() and 0.0 <= s1["best_acc"] <= 1.0
     ck = torch.load(tmp_path / "m.last.pt", weights_only=False)
     assert ck["epoch"] == 1 and ck["model_config"]["layer"]["adaptive_conv"] is True
+
+
+def test_arch_search_grids_and_pareto(tmp_path):
+    from ml_experiments_b200.cli import arch_search as A
+
+    rows = [{"arch": "a", "params": 10, "f1": 0.5}, {"arch": "b", "params": 20, "f1": 0.4}, {"arch": "c", "params": 30, "f1": 0.9},
+            {"arch": "d", "params": 30, "f1": 0.7}]
+    assert [r["arch"] for r in A.pareto_front(rows, "f1")] == ["a", "c"]
+    assert len(A.line_filter_space(True)) == 8 and len({c.name() for c in A.line_filter_space(False)}) == len(A.line_filter_space(False))
+    assert all(c.width % c.groups == 0 for c in A.bytemasker_space(False))
+    summary, res = A.main(["--task", "line-filter", "--quick", "--max-candidates", "2", "--synthetic", "96", "--epochs", "1", "--max-len", "64",
+                           "--no-swa", "--device", "cpu", "--output", str(tmp_path / "lf.csv")])
+    assert summary["candidates"] == 2 and res[0]["params"] != res[1]["params"]        # the axes change the model
+    assert (tmp_path / "lf.csv").read_text().startswith("arch,arch_type,embed_width")
+    summary, res = A.main(["--task", "bytemasker", "--quick", "--max-candidates", "2", "--synthetic", "96", "--epochs", "1", "--max-len", "64",
+                           "--device", "cpu"])
+    assert summary["task"] == "bytemasker" and all(0.0 <= r["recall"] <= 1.0 and r["samples_per_sec"] > 0 for r in res)
+
+
+def test_memory_diagnostics_run_every_strategy_on_the_host():
+    from ml_experiments_b200.cli import diagnose_memory as D
+
+    rows = D.main(["--what", "gather", "--lengths", "32", "--batch", "2", "--channels", "16", "--heads", "2", "--samples", "3", "--device", "cpu"])
+    assert set(rows[0]) >= {"materialise", "per_tap", "fused"}
+    cases, x = D.gather_cases(2, 32, 16, 2, 3, torch.device("cpu"), torch.float32)
+    a, b = cases["materialise"](), cases["per_tap"]()
+    assert torch.allclose(a, b, atol=1e-5)                  # both strategies compute the same nearest-tap gather
+    rows = D.main(["--what", "telephone", "--lengths", "64", "--batch", "1", "--channels", "16", "--heads", "2", "--device", "cpu"])
+    assert set(rows[0]) == {"L", "fused_or_whole", "chunked_checkpoint"}
