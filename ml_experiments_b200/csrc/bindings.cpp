@@ -343,6 +343,11 @@ void allreduce_mean(at::IntArrayRef buf_ptrs, int64_t rank, int64_t n, int64_t d
 
 
 // ---------------------------------------------------------------------------------------------- S6 selective scan
+void s6_set_states_per_thread(int64_t fwd_qs, int64_t bwd_qs, const Tensor& like) {
+  (void)like;  // only selects the CUDA dispatch key
+  b200::s6_set_states_per_thread((int)fwd_qs, (int)bwd_qs);
+}
+
 void s6_scan_fwd(const Tensor& u, const Tensor& delta, const c10::optional<Tensor>& delta_bias, bool softplus, const Tensor& A,
                  const Tensor& Bm, const Tensor& Cm, const c10::optional<Tensor>& Dv, const c10::optional<Tensor>& z,
                  const c10::optional<Tensor>& y_pre, Tensor out, const c10::optional<Tensor>& state) {
@@ -646,6 +651,7 @@ TORCH_LIBRARY(b200, m) {
   m.def("ag_wait_apply(Tensor(a!) p, Tensor u, Tensor(b!)? p_bf16, float alpha, int world, Tensor flags, int channel, int epoch, Tensor(c!) status) -> ()");
   m.def("allreduce_mean_multimem(int mc_ptr, int world, int rank, int n, int dtype, Tensor flags, int[] peer_flags, int channel, int epoch, Tensor(a!) status) -> ()");
   m.def("allreduce_mean(int[] buf_ptrs, int rank, int n, int dtype, Tensor flags, int[] peer_flags, int channel, int epoch, Tensor(a!) status) -> ()");
+  m.def("s6_set_states_per_thread(int fwd_qs, int bwd_qs, Tensor like) -> ()");
   m.def("s6_scan_fwd(Tensor u, Tensor delta, Tensor? delta_bias, bool softplus, Tensor A, Tensor Bm, Tensor Cm, Tensor? Dv, Tensor? z, Tensor(a!)? y_pre, Tensor(b!) out, Tensor(c!)? state) -> ()");
   m.def("s6_scan_bwd(Tensor u, Tensor delta, Tensor? delta_bias, bool softplus, Tensor A, Tensor Bm, Tensor Cm, Tensor? Dv, Tensor? z, Tensor? y_pre, Tensor dout, Tensor state, Tensor(a!) du, Tensor(b!) ddelta, Tensor(c!) dA, Tensor(d!) dB_part, Tensor(e!) dC_part, Tensor(f!)? dD, Tensor(g!)? dz, Tensor(h!)? ddelta_bias) -> ()");
   m.def("causal_conv1d_silu_fwd(Tensor x, Tensor w, Tensor? bias, Tensor(a!) y) -> ()");
@@ -695,6 +701,7 @@ TORCH_LIBRARY_IMPL(b200, CUDA, m) {
   m.impl("ag_wait_apply", &ag_wait_apply);
   m.impl("allreduce_mean_multimem", &allreduce_mean_multimem);
   m.impl("allreduce_mean", &allreduce_mean);
+  m.impl("s6_set_states_per_thread", &s6_set_states_per_thread);
   m.impl("s6_scan_fwd", &s6_scan_fwd);
   m.impl("s6_scan_bwd", &s6_scan_bwd);
   m.impl("causal_conv1d_silu_fwd", &causal_conv1d_silu_fwd);

@@ -4,7 +4,8 @@
 //   h_t[d,n] = exp(dt_t[d] * A[d,n]) * h_{t-1}[d,n] + dt_t[d] * B_t[n] * u_t[d]
 //   y_t[d]   = sum_n C_t[n] * h_t[d,n] + D[d] * u_t[d] ;   out = y * silu(z)
 //
-// Thread mapping: a block owns 32 channels; lane = channel, warp = one quarter of the 16 states (4 states in registers).
+// Thread mapping: a block owns 32 channels; lane = channel, warp = QS of the 16 states in registers (QS = 4: four warps
+// per block, QS = 2: eight warps per block, twice the warps per SM to hide the exp / FMA latency of the recurrence).
 // B_t / C_t are then warp-uniform shared-memory broadcasts, dt / u loads are conflict-free, the forward needs no
 // shuffles at all (the four partial sums over states meet in shared memory), and the backward's dB_t / dC_t, which sum
 // over channels, are 8 values reduced across the 32 lanes with a halving butterfly (9 shuffles for all 8).
@@ -30,10 +31,40 @@ namespace {
 
 using bf16 = __nv_bfloat16;
 constexpr int NS = 16;    // states per channel
-constexpr int QS = 4;     // states per thread
 constexpr int CB = 32;    // channels per block (= lanes)
 constexpr int SUB = 16;   // time steps per tile and per state checkpoint
-constexpr int NT = 128;   // threads per block
+int g_fwd_qs = 2, g_bwd_qs = 4;  // measured on 8 x 4096 x 2048: forward 0.72 ms at 2 (0.80 at 4); backward 2.6 ms at 4 (5.5 at 2: spills)
+
+// State checkpoints are stored in groups of four states whatever QS the kernels run with:
+// [B][tiles][4][Din][4]; a thread's QS states (first state n0 = w * QS) are contiguous in it.
+__device__ __forceinline__ long long state_off(int b, int nsub, int tile, int n0, int Din, int d) {
+  return ((((long long)b * nsub + tile) * 4 + (n0 >> 2)) * Din + d) * 4 + (n0 & 3);
+}
+
+template <int QS>
+struct Shape {
+  static constexpr int NW = NS / QS;          // warps per block
+  static constexpr int NT = 32 * NW;          // threads per block
+  static constexpr int RPT = SUB / NW;        // rows of a [16][32] tile staged per thread
+  static constexpr int BCPT = SUB * NS / NT;  // B (and C) elements staged per thread
+};
+
+// QS consecutive floats as one vector access
+template <int QS>
+__device__ __forceinline__ void ldv(float (&o)[QS], const float* p) {
+  if constexpr (QS == 4) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    o[0] = v.x, o[1] = v.y, o[2] = v.z, o[3] = v.w;
+  } else {
+    const float2 v = *reinterpret_cast<const float2*>(p);
+    o[0] = v.x, o[1] = v.y;
+  }
+}
+template <int QS>
+__device__ __forceinline__ void stv(float* p, const float (&o)[QS]) {
+  if constexpr (QS == 4) *reinterpret_cast<float4*>(p) = make_float4(o[0], o[1], o[2], o[3]);
+  else *reinterpret_cast<float2*>(p) = make_float2(o[0], o[1]);
+}
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ float ex2(float x) {
@@ -49,6 +80,7 @@ __device__ __forceinline__ void st(bf16* p, long long i, float v) { p[i] = __flo
 __device__ __forceinline__ float sigmoidf(float x) { return 1.f / (1.f + __expf(-x)); }
 __device__ __forceinline__ float softplusf(float x) { return x > 20.f ? x : log1pf(__expf(x)); }
 
+template <int QS>
 struct FwdSmem {
   float dt[SUB][CB];
   float u[SUB][CB];
@@ -57,14 +89,15 @@ struct FwdSmem {
   float yp[NS / QS][SUB][CB];
 };
 
-// grid (ceil(Din / 32), batch), 128 threads. DT = element type of delta (fp32 or bf16).
-template <typename DT>
-__global__ void __launch_bounds__(NT, 8)
+// grid (ceil(Din / 32), batch), 32 * 16 / QS threads. DT = element type of delta (fp32 or bf16).
+template <typename DT, int QS>
+__global__ void __launch_bounds__(Shape<QS>::NT, 1024 / Shape<QS>::NT)
 s6_fwd_kernel(const bf16* __restrict__ u, const DT* __restrict__ delta, const float* __restrict__ delta_bias,
               int softplus, const float* __restrict__ A, const float* __restrict__ Bm, const float* __restrict__ Cm,
               const float* __restrict__ Dv, const bf16* __restrict__ z, bf16* __restrict__ y_pre,
               bf16* __restrict__ out, float* __restrict__ state, int L, int Din) {
-  __shared__ __align__(16) FwdSmem s;
+  constexpr int NW = Shape<QS>::NW, NT = Shape<QS>::NT, RPT = Shape<QS>::RPT, BCPT = Shape<QS>::BCPT;
+  __shared__ __align__(16) FwdSmem<QS> s;
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const int b = blockIdx.y, d0 = blockIdx.x * CB, d = d0 + lane;
   const bool dok = d < Din;
@@ -77,13 +110,13 @@ s6_fwd_kernel(const bf16* __restrict__ u, const DT* __restrict__ delta, const fl
   }
   const float bias = (dok && delta_bias) ? delta_bias[d] : 0.f;
   const float dsk = (dok && Dv) ? Dv[d] : 0.f;
-  // staging registers for the next tile: the thread covers rows w + 4j of the [16][32] tiles and two B / C elements
-  float pdt[SUB / 4], pu[SUB / 4], pz[SUB / 4], pB[2], pC[2];
+  // staging registers for the next tile: the thread covers rows w + NW * j of the [16][32] tiles and BCPT B / C elements
+  float pdt[RPT], pu[RPT], pz[RPT], pB[BCPT], pC[BCPT];
   auto fetch = [&](int tile) {
     const int t0 = tile * SUB;
 #pragma unroll
-    for (int j = 0; j < SUB / 4; ++j) {
-      const int t = t0 + w + 4 * j;
+    for (int j = 0; j < RPT; ++j) {
+      const int t = t0 + w + NW * j;
       const bool ok = dok && t < L;
       const long long off = ((long long)b * L + t) * Din + d;
       pdt[j] = ok ? ld(delta, off) : 0.f;
@@ -91,7 +124,7 @@ s6_fwd_kernel(const bf16* __restrict__ u, const DT* __restrict__ delta, const fl
       pz[j] = (ok && z) ? __bfloat162float(z[off]) : 0.f;
     }
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
+    for (int j = 0; j < BCPT; ++j) {
       const int i = tid + NT * j, t = t0 + i / NS;
       const long long off = ((long long)b * L + t) * NS + (i % NS);
       pB[j] = t < L ? Bm[off] : 0.f;
@@ -102,33 +135,32 @@ s6_fwd_kernel(const bf16* __restrict__ u, const DT* __restrict__ delta, const fl
   for (int tile = 0; tile < nsub; ++tile) {
     const int t0 = tile * SUB;
 #pragma unroll
-    for (int j = 0; j < SUB / 4; ++j) {
-      const int t = w + 4 * j;
+    for (int j = 0; j < RPT; ++j) {
+      const int t = w + NW * j;
       float dtv = pdt[j];
       if (softplus) dtv = (dok && t0 + t < L) ? softplusf(dtv + bias) : 0.f;
       s.dt[t][lane] = dtv;
       s.u[t][lane] = pu[j];
     }
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
+    for (int j = 0; j < BCPT; ++j) {
       const int i = tid + NT * j;
       s.B[i / NS][i % NS] = pB[j];
       s.C[i / NS][i % NS] = pC[j];
     }
-    float zc[SUB / 4];  // this tile's gate inputs (the staging registers are about to be refilled)
+    float zc[RPT];  // this tile's gate inputs (the staging registers are about to be refilled)
 #pragma unroll
-    for (int j = 0; j < SUB / 4; ++j) zc[j] = pz[j];
+    for (int j = 0; j < RPT; ++j) zc[j] = pz[j];
     __syncthreads();
     if (tile + 1 < nsub) fetch(tile + 1);
     if (state && dok)
-      *reinterpret_cast<float4*>(&state[((((long long)b * nsub + tile) * (NS / QS) + w) * Din + d) * QS]) =
-          make_float4(h[0], h[1], h[2], h[3]);
+      stv<QS>(&state[state_off(b, nsub, tile, w * QS, Din, d)], h);
 #pragma unroll
     for (int t = 0; t < SUB; ++t) {
       const float dt = s.dt[t][lane], dtu = dt * s.u[t][lane];
-      const float4 b4 = *reinterpret_cast<const float4*>(&s.B[t][w * QS]);
-      const float4 c4 = *reinterpret_cast<const float4*>(&s.C[t][w * QS]);
-      const float bb[QS] = {b4.x, b4.y, b4.z, b4.w}, cc[QS] = {c4.x, c4.y, c4.z, c4.w};
+      float bb[QS], cc[QS];
+      ldv<QS>(bb, &s.B[t][w * QS]);
+      ldv<QS>(cc, &s.C[t][w * QS]);
       float y = 0.f;
 #pragma unroll
       for (int k = 0; k < QS; ++k) {
@@ -139,11 +171,13 @@ s6_fwd_kernel(const bf16* __restrict__ u, const DT* __restrict__ delta, const fl
     }
     __syncthreads();
 #pragma unroll
-    for (int j = 0; j < SUB / 4; ++j) {
-      const int t = w + 4 * j;
+    for (int j = 0; j < RPT; ++j) {
+      const int t = w + NW * j;
       if (dok && t0 + t < L) {
         const long long off = ((long long)b * L + t0 + t) * Din + d;
-        const float yv = s.yp[0][t][lane] + s.yp[1][t][lane] + s.yp[2][t][lane] + s.yp[3][t][lane] + dsk * s.u[t][lane];
+        float yv = dsk * s.u[t][lane];
+#pragma unroll
+        for (int q = 0; q < NW; ++q) yv += s.yp[q][t][lane];
         if (y_pre) y_pre[off] = __float2bfloat16_rn(yv);
         float o = yv;
         if (z) o = yv * zc[j] * sigmoidf(zc[j]);
@@ -154,6 +188,7 @@ s6_fwd_kernel(const bf16* __restrict__ u, const DT* __restrict__ delta, const fl
   }
 }
 
+template <int QS>
 struct BwdSmem {
   float dt[SUB][CB];
   float u[SUB][CB];
@@ -188,10 +223,27 @@ __device__ __forceinline__ float reduce8(const float (&v)[8], int lane) {
   return p;
 }
 
-// grid (ceil(Din / 32), batch), 128 threads. dout is the gradient of `out`; with z given the gate's backward is applied
+// Same for 4 per-lane values: afterwards every lane holds the total of value ((lane >> 4) & 1) * 2 + ((lane >> 3) & 1).
+__device__ __forceinline__ float reduce4(const float (&v)[4], int lane) {
+  const bool b4 = lane & 16, b3 = lane & 8;
+  float r[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const float send = b4 ? v[i] : v[i + 2], keep = b4 ? v[i + 2] : v[i];
+    r[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+  }
+  const float send = b3 ? r[0] : r[1], keep = b3 ? r[1] : r[0];
+  float p = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+  p += __shfl_xor_sync(0xffffffffu, p, 4);
+  p += __shfl_xor_sync(0xffffffffu, p, 2);
+  p += __shfl_xor_sync(0xffffffffu, p, 1);
+  return p;
+}
+
+// grid (ceil(Din / 32), batch), 32 * 16 / QS threads. dout is the gradient of `out`; with z given the gate's backward is applied
 // here (dy = dout * silu(z), dz = dout * y_pre * silu'(z)).
-template <typename DT>
-__global__ void __launch_bounds__(NT, 4)
+template <typename DT, int QS>
+__global__ void __launch_bounds__(Shape<QS>::NT, 4)
 s6_bwd_kernel(const bf16* __restrict__ u, const DT* __restrict__ delta, const float* __restrict__ delta_bias,
               int softplus, const float* __restrict__ A, const float* __restrict__ Bm, const float* __restrict__ Cm,
               const float* __restrict__ Dv, const bf16* __restrict__ z, const bf16* __restrict__ y_pre,
@@ -199,7 +251,8 @@ s6_bwd_kernel(const bf16* __restrict__ u, const DT* __restrict__ delta, const fl
               DT* __restrict__ ddelta, float* __restrict__ dA, float* __restrict__ dB_part,
               float* __restrict__ dC_part, float* __restrict__ dD, bf16* __restrict__ dz,
               float* __restrict__ ddelta_bias, int L, int Din) {
-  __shared__ __align__(16) BwdSmem s;
+  constexpr int NW = Shape<QS>::NW, NT = Shape<QS>::NT, RPT = Shape<QS>::RPT, BCPT = Shape<QS>::BCPT;
+  __shared__ __align__(16) BwdSmem<QS> s;
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const int b = blockIdx.y, d0 = blockIdx.x * CB, d = d0 + lane, nblk = gridDim.x;
   const bool dok = d < Din;
@@ -217,10 +270,10 @@ s6_bwd_kernel(const bf16* __restrict__ u, const DT* __restrict__ delta, const fl
   float dDa = 0.f, dbias = 0.f;
   for (int tile = nsub - 1; tile >= 0; --tile) {
     const int t0 = tile * SUB;
-    float sp[SUB / 4];  // d softplus / d raw for the rows this thread stages (and writes back)
+    float sp[RPT];  // d softplus / d raw for the rows this thread stages (and writes back)
 #pragma unroll
-    for (int j = 0; j < SUB / 4; ++j) {
-      const int t = w + 4 * j;
+    for (int j = 0; j < RPT; ++j) {
+      const int t = w + NW * j;
       const bool ok = dok && t0 + t < L;
       const long long off = ((long long)b * L + t0 + t) * Din + d;
       float dtv = ok ? ld(delta, off) : 0.f;
@@ -241,21 +294,21 @@ s6_bwd_kernel(const bf16* __restrict__ u, const DT* __restrict__ delta, const fl
       s.dy[t][lane] = g;
     }
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
+    for (int j = 0; j < BCPT; ++j) {
       const int i = tid + NT * j, t = t0 + i / NS;
       const long long off = ((long long)b * L + t) * NS + (i % NS);
       s.B[i / NS][i % NS] = t < L ? Bm[off] : 0.f;
       s.C[i / NS][i % NS] = t < L ? Cm[off] : 0.f;
     }
-    float4 h04 = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (dok)
-      h04 = *reinterpret_cast<const float4*>(&state[((((long long)b * nsub + tile) * (NS / QS) + w) * Din + d) * QS]);
-    const float h0[QS] = {h04.x, h04.y, h04.z, h04.w};
+    float h0[QS];
+#pragma unroll
+    for (int k = 0; k < QS; ++k) h0[k] = 0.f;
+    if (dok) ldv<QS>(h0, &state[state_off(b, nsub, tile, w * QS, Din, d)]);
     __syncthreads();
     if (tile > 0) {  // warm L2 with the rows of the tile processed next (one tile earlier in time)
 #pragma unroll
-      for (int j = 0; j < SUB / 4; ++j) {
-        const long long off = ((long long)b * L + t0 - SUB + w + 4 * j) * Din + d;
+      for (int j = 0; j < RPT; ++j) {
+        const long long off = ((long long)b * L + t0 - SUB + w + NW * j) * Din + d;
         if (dok) {
           prefetch_l2(delta + off);
           prefetch_l2(u + off);
@@ -266,7 +319,7 @@ s6_bwd_kernel(const bf16* __restrict__ u, const DT* __restrict__ delta, const fl
           }
         }
       }
-      if (dok) prefetch_l2(&state[((((long long)b * nsub + tile - 1) * (NS / QS) + w) * Din + d) * QS]);
+      if (dok) prefetch_l2(&state[state_off(b, nsub, tile - 1, w * QS, Din, d)]);
       if (tid < 2 * SUB) {
         const long long off = ((long long)b * L + t0 - SUB + (tid >> 1)) * NS;
         prefetch_l2((tid & 1) ? Cm + off : Bm + off);
@@ -274,12 +327,14 @@ s6_bwd_kernel(const bf16* __restrict__ u, const DT* __restrict__ delta, const fl
     }
     float hs[SUB][QS];
     {
-      float hh[QS] = {h0[0], h0[1], h0[2], h0[3]};
+      float hh[QS];
+#pragma unroll
+      for (int k = 0; k < QS; ++k) hh[k] = h0[k];
 #pragma unroll
       for (int t = 0; t < SUB; ++t) {
         const float dt = s.dt[t][lane], dtu = dt * s.u[t][lane];
-        const float4 b4 = *reinterpret_cast<const float4*>(&s.B[t][w * QS]);
-        const float bb[QS] = {b4.x, b4.y, b4.z, b4.w};
+        float bb[QS];
+        ldv<QS>(bb, &s.B[t][w * QS]);
 #pragma unroll
         for (int k = 0; k < QS; ++k) {
           hh[k] = fmaf(ex2(dt * a2[k]), hh[k], dtu * bb[k]);
@@ -290,10 +345,10 @@ s6_bwd_kernel(const bf16* __restrict__ u, const DT* __restrict__ delta, const fl
 #pragma unroll
     for (int t = SUB - 1; t >= 0; --t) {
       const float dt = s.dt[t][lane], uu = s.u[t][lane], gy = s.dy[t][lane], dtu = dt * uu;
-      const float4 b4 = *reinterpret_cast<const float4*>(&s.B[t][w * QS]);
-      const float4 c4 = *reinterpret_cast<const float4*>(&s.C[t][w * QS]);
-      const float bb[QS] = {b4.x, b4.y, b4.z, b4.w}, cc[QS] = {c4.x, c4.y, c4.z, c4.w};
-      float v[8], ddt_p = 0.f, du_p = 0.f;
+      float bb[QS], cc[QS];
+      ldv<QS>(bb, &s.B[t][w * QS]);
+      ldv<QS>(cc, &s.C[t][w * QS]);
+      float v[2 * QS], ddt_p = 0.f, du_p = 0.f;
 #pragma unroll
       for (int k = 0; k < QS; ++k) {
         const float gh = fmaf(cc[k], gy, cr[k]);  // dL/dh_t
@@ -303,34 +358,48 @@ s6_bwd_kernel(const bf16* __restrict__ u, const DT* __restrict__ delta, const fl
         ddt_p = fmaf(gha * hprev, ar[k], ddt_p);
         du_p = fmaf(gh, bb[k], du_p);
         v[k] = gh * dtu;
-        v[4 + k] = gy * hs[t][k];
+        v[QS + k] = gy * hs[t][k];
         cr[k] = gha;
       }
       s.pddt[w][t][lane] = fmaf(du_p, uu, ddt_p);  // d(dt * B * u) / d dt = B * u
       s.pdu[w][t][lane] = du_p * dt;
-      const float p = reduce8(v, lane);
-      if ((lane & 3) == 0) {
-        const int idx = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
-        if (idx < 4) s.dB[t][w * QS + idx] = p;
-        else s.dC[t][w * QS + idx - 4] = p;
+      if constexpr (QS == 4) {
+        const float p = reduce8(v, lane);
+        if ((lane & 3) == 0) {
+          const int idx = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+          if (idx < 4) s.dB[t][w * QS + idx] = p;
+          else s.dC[t][w * QS + idx - 4] = p;
+        }
+      } else {
+        const float p = reduce4(v, lane);
+        if ((lane & 7) == 0) {
+          const int idx = ((lane >> 4) & 1) * 2 + ((lane >> 3) & 1);
+          if (idx < 2) s.dB[t][w * QS + idx] = p;
+          else s.dC[t][w * QS + idx - 2] = p;
+        }
       }
       if (w == 0) dDa = fmaf(gy, uu, dDa);
     }
     __syncthreads();
 #pragma unroll
-    for (int j = 0; j < SUB / 4; ++j) {
-      const int t = w + 4 * j;
+    for (int j = 0; j < RPT; ++j) {
+      const int t = w + NW * j;
       if (dok && t0 + t < L) {
         const long long off = ((long long)b * L + t0 + t) * Din + d;
-        const float g = (s.pddt[0][t][lane] + s.pddt[1][t][lane] + s.pddt[2][t][lane] + s.pddt[3][t][lane]) * sp[j];
+        float g = 0.f, gu = dsk * s.dy[t][lane];
+#pragma unroll
+        for (int q = 0; q < NW; ++q) {
+          g += s.pddt[q][t][lane];
+          gu += s.pdu[q][t][lane];
+        }
+        g *= sp[j];
         st(ddelta, off, g);
         dbias += g;
-        du[off] = __float2bfloat16_rn(s.pdu[0][t][lane] + s.pdu[1][t][lane] + s.pdu[2][t][lane] + s.pdu[3][t][lane] +
-                                      dsk * s.dy[t][lane]);
+        du[off] = __float2bfloat16_rn(gu);
       }
     }
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
+    for (int j = 0; j < BCPT; ++j) {
       const int i = tid + NT * j, t = t0 + i / NS;
       if (t < L) {
         const long long off = ((((long long)b * nblk + blockIdx.x) * L) + t) * NS + (i % NS);
@@ -358,17 +427,33 @@ void check(const char* what) {
 int s6_channel_blocks(int Din) { return (Din + CB - 1) / CB; }
 int s6_num_chunks(int L) { return (L + SUB - 1) / SUB; }
 
+void s6_set_states_per_thread(int fwd_qs, int bwd_qs) {
+  if ((fwd_qs != 2 && fwd_qs != 4) || (bwd_qs != 2 && bwd_qs != 4))
+    throw std::runtime_error("s6_scan: states per thread must be 2 or 4");
+  g_fwd_qs = fwd_qs;
+  g_bwd_qs = bwd_qs;
+}
+
+#define S6_FWD(DT, QS)                                                                                               \
+  s6_fwd_kernel<DT, QS><<<grid, Shape<QS>::NT, 0, st>>>((const bf16*)u, (const DT*)delta, delta_bias, softplus ? 1 : 0, \
+                                                        A, Bm, Cm, Dv, (const bf16*)z, (bf16*)y_pre, (bf16*)out, state, L, Din)
+#define S6_BWD(DT, QS)                                                                                               \
+  s6_bwd_kernel<DT, QS><<<grid, Shape<QS>::NT, 0, st>>>((const bf16*)u, (const DT*)delta, delta_bias, softplus ? 1 : 0, \
+                                                        A, Bm, Cm, Dv, (const bf16*)z, (const bf16*)y_pre,            \
+                                                        (const bf16*)dout, state, (bf16*)du, (DT*)ddelta, dA, dB_part, \
+                                                        dC_part, dD, (bf16*)dz, ddelta_bias, L, Din)
+
 void s6_scan_fwd(const void* u, const void* delta, bool delta_bf16, const float* delta_bias, bool softplus,
                  const float* A, const float* Bm, const float* Cm, const float* Dv, const void* z, void* y_pre, void* out,
                  float* state, int batch, int L, int Din, int N, cudaStream_t st) {
   if (N != NS) throw std::runtime_error("s6_scan: state dimension must be 16");
   dim3 grid(s6_channel_blocks(Din), batch);
-  if (delta_bf16)
-    s6_fwd_kernel<bf16><<<grid, NT, 0, st>>>((const bf16*)u, (const bf16*)delta, delta_bias, softplus ? 1 : 0, A, Bm, Cm, Dv,
-                                             (const bf16*)z, (bf16*)y_pre, (bf16*)out, state, L, Din);
-  else
-    s6_fwd_kernel<float><<<grid, NT, 0, st>>>((const bf16*)u, (const float*)delta, delta_bias, softplus ? 1 : 0, A, Bm, Cm, Dv,
-                                              (const bf16*)z, (bf16*)y_pre, (bf16*)out, state, L, Din);
+  const bool q2 = g_fwd_qs == 2;
+  if (delta_bf16) {
+    if (q2) S6_FWD(bf16, 2); else S6_FWD(bf16, 4);
+  } else {
+    if (q2) S6_FWD(float, 2); else S6_FWD(float, 4);
+  }
   check("s6_scan_fwd");
 }
 
@@ -379,14 +464,12 @@ void s6_scan_bwd(const void* u, const void* delta, bool delta_bf16, const float*
   if (N != NS) throw std::runtime_error("s6_scan: state dimension must be 16");
   if (z && !y_pre) throw std::runtime_error("s6_scan_bwd: the gate's backward needs y_pre");
   dim3 grid(s6_channel_blocks(Din), batch);
-  if (delta_bf16)
-    s6_bwd_kernel<bf16><<<grid, NT, 0, st>>>((const bf16*)u, (const bf16*)delta, delta_bias, softplus ? 1 : 0, A, Bm, Cm, Dv,
-                                             (const bf16*)z, (const bf16*)y_pre, (const bf16*)dout, state, (bf16*)du,
-                                             (bf16*)ddelta, dA, dB_part, dC_part, dD, (bf16*)dz, ddelta_bias, L, Din);
-  else
-    s6_bwd_kernel<float><<<grid, NT, 0, st>>>((const bf16*)u, (const float*)delta, delta_bias, softplus ? 1 : 0, A, Bm, Cm, Dv,
-                                              (const bf16*)z, (const bf16*)y_pre, (const bf16*)dout, state, (bf16*)du,
-                                              (float*)ddelta, dA, dB_part, dC_part, dD, (bf16*)dz, ddelta_bias, L, Din);
+  const bool q2 = g_bwd_qs == 2;
+  if (delta_bf16) {
+    if (q2) S6_BWD(bf16, 2); else S6_BWD(bf16, 4);
+  } else {
+    if (q2) S6_BWD(float, 2); else S6_BWD(float, 4);
+  }
   check("s6_scan_bwd");
 }
 

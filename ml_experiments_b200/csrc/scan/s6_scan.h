@@ -12,6 +12,9 @@ namespace b200 {
 
 int s6_channel_blocks(int Din);  // ceil(Din / 32)
 int s6_num_chunks(int L);        // ceil(L / 16)
+// States held per thread (2 or 4) by the forward and by the backward kernel: 4 = four warps per 32-channel block,
+// 2 = eight warps per block (more warps per SM to hide latency, more shared-memory traffic). Default 2 / 4.
+void s6_set_states_per_thread(int fwd_qs, int bwd_qs);
 
 void s6_scan_fwd(const void* u, const void* delta, bool delta_bf16, const float* delta_bias, bool softplus, const float* A,
                  const float* Bm, const float* Cm, const float* Dv, const void* z, void* y_pre, void* out,

@@ -67,6 +67,7 @@ def main(argv=None):
     ap.add_argument("--channels", type=int, default=2048)
     ap.add_argument("--taps", type=int, default=16)
     ap.add_argument("--epilogue", default="none", choices=["none", "relu2", "axpby"])
+    ap.add_argument("--s6-qs", default=None, help="states per thread of the S6 forward,backward kernels, e.g. 2,4")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     a = ap.parse_args(argv)
@@ -111,7 +112,9 @@ def main(argv=None):
         fn = lambda: Fz.softcap_ce(logits, tgt, grad_out=grad)
         bytes_ = 2.0 * 2 * a.tokens * a.vocab
     elif a.op in ("s6_fwd", "s6_bwd"):
-        from .selective_scan import selective_scan
+        from .selective_scan import selective_scan, set_states_per_thread
+        if a.s6_qs:
+            set_states_per_thread(*[int(v) for v in a.s6_qs.split(",")])
         b, L, d, n = a.batch, a.seq, a.channels, 16
         u = torch.randn(b, L, d, device=dev, dtype=bf, requires_grad=True)
         delta = (torch.rand(b, L, d, device=dev) * 0.1).requires_grad_(True)

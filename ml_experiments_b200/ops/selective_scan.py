@@ -37,6 +37,13 @@ def selective_scan_ref(u, delta, A, B, C, D=None, z=None, delta_bias=None, delta
     return y.to(dtype_in)
 
 
+def set_states_per_thread(fwd: int = 2, bwd: int = 4, device="cuda") -> None:
+    """States of a channel held per thread (2 or 4) by the forward and the backward scan kernel: 4 runs four warps per
+    32-channel block, 2 runs eight (more warps per SM to hide the latency of the recurrence, more shared-memory
+    traffic). The state checkpoints have one layout for both, so the two choices are independent."""
+    ops().s6_set_states_per_thread(int(fwd), int(bwd), torch.empty(0, device=device))
+
+
 class _S6Scan(torch.autograd.Function):
     """CUDA path: softplus / bias / gate and their backward all run inside the two kernels."""
 

@@ -319,19 +319,45 @@ class FusedGradSync:
             o.allreduce_mean(self.b32.ptrs, w.rank, self.n32, 0, w.flags.local, w.flags.ptrs, CH_F32_IN, self._step, self._status)
 
     @torch.no_grad()
-    def finish(self):
+    def wait(self):
+        """Device-side wait until every peer has stored its reduced slice into this rank's buckets."""
         o = ops()
         w = self.w
         if self.n16:
             o.comm_wait(w.flags.local, w.world, CH_B16_OUT, self._step, self._status)
         if self.n32:
             o.comm_wait(w.flags.local, w.world, CH_F32_OUT, self._step, self._status)
+
+    @torch.no_grad()
+    def adopt(self):
+        """Point ``p.grad`` at the reduced bucket views (host-side only)."""
         for plist, views in ((self.p16, self.views16), (self.p32, self.views32)):
             for p, v in zip(plist, views):
                 if p.grad is not None:
                     p.grad = v
 
+    def finish(self):
+        self.wait()
+        self.adopt()
+
     def sync_non_muon_grads(self):
         self.publish()
         self.reduce()
         self.finish()
+
+    # -- overlapped form: the link-bound all-reduce runs on a side stream while the caller's stream does other work
+    def start_async(self):
+        """Publish on the current stream, then reduce + wait on a side stream. The signals every peer waits for are
+        all enqueued before the fork, so no kernel of either stream waits on work queued behind a waiting kernel."""
+        self.publish()
+        cur = torch.cuda.current_stream()
+        if getattr(self, "_side", None) is None:
+            self._side = torch.cuda.Stream()
+        self._side.wait_stream(cur)
+        with torch.cuda.stream(self._side):
+            self.reduce()
+            self.wait()
+
+    def join_async(self):
+        torch.cuda.current_stream().wait_stream(self._side)
+        self.adopt()

@@ -26,15 +26,21 @@ class RankFailure(RuntimeError):
 class Heartbeat:
     """``store`` is any ``torch.distributed.Store`` (TCPStore, FileStore, HashStore) shared by the ranks."""
 
-    def __init__(self, store, rank: int, world_size: int, timeout: float = 30.0, prefix: str = "hb"):
+    def __init__(self, store, rank: int, world_size: int, timeout: float = 30.0, prefix: str = "hb", store_rank: int = 0):
         self.store, self.rank, self.world_size, self.timeout, self.prefix = store, rank, world_size, timeout, prefix
+        self.store_rank = store_rank          # the rank that hosts the store: losing the store means losing that rank
         self._started = time.time()
 
     def _key(self, rank: int, what: str) -> str:
         return f"{self.prefix}/{what}/{rank}"
 
     def beat(self, step: int) -> None:
-        self.store.set(self._key(self.rank, "beat"), f"{step}:{time.time()}")
+        try:
+            self.store.set(self._key(self.rank, "beat"), f"{step}:{time.time()}")
+        except Exception as e:  # noqa: BLE001 - the store's host is gone
+            if self.rank == self.store_rank:
+                raise
+            raise RankFailure(self.store_rank, f"heartbeat store unreachable: {type(e).__name__}") from e
 
     def mark_failed(self, reason: str) -> None:
         self.store.set(self._key(self.rank, "failed"), reason or "failed")

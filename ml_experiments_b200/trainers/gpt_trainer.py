@@ -112,6 +112,11 @@ class GPTTrainer:
         else:
             self.optimizer2 = Muon(hidden, lr=hp_.muon_lr, momentum=hp_.muon_momentum, rank=rank, world_size=world_size)
         self.optimizers = [self.optimizer1, self.optimizer2]
+        # B200_OVERLAP_SYNC=0 serialises gradient all-reduce and optimizer steps again
+        # (only beside the fused Muon step: Dion's own all-reduces share the bucket all-reduce's flag channel and counter)
+        self.overlap_sync = (self.comm_mode == "fused-p2p" and hasattr(self.comm, "start_async")
+                             and type(self.optimizer2).__name__ == "FusedDistMuon"
+                             and os.environ.get("B200_OVERLAP_SYNC", "1") != "0")
         for opt in self.optimizers:
             for g in opt.param_groups:
                 g["initial_lr"] = g["lr"]
@@ -139,7 +144,6 @@ class GPTTrainer:
         w = window_blocks(self.step, hp) if window is None else window
         loss = self.model(inputs, targets, w)
         loss.backward()
-        self._sync_grads()
         frac = min(self.step / hp.muon_momentum_warmup_steps, 1)
         for g in self.optimizer2.param_groups:
             g["momentum"] = (1 - frac) * 0.85 + frac * 0.95
@@ -147,7 +151,16 @@ class GPTTrainer:
         for opt in self.optimizers:
             for g in opt.param_groups:
                 g["lr"] = g["initial_lr"] * lr_mul
-            opt.step()
+        if self.overlap_sync:
+            # the all-reduce of the embedding / head gradients (link-bound) runs beside the Muon step (GEMM-bound)
+            self.comm.start_async()
+            self.optimizer2.step()
+            self.comm.join_async()
+            self.optimizer1.step()
+        else:
+            self._sync_grads()
+            for opt in self.optimizers:
+                opt.step()
         self.model.zero_grad(set_to_none=True)
         self.step += 1
         return loss.detach()

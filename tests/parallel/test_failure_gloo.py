@@ -55,6 +55,11 @@ def _worker(rank, world, port, tmp, plan_kind):
         outcome = "injected"
     with open(os.path.join(tmp, f"out{rank}.txt"), "w") as f:
         f.write(outcome)
+    if rank == 0:
+        # the store lives in this process: keep it up until the other survivors have read the failure from it
+        deadline = time.time() + 30
+        while time.time() < deadline and not all(os.path.exists(os.path.join(tmp, f"out{r}.txt")) for r in range(world) if r != 1):
+            time.sleep(0.05)
     # no collective on the way out: the failed rank is gone
     os._exit(0)
 

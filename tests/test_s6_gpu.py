@@ -5,10 +5,19 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("bsz,L,din", [(2, 200, 128), (1, 64, 72), (3, 333, 192)])
-def test_scan_forward_backward(bsz, L, din):
-    from ml_experiments_b200.ops.selective_scan import selective_scan, selective_scan_ref
+@pytest.fixture
+def default_scan_shape():
+    yield
+    from ml_experiments_b200.ops.selective_scan import set_states_per_thread
+    set_states_per_thread()
 
+
+@pytest.mark.parametrize("qs", [(4, 4), (2, 4), (4, 2), (2, 2)])
+@pytest.mark.parametrize("bsz,L,din", [(2, 200, 128), (1, 64, 72), (3, 333, 192)])
+def test_scan_forward_backward(bsz, L, din, qs, default_scan_shape):
+    from ml_experiments_b200.ops.selective_scan import selective_scan, selective_scan_ref, set_states_per_thread
+
+    set_states_per_thread(*qs)
     torch.manual_seed(0)
     n = 16
     dev = "cuda"
