@@ -1,0 +1,115 @@
+"""Sweep results as tables (role of zoology/analysis/utils.py ``fetch_wandb_runs`` and the plotting examples in
+zoology/analysis/mqar_plotting_example.py): runs are read from what the trainer writes locally — the results CSV
+(one row per finished run) and the JSON-lines logs of ``ZOOLOGY_LOG_DIR`` (one file per run with its config and
+per-epoch metrics) — there is no network on the training box to fetch anything from. The MQAR figure of the reference
+(accuracy against model dimension, one panel per sequence length, one line per mixer, best learning rate per point) is
+produced as a pivot table, and optionally as a matplotlib figure when that library is importable.
+"""
+from __future__ import annotations
+
+import glob
+import json
+import os
+
+import pandas as pd
+
+
+def load_results(csv_path: str | None = None, log_dir: str | None = None) -> pd.DataFrame:
+    """One row per run. ``csv_path``: the trainer's results CSV. ``log_dir``: JSON-lines run logs; the best
+    ``valid/accuracy`` of each log and the fields of its config are flattened into the row."""
+    frames = []
+    if csv_path and os.path.exists(csv_path):
+        frames.append(pd.read_csv(csv_path))
+    if log_dir:
+        rows = []
+        for path in sorted(glob.glob(os.path.join(log_dir, "*.jsonl"))):
+            cfg, best, n_params, state = {}, None, None, None
+            with open(path) as f:
+                for line in f:
+                    d = json.loads(line)
+                    if "config" in d:
+                        cfg = d["config"]
+                    n_params = d.get("num_parameters", n_params)
+                    state = d.get("state_size", state)
+                    if "valid/accuracy" in d and (best is None or d["valid/accuracy"] > best["valid/accuracy"]):
+                        best = d
+            if best is None:
+                continue
+            model, data = cfg.get("model", {}), cfg.get("data", {})
+            mixer = (model.get("sequence_mixer") or {}).get("name", "")
+            train_cfgs = data.get("train_configs") or [{}]
+            rows.append({"run_id": cfg.get("run_id", os.path.basename(path)[:-6]), "mixer": mixer, "d_model": model.get("d_model"),
+                         "n_layers": model.get("n_layers"), "vocab_size": model.get("vocab_size"), "seq_len": train_cfgs[0].get("input_seq_len"),
+                         "lr": cfg.get("learning_rate"), "n_params": n_params, "state_size": state, "best_acc": best["valid/accuracy"],
+                         "best_loss": best.get("valid/loss"), "best_epoch": best.get("epoch")})
+        if rows:
+            frames.append(pd.DataFrame(rows))
+    if not frames:
+        return pd.DataFrame(columns=["run_id", "mixer", "d_model", "seq_len", "lr", "best_acc"])
+    df = pd.concat(frames, ignore_index=True)
+    return df.drop_duplicates(subset=["run_id"], keep="last") if "run_id" in df else df
+
+
+def short_mixer(name: str) -> str:
+    return str(name).rsplit(".", 1)[-1]
+
+
+def best_by(df: pd.DataFrame, keys=("mixer", "seq_len", "d_model"), metric: str = "best_acc") -> pd.DataFrame:
+    """Best run of every ``keys`` group (the reference keeps the best learning rate per plotted point)."""
+    if df.empty:
+        return df
+    idx = df.groupby(list(keys))[metric].idxmax()
+    return df.loc[idx].reset_index(drop=True)
+
+
+def mqar_table(df: pd.DataFrame, metric: str = "best_acc") -> pd.DataFrame:
+    """Rows (seq_len, mixer), columns d_model, values the best ``metric`` over learning rates."""
+    if df.empty:
+        return df
+    d = best_by(df.assign(mixer=df["mixer"].map(short_mixer)), metric=metric)
+    return d.pivot_table(index=["seq_len", "mixer"], columns="d_model", values=metric, aggfunc="max").sort_index()
+
+
+def plot_mqar(df: pd.DataFrame, path: str, metric: str = "best_acc") -> bool:
+    """One panel per sequence length, accuracy against d_model, one line per mixer. False when matplotlib is absent."""
+    try:
+        import matplotlib
+        matplotlib.use("Agg")
+        import matplotlib.pyplot as plt
+    except ImportError:
+        return False
+    d = best_by(df.assign(mixer=df["mixer"].map(short_mixer)), metric=metric)
+    lens = sorted(d["seq_len"].unique())
+    fig, axes = plt.subplots(1, len(lens), figsize=(4 * len(lens), 3.2), squeeze=False)
+    for ax, L in zip(axes[0], lens):
+        for mixer, g in d[d["seq_len"] == L].groupby("mixer"):
+            g = g.sort_values("d_model")
+            ax.plot(g["d_model"], g[metric], marker="o", label=mixer)
+        ax.set_xscale("log", base=2)
+        ax.set_title(f"seq_len {L}")
+        ax.set_xlabel("d_model")
+        ax.set_ylabel(metric)
+    axes[0][0].legend(fontsize=7)
+    fig.tight_layout()
+    fig.savefig(path, dpi=120)
+    plt.close(fig)
+    return True
+
+
+def main(argv=None):
+    import argparse
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--csv", default=os.environ.get("ZOOLOGY_CSV", "zoology_results.csv"))
+    ap.add_argument("--log-dir", default=os.environ.get("ZOOLOGY_LOG_DIR"))
+    ap.add_argument("--plot", default=None, help="write the MQAR figure to this file")
+    a = ap.parse_args(argv)
+    df = load_results(a.csv, a.log_dir)
+    table = mqar_table(df)
+    print(table.to_string() if not table.empty else "no runs found")
+    if a.plot and not df.empty:
+        print("figure written" if plot_mqar(df, a.plot) else "matplotlib is not installed: no figure")
+    return table
+
+
+if __name__ == "__main__":
+    main()

@@ -242,3 +242,35 @@ def test_experiment_definitions_build_and_instantiate():
             continue
         seen.add(m.name)
         assert LanguageModel(m)(x).shape == (2, 64, 64), m.name
+
+
+def test_analysis_tables_and_wall_clock(tmp_path):
+    import json
+
+    import pandas as pd
+
+    from ml_experiments_b200.zoology.analysis import results as R
+    from ml_experiments_b200.zoology.analysis import wall_clock as W
+
+    rows = [dict(run_id=f"r{i}", mixer=m, d_model=d, seq_len=L, lr=lr, best_acc=acc)
+            for i, (m, d, L, lr, acc) in enumerate([("a.b.MHA", 64, 128, 1e-3, 0.5), ("a.b.MHA", 64, 128, 1e-2, 0.9), ("a.b.MHA", 128, 128, 1e-3, 0.95),
+                                                    ("x.Mamba", 64, 128, 1e-3, 0.7), ("x.Mamba", 64, 256, 1e-3, 0.4)])]
+    pd.DataFrame(rows).to_csv(tmp_path / "res.csv", index=False)
+    log = tmp_path / "logs"
+    log.mkdir()
+    with open(log / "z1.jsonl", "w") as f:
+        f.write(json.dumps({"config": {"run_id": "z1", "learning_rate": 3e-3, "model": {"d_model": 256, "n_layers": 2, "sequence_mixer": {"name": "x.Mamba"}},
+                                       "data": {"train_configs": [{"input_seq_len": 256}]}}}) + "\n")
+        f.write(json.dumps({"num_parameters": 1234, "state_size": 99}) + "\n")
+        f.write(json.dumps({"epoch": 0, "valid/accuracy": 0.3, "valid/loss": 2.0}) + "\n")
+        f.write(json.dumps({"epoch": 1, "valid/accuracy": 0.8, "valid/loss": 1.0}) + "\n")
+    df = R.load_results(str(tmp_path / "res.csv"), str(log))
+    assert len(df) == 6 and df[df.run_id == "z1"].iloc[0].best_acc == 0.8 and df[df.run_id == "z1"].iloc[0].n_params == 1234
+    t = R.mqar_table(df)
+    assert t.loc[(128, "MHA"), 64] == 0.9 and t.loc[(128, "MHA"), 128] == 0.95          # best learning rate per point
+    assert t.loc[(256, "Mamba"), 256] == 0.8 and t.loc[(256, "Mamba"), 64] == 0.4
+    assert len(R.best_by(df)) == 5
+    assert R.load_results(str(tmp_path / "none.csv")).empty
+    table = W.wall_clock_table(("mamba1", "mamba2", "attention", "gla", "long_conv"), (32,), batch=1, heads=2, head_dim=8, dstate=8, iters=1, warmup=0,
+                               backward=True, device="cpu")
+    assert table[0]["seq_len"] == 32 and all(table[0][k] > 0 for k in W.OPERATORS)
