@@ -139,6 +139,21 @@ def run_ours(args, rank, local, world):
             losses.append(float(loss.item()))               # D2H read of the step's result
 
     device_loop(args.warmup)
+    if args.breakdown:
+        # not a timing run: per-kernel device time of three steps, as shares of one step
+        from torch.profiler import ProfilerActivity, profile
+
+        barrier()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            device_loop(3)
+            torch.cuda.synchronize()
+        if rank == 0:
+            ev = [e for e in prof.key_averages() if e.device_time_total > 0]
+            total = sum(e.device_time_total for e in ev)
+            print(f"device time per step: {total / 3e3:.2f} ms over {sum(e.count for e in ev) // 3} launches")
+            for e in sorted(ev, key=lambda e: -e.device_time_total)[: args.breakdown]:
+                print(f"{100 * e.device_time_total / total:5.1f} %  {e.device_time_total / 3e3:8.3f} ms/step  {e.count // 3:4d} x {e.device_time_total / e.count:9.1f} us  {e.key[:110]}")
+        return
     ms, launches, clocks = timed(device_loop, args.steps)
     e2e_loop(min(2, args.warmup))
     ms_e2e, _, _ = timed(e2e_loop, args.steps)
@@ -181,6 +196,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--breakdown", type=int, default=0, metavar="ROWS",
+                    help="instead of timing, profile 3 steps with torch.profiler and print the ROWS kernels with the most device time")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     world_env = int(os.environ.get("WORLD_SIZE", "1"))
