@@ -594,6 +594,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
       }
     }
+  } else if (kv < p.T) {
+    // no query tile attends this key tile: its gradients are zero (the caller does not pre-zero dk / dv)
+    __nv_bfloat16* dvrow = p.dv + (long long)kv * p.ld_dv + h * D + half * (D / 2);
+    __nv_bfloat16* dkrow = p.dk + (long long)kv * p.ld_dk + h * D + half * (D / 2);
+#pragma unroll
+    for (int j = 0; j < D / 16; ++j) {
+      reinterpret_cast<uint4*>(dvrow)[j] = make_uint4(0u, 0u, 0u, 0u);
+      reinterpret_cast<uint4*>(dkrow)[j] = make_uint4(0u, 0u, 0u, 0u);
+    }
   }
   if (issue_red) tma_store_wait_all<0>();
   if (tid == 0) {

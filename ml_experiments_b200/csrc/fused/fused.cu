@@ -437,7 +437,12 @@ __global__ void cast_fp8_kernel(const TI* __restrict__ x, uint8_t* __restrict__ 
 
 // ---------------------------------------------------------------------------------------------- soft-capped CE
 // One block per row. z = cap * sigmoid(x / div) is bounded by cap (30), so exp(z) needs no running maximum.
-__global__ void __launch_bounds__(512)
+// The kernel is bound by the SFU (tanh + exp per element and pass). With CACHE the first pass keeps exp(z) of the whole
+// row in shared memory as bf16 (2 bytes per column; two 1024-thread blocks, i.e. two rows, per SM at a 50k vocabulary); the gradient pass
+// then reads neither the logits nor evaluates tanh / exp again: sigmoid = log(e) / cap costs one SFU op instead of two,
+// and the 0.4 % rounding of e moves the sigmoid by 1e-4.
+template <bool CACHE>
+__global__ void __launch_bounds__(CACHE ? 1024 : 512)
 softcap_ce_kernel(const bf16* __restrict__ logits, const long long* __restrict__ targets,
                   float* __restrict__ loss_rows, uint8_t* __restrict__ grad, int grad_is_bf16, int T, int V, long long ld,
                   float cap, float inv_div, float shift, float loss_scale, float grad_scale,
@@ -445,7 +450,9 @@ softcap_ce_kernel(const bf16* __restrict__ logits, const long long* __restrict__
   // z = cap * sigmoid((x + shift) / div); loss_row = sum_k w_k (lse - z[target[row + k]]) over the rows that exist
   // (multi-token prediction: row r also predicts the targets of the next n_predict - 1 rows), w = {1} by default.
   constexpr int MAXP = 4;
-  __shared__ float red[16];
+  extern __shared__ __align__(16) uint8_t s_cache_raw[];
+  bf16* s_cache = reinterpret_cast<bf16*>(s_cache_raw);     // [V] exp(z) of this row
+  __shared__ float red[32];
   __shared__ float s_total;
   const int row = blockIdx.x;
   const bf16* x = logits + (long long)row * ld;
@@ -470,10 +477,14 @@ softcap_ce_kernel(const bf16* __restrict__ logits, const long long* __restrict__
     float f[8];
     load8(x + ci * 8, f);
 #pragma unroll
+    float e[8];
+#pragma unroll
     for (int i = 0; i < 8; ++i) {
       const float sg = 0.5f * tanhf(0.5f * (f[i] + shift) * inv_div) + 0.5f;  // sigmoid, one MUFU under fast-math
-      sum += exp2f(cap * sg * L2E);
+      e[i] = exp2f(cap * sg * L2E);
+      sum += e[i];
     }
+    if constexpr (CACHE) store8(s_cache + ci * 8, e);   // read back by the same thread: no barrier needed for the cache
   }
   sum = warp_sum(sum);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sum;
@@ -500,13 +511,22 @@ softcap_ce_kernel(const bf16* __restrict__ logits, const long long* __restrict__
   if (!grad) return;
   const float inv_total = 1.f / total;
   const float gs = grad_scale * cap * inv_div;
+  const float inv_cap_l2e = 1.f / (cap * L2E);
   for (int ci = threadIdx.x; ci < nch; ci += blockDim.x) {
     float f[8], g[8];
-    load8(x + ci * 8, f);
+    if constexpr (CACHE) load8(s_cache + ci * 8, f);
+    else load8(x + ci * 8, f);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const float sg = 0.5f * tanhf(0.5f * (f[i] + shift) * inv_div) + 0.5f;
-      const float pr = exp2f(cap * sg * L2E) * inv_total;
+      float sg, ev;
+      if constexpr (CACHE) {
+        ev = f[i];
+        sg = __log2f(ev) * inv_cap_l2e;
+      } else {
+        sg = 0.5f * tanhf(0.5f * (f[i] + shift) * inv_div) + 0.5f;
+        ev = exp2f(cap * sg * L2E);
+      }
+      const float pr = ev * inv_total;
       const int col = ci * 8 + i;
       float hot = 0.f;
 #pragma unroll
@@ -686,8 +706,20 @@ void softcap_ce(const void* logits, const long long* targets, float* loss_rows, 
                 const float* mtp_w, int n_predict, cudaStream_t s) {
   if (V % 8 != 0 || ld % 8 != 0) throw std::runtime_error("softcap_ce: vocabulary and row pitch must be multiples of 8");
   if (n_predict < 1 || n_predict > 4) throw std::runtime_error("softcap_ce: 1 to 4 prediction offsets");
-  softcap_ce_kernel<<<T, 512, 0, s>>>((const bf16*)logits, targets, loss_rows, (uint8_t*)grad, grad_is_bf16, T, V, ld, cap,
-                                      1.f / div, shift, loss_scale, grad_scale, mtp_w, n_predict);
+  const size_t cache_bytes = (size_t)V * 2;
+  if (grad && cache_bytes <= 110 * 1024) {   // two rows per SM
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaFuncSetAttribute(softcap_ce_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
+      attr_set = true;
+    }
+    softcap_ce_kernel<true><<<T, 1024, cache_bytes, s>>>((const bf16*)logits, targets, loss_rows, (uint8_t*)grad, grad_is_bf16,
+                                                        T, V, ld, cap, 1.f / div, shift, loss_scale, grad_scale, mtp_w,
+                                                        n_predict);
+  } else {
+    softcap_ce_kernel<false><<<T, 512, 0, s>>>((const bf16*)logits, targets, loss_rows, (uint8_t*)grad, grad_is_bf16, T, V,
+                                               ld, cap, 1.f / div, shift, loss_scale, grad_scale, mtp_w, n_predict);
+  }
   check("softcap_ce");
 }
 

@@ -238,6 +238,17 @@ class GPT(nn.Module):
             return fused_gpt_loss(self, input_seq, target_seq, swb)
         return self.forward_reference(input_seq, target_seq, swb)
 
+    def loss_and_grad(self, input_seq: Tensor, target_seq: Tensor, sliding_window_num_blocks) -> Tensor:
+        """``loss = self(...); loss.backward()`` in one call; returns the detached loss. The fused CUDA path fills
+        ``p.grad`` directly."""
+        swb = int(sliding_window_num_blocks)
+        if input_seq.is_cuda and self.fused and torch.is_grad_enabled():
+            from .gpt_fused import fused_gpt_step
+            return fused_gpt_step(self, input_seq, target_seq, swb)
+        loss = self(input_seq, target_seq, swb)
+        loss.backward()
+        return loss.detach()
+
     def forward_reference(self, input_seq: Tensor, target_seq: Tensor, sliding_window_num_blocks: int) -> Tensor:
         """Plain PyTorch path (dense masks; meant for CPU tests and small sequences)."""
         c = self.config

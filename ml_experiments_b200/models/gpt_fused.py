@@ -228,3 +228,24 @@ def fused_gpt_loss(model, input_seq: Tensor, target_seq: Tensor, swb: int) -> Te
     params = [p for p in model.parameters() if p.requires_grad]
     need_grad = torch.is_grad_enabled() and len(params) > 0
     return _FusedGPTLoss.apply(model, input_seq, target_seq, swb, need_grad, *params)
+
+
+def fused_gpt_step(model, input_seq: Tensor, target_seq: Tensor, swb: int) -> Tensor:
+    """Loss of one training step with the parameter gradients written straight into ``p.grad`` (accumulated when a
+    gradient is already there): what ``fused_gpt_loss(...).backward()`` produces, without the autograd node and its
+    multiply of every gradient by the incoming loss gradient (which is 1 for a plain ``backward()``)."""
+    loss, grads = _forward_backward(model, input_seq, target_seq, swb, True)
+    for p in model.parameters():
+        if not p.requires_grad:
+            continue
+        g = grads.get(id(p))
+        if g is None:
+            continue
+        g = g.view(p.shape)
+        if g.dtype != p.dtype:
+            g = g.to(p.dtype)
+        if p.grad is None:
+            p.grad = g
+        else:
+            p.grad.add_(g)
+    return loss.detach()

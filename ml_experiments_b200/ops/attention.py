@@ -85,8 +85,8 @@ def flash_attention_backward(q, k, v, o, d_o, lse, doc_start, doc_end, scale: fl
     t, h, d = q.shape
     if dq_acc is None:
         dq_acc = torch.zeros(t, h, d, dtype=torch.float32, device=q.device)
-    dk = torch.zeros(t, h, d, dtype=torch.bfloat16, device=q.device)
-    dv = torch.zeros(t, h, d, dtype=torch.bfloat16, device=q.device)
+    dk = torch.empty(t, h, d, dtype=torch.bfloat16, device=q.device)   # every row is written by its key tile's CTA
+    dv = torch.empty(t, h, d, dtype=torch.bfloat16, device=q.device)
     delta = torch.empty(h, t, dtype=torch.float32, device=q.device)
     if d_o.stride(2) != 1 or d_o.stride(1) != d:
         d_o = d_o.contiguous()

@@ -142,8 +142,7 @@ class GPTTrainer:
         if targets.dtype != torch.int64:
             targets = targets.to(torch.int64)
         w = window_blocks(self.step, hp) if window is None else window
-        loss = self.model(inputs, targets, w)
-        loss.backward()
+        loss = self.model.loss_and_grad(inputs, targets, w)
         frac = min(self.step / hp.muon_momentum_warmup_steps, 1)
         for g in self.optimizer2.param_groups:
             g["momentum"] = (1 - frac) * 0.85 + frac * 0.95
@@ -163,7 +162,7 @@ class GPTTrainer:
                 opt.step()
         self.model.zero_grad(set_to_none=True)
         self.step += 1
-        return loss.detach()
+        return loss
 
     @torch.no_grad()
     def eval_loss(self, inputs: torch.Tensor, targets: torch.Tensor, window: int) -> torch.Tensor:

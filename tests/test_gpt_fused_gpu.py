@@ -73,3 +73,26 @@ def test_muon_fused_matches_torch():
         delta = (p.detach().cpu() - q.detach()).norm() / (q.detach() - q.detach().round()).norm().clamp_min(1e-3)
         upd_err = (p.detach().cpu() - q.detach()).abs().max().item()
         assert upd_err < 2e-2, upd_err
+
+
+def test_loss_and_grad_equals_backward_of_the_loss():
+    """The trainer's direct path fills p.grad with what autograd would have produced, and accumulates on a second call."""
+    m = _model(True)
+    t = 1024
+    x = torch.randint(0, 50257, (t,), device="cuda")
+    y = torch.randint(0, 50257, (t,), device="cuda")
+    loss = m(x, y, 2)
+    loss.backward()
+    want = {n: p.grad.clone() for n, p in m.named_parameters() if p.grad is not None}
+    m.zero_grad(set_to_none=True)
+    loss2 = m.loss_and_grad(x, y, 2)
+    assert not loss2.requires_grad and torch.allclose(loss2, loss.detach())
+    got = {n: p.grad for n, p in m.named_parameters() if p.grad is not None}
+    assert set(got) == set(want)
+    for n in want:
+        assert got[n].dtype == want[n].dtype and got[n].shape == want[n].shape, n
+        # weight-gradient GEMMs use split-K atomics: equal up to summation order
+        assert (got[n].float() - want[n].float()).norm() <= 2e-3 * want[n].float().norm() + 1e-8, n
+    m.loss_and_grad(x, y, 2)
+    for n in want:
+        assert (m.get_parameter(n).grad.float() - 2 * want[n].float()).norm() <= 1e-2 * (2 * want[n].float()).norm() + 1e-8, n
