@@ -204,6 +204,16 @@ void embed_scatter_add(const Tensor& idx, const Tensor& src, Tensor grad_table) 
                           (int)grad_table.size(1), cur_stream());
 }
 
+void doc_bounds(const Tensor& tokens, int64_t bos, Tensor doc_start, Tensor doc_end) {
+  const c10::cuda::CUDAGuard guard(tokens.device());
+  TORCH_CHECK(tokens.scalar_type() == at::kLong && tokens.is_contiguous() && tokens.dim() == 1, "doc_bounds: tokens int64 [T]");
+  TORCH_CHECK(doc_start.scalar_type() == at::kInt && doc_end.scalar_type() == at::kInt && doc_start.is_contiguous() &&
+              doc_end.is_contiguous() && doc_start.numel() == tokens.numel() && doc_end.numel() == tokens.numel(),
+              "doc_bounds: doc_start / doc_end int32 [T]");
+  b200::doc_bounds(reinterpret_cast<const long long*>(tokens.data_ptr<int64_t>()), (long long)bos,
+                   doc_start.data_ptr<int>(), doc_end.data_ptr<int>(), (int)tokens.numel(), cur_stream());
+}
+
 void cast_fp8(const Tensor& x, Tensor out, double scale) {
   const c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(x.is_contiguous() && out.is_contiguous() && x.numel() == out.numel(), "cast_fp8: layout");
@@ -637,6 +647,7 @@ TORCH_LIBRARY(b200, m) {
   m.def("qkv_post_bwd(Tensor dq, Tensor dk, Tensor dv, Tensor qkv, Tensor? ve, Tensor lam, Tensor cos, Tensor sin, Tensor(a!) dqkv, Tensor(b!)? dve, Tensor(c!) dlam, int H, int D, float eps) -> ()");
   m.def("embed_gather(Tensor idx, Tensor table, Tensor(a!) out, bool normalize, float eps) -> ()");
   m.def("embed_scatter_add(Tensor idx, Tensor src, Tensor(a!) grad_table) -> ()");
+  m.def("doc_bounds(Tensor tokens, int bos, Tensor(a!) doc_start, Tensor(b!) doc_end) -> ()");
   m.def("cast_fp8(Tensor x, Tensor(a!) out, float scale) -> ()");
   m.def("softcap_ce(Tensor logits, Tensor targets, Tensor(a!) loss_rows, Tensor(b!)? grad, float cap, float div, float loss_scale, float grad_scale, float shift=0.0, Tensor? mtp_w=None) -> ()");
   m.def("adam_step(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, float lr, float beta1, float beta2, float eps, float wd, float bias1, float bias2, float grad_scale) -> ()");
@@ -687,6 +698,7 @@ TORCH_LIBRARY_IMPL(b200, CUDA, m) {
   m.impl("qkv_post_bwd", &qkv_post_bwd);
   m.impl("embed_gather", &embed_gather);
   m.impl("embed_scatter_add", &embed_scatter_add);
+  m.impl("doc_bounds", &doc_bounds);
   m.impl("cast_fp8", &cast_fp8);
   m.impl("softcap_ce", &softcap_ce);
   m.impl("adam_step", &adam_step);

@@ -412,6 +412,45 @@ __global__ void embed_scatter_add_kernel(const int* __restrict__ idx, const TS* 
   for (int k = 0; k < 4; ++k) atomicAdd(dst + k, (float)s[k]);
 }
 
+// ---------------------------------------------------------------------------------------------- document bounds
+// doc_start[i] = last position <= i whose token equals `bos` (position 0 always starts a document);
+// doc_end[i] = first such position > i, or T. One block: each thread owns a contiguous chunk, the chunk summaries are
+// combined with a max / min scan over the threads in shared memory.
+__global__ void __launch_bounds__(1024)
+doc_bounds_kernel(const long long* __restrict__ tokens, long long bos, int* __restrict__ doc_start,
+                  int* __restrict__ doc_end, int T) {
+  __shared__ int s_last[1024], s_next[1024];
+  const int tid = threadIdx.x, per = (T + blockDim.x - 1) / blockDim.x;
+  const int lo = min(tid * per, T), hi = min(lo + per, T);
+  int last = -1, first = T;
+  for (int i = lo; i < hi; ++i)
+    if (i == 0 || tokens[i] == bos) {
+      last = i;
+      if (first == T) first = i;
+    }
+  s_last[tid] = last;
+  s_next[tid] = first;
+  __syncthreads();
+  for (int off = 1; off < (int)blockDim.x; off <<= 1) {   // inclusive max scan (left) and min scan (right)
+    const int a = tid >= off ? s_last[tid - off] : -1;
+    const int b = tid + off < (int)blockDim.x ? s_next[tid + off] : T;
+    __syncthreads();
+    s_last[tid] = max(s_last[tid], a);
+    s_next[tid] = min(s_next[tid], b);
+    __syncthreads();
+  }
+  int cur = tid > 0 ? s_last[tid - 1] : 0;
+  for (int i = lo; i < hi; ++i) {
+    if (i == 0 || tokens[i] == bos) cur = i;
+    doc_start[i] = cur;
+  }
+  int nxt = tid + 1 < (int)blockDim.x ? s_next[tid + 1] : T;
+  for (int i = hi - 1; i >= lo; --i) {
+    doc_end[i] = nxt;
+    if (i == 0 || tokens[i] == bos) nxt = i;
+  }
+}
+
 // ---------------------------------------------------------------------------------------------- fp8 cast
 template <typename TI>
 __global__ void cast_fp8_kernel(const TI* __restrict__ x, uint8_t* __restrict__ out, float scale, long long n,
@@ -691,6 +730,12 @@ void embed_scatter_add(const int* idx, const void* src, int src_is_f32, float* g
   if (src_is_f32) embed_scatter_add_kernel<float><<<blocks, 256, 0, s>>>(idx, (const float*)src, grad_table, T, C);
   else embed_scatter_add_kernel<bf16><<<blocks, 256, 0, s>>>(idx, (const bf16*)src, grad_table, T, C);
   check("embed_scatter_add");
+}
+
+void doc_bounds(const long long* tokens, long long bos, int* doc_start, int* doc_end, int T, cudaStream_t s) {
+  if (T <= 0) return;
+  doc_bounds_kernel<<<1, 1024, 0, s>>>(tokens, bos, doc_start, doc_end, T);
+  check("doc_bounds");
 }
 
 void cast_fp8(const void* x, void* out, float scale, long long n, int in_kind, int out_kind, cudaStream_t s) {

@@ -44,6 +44,9 @@ void embed_scatter_add(const int* idx, const void* src, int src_is_f32, float* g
                        cudaStream_t s);
 
 // out = fp8(x * scale) ; in_kind: 0 = bf16, 1 = fp32 ; out_kind: 0 = e4m3, 1 = e5m2
+// Per-token document bounds of a packed token stream: doc_start[i] = last position <= i holding `bos` (position 0
+// always starts a document), doc_end[i] = first such position > i, or T.
+void doc_bounds(const long long* tokens, long long bos, int* doc_start, int* doc_end, int T, cudaStream_t s);
 void cast_fp8(const void* x, void* out, float scale, long long n, int in_kind, int out_kind, cudaStream_t s);
 
 // Soft-capped cross entropy over bf16 logits [T][V]:  z = cap * sigmoid(logit / div),

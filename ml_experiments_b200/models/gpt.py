@@ -25,7 +25,7 @@ import torch.nn.functional as F
 from torch import Tensor, nn
 
 from ..ops import fused as Fz
-from ..ops.attention import attention_mask, doc_bounds_from_starts
+from ..ops.attention import attention_mask, doc_bounds_from_starts, doc_bounds_from_tokens  # noqa: F401
 
 BOS_ID = 50256
 
@@ -222,7 +222,7 @@ class GPT(nn.Module):
         return self
 
     def document_bounds(self, input_seq: Tensor):
-        return doc_bounds_from_starts(input_seq == BOS_ID)
+        return doc_bounds_from_tokens(input_seq, BOS_ID)
 
     def layer_windows(self, sliding_window_num_blocks: int) -> list[int]:
         long_w = int(sliding_window_num_blocks)

@@ -53,3 +53,15 @@ def test_doc_bounds():
     ds, de = doc_bounds_from_starts(s)
     assert ds.tolist() == [0, 0, 0, 3, 3, 5, 5, 5]
     assert de.tolist() == [3, 3, 3, 5, 5, 8, 8, 8]
+
+
+def test_doc_bounds_kernel_matches_the_scan_formulation():
+    from ml_experiments_b200.ops.attention import doc_bounds_from_starts, doc_bounds_from_tokens
+
+    g = torch.Generator(device="cuda").manual_seed(3)
+    for t, p in ((1, 0.5), (77, 0.1), (1024, 0.01), (49152, 0.001), (5000, 0.0)):
+        tok = torch.randint(0, 50, (t,), device="cuda", generator=g)
+        tok = torch.where(torch.rand(t, device="cuda", generator=g) < p, torch.full_like(tok, 99), tok)
+        s0, e0 = doc_bounds_from_starts(tok == 99)
+        s1, e1 = doc_bounds_from_tokens(tok, 99)
+        assert torch.equal(s0, s1) and torch.equal(e0, e1), t
