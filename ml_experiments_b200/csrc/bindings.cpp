@@ -204,6 +204,11 @@ void embed_scatter_add(const Tensor& idx, const Tensor& src, Tensor grad_table) 
                           (int)grad_table.size(1), cur_stream());
 }
 
+void softcap_ce_set_cache(bool on, const Tensor& like) {
+  (void)like;
+  b200::softcap_ce_set_cache(on);
+}
+
 void doc_bounds(const Tensor& tokens, int64_t bos, Tensor doc_start, Tensor doc_end) {
   const c10::cuda::CUDAGuard guard(tokens.device());
   TORCH_CHECK(tokens.scalar_type() == at::kLong && tokens.is_contiguous() && tokens.dim() == 1, "doc_bounds: tokens int64 [T]");
@@ -647,6 +652,7 @@ TORCH_LIBRARY(b200, m) {
   m.def("qkv_post_bwd(Tensor dq, Tensor dk, Tensor dv, Tensor qkv, Tensor? ve, Tensor lam, Tensor cos, Tensor sin, Tensor(a!) dqkv, Tensor(b!)? dve, Tensor(c!) dlam, int H, int D, float eps) -> ()");
   m.def("embed_gather(Tensor idx, Tensor table, Tensor(a!) out, bool normalize, float eps) -> ()");
   m.def("embed_scatter_add(Tensor idx, Tensor src, Tensor(a!) grad_table) -> ()");
+  m.def("softcap_ce_set_cache(bool on, Tensor like) -> ()");
   m.def("doc_bounds(Tensor tokens, int bos, Tensor(a!) doc_start, Tensor(b!) doc_end) -> ()");
   m.def("cast_fp8(Tensor x, Tensor(a!) out, float scale) -> ()");
   m.def("softcap_ce(Tensor logits, Tensor targets, Tensor(a!) loss_rows, Tensor(b!)? grad, float cap, float div, float loss_scale, float grad_scale, float shift=0.0, Tensor? mtp_w=None) -> ()");
@@ -698,6 +704,7 @@ TORCH_LIBRARY_IMPL(b200, CUDA, m) {
   m.impl("qkv_post_bwd", &qkv_post_bwd);
   m.impl("embed_gather", &embed_gather);
   m.impl("embed_scatter_add", &embed_scatter_add);
+  m.impl("softcap_ce_set_cache", &softcap_ce_set_cache);
   m.impl("doc_bounds", &doc_bounds);
   m.impl("cast_fp8", &cast_fp8);
   m.impl("softcap_ce", &softcap_ce);

@@ -480,6 +480,8 @@ __global__ void cast_fp8_kernel(const TI* __restrict__ x, uint8_t* __restrict__ 
 // row in shared memory as bf16 (2 bytes per column; two 1024-thread blocks, i.e. two rows, per SM at a 50k vocabulary); the gradient pass
 // then reads neither the logits nor evaluates tanh / exp again: sigmoid = log(e) / cap costs one SFU op instead of two,
 // and the 0.4 % rounding of e moves the sigmoid by 1e-4.
+bool g_ce_cache = false;
+
 template <bool CACHE>
 __global__ void __launch_bounds__(CACHE ? 1024 : 512)
 softcap_ce_kernel(const bf16* __restrict__ logits, const long long* __restrict__ targets,
@@ -511,16 +513,16 @@ softcap_ce_kernel(const bf16* __restrict__ logits, const long long* __restrict__
   if (single_ignored) wsum = 0.f;
   const int nch = V / 8;
   const float L2E = 1.4426950408889634f;
+  const float ta = 0.5f * inv_div, tb = shift * ta, zc = 0.5f * cap * L2E;
   float sum = 0.f;
   for (int ci = threadIdx.x; ci < nch; ci += blockDim.x) {
     float f[8];
     load8(x + ci * 8, f);
-#pragma unroll
     float e[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const float sg = 0.5f * tanhf(0.5f * (f[i] + shift) * inv_div) + 0.5f;  // sigmoid, one MUFU under fast-math
-      e[i] = exp2f(cap * sg * L2E);
+      const float th = tanhf(fmaf(f[i], ta, tb));   // sigmoid = 0.5 * th + 0.5: one MUFU under fast-math
+      e[i] = exp2f(fmaf(th, zc, zc));               // exp(cap * sigmoid)
       sum += e[i];
     }
     if constexpr (CACHE) store8(s_cache + ci * 8, e);   // read back by the same thread: no barrier needed for the cache
@@ -548,29 +550,36 @@ softcap_ce_kernel(const bf16* __restrict__ logits, const long long* __restrict__
     loss_rows[row] = loss * loss_scale;
   }
   if (!grad) return;
-  const float inv_total = 1.f / total;
-  const float gs = grad_scale * cap * inv_div;
+  const float c1 = wsum / total;                       // probability term: wsum * exp(z) / total
+  const float gs = grad_scale * cap * inv_div;         // d z / d x = cap / div * sg * (1 - sg)
   const float inv_cap_l2e = 1.f / (cap * L2E);
   for (int ci = threadIdx.x; ci < nch; ci += blockDim.x) {
-    float f[8], g[8];
+    float f[8], g[8], dd[8];
     if constexpr (CACHE) load8(s_cache + ci * 8, f);
     else load8(x + ci * 8, f);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      float sg, ev;
+      float ev;
       if constexpr (CACHE) {
         ev = f[i];
-        sg = __log2f(ev) * inv_cap_l2e;
+        const float sg = __log2f(ev) * inv_cap_l2e;
+        dd[i] = fmaf(-sg, sg, sg) * gs;
       } else {
-        sg = 0.5f * tanhf(0.5f * (f[i] + shift) * inv_div) + 0.5f;
-        ev = exp2f(cap * sg * L2E);
+        const float th = tanhf(fmaf(f[i], ta, tb));
+        ev = exp2f(fmaf(th, zc, zc));
+        dd[i] = fmaf(-th, th, 1.f) * (0.25f * gs);     // sg * (1 - sg) = (1 - th^2) / 4
       }
-      const float pr = ev * inv_total;
-      const int col = ci * 8 + i;
-      float hot = 0.f;
+      g[i] = ev * c1 * dd[i];
+    }
+    // the one-hot terms touch at most MAXP columns of the row: test the chunk, not every element
 #pragma unroll
-      for (int k = 0; k < MAXP; ++k) hot += (col == tg[k]) ? wk[k] : 0.f;
-      g[i] = (wsum * pr - hot) * sg * (1.f - sg) * gs;
+    for (int k = 0; k < MAXP; ++k) {
+      const unsigned rel = (unsigned)(tg[k] - ci * 8);
+      if (rel < 8u) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if ((unsigned)i == rel) g[i] -= wk[k] * dd[i];
+      }
     }
     if (grad_is_bf16) {
       store8(reinterpret_cast<bf16*>(grad) + (long long)row * ld + ci * 8, g);
@@ -587,22 +596,59 @@ softcap_ce_kernel(const bf16* __restrict__ logits, const long long* __restrict__
 }
 
 // ---------------------------------------------------------------------------------------------- optimizer pieces
-template <typename TP, typename TG>
+__device__ __forceinline__ void ld4(const float* p, float (&f)[4]) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  f[0] = v.x, f[1] = v.y, f[2] = v.z, f[3] = v.w;
+}
+__device__ __forceinline__ void ld4(const bf16* p, float (&f)[4]) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+  const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+  f[0] = a.x, f[1] = a.y, f[2] = b.x, f[3] = b.y;
+}
+__device__ __forceinline__ void st4(float* p, const float (&f)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+}
+__device__ __forceinline__ void st4(bf16* p, const float (&f)[4]) {
+  uint2 u;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+  h[0] = __floats2bfloat162_rn(f[0], f[1]);
+  h[1] = __floats2bfloat162_rn(f[2], f[3]);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+
+__device__ __forceinline__ void adam_one(float& pi, float gi, float& mi, float& vi, float lr, float b1, float b2, float eps,
+                                         float wd, float bias1, float inv_sqrt_bias2) {
+  mi = b1 * mi + (1.f - b1) * gi;
+  vi = b2 * vi + (1.f - b2) * gi * gi;
+  pi -= lr * wd * pi;
+  const float denom = sqrtf(vi) * inv_sqrt_bias2 + eps;
+  pi -= (lr / bias1) * mi / denom;
+}
+
+// VEC = 4: four consecutive elements per thread with 8 / 16-byte accesses (all pointers 16-byte aligned); VEC = 1 otherwise.
+template <typename TP, typename TG, int VEC>
 __global__ void adam_kernel(TP* __restrict__ p, const TG* __restrict__ g, float* __restrict__ m,
                             float* __restrict__ v, long long n, float lr, float b1, float b2, float eps, float wd,
                             float bias1, float bias2, float grad_scale) {
-  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
   if (i >= n) return;
-  const float gi = (float)g[i] * grad_scale;
-  const float mi = b1 * m[i] + (1.f - b1) * gi;
-  const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
-  m[i] = mi;
-  v[i] = vi;
-  float pi = (float)p[i];
-  pi -= lr * wd * pi;
-  const float denom = sqrtf(vi) / sqrtf(bias2) + eps;
-  pi -= (lr / bias1) * mi / denom;
-  p[i] = (TP)pi;
+  const float isb2 = rsqrtf(bias2);
+  if (VEC == 4 && i + 4 <= n) {
+    float pf[4], gf[4], mf[4], vf[4];
+    ld4(p + i, pf); ld4(g + i, gf); ld4(m + i, mf); ld4(v + i, vf);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) adam_one(pf[k], gf[k] * grad_scale, mf[k], vf[k], lr, b1, b2, eps, wd, bias1, isb2);
+    st4(m + i, mf); st4(v + i, vf); st4(p + i, pf);
+    return;
+  }
+  for (long long j = i; j < n && j < i + VEC; ++j) {
+    float pi = (float)p[j], mi = m[j], vi = v[j];
+    adam_one(pi, (float)g[j] * grad_scale, mi, vi, lr, b1, b2, eps, wd, bias1, isb2);
+    m[j] = mi;
+    v[j] = vi;
+    p[j] = (TP)pi;
+  }
 }
 
 __global__ void muon_momentum_kernel(const float* __restrict__ g, float* __restrict__ buf, bf16* __restrict__ out,
@@ -746,13 +792,15 @@ void cast_fp8(const void* x, void* out, float scale, long long n, int in_kind, i
   check("cast_fp8");
 }
 
+void softcap_ce_set_cache(bool on) { g_ce_cache = on; }
+
 void softcap_ce(const void* logits, const long long* targets, float* loss_rows, void* grad, int grad_is_bf16, int T,
                 int V, long long ld, float cap, float div, float shift, float loss_scale, float grad_scale,
                 const float* mtp_w, int n_predict, cudaStream_t s) {
   if (V % 8 != 0 || ld % 8 != 0) throw std::runtime_error("softcap_ce: vocabulary and row pitch must be multiples of 8");
   if (n_predict < 1 || n_predict > 4) throw std::runtime_error("softcap_ce: 1 to 4 prediction offsets");
   const size_t cache_bytes = (size_t)V * 2;
-  if (grad && cache_bytes <= 110 * 1024) {   // two rows per SM
+  if (grad && g_ce_cache && cache_bytes <= 110 * 1024) {   // two rows per SM
     static bool attr_set = false;
     if (!attr_set) {
       cudaFuncSetAttribute(softcap_ce_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
@@ -771,11 +819,21 @@ void softcap_ce(const void* logits, const long long* targets, float* loss_rows, 
 void adam_step(void* p, int p_is_bf16, const void* g, int g_is_bf16, float* m, float* v, long long n, float lr,
                float beta1, float beta2, float eps, float wd, float bias1, float bias2, float grad_scale,
                cudaStream_t s) {
-  const int blocks = (int)((n + 255) / 256);
-  if (p_is_bf16 && g_is_bf16) adam_kernel<bf16, bf16><<<blocks, 256, 0, s>>>((bf16*)p, (const bf16*)g, m, v, n, lr, beta1, beta2, eps, wd, bias1, bias2, grad_scale);
-  else if (p_is_bf16) adam_kernel<bf16, float><<<blocks, 256, 0, s>>>((bf16*)p, (const float*)g, m, v, n, lr, beta1, beta2, eps, wd, bias1, bias2, grad_scale);
-  else if (g_is_bf16) adam_kernel<float, bf16><<<blocks, 256, 0, s>>>((float*)p, (const bf16*)g, m, v, n, lr, beta1, beta2, eps, wd, bias1, bias2, grad_scale);
-  else adam_kernel<float, float><<<blocks, 256, 0, s>>>((float*)p, (const float*)g, m, v, n, lr, beta1, beta2, eps, wd, bias1, bias2, grad_scale);
+  const bool vec = (((uintptr_t)p | (uintptr_t)g | (uintptr_t)m | (uintptr_t)v) & 15) == 0 && n >= 4;
+#define ADAM_LAUNCH(TP, TG)                                                                                          \
+  do {                                                                                                               \
+    if (vec)                                                                                                         \
+      adam_kernel<TP, TG, 4><<<(int)((n + 1023) / 1024), 256, 0, s>>>((TP*)p, (const TG*)g, m, v, n, lr, beta1, beta2, \
+                                                                      eps, wd, bias1, bias2, grad_scale);            \
+    else                                                                                                             \
+      adam_kernel<TP, TG, 1><<<(int)((n + 255) / 256), 256, 0, s>>>((TP*)p, (const TG*)g, m, v, n, lr, beta1, beta2, \
+                                                                    eps, wd, bias1, bias2, grad_scale);              \
+  } while (0)
+  if (p_is_bf16 && g_is_bf16) ADAM_LAUNCH(bf16, bf16);
+  else if (p_is_bf16) ADAM_LAUNCH(bf16, float);
+  else if (g_is_bf16) ADAM_LAUNCH(float, bf16);
+  else ADAM_LAUNCH(float, float);
+#undef ADAM_LAUNCH
   check("adam_step");
 }
 

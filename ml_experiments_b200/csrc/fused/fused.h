@@ -55,6 +55,8 @@ void cast_fp8(const void* x, void* out, float scale, long long n, int in_kind, i
 // {1} when null: plain next-token loss); grad (e5m2) = dL/dlogit * grad_scale.
 // Targets outside [0, V) are ignored (with n_predict = 1: zero loss and gradient). grad may be null (evaluation).
 // grad_is_bf16 selects a bf16 gradient buffer instead of e5m2.
+// Keep exp(z) of the row in shared memory between the two passes (one SFU op less per element, half the occupancy).
+void softcap_ce_set_cache(bool on);
 void softcap_ce(const void* logits, const long long* targets, float* loss_rows, void* grad, int grad_is_bf16, int T,
                 int V, long long ld, float cap, float div, float shift, float loss_scale, float grad_scale,
                 const float* mtp_w, int n_predict, cudaStream_t s);

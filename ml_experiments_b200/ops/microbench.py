@@ -67,6 +67,7 @@ def main(argv=None):
     ap.add_argument("--channels", type=int, default=2048)
     ap.add_argument("--taps", type=int, default=16)
     ap.add_argument("--epilogue", default="none", choices=["none", "relu2", "axpby"])
+    ap.add_argument("--ce-cache", action="store_true", help="softcap_ce: keep exp(z) of the row in shared memory")
     ap.add_argument("--s6-qs", default=None, help="states per thread of the S6 forward,backward kernels, e.g. 2,4")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
@@ -106,6 +107,8 @@ def main(argv=None):
         bytes_ = 2.0 * 4 * t * h * d
     elif a.op == "softcap_ce":
         from . import fused as Fz
+        from .runtime import ops as _ops
+        _ops().softcap_ce_set_cache(bool(a.ce_cache), torch.empty(0, device=dev))
         logits = torch.randn(a.tokens, a.vocab, device=dev, dtype=bf)
         tgt = torch.randint(0, a.vocab, (a.tokens,), device=dev, dtype=torch.int64)
         grad = torch.empty_like(logits)

@@ -113,10 +113,13 @@ def test_cast_fp8():
         assert torch.equal(got.float(), ref.float())
 
 
-@pytest.mark.parametrize("t,v", [(300, 50304), (64, 65536)])   # exp(z) of the row cached in shared memory / recomputed
-def test_softcap_ce(t, v):
+@pytest.mark.parametrize("cache", [False, True])               # exp(z) of the row recomputed / cached in shared memory
+@pytest.mark.parametrize("t,v", [(300, 50304), (64, 65536)])
+def test_softcap_ce(t, v, cache):
     from ml_experiments_b200.ops import fused as Fz
+    from ml_experiments_b200.ops.runtime import ops
 
+    ops().softcap_ce_set_cache(cache, torch.empty(0, device="cuda"))
     torch.manual_seed(4)
     logits = (torch.randn(t, v, device="cuda") * 3).bfloat16()
     tg = torch.randint(0, v - 47, (t,), device="cuda")
@@ -131,6 +134,7 @@ def test_softcap_ce(t, v):
     g8 = torch.empty(t, v, device="cuda", dtype=torch.float8_e5m2)
     Fz.softcap_ce(logits, tg, g8, grad_scale=1.0 / t * 2.0 ** 19)
     rel8 = ((g8.float() / 2.0 ** 19 - lf.grad).norm() / lf.grad.norm()).item()
+    ops().softcap_ce_set_cache(False, torch.empty(0, device="cuda"))
     assert rel8 < 0.15, rel8
 
 
@@ -163,3 +167,30 @@ def test_optimizer_pieces():
     ops().axpy_bf16_to_f32(p2, out, pb, -0.5)
     assert torch.allclose(p2, p - 0.5 * out.float(), rtol=1e-5, atol=1e-6)
     assert torch.equal(pb, p2.bfloat16())
+
+
+@pytest.mark.parametrize("n,off", [(4096 + 3, 0), (1001, 1), (8, 0), (3, 0)])
+@pytest.mark.parametrize("p_dtype,g_dtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16), (torch.bfloat16, torch.float32)])
+def test_adam_step_vector_and_scalar_paths(n, off, p_dtype, g_dtype):
+    """Aligned tensors take the 4-wide path with a scalar tail; views at odd offsets take the scalar kernel."""
+    from ml_experiments_b200.ops.runtime import ops
+
+    torch.manual_seed(n)
+    p0 = torch.randn(n + off, device="cuda").to(p_dtype)[off:]
+    g = (torch.randn(n + off, device="cuda") * 1e-2).to(g_dtype)[off:]
+    m = torch.zeros(n + off, device="cuda")[off:]
+    v = torch.zeros(n + off, device="cuda")[off:]
+    p = p0.clone() if off == 0 else torch.cat([p0.new_zeros(off), p0])[off:]
+    pf, mf, vf, gf = p.float().clone(), torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda"), g.float()
+    for step in range(1, 3):
+        b1c, b2c = 1 - 0.8 ** step, 1 - 0.95 ** step
+        ops().adam_step(p, g, m, v, 0.01, 0.8, 0.95, 1e-10, 0.1, b1c, b2c, 1.0)
+        mf = 0.8 * mf + 0.2 * gf
+        vf = 0.95 * vf + 0.05 * gf * gf
+        pf = pf - 0.01 * 0.1 * pf
+        pf = pf - (0.01 / b1c) * mf / (vf.sqrt() / b2c ** 0.5 + 1e-10)
+        if p_dtype == torch.bfloat16:
+            pf = pf.bfloat16().float()
+    tol = 1e-2 if p_dtype == torch.bfloat16 else 1e-4
+    assert torch.allclose(p.float(), pf, rtol=tol, atol=tol)
+    assert torch.allclose(m, mf, rtol=1e-4, atol=1e-7) and torch.allclose(v, vf, rtol=1e-4, atol=1e-10)
