@@ -480,7 +480,7 @@ __global__ void cast_fp8_kernel(const TI* __restrict__ x, uint8_t* __restrict__ 
 // row in shared memory as bf16 (2 bytes per column; two 1024-thread blocks, i.e. two rows, per SM at a 50k vocabulary); the gradient pass
 // then reads neither the logits nor evaluates tanh / exp again: sigmoid = log(e) / cap costs one SFU op instead of two,
 // and the 0.4 % rounding of e moves the sigmoid by 1e-4.
-bool g_ce_cache = false;
+bool g_ce_cache = true;   // measured 49152 x 50304: 2.32 ms cached, 2.55 ms recomputed
 
 template <bool CACHE>
 __global__ void __launch_bounds__(CACHE ? 1024 : 512)

@@ -21,6 +21,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 from torch.utils.checkpoint import checkpoint as grad_checkpoint
 
+from ..ops.attention import differential_flash_attention
 from ..ops.fused_taps import adaptive_local_gather, telephone_gather
 from ..ops.gather_conv import gather_conv, linear_resample
 from ..ops.norm_act import rms_norm_act
@@ -360,6 +361,11 @@ class CausalSelfAttention(nn.Module):
             q1, q2 = self._rope(self.q_norm(q[..., :D2])), self._rope(self.q_norm(q[..., D2:]))
             k1, k2 = self._rope(self.k_norm(k[..., :D2])), self._rope(self.k_norm(k[..., D2:]))
             lam = _diff_lambda(self.lambda_q1, self.lambda_k1, self.lambda_q2, self.lambda_k2, self.lambda_init)
+            if x.is_cuda and p == 0.0 and D <= 128:
+                # both score streams as 2H heads of one flash-attention launch (no attention dropout in this mode)
+                f1, f2 = differential_flash_attention(q1, k1, q2, k2, v)
+                out = (self.head_norm((f1.to(x.dtype) - lam * f2.to(x.dtype))) * (1 - self.lambda_init)).reshape(B, L, C)
+                return self.act(self.out_proj(out)), {}
             o1 = F.scaled_dot_product_attention(q1.transpose(1, 2), k1.transpose(1, 2), vt, is_causal=True, dropout_p=p)
             o2 = F.scaled_dot_product_attention(q2.transpose(1, 2), k2.transpose(1, 2), vt, is_causal=True, dropout_p=p)
             out = (self.head_norm(o1 - lam * o2) * (1 - self.lambda_init)).transpose(1, 2).reshape(B, L, C)

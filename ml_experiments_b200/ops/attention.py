@@ -111,3 +111,36 @@ def flash_attention(q, k, v, doc_start, doc_end, scale: float, window_blocks: in
     if not q.is_cuda:
         return attention_reference(q, k, v, doc_start, scale, window_blocks).to(q.dtype)
     return _FlashAttn.apply(q, k, v, doc_start, doc_end, float(scale), int(window_blocks))
+
+
+def differential_flash_attention(q1, k1, q2, k2, v, scale: float | None = None):
+    """Both score streams of causal differential attention in ONE launch of the flash kernel.
+
+    ``q1, k1, q2, k2 [B, L, H, d]`` and the shared values ``v [B, L, H, dv]`` -> ``(o1, o2)``, each ``[B, L, H, dv]``
+    with ``o_i = softmax(q_i k_i^T * scale, causal) v``. The two streams become ``2 H`` heads of one call: the narrower
+    q / k head dimension is zero-padded to the kernel's head size (zeros do not change a dot product), every batch
+    element is one document of the packed token stream, and the values are laid out once per stream. Gradients flow
+    through the kernel's backward; the padding and the stacking are plain autograd ops.
+    """
+    B, L, H, d = q1.shape
+    dv = v.shape[-1]
+    scale = float(scale) if scale is not None else d ** -0.5
+    D = 64 if max(d, dv) <= 64 else 128
+    if max(d, dv) > 128:
+        raise ValueError("differential_flash_attention: head dimensions up to 128")
+    T = B * L
+    bf = torch.bfloat16
+
+    def pad(t, w):
+        t = t.reshape(T, H, w).to(bf)
+        return t if w == D else torch.nn.functional.pad(t, (0, D - w))
+
+    q = torch.cat([pad(q1, d), pad(q2, d)], 1).contiguous()          # [T, 2H, D]
+    k = torch.cat([pad(k1, d), pad(k2, d)], 1).contiguous()
+    vv = pad(v, dv)
+    vv = torch.cat([vv, vv], 1).contiguous()
+    pos = torch.arange(T, device=q.device, dtype=torch.int32)
+    start = pos // L * L
+    o = flash_attention(q, k, vv, start, start + L, scale)            # [T, 2H, D]
+    o = o[..., :dv].reshape(B, L, 2, H, dv)
+    return o[:, :, 0], o[:, :, 1]

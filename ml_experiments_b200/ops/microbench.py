@@ -67,7 +67,7 @@ def main(argv=None):
     ap.add_argument("--channels", type=int, default=2048)
     ap.add_argument("--taps", type=int, default=16)
     ap.add_argument("--epilogue", default="none", choices=["none", "relu2", "axpby"])
-    ap.add_argument("--ce-cache", action="store_true", help="softcap_ce: keep exp(z) of the row in shared memory")
+    ap.add_argument("--ce-cache", type=int, default=1, help="softcap_ce: 1 keeps exp(z) of the row in shared memory, 0 recomputes it")
     ap.add_argument("--s6-qs", default=None, help="states per thread of the S6 forward,backward kernels, e.g. 2,4")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)

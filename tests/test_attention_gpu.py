@@ -65,3 +65,40 @@ def test_doc_bounds_kernel_matches_the_scan_formulation():
         s0, e0 = doc_bounds_from_starts(tok == 99)
         s1, e1 = doc_bounds_from_tokens(tok, 99)
         assert torch.equal(s0, s1) and torch.equal(e0, e1), t
+
+
+@pytest.mark.parametrize("d,dv", [(32, 64), (16, 32), (64, 128)])
+def test_differential_flash_attention_matches_two_sdpa_calls(d, dv):
+    import torch.nn.functional as F
+
+    from ml_experiments_b200.ops.attention import differential_flash_attention
+
+    torch.manual_seed(d)
+    B, L, H = 2, 200, 3
+    mk = lambda w: torch.randn(B, L, H, w, device="cuda").bfloat16().float().requires_grad_(True)
+    q1, k1, q2, k2, v = mk(d), mk(d), mk(d), mk(d), mk(dv)
+    o1, o2 = differential_flash_attention(q1, k1, q2, k2, v)
+    t = lambda x: x.transpose(1, 2)
+    r1 = t(F.scaled_dot_product_attention(t(q1), t(k1), t(v), is_causal=True))
+    r2 = t(F.scaled_dot_product_attention(t(q2), t(k2), t(v), is_causal=True))
+    assert o1.shape == r1.shape and (o1.float() - r1).abs().max() < 3e-2 and (o2.float() - r2).abs().max() < 3e-2
+    w1, w2 = torch.randn_like(r1), torch.randn_like(r2)
+    (o1.float() * w1).sum().add((o2.float() * w2).sum()).backward()
+    got = [x.grad.clone() for x in (q1, k1, q2, k2, v)]
+    for x in (q1, k1, q2, k2, v):
+        x.grad = None
+    ((r1 * w1).sum() + (r2 * w2).sum()).backward()
+    for name, g, x in zip("q1 k1 q2 k2 v".split(), got, (q1, k1, q2, k2, v)):
+        rel = ((g - x.grad).norm() / x.grad.norm()).item()
+        assert rel < 3e-2, (name, rel)
+
+
+def test_causal_self_attention_module_uses_the_flash_path_in_eval():
+    from ml_experiments_b200.models.ripple_ops import CausalSelfAttention
+
+    torch.manual_seed(0)
+    m = CausalSelfAttention(256, num_heads=4, differential=True).cuda().eval()
+    x = torch.randn(2, 160, 256, device="cuda")
+    y, _ = m(x)
+    ref, _ = m.cpu()(x.cpu())
+    assert (y.cpu() - ref).abs().max() < 5e-2 * ref.abs().max() + 1e-2
