@@ -414,41 +414,58 @@ __global__ void embed_scatter_add_kernel(const int* __restrict__ idx, const TS* 
 
 // ---------------------------------------------------------------------------------------------- document bounds
 // doc_start[i] = last position <= i whose token equals `bos` (position 0 always starts a document);
-// doc_end[i] = first such position > i, or T. One block: each thread owns a contiguous chunk, the chunk summaries are
-// combined with a max / min scan over the threads in shared memory.
+// doc_end[i] = first such position > i, or T. One block per 1024 tokens: starts inside the tile are located with warp
+// ballots; a token whose document begins (ends) outside the tile takes the block's carry, which the block finds by
+// scanning backwards (forwards) from the tile edge 1024 tokens at a time until a start turns up.
 __global__ void __launch_bounds__(1024)
 doc_bounds_kernel(const long long* __restrict__ tokens, long long bos, int* __restrict__ doc_start,
                   int* __restrict__ doc_end, int T) {
-  __shared__ int s_last[1024], s_next[1024];
-  const int tid = threadIdx.x, per = (T + blockDim.x - 1) / blockDim.x;
-  const int lo = min(tid * per, T), hi = min(lo + per, T);
-  int last = -1, first = T;
-  for (int i = lo; i < hi; ++i)
-    if (i == 0 || tokens[i] == bos) {
-      last = i;
-      if (first == T) first = i;
-    }
-  s_last[tid] = last;
-  s_next[tid] = first;
+  __shared__ int s_last[32], s_first[32], s_carry[2];
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int t0 = blockIdx.x * 1024, i = t0 + tid;
+  const bool flag = i < T && (i == 0 || tokens[i] == bos);
+  const unsigned m = __ballot_sync(0xffffffffu, flag);
+  if (lane == 0) {
+    s_last[w] = m ? t0 + w * 32 + 31 - __clz(m) : -1;
+    s_first[w] = m ? t0 + w * 32 + __ffs(m) - 1 : T;
+  }
+  if (tid == 0) s_carry[0] = -1, s_carry[1] = T;
   __syncthreads();
-  for (int off = 1; off < (int)blockDim.x; off <<= 1) {   // inclusive max scan (left) and min scan (right)
-    const int a = tid >= off ? s_last[tid - off] : -1;
-    const int b = tid + off < (int)blockDim.x ? s_next[tid + off] : T;
+  // carries: block-parallel search outside the tile, only as far as the neighbouring start. Every thread reads the
+  // carry, then a barrier, then the (uniform) exit test: no warp can publish a hit before all have read.
+  for (int base = t0 - 1024;; base -= 1024) {   // backwards
+    const int c = s_carry[0];
     __syncthreads();
-    s_last[tid] = max(s_last[tid], a);
-    s_next[tid] = min(s_next[tid], b);
+    if (c >= 0 || base <= -1024) break;
+    const int j = base + tid;
+    const bool f = j >= 0 && (j == 0 || tokens[j] == bos);
+    const unsigned mm = __ballot_sync(0xffffffffu, f);
+    if (lane == 0 && mm) atomicMax(&s_carry[0], base + w * 32 + 31 - __clz(mm));
     __syncthreads();
   }
-  int cur = tid > 0 ? s_last[tid - 1] : 0;
-  for (int i = lo; i < hi; ++i) {
-    if (i == 0 || tokens[i] == bos) cur = i;
-    doc_start[i] = cur;
+  for (int base = t0 + 1024;; base += 1024) {   // forwards
+    const int c = s_carry[1];
+    __syncthreads();
+    if (c < T || base >= T) break;
+    const int j = base + tid;
+    const bool f = j < T && tokens[j] == bos;
+    const unsigned mm = __ballot_sync(0xffffffffu, f);
+    if (lane == 0 && mm) atomicMin(&s_carry[1], base + w * 32 + __ffs(mm) - 1);
+    __syncthreads();
   }
-  int nxt = tid + 1 < (int)blockDim.x ? s_next[tid + 1] : T;
-  for (int i = hi - 1; i >= lo; --i) {
-    doc_end[i] = nxt;
-    if (i == 0 || tokens[i] == bos) nxt = i;
-  }
+  if (i >= T) return;
+  // last start <= i: own warp (lanes <= lane), else earlier warps of the tile, else the carry
+  const unsigned lo = m & (0xffffffffu >> (31 - lane));
+  int st = lo ? t0 + w * 32 + 31 - __clz(lo) : -1;
+  for (int q = w - 1; st < 0 && q >= 0; --q) st = s_last[q];
+  if (st < 0) st = s_carry[0];
+  doc_start[i] = max(st, 0);
+  // first start > i
+  const unsigned hi = lane == 31 ? 0u : (m & (0xffffffffu << (lane + 1)));
+  int en = hi ? t0 + w * 32 + __ffs(hi) - 1 : T;
+  for (int q = w + 1; en >= T && q < 32; ++q) en = s_first[q];
+  if (en >= T) en = s_carry[1];
+  doc_end[i] = min(en, T);
 }
 
 // ---------------------------------------------------------------------------------------------- fp8 cast
@@ -780,7 +797,7 @@ void embed_scatter_add(const int* idx, const void* src, int src_is_f32, float* g
 
 void doc_bounds(const long long* tokens, long long bos, int* doc_start, int* doc_end, int T, cudaStream_t s) {
   if (T <= 0) return;
-  doc_bounds_kernel<<<1, 1024, 0, s>>>(tokens, bos, doc_start, doc_end, T);
+  doc_bounds_kernel<<<(T + 1023) / 1024, 1024, 0, s>>>(tokens, bos, doc_start, doc_end, T);
   check("doc_bounds");
 }
 
