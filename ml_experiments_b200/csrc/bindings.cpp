@@ -152,14 +152,18 @@ void norm_bwd_add(const Tensor& dy, const Tensor& x, const c10::optional<Tensor>
 
 void mix_bwd(const Tensor& dmix, const Tensor& x, const Tensor& x0, const c10::optional<Tensor>& skip,
              const Tensor& lam, const c10::optional<Tensor>& skip_w, Tensor dx, const c10::optional<Tensor>& dskip,
-             Tensor dx0_acc, Tensor dlam, const c10::optional<Tensor>& dskip_w) {
+             Tensor dx0_acc, Tensor dlam, const c10::optional<Tensor>& dskip_w, const c10::optional<Tensor>& dx_add) {
   const c10::cuda::CUDAGuard guard(x.device());
   chk_bf16c(dmix, "dmix"); chk_bf16c(x, "x"); chk_bf16c(x0, "x0"); chk_bf16c(dx, "dx");
+  if (dx_add.has_value()) {
+    chk_bf16c(*dx_add, "dx_add");
+    TORCH_CHECK(dx_add->numel() == x.numel(), "dx_add: same size as x");
+  }
   TORCH_CHECK(dx0_acc.scalar_type() == at::kFloat && dx0_acc.is_contiguous(), "dx0_acc: contiguous fp32");
   const int C = (int)x.size(-1), R = (int)(x.numel() / C);
   b200::mix_bwd(dmix.data_ptr(), x.data_ptr(), x0.data_ptr(), optp(skip), lam.data_ptr<float>(), optf(skip_w),
                 dx.data_ptr(), dskip.has_value() ? dskip->data_ptr() : nullptr, dx0_acc.data_ptr<float>(),
-                dlam.data_ptr<float>(), dskip_w.has_value() ? dskip_w->data_ptr<float>() : nullptr, R, C, cur_stream());
+                dlam.data_ptr<float>(), dskip_w.has_value() ? dskip_w->data_ptr<float>() : nullptr, optp(dx_add), R, C, cur_stream());
 }
 
 void qkv_post_fwd(const Tensor& qkv, const c10::optional<Tensor>& ve, const Tensor& lam, const Tensor& cos,
@@ -194,13 +198,15 @@ void embed_gather(const Tensor& idx, const Tensor& table, Tensor out, bool norma
                      normalize, (float)eps, cur_stream());
 }
 
-void embed_scatter_add(const Tensor& idx, const Tensor& src, Tensor grad_table) {
+void embed_scatter_add(const Tensor& idx, const Tensor& src, Tensor grad_table, const c10::optional<Tensor>& src2) {
   const c10::cuda::CUDAGuard guard(src.device());
   TORCH_CHECK(idx.scalar_type() == at::kInt && idx.is_contiguous() && src.is_contiguous(), "embed_scatter_add: layout");
   TORCH_CHECK(grad_table.scalar_type() == at::kFloat && grad_table.is_contiguous(), "grad_table: contiguous fp32");
   const bool f32 = src.scalar_type() == at::kFloat;
   TORCH_CHECK(f32 || src.scalar_type() == at::kBFloat16, "src: fp32 or bf16");
-  b200::embed_scatter_add(idx.data_ptr<int>(), src.data_ptr(), f32, grad_table.data_ptr<float>(), (int)idx.numel(),
+  if (src2.has_value())
+    TORCH_CHECK(src2->scalar_type() == src.scalar_type() && src2->is_contiguous() && src2->sizes() == src.sizes(), "src2: same dtype and shape as src");
+  b200::embed_scatter_add(idx.data_ptr<int>(), src.data_ptr(), src2.has_value() ? src2->data_ptr() : nullptr, f32, grad_table.data_ptr<float>(), (int)idx.numel(),
                           (int)grad_table.size(1), cur_stream());
 }
 
@@ -647,11 +653,11 @@ TORCH_LIBRARY(b200, m) {
   m.def("attn_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor d_o, Tensor lse, Tensor(a!) delta, Tensor(b!) dq_acc, Tensor(c!) dk, Tensor(d!) dv, Tensor doc_start, Tensor doc_end, float scale, int window_blocks, Tensor status) -> ()");
   m.def("mix_norm_fwd(Tensor x, Tensor? x0, Tensor? skip, Tensor? lam, Tensor? skip_w, Tensor(a!)? x_mix, Tensor(b!)? xn, float eps) -> ()");
   m.def("norm_bwd_add(Tensor dy, Tensor x, Tensor? dres, Tensor(a!) out, float eps) -> ()");
-  m.def("mix_bwd(Tensor dmix, Tensor x, Tensor x0, Tensor? skip, Tensor lam, Tensor? skip_w, Tensor(a!) dx, Tensor(b!)? dskip, Tensor(c!) dx0_acc, Tensor(d!) dlam, Tensor(e!)? dskip_w) -> ()");
+  m.def("mix_bwd(Tensor dmix, Tensor x, Tensor x0, Tensor? skip, Tensor lam, Tensor? skip_w, Tensor(a!) dx, Tensor(b!)? dskip, Tensor(c!) dx0_acc, Tensor(d!) dlam, Tensor(e!)? dskip_w, Tensor? dx_add=None) -> ()");
   m.def("qkv_post_fwd(Tensor qkv, Tensor? ve, Tensor lam, Tensor cos, Tensor sin, Tensor(a!) out, int H, int D, float eps) -> ()");
   m.def("qkv_post_bwd(Tensor dq, Tensor dk, Tensor dv, Tensor qkv, Tensor? ve, Tensor lam, Tensor cos, Tensor sin, Tensor(a!) dqkv, Tensor(b!)? dve, Tensor(c!) dlam, int H, int D, float eps) -> ()");
   m.def("embed_gather(Tensor idx, Tensor table, Tensor(a!) out, bool normalize, float eps) -> ()");
-  m.def("embed_scatter_add(Tensor idx, Tensor src, Tensor(a!) grad_table) -> ()");
+  m.def("embed_scatter_add(Tensor idx, Tensor src, Tensor(a!) grad_table, Tensor? src2=None) -> ()");
   m.def("softcap_ce_set_cache(bool on, Tensor like) -> ()");
   m.def("doc_bounds(Tensor tokens, int bos, Tensor(a!) doc_start, Tensor(b!) doc_end) -> ()");
   m.def("cast_fp8(Tensor x, Tensor(a!) out, float scale) -> ()");

@@ -36,6 +36,27 @@ __device__ __forceinline__ void store8(bf16* p, const float (&f)[8]) {
   for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
   *reinterpret_cast<uint4*>(p) = u;
 }
+__device__ __forceinline__ void ld4(const float* p, float (&f)[4]) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  f[0] = v.x, f[1] = v.y, f[2] = v.z, f[3] = v.w;
+}
+__device__ __forceinline__ void ld4(const bf16* p, float (&f)[4]) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+  const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+  f[0] = a.x, f[1] = a.y, f[2] = b.x, f[3] = b.y;
+}
+__device__ __forceinline__ void st4(float* p, const float (&f)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+}
+__device__ __forceinline__ void st4(bf16* p, const float (&f)[4]) {
+  uint2 u;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+  h[0] = __floats2bfloat162_rn(f[0], f[1]);
+  h[1] = __floats2bfloat162_rn(f[2], f[3]);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+
 __device__ __forceinline__ void round8(float (&f)[8]) {
 #pragma unroll
   for (int i = 0; i < 8; ++i) f[i] = __bfloat162float(__float2bfloat16_rn(f[i]));
@@ -152,7 +173,7 @@ __global__ void __launch_bounds__(kRowThreads)
 mix_bwd_kernel(const bf16* __restrict__ dmix, const bf16* __restrict__ x, const bf16* __restrict__ x0,
                const bf16* __restrict__ skip, const float* __restrict__ lam, const float* __restrict__ skip_w,
                bf16* __restrict__ dx, bf16* __restrict__ dskip, float* __restrict__ dx0_acc, float* __restrict__ dlam,
-               float* __restrict__ dskip_w, int R, int C) {
+               float* __restrict__ dskip_w, const bf16* __restrict__ dx_add, int R, int C) {
   __shared__ float red[3][kRowThreads / 32];
   const int warp_in_block = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -185,6 +206,12 @@ mix_bwd_kernel(const bf16* __restrict__ dmix, const bf16* __restrict__ x, const 
           a0 = fmaf(g[i], xv[i], a0);
           a1 = fmaf(g[i], zv[i], a1);
           o[i] = l0 * g[i];
+        }
+        if (dx_add) {   // a second gradient of the same activation (the U-net skip path), added before the rounding
+          float av[8];
+          load8(dx_add + base + c, av);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] += av[i];
         }
         store8(dx + base + c, o);
         float4* acc = reinterpret_cast<float4*>(dx0_acc + base + c);
@@ -399,17 +426,23 @@ embed_gather_kernel(const int* __restrict__ idx, const bf16* __restrict__ table,
   }
 }
 
+// grad_table[idx[t]] += src[t] (+ src2[t]): one 16-byte vector atomic per four channels.
 template <typename TS>
 __global__ void embed_scatter_add_kernel(const int* __restrict__ idx, const TS* __restrict__ src,
-                                         float* __restrict__ grad_table, int T, int C) {
+                                         const TS* __restrict__ src2, float* __restrict__ grad_table, int T, int C) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const int cq = C / 4;
   if (i >= (long long)T * cq) return;
   const int t = (int)(i / cq), c = (int)(i % cq) * 4;
-  float* dst = grad_table + (long long)idx[t] * C + c;
-  const TS* s = src + (long long)t * C + c;
+  float f[4];
+  ld4(src + (long long)t * C + c, f);
+  if (src2) {
+    float h[4];
+    ld4(src2 + (long long)t * C + c, h);
 #pragma unroll
-  for (int k = 0; k < 4; ++k) atomicAdd(dst + k, (float)s[k]);
+    for (int k = 0; k < 4; ++k) f[k] += h[k];
+  }
+  atomicAdd(reinterpret_cast<float4*>(grad_table + (long long)idx[t] * C + c), make_float4(f[0], f[1], f[2], f[3]));
 }
 
 // ---------------------------------------------------------------------------------------------- document bounds
@@ -613,27 +646,6 @@ softcap_ce_kernel(const bf16* __restrict__ logits, const long long* __restrict__
 }
 
 // ---------------------------------------------------------------------------------------------- optimizer pieces
-__device__ __forceinline__ void ld4(const float* p, float (&f)[4]) {
-  const float4 v = *reinterpret_cast<const float4*>(p);
-  f[0] = v.x, f[1] = v.y, f[2] = v.z, f[3] = v.w;
-}
-__device__ __forceinline__ void ld4(const bf16* p, float (&f)[4]) {
-  const uint2 u = *reinterpret_cast<const uint2*>(p);
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
-  const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
-  f[0] = a.x, f[1] = a.y, f[2] = b.x, f[3] = b.y;
-}
-__device__ __forceinline__ void st4(float* p, const float (&f)[4]) {
-  *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
-}
-__device__ __forceinline__ void st4(bf16* p, const float (&f)[4]) {
-  uint2 u;
-  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
-  h[0] = __floats2bfloat162_rn(f[0], f[1]);
-  h[1] = __floats2bfloat162_rn(f[2], f[3]);
-  *reinterpret_cast<uint2*>(p) = u;
-}
-
 __device__ __forceinline__ void adam_one(float& pi, float gi, float& mi, float& vi, float lr, float b1, float b2, float eps,
                                          float wd, float bias1, float inv_sqrt_bias2) {
   mi = b1 * mi + (1.f - b1) * gi;
@@ -747,12 +759,12 @@ void norm_bwd_add(const void* dy, const void* x, const void* dres, void* out, in
 }
 
 void mix_bwd(const void* dmix, const void* x, const void* x0, const void* skip, const float* lam,
-             const float* skip_w, void* dx, void* dskip, float* dx0_acc, float* dlam, float* dskip_w, int R, int C,
-             cudaStream_t s) {
+             const float* skip_w, void* dx, void* dskip, float* dx0_acc, float* dlam, float* dskip_w, const void* dx_add,
+             int R, int C, cudaStream_t s) {
   const int blocks = 148 * 4;
   DISPATCH_NCH(C, (mix_bwd_kernel<N_><<<blocks, kRowThreads, 0, s>>>((const bf16*)dmix, (const bf16*)x, (const bf16*)x0,
                                                                     (const bf16*)skip, lam, skip_w, (bf16*)dx,
-                                                                    (bf16*)dskip, dx0_acc, dlam, dskip_w, R, C)));
+                                                                    (bf16*)dskip, dx0_acc, dlam, dskip_w, (const bf16*)dx_add, R, C)));
   check("mix_bwd");
 }
 
@@ -785,13 +797,13 @@ void embed_gather(const int* idx, const void* table, void* out, int T, int C, in
   check("embed_gather");
 }
 
-void embed_scatter_add(const int* idx, const void* src, int src_is_f32, float* grad_table, int T, int C,
+void embed_scatter_add(const int* idx, const void* src, const void* src2, int src_is_f32, float* grad_table, int T, int C,
                        cudaStream_t s) {
   if (C % 4 != 0) throw std::runtime_error("embed_scatter_add: C must be a multiple of 4");
   const long long n = (long long)T * (C / 4);
   const int blocks = (int)((n + 255) / 256);
-  if (src_is_f32) embed_scatter_add_kernel<float><<<blocks, 256, 0, s>>>(idx, (const float*)src, grad_table, T, C);
-  else embed_scatter_add_kernel<bf16><<<blocks, 256, 0, s>>>(idx, (const bf16*)src, grad_table, T, C);
+  if (src_is_f32) embed_scatter_add_kernel<float><<<blocks, 256, 0, s>>>(idx, (const float*)src, (const float*)src2, grad_table, T, C);
+  else embed_scatter_add_kernel<bf16><<<blocks, 256, 0, s>>>(idx, (const bf16*)src, (const bf16*)src2, grad_table, T, C);
   check("embed_scatter_add");
 }
 

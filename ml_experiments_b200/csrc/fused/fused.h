@@ -22,8 +22,8 @@ void norm_bwd_add(const void* dy, const void* x, const void* dres, void* out, in
 //   dx = lam0 * dmix ; dskip = lam0 * skip_w * dmix ; dx0_acc += lam1 * dmix  (fp32 accumulator)
 //   dlam[0] += sum(dmix * (x + skip_w*skip)) ; dlam[1] += sum(dmix * x0) ; dskip_w += sum(lam0 * dmix * skip)
 void mix_bwd(const void* dmix, const void* x, const void* x0, const void* skip, const float* lam,
-             const float* skip_w, void* dx, void* dskip, float* dx0_acc, float* dlam, float* dskip_w, int R, int C,
-             cudaStream_t s);
+             const float* skip_w, void* dx, void* dskip, float* dx0_acc, float* dlam, float* dskip_w, const void* dx_add,
+             int R, int C, cudaStream_t s);   // dx_add (bf16, optional) is added to dx before it is rounded
 
 // qkv [T][3][H][D] -> out [T][3][H][D]:  q,k <- rope(rmsnorm_head(q,k)) ; v <- lam[0]*v + lam[1]*ve
 // cos/sin : fp32 [>=T][D/2], position = row index. ve ([T][H*D]) may be null.
@@ -39,8 +39,8 @@ void qkv_post_bwd(const float* dq, const void* dk, const void* dv, const void* q
 // out[t] = table[idx[t]]  (bf16 rows of C elements); normalize != 0 applies rmsnorm to each gathered row.
 void embed_gather(const int* idx, const void* table, void* out, int T, int C, int normalize, float eps,
                   cudaStream_t s);
-// grad_table[idx[t]] += src[t]   (fp32 atomics; src bf16 or fp32 selected by src_is_f32)
-void embed_scatter_add(const int* idx, const void* src, int src_is_f32, float* grad_table, int T, int C,
+// grad_table[idx[t]] += src[t] (+ src2[t] when given)   (16-byte fp32 vector atomics; src bf16 or fp32 by src_is_f32)
+void embed_scatter_add(const int* idx, const void* src, const void* src2, int src_is_f32, float* grad_table, int T, int C,
                        cudaStream_t s);
 
 // out = fp8(x * scale) ; in_kind: 0 = bf16, 1 = fp32 ; out_kind: 0 = e4m3, 1 = e5m2

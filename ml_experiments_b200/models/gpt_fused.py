@@ -127,6 +127,7 @@ def _forward_backward(model, input_seq: Tensor, target_seq: Tensor, swb: int, ne
     dskip_w = torch.zeros_like(model.skip_weights)
     dskips: dict[int, Tensor] = {}
     ve_grads = [None] * len(model.value_embeds.embed)
+    dve_wait: dict[int, Tensor] = {}
     dq_acc = None
     for i in reversed(range(len(model.blocks))):
         blk, s = model.blocks[i], saved[i]
@@ -158,9 +159,14 @@ def _forward_backward(model, input_seq: Tensor, target_seq: Tensor, swb: int, ne
             o.qkv_post_bwd(dq, dk, dv, s.qkv, ve, a.lambdas, cos, sin, dqkv, dve, dlam, H, D, EPS)
             put(a.lambdas, dlam)
             if dve is not None:
-                if ve_grads[vi] is None:
-                    ve_grads[vi] = torch.zeros(model.value_embeds.embed[vi].weight.shape, dtype=torch.float32, device=dev)
-                o.embed_scatter_add(idx, dve, ve_grads[vi])
+                # a value embedding feeds several layers: the first gradient waits for the next one and the two are
+                # summed inside one scatter; what is still waiting at the end is flushed below
+                if vi in dve_wait:
+                    if ve_grads[vi] is None:
+                        ve_grads[vi] = torch.zeros(model.value_embeds.embed[vi].weight.shape, dtype=torch.float32, device=dev)
+                    o.embed_scatter_add(idx, dve, ve_grads[vi], dve_wait.pop(vi))
+                else:
+                    dve_wait[vi] = dve
             dxn = G.gemm(dqkv, w16(a.qkv_w).view(3 * HD, C), b_mn=True)
             put(a.qkv_w, _wgrad(dqkv, s.xn, a.qkv_w.shape))
             dx_mix = Fz.norm_bwd_add(dxn, s.x_mix, dx_a, EPS)
@@ -168,14 +174,16 @@ def _forward_backward(model, input_seq: Tensor, target_seq: Tensor, swb: int, ne
             dx_mix = dx_a
         dx_prev = torch.empty_like(dx_mix)
         dlam_b = torch.zeros(2, dtype=torch.float32, device=dev)
+        # the skip gradient waiting for the layer below is added inside this kernel, before dx_prev is rounded
+        add_in = dskips.pop(i - 1, None)
         if s.skip is not None:
             dsk = torch.empty_like(dx_mix)
             j = i - enc
             o.mix_bwd(dx_mix, s.x_in, x0, s.skip, blk.lambdas, model.skip_weights[j:j + 1], dx_prev, dsk, dx0_acc, dlam_b,
-                      dskip_w[j:j + 1])
+                      dskip_w[j:j + 1], add_in)
             dskips[s.skip_idx] = dsk
         else:
-            o.mix_bwd(dx_mix, s.x_in, x0, None, blk.lambdas, None, dx_prev, None, dx0_acc, dlam_b, None)
+            o.mix_bwd(dx_mix, s.x_in, x0, None, blk.lambdas, None, dx_prev, None, dx0_acc, dlam_b, None, add_in)
         put(blk.lambdas, dlam_b)
         dx = dx_prev
         saved[i] = None
@@ -187,6 +195,10 @@ def _forward_backward(model, input_seq: Tensor, target_seq: Tensor, swb: int, ne
     g_embed = torch.zeros(model.embed.weight.shape, dtype=torch.float32, device=dev)
     o.embed_scatter_add(idx, d_e, g_embed)
     put(model.embed.weight, g_embed)
+    for vi, dve in dve_wait.items():
+        if ve_grads[vi] is None:
+            ve_grads[vi] = torch.zeros(model.value_embeds.embed[vi].weight.shape, dtype=torch.float32, device=dev)
+        o.embed_scatter_add(idx, dve, ve_grads[vi])
     for vi, e in enumerate(model.value_embeds.embed):
         if ve_grads[vi] is not None:
             put(e.weight, ve_grads[vi])

@@ -194,3 +194,20 @@ def test_adam_step_vector_and_scalar_paths(n, off, p_dtype, g_dtype):
     tol = 1e-2 if p_dtype == torch.bfloat16 else 1e-4
     assert torch.allclose(p.float(), pf, rtol=tol, atol=tol)
     assert torch.allclose(m, mf, rtol=1e-4, atol=1e-7) and torch.allclose(v, vf, rtol=1e-4, atol=1e-10)
+
+
+def test_embed_scatter_add_two_sources():
+    from ml_experiments_b200.ops.runtime import ops
+
+    torch.manual_seed(9)
+    t, c, rows = 1000, 768, 64
+    idx = torch.randint(0, rows, (t,), device="cuda", dtype=torch.int32)
+    a = torch.randn(t, c, device="cuda").bfloat16()
+    b = torch.randn(t, c, device="cuda").bfloat16()
+    table = torch.zeros(rows, c, device="cuda")
+    ops().embed_scatter_add(idx, a, table, b)
+    ref = torch.zeros(rows, c, device="cuda").index_add_(0, idx.long(), a.float() + b.float())
+    assert torch.allclose(table, ref, rtol=1e-4, atol=1e-3)
+    table.zero_()
+    ops().embed_scatter_add(idx, a.float(), table)
+    assert torch.allclose(table, torch.zeros(rows, c, device="cuda").index_add_(0, idx.long(), a.float()), rtol=1e-4, atol=1e-3)
