@@ -303,6 +303,34 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, long long
   if (lane == 0) delta[(long long)h * T + t] = acc;
 }
 
+// Same with 16-byte loads: D / 8 adjacent lanes own a row, a warp covers 32 / (D / 8) rows (needs 16-byte aligned rows).
+template <int D>
+__global__ void attn_delta_vec_kernel(const __nv_bfloat16* __restrict__ o, long long ld_o,
+                                      const __nv_bfloat16* __restrict__ d_o, long long ld_do,
+                                      float* __restrict__ delta, int T, int H) {
+  constexpr int LPR = D / 8;
+  const long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / LPR;
+  const int sub = threadIdx.x % LPR;
+  float acc = 0.f;
+  int t = 0, h = 0;
+  const bool on = row < (long long)T * H;
+  if (on) {
+    t = (int)(row / H), h = (int)(row % H);
+    const uint4 ua = *reinterpret_cast<const uint4*>(o + (long long)t * ld_o + h * D + sub * 8);
+    const uint4 ub = *reinterpret_cast<const uint4*>(d_o + (long long)t * ld_do + h * D + sub * 8);
+    const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&ua);
+    const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&ub);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 x = __bfloat1622float2(pa[i]), y = __bfloat1622float2(pb[i]);
+      acc = fmaf(x.x, y.x, fmaf(x.y, y.y, acc));
+    }
+  }
+#pragma unroll
+  for (int s = LPR / 2; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+  if (on && sub == 0) delta[(long long)h * T + t] = acc;
+}
+
 // ------------------------------------------------------------------------------------------------
 // backward
 // ------------------------------------------------------------------------------------------------
@@ -702,8 +730,17 @@ void attn_delta_sm100(const AttnArgs& a) {
   const int blocks = (int)((warps * 32 + threads - 1) / threads);
   auto* o = reinterpret_cast<const __nv_bfloat16*>(a.o);
   auto* d_o = reinterpret_cast<const __nv_bfloat16*>(a.d_o);
-  if (a.D == 128) attn_delta_kernel<128><<<blocks, threads, 0, a.stream>>>(o, a.ld_o, d_o, a.ld_do, a.delta, a.T, a.H);
-  else            attn_delta_kernel<64><<<blocks, threads, 0, a.stream>>>(o, a.ld_o, d_o, a.ld_do, a.delta, a.T, a.H);
+  const bool aligned = (((uintptr_t)o | (uintptr_t)d_o) & 15) == 0 && a.ld_o % 8 == 0 && a.ld_do % 8 == 0;
+  if (aligned) {
+    const long long lanes = warps * (a.D / 8);
+    const int vblocks = (int)((lanes + threads - 1) / threads);
+    if (a.D == 128) attn_delta_vec_kernel<128><<<vblocks, threads, 0, a.stream>>>(o, a.ld_o, d_o, a.ld_do, a.delta, a.T, a.H);
+    else            attn_delta_vec_kernel<64><<<vblocks, threads, 0, a.stream>>>(o, a.ld_o, d_o, a.ld_do, a.delta, a.T, a.H);
+  } else if (a.D == 128) {
+    attn_delta_kernel<128><<<blocks, threads, 0, a.stream>>>(o, a.ld_o, d_o, a.ld_do, a.delta, a.T, a.H);
+  } else {
+    attn_delta_kernel<64><<<blocks, threads, 0, a.stream>>>(o, a.ld_o, d_o, a.ld_do, a.delta, a.T, a.H);
+  }
   check_launch("attn_delta launch");
 }
 
