@@ -274,8 +274,11 @@ void muon_momentum(const Tensor& g, Tensor buf, Tensor out, Tensor sumsq, double
   TORCH_CHECK(g.is_contiguous() && buf.is_contiguous() && out.is_contiguous(), "muon_momentum: contiguous");
   TORCH_CHECK(g.scalar_type() == at::kFloat && buf.scalar_type() == at::kFloat && out.scalar_type() == at::kBFloat16 &&
               sumsq.scalar_type() == at::kFloat, "muon_momentum: dtypes");
-  b200::muon_momentum(g.data_ptr<float>(), buf.data_ptr<float>(), out.data_ptr(), sumsq.data_ptr<float>(), g.numel(),
-                      (float)mu, nesterov, (float)grad_scale, cur_stream());
+  const int64_t nmat = sumsq.numel();   // g, buf, out are stacks of nmat equally sized matrices
+  TORCH_CHECK(nmat >= 1 && g.numel() % nmat == 0 && buf.numel() == g.numel() && out.numel() == g.numel() && sumsq.is_contiguous(),
+              "muon_momentum: g, buf, out [nmat, n] with sumsq [nmat]");
+  b200::muon_momentum(g.data_ptr<float>(), buf.data_ptr<float>(), out.data_ptr(), sumsq.data_ptr<float>(), g.numel() / nmat,
+                      (int)nmat, (float)mu, nesterov, (float)grad_scale, cur_stream());
 }
 
 void scale_by_inv_norm(Tensor x, const Tensor& sumsq, double eps) {

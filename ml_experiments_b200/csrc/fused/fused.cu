@@ -680,20 +680,42 @@ __global__ void adam_kernel(TP* __restrict__ p, const TG* __restrict__ g, float*
   }
 }
 
+// grid (blocks per matrix, matrices): matrix blockIdx.y of the contiguous stacks g / buf / out [nmat][n], one sum of
+// squares per matrix. Four elements per thread (`vec`) when n % 4 == 0 and the stacks are 16-byte aligned.
 __global__ void muon_momentum_kernel(const float* __restrict__ g, float* __restrict__ buf, bf16* __restrict__ out,
                                      float* __restrict__ sumsq, long long n, float mu, int nesterov,
-                                     float grad_scale) {
+                                     float grad_scale, int vec) {
   __shared__ float red[8];
+  const long long off = (long long)blockIdx.y * n;
+  g += off; buf += off; out += off;
   float acc = 0.f;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-    const float gi = g[i] * grad_scale;
-    const float b = mu * buf[i] + (1.f - mu) * gi;
-    buf[i] = b;
-    const float u = nesterov ? (1.f - mu) * gi + mu * b : b;
-    const bf16 ub = __float2bfloat16_rn(u);
-    out[i] = ub;
-    const float uf = __bfloat162float(ub);
-    acc = fmaf(uf, uf, acc);
+  if (vec) {
+    for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += (long long)gridDim.x * blockDim.x * 4) {
+      float gv[4], bv[4], uv[4];
+      ld4(g + i, gv);
+      ld4(buf + i, bv);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float gi = gv[k] * grad_scale;
+        bv[k] = mu * bv[k] + (1.f - mu) * gi;
+        const float u = nesterov ? (1.f - mu) * gi + mu * bv[k] : bv[k];
+        uv[k] = __bfloat162float(__float2bfloat16_rn(u));
+        acc = fmaf(uv[k], uv[k], acc);
+      }
+      st4(buf + i, bv);
+      st4(out + i, uv);
+    }
+  } else {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+      const float gi = g[i] * grad_scale;
+      const float b = mu * buf[i] + (1.f - mu) * gi;
+      buf[i] = b;
+      const float u = nesterov ? (1.f - mu) * gi + mu * b : b;
+      const bf16 ub = __float2bfloat16_rn(u);
+      out[i] = ub;
+      const float uf = __bfloat162float(ub);
+      acc = fmaf(uf, uf, acc);
+    }
   }
   acc = warp_sum(acc);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
@@ -701,7 +723,7 @@ __global__ void muon_momentum_kernel(const float* __restrict__ g, float* __restr
   if (threadIdx.x == 0) {
     float t = 0.f;
     for (int i = 0; i < (int)(blockDim.x >> 5); ++i) t += red[i];
-    atomicAdd(sumsq, t);
+    atomicAdd(sumsq + blockIdx.y, t);
   }
 }
 
@@ -866,11 +888,14 @@ void adam_step(void* p, int p_is_bf16, const void* g, int g_is_bf16, float* m, f
   check("adam_step");
 }
 
-void muon_momentum(const float* g, float* buf, void* out_bf16, float* sumsq, long long n, float mu, int nesterov,
-                   float grad_scale, cudaStream_t s) {
-  int blocks = (int)((n + 255) / 256);
-  if (blocks > 148 * 8) blocks = 148 * 8;
-  muon_momentum_kernel<<<blocks, 256, 0, s>>>(g, buf, (bf16*)out_bf16, sumsq, n, mu, nesterov, grad_scale);
+void muon_momentum(const float* g, float* buf, void* out_bf16, float* sumsq, long long n, int nmat, float mu,
+                   int nesterov, float grad_scale, cudaStream_t s) {
+  if (nmat <= 0 || n <= 0) return;
+  int blocks = (int)((n / 4 + 255) / 256) + 1;
+  const int cap = (148 * 8 + nmat - 1) / nmat;
+  if (blocks > cap) blocks = cap;
+  const int vec = (n & 3) == 0 && ((((uintptr_t)g | (uintptr_t)buf) & 15) == 0) && (((uintptr_t)out_bf16 & 7) == 0);
+  muon_momentum_kernel<<<dim3(blocks, nmat), 256, 0, s>>>(g, buf, (bf16*)out_bf16, sumsq, n, mu, nesterov, grad_scale, vec);
   check("muon_momentum");
 }
 

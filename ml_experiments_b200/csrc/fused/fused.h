@@ -70,8 +70,8 @@ void adam_step(void* p, int p_is_bf16, const void* g, int g_is_bf16, float* m, f
 
 // Muon momentum: buf = mu*buf + (1-mu)*g ; u = nesterov ? (1-mu)*g + mu*buf : buf ; out_bf16 = u ; also
 // accumulates sum(u^2) into sumsq[0] (fp32) for the Frobenius normalisation.
-void muon_momentum(const float* g, float* buf, void* out_bf16, float* sumsq, long long n, float mu, int nesterov,
-                   float grad_scale, cudaStream_t s);
+void muon_momentum(const float* g, float* buf, void* out_bf16, float* sumsq, long long n, int nmat, float mu,
+                   int nesterov, float grad_scale, cudaStream_t s);   // stacks [nmat][n], sumsq [nmat]
 // x_bf16 *= 1 / (sqrt(sumsq[0]) + eps)
 void scale_by_inv_norm(void* x_bf16, const float* sumsq, long long n, float eps, cudaStream_t s);
 // p (fp32) += alpha * u (bf16) ; optionally also writes the bf16 copy p_bf16 used by the forward GEMMs

@@ -62,33 +62,42 @@ class Muon(torch.optim.Optimizer):
         for (r, c), plist in by_shape.items():
             total = sum(n for _, n in plist)
             dev = plist[0][0].device
-            stack = torch.empty(total, r, c, dtype=torch.bfloat16, device=dev)
-            sumsq = torch.zeros(total, dtype=torch.float32, device=dev)
-            out.append((r, c, plist, stack, sumsq))
+            ent = dict(r=r, c=c, plist=plist, total=total,
+                       stack=torch.empty(total, r, c, dtype=torch.bfloat16, device=dev),       # normalised updates (NS input)
+                       grads=torch.empty(total, r, c, dtype=torch.float32, device=dev),        # gradients, stacked
+                       mom=torch.zeros(total, r, c, dtype=torch.float32, device=dev),          # momentum, stacked
+                       sumsq=torch.zeros(total, dtype=torch.float32, device=dev))
+            slot, ent["gviews"], ent["mviews"] = 0, [], []
+            for p, nmat in plist:
+                ent["gviews"].append(ent["grads"][slot:slot + nmat].view(p.shape))
+                ent["mviews"].append(ent["mom"][slot:slot + nmat].view(p.shape))
+                slot += nmat
+            out.append(ent)
         self._stacks[key] = out
         return out
 
     @torch.no_grad()
     def _step_fused(self, group):
+        """All matrices of one shape are one stack: one copy of the gradients into it, one momentum + sum-of-squares
+        launch, one normalisation, one batched Newton-Schulz; only the weight update runs per parameter."""
         o = ops()
         mu, nesterov, lr = float(group["momentum"]), bool(group["nesterov"]), float(group["lr"])
         coeffs = [NS5_COEFFS[0]] * group["ns_steps"]
         params = [p for p in group["params"] if p.grad is not None]
-        for r, c, plist, stack, sumsq in self._slots(params):
-            sumsq.zero_()
-            slot = 0
-            for p, nmat in plist:
+        for ent in self._slots(params):
+            r, c, plist = ent["r"], ent["c"], ent["plist"]
+            for (p, _), mv in zip(plist, ent["mviews"]):
                 st = self.state[p]
-                if "momentum_buffer" not in st:
-                    st["momentum_buffer"] = torch.zeros(p.shape, dtype=torch.float32, device=p.device)
-                g = p.grad if p.grad.dtype == torch.float32 else p.grad.float()
-                g = g.contiguous().view(nmat, r, c)
-                buf = st["momentum_buffer"].view(nmat, r, c)
-                for j in range(nmat):
-                    o.muon_momentum(g[j], buf[j], stack[slot + j], sumsq[slot + j:slot + j + 1], mu, nesterov, 1.0)
-                    o.scale_by_inv_norm(stack[slot + j], sumsq[slot + j:slot + j + 1], 1e-7)
-                slot += nmat
-            u = newton_schulz_(stack, coeffs, self._work)
+                cur = st.get("momentum_buffer")
+                if cur is None or cur.data_ptr() != mv.data_ptr():
+                    if cur is not None:            # a buffer restored from a checkpoint: move it into the stack
+                        mv.copy_(cur.view(mv.shape))
+                    st["momentum_buffer"] = mv
+            torch._foreach_copy_(ent["gviews"], [p.grad for p, _ in plist])
+            ent["sumsq"].zero_()
+            o.muon_momentum(ent["grads"], ent["mom"], ent["stack"], ent["sumsq"], mu, nesterov, 1.0)
+            o.stack_scale_by_inv_norm(ent["stack"], ent["sumsq"], ent["total"], r * c, 1e-7)
+            u = newton_schulz_(ent["stack"], coeffs, self._work)
             alpha = -lr * max(1.0, r / c) ** 0.5
             slot = 0
             for p, nmat in plist:
