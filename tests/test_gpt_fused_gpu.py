@@ -96,3 +96,31 @@ def test_loss_and_grad_equals_backward_of_the_loss():
     m.loss_and_grad(x, y, 2)
     for n in want:
         assert (m.get_parameter(n).grad.float() - 2 * want[n].float()).norm() <= 1e-2 * (2 * want[n].float()).norm() + 1e-8, n
+
+
+def test_muon_momentum_survives_a_state_dict_round_trip():
+    """A momentum buffer restored from a checkpoint is moved into the optimizer's stacked buffer before the next step."""
+    from ml_experiments_b200.optim import Muon
+
+    torch.manual_seed(2)
+    shapes = [(2, 256, 256), (256, 256), (512, 256)]
+    grads = [[torch.randn(s, device="cuda") for s in shapes] for _ in range(3)]
+
+    def run(resume_after):
+        torch.manual_seed(3)
+        ps = [torch.randn(s, device="cuda").requires_grad_(True) for s in shapes]
+        opt = Muon(ps, lr=0.05, momentum=0.9)
+        for step, gs in enumerate(grads):
+            if step == resume_after:
+                import copy
+                sd = copy.deepcopy(opt.state_dict())
+                opt = Muon(ps, lr=0.05, momentum=0.9)
+                opt.load_state_dict(sd)
+            for p, g in zip(ps, gs):
+                p.grad = g.clone()
+            opt.step()
+        return [p.detach().clone() for p in ps]
+
+    a, b = run(resume_after=-1), run(resume_after=2)
+    for x, y in zip(a, b):
+        assert torch.allclose(x, y, rtol=0, atol=1e-3)     # a lost momentum buffer would move the weights by ~5e-2
