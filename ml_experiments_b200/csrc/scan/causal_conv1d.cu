@@ -24,6 +24,11 @@ __device__ __forceinline__ void ld8(const bf16* p, float (&f)[8]) {
 #pragma unroll
   for (int i = 0; i < 4; ++i) { const float2 x = __bfloat1622float2(h[i]); f[2 * i] = x.x; f[2 * i + 1] = x.y; }
 }
+__device__ __forceinline__ void cvt8(const uint4& u, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 x = __bfloat1622float2(h[i]); f[2 * i] = x.x; f[2 * i + 1] = x.y; }
+}
 __device__ __forceinline__ void st8(bf16* p, const float (&f)[8]) {
   uint4 u;
   __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
@@ -68,7 +73,7 @@ conv_fwd_kernel(const bf16* __restrict__ x, long long ldx, const float* __restri
   }
 }
 
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 3)
 conv_bwd_kernel(const bf16* __restrict__ x, long long ldx, const float* __restrict__ w, const float* __restrict__ bias,
                 const bf16* __restrict__ dy, bf16* __restrict__ dx, long long lddx, float* __restrict__ dw,
                 float* __restrict__ dbias, int L, int C) {
@@ -95,12 +100,23 @@ conv_bwd_kernel(const bf16* __restrict__ x, long long ldx, const float* __restri
     }
   }
   const int tend = min(t0 + TT, L);
+  // the rows of step t + 1 are requested before step t is computed (raw 16-byte registers), so two steps' loads are in flight
+  uint4 nx = make_uint4(0u, 0u, 0u, 0u), ng = nx;
+  if (t0 < L) {
+    nx = *reinterpret_cast<const uint4*>(x + ((long long)b * L + t0) * ldx + c0);
+    ng = *reinterpret_cast<const uint4*>(dy + ((long long)b * L + t0) * C + c0);
+  }
   for (int t = t0; t < tend + 3; ++t) {
     float cur[8], g[8], dpre[8];
     const bool in = t < L;
+    const uint4 ux = nx, ug = ng;
+    if (t + 1 < tend + 3 && t + 1 < L) {
+      nx = *reinterpret_cast<const uint4*>(x + ((long long)b * L + t + 1) * ldx + c0);
+      ng = *reinterpret_cast<const uint4*>(dy + ((long long)b * L + t + 1) * C + c0);
+    }
     if (in) {
-      ld8(x + ((long long)b * L + t) * ldx + c0, cur);
-      ld8(dy + ((long long)b * L + t) * C + c0, g);
+      cvt8(ux, cur);
+      cvt8(ug, g);
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
