@@ -72,7 +72,8 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+// Request a line into L1 (and L2) without holding a register for it.
+__device__ __forceinline__ void prefetch_near(const void* p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
 __device__ __forceinline__ float ld(const float* p, long long i) { return p[i]; }
 __device__ __forceinline__ float ld(const bf16* p, long long i) { return __bfloat162float(p[i]); }
 __device__ __forceinline__ void st(float* p, long long i, float v) { p[i] = v; }
@@ -305,24 +306,24 @@ s6_bwd_kernel(const bf16* __restrict__ u, const DT* __restrict__ delta, const fl
     for (int k = 0; k < QS; ++k) h0[k] = 0.f;
     if (dok) ldv<QS>(h0, &state[state_off(b, nsub, tile, w * QS, Din, d)]);
     __syncthreads();
-    if (tile > 0) {  // warm L2 with the rows of the tile processed next (one tile earlier in time)
+    if (tile > 0) {  // warm L1 with the rows of the tile processed next (one tile earlier in time)
 #pragma unroll
       for (int j = 0; j < RPT; ++j) {
         const long long off = ((long long)b * L + t0 - SUB + w + NW * j) * Din + d;
         if (dok) {
-          prefetch_l2(delta + off);
-          prefetch_l2(u + off);
-          prefetch_l2(dout + off);
+          prefetch_near(delta + off);
+          prefetch_near(u + off);
+          prefetch_near(dout + off);
           if (z) {
-            prefetch_l2(z + off);
-            prefetch_l2(y_pre + off);
+            prefetch_near(z + off);
+            prefetch_near(y_pre + off);
           }
         }
       }
-      if (dok) prefetch_l2(&state[state_off(b, nsub, tile - 1, w * QS, Din, d)]);
+      if (dok) prefetch_near(&state[state_off(b, nsub, tile - 1, w * QS, Din, d)]);
       if (tid < 2 * SUB) {
         const long long off = ((long long)b * L + t0 - SUB + (tid >> 1)) * NS;
-        prefetch_l2((tid & 1) ? Cm + off : Bm + off);
+        prefetch_near((tid & 1) ? Cm + off : Bm + off);
       }
     }
     float hs[SUB][QS];
