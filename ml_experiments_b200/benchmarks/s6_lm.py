@@ -22,6 +22,8 @@ def main():
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--breakdown", type=int, default=0, metavar="ROWS",
+                    help="instead of timing, profile one step with torch.profiler and print the ROWS kernels with the most device time")
     a = ap.parse_args()
     rank, world, local = init_dist()
     dev = torch.device("cuda", local)
@@ -51,6 +53,22 @@ def main():
         opt.step()
         opt.zero_grad(set_to_none=True)
 
+    if a.breakdown:
+        from torch.profiler import ProfilerActivity, profile
+
+        for _ in range(a.warmup):
+            step()
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            step()
+            torch.cuda.synchronize()
+        if rank == 0:
+            ev = [e for e in prof.key_averages() if e.device_time_total > 0]
+            total = sum(e.device_time_total for e in ev)
+            print(f"device time per step: {total / 1e3:.2f} ms over {sum(e.count for e in ev)} launches")
+            for e in sorted(ev, key=lambda e: -e.device_time_total)[: a.breakdown]:
+                print(f"{100 * e.device_time_total / total:5.1f} %  {e.device_time_total / 1e3:8.3f} ms  {e.count:4d} x {e.device_time_total / e.count:9.1f} us  {e.key[:100]}")
+        return
     ms = timed_steps(step, a.steps, a.warmup, world, dev)
     from ..ops.runtime import check_status
 
