@@ -5,7 +5,7 @@
         bench.py --gpus N --steps K --warmup W
     python bench.py --impl reference ...      # the unmodified reference model / optimizer classes, same protocol
 
-Config (BASELINE config #2): 12 layers, d_model 768, 6 heads x 128, vocab 50304 (fp8 lm_head), RoPE, ReLU², RMSNorm;
+Config: 12 layers, d_model 768, 6 heads x 128, vocab 50304 (fp8 lm_head), RoPE, ReLU², RMSNorm;
 Muon on hidden matrices, Adam on embeddings / head / scalars; 48 x 1024 tokens per rank per step (weak scaling), token
 ids uniform in [0, 50257) with a BOS token every 1024 positions (documents of 1024 tokens), random-init weights.
 
@@ -138,7 +138,8 @@ def run_ours(args, rank, local, world):
             loss = trainer.train_step(x, y, window=WINDOW_BLOCKS)
             losses.append(float(loss.item()))               # D2H read of the step's result
 
-    device_loop(args.warmup)
+    first_loss = float(trainer.train_step(*dev_pool[0], window=WINDOW_BLOCKS).item())   # loss at initialisation (= ln V)
+    device_loop(args.warmup - 1)
     if args.breakdown:
         # not a timing run: per-kernel device time of three steps, as shares of one step
         from torch.profiler import ProfilerActivity, profile
@@ -177,17 +178,26 @@ def run_ours(args, rank, local, world):
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
             "gpu_launches": launches,
-            "final_loss": losses[-1] if losses else None,
+            "first_loss": first_loss, "final_loss": losses[-1] if losses else None,
         }), flush=True)
+    # a run whose loss never moved (or is not finite) did not train: fail loudly instead of reporting a throughput
+    final = losses[-1] if losses else float("nan")
+    trained = final == final and abs(final) != float("inf") and final != first_loss
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if not trained:
+        if rank == 0:
+            print(f"bench.py: loss did not move or is not finite ({first_loss} -> {final}); the timed steps are not valid training steps",
+                  file=sys.stderr, flush=True)
+        sys.exit(3)
 
 
-def run_reference(args, rank, local, world):
+def run_reference(args):
+    """The reference's own classes and code path (see baseline/reference_arm.py); imports nothing of this package."""
     from baseline.reference_arm import run as run_ref
 
-    run_ref(args, rank, local, world, SEQ_LEN, WINDOW_BLOCKS, BASELINE_TOKENS_PER_S, ClockSampler)
+    run_ref(args, SEQ_LEN, WINDOW_BLOCKS, BASELINE_TOKENS_PER_S, ClockSampler)
 
 
 def main():
@@ -209,12 +219,14 @@ def main():
         sys.exit(subprocess.call(cmd))
     if args.impl == "reference":
         try:
-            from ml_experiments_b200.trainers.gpt_trainer import init_distributed
-            rank, local, world = init_distributed()
-            run_reference(args, rank, local, world)
-        except Exception as e:  # the reference arm must never fail the driver: report why it is unavailable
+            run_reference(args)
+        except Exception as e:  # the reference arm must never fail the driver: report the actual error
+            import traceback
+
+            traceback.print_exc()
             if int(os.environ.get("RANK", "0")) == 0:
-                print(json.dumps({"impl": "reference", "unavailable": f"{type(e).__name__}: {str(e)[:300]}"}), flush=True)
+                msg = " ".join(f"{type(e).__name__}: {e}".split())
+                print(json.dumps({"impl": "reference", "unavailable": msg[:400]}), flush=True)
         return
     from ml_experiments_b200.trainers.gpt_trainer import init_distributed
 

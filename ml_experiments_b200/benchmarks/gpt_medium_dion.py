@@ -1,5 +1,5 @@
 """GPT-2 medium (24 layers, d_model 1024, 16 heads x 64, vocab 50304) with the Dion optimizer (rank d/4), bf16,
-32 x 1024 tokens per rank per step (BASELINE config #5).
+32 x 1024 tokens per rank per step.
 
     python -m ml_experiments_b200.benchmarks.gpt_medium_dion [--shape medium|medium_track] [--steps 5]
 ``--shape medium_track`` selects the reference's own medium-track shape (16 layers, 8 heads x 128).

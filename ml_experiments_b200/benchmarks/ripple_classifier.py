@@ -1,4 +1,4 @@
-"""Scatter / hierarchical-attention classifier on long sequences (BASELINE config #4): 128x128 uint8 images flattened
+"""Scatter / hierarchical-attention classifier on long sequences: 128x128 uint8 images flattened
 to 16 384 tokens, 8 layers, d_model 256, 4 heads, 2 classes, batch 32 per rank, bf16 autocast, AdamW.
 
     python -m ml_experiments_b200.benchmarks.ripple_classifier [--batch 32 --layers 8 --side 128]

@@ -1,4 +1,4 @@
-"""S6 selective-scan byte LM (BASELINE config #3): 24 layers, d_model 1024, expand 2, state 16, chunk 64, vocab 256,
+"""S6 selective-scan byte LM: 24 layers, d_model 1024, expand 2, state 16, chunk 64, vocab 256,
 sequence 4096, batch 8 per rank, bf16, AdamW, DDP with bucketed all-reduce overlapped with backward.
 
     python -m ml_experiments_b200.benchmarks.s6_lm [--layers 24 --d-model 1024 --batch 8 --seq 4096 --steps 5]

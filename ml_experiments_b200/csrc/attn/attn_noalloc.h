@@ -10,8 +10,12 @@
 // Here that temporary lives in a fixed array inside the library image: B200_ATTN_NOALLOC_MAX_HT floats (4 MiB) per
 // GPU that loads the library, held until the process exits. Consequences for the caller:
 //   * H * T must not exceed B200_ATTN_NOALLOC_MAX_HT; larger problems are refused with an error code.
-//   * The first call on each device looks up the array's device address (cudaGetSymbolAddress) and configures the
-//     kernels; make that first call outside of any stream capture.
+//   * The first call on each device (with that device current) looks up the array's device address
+//     (cudaGetSymbolAddress) and opts the kernels into their shared-memory size on that device; make that first
+//     call outside of any stream capture. Both pieces of set-up are remembered per device ordinal, so one process
+//     may drive several GPUs. `stream` must belong to the device that is current at the call.
+//   * The per-device set-up is not locked: two host threads that make the first call on the same device at the same
+//     time both perform it (same address, same attribute value), which is harmless.
 //   * All calls on one device share the array. It is fully rewritten at the start of every call, so nothing needs
 //     clearing, but two calls whose kernels may overlap on the GPU (different streams) race on it: serialise them.
 //   * The function itself never calls cudaMalloc / cudaFree or any allocating library routine.
@@ -24,7 +28,7 @@
 extern "C" {
 #endif
 
-// Tensors: bf16, element (t, h, d) at base + t * ld + h * D + d (ld in elements), D = 128.
+// Tensors: bf16, element (t, h, d) at base + t * ld + h * D + d (ld in elements), D = 64 or 128.
 //   q, k, v, o, d_o : inputs;  lse : fp32 [H][T] from the forward;  doc_start / doc_end : int32 [T]
 //   dq_acc          : fp32 [T][H][D] with row pitch ld_dq, must be zero on entry, receives dQ
 //   dk, dv          : bf16 outputs

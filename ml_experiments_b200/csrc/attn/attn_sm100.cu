@@ -11,6 +11,7 @@
 //            formed transposed so that Pᵀ / dSᵀ rows are owned by one thread each and feed
 //            dV += Pᵀ·dO, dK += dSᵀ·Q (TMEM-resident accumulators) and dQᵀ = Kᵀ·dSᵀ, which is
 //            added into an fp32 dQ buffer by TMA reduce-add.
+#include "../common/per_device.h"
 #include "attn.h"
 
 #include <stdexcept>
@@ -691,8 +692,9 @@ void fwd_impl(const AttnArgs& a) {
   CUtensorMap tk = qkv_map(a.k, a.T, a.H, D, a.ld_k, 64);
   CUtensorMap tv = qkv_map(a.v, a.T, a.H, D, a.ld_v, 64);
   auto kern = attn_fwd_kernel<D>;
-  static bool cfg = false;
-  if (!cfg) { set_smem(kern, smem); cfg = true; }
+  static PerDeviceOnce cfg;   // the shared-memory opt-in is a per-device attribute
+  int dev = 0;
+  if (cfg.pending(&dev)) { set_smem(kern, smem); cfg.done(dev); }
   dim3 grid((a.T + 127) / 128, a.H);
   kern<<<grid, 128, smem, a.stream>>>(tq, tk, tv, make_kp(a));
   check_launch("attn_fwd launch");
@@ -709,8 +711,9 @@ void bwd_impl(const AttnArgs& a) {
   CUtensorMap tdq = make_tmap_3d(a.dq_acc, TmapDtype::F32, (uint64_t)D, (uint64_t)a.T, (uint64_t)a.H,
                                  (uint64_t)a.ld_dq * 4, (uint64_t)D * 4, (uint32_t)D, 64, false);
   auto kern = attn_bwd_kernel<D>;
-  static bool cfg = false;
-  if (!cfg) { set_smem(kern, smem); cfg = true; }
+  static PerDeviceOnce cfg;   // the shared-memory opt-in is a per-device attribute
+  int dev = 0;
+  if (cfg.pending(&dev)) { set_smem(kern, smem); cfg.done(dev); }
   dim3 grid((a.T + 127) / 128, a.H);
   kern<<<grid, 256, smem, a.stream>>>(tq, tk, tv, tdo, tdq, make_kp(a));
   check_launch("attn_bwd launch");
@@ -762,7 +765,9 @@ static __device__ __align__(256) float g_noalloc_delta[B200_ATTN_NOALLOC_MAX_HT]
 
 namespace {
 thread_local std::string t_noalloc_error;
-float* g_noalloc_delta_addr[64] = {nullptr};  // device address of the scratch array, per device ordinal
+// Device address of the scratch array, per device ordinal. Two host threads that make the first call on one device
+// both store the same value.
+std::atomic<float*> g_noalloc_delta_addr[64];
 }  // namespace
 
 extern "C" const char* b200_attn_bwd_noalloc_error(void) { return t_noalloc_error.c_str(); }
@@ -778,8 +783,8 @@ extern "C" int b200_attn_bwd_noalloc(const void* q, const void* k, const void* v
       t_noalloc_error = "null pointer or empty problem";
       return -1;
     }
-    if (D != 128) {
-      t_noalloc_error = "head_dim must be 128";
+    if (D != 128 && D != 64) {
+      t_noalloc_error = "head_dim must be 64 or 128";
       return -1;
     }
     if ((long long)T * H > (long long)B200_ATTN_NOALLOC_MAX_HT) {
@@ -792,7 +797,8 @@ extern "C" int b200_attn_bwd_noalloc(const void* q, const void* k, const void* v
       t_noalloc_error = "cannot determine the current device";
       return -3;
     }
-    if (g_noalloc_delta_addr[dev] == nullptr) {
+    float* scratch = g_noalloc_delta_addr[dev].load(std::memory_order_acquire);
+    if (scratch == nullptr) {
       // Once per device, with that device current: in host code the array's name is only a handle, the address a
       // kernel can use has to be asked for.
       void* ptr = nullptr;
@@ -801,13 +807,14 @@ extern "C" int b200_attn_bwd_noalloc(const void* q, const void* k, const void* v
         t_noalloc_error = std::string("cudaGetSymbolAddress failed: ") + cudaGetErrorString(e);
         return -3;
       }
-      g_noalloc_delta_addr[dev] = static_cast<float*>(ptr);
+      scratch = static_cast<float*>(ptr);
+      g_noalloc_delta_addr[dev].store(scratch, std::memory_order_release);
     }
     b200::AttnArgs a;
     a.q = q; a.k = k; a.v = v; a.o = const_cast<void*>(o); a.d_o = d_o;
     a.dq_acc = dq_acc; a.dk = dk; a.dv = dv;
     a.lse = const_cast<float*>(lse);
-    a.delta = g_noalloc_delta_addr[dev];
+    a.delta = scratch;
     a.doc_start = doc_start; a.doc_end = doc_end;
     a.T = T; a.H = H; a.D = D;
     a.ld_q = ld_q; a.ld_k = ld_k; a.ld_v = ld_v; a.ld_o = ld_o; a.ld_do = ld_do; a.ld_dq = ld_dq; a.ld_dk = ld_dk;

@@ -256,7 +256,8 @@ void softcap_ce(const Tensor& logits, const Tensor& targets, Tensor loss_rows, c
 }
 
 void adam_step(Tensor p, const Tensor& g, Tensor m, Tensor v, double lr, double beta1, double beta2, double eps,
-               double wd, double bias1, double bias2, double grad_scale) {
+               double wd, double bias1, double bias2, double grad_scale, const c10::optional<Tensor>& shadow,
+               double shadow_scale) {
   const c10::cuda::CUDAGuard guard(p.device());
   TORCH_CHECK(p.is_contiguous() && g.is_contiguous() && m.is_contiguous() && v.is_contiguous(), "adam_step: contiguous");
   TORCH_CHECK(m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat, "adam_step: fp32 m/v");
@@ -265,8 +266,17 @@ void adam_step(Tensor p, const Tensor& g, Tensor m, Tensor v, double lr, double 
   TORCH_CHECK(pb || p.scalar_type() == at::kFloat, "adam_step: p must be fp32 or bf16");
   TORCH_CHECK(gb || g.scalar_type() == at::kFloat, "adam_step: g must be fp32 or bf16");
   TORCH_CHECK(g.numel() == p.numel() && m.numel() == p.numel() && v.numel() == p.numel(), "adam_step: size mismatch");
+  int kind = 0;
+  void* sh = nullptr;
+  if (shadow.has_value()) {
+    TORCH_CHECK(shadow->is_contiguous() && shadow->numel() == p.numel(), "adam_step: shadow must be contiguous and of p's size");
+    kind = shadow->scalar_type() == at::kBFloat16 ? 1 : shadow->scalar_type() == at::kFloat8_e4m3fn ? 2 : 0;
+    TORCH_CHECK(kind != 0, "adam_step: shadow must be bf16 or float8_e4m3fn");
+    sh = shadow->data_ptr();
+  }
   b200::adam_step(p.data_ptr(), pb, g.data_ptr(), gb, m.data_ptr<float>(), v.data_ptr<float>(), p.numel(), (float)lr,
-                  (float)beta1, (float)beta2, (float)eps, (float)wd, (float)bias1, (float)bias2, (float)grad_scale, cur_stream());
+                  (float)beta1, (float)beta2, (float)eps, (float)wd, (float)bias1, (float)bias2, (float)grad_scale, sh,
+                  kind, (float)shadow_scale, cur_stream());
 }
 
 void muon_momentum(const Tensor& g, Tensor buf, Tensor out, Tensor sumsq, double mu, bool nesterov, double grad_scale) {
@@ -665,7 +675,7 @@ TORCH_LIBRARY(b200, m) {
   m.def("doc_bounds(Tensor tokens, int bos, Tensor(a!) doc_start, Tensor(b!) doc_end) -> ()");
   m.def("cast_fp8(Tensor x, Tensor(a!) out, float scale) -> ()");
   m.def("softcap_ce(Tensor logits, Tensor targets, Tensor(a!) loss_rows, Tensor(b!)? grad, float cap, float div, float loss_scale, float grad_scale, float shift=0.0, Tensor? mtp_w=None) -> ()");
-  m.def("adam_step(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, float lr, float beta1, float beta2, float eps, float wd, float bias1, float bias2, float grad_scale) -> ()");
+  m.def("adam_step(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, float lr, float beta1, float beta2, float eps, float wd, float bias1, float bias2, float grad_scale, Tensor(d!)? shadow=None, float shadow_scale=1.0) -> ()");
   m.def("muon_momentum(Tensor g, Tensor(a!) buf, Tensor(b!) out, Tensor(c!) sumsq, float mu, bool nesterov, float grad_scale) -> ()");
   m.def("scale_by_inv_norm(Tensor(a!) x, Tensor sumsq, float eps) -> ()");
   m.def("axpy_bf16_to_f32(Tensor(a!) p, Tensor u, Tensor(b!)? p_bf16, float alpha) -> ()");

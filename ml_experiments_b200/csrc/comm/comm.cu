@@ -15,7 +15,15 @@ namespace {
 using bf16 = __nv_bfloat16;
 
 // A peer rank can lag by a whole step (data loading, host jitter): allow far more than an on-chip wait.
+// The default can be overridden at run time: word 1 of the status buffer holds the limit in microseconds (0 = default),
+// so a host can shorten it (failure-detection tests let a wait on a flag that nobody sets expire after a millisecond).
 constexpr unsigned long long kPeerWaitNs = 5000000000ull;
+
+__device__ __forceinline__ unsigned long long peer_wait_limit_ns(const int* status) {
+  if (status == nullptr) return kPeerWaitNs;
+  const int us = *reinterpret_cast<const volatile int*>(status + 1);
+  return us > 0 ? (unsigned long long)us * 1000ull : kPeerWaitNs;
+}
 
 __device__ __forceinline__ void st_release_sys(int* p, int v) {
   asm volatile("st.release.sys.global.b32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -36,10 +44,11 @@ __device__ bool block_wait_flags(const int* flags, int world, int channel, int e
     const int* f = flags + channel * kMaxWorld + threadIdx.x;
     if (ld_acquire_sys(f) < epoch) {
       const uint64_t t0 = globaltimer_ns();
+      const unsigned long long limit = peer_wait_limit_ns(status);
       for (;;) {
         if (ld_acquire_sys(f) >= epoch) break;
         if (status_poisoned(status)) { s_fail = 1; break; }
-        if (globaltimer_ns() - t0 > kPeerWaitNs) {
+        if (globaltimer_ns() - t0 > limit) {
           if (status) atomicCAS(status, 0, ERR_WAIT_PEER_FLAG);
           s_fail = 1;
           break;

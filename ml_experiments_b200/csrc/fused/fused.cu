@@ -656,10 +656,13 @@ __device__ __forceinline__ void adam_one(float& pi, float gi, float& mi, float& 
 }
 
 // VEC = 4: four consecutive elements per thread with 8 / 16-byte accesses (all pointers 16-byte aligned); VEC = 1 otherwise.
+// shadow_kind: 0 none, 1 bf16 copy of the new parameter, 2 e4m3 copy of (new parameter * shadow_scale): the
+// low-precision operand that the next forward GEMM reads is produced in the same pass as the update.
 template <typename TP, typename TG, int VEC>
 __global__ void adam_kernel(TP* __restrict__ p, const TG* __restrict__ g, float* __restrict__ m,
                             float* __restrict__ v, long long n, float lr, float b1, float b2, float eps, float wd,
-                            float bias1, float bias2, float grad_scale) {
+                            float bias1, float bias2, float grad_scale, void* __restrict__ shadow, int shadow_kind,
+                            float shadow_scale) {
   const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
   if (i >= n) return;
   const float isb2 = rsqrtf(bias2);
@@ -669,6 +672,14 @@ __global__ void adam_kernel(TP* __restrict__ p, const TG* __restrict__ g, float*
 #pragma unroll
     for (int k = 0; k < 4; ++k) adam_one(pf[k], gf[k] * grad_scale, mf[k], vf[k], lr, b1, b2, eps, wd, bias1, isb2);
     st4(m + i, mf); st4(v + i, vf); st4(p + i, pf);
+    if (shadow_kind == 1) {
+      st4(reinterpret_cast<bf16*>(shadow) + i, pf);
+    } else if (shadow_kind == 2) {
+      const uint32_t w =
+          (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(pf[0] * shadow_scale, pf[1] * shadow_scale), __NV_SATFINITE, __NV_E4M3) |
+          ((uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(pf[2] * shadow_scale, pf[3] * shadow_scale), __NV_SATFINITE, __NV_E4M3) << 16);
+      *reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(shadow) + i) = w;
+    }
     return;
   }
   for (long long j = i; j < n && j < i + VEC; ++j) {
@@ -677,6 +688,9 @@ __global__ void adam_kernel(TP* __restrict__ p, const TG* __restrict__ g, float*
     m[j] = mi;
     v[j] = vi;
     p[j] = (TP)pi;
+    if (shadow_kind == 1) reinterpret_cast<bf16*>(shadow)[j] = __float2bfloat16(pi);
+    else if (shadow_kind == 2)
+      reinterpret_cast<uint8_t*>(shadow)[j] = __nv_cvt_float_to_fp8(pi * shadow_scale, __NV_SATFINITE, __NV_E4M3);
   }
 }
 
@@ -869,16 +883,19 @@ void softcap_ce(const void* logits, const long long* targets, float* loss_rows, 
 
 void adam_step(void* p, int p_is_bf16, const void* g, int g_is_bf16, float* m, float* v, long long n, float lr,
                float beta1, float beta2, float eps, float wd, float bias1, float bias2, float grad_scale,
-               cudaStream_t s) {
-  const bool vec = (((uintptr_t)p | (uintptr_t)g | (uintptr_t)m | (uintptr_t)v) & 15) == 0 && n >= 4;
+               void* shadow, int shadow_kind, float shadow_scale, cudaStream_t s) {
+  bool vec = (((uintptr_t)p | (uintptr_t)g | (uintptr_t)m | (uintptr_t)v) & 15) == 0 && n >= 4;
+  if (shadow_kind && ((uintptr_t)shadow & 7)) vec = false;
 #define ADAM_LAUNCH(TP, TG)                                                                                          \
   do {                                                                                                               \
     if (vec)                                                                                                         \
       adam_kernel<TP, TG, 4><<<(int)((n + 1023) / 1024), 256, 0, s>>>((TP*)p, (const TG*)g, m, v, n, lr, beta1, beta2, \
-                                                                      eps, wd, bias1, bias2, grad_scale);            \
+                                                                      eps, wd, bias1, bias2, grad_scale, shadow,     \
+                                                                      shadow_kind, shadow_scale);                    \
     else                                                                                                             \
       adam_kernel<TP, TG, 1><<<(int)((n + 255) / 256), 256, 0, s>>>((TP*)p, (const TG*)g, m, v, n, lr, beta1, beta2, \
-                                                                    eps, wd, bias1, bias2, grad_scale);              \
+                                                                    eps, wd, bias1, bias2, grad_scale, shadow,       \
+                                                                    shadow_kind, shadow_scale);                      \
   } while (0)
   if (p_is_bf16 && g_is_bf16) ADAM_LAUNCH(bf16, bf16);
   else if (p_is_bf16) ADAM_LAUNCH(bf16, float);

@@ -64,9 +64,11 @@ void softcap_ce(const void* logits, const long long* targets, float* loss_rows, 
 // ---- optimizer pieces -------------------------------------------------------------------------
 // Adam (bias-corrected, decoupled weight decay wd*lr) over n elements. p : fp32 or bf16 (p_is_bf16);
 // g : fp32 or bf16 (g_is_bf16) ; m, v : fp32. lr, step-dependent corrections are passed as scalars.
+// shadow (optional): the low-precision copy of the updated parameter that the forward GEMMs read, written in the
+// same pass: shadow_kind 1 = bf16, 2 = e4m3 of (p * shadow_scale), 0 = none.
 void adam_step(void* p, int p_is_bf16, const void* g, int g_is_bf16, float* m, float* v, long long n, float lr,
                float beta1, float beta2, float eps, float wd, float bias1, float bias2, float grad_scale,
-               cudaStream_t s);
+               void* shadow, int shadow_kind, float shadow_scale, cudaStream_t s);
 
 // Muon momentum: buf = mu*buf + (1-mu)*g ; u = nesterov ? (1-mu)*g + mu*buf : buf ; out_bf16 = u ; also
 // accumulates sum(u^2) into sumsq[0] (fp32) for the Frobenius normalisation.

@@ -9,6 +9,7 @@
 // descriptor and the instruction descriptor), so forward (A·Wᵀ), data-gradient (dY·W) and
 // weight-gradient (dYᵀ·X) products all run without a transpose pass. bf16 and fp8 (e4m3/e5m2)
 // inputs, fp32 accumulation, bf16 or fp32 output, batched, optional split-K by TMA reduce-add.
+#include "../common/per_device.h"
 #include "gemm.h"
 
 #include <stdexcept>
@@ -379,11 +380,12 @@ void launch(const GemmArgs& a, const KParams& kp, const CUtensorMap& tA, const C
             const CUtensorMap& tC, const CUtensorMap& tX, int grid) {
   using L = SmemLayout<BN, STAGES>;
   auto kern = gemm_kernel<BN, STAGES, AMN, BMN, ESZ>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;   // the shared-memory opt-in is a per-device attribute
+  int dev = 0;
+  if (configured.pending(&dev)) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
     if (e != cudaSuccess) throw std::runtime_error(std::string("gemm: cudaFuncSetAttribute: ") + cudaGetErrorString(e));
-    configured = true;
+    configured.done(dev);
   }
   kern<<<grid, kThreads, L::kTotal, a.stream>>>(tA, tB, tC, tX, kp);
   cudaError_t e = cudaGetLastError();

@@ -64,13 +64,17 @@ def reset_launch_count() -> None:
     _launches = 0
 
 
+STATUS_WORDS = 4   # [0] error code, [1] peer-wait limit in microseconds (0 = the kernels' default of 5 s), [2:] spare
+
+
 def status(device=None) -> torch.Tensor:
-    """The ``int32[1]`` status word of ``device`` (created zeroed on first use)."""
+    """The ``int32[4]`` status buffer of ``device`` (created zeroed on first use). Word 0 is the error code that the
+    kernels test and set; word 1 is the limit of a wait for a peer flag in microseconds (0: the built-in 5 s)."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     idx = dev.index if dev.index is not None else torch.cuda.current_device()
     t = _status.get(idx)
     if t is None:
-        t = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        t = torch.zeros(STATUS_WORDS, dtype=torch.int32, device=torch.device("cuda", idx))
         _status[idx] = t
     return t
 
@@ -78,7 +82,14 @@ def status(device=None) -> torch.Tensor:
 def check_status(device=None) -> None:
     """Synchronises and raises ``RuntimeError`` if any kernel on ``device`` recorded a failed wait."""
     t = status(device)
-    code = int(t.item())
+    code = int(t[0].item())
     if code != 0:
-        t.zero_()
+        t[0].zero_()
         raise RuntimeError(f"b200 kernel reported status {code}: {STATUS_CODES.get(code, 'unknown')}")
+
+
+def set_peer_wait_limit_ms(ms: float | None, device=None) -> None:
+    """Limit of every in-kernel wait for a peer's flag on ``device`` (``None`` or 0: back to the default of 5 s). A rank
+    that can tell from the host that a peer is gone (heartbeat) shortens the limit so that a collective already
+    enqueued gives up quickly and reports through :func:`check_status` instead of holding the GPU for seconds."""
+    status(device)[1] = 0 if not ms else max(int(ms * 1000), 1)

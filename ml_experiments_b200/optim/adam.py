@@ -9,6 +9,7 @@ from __future__ import annotations
 import torch
 
 from ..ops.runtime import ops
+from ..utils.shadow import mark_modified, set_shadow, shadow_entries
 
 
 class FusedAdam(torch.optim.Optimizer):
@@ -40,8 +41,17 @@ class FusedAdam(torch.optim.Optimizer):
                 g = p.grad
                 if p.is_cuda and p.is_contiguous() and g.is_contiguous() and p.dtype in (torch.float32, torch.bfloat16) \
                         and g.dtype in (torch.float32, torch.bfloat16):
+                    # the kernel updates p without bumping Tensor._version: tell the shadow cache. If the forward keeps a
+                    # bf16 / e4m3 copy of this parameter (the fp8 lm_head), the same kernel pass refreshes it.
+                    ents = [e for e in shadow_entries(p) if e[0] in (torch.bfloat16, torch.float8_e4m3fn)
+                            and e[2].is_contiguous() and e[2].shape == p.shape]
+                    sh = ents[0] if len(ents) == 1 else None
                     ops().adam_step(p, g, st["exp_avg"], st["exp_avg_sq"], lr, b1, b2, group["eps"],
-                                    group["weight_decay"], bias1, bias2, 1.0)
+                                    group["weight_decay"], bias1, bias2, 1.0, None if sh is None else sh[2],
+                                    1.0 if sh is None else float(sh[1]))
+                    mark_modified(p)
+                    if sh is not None:
+                        set_shadow(p, sh[2], sh[1])
                 else:
                     gf = g.float()
                     m, v = st["exp_avg"], st["exp_avg_sq"]
@@ -51,4 +61,5 @@ class FusedAdam(torch.optim.Optimizer):
                     pf.mul_(1 - lr * group["weight_decay"])
                     pf.addcdiv_(m, v.sqrt() / (bias2 ** 0.5) + group["eps"], value=-lr / bias1)
                     p.copy_(pf)
+                    mark_modified(p)
         return loss

@@ -15,7 +15,7 @@ import torch
 
 from ..ops.newton_schulz import NS5_COEFFS, newton_schulz_, newton_schulz_torch
 from ..ops.runtime import ops
-from ..utils.shadow import get_shadow_buffer, set_shadow
+from ..utils.shadow import get_shadow_buffer, mark_modified, set_shadow
 
 
 class Muon(torch.optim.Optimizer):
@@ -107,6 +107,7 @@ class Muon(torch.optim.Optimizer):
                     if sh is None:
                         sh = torch.empty(p.shape, dtype=torch.bfloat16, device=p.device)
                     o.axpy_bf16_to_f32(p, upd, sh, alpha)
+                    mark_modified(p)
                     set_shadow(p, sh)
                 else:
                     p.add_(upd.to(p.dtype), alpha=alpha)

@@ -24,7 +24,7 @@ import torch.distributed as dist
 
 from ..ops.newton_schulz import NS5_COEFFS, newton_schulz_
 from ..ops.runtime import ops
-from ..utils.shadow import get_shadow_buffer, set_shadow
+from ..utils.shadow import get_shadow_buffer, mark_modified, set_shadow
 
 
 class GradSync:
@@ -130,6 +130,7 @@ class DistMuon(torch.optim.Optimizer):
                 if sh is None:
                     sh = torch.empty(p.shape, dtype=torch.bfloat16, device=p.device)
                 o.axpy_bf16_to_f32(p, upd, sh, alpha)
+                mark_modified(p)
                 set_shadow(p, sh)
                 slot += nmat
         return None
@@ -240,6 +241,7 @@ class MuonShardEngine:
                             (self._step - 1) * ng + gi + 1, self._status)
             slot = 0
             for p, nmat in g["plist"]:
+                mark_modified(p)
                 set_shadow(p, g["sh_stack"][slot:slot + nmat].view(p.shape))
                 slot += nmat
 

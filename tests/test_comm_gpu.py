@@ -36,19 +36,50 @@ def test_allreduce_mean_virtual_ranks():
 
 
 def test_wait_times_out_cleanly():
-    """A flag that nobody sets makes the wait give up and report through the status word; the context stays usable."""
+    """A wait on a flag that nobody sets really runs out (limit shortened to 1 ms), reports code 5 through the status
+    word, and the context stays usable. Nothing is poisoned beforehand: the expiry branch itself is what runs."""
+    from ml_experiments_b200.ops.runtime import check_status, ops, set_peer_wait_limit_ms, status
+    from ml_experiments_b200.parallel.symm import VirtualWorld
+
+    vw = VirtualWorld(2)
+    st = status()
+    check_status()
+    set_peer_wait_limit_ms(1.0)
+    try:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        ops().comm_wait(vw.worlds[0].flags.local, 2, 6, 123, st)
+        e1.record()
+        torch.cuda.synchronize()
+        assert 0.5 < e0.elapsed_time(e1) < 500.0          # it waited about a millisecond, not 0 and not 5 s
+        with pytest.raises(RuntimeError, match="peer flag"):
+            check_status()
+        check_status()  # cleared by the failed check
+        # a second wait after the failure was cleared times out again on its own (no sticky state)
+        ops().comm_wait(vw.worlds[0].flags.local, 2, 6, 124, st)
+        with pytest.raises(RuntimeError, match="peer flag"):
+            check_status()
+    finally:
+        set_peer_wait_limit_ms(None)
+    assert torch.ones(4, device="cuda").sum().item() == 4
+
+
+def test_poisoned_status_makes_waits_return_at_once():
     from ml_experiments_b200.ops.runtime import check_status, ops, status
     from ml_experiments_b200.parallel.symm import VirtualWorld
 
     vw = VirtualWorld(2)
     st = status()
-    st.fill_(9)  # a poisoned status word makes every wait return at once instead of spinning for its full limit
+    st[0] = 9
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
     ops().comm_wait(vw.worlds[0].flags.local, 2, 6, 123, st)
+    e1.record()
     torch.cuda.synchronize()
+    assert e0.elapsed_time(e1) < 100.0
     with pytest.raises(RuntimeError):
         check_status()
-    check_status()  # cleared by the failed check
-    assert torch.ones(4, device="cuda").sum().item() == 4
+    check_status()
 
 
 def test_fused_muon_matches_single_process():
