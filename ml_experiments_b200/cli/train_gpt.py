@@ -22,7 +22,6 @@ import torch.distributed as dist
 from ..data.nanogpt_loader import distributed_data_generator
 from ..models.gpt import GPTConfig
 from ..trainers.gpt_trainer import GPTTrainer, Hyperparameters, init_distributed, synthetic_batch, window_blocks
-from ..utils.checkpoint import save_checkpoint
 
 
 def main(argv=None):
@@ -34,6 +33,7 @@ def main(argv=None):
     ap.add_argument("--val-tokens", type=int, default=10485760)
     ap.add_argument("--val-loss-every", type=int, default=125)
     ap.add_argument("--save-checkpoint", action="store_true")
+    ap.add_argument("--resume", default=None, help="checkpoint written by --save-checkpoint (any world size)")
     ap.add_argument("--synthetic", action="store_true")
     ap.add_argument("--layers", type=int, default=12)
     a = ap.parse_args(argv)
@@ -42,6 +42,12 @@ def main(argv=None):
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
     run_id = uuid.uuid4()
+    if world > 1:      # every rank writes its optimizer shard into the run's checkpoint folder: agree on the id
+        import torch.distributed as dist
+
+        box = [str(run_id)]
+        dist.broadcast_object_list(box, src=0)
+        run_id = box[0]
     logfile = None
     if master:
         os.makedirs("logs", exist_ok=True)
@@ -66,6 +72,9 @@ def main(argv=None):
     hp = Hyperparameters(num_iterations=a.num_iterations, seq_len=a.seq_len, val_tokens=a.val_tokens, val_loss_every=a.val_loss_every)
     cfg = GPTConfig(num_layers=a.layers, max_seq_len=a.seq_len, skip_attn_layers=(7,) if a.layers == 12 else ())
     tr = GPTTrainer(cfg, hp, device=dev, rank=rank, world_size=world)
+    if a.resume:
+        tr.load_checkpoint(a.resume)
+        print0(f"resumed from {a.resume} at step {tr.step}", console=True)
     if a.synthetic:
         def batches(seed0):
             i = 0
@@ -83,7 +92,7 @@ def main(argv=None):
     training_time_ms = 0.0
     torch.cuda.synchronize()
     t0 = time.perf_counter()
-    for step in range(a.num_iterations + 1):
+    for step in range(tr.step, a.num_iterations + 1):
         last = step == a.num_iterations
         if step == 10:
             training_time_ms, t0 = 0.0, time.perf_counter()
@@ -104,10 +113,10 @@ def main(argv=None):
             torch.cuda.synchronize()
             t0 = time.perf_counter()
         if last:
-            if master and a.save_checkpoint:
+            if a.save_checkpoint:
+                # rank 0: step / model / replicated optimizer state; every rank: its slice of the Muon momentum
                 os.makedirs(f"logs/{run_id}", exist_ok=True)
-                save_checkpoint(dict(step=step, code=open(__file__).read(), **tr.state_dict()),
-                                f"logs/{run_id}/state_step{step:06d}.pt")
+                tr.save_checkpoint(f"logs/{run_id}/state_step{step:06d}.pt")
             break
         x, y = next(train_iter)
         tr.train_step(x, y, window=w)

@@ -28,6 +28,7 @@ class Muon(torch.optim.Optimizer):
         super().__init__(params, defaults)
         self._work: dict = {}
         self._stacks: dict = {}
+        self._pending_shard = None
 
     # ------------------------------------------------------------------------------------------ torch path
     @torch.no_grad()
@@ -93,6 +94,10 @@ class Muon(torch.optim.Optimizer):
                     if cur is not None:            # a buffer restored from a checkpoint: move it into the stack
                         mv.copy_(cur.view(mv.shape))
                     st["momentum_buffer"] = mv
+            if self._pending_shard is not None:
+                t = self._pending_shard.get(f"mom_{r}x{c}")
+                if t is not None:
+                    ent["mom"].copy_(t[: ent["total"]])
             torch._foreach_copy_(ent["gviews"], [p.grad for p, _ in plist])
             ent["sumsq"].zero_()
             o.muon_momentum(ent["grads"], ent["mom"], ent["stack"], ent["sumsq"], mu, nesterov, 1.0)
@@ -112,6 +117,22 @@ class Muon(torch.optim.Optimizer):
                 else:
                     p.add_(upd.to(p.dtype), alpha=alpha)
                 slot += nmat
+        self._pending_shard = None
+
+    # -- the same checkpoint interface as the distributed forms (parallel/muon_dist.py): per-shape momentum stacks
+    def sharded_state(self) -> dict:
+        out = {}
+        for ents in self._stacks.values():
+            for ent in ents:
+                out[f"mom_{ent['r']}x{ent['c']}"] = ent["mom"].detach().clone()
+        return out
+
+    def sharded_rows(self) -> dict:
+        return {f"mom_{e['r']}x{e['c']}": e["total"] for ents in self._stacks.values() for e in ents}
+
+    def load_sharded_state(self, shard: dict) -> None:
+        """Momentum stacks saved by any of the Muon forms (re-partitioned for one rank); applied at the next step."""
+        self._pending_shard = dict(shard)
 
     @torch.no_grad()
     def step(self, closure=None):

@@ -187,10 +187,13 @@ class NorMuonAndAdam:
         st["step"] += 1
         b1, b2 = cfg.adam_betas
         t = st["step"]
-        step_size = cfg.lr * cfg.lr_mul * math.sqrt(1 - b2 ** t) / (1 - b1 ** t)
+        lr = cfg.lr * cfg.lr_mul
+        step_size = lr * math.sqrt(1 - b2 ** t) / (1 - b1 ** t)
         p_slice = self._shard(label, self._view(label))
+        # the decay is scheduled by the learning rate twice: lr_eff**2 * weight_decay * wd_mul
+        # (modded-nanogpt/train_gpt.py:658-672)
         adam_cautious_(p_slice, g.float(), st["exp_avg"], st["exp_avg_sq"], b1, b2, cfg.eps, step_size,
-                       cfg.wd_mul * cfg.weight_decay * cfg.lr)
+                       lr * lr * cfg.weight_decay * cfg.wd_mul)
 
     def _normuon(self, label: str, g: torch.Tensor) -> None:
         cfg, st = self.cfgs[label], self.param_states[label]
@@ -200,14 +203,18 @@ class NorMuonAndAdam:
         v = polar_express(u)
         v = normuon_variance_reduction(v, st["second_momentum_buffer"], cfg.beta2, st["red_dim"])
         p_slice = self._shard(label, self._view(label))
-        wd_lr = cfg.wd_mul * cfg.weight_decay * cfg.lr
+        # p -= p * mask * (wd_mul * wd * lr) * lr_eff + v * lr_eff (modded-nanogpt/train_gpt.py:708-760): the decay
+        # coefficient carries the effective learning rate of the matrix as well
+        wd = cfg.wd_mul * cfg.weight_decay * cfg.lr
         if cfg.per_matrix_lr_mul is not None:
             for i in range(p_slice.shape[0]):
                 j = self.rank * cfg.chunk_size + i if cfg.comms == "sharded" else i
                 mant = st["mantissa"][i] if "mantissa" in st else None
-                cautious_update_(p_slice[i], mant, v[i], cfg.lr * cfg.lr_mul * cfg.per_matrix_lr_mul[j], wd_lr)
+                lr_eff = cfg.lr * cfg.lr_mul * cfg.per_matrix_lr_mul[j]
+                cautious_update_(p_slice[i], mant, v[i], lr_eff, wd * lr_eff)
         else:
-            cautious_update_(p_slice, st.get("mantissa"), v, cfg.lr * cfg.lr_mul, wd_lr)
+            lr_eff = cfg.lr * cfg.lr_mul
+            cautious_update_(p_slice, st.get("mantissa"), v, lr_eff, wd * lr_eff)
 
     @torch.no_grad()
     def step(self, do_adam: bool = True) -> None:
@@ -309,7 +316,11 @@ class NorMuon(torch.optim.Optimizer):
                     full = v
                 scale = max(1.0, shape[-2] / shape[-1]) ** 0.5
                 for i, p in enumerate(plist):
-                    cautious_update_(p, None, full[i] * scale, hp["lr"], hp["weight_decay"] * hp["lr"])
+                    # eff_lr = shape_mult * lr_mul * lr ; eff_wd = wd_mul * wd * lr ; decay coefficient eff_wd * eff_lr
+                    # (modded-nanogpt/train_gpt_medium.py:428-433,626-647)
+                    lr_eff = scale * getattr(p, "lr_mul", 1.0) * hp["lr"]
+                    wd = getattr(p, "wd_mul", 1.0) * hp["weight_decay"] * hp["lr"]
+                    cautious_update_(p, None, full[i], lr_eff, wd * lr_eff)
 
 
 class DistAdam(torch.optim.Optimizer):
@@ -364,8 +375,11 @@ class DistAdam(torch.optim.Optimizer):
                     st["exp_avg_sq"] = torch.zeros_like(p_slice, dtype=torch.float32)
                 st["step"] += 1
                 t = st["step"]
+                # lr = group lr * param.lr_mul ; decay = lr * wd * wd_mul * lr (modded-nanogpt/train_gpt_medium.py:805-826)
+                lr = hp["lr"] * getattr(p, "lr_mul", 1.0)
                 adam_cautious_(p_slice, g.float(), st["exp_avg"], st["exp_avg_sq"], b1, b2, hp["eps"],
-                               hp["lr"] * math.sqrt(1 - b2 ** t) / (1 - b1 ** t), hp["weight_decay"] * hp["lr"])
+                               lr * math.sqrt(1 - b2 ** t) / (1 - b1 ** t),
+                               lr * lr * hp["weight_decay"] * getattr(p, "wd_mul", 1.0))
                 if sharded:
                     gathers.append(dist.all_gather_into_tensor(p.data, p_slice.contiguous(), group=self.group, async_op=True))
         for w in gathers:

@@ -85,6 +85,8 @@ class DistributedDataParallel(nn.Module):
                 p.register_post_accumulate_grad_hook(self._hook)
         self._comm_stream = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
         self._in_flight = False
+        self._next_launch = 0
+        self.launch_order: list[int] = []     # bucket indices in the order their all-reduce was enqueued (last backward)
 
     def forward(self, *args, **kwargs):
         return self.module(*args, **kwargs)
@@ -106,15 +108,24 @@ class DistributedDataParallel(nn.Module):
         if not self._in_flight:
             self._in_flight = True
             self._step += 1
+            self._next_launch = 0
             for bb in self.buckets:
                 bb.pending = len(bb.params)
         b.views[pi].copy_(p.grad)
         b.pending -= 1
-        if b.pending == 0:
-            self._launch(bi)
+        # Buckets are launched strictly in index order on every rank, whatever order they fill in (a parameter used by
+        # every layer, listed late, gets its gradient last and would otherwise let a higher bucket go first): all
+        # buckets share one pair of flag channels whose epoch grows with the bucket index, so an out-of-order launch
+        # would let a peer's wait for bucket i be satisfied by bucket i+1's larger epoch.
+        while self._next_launch < len(self.buckets) and self.buckets[self._next_launch].pending == 0:
+            self._launch(self._next_launch)
+            self._next_launch += 1
 
     def _launch(self, bi: int):
         b = self.buckets[bi]
+        if bi == 0:
+            self.launch_order = []
+        self.launch_order.append(bi)
         if b.symm is not None:
             from ..ops.runtime import ops, status
 

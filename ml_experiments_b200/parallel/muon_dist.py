@@ -57,6 +57,21 @@ class GradSync:
             w.wait()
 
 
+def _momentum_shards(groups) -> dict:
+    return {f"mom_{g['r']}x{g['c']}": g["mom"].detach().clone() for g in groups}
+
+
+def _load_momentum(groups, shard: dict) -> None:
+    for g in groups:
+        t = shard.get(f"mom_{g['r']}x{g['c']}")
+        if t is None:
+            continue
+        if tuple(t.shape) != tuple(g["mom"].shape):
+            raise ValueError(f"momentum shard {tuple(t.shape)} does not fit this rank's slice {tuple(g['mom'].shape)}: "
+                             "load it through utils.checkpoint.load_sharded, which re-partitions for the world size")
+        g["mom"].copy_(t)
+
+
 class DistMuon(torch.optim.Optimizer):
     def __init__(self, params, comm: GradSync, lr: float = 0.02, momentum: float = 0.95, nesterov: bool = True,
                  ns_steps: int = 5):
@@ -65,6 +80,7 @@ class DistMuon(torch.optim.Optimizer):
         self.rank, self.world, self.group = comm.rank, comm.world, comm.group
         self._work: dict = {}
         self._groups = None
+        self._pending_shard = None
 
     def _build(self, params):
         W = self.world
@@ -87,6 +103,24 @@ class DistMuon(torch.optim.Optimizer):
                 u_full=torch.empty(padded, r, c, dtype=torch.bfloat16, device=dev),
                 sumsq=torch.zeros(per, dtype=torch.float32, device=dev)))
         self._groups = groups
+        if self._pending_shard is not None:
+            _load_momentum(self._groups, self._pending_shard)
+            self._pending_shard = None
+
+    # -- sharded momentum: lives in the per-shape stacks, not in ``Optimizer.state`` (one slice per rank)
+    def sharded_state(self) -> dict:
+        """``{"mom_{rows}x{cols}": this rank's [per, rows, cols] momentum slice}`` (empty before the first step)."""
+        return _momentum_shards(self._groups or [])
+
+    def sharded_rows(self) -> dict:
+        """Number of real (unpadded) matrices per stack, for re-partitioning under another world size."""
+        return {f"mom_{g['r']}x{g['c']}": g["total"] for g in (self._groups or [])}
+
+    def load_sharded_state(self, shard: dict) -> None:
+        if self._groups is None:
+            self._pending_shard = shard        # the stacks are built at the first step
+        else:
+            _load_momentum(self._groups, shard)
 
     @torch.no_grad()
     def step(self, closure=None):
@@ -94,9 +128,11 @@ class DistMuon(torch.optim.Optimizer):
         params = [p for p in group["params"] if p.grad is not None]
         if self._groups is None:
             self._build(params)
-        o = ops()
         mu, nesterov, lr = float(group["momentum"]), bool(group["nesterov"]), float(group["lr"])
         coeffs = [NS5_COEFFS[0]] * group["ns_steps"]
+        if not params[0].is_cuda:
+            return self._step_host(mu, nesterov, lr, coeffs)
+        o = ops()
         # 1. stack gradients and launch every reduce-scatter
         works = []
         for g in self._groups:
@@ -132,6 +168,40 @@ class DistMuon(torch.optim.Optimizer):
                 o.axpy_bf16_to_f32(p, upd, sh, alpha)
                 mark_modified(p)
                 set_shadow(p, sh)
+                slot += nmat
+        return None
+
+
+    def _step_host(self, mu, nesterov, lr, coeffs):
+        """The same work split in plain torch for CPU tensors (gloo ranks): what the host-side logic (ownership,
+        padding, sharded momentum, checkpoints) is tested with where no GPU is present."""
+        from ..ops.newton_schulz import newton_schulz_torch
+
+        for g in self._groups:
+            slot = 0
+            for p, nmat in g["plist"]:
+                g["g_full"][slot:slot + nmat].view(p.shape).copy_(p.grad.float())
+                slot += nmat
+            if self.world > 1:
+                # gloo has no reduce-scatter: all-reduce the stack and keep the owned slice
+                dist.all_reduce(g["g_full"], op=dist.ReduceOp.SUM, group=self.group)
+                g["g_full"].div_(self.world)
+            per = g["per"]
+            mine = g["g_full"][self.rank * per:(self.rank + 1) * per]
+            g["mom"].lerp_(mine, 1 - mu)
+            u = mine.lerp(g["mom"], mu) if nesterov else g["mom"]
+            g["u_shard"].copy_(newton_schulz_torch(u, coeffs))
+            if self.world > 1:
+                parts = [torch.empty_like(g["u_shard"]) for _ in range(self.world)]
+                dist.all_gather(parts, g["u_shard"].contiguous(), group=self.group)
+                g["u_full"].copy_(torch.cat(parts, 0))
+            else:
+                g["u_full"].copy_(g["u_shard"])
+            alpha = -lr * max(1.0, g["r"] / g["c"]) ** 0.5
+            slot = 0
+            for p, nmat in g["plist"]:
+                p.add_(g["u_full"][slot:slot + nmat].view(p.shape).to(p.dtype), alpha=alpha)
+                mark_modified(p)
                 slot += nmat
         return None
 
@@ -253,6 +323,15 @@ class FusedDistMuon(torch.optim.Optimizer):
         params = [*params]
         super().__init__(params, dict(lr=lr, momentum=momentum, nesterov=nesterov, ns_steps=ns_steps))
         self.engine = MuonShardEngine(params, world)
+
+    def sharded_state(self) -> dict:
+        return _momentum_shards(self.engine.groups)
+
+    def sharded_rows(self) -> dict:
+        return {f"mom_{g['r']}x{g['c']}": g["total"] for g in self.engine.groups}
+
+    def load_sharded_state(self, shard: dict) -> None:
+        _load_momentum(self.engine.groups, shard)
 
     @torch.no_grad()
     def step(self, closure=None):

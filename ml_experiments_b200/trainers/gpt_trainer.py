@@ -179,9 +179,40 @@ class GPTTrainer:
 
     def load_state_dict(self, sd):
         self.step = sd["step"]
-        self.model.load_state_dict(sd["model"])
+        with torch.no_grad():
+            # copy into the existing storage: the distributed Muon keeps its matrices in banked buffers
+            for n, p in self.model.state_dict().items():
+                p.copy_(sd["model"][n])
+        from ..utils.shadow import mark_modified
+
+        for p in self.model.parameters():
+            mark_modified(p)
         for opt, s in zip(self.optimizers, sd["optimizers"]):
             opt.load_state_dict(s)
+
+    # -- checkpoints of a distributed run: the replicated part once, the sharded Muon momentum from every rank
+    def save_checkpoint(self, path) -> None:
+        """Every rank must call this. Rank 0 writes ``path`` (step, model, replicated optimizer state); each rank
+        writes ``path.rank{r}`` with its slice of the Muon momentum (which lives outside ``Optimizer.state``)."""
+        from ..utils.checkpoint import save_sharded
+
+        opt2 = self.optimizer2
+        shard = opt2.sharded_state() if hasattr(opt2, "sharded_state") else {}
+        rows = opt2.sharded_rows() if hasattr(opt2, "sharded_rows") else {}
+        sd = self.state_dict()
+        if shard:
+            # the momentum is saved through the shards; drop per-parameter views of the same buffers
+            sd["optimizers"][1] = dict(sd["optimizers"][1], state={})
+        save_sharded(sd, {k: v.cpu() for k, v in shard.items()}, path, self.rank, self.world_size, rows)
+
+    def load_checkpoint(self, path) -> None:
+        """Counterpart of :meth:`save_checkpoint`; the world size may differ from the one that saved."""
+        from ..utils.checkpoint import load_sharded
+
+        rep, shard = load_sharded(path, self.rank, self.world_size)
+        self.load_state_dict(rep)
+        if shard and hasattr(self.optimizer2, "load_sharded_state"):
+            self.optimizer2.load_sharded_state({k: v.to(self.device) for k, v in shard.items()})
 
 
 def synthetic_batch(seq_len: int, vocab: int = 50257, doc_len: int = 1024, seed: int = 0, pin: bool = True):

@@ -66,3 +66,58 @@ def test_ddp_matches_single_process(tmp_path):
         opt.zero_grad()
     want = torch.cat([p.detach().reshape(-1) for p in net.parameters()])
     assert torch.allclose(got, want, atol=1e-5), (got - want).abs().max()
+
+
+class _LateScale(torch.nn.Module):
+    """The parameter listed LAST (so it sits in bucket 0) is used by the first layer: its gradient arrives last and
+    every other bucket is complete before bucket 0."""
+
+    def __init__(self):
+        super().__init__()
+        self.a = torch.nn.Linear(8, 16)
+        self.b = torch.nn.Linear(16, 4)
+        self.late = torch.nn.ParameterList([torch.nn.Parameter(torch.ones(8))])   # a child registered last: listed last
+
+    def forward(self, x):
+        return self.b(torch.tanh(self.a(x * self.late[0])))
+
+
+def _worker_out_of_order(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from ml_experiments_b200.parallel.ddp import DistributedDataParallel as DDP
+
+        torch.manual_seed(0)
+        net = _LateScale()
+        ddp = DDP(net, bucket_cap_mb=0.00001)          # one bucket per parameter
+        assert len(ddp.buckets) == 5 and ddp.buckets[0].params[0] is net.late[0]
+        filled = []
+        orig = ddp._launch
+        ddp._launch = lambda bi: (filled.append([b.pending for b in ddp.buckets]), orig(bi))[1]
+        g = torch.Generator().manual_seed(5)
+        x, y = torch.randn(world * 4, 8, generator=g), torch.randn(world * 4, 4, generator=g)
+        torch.nn.functional.mse_loss(ddp(x[rank * 4:(rank + 1) * 4]), y[rank * 4:(rank + 1) * 4]).backward()
+        # bucket 0 was the last to fill, yet the launches went out as 0, 1, 2, ... (all at once, after it filled)
+        assert ddp.launch_order == list(range(5)), ddp.launch_order
+        assert filled[0] == [0] * 5, filled
+        ddp.finish()
+        if rank == 0:
+            torch.save(torch.cat([p.grad.reshape(-1) for p in net.parameters()]), out)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_buckets_launch_in_index_order_when_they_fill_out_of_order(tmp_path):
+    world = 2
+    out = str(tmp_path / "g.pt")
+    mp.spawn(_worker_out_of_order, args=(world, _free_port(), out), nprocs=world, join=True)
+    got = torch.load(out)
+    torch.manual_seed(0)
+    net = _LateScale()
+    g = torch.Generator().manual_seed(5)
+    x, y = torch.randn(world * 4, 8, generator=g), torch.randn(world * 4, 4, generator=g)
+    loss = sum(torch.nn.functional.mse_loss(net(x[r * 4:(r + 1) * 4]), y[r * 4:(r + 1) * 4]) for r in range(world)) / world
+    loss.backward()
+    want = torch.cat([p.grad.reshape(-1) for p in net.parameters()])
+    assert torch.allclose(got, want, atol=1e-6)

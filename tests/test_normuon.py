@@ -132,3 +132,64 @@ def test_sharded_equals_single_process_on_mean_gradient(tmp_path):
         opt.step()
     for k in params:
         assert torch.allclose(got[k], params[k].detach(), atol=2e-3), (k, (got[k] - params[k]).abs().max())
+
+
+def _reference_adam_step(p, g, m, v, beta1, beta2, eps, step_size, eff_wd):
+    """The reference's compiled Adam update (modded-nanogpt/train_gpt.py:683-691), restated line by line."""
+    m.mul_(beta1).add_(g, alpha=1 - beta1)
+    v.mul_(beta2).addcmul_(g, g, value=1 - beta2)
+    update = m.div(v.sqrt().add_(eps)).mul_(step_size)
+    mask = (update * p) > 0
+    update.addcmul_(p, mask, value=eff_wd)
+    p.add_(other=update, alpha=-1.0)
+
+
+def test_adam_weight_decay_follows_lr_squared_schedule():
+    """eff_wd = (lr * lr_mul)**2 * weight_decay * wd_mul in the combined optimizer (modded-nanogpt/train_gpt.py:658-672)
+    and lr * wd * wd_mul * lr with lr = group lr * param.lr_mul in DistAdam (train_gpt_medium.py:805-826)."""
+    torch.manual_seed(5)
+    lr, wd, lr_mul, wd_mul, betas = 0.008, 0.005, 5.0, 3.0, (0.65, 0.95)
+    p0 = torch.randn(64, 8)
+    grads = [torch.randn(64, 8) for _ in range(3)]
+    # combined optimizer
+    p = torch.nn.Parameter(p0.clone())
+    opt = NorMuonAndAdam([("x", p)], {"x": dict(optim="adam", comms="none", adam_betas=betas, lr_mul=lr_mul, wd_mul=wd_mul)},
+                         adam_defaults=None, world_size=1, rank=0)
+    ref, m, v = p0.clone(), torch.zeros_like(p0), torch.zeros_like(p0)
+    for t, g in enumerate(grads, 1):
+        p.grad = g.clone()
+        opt.step()
+        l = lr * lr_mul
+        _reference_adam_step(ref, g, m, v, betas[0], betas[1], 1e-10, l * ((1 - betas[1] ** t) ** 0.5 / (1 - betas[0] ** t)),
+                             l * l * wd * wd_mul)
+    assert torch.allclose(p.detach(), ref, atol=1e-6), (p.detach() - ref).abs().max()
+    # DistAdam honours p.lr_mul / p.wd_mul
+    q = torch.nn.Parameter(p0.clone())
+    q.lr_mul, q.wd_mul = lr_mul, wd_mul
+    da = DistAdam([q], lr=lr, betas=betas, eps=1e-10, weight_decay=wd)
+    ref, m, v = p0.clone(), torch.zeros_like(p0), torch.zeros_like(p0)
+    for t, g in enumerate(grads, 1):
+        q.grad = g.clone()
+        da.step()
+        l = lr * lr_mul
+        _reference_adam_step(ref, g, m, v, betas[0], betas[1], 1e-10, l * ((1 - betas[1] ** t) ** 0.5 / (1 - betas[0] ** t)),
+                             l * wd * wd_mul * l)
+    assert torch.allclose(q.detach(), ref, atol=1e-6), (q.detach() - ref).abs().max()
+
+
+def test_normuon_decay_is_scaled_by_the_effective_lr():
+    """p -= p * mask * (wd_mul * wd * lr) * lr_eff + v * lr_eff (modded-nanogpt/train_gpt.py:708-760)."""
+    torch.manual_seed(6)
+    p0 = torch.randn(2, 16, 16) * 0.3
+    p = torch.nn.Parameter(p0.clone())
+    opt = NorMuonAndAdam([("w", p)], {"w": dict(optim="normuon", comms="none", lr=0.02, weight_decay=1.5, lr_mul=2.0, wd_mul=0.5)},
+                         world_size=1, rank=0)
+    g = torch.randn_like(p0)
+    p.grad = g.clone()
+    opt.step()
+    mom = torch.zeros_like(g).lerp_(g, 1 - 0.95)
+    u = g.lerp(mom, 0.95)
+    v = normuon_variance_reduction(polar_express(u), torch.zeros(2, 16, 1), 0.95, -1).float()
+    lr_eff = 0.02 * 2.0
+    want = p0 - p0 * ((v * p0) >= 0) * (0.5 * 1.5 * 0.02) * lr_eff - v * lr_eff
+    assert torch.allclose(p.detach(), want, atol=1e-6), (p.detach() - want).abs().max()
