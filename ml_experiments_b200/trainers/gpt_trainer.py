@@ -133,16 +133,27 @@ class GPTTrainer:
             if p.grad is not None:
                 dist.all_reduce(p.grad, op=dist.ReduceOp.AVG)
 
-    def train_step(self, inputs: torch.Tensor, targets: torch.Tensor, window: int | None = None) -> torch.Tensor:
-        """One optimizer step on a flat token sequence. Host tensors are copied to the device (non-blocking)."""
+    def train_step(self, inputs, targets, window: int | None = None) -> torch.Tensor:
+        """One optimizer step on a flat token sequence. Host tensors are copied to the device (non-blocking).
+
+        ``inputs`` / ``targets`` may also be equally long lists of sequences: their gradients are accumulated and
+        averaged before the one optimizer step (the reference's single-GPU runs reach the 8-GPU batch this way:
+        records/track_1_short/2026-01-10_FusedLinearReLUSquare/single_gpu_run.txt, grad-accum 8)."""
         hp = self.hp
-        if inputs.device != self.device:
-            inputs = inputs.to(self.device, non_blocking=True)
-            targets = targets.to(self.device, non_blocking=True)
-        if targets.dtype != torch.int64:
-            targets = targets.to(torch.int64)
         w = window_blocks(self.step, hp) if window is None else window
-        loss = self.model.loss_and_grad(inputs, targets, w)
+        micro = list(zip(inputs, targets)) if isinstance(inputs, (list, tuple)) else [(inputs, targets)]
+        loss = None
+        for x, y in micro:
+            if x.device != self.device:
+                x = x.to(self.device, non_blocking=True)
+                y = y.to(self.device, non_blocking=True)
+            if y.dtype != torch.int64:
+                y = y.to(torch.int64)
+            l = self.model.loss_and_grad(x, y, w)
+            loss = l if loss is None else loss + l
+        if len(micro) > 1:
+            loss = loss / len(micro)
+            torch._foreach_mul_([p.grad for p in self.model.parameters() if p.grad is not None], 1.0 / len(micro))
         frac = min(self.step / hp.muon_momentum_warmup_steps, 1)
         for g in self.optimizer2.param_groups:
             g["momentum"] = (1 - frac) * 0.85 + frac * 0.95

@@ -1,0 +1,30 @@
+"""Multi-process checks on real GPUs (skipped on a box with fewer than 2): launched as torchrun children."""
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _torchrun(script, *args, nproc=2, timeout=600):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), os.path.join(ROOT, script), *args]
+    return subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, cwd=ROOT)
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("mode", ["fused", "nccl"])
+def test_two_ranks_match_single_process_with_accumulation(mode):
+    r = _torchrun("tests/multi_gpu/check_gpt_ranks_vs_single.py", "--mode", mode)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
