@@ -1,10 +1,21 @@
-"""Learned auxiliary loss ("ponder"): a small network scores ``(logits, target)`` pairs and the classifier minimises
-cross-entropy plus that score, while the scorer is trained first to predict per-sample CE and then by REINFORCE on the
-accuracy gain of each base step. Mirrors src/heuristic_secrets/models/ponder.py:15-319.
+"""Learned auxiliary loss ("ponder") for classifiers.
+
+A small scoring network looks at ``(logits, target)`` and emits a positive number per sample; the classifier is trained
+on cross entropy plus that (batch-normalised) score. The scorer itself learns in two regimes that are blended by a
+schedule: regression onto the per-sample cross entropy, and REINFORCE with the accuracy gained by the classifier's
+last update as reward. Public names and constructor arguments follow the reference
+(src/heuristic_secrets/models/ponder.py: ``SiLUAttentionBlock``, ``InternalLossNetwork``, ``PonderWrapper``,
+``PonderTrainConfig``, ``PonderTrainer``).
+
+Organisation here: one optimisation step is three explicit phases (:meth:`PonderTrainer._classifier_phase`,
+:meth:`_reward_phase`, :meth:`_scorer_phase`). The classifier runs twice per batch, not four times: the logits of the
+training forward also give the accuracy before the update, and the no-grad forward after the update gives both the
+reward and the (detached) scorer input, because the scorer phase never updates the classifier.
 """
 from __future__ import annotations
 
 import math
+from collections import defaultdict
 from dataclasses import dataclass
 
 import torch
@@ -12,70 +23,83 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 
+# ------------------------------------------------------------------------------------------------ scorer
 class SiLUAttentionBlock(nn.Module):
-    """Pre-norm attention block whose q, k, v pass through SiLU, followed by a SiLU MLP."""
+    """Pre-norm self-attention with SiLU applied to the projected q, k and v, then a SiLU MLP; both residual."""
 
     def __init__(self, dim: int, n_heads: int = 4):
         super().__init__()
+        if dim % n_heads:
+            raise ValueError(f"dim {dim} is not divisible by n_heads {n_heads}")
         self.n_heads, self.head_dim = n_heads, dim // n_heads
-        self.q, self.k, self.v, self.out = (nn.Linear(dim, dim) for _ in range(4))
-        self.mlp = nn.Sequential(nn.Linear(dim, dim * 2), nn.SiLU(), nn.Linear(dim * 2, dim))
+        self.q, self.k, self.v, self.out = nn.Linear(dim, dim), nn.Linear(dim, dim), nn.Linear(dim, dim), nn.Linear(dim, dim)
+        self.mlp = nn.Sequential(nn.Linear(dim, 2 * dim), nn.SiLU(), nn.Linear(2 * dim, dim))
         self.norm1, self.norm2 = nn.LayerNorm(dim), nn.LayerNorm(dim)
 
-    def forward(self, x):
-        B, L, C = x.shape
+    def _heads(self, proj: nn.Linear, h: torch.Tensor) -> torch.Tensor:
+        return F.silu(proj(h)).unflatten(-1, (self.n_heads, self.head_dim)).transpose(-3, -2)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
         h = self.norm1(x)
-        split = lambda lin: F.silu(lin(h)).view(B, L, self.n_heads, self.head_dim).transpose(1, 2)
-        o = F.scaled_dot_product_attention(split(self.q), split(self.k), split(self.v)).transpose(1, 2).reshape(B, L, C)
-        x = x + self.out(o)
+        att = F.scaled_dot_product_attention(self._heads(self.q, h), self._heads(self.k, h), self._heads(self.v, h))
+        x = x + self.out(att.transpose(-3, -2).flatten(-2))
         return x + self.mlp(self.norm2(x))
 
 
 class InternalLossNetwork(nn.Module):
-    """``(logits [B, C], targets [B]) -> positive score [B]``: two tokens (logits, one-hot target) through attention."""
+    """Scores ``(logits [B, C], targets [B])`` with a positive number per sample. The logits and the one-hot target are
+    embedded by the same projection and attended to as a two-token sequence."""
 
     def __init__(self, n_classes: int, n_layers: int = 1, width: int | None = None, n_heads: int = 2):
         super().__init__()
         if width is None:
-            width = max(n_heads, n_classes)
-            width -= width % n_heads
-        self.proj_in = nn.Linear(n_classes, width) if n_classes != width else nn.Identity()
-        self.blocks = nn.ModuleList([SiLUAttentionBlock(width, n_heads) for _ in range(n_layers)])
+            width = max(n_heads, n_classes) // n_heads * n_heads
+        self.n_classes = n_classes
+        self.proj_in = nn.Identity() if n_classes == width else nn.Linear(n_classes, width)
+        self.blocks = nn.ModuleList(SiLUAttentionBlock(width, n_heads) for _ in range(n_layers))
         self.head = nn.Linear(width, 1)
         nn.init.xavier_normal_(self.head.weight, gain=0.1)
         nn.init.zeros_(self.head.bias)
 
-    def forward(self, logits, targets):
-        onehot = F.one_hot(targets, logits.shape[1]).to(logits.dtype)
-        x = torch.stack([self.proj_in(logits), self.proj_in(onehot)], dim=1)
-        for block in self.blocks:
-            x = block(x)
-        return F.softplus(self.head(x.mean(dim=1)).squeeze(-1))
+    def forward(self, logits: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        tokens = torch.stack((logits, F.one_hot(targets, self.n_classes).type_as(logits)), dim=1)   # [B, 2, C]
+        h = self.proj_in(tokens)
+        for blk in self.blocks:
+            h = blk(h)
+        return F.softplus(self.head(h.mean(1))[:, 0])
 
 
 class PonderWrapper(nn.Module):
+    """``base`` classifier plus its scorer ``l_internal``. ``forward(x, targets)`` returns ``(logits, aux, raw)`` where
+    ``raw`` is the scorer output and ``aux = raw / mean(raw) * CE`` (statistics detached) is the term added to the loss."""
+
     def __init__(self, model: nn.Module, n_classes: int | None = None, loss_net_width: int | None = None, loss_net_layers: int = 1):
         super().__init__()
         self.base = model
         head = getattr(model, "head", None)
+        n_classes = n_classes if n_classes is not None else getattr(head, "out_features", None)
         if n_classes is None:
-            if head is None or not hasattr(head, "out_features"):
-                raise ValueError("Cannot infer n_classes; pass it explicitly")
-            n_classes = head.out_features
-        if loss_net_width is None and head is not None and hasattr(head, "in_features"):
-            loss_net_width = head.in_features
+            raise ValueError("Cannot infer n_classes; pass it explicitly")
+        if loss_net_width is None:
+            loss_net_width = getattr(head, "in_features", None)
         self.n_classes = n_classes
         self.l_internal = InternalLossNetwork(n_classes, loss_net_layers, loss_net_width)
+
+    def score(self, logits: torch.Tensor, targets: torch.Tensor):
+        raw = self.l_internal(logits, targets)
+        with torch.no_grad():
+            gain = F.cross_entropy(logits, targets) / (raw.mean() + 1e-8)
+        return raw * gain, raw
 
     def forward(self, x, targets=None):
         logits = self.base(x)
         if targets is None:
             return logits, None, None
-        raw = self.l_internal(logits, targets)
-        ce = F.cross_entropy(logits.detach(), targets).detach()
-        return logits, raw / (raw.detach().mean() + 1e-8) * ce, raw
+        aux, raw = self.score(logits, targets)
+        return logits, aux, raw
 
 
+# ------------------------------------------------------------------------------------------------ training
 @dataclass
 class PonderTrainConfig:
     meta_lr: float = 3e-4
@@ -92,96 +116,131 @@ class PonderTrainConfig:
 
 
 def warmup_cosine(total_steps: int, warmup_steps: int):
-    def f(step: int) -> float:
+    """LR multiplier: linear 0 -> 1 over ``warmup_steps``, then half a cosine down to 0 at ``total_steps``."""
+    span = max(total_steps - warmup_steps, 1)
+
+    def mult(step: int) -> float:
         if step < warmup_steps:
             return step / max(warmup_steps, 1)
-        return 0.5 * (1 + math.cos(math.pi * (step - warmup_steps) / max(total_steps - warmup_steps, 1)))
-    return f
+        return 0.5 + 0.5 * math.cos(math.pi * (step - warmup_steps) / span)
+
+    return mult
+
+
+class _Half:
+    """Optimizer + scheduler + clipping of one of the two parameter sets."""
+
+    def __init__(self, params, lr, weight_decay, clip, lr_mult):
+        self.params = list(params)
+        self.clip = clip
+        self.opt = torch.optim.AdamW(self.params, lr=lr, weight_decay=weight_decay)
+        self.sched = torch.optim.lr_scheduler.LambdaLR(self.opt, lr_mult)
+
+    def update(self, loss: torch.Tensor) -> None:
+        self.opt.zero_grad(set_to_none=True)
+        loss.backward()
+        torch.nn.utils.clip_grad_norm_(self.params, self.clip)
+        self.opt.step()
+        self.sched.step()
 
 
 class PonderTrainer:
     def __init__(self, ponder: PonderWrapper, train_loader, test_loader, device, config: PonderTrainConfig | None = None,
                  flatten_input: bool = False, squeeze_channel: bool = True):
-        self.ponder, self.device = ponder.to(device), device
-        self.train_loader, self.test_loader = train_loader, test_loader
         self.config = cfg = config or PonderTrainConfig()
+        self.device = device
+        self.ponder = ponder.to(device)
+        self.train_loader, self.test_loader = train_loader, test_loader
         self.flatten_input, self.squeeze_channel = flatten_input, squeeze_channel
-        self.model_optimizer = torch.optim.AdamW(ponder.base.parameters(), lr=cfg.model_lr, weight_decay=cfg.weight_decay)
-        self.meta_optimizer = torch.optim.AdamW(ponder.l_internal.parameters(), lr=cfg.meta_lr, weight_decay=cfg.weight_decay)
-        sched = warmup_cosine(cfg.epochs * len(train_loader), cfg.warmup_epochs * len(train_loader))
-        self.model_scheduler = torch.optim.lr_scheduler.LambdaLR(self.model_optimizer, sched)
-        self.meta_scheduler = torch.optim.lr_scheduler.LambdaLR(self.meta_optimizer, sched)
-        self.best_acc, self._reward_ema = 0.0, 0.0
+        steps = len(train_loader)
+        mult = warmup_cosine(cfg.epochs * steps, cfg.warmup_epochs * steps)
+        self._classifier = _Half(ponder.base.parameters(), cfg.model_lr, cfg.weight_decay, cfg.grad_clip, mult)
+        self._scorer = _Half(ponder.l_internal.parameters(), cfg.meta_lr, cfg.weight_decay, cfg.grad_clip, mult)
+        self.model_optimizer, self.meta_optimizer = self._classifier.opt, self._scorer.opt
+        self.model_scheduler, self.meta_scheduler = self._classifier.sched, self._scorer.sched
+        self.best_acc = 0.0
+        self._reward_ema = 0.0
 
-    def _prep_input(self, images):
+    # -- helpers
+    def _prep_input(self, images: torch.Tensor) -> torch.Tensor:
         images = images.to(self.device)
         if self.flatten_input:
-            return images.view(images.size(0), -1)
-        return images.squeeze(1) if self.squeeze_channel and images.dim() == 4 else images
+            return images.flatten(1)
+        if self.squeeze_channel and images.dim() == 4:
+            return images.squeeze(1)
+        return images
 
     def _reinforce_alpha(self, epoch: int) -> float:
+        """Share of the REINFORCE objective in the scorer loss: 0 during the scorer's warm-up, then a linear ramp over
+        ``meta_wean_epochs`` up to ``1 - meta_min_supervised``."""
         cfg = self.config
-        if epoch < cfg.meta_warmup_epochs:
-            return 0.0
-        return min((epoch - cfg.meta_warmup_epochs) / max(cfg.meta_wean_epochs, 1), 1.0 - cfg.meta_min_supervised)
+        ramp = (epoch - cfg.meta_warmup_epochs) / max(cfg.meta_wean_epochs, 1)
+        return min(max(ramp, 0.0), 1.0 - cfg.meta_min_supervised)
 
+    # -- the three phases of a step
+    def _classifier_phase(self, x, y):
+        """CE + auxiliary score -> classifier update. Returns the accuracy before the update and the mean raw score."""
+        logits, aux, raw = self.ponder(x, y)
+        acc_before = (logits.detach().argmax(-1) == y).float().mean().item()
+        self._classifier.update(F.cross_entropy(logits, y) + aux.mean())
+        return acc_before, raw.detach().mean().item()
+
+    @torch.no_grad()
+    def _reward_phase(self, x, y, acc_before: float):
+        """Accuracy gained by the update, centred by a running mean and scaled. Also returns the fresh logits."""
+        logits = self.ponder.base(x)
+        acc = (logits.argmax(-1) == y).float().mean().item()
+        gain = acc - acc_before
+        self._reward_ema += 0.01 * (gain - self._reward_ema)
+        return logits, acc, (gain - self._reward_ema) * self.config.reward_scale
+
+    def _scorer_phase(self, logits, y, reward: float, alpha: float) -> float:
+        """Scorer update on detached logits: ``alpha`` * REINFORCE + ``(1 - alpha)`` * regression onto per-sample CE."""
+        aux, _ = self.ponder.score(logits, y)
+        target = F.cross_entropy(logits, y, reduction="none")
+        loss = (1.0 - alpha) * F.mse_loss(aux, target) - alpha * reward * aux.mean()
+        self._scorer.update(loss)
+        return loss.item()
+
+    # -- epochs
     def train_epoch(self, epoch: int) -> dict:
         self.ponder.train()
-        cfg, alpha = self.config, self._reinforce_alpha(epoch)
-        running, count = {}, 0
+        alpha = self._reinforce_alpha(epoch)
+        sums: dict = defaultdict(float)
+        n = 0
         for images, labels in self.train_loader:
-            images, labels = self._prep_input(images), labels.to(self.device)
-            with torch.no_grad():
-                pre_acc = (self.ponder(images, labels)[0].argmax(-1) == labels).float().mean()
-            self.model_optimizer.zero_grad()
-            logits, predicted, raw = self.ponder(images, labels)
-            (F.cross_entropy(logits, labels) + predicted.mean()).backward()
-            torch.nn.utils.clip_grad_norm_(self.ponder.base.parameters(), cfg.grad_clip)
-            self.model_optimizer.step()
-            self.model_scheduler.step()
-            with torch.no_grad():
-                post = self.ponder(images, labels)[0]
-                post_ce, post_acc = F.cross_entropy(post, labels), (post.argmax(-1) == labels).float().mean()
-                gain = (post_acc - pre_acc).item()
-                self._reward_ema = 0.99 * self._reward_ema + 0.01 * gain
-                reward = (gain - self._reward_ema) * cfg.reward_scale
-            self.meta_optimizer.zero_grad()
-            logits_m, predicted_m, _ = self.ponder(images, labels)
-            per_sample_ce = F.cross_entropy(logits_m, labels, reduction="none").detach()
-            meta_loss = alpha * -(reward * predicted_m).mean() + (1 - alpha) * F.mse_loss(predicted_m, per_sample_ce)
-            meta_loss.backward()
-            torch.nn.utils.clip_grad_norm_(self.ponder.l_internal.parameters(), cfg.grad_clip)
-            self.meta_optimizer.step()
-            self.meta_scheduler.step()
-            step = {"predicted_loss": raw.detach().mean().item(), "ce": post_ce.item(), "reward": reward,
-                    "accuracy": post_acc.item(), "alpha": alpha, "meta_loss": meta_loss.item()}
-            for k, v in step.items():
-                running[k] = running.get(k, 0.0) + v
-            count += 1
-        return {k: v / max(count, 1) for k, v in running.items()}
+            x, y = self._prep_input(images), labels.to(self.device)
+            acc_before, score = self._classifier_phase(x, y)
+            logits, acc, reward = self._reward_phase(x, y, acc_before)
+            meta_loss = self._scorer_phase(logits, y, reward, alpha)
+            for k, v in (("predicted_loss", score), ("ce", F.cross_entropy(logits, y).item()), ("reward", reward),
+                         ("accuracy", acc), ("alpha", alpha), ("meta_loss", meta_loss)):
+                sums[k] += v
+            n += 1
+        return {k: v / max(n, 1) for k, v in sums.items()}
 
     @torch.no_grad()
     def evaluate(self) -> tuple[float, float, float]:
+        """``(mean CE, accuracy, mean raw score)`` on the test loader."""
         self.ponder.eval()
-        correct = total = 0
-        ce = pred = 0.0
+        ce = score = 0.0
+        hits = seen = 0
         for images, labels in self.test_loader:
-            images, labels = self._prep_input(images), labels.to(self.device)
-            logits, _, raw = self.ponder(images, labels)
-            ce += F.cross_entropy(logits, labels).item() * labels.size(0)
-            pred += raw.sum().item()
-            correct += (logits.argmax(-1) == labels).sum().item()
-            total += labels.size(0)
-        n = max(total, 1)
-        return ce / n, correct / n, pred / n
+            x, y = self._prep_input(images), labels.to(self.device)
+            logits, _, raw = self.ponder(x, y)
+            ce += F.cross_entropy(logits, y, reduction="sum").item()
+            score += raw.sum().item()
+            hits += int((logits.argmax(-1) == y).sum())
+            seen += y.numel()
+        seen = max(seen, 1)
+        return ce / seen, hits / seen, score / seen
 
     def train(self, epochs: int | None = None, verbose: bool = True) -> float:
         for epoch in range(epochs or self.config.epochs):
             m = self.train_epoch(epoch)
-            test_ce, test_acc, test_pred = self.evaluate()
+            test_ce, test_acc, test_score = self.evaluate()
             self.best_acc = max(self.best_acc, test_acc)
             if verbose:
-                print(f"Epoch {epoch + 1:3d}: pred={m['predicted_loss']:.4f} ce={m['ce']:.4f} rw={m['reward']:.4f} "
-                      f"acc={m['accuracy']:.4f} alpha={m['alpha']:.2f} | test_ce={test_ce:.4f} test_pred={test_pred:.4f} "
-                      f"test_acc={test_acc:.4f}")
+                train = " ".join(f"{k}={m[k]:.4f}" for k in ("predicted_loss", "ce", "reward", "accuracy", "alpha"))
+                print(f"[ponder] epoch {epoch + 1}: {train} | test ce={test_ce:.4f} score={test_score:.4f} acc={test_acc:.4f}")
         return self.best_acc

@@ -12,6 +12,7 @@ from functools import partial
 
 import torch
 import torch.nn as nn
+import torch.nn.functional as F
 
 from .config import ModelConfig
 
@@ -32,100 +33,113 @@ class StochasticDepth(nn.Module):
 
 
 class TokenEmbeddings(nn.Module):
+    """Word embeddings (optionally of a narrower width with an input projection, optionally frozen) plus optional
+    learned absolute positions. ``init_type``: ``default`` leaves the table to the model-wide initialiser;
+    ``spherical`` puts every row on the unit sphere; ``normal`` draws N(0, 1)."""
+
     def __init__(self, embed_dim, vocab_size, max_position_embeddings, padding_idx=None, word_embed_proj_dim=None,
                  learnable: bool = True, init_type: str = "default", device=None, dtype=torch.float32):
         super().__init__()
-        dim = word_embed_proj_dim or embed_dim
-        self.word_embeddings = nn.Embedding(vocab_size, dim, padding_idx=padding_idx, device=device, dtype=dtype)
-        self._init_embeddings(self.word_embeddings, init_type, padding_idx)
-        self.project_in = nn.Linear(word_embed_proj_dim, embed_dim, bias=False, device=device, dtype=dtype) if word_embed_proj_dim else None
-        if not learnable:
-            self.word_embeddings.weight.requires_grad = False
+        kw = dict(device=device, dtype=dtype)
+        narrow = word_embed_proj_dim is not None and word_embed_proj_dim > 0
+        self.word_embeddings = nn.Embedding(vocab_size, word_embed_proj_dim if narrow else embed_dim, padding_idx=padding_idx, **kw)
+        self.project_in = nn.Linear(word_embed_proj_dim, embed_dim, bias=False, **kw) if narrow else None
         self.max_position_embeddings = max_position_embeddings
         if max_position_embeddings > 0:
-            self.position_embeddings = nn.Embedding(max_position_embeddings, embed_dim, device=device, dtype=dtype)
+            self.position_embeddings = nn.Embedding(max_position_embeddings, embed_dim, **kw)
+        self._init_embeddings(self.word_embeddings, init_type, padding_idx)
+        self.word_embeddings.weight.requires_grad_(learnable)
 
     @staticmethod
     def _init_embeddings(embedding: nn.Embedding, init_type: str, padding_idx=None):
-        if init_type == "default":
-            return  # the model-wide initialiser sets N(0, 0.02)
+        draw = {"default": None, "spherical": lambda w: F.normalize(torch.randn_like(w), dim=1),
+                "normal": lambda w: torch.randn_like(w)}
+        if init_type not in draw:
+            raise ValueError(f"Unknown init_type: {init_type}. Choose from 'default', 'spherical', 'normal'")
+        if draw[init_type] is None:
+            return
         with torch.no_grad():
-            if init_type == "spherical":
-                v = torch.randn_like(embedding.weight)
-                embedding.weight.copy_(v / v.norm(dim=1, keepdim=True))
-            elif init_type == "normal":
-                embedding.weight.normal_(0.0, 1.0)
-            else:
-                raise ValueError(f"Unknown init_type: {init_type}. Choose from 'default', 'spherical', 'normal'")
+            embedding.weight.copy_(draw[init_type](embedding.weight))
             if padding_idx is not None:
-                embedding.weight[padding_idx].zero_()
-        embedding._no_reinit = True
+                embedding.weight[padding_idx] = 0
+        embedding._no_reinit = True      # the model-wide initialiser must not overwrite it
 
     def forward(self, input_ids, position_ids=None):
-        emb = self.word_embeddings(input_ids)
+        x = self.word_embeddings(input_ids)
         if self.project_in is not None:
-            emb = self.project_in(emb)
+            x = self.project_in(x)
         if self.max_position_embeddings > 0:
-            if position_ids is None:
-                position_ids = torch.arange(input_ids.shape[1], dtype=torch.long, device=input_ids.device)
-            emb = emb + self.position_embeddings(position_ids)
-        return emb
+            pos = position_ids if position_ids is not None else torch.arange(input_ids.shape[1], device=input_ids.device)
+            x = x + self.position_embeddings(pos)
+        return x
+
+
+# Parameters that write into the residual stream: their initial scale shrinks with depth.
+_RESIDUAL_OUTPUTS = ("out_proj.weight", "fc2.weight", "output_linear.0.weight")
 
 
 def _init_weights(module, n_layers, block_type, initializer_range=0.02, rescale_prenorm_residual=True, n_residuals_per_layer=1):
-    mamba = "Mamba" in block_type
+    """Applied to every sub-module (``nn.Module.apply``): N(0, ``initializer_range``) for linear and embedding
+    weights, zero biases, and GPT-2's 1/sqrt(2 n_layers) shrink of everything that writes into the residual stream.
+    Mamba blocks keep their own linear initialisation; their residual outputs are re-drawn Kaiming-uniform and
+    divided by sqrt(n_residuals_per_layer * n_layers). Tensors marked ``_no_reinit`` are left alone."""
+    is_mamba = "Mamba" in block_type
+    skip = lambda t: t is None or getattr(t, "_no_reinit", False)
+    if isinstance(module, nn.Embedding) and not skip(module):
+        nn.init.normal_(module.weight, std=initializer_range)
     if isinstance(module, nn.Linear):
-        if not mamba:
+        if not is_mamba:
             nn.init.normal_(module.weight, std=initializer_range)
-        if module.bias is not None and not getattr(module.bias, "_no_reinit", False):
+        if not skip(module.bias):
             nn.init.zeros_(module.bias)
-    elif isinstance(module, nn.Embedding):
-        if not getattr(module, "_no_reinit", False):
-            nn.init.normal_(module.weight, std=initializer_range)
     if not rescale_prenorm_residual:
         return
-    # residual output projections shrink with depth (GPT-2): std / sqrt(2 * n_layers)
     for name, p in module.named_parameters():
-        if mamba:
-            if name in ("out_proj.weight", "fc2.weight"):
-                nn.init.kaiming_uniform_(p, a=math.sqrt(5))
-                with torch.no_grad():
-                    p /= math.sqrt(n_residuals_per_layer * n_layers)
-        elif "out_proj.weight" in name or "fc2.weight" in name or "output_linear.0.weight" in name:
+        if is_mamba and name in _RESIDUAL_OUTPUTS[:2]:
+            nn.init.kaiming_uniform_(p, a=math.sqrt(5))
+            with torch.no_grad():
+                p.div_(math.sqrt(n_residuals_per_layer * n_layers))
+        elif not is_mamba and any(tag in name for tag in _RESIDUAL_OUTPUTS):
             nn.init.normal_(p, mean=0.0, std=initializer_range / math.sqrt(2 * n_layers))
 
 
+def _join_stream(branch, residual, dropout, drop_path, norm):
+    """Residual-stream bookkeeping shared by the blocks and the backbone's last norm: regularise the branch output,
+    add it to the stream (which starts as the first branch output), return ``(norm(stream), stream)``."""
+    branch = drop_path(dropout(branch)) if drop_path is not None else dropout(branch)
+    stream = branch if residual is None else branch + residual
+    return norm(stream.to(norm.weight.dtype)), stream
+
+
 class TransformerBlock(nn.Module):
+    """Pre-norm block in residual-stream form: it receives the previous branch output and the stream, and returns its
+    own last branch output and the updated stream, so every add sits right before the norm that consumes it."""
+
     def __init__(self, config: ModelConfig, layer_idx: int):
         super().__init__()
-        self.sequence_mixer = config.sequence_mixer.instantiate(d_model=config.d_model, layer_idx=layer_idx)
-        self.state_mixer = config.state_mixer.instantiate(d_model=config.d_model, layer_idx=layer_idx)
+        d = config.d_model
+        self.sequence_mixer = config.sequence_mixer.instantiate(d_model=d, layer_idx=layer_idx)
+        self.state_mixer = config.state_mixer.instantiate(d_model=d, layer_idx=layer_idx)
         self.dropout1 = nn.Dropout(config.embed_dropout if layer_idx == 0 else config.resid_dropout)
-        self.drop_path1 = StochasticDepth(config.drop_path, mode="row")
-        self.norm1 = nn.LayerNorm(config.d_model)
         self.dropout2 = nn.Dropout(config.resid_dropout)
-        self.drop_path2 = StochasticDepth(config.drop_path, mode="row")
-        self.norm2 = nn.LayerNorm(config.d_model)
+        self.drop_path1, self.drop_path2 = StochasticDepth(config.drop_path, mode="row"), StochasticDepth(config.drop_path, mode="row")
+        self.norm1, self.norm2 = nn.LayerNorm(d), nn.LayerNorm(d)
 
     def forward(self, hidden_states, residual=None):
-        dropped = self.drop_path1(self.dropout1(hidden_states))
-        residual = dropped if residual is None else dropped + residual
-        hidden_states = self.sequence_mixer(self.norm1(residual.to(self.norm1.weight.dtype)))
-        dropped = self.drop_path2(self.dropout2(hidden_states))
-        residual = dropped + residual
-        return self.state_mixer(self.norm2(residual.to(self.norm2.weight.dtype))), residual
+        normed, residual = _join_stream(hidden_states, residual, self.dropout1, self.drop_path1, self.norm1)
+        normed, residual = _join_stream(self.sequence_mixer(normed), residual, self.dropout2, self.drop_path2, self.norm2)
+        return self.state_mixer(normed), residual
 
 
 def _block_class(block_type: str):
     if block_type == "TransformerBlock":
         return TransformerBlock
-    if block_type == "MambaBlock":
-        from .mixers.mamba import MambaBlock
-        return MambaBlock
-    if block_type == "Mamba2Block":
-        from .mixers.mamba2 import Mamba2Block
-        return Mamba2Block
-    raise ValueError(f"unknown block_type {block_type}")
+    lazy = {"MambaBlock": ".mixers.mamba", "Mamba2Block": ".mixers.mamba2"}
+    if block_type not in lazy:
+        raise ValueError(f"unknown block_type {block_type}")
+    import importlib
+
+    return getattr(importlib.import_module(lazy[block_type], __package__), block_type)
 
 
 class LMBackbone(nn.Module):
@@ -134,7 +148,7 @@ class LMBackbone(nn.Module):
         self.embeddings = TokenEmbeddings(config.d_model, config.vocab_size, config.max_position_embeddings,
                                           learnable=config.learnable_word_embeddings, init_type=config.embedding_init_type)
         block = _block_class(config.block_type)
-        self.layers = nn.ModuleList([block(config=config, layer_idx=i) for i in range(config.n_layers)])
+        self.layers = nn.ModuleList(block(config=config, layer_idx=i) for i in range(config.n_layers))
         self.drop_f = nn.Dropout(config.resid_dropout)
         self.ln_f = nn.LayerNorm(config.d_model, eps=config.layer_norm_epsilon)
         self.apply(partial(_init_weights, n_layers=config.n_layers, block_type=config.block_type))
@@ -143,9 +157,7 @@ class LMBackbone(nn.Module):
         residual = None
         for layer in self.layers:
             hidden_states, residual = layer(hidden_states, residual)
-        dropped = self.drop_f(hidden_states)
-        residual = dropped if residual is None else dropped + residual
-        return self.ln_f(residual.to(self.ln_f.weight.dtype))
+        return _join_stream(hidden_states, residual, self.drop_f, None, self.ln_f)[0]
 
     def forward(self, input_ids, position_ids=None):
         return self.layers_forward(self.embeddings(input_ids, position_ids=position_ids))
