@@ -337,6 +337,20 @@ void muon_rs_momentum(at::IntArrayRef grad_ptrs, int64_t elem_off, int64_t nmat,
                          (int)epoch, status.data_ptr<int>(), cur_stream());
 }
 
+void adam_shard(at::IntArrayRef grad_ptrs, at::IntArrayRef param_ptrs, int64_t rank, int64_t lo, int64_t hi, int64_t dtype,
+                Tensor m, Tensor v, double lr, double beta1, double beta2, double eps, double wd, double bias1, double bias2,
+                const Tensor& flags, at::IntArrayRef peer_flags, int64_t channel, int64_t epoch, Tensor status,
+                int64_t max_blocks) {
+  const c10::cuda::CUDAGuard guard(m.device());
+  TORCH_CHECK(grad_ptrs.size() == param_ptrs.size() && grad_ptrs.size() == peer_flags.size(), "adam_shard: one pointer per rank");
+  TORCH_CHECK(m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat && m.is_contiguous() && v.is_contiguous() &&
+              m.numel() >= hi - lo && v.numel() >= hi - lo, "adam_shard: m, v fp32 of at least the owned range");
+  b200::adam_shard(to_peers(grad_ptrs), to_peers(param_ptrs), (int)grad_ptrs.size(), (int)rank, lo, hi, (int)dtype,
+                   m.data_ptr<float>(), v.data_ptr<float>(), (float)lr, (float)beta1, (float)beta2, (float)eps, (float)wd,
+                   (float)bias1, (float)bias2, flags.data_ptr<int>(), to_peers(peer_flags), (int)channel, (int)epoch,
+                   status.data_ptr<int>(), (int)max_blocks, cur_stream());
+}
+
 void stack_scale_by_inv_norm(Tensor x, const Tensor& sumsq, int64_t nmat, int64_t mat_elems, double eps) {
   const c10::cuda::CUDAGuard guard(x.device());
   chk_bf16c(x, "x");
@@ -680,6 +694,7 @@ TORCH_LIBRARY(b200, m) {
   m.def("scale_by_inv_norm(Tensor(a!) x, Tensor sumsq, float eps) -> ()");
   m.def("axpy_bf16_to_f32(Tensor(a!) p, Tensor u, Tensor(b!)? p_bf16, float alpha) -> ()");
   m.def("comm_signal(int[] peer_flags, int rank, int channel, int epoch, Tensor like) -> ()");
+  m.def("adam_shard(int[] grad_ptrs, int[] param_ptrs, int rank, int lo, int hi, int dtype, Tensor(a!) m, Tensor(b!) v, float lr, float beta1, float beta2, float eps, float wd, float bias1, float bias2, Tensor flags, int[] peer_flags, int channel, int epoch, Tensor(c!) status, int max_blocks=0) -> ()");
   m.def("comm_wait(Tensor flags, int world, int channel, int epoch, Tensor(a!) status) -> ()");
   m.def("muon_rs_momentum(int[] grad_ptrs, int elem_off, int nmat, int mat_elems, Tensor(a!) mom, Tensor(b!) u_out, Tensor(c!) sumsq, float mu, bool nesterov, Tensor flags, int channel, int epoch, Tensor(d!) status) -> ()");
   m.def("stack_scale_by_inv_norm(Tensor(a!) x, Tensor sumsq, int nmat, int mat_elems, float eps) -> ()");
@@ -732,6 +747,7 @@ TORCH_LIBRARY_IMPL(b200, CUDA, m) {
   m.impl("scale_by_inv_norm", &scale_by_inv_norm);
   m.impl("axpy_bf16_to_f32", &axpy_bf16_to_f32);
   m.impl("comm_signal", &comm_signal);
+  m.impl("adam_shard", &adam_shard);
   m.impl("comm_wait", &comm_wait);
   m.impl("muon_rs_momentum", &muon_rs_momentum);
   m.impl("stack_scale_by_inv_norm", &stack_scale_by_inv_norm);

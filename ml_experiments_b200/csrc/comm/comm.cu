@@ -293,6 +293,132 @@ allreduce_multimem_kernel(void* mc, int world, int rank, long long lo, long long
   block_done_then_signal(counter, peer_flags, world, rank, channel + 1, epoch);
 }
 
+
+// ---------------------------------------------------------------------------------------------- sharded Adam
+// Reduce-scatter + Adam + all-gather in one kernel. Gradients and parameters live in symmetric buffers of the same
+// layout on every rank; this rank owns elements [lo, hi): it sums the peers' gradients for its slice by peer loads,
+// runs Adam on its fp32 moments (held only here), and stores the updated parameter into every rank's parameter buffer.
+// Afterwards it raises flag [channel + 1][rank] on every peer; a rank's parameters are complete when all `world`
+// flags of channel + 1 have reached `epoch`.
+template <typename T>
+struct Vec16 {};
+template <>
+struct Vec16<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void unpack(const uint4& r, float* f) {
+    const float4 v = *reinterpret_cast<const float4*>(&r);
+    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+  }
+  static __device__ __forceinline__ uint4 pack(const float* f) {
+    const float4 v = make_float4(f[0], f[1], f[2], f[3]);
+    return *reinterpret_cast<const uint4*>(&v);
+  }
+};
+template <>
+struct Vec16<bf16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void unpack(const uint4& r, float* f) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 x = __bfloat1622float2(h[k]);
+      f[2 * k] = x.x; f[2 * k + 1] = x.y;
+    }
+  }
+  static __device__ __forceinline__ uint4 pack(const float* f) {
+    uint4 o;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) h[k] = __floats2bfloat162_rn(f[2 * k], f[2 * k + 1]);
+    return o;
+  }
+};
+
+struct AdamHyper {
+  float lr, b1, b2, eps, wd, bias1, inv_sqrt_bias2;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+adam_shard_kernel(PeerPtrs grads, PeerPtrs params, int world, int rank, long long lo, long long hi,
+                  float* __restrict__ m, float* __restrict__ v, AdamHyper h, const int* flags, PeerPtrs peer_flags,
+                  int channel, int epoch, int* status, int* counter) {
+  if (status_poisoned(status)) return;
+  const bool ok = block_wait_flags(flags, world, channel, epoch, status);
+  constexpr int VEC = Vec16<T>::N;
+  const float inv_w = 1.f / world;
+  if (ok) {
+    constexpr int UNR = 2;
+    const long long stride = (long long)gridDim.x * blockDim.x * VEC;
+    for (long long i0 = lo + ((long long)blockIdx.x * blockDim.x + threadIdx.x) * VEC; i0 < hi; i0 += stride * UNR) {
+      float g[UNR][VEC];
+#pragma unroll
+      for (int u = 0; u < UNR; ++u)
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) g[u][k] = 0.f;
+      // the peers are walked starting after this rank, so that at any moment the ranks read from different peers
+      for (int r0 = 0; r0 < world; r0 += 4) {
+        uint4 raw[UNR][4];
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+          const long long i = i0 + u * stride;
+#pragma unroll
+          for (int r = 0; r < 4; ++r)
+            if (r0 + r < world && i < hi) {
+              const int src = (rank + 1 + r0 + r) % world;
+              raw[u][r] = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(grads.p[src]) + i));
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+          if (i0 + u * stride >= hi) continue;
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            if (r0 + r >= world) continue;
+            float f[VEC];
+            Vec16<T>::unpack(raw[u][r], f);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) g[u][k] += f[k];
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const long long i = i0 + u * stride;
+        if (i >= hi) continue;
+        float pf[VEC];
+        const uint4 praw = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(params.p[rank]) + i);
+        Vec16<T>::unpack(praw, pf);
+        float* mp = m + (i - lo);
+        float* vp = v + (i - lo);
+#pragma unroll
+        for (int q = 0; q < VEC / 4; ++q) {
+          float4 mm = *reinterpret_cast<float4*>(mp + 4 * q), vv = *reinterpret_cast<float4*>(vp + 4 * q);
+          float mf[4] = {mm.x, mm.y, mm.z, mm.w}, vf[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float gi = g[u][4 * q + k] * inv_w;
+            mf[k] = h.b1 * mf[k] + (1.f - h.b1) * gi;
+            vf[k] = h.b2 * vf[k] + (1.f - h.b2) * gi * gi;
+            float pi = pf[4 * q + k];
+            pi -= h.lr * h.wd * pi;
+            pi -= (h.lr / h.bias1) * mf[k] / (sqrtf(vf[k]) * h.inv_sqrt_bias2 + h.eps);
+            pf[4 * q + k] = pi;
+          }
+          *reinterpret_cast<float4*>(mp + 4 * q) = make_float4(mf[0], mf[1], mf[2], mf[3]);
+          *reinterpret_cast<float4*>(vp + 4 * q) = make_float4(vf[0], vf[1], vf[2], vf[3]);
+        }
+        const uint4 out = Vec16<T>::pack(pf);
+        for (int r = 0; r < world; ++r) {
+          const int dst = (rank + r) % world;
+          *reinterpret_cast<uint4*>(reinterpret_cast<T*>(params.p[dst]) + i) = out;
+        }
+      }
+    }
+  }
+  block_done_then_signal(counter, peer_flags, world, rank, channel + 1, epoch);
+}
+
 void check(const char* what) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
@@ -401,6 +527,27 @@ void allreduce_mean_multimem(void* mc, int world, int rank, long long n, int dty
   else
     allreduce_multimem_kernel<1><<<blocks, 256, 0, s>>>(mc, world, rank, lo, hi, flags, peer_flags, channel, epoch, status, ctr);
   check("allreduce_mean_multimem");
+}
+
+void adam_shard(const PeerPtrs& grads, const PeerPtrs& params, int world, int rank, long long lo, long long hi, int dtype,
+                float* m, float* v, float lr, float beta1, float beta2, float eps, float wd, float bias1, float bias2,
+                const int* flags, const PeerPtrs& peer_flags, int channel, int epoch, int* status, int max_blocks,
+                cudaStream_t s) {
+  const int vec = dtype == 0 ? 4 : 8;
+  if (lo % vec != 0 || hi % vec != 0 || hi < lo) throw std::runtime_error("adam_shard: the owned range must be aligned to 16-byte vectors");
+  int blocks = (int)(((hi - lo) / vec + 511) / 512);
+  const int cap = max_blocks > 0 ? max_blocks : 148 * 4;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  AdamHyper h{lr, beta1, beta2, eps, wd, bias1, 1.f / sqrtf(bias2)};
+  int* ctr = device_counter() + 3;
+  if (dtype == 0)
+    adam_shard_kernel<float><<<blocks, 256, 0, s>>>(grads, params, world, rank, lo, hi, m, v, h, flags, peer_flags, channel,
+                                                    epoch, status, ctr);
+  else
+    adam_shard_kernel<bf16><<<blocks, 256, 0, s>>>(grads, params, world, rank, lo, hi, m, v, h, flags, peer_flags, channel,
+                                                   epoch, status, ctr);
+  check("adam_shard");
 }
 
 }  // namespace b200

@@ -55,6 +55,18 @@ void allreduce_mean(const PeerPtrs& bufs, int world, int rank, long long n, int 
 void allreduce_mean_multimem(void* mc, int world, int rank, long long n, int dtype, const int* flags,
                              const PeerPtrs& peer_flags, int channel, int epoch, int* status, cudaStream_t s);
 
+// Sharded Adam fused with its collectives. `grads` / `params` are symmetric buffers (same layout on every rank, dtype 0 =
+// fp32, 1 = bf16, both of the same type); this rank owns elements [lo, hi) (multiples of the 16-byte vector) and keeps
+// the fp32 moments m, v of that slice only (indexed from lo). The kernel waits for `channel` (every rank's gradients are
+// in place), averages the slice over the ranks by peer loads, applies Adam (decoupled weight decay wd * lr) and stores
+// the new parameters into every rank's buffer, then signals `channel + 1`. Two launches that use the same channel
+// pair must be enqueued in the same order on every rank. `max_blocks` > 0 caps the grid (a small grid leaves SMs to a
+// concurrent compute stream; the copy is link-bound long before it needs the whole machine).
+void adam_shard(const PeerPtrs& grads, const PeerPtrs& params, int world, int rank, long long lo, long long hi, int dtype,
+                float* m, float* v, float lr, float beta1, float beta2, float eps, float wd, float bias1, float bias2,
+                const int* flags, const PeerPtrs& peer_flags, int channel, int epoch, int* status, int max_blocks,
+                cudaStream_t s);
+
 // Blocks the stream (bounded) until flags[channel][r] >= epoch for every r.
 void comm_wait(const int* flags, int world, int channel, int epoch, int* status, cudaStream_t s);
 

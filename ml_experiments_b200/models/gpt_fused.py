@@ -110,13 +110,32 @@ def _forward_backward(model, input_seq: Tensor, target_seq: Tensor, swb: int, ne
 
     # ------------------------------------------------------------------ backward
     grads: dict[int, Tensor] = {}
+    # Optional hand-over to a distributed optimizer: ``model._grad_out`` maps id(param) -> a preallocated gradient
+    # buffer (e.g. a view of a peer-mapped bucket) that the producing kernel writes directly; ``model._grad_hooks``
+    # maps id(param) -> callable(param, grad) invoked as soon as that gradient is complete (the head's is at the very
+    # start of backward, so its collective overlaps everything below). A buffer is only used while the parameter
+    # holds no gradient yet (with gradient accumulation the second micro-batch must not overwrite the first).
+    grad_out = getattr(model, "_grad_out", None) or {}
+    grad_hooks = getattr(model, "_grad_hooks", None) or {}
+
+    def out_buf(p):
+        return grad_out.get(id(p)) if p.grad is None else None
+
+    def new_grad(p):
+        # embedding gradients are accumulated by fp32 atomics whatever the table's dtype; the cast to the parameter's
+        # dtype at the end of the step lands in the hand-over buffer (see fused_gpt_step)
+        return torch.zeros(p.shape, dtype=torch.float32, device=dev)
 
     def put(p, g):
         grads[id(p)] = g if id(p) not in grads else grads[id(p)] + g
+        hook = grad_hooks.get(id(p))
+        if hook is not None:
+            hook(p, grads[id(p)])
 
     if head.use_fp8:
         dxf = G.gemm(gl, w8, b_mn=True, alpha=1.0 / (grad_s * head.w_s))
-        put(head.weight, G.gemm(gl, x8, a_mn=True, b_mn=True, out_dtype=torch.float32, alpha=1.0 / (grad_s * head.x_s)))
+        put(head.weight, G.gemm(gl, x8, a_mn=True, b_mn=True, out=out_buf(head.weight), out_dtype=torch.float32,
+                                alpha=1.0 / (grad_s * head.x_s)))
     else:
         dxf = G.gemm(gl, w16(head.weight), b_mn=True)
         put(head.weight, _wgrad(gl, xf, head.weight.shape))
@@ -163,7 +182,7 @@ def _forward_backward(model, input_seq: Tensor, target_seq: Tensor, swb: int, ne
                 # summed inside one scatter; what is still waiting at the end is flushed below
                 if vi in dve_wait:
                     if ve_grads[vi] is None:
-                        ve_grads[vi] = torch.zeros(model.value_embeds.embed[vi].weight.shape, dtype=torch.float32, device=dev)
+                        ve_grads[vi] = new_grad(model.value_embeds.embed[vi].weight)
                     o.embed_scatter_add(idx, dve, ve_grads[vi], dve_wait.pop(vi))
                 else:
                     dve_wait[vi] = dve
@@ -192,12 +211,12 @@ def _forward_backward(model, input_seq: Tensor, target_seq: Tensor, swb: int, ne
     dx0_total = (dx0_acc + dx.float()).to(torch.bfloat16)
     e_raw = Fz.embed_gather(idx, model.embed.weight)
     d_e = Fz.norm_bwd_add(dx0_total, e_raw, None, EPS)
-    g_embed = torch.zeros(model.embed.weight.shape, dtype=torch.float32, device=dev)
+    g_embed = new_grad(model.embed.weight)
     o.embed_scatter_add(idx, d_e, g_embed)
     put(model.embed.weight, g_embed)
     for vi, dve in dve_wait.items():
         if ve_grads[vi] is None:
-            ve_grads[vi] = torch.zeros(model.value_embeds.embed[vi].weight.shape, dtype=torch.float32, device=dev)
+            ve_grads[vi] = new_grad(model.value_embeds.embed[vi].weight)
         o.embed_scatter_add(idx, dve, ve_grads[vi])
     for vi, e in enumerate(model.value_embeds.embed):
         if ve_grads[vi] is not None:
@@ -247,6 +266,7 @@ def fused_gpt_step(model, input_seq: Tensor, target_seq: Tensor, swb: int) -> Te
     gradient is already there): what ``fused_gpt_loss(...).backward()`` produces, without the autograd node and its
     multiply of every gradient by the incoming loss gradient (which is 1 for a plain ``backward()``)."""
     loss, grads = _forward_backward(model, input_seq, target_seq, swb, True)
+    grad_out = getattr(model, "_grad_out", None) or {}
     for p in model.parameters():
         if not p.requires_grad:
             continue
@@ -254,7 +274,11 @@ def fused_gpt_step(model, input_seq: Tensor, target_seq: Tensor, swb: int) -> Te
         if g is None:
             continue
         g = g.view(p.shape)
-        if g.dtype != p.dtype:
+        buf = grad_out.get(id(p)) if p.grad is None else None
+        if buf is not None and buf.data_ptr() != g.data_ptr():
+            buf.copy_(g)                      # cast (if any) and hand-over in one pass
+            g = buf
+        elif g.dtype != p.dtype:
             g = g.to(p.dtype)
         if p.grad is None:
             p.grad = g

@@ -17,7 +17,7 @@ import torch
 import torch.distributed as dist
 
 MAX_WORLD = 16
-NUM_CHANNELS = 8
+NUM_CHANNELS = 16
 
 
 @dataclass

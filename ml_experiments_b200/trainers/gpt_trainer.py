@@ -48,6 +48,13 @@ def window_blocks(step: int, hp: Hyperparameters) -> int:
     return next_multiple_of_n(1728 * step / hp.num_iterations, n=128) // 128
 
 
+class _NoSync:
+    """Stands in for a gradient synchroniser when every parameter's averaging is fused into its optimizer kernel."""
+
+    def sync_non_muon_grads(self):
+        pass
+
+
 class GPTTrainer:
     """Owns model, optimizers and (optionally) the process group; ``train_step`` runs one optimizer step."""
 
@@ -68,7 +75,9 @@ class GPTTrainer:
         hp_ = self.hp
         adam_groups = [dict(params=head, lr=hp_.head_lr), dict(params=embed, lr=hp_.embed_lr),
                        dict(params=scalar, lr=hp_.scalar_lr)]
-        self.optimizer1 = FusedAdam(adam_groups, betas=(0.8, 0.95), eps=1e-10)
+        self.optimizer1 = None
+        self.sharded_adam = False
+        self._adam_stream = None
         self.grad_sync = grad_sync
         self.comm = None
         self.comm_mode = "single"
@@ -96,8 +105,21 @@ class GPTTrainer:
                     from ..parallel.symm import SymmWorld
 
                     sw = SymmWorld.create(rank, world_size, self.device)
-                    self.comm = md.FusedGradSync(model, hidden, sw)
                     self.optimizer2 = md.FusedDistMuon(hidden, sw, lr=hp_.muon_lr, momentum=hp_.muon_momentum)
+                    if os.environ.get("B200_SHARDED_ADAM", "1") == "1":
+                        # Adam state sharded over the ranks; reduce-scatter, update and all-gather are one kernel per
+                        # table, the head's launched from backward as soon as its gradient exists
+                        from ..parallel.adam_dist import ShardedAdam
+
+                        self.optimizer1 = ShardedAdam(adam_groups, sw, betas=(0.8, 0.95), eps=1e-10,
+                                                      max_blocks=int(os.environ.get("B200_ADAM_BLOCKS", "96")))
+                        self.sharded_adam = True
+                        model._grad_out = self.optimizer1.grad_views
+                        self._head_seg = self.optimizer1.segment_of(model.lm_head.weight)
+                        self._adam_stream = torch.cuda.Stream(self.device)
+                        self.comm = _NoSync()
+                    else:
+                        self.comm = md.FusedGradSync(model, hidden, sw)
                     self.comm_mode = "fused-p2p"
                 except Exception as e:  # symmetric memory unavailable: NCCL plumbing with the same work split
                     if grad_sync == "fused":
@@ -111,6 +133,8 @@ class GPTTrainer:
                 self.comm_mode = "nccl"
         else:
             self.optimizer2 = Muon(hidden, lr=hp_.muon_lr, momentum=hp_.muon_momentum, rank=rank, world_size=world_size)
+        if self.optimizer1 is None:
+            self.optimizer1 = FusedAdam(adam_groups, betas=(0.8, 0.95), eps=1e-10)
         self.optimizers = [self.optimizer1, self.optimizer2]
         # B200_OVERLAP_SYNC=1 runs the bucket all-reduce on a side stream beside the Muon step (measured: no gain at 2 or 8 GPUs)
         # (only beside the fused Muon step: Dion's own all-reduces share the bucket all-reduce's flag channel and counter)
@@ -142,6 +166,16 @@ class GPTTrainer:
         hp = self.hp
         w = window_blocks(self.step, hp) if window is None else window
         micro = list(zip(inputs, targets)) if isinstance(inputs, (list, tuple)) else [(inputs, targets)]
+        # hyper-parameters of this step first: with the sharded Adam the head's update is launched from inside backward
+        frac = min(self.step / hp.muon_momentum_warmup_steps, 1)
+        for g in self.optimizer2.param_groups:
+            g["momentum"] = (1 - frac) * 0.85 + frac * 0.95
+        lr_mul = get_lr(min(self.step, hp.num_iterations), hp)
+        for opt in self.optimizers:
+            for g in opt.param_groups:
+                g["lr"] = g["initial_lr"] * lr_mul
+        if self.sharded_adam and len(micro) == 1:
+            self.model._grad_hooks = {id(self.model.lm_head.weight): self._head_grad_ready}
         loss = None
         for x, y in micro:
             if x.device != self.device:
@@ -151,17 +185,25 @@ class GPTTrainer:
                 y = y.to(torch.int64)
             l = self.model.loss_and_grad(x, y, w)
             loss = l if loss is None else loss + l
+        self.model._grad_hooks = None
         if len(micro) > 1:
             loss = loss / len(micro)
             torch._foreach_mul_([p.grad for p in self.model.parameters() if p.grad is not None], 1.0 / len(micro))
-        frac = min(self.step / hp.muon_momentum_warmup_steps, 1)
-        for g in self.optimizer2.param_groups:
-            g["momentum"] = (1 - frac) * 0.85 + frac * 0.95
-        lr_mul = get_lr(min(self.step, hp.num_iterations), hp)
-        for opt in self.optimizers:
-            for g in opt.param_groups:
-                g["lr"] = g["initial_lr"] * lr_mul
-        if self.overlap_sync:
+        if self.sharded_adam:
+            # the remaining tables (embeddings, scalars) go out on the side stream beside the Muon step: link-bound
+            # copies with a capped grid next to the GEMM-bound Newton-Schulz iterations
+            cur = torch.cuda.current_stream(self.device)
+            ready = torch.cuda.Event()
+            ready.record(cur)
+            with torch.cuda.stream(self._adam_stream):
+                self._adam_stream.wait_event(ready)
+                for i in range(len(self.optimizer1.segments)):
+                    if i not in self.optimizer1._launched:
+                        self.optimizer1.launch(i)
+            self.optimizer2.step()
+            cur.wait_stream(self._adam_stream)
+            self.optimizer1.finish()
+        elif self.overlap_sync:
             # the all-reduce of the embedding / head gradients (link-bound) runs beside the Muon step (GEMM-bound)
             self.comm.start_async()
             self.optimizer2.step()
@@ -174,6 +216,20 @@ class GPTTrainer:
         self.model.zero_grad(set_to_none=True)
         self.step += 1
         return loss
+
+    def _head_grad_ready(self, p, g):
+        """Called from backward when the head's weight gradient is complete: its fused reduce-scatter + Adam +
+        all-gather starts on the side stream right away and runs under the rest of backward."""
+        opt = self.optimizer1
+        view = opt.grad_views[id(p)]
+        if g.data_ptr() != view.data_ptr():
+            view.copy_(g.view_as(view))
+        cur = torch.cuda.current_stream(self.device)
+        ready = torch.cuda.Event()
+        ready.record(cur)
+        with torch.cuda.stream(self._adam_stream):
+            self._adam_stream.wait_event(ready)
+            opt.launch(self._head_seg, early=True)
 
     @torch.no_grad()
     def eval_loss(self, inputs: torch.Tensor, targets: torch.Tensor, window: int) -> torch.Tensor:
@@ -207,11 +263,13 @@ class GPTTrainer:
         writes ``path.rank{r}`` with its slice of the Muon momentum (which lives outside ``Optimizer.state``)."""
         from ..utils.checkpoint import save_sharded
 
-        opt2 = self.optimizer2
-        shard = opt2.sharded_state() if hasattr(opt2, "sharded_state") else {}
-        rows = opt2.sharded_rows() if hasattr(opt2, "sharded_rows") else {}
+        shard, rows = {}, {}
+        for opt in self.optimizers:
+            if hasattr(opt, "sharded_state"):
+                shard.update(opt.sharded_state())
+                rows.update(opt.sharded_rows())
         sd = self.state_dict()
-        if shard:
+        if any(k.startswith("mom_") for k in shard):
             # the momentum is saved through the shards; drop per-parameter views of the same buffers
             sd["optimizers"][1] = dict(sd["optimizers"][1], state={})
         save_sharded(sd, {k: v.cpu() for k, v in shard.items()}, path, self.rank, self.world_size, rows)
@@ -222,8 +280,10 @@ class GPTTrainer:
 
         rep, shard = load_sharded(path, self.rank, self.world_size)
         self.load_state_dict(rep)
-        if shard and hasattr(self.optimizer2, "load_sharded_state"):
-            self.optimizer2.load_sharded_state({k: v.to(self.device) for k, v in shard.items()})
+        shard = {k: v.to(self.device) for k, v in shard.items()}
+        for opt in self.optimizers:
+            if shard and hasattr(opt, "load_sharded_state"):
+                opt.load_sharded_state(shard)
 
 
 def synthetic_batch(seq_len: int, vocab: int = 50257, doc_len: int = 1024, seed: int = 0, pin: bool = True):

@@ -29,8 +29,12 @@ def _cfg():
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--mode", choices=["fused", "nccl"], default="fused")
+    ap.add_argument("--mode", choices=["fused", "fused_allreduce", "nccl"], default="fused",
+                    help="fused: peer-memory Muon + sharded Adam kernels; fused_allreduce: peer-memory Muon, bucket all-reduce + "
+                         "replicated Adam; nccl: NCCL collectives")
     a = ap.parse_args()
+    if a.mode == "fused_allreduce":
+        os.environ["B200_SHARDED_ADAM"] = "0"
     from ml_experiments_b200.ops.runtime import check_status
     from ml_experiments_b200.trainers.gpt_trainer import GPTTrainer, Hyperparameters, init_distributed, synthetic_batch
 
@@ -41,8 +45,9 @@ def main():
     # the model starts with a zero head and zero output projections: the first step moves only the head, the later ones
     # every parameter group
     tr = GPTTrainer(_cfg(), Hyperparameters(seq_len=T), device=dev, rank=rank, world_size=world, seed=0,
-                    grad_sync="fused" if a.mode == "fused" else "nccl")
-    assert tr.comm_mode == ("fused-p2p" if a.mode == "fused" else "nccl"), tr.comm_mode
+                    grad_sync="nccl" if a.mode == "nccl" else "fused")
+    assert tr.comm_mode == ("nccl" if a.mode == "nccl" else "fused-p2p"), tr.comm_mode
+    assert tr.sharded_adam == (a.mode == "fused")
     x, y = batches[rank]
     losses = [float(tr.train_step(x.to(dev), y.to(dev), window=2)) for _ in range(STEPS)]
     check_status()
