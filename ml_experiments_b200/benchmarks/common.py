@@ -42,3 +42,18 @@ def timed_steps(step_fn, steps: int, warmup: int, world: int, device) -> float:
 def emit(rank: int, **kw):
     if rank == 0:
         print(json.dumps(kw), flush=True)
+
+
+def reference_root() -> str | None:
+    """Folder that holds a plain copy of the reference's packages (``heuristic_secrets``, ``zoology``), or None."""
+    here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    for c in (os.path.join(here, "baseline", "_ref"), os.environ.get("ML_EXPERIMENTS_REFERENCE_SRC", "")):
+        if c and os.path.isdir(os.path.join(c, "heuristic_secrets")):
+            return c
+    return None
+
+
+def unavailable(rank: int, why: Exception | str) -> None:
+    """The one line a reference arm prints when the reference's code cannot run on this box."""
+    msg = why if isinstance(why, str) else " ".join(f"{type(why).__name__}: {why}".split())
+    emit(rank, impl="reference", unavailable=msg[:400])

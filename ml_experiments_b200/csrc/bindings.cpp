@@ -358,11 +358,11 @@ void stack_scale_by_inv_norm(Tensor x, const Tensor& sumsq, int64_t nmat, int64_
 }
 
 void ag_push(const Tensor& src, at::IntArrayRef u_full_ptrs, int64_t rank, int64_t dst_off, at::IntArrayRef peer_flags,
-             int64_t channel, int64_t epoch) {
+             int64_t channel, int64_t epoch, int64_t slot) {
   const c10::cuda::CUDAGuard guard(src.device());
   chk_bf16c(src, "src");
   b200::ag_push(src.data_ptr(), to_peers(u_full_ptrs), (int)u_full_ptrs.size(), (int)rank, dst_off, src.numel(),
-                to_peers(peer_flags), (int)channel, (int)epoch, cur_stream());
+                to_peers(peer_flags), (int)channel, (int)epoch, (int)slot, cur_stream());
 }
 
 void ag_wait_apply(Tensor p, const Tensor& u, const c10::optional<Tensor>& p_bf16, double alpha, int64_t world,
@@ -698,7 +698,7 @@ TORCH_LIBRARY(b200, m) {
   m.def("comm_wait(Tensor flags, int world, int channel, int epoch, Tensor(a!) status) -> ()");
   m.def("muon_rs_momentum(int[] grad_ptrs, int elem_off, int nmat, int mat_elems, Tensor(a!) mom, Tensor(b!) u_out, Tensor(c!) sumsq, float mu, bool nesterov, Tensor flags, int channel, int epoch, Tensor(d!) status) -> ()");
   m.def("stack_scale_by_inv_norm(Tensor(a!) x, Tensor sumsq, int nmat, int mat_elems, float eps) -> ()");
-  m.def("ag_push(Tensor src, int[] u_full_ptrs, int rank, int dst_off, int[] peer_flags, int channel, int epoch) -> ()");
+  m.def("ag_push(Tensor src, int[] u_full_ptrs, int rank, int dst_off, int[] peer_flags, int channel, int epoch, int slot=0) -> ()");
   m.def("ag_wait_apply(Tensor(a!) p, Tensor u, Tensor(b!)? p_bf16, float alpha, int world, Tensor flags, int channel, int epoch, Tensor(c!) status) -> ()");
   m.def("allreduce_mean_multimem(int mc_ptr, int world, int rank, int n, int dtype, Tensor flags, int[] peer_flags, int channel, int epoch, Tensor(a!) status) -> ()");
   m.def("allreduce_mean(int[] buf_ptrs, int rank, int n, int dtype, Tensor flags, int[] peer_flags, int channel, int epoch, Tensor(a!) status) -> ()");

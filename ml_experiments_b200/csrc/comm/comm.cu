@@ -473,13 +473,15 @@ void stack_scale_by_inv_norm(void* x_bf16, const float* sumsq, int nmat, long lo
 }
 
 void ag_push(const void* src_bf16, const PeerPtrs& u_full, int world, int rank, long long dst_off, long long n,
-             const PeerPtrs& peer_flags, int channel, int epoch, cudaStream_t s) {
+             const PeerPtrs& peer_flags, int channel, int epoch, int slot, cudaStream_t s) {
+  if (slot < 0 || slot >= 16) throw std::runtime_error("ag_push: slot must be in 0..15");
   if (n % 8 != 0 || dst_off % 8 != 0) throw std::runtime_error("ag_push: sizes must be multiples of 8");
   int blocks = (int)((n / 8 + 255) / 256);
   if (blocks > 148 * 4) blocks = 148 * 4;
   if (blocks < 1) blocks = 1;
+  // pushes that may run at the same time (different streams) count their finished blocks in different slots
   ag_push_kernel<<<blocks, 256, 0, s>>>((const bf16*)src_bf16, u_full, world, rank, dst_off, n, peer_flags, channel, epoch,
-                                        device_counter());
+                                        slot == 0 ? device_counter() : device_counter() + 16 + slot);
   check("ag_push");
 }
 

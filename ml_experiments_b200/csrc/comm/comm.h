@@ -36,8 +36,9 @@ void stack_scale_by_inv_norm(void* x_bf16, const float* sumsq, int nmat, long lo
 
 // All-gather by peer stores: copies this rank's `n` bf16 elements to element offset `dst_off` of every rank's
 // `u_full` buffer (16-byte vector stores), then signals flags[channel][rank] = epoch on every peer.
+// `slot` (0..15) selects the completion counter: launches that can overlap on the device must use different slots.
 void ag_push(const void* src_bf16, const PeerPtrs& u_full, int world, int rank, long long dst_off, long long n,
-             const PeerPtrs& peer_flags, int channel, int epoch, cudaStream_t s);
+             const PeerPtrs& peer_flags, int channel, int epoch, int slot, cudaStream_t s);
 
 // Waits for every rank's ag_push of `epoch`, then applies p += alpha * u (fp32 master) and refreshes the bf16 copy.
 void ag_wait_apply(float* p, const void* u_bf16, void* p_bf16, long long n, float alpha, int world, const int* flags,

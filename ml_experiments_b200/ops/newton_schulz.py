@@ -67,3 +67,44 @@ def newton_schulz_(X: torch.Tensor, coeffs=NS5_COEFFS, work: dict | None = None)
         X, X2 = X2, X
     work[key] = (A, Bm, X2)
     return X
+
+
+class GraphedNewtonSchulz:
+    """The Newton-Schulz iteration of one stack captured once as a CUDA graph and replayed every step.
+
+    One orthogonalisation is 15 dependent GEMM launches on small matrices; issued one by one, the host cost of each
+    launch (argument checks, tensor-map encoding, the launch itself) is of the order of the kernel's run time. The
+    stack ``X`` is a persistent buffer (the optimizer writes the normalised update into it every step), the work
+    buffers and coefficients never change, so the whole chain is static: it is captured after one eager warm-up on
+    placeholder data and replayed with a single graph launch on whatever stream is current. Independent stacks
+    replayed on different streams run side by side, which matters because a single small GEMM does not fill 148 SMs.
+
+    ``X`` is overwritten by the iteration (ping-pong with a work buffer); the result is :attr:`out`.
+    """
+
+    def __init__(self, X: torch.Tensor, coeffs=NS5_COEFFS):
+        from . import runtime
+
+        assert X.is_cuda and X.dtype == torch.bfloat16 and X.dim() == 3 and X.is_contiguous()
+        self.X, self.coeffs = X, [tuple(c) for c in coeffs]
+        self._work: dict = {}
+        keep = X.clone()
+        side = torch.cuda.Stream(X.device)
+        side.wait_stream(torch.cuda.current_stream(X.device))
+        with torch.cuda.stream(side):
+            X.normal_(0, 1.0 / max(X.shape[-1], X.shape[-2]) ** 0.5)          # placeholder with a sane spectrum
+            newton_schulz_(X, self.coeffs, self._work)                        # eager warm-up: kernels get configured
+            n0 = runtime.launch_count()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=side, capture_error_mode="thread_local"):
+                self.out = newton_schulz_(X, self.coeffs, self._work)
+            self.launches = runtime.launch_count() - n0
+            X.copy_(keep)
+        torch.cuda.current_stream(X.device).wait_stream(side)
+
+    def __call__(self) -> torch.Tensor:
+        from . import runtime
+
+        self.graph.replay()
+        runtime.add_launches(self.launches)
+        return self.out

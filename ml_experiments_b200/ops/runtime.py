@@ -64,6 +64,12 @@ def reset_launch_count() -> None:
     _launches = 0
 
 
+def add_launches(n: int) -> None:
+    """Accounts for kernels of this package that run without passing through :func:`ops` (CUDA-graph replays)."""
+    global _launches
+    _launches += n
+
+
 STATUS_WORDS = 4   # [0] error code, [1] peer-wait limit in microseconds (0 = the kernels' default of 5 s), [2:] spare
 
 

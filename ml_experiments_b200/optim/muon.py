@@ -13,7 +13,9 @@ from collections import defaultdict
 
 import torch
 
-from ..ops.newton_schulz import NS5_COEFFS, newton_schulz_, newton_schulz_torch
+import os
+
+from ..ops.newton_schulz import NS5_COEFFS, GraphedNewtonSchulz, newton_schulz_, newton_schulz_torch
 from ..ops.runtime import ops
 from ..utils.shadow import get_shadow_buffer, mark_modified, set_shadow
 
@@ -29,6 +31,7 @@ class Muon(torch.optim.Optimizer):
         self._work: dict = {}
         self._stacks: dict = {}
         self._pending_shard = None
+        self._streams: list = []
 
     # ------------------------------------------------------------------------------------------ torch path
     @torch.no_grad()
@@ -85,39 +88,65 @@ class Muon(torch.optim.Optimizer):
         mu, nesterov, lr = float(group["momentum"]), bool(group["nesterov"]), float(group["lr"])
         coeffs = [NS5_COEFFS[0]] * group["ns_steps"]
         params = [p for p in group["params"] if p.grad is not None]
-        for ent in self._slots(params):
-            r, c, plist = ent["r"], ent["c"], ent["plist"]
-            for (p, _), mv in zip(plist, ent["mviews"]):
-                st = self.state[p]
-                cur = st.get("momentum_buffer")
-                if cur is None or cur.data_ptr() != mv.data_ptr():
-                    if cur is not None:            # a buffer restored from a checkpoint: move it into the stack
-                        mv.copy_(cur.view(mv.shape))
-                    st["momentum_buffer"] = mv
-            if self._pending_shard is not None:
-                t = self._pending_shard.get(f"mom_{r}x{c}")
-                if t is not None:
-                    ent["mom"].copy_(t[: ent["total"]])
-            torch._foreach_copy_(ent["gviews"], [p.grad for p, _ in plist])
-            ent["sumsq"].zero_()
-            o.muon_momentum(ent["grads"], ent["mom"], ent["stack"], ent["sumsq"], mu, nesterov, 1.0)
-            o.stack_scale_by_inv_norm(ent["stack"], ent["sumsq"], ent["total"], r * c, 1e-7)
-            u = newton_schulz_(ent["stack"], coeffs, self._work)
-            alpha = -lr * max(1.0, r / c) ** 0.5
-            slot = 0
-            for p, nmat in plist:
-                upd = u[slot:slot + nmat].view(p.shape)
-                if p.dtype == torch.float32:
-                    sh = get_shadow_buffer(p, torch.bfloat16)
-                    if sh is None:
-                        sh = torch.empty(p.shape, dtype=torch.bfloat16, device=p.device)
-                    o.axpy_bf16_to_f32(p, upd, sh, alpha)
-                    mark_modified(p)
-                    set_shadow(p, sh)
-                else:
-                    p.add_(upd.to(p.dtype), alpha=alpha)
-                slot += nmat
+        ents = self._slots(params)
+        # every shape stack is an independent chain: on its own stream, with its 15 GEMMs replayed as one CUDA graph,
+        # the small Newton-Schulz products of different shapes share the machine instead of running one after another
+        use_graph = os.environ.get("B200_NS_GRAPH", "1") == "1"
+        cur = torch.cuda.current_stream()
+        side = len(ents) > 1 and os.environ.get("B200_MUON_STREAMS", "1") == "1"
+        if side and len(self._streams) < len(ents):
+            self._streams = [torch.cuda.Stream() for _ in ents]
+        fork = torch.cuda.Event()
+        fork.record(cur)
+        for ei, ent in enumerate(ents):
+            st = self._streams[ei] if side else cur
+            with torch.cuda.stream(st):
+                if side:
+                    st.wait_event(fork)
+                self._step_stack(ent, o, mu, nesterov, lr, coeffs, use_graph)
+        if side:
+            for st in self._streams[: len(ents)]:
+                cur.wait_stream(st)
         self._pending_shard = None
+
+    def _step_stack(self, ent, o, mu, nesterov, lr, coeffs, use_graph):
+        r, c, plist = ent["r"], ent["c"], ent["plist"]
+        for (p, _), mv in zip(plist, ent["mviews"]):
+            st = self.state[p]
+            cur = st.get("momentum_buffer")
+            if cur is None or cur.data_ptr() != mv.data_ptr():
+                if cur is not None:            # a buffer restored from a checkpoint: move it into the stack
+                    mv.copy_(cur.view(mv.shape))
+                st["momentum_buffer"] = mv
+        if self._pending_shard is not None:
+            t = self._pending_shard.get(f"mom_{r}x{c}")
+            if t is not None:
+                ent["mom"].copy_(t[: ent["total"]])
+        torch._foreach_copy_(ent["gviews"], [p.grad for p, _ in plist])
+        ent["sumsq"].zero_()
+        o.muon_momentum(ent["grads"], ent["mom"], ent["stack"], ent["sumsq"], mu, nesterov, 1.0)
+        o.stack_scale_by_inv_norm(ent["stack"], ent["sumsq"], ent["total"], r * c, 1e-7)
+        key = tuple(coeffs)
+        if use_graph:
+            if ent.get("ns_key") != key:
+                ent["ns"], ent["ns_key"] = GraphedNewtonSchulz(ent["stack"], coeffs), key
+            u = ent["ns"]()
+        else:
+            u = newton_schulz_(ent["stack"], coeffs, self._work)
+        alpha = -lr * max(1.0, r / c) ** 0.5
+        slot = 0
+        for p, nmat in plist:
+            upd = u[slot:slot + nmat].view(p.shape)
+            if p.dtype == torch.float32:
+                sh = get_shadow_buffer(p, torch.bfloat16)
+                if sh is None:
+                    sh = torch.empty(p.shape, dtype=torch.bfloat16, device=p.device)
+                o.axpy_bf16_to_f32(p, upd, sh, alpha)
+                mark_modified(p)
+                set_shadow(p, sh)
+            else:
+                p.add_(upd.to(p.dtype), alpha=alpha)
+            slot += nmat
 
     # -- the same checkpoint interface as the distributed forms (parallel/muon_dist.py): per-shape momentum stacks
     def sharded_state(self) -> dict:

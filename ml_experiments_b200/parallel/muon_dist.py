@@ -22,7 +22,9 @@ from collections import defaultdict
 import torch
 import torch.distributed as dist
 
-from ..ops.newton_schulz import NS5_COEFFS, newton_schulz_
+import os
+
+from ..ops.newton_schulz import NS5_COEFFS, GraphedNewtonSchulz, newton_schulz_
 from ..ops.runtime import ops
 from ..utils.shadow import get_shadow_buffer, mark_modified, set_shadow
 
@@ -210,6 +212,7 @@ class DistMuon(torch.optim.Optimizer):
 # Fused path: the same work split, with both collectives done by this package's kernels over peer memory
 # ======================================================================================================================
 CH_GRADS, CH_AG, CH_B16_IN, CH_B16_OUT, CH_F32_IN, CH_F32_OUT = 0, 1, 2, 3, 4, 5
+CH_AG_GROUP0, MAX_CONCURRENT_GROUPS = 12, 4     # one "pushed" channel per shape group when the groups run concurrently
 
 
 class MuonShardEngine:
@@ -265,6 +268,8 @@ class MuonShardEngine:
             self.groups.append(g)
         self._work: dict = {}
         self._step = 0
+        self._streams = None
+        self._concurrent = False
 
     @torch.no_grad()
     def publish_grads(self):
@@ -287,18 +292,49 @@ class MuonShardEngine:
 
     @torch.no_grad()
     def reduce_ns_push(self, mu: float, nesterov: bool, coeffs):
+        """Every shape group is an independent chain (reduce-scatter + momentum -> normalise -> Newton-Schulz -> push)
+        and runs on its own stream, so that the link-bound collectives of one group overlap the GEMMs of another and
+        small GEMMs of different groups share the machine. The 15 GEMMs of a group are one CUDA-graph launch
+        (``B200_NS_GRAPH=0`` issues them one by one)."""
         o = ops()
         w = self.w
         ng = len(self.groups)
+        use_graph = os.environ.get("B200_NS_GRAPH", "1") == "1"
+        # concurrent groups need a flag channel each: a group that finishes early must not satisfy (or later undo) the
+        # wait for another group's push
+        concurrent = 1 < ng <= MAX_CONCURRENT_GROUPS and os.environ.get("B200_MUON_STREAMS", "1") == "1"
+        self._concurrent = concurrent
+        cur = torch.cuda.current_stream()
+        if self._streams is None:
+            self._streams = [torch.cuda.Stream() for _ in self.groups]
+        fork = torch.cuda.Event()
+        fork.record(cur)
         for gi, g in enumerate(self.groups):
-            per, mat = g["per"], g["mat"]
-            g["sumsq"].zero_()
-            o.muon_rs_momentum(g["g_full"].ptrs, w.rank * per * mat, per, mat, g["mom"], g["u_shard"], g["sumsq"], mu,
-                               nesterov, w.flags.local, CH_GRADS, self._step, self._status)
-            o.stack_scale_by_inv_norm(g["u_shard"], g["sumsq"], per, mat, 1e-7)
-            u = newton_schulz_(g["u_shard"], coeffs, self._work)
-            o.ag_push(u.contiguous(), g["u_full"].ptrs, w.rank, w.rank * per * mat, w.flags.ptrs, CH_AG,
-                      (self._step - 1) * ng + gi + 1)
+            st = self._streams[gi] if concurrent else cur
+            with torch.cuda.stream(st):
+                if st is not cur:
+                    st.wait_event(fork)
+                per, mat = g["per"], g["mat"]
+                g["sumsq"].zero_()
+                o.muon_rs_momentum(g["g_full"].ptrs, w.rank * per * mat, per, mat, g["mom"], g["u_shard"], g["sumsq"], mu,
+                                   nesterov, w.flags.local, CH_GRADS, self._step, self._status)
+                o.stack_scale_by_inv_norm(g["u_shard"], g["sumsq"], per, mat, 1e-7)
+                key = tuple(tuple(c) for c in coeffs)
+                if use_graph:
+                    if g.get("ns_key") != key:
+                        g["ns"], g["ns_key"] = GraphedNewtonSchulz(g["u_shard"], coeffs), key
+                    u = g["ns"]()
+                else:
+                    u = newton_schulz_(g["u_shard"], coeffs, self._work)
+                if concurrent:
+                    o.ag_push(u.contiguous(), g["u_full"].ptrs, w.rank, w.rank * per * mat, w.flags.ptrs, CH_AG_GROUP0 + gi,
+                              self._step, gi + 1)
+                else:
+                    o.ag_push(u.contiguous(), g["u_full"].ptrs, w.rank, w.rank * per * mat, w.flags.ptrs, CH_AG,
+                              (self._step - 1) * ng + gi + 1, 0)
+        if concurrent:
+            for st in self._streams:
+                cur.wait_stream(st)
 
     @torch.no_grad()
     def apply(self, lr: float):
@@ -307,8 +343,8 @@ class MuonShardEngine:
         ng = len(self.groups)
         for gi, g in enumerate(self.groups):
             alpha = -lr * max(1.0, g["r"] / g["c"]) ** 0.5
-            o.ag_wait_apply(g["p_stack"], g["u_full"].local, g["sh_stack"], alpha, w.world, w.flags.local, CH_AG,
-                            (self._step - 1) * ng + gi + 1, self._status)
+            ch, ep = (CH_AG_GROUP0 + gi, self._step) if self._concurrent else (CH_AG, (self._step - 1) * ng + gi + 1)
+            o.ag_wait_apply(g["p_stack"], g["u_full"].local, g["sh_stack"], alpha, w.world, w.flags.local, ch, ep, self._status)
             slot = 0
             for p, nmat in g["plist"]:
                 mark_modified(p)
