@@ -306,6 +306,46 @@ void axpy_bf16_to_f32(Tensor p, const Tensor& u, const c10::optional<Tensor>& p_
 }
 
 
+void normuon_scales(const Tensor& v, Tensor stat, Tensor second, bool red_cols, double beta2) {
+  const c10::cuda::CUDAGuard guard(v.device());
+  TORCH_CHECK(v.dim() == 3 && v.is_contiguous(), "normuon_scales: v [nmat, R, C] contiguous");
+  const bool vb = v.scalar_type() == at::kBFloat16;
+  TORCH_CHECK(vb || v.scalar_type() == at::kFloat, "normuon_scales: v bf16 or fp32");
+  const int64_t nmat = v.size(0), R = v.size(1), C = v.size(2), ns = red_cols ? R : C;
+  TORCH_CHECK(stat.scalar_type() == at::kFloat && second.scalar_type() == at::kFloat && stat.is_contiguous() &&
+              second.is_contiguous() && stat.numel() == nmat * ns && second.numel() == nmat * ns,
+              "normuon_scales: stat / second fp32 with one entry per row (red_cols) or column");
+  b200::normuon_scales(v.data_ptr(), vb, stat.data_ptr<float>(), second.data_ptr<float>(), (int)nmat, (int)R, (int)C, red_cols,
+                       (float)beta2, cur_stream());
+}
+
+void normuon_update(Tensor p, const c10::optional<Tensor>& mant, const Tensor& v, const c10::optional<Tensor>& scale,
+                    bool scale_per_row, double lr, double wd_lr, const c10::optional<Tensor>& lr_mat,
+                    const c10::optional<Tensor>& wd_mat) {
+  const c10::cuda::CUDAGuard guard(p.device());
+  TORCH_CHECK(v.dim() == 3 && v.is_contiguous() && p.is_contiguous() && p.numel() == v.numel(), "normuon_update: p, v [nmat, R, C]");
+  const bool pb = p.scalar_type() == at::kBFloat16, vb = v.scalar_type() == at::kBFloat16;
+  TORCH_CHECK((pb || p.scalar_type() == at::kFloat) && (vb || v.scalar_type() == at::kFloat), "normuon_update: bf16 or fp32");
+  unsigned short* mp = nullptr;
+  if (mant.has_value()) {
+    TORCH_CHECK(pb && mant->is_contiguous() && mant->numel() == p.numel() && mant->element_size() == 2, "normuon_update: mantissa is a 16-bit buffer of a bf16 p");
+    mp = reinterpret_cast<unsigned short*>(mant->data_ptr());
+  }
+  const int64_t nmat = v.size(0), R = v.size(1), C = v.size(2);
+  const float* sp = nullptr;
+  if (scale.has_value()) {
+    TORCH_CHECK(scale->scalar_type() == at::kFloat && scale->is_contiguous() && scale->numel() == nmat * (scale_per_row ? R : C), "normuon_update: scale");
+    sp = scale->data_ptr<float>();
+  }
+  auto per_mat = [&](const c10::optional<Tensor>& t) -> const float* {
+    if (!t.has_value()) return nullptr;
+    TORCH_CHECK(t->scalar_type() == at::kFloat && t->is_contiguous() && t->numel() == nmat && t->is_cuda(), "normuon_update: per-matrix values fp32 [nmat] on the device");
+    return t->data_ptr<float>();
+  };
+  b200::normuon_update(p.data_ptr(), pb, mp, v.data_ptr(), vb, sp, (int)nmat, (int)R, (int)C, scale_per_row, (float)lr, (float)wd_lr,
+                       per_mat(lr_mat), per_mat(wd_mat), cur_stream());
+}
+
 // ---------------------------------------------------------------------------------------------- peer-memory collectives
 b200::PeerPtrs to_peers(at::IntArrayRef ptrs) {
   TORCH_CHECK(ptrs.size() >= 1 && (int)ptrs.size() <= b200::kMaxWorld, "peer pointer list: 1..", b200::kMaxWorld, " entries");
@@ -690,6 +730,8 @@ TORCH_LIBRARY(b200, m) {
   m.def("cast_fp8(Tensor x, Tensor(a!) out, float scale) -> ()");
   m.def("softcap_ce(Tensor logits, Tensor targets, Tensor(a!) loss_rows, Tensor(b!)? grad, float cap, float div, float loss_scale, float grad_scale, float shift=0.0, Tensor? mtp_w=None) -> ()");
   m.def("adam_step(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, float lr, float beta1, float beta2, float eps, float wd, float bias1, float bias2, float grad_scale, Tensor(d!)? shadow=None, float shadow_scale=1.0) -> ()");
+  m.def("normuon_scales(Tensor v, Tensor(a!) stat, Tensor(b!) second, bool red_cols, float beta2) -> ()");
+  m.def("normuon_update(Tensor(a!) p, Tensor(b!)? mant, Tensor v, Tensor? scale, bool scale_per_row, float lr, float wd_lr, Tensor? lr_mat=None, Tensor? wd_mat=None) -> ()");
   m.def("muon_momentum(Tensor g, Tensor(a!) buf, Tensor(b!) out, Tensor(c!) sumsq, float mu, bool nesterov, float grad_scale) -> ()");
   m.def("scale_by_inv_norm(Tensor(a!) x, Tensor sumsq, float eps) -> ()");
   m.def("axpy_bf16_to_f32(Tensor(a!) p, Tensor u, Tensor(b!)? p_bf16, float alpha) -> ()");
@@ -743,6 +785,8 @@ TORCH_LIBRARY_IMPL(b200, CUDA, m) {
   m.impl("cast_fp8", &cast_fp8);
   m.impl("softcap_ce", &softcap_ce);
   m.impl("adam_step", &adam_step);
+  m.impl("normuon_scales", &normuon_scales);
+  m.impl("normuon_update", &normuon_update);
   m.impl("muon_momentum", &muon_momentum);
   m.impl("scale_by_inv_norm", &scale_by_inv_norm);
   m.impl("axpy_bf16_to_f32", &axpy_bf16_to_f32);

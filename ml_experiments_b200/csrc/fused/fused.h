@@ -79,4 +79,15 @@ void scale_by_inv_norm(void* x_bf16, const float* sumsq, long long n, float eps,
 // p (fp32) += alpha * u (bf16) ; optionally also writes the bf16 copy p_bf16 used by the forward GEMMs
 void axpy_bf16_to_f32(float* p, const void* u_bf16, void* p_bf16, long long n, float alpha, cudaStream_t s);
 
+// ---- NorMuon (normuon.cu) ---------------------------------------------------------------------
+// v : stack [nmat][R][C] (bf16 or fp32). red_cols != 0: statistics per row (reduced over the C columns), else per column.
+// stat : scratch [nmat][R or C], receives the per-row / per-column scale; second : running second moment, same shape.
+void normuon_scales(const void* v, int v_is_bf16, float* stat, float* second, int nmat, int R, int C, int red_cols,
+                    float beta2, cudaStream_t s);
+// p -= p * [u * p >= 0] * wd_lr + u * lr with u = v * scale (scale may be null). p fp32, or bf16 with an optional
+// uint16 mantissa buffer (p and mant together are one fp32 number). lr_mat / wd_mat (optional): values per matrix.
+void normuon_update(void* p, int p_is_bf16, unsigned short* mant, const void* v, int v_is_bf16, const float* scale,
+                    int nmat, int R, int C, int scale_per_row, float lr, float wd_lr, const float* lr_mat,
+                    const float* wd_mat, cudaStream_t s);
+
 }  // namespace b200

@@ -37,6 +37,42 @@ def polar_express(G: torch.Tensor) -> torch.Tensor:
     return newton_schulz_torch(G, POLAR_EXPRESS_COEFFS, eps=1e-6, norm_scale=1.02)
 
 
+def _cuda_stack(t: torch.Tensor) -> bool:
+    return t.is_cuda and t.dim() >= 2 and t.is_contiguous() and t.dtype in (torch.bfloat16, torch.float32)
+
+
+def normuon_step_(p: torch.Tensor, mantissa, v: torch.Tensor, second_momentum: torch.Tensor, beta2: float, red_dim: int,
+                  lr, wd_lr) -> None:
+    """Variance reduction of ``v`` and the cautious update of ``p`` in one go. On CUDA this is three kernels
+    (sums of squares, per-matrix scale, fused scale + decay + step: ``csrc/fused/normuon.cu``) and the rescaled update is
+    never written to memory; elsewhere it is :func:`normuon_variance_reduction` + :func:`cautious_update_`.
+    ``lr`` / ``wd_lr``: floats, or per-matrix lists for a stack whose matrices have different multipliers."""
+    per_matrix = isinstance(lr, (list, tuple))
+    if _cuda_stack(v) and _cuda_stack(p) and second_momentum.is_cuda and second_momentum.dtype == torch.float32:
+        from ..ops.runtime import ops
+
+        o = ops()
+        v3 = v.reshape(-1, *v.shape[-2:])
+        p3 = p.reshape(-1, *p.shape[-2:])
+        red_cols = red_dim in (-1, v.dim() - 1)
+        stat = torch.empty(second_momentum.shape, dtype=torch.float32, device=v.device)
+        o.normuon_scales(v3, stat, second_momentum, red_cols, float(beta2))
+        m16 = None if mantissa is None else mantissa.view(torch.int16) if mantissa.element_size() == 2 else None
+        if mantissa is not None and m16 is None:
+            raise TypeError("the mantissa buffer of a bf16 parameter must be a 16-bit integer tensor on CUDA")
+        lr_t = torch.tensor(list(lr), dtype=torch.float32, device=v.device) if per_matrix else None
+        wd_t = torch.tensor(list(wd_lr), dtype=torch.float32, device=v.device) if per_matrix else None
+        o.normuon_update(p3, m16, v3, stat.reshape(-1), red_cols, 0.0 if per_matrix else float(lr),
+                         0.0 if per_matrix else float(wd_lr), lr_t, wd_t)
+        return
+    v = normuon_variance_reduction(v, second_momentum, beta2, red_dim)
+    if per_matrix:
+        for i in range(p.shape[0]):
+            cautious_update_(p[i], None if mantissa is None else mantissa[i], v[i], lr[i], wd_lr[i])
+    else:
+        cautious_update_(p, mantissa, v, lr, wd_lr)
+
+
 def normuon_variance_reduction(v: torch.Tensor, second_momentum: torch.Tensor, beta2: float, red_dim: int) -> torch.Tensor:
     """Rescales rows (or columns) of the orthogonalised update by a running second moment while keeping its norm."""
     v_mean = v.float().square().mean(dim=red_dim, keepdim=True)
@@ -158,7 +194,7 @@ class NorMuonAndAdam:
             st["second_momentum_buffer"] = torch.zeros(shp, dtype=torch.float32, device=s.device)
             st["red_dim"] = red
             if s.dtype == torch.bfloat16:
-                st["mantissa"] = torch.zeros_like(s, dtype=torch.int32)
+                st["mantissa"] = torch.zeros_like(s, dtype=torch.int16)
         self.param_states[label] = st
 
     # ------------------------------------------------------------------------------------------ communication
@@ -201,20 +237,19 @@ class NorMuonAndAdam:
         st["momentum_buffer"].lerp_(g, 1 - cfg.momentum)
         u = g.lerp(st["momentum_buffer"], cfg.momentum)
         v = polar_express(u)
-        v = normuon_variance_reduction(v, st["second_momentum_buffer"], cfg.beta2, st["red_dim"])
         p_slice = self._shard(label, self._view(label))
         # p -= p * mask * (wd_mul * wd * lr) * lr_eff + v * lr_eff (modded-nanogpt/train_gpt.py:708-760): the decay
         # coefficient carries the effective learning rate of the matrix as well
         wd = cfg.wd_mul * cfg.weight_decay * cfg.lr
         if cfg.per_matrix_lr_mul is not None:
-            for i in range(p_slice.shape[0]):
-                j = self.rank * cfg.chunk_size + i if cfg.comms == "sharded" else i
-                mant = st["mantissa"][i] if "mantissa" in st else None
-                lr_eff = cfg.lr * cfg.lr_mul * cfg.per_matrix_lr_mul[j]
-                cautious_update_(p_slice[i], mant, v[i], lr_eff, wd * lr_eff)
+            first = self.rank * cfg.chunk_size if cfg.comms == "sharded" else 0
+            lrs = [cfg.lr * cfg.lr_mul * cfg.per_matrix_lr_mul[first + i] for i in range(p_slice.shape[0])]
+            normuon_step_(p_slice, st.get("mantissa"), v, st["second_momentum_buffer"], cfg.beta2, st["red_dim"], lrs,
+                          [wd * l for l in lrs])
         else:
             lr_eff = cfg.lr * cfg.lr_mul
-            cautious_update_(p_slice, st.get("mantissa"), v, lr_eff, wd * lr_eff)
+            normuon_step_(p_slice, st.get("mantissa"), v, st["second_momentum_buffer"], cfg.beta2, st["red_dim"], lr_eff,
+                          wd * lr_eff)
 
     @torch.no_grad()
     def step(self, do_adam: bool = True) -> None:
