@@ -98,22 +98,16 @@ class FixtureScraper(Collector):
                                            [infer_category(f"{f.name} {n}", v).value for _, _, v, n in lits])
 
 
-class DetectSecretsCollector(FixtureScraper):
-    name = "detect_secrets"
-    repo_url = "https://github.com/Yelp/detect-secrets"
+class GenericFixtureCollector(FixtureScraper):
+    """Literal scraper over an arbitrary checkout (every hit is labelled positive): the fallback for scanner
+    repositories that do not follow the layouts the per-tool collectors of :mod:`.tools` read."""
 
+    name = "fixtures"
 
-class GitleaksCollector(FixtureScraper):
-    name = "gitleaks"
-    repo_url = "https://github.com/gitleaks/gitleaks"
-    include = ("test", "testdata", "cmd/generate", "rules")
-
-
-class TrufflehogCollector(FixtureScraper):
-    name = "trufflehog"
-    repo_url = "https://github.com/trufflesecurity/trufflehog"
-    include = ("test", "detectors")
-    suffixes = (".go", ".yaml", ".json", ".txt")
+    def __init__(self, root: Path | None = None, max_files: int = 5000, name: str | None = None):
+        super().__init__(root, max_files)
+        if name:
+            self.name = name
 
 
 class CredDataCollector(Collector):

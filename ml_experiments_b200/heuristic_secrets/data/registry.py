@@ -5,7 +5,8 @@ from typing import Type
 
 from .collector import Collector
 from .collectors.generated import Base64Generator, HashGenerator, UUIDGenerator
-from .collectors.scrapers import CredDataCollector, DetectSecretsCollector, GitleaksCollector, TrufflehogCollector
+from .collectors.scrapers import CredDataCollector
+from .collectors.tools import DetectSecretsCollector, GitleaksCollector, TrufflehogCollector
 
 
 class CollectorRegistry:
