@@ -14,6 +14,7 @@
 #include "gemm/gemm.h"
 #include "mra/mra.h"
 #include "scan/s6_scan.h"
+#include "scan/ssd.h"
 #include "window/window_attn.h"
 #include "wkv/wkv.h"
 
@@ -436,6 +437,34 @@ void s6_set_states_per_thread(int64_t fwd_qs, int64_t bwd_qs, const Tensor& like
   b200::s6_set_states_per_thread((int)fwd_qs, (int)bwd_qs);
 }
 
+bool ssd_fwd_supported(int64_t L, int64_t H, int64_t Hb, int64_t N, int64_t P) {
+  return b200::ssd_fwd_supported((int)L, (int)H, (int)Hb, (int)N, (int)P);
+}
+
+void ssd_fwd(const Tensor& x, const Tensor& Bm, const Tensor& Cm, const Tensor& log_a, const Tensor& g_off, const Tensor& g_diag,
+             Tensor y, const c10::optional<Tensor>& init_state, const c10::optional<Tensor>& final_state, Tensor status) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 4 && Bm.dim() == 4 && Cm.dim() == 4, "ssd_fwd: x [b, L, H, P], B / C [b, L, Hb, N]");
+  for (const Tensor* t : {&x, &Bm, &Cm, (const Tensor*)&y}) TORCH_CHECK(t->scalar_type() == at::kBFloat16 && t->is_contiguous(), "ssd_fwd: bf16 contiguous x, B, C, y");
+  for (const Tensor* t : {&log_a, &g_off, &g_diag})
+    TORCH_CHECK(t->scalar_type() == at::kFloat && t->is_contiguous() && t->numel() == x.size(0) * x.size(1) * x.size(2), "ssd_fwd: fp32 [b, L, H] decay / weights");
+  TORCH_CHECK(Bm.sizes() == Cm.sizes() && Bm.size(0) == x.size(0) && Bm.size(1) == x.size(1) && y.sizes() == x.sizes(), "ssd_fwd: shapes");
+  b200::SsdArgs a;
+  a.batch = (int)x.size(0); a.L = (int)x.size(1); a.H = (int)x.size(2); a.P = (int)x.size(3);
+  a.Hb = (int)Bm.size(2); a.N = (int)Bm.size(3);
+  const int64_t ns = (int64_t)a.batch * a.H * a.N * a.P;
+  auto st = [&](const c10::optional<Tensor>& t) -> float* {
+    if (!t.has_value()) return nullptr;
+    TORCH_CHECK(t->scalar_type() == at::kFloat && t->is_contiguous() && t->numel() == ns, "ssd_fwd: state fp32 [b, H, N, P]");
+    return t->data_ptr<float>();
+  };
+  a.x = x.data_ptr(); a.B = Bm.data_ptr(); a.C = Cm.data_ptr(); a.y = y.data_ptr();
+  a.log_a = log_a.data_ptr<float>(); a.g_off = g_off.data_ptr<float>(); a.g_diag = g_diag.data_ptr<float>();
+  a.init_state = st(init_state); a.final_state = st(final_state);
+  a.status = status.data_ptr<int>(); a.stream = cur_stream();
+  b200::ssd_fwd_sm100(a);
+}
+
 void s6_scan_fwd(const Tensor& u, const Tensor& delta, const c10::optional<Tensor>& delta_bias, bool softplus, const Tensor& A,
                  const Tensor& Bm, const Tensor& Cm, const c10::optional<Tensor>& Dv, const c10::optional<Tensor>& z,
                  const c10::optional<Tensor>& y_pre, Tensor out, const c10::optional<Tensor>& state) {
@@ -745,6 +774,7 @@ TORCH_LIBRARY(b200, m) {
   m.def("allreduce_mean_multimem(int mc_ptr, int world, int rank, int n, int dtype, Tensor flags, int[] peer_flags, int channel, int epoch, Tensor(a!) status) -> ()");
   m.def("allreduce_mean(int[] buf_ptrs, int rank, int n, int dtype, Tensor flags, int[] peer_flags, int channel, int epoch, Tensor(a!) status) -> ()");
   m.def("s6_set_states_per_thread(int fwd_qs, int bwd_qs, Tensor like) -> ()");
+  m.def("ssd_fwd(Tensor x, Tensor B, Tensor C, Tensor log_a, Tensor g_off, Tensor g_diag, Tensor(a!) y, Tensor? init_state, Tensor(b!)? final_state, Tensor(c!) status) -> ()");
   m.def("s6_scan_fwd(Tensor u, Tensor delta, Tensor? delta_bias, bool softplus, Tensor A, Tensor Bm, Tensor Cm, Tensor? Dv, Tensor? z, Tensor(a!)? y_pre, Tensor(b!) out, Tensor(c!)? state) -> ()");
   m.def("s6_scan_bwd(Tensor u, Tensor delta, Tensor? delta_bias, bool softplus, Tensor A, Tensor Bm, Tensor Cm, Tensor? Dv, Tensor? z, Tensor? y_pre, Tensor dout, Tensor state, Tensor(a!) du, Tensor(b!) ddelta, Tensor(c!) dA, Tensor(d!) dB_part, Tensor(e!) dC_part, Tensor(f!)? dD, Tensor(g!)? dz, Tensor(h!)? ddelta_bias) -> ()");
   m.def("causal_conv1d_silu_fwd(Tensor x, Tensor w, Tensor? bias, Tensor(a!) y) -> ()");
@@ -800,6 +830,7 @@ TORCH_LIBRARY_IMPL(b200, CUDA, m) {
   m.impl("allreduce_mean_multimem", &allreduce_mean_multimem);
   m.impl("allreduce_mean", &allreduce_mean);
   m.impl("s6_set_states_per_thread", &s6_set_states_per_thread);
+  m.impl("ssd_fwd", &ssd_fwd);
   m.impl("s6_scan_fwd", &s6_scan_fwd);
   m.impl("s6_scan_bwd", &s6_scan_bwd);
   m.impl("causal_conv1d_silu_fwd", &causal_conv1d_silu_fwd);

@@ -5,8 +5,10 @@
 #include <cuda_runtime.h>
 #include <cstdint>
 #include <cstdio>
+#include <cstring>
 #include <stdexcept>
 #include <string>
+#include <unordered_map>
 
 namespace b200 {
 
@@ -38,11 +40,43 @@ inline PFN_encodeTiled get_encode_fn() {
   return fn;
 }
 
+// A training step issues the same few hundred (pointer, shape, box) combinations every iteration (the caching
+// allocator hands the same activation buffers back), so encoded maps are kept per host thread and looked up by value.
+struct TmapKey {
+  uint64_t v[10];
+  bool operator==(const TmapKey& o) const { return std::memcmp(v, o.v, sizeof v) == 0; }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    uint64_t h = 1469598103934665603ull;
+    for (uint64_t x : k.v) { h ^= x; h *= 1099511628211ull; h ^= h >> 29; }
+    return (size_t)h;
+  }
+};
+
+inline CUtensorMap encode_tmap_3d(const void* base, TmapDtype dt, uint64_t d0, uint64_t d1, uint64_t d2,
+                                  uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t b0, uint32_t b1,
+                                  bool swizzle128);
+
 // rank-3 row-major tensor map: dims (fastest first) {d0, d1, d2}, strides in BYTES for d1, d2,
 // box {b0, b1, 1}. swizzle128 selects CU_TENSOR_MAP_SWIZZLE_128B (b0 * elt must be 128 bytes then).
 inline CUtensorMap make_tmap_3d(const void* base, TmapDtype dt, uint64_t d0, uint64_t d1, uint64_t d2,
                                 uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t b0, uint32_t b1,
                                 bool swizzle128) {
+  thread_local std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
+  const TmapKey key{{(uint64_t)reinterpret_cast<uintptr_t>(base), (uint64_t)dt, d0, d1, d2, stride1_bytes, stride2_bytes, b0, b1,
+                     (uint64_t)swizzle128}};
+  auto it = cache.find(key);
+  if (it != cache.end()) return it->second;
+  if (cache.size() > 8192) cache.clear();
+  const CUtensorMap m = encode_tmap_3d(base, dt, d0, d1, d2, stride1_bytes, stride2_bytes, b0, b1, swizzle128);
+  cache.emplace(key, m);
+  return m;
+}
+
+inline CUtensorMap encode_tmap_3d(const void* base, TmapDtype dt, uint64_t d0, uint64_t d1, uint64_t d2,
+                                  uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t b0, uint32_t b1,
+                                  bool swizzle128) {
   CUtensorMap m;
   CUtensorMapDataType cdt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   switch (dt) {

@@ -194,12 +194,29 @@ def main(argv=None):
         Bm, Cm = (torch.randn(b, L, h, n, device=dev, dtype=bf) for _ in range(2))
         la = -torch.rand(b, L, h, device=dev) * 0.1
         gm = torch.rand(b, L, h, device=dev)
-        fn = lambda: ssd_chunk_scan(x, Bm, Cm, la, gm)
-        flops = 2.0 * b * L * h * (64 * n + 64 * p + 2 * n * p)
+        import os
+
+        from .ssd_scan import _ssd_chunk_scan_torch
+
+        with torch.no_grad():
+            fn_t = lambda: _ssd_chunk_scan_torch(x, Bm, Cm, la, gm)
+            torch_ms = _time(fn_t, max(a.iters // 4, 2), 2)          # the batched-GEMM formulation, for the ratio
+        fn_inner = lambda: ssd_chunk_scan(x, Bm, Cm, la, gm)
+
+        def fn():
+            with torch.no_grad():
+                return fn_inner()
+        flops = 2.0 * b * L * h * (128 * n + 128 * p + 2 * n * p)     # kernel: 128-step chunks
+        bytes_ = (x.numel() * 2 + Bm.numel() * 2) * 2.0 + la.numel() * 12.0
+        extra = {"torch_formulation_ms": round(torch_ms, 4)}
     ms = _time(fn, a.iters, a.warmup)
     check_status()
+    extra = locals().get("extra", {})
     pk = _peaks()
     out = {"op": a.op, "ms": round(ms, 4), "args": {k: v for k, v in vars(a).items() if k != "op"}, "peaks": pk["source"]}
+    out.update(extra)
+    if "torch_formulation_ms" in extra:
+        out["speedup_vs_torch_formulation"] = round(extra["torch_formulation_ms"] / ms, 2)
     if flops:
         out["tflops"] = round(flops / ms / 1e9, 1)
         out["frac_of_bf16_peak"] = round(flops / ms / 1e9 / pk["bf16_tflops"], 3)

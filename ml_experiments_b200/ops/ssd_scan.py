@@ -11,6 +11,11 @@ and materialises the ``[B, L, H, N, P]`` outer products, and of the vendored Mam
 products that land on the tensor cores -- intra-chunk ``(C B^T o decay) U``, per-chunk end states, a logarithmic-depth
 inter-chunk state pass, and the carried-state contribution -- and nothing of size ``L*N*P`` is ever formed.
 Differentiable through autograd. ``ssd_scan_ref`` is the sequential fp32 oracle.
+
+On a B200 with bf16 inputs and supported shapes (``L % 128 == 0``, ``N`` and ``P`` in {64, 128}) the forward runs in ONE
+hand-written kernel (``csrc/scan/ssd_sm100.cu``): a CTA per (batch, head) walks 128-step chunks with the four
+products on tcgen05 and the running state resident in tensor memory; the backward differentiates the batched-GEMM
+formulation below (recomputed from the saved inputs). ``B200_SSD_KERNEL=0`` disables the kernel path.
 """
 from __future__ import annotations
 
@@ -79,12 +84,83 @@ def _exclusive_state_pass(log_a, s, s0=None, block: int = 64):
     return excl, final
 
 
+def kernel_supported(x, B, C) -> bool:
+    import os
+
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and os.environ.get("B200_SSD_KERNEL", "1") == "1"):
+        return False
+    b, L, H, P = x.shape
+    Hb = B.shape[2]
+    return L % 128 == 0 and B.shape[-1] in (64, 128) and P in (64, 128) and H % Hb == 0 and B.shape == C.shape
+
+
+def _fold_weights(log_alpha, gamma, beta):
+    """``(g_off, g_diag)`` of the kernel: the look-back term ``beta_t B_{t-1} x_{t-1}`` is the outer product of step
+    ``t-1`` entering one step late and without that step's decay, i.e. weight ``beta_t / alpha_t`` on top of
+    ``gamma_{t-1}`` for every later output and for the state."""
+    g = gamma.float()
+    if beta is None:
+        return g.contiguous(), g.contiguous()
+    late = beta.float() * torch.exp(-log_alpha.float().clamp_min(-80.0))
+    return (g + F.pad(late[:, 1:], (0, 0, 0, 1))).contiguous(), g.contiguous()
+
+
+def ssd_forward_kernel(x, B, C, log_alpha, gamma, beta=None, init_state=None, return_state: bool = False):
+    """Forward only, on the tcgen05 kernel. Shapes as :func:`ssd_chunk_scan`; ``x, B, C`` bf16."""
+    from .runtime import ops, status
+
+    g_off, g_diag = _fold_weights(log_alpha, gamma, beta)
+    y = torch.empty_like(x)
+    b, L, H, P = x.shape
+    N = B.shape[-1]
+    fin = torch.empty(b, H, N, P, dtype=torch.float32, device=x.device) if return_state else None
+    init = None if init_state is None else init_state.float().contiguous()
+    ops().ssd_fwd(x.contiguous(), B.contiguous(), C.contiguous(), log_alpha.float().contiguous(), g_off, g_diag, y, init, fin,
+                  status(x.device))
+    return (y, fin) if return_state else y
+
+
+class _SsdKernelFn(torch.autograd.Function):
+    """Kernel forward; backward = autograd through the batched-GEMM formulation on the saved inputs."""
+
+    @staticmethod
+    def forward(ctx, x, B, C, log_alpha, gamma, beta, init_state, return_state):
+        ctx.save_for_backward(x, B, C, log_alpha, gamma, beta, init_state)
+        ctx.return_state = return_state
+        out = ssd_forward_kernel(x, B, C, log_alpha, gamma, beta, init_state, return_state)
+        return out if return_state else (out, None)
+
+    @staticmethod
+    def backward(ctx, dy, dstate):
+        saved = ctx.saved_tensors
+        with torch.enable_grad():
+            ins = [None if t is None else t.detach().requires_grad_(t.is_floating_point()) for t in saved]
+            x, B, C, la, g, bt, s0 = ins
+            out = _ssd_chunk_scan_torch(x, B, C, la, g, bt, 64, s0, ctx.return_state)
+            y, st = out if ctx.return_state else (out, None)
+            outs, gouts = [y], [dy]
+            if st is not None and dstate is not None:
+                outs.append(st)
+                gouts.append(dstate.to(st.dtype))
+            need = [t for t, n in zip(ins, ctx.needs_input_grad[:7]) if t is not None and n]
+            grads = iter(torch.autograd.grad(outs, need, gouts, allow_unused=True))
+        res = [next(grads) if (t is not None and n) else None for t, n in zip(ins, ctx.needs_input_grad[:7])]
+        return (*res, None)
+
+
 def ssd_chunk_scan(x, B, C, log_alpha, gamma, beta=None, chunk: int = 64, init_state=None, return_state: bool = False):
     """Chunk-parallel evaluation of the recurrence in the module docstring.
 
     ``x [b,L,H,P]``; ``B, C [b,L,H,N]`` (a size-1 head dim broadcasts: grouped B/C); ``log_alpha, gamma, beta [b,L,H]``.
     Returns ``y [b,L,H,P]`` (and the final state ``[b,H,N,P]`` if ``return_state``).
     """
+    if kernel_supported(x, B, C) and B.dtype == torch.bfloat16 and C.dtype == torch.bfloat16:
+        y, st = _SsdKernelFn.apply(x, B, C, log_alpha, gamma, beta, init_state, return_state)
+        return (y, st) if return_state else y
+    return _ssd_chunk_scan_torch(x, B, C, log_alpha, gamma, beta, chunk, init_state, return_state)
+
+
+def _ssd_chunk_scan_torch(x, B, C, log_alpha, gamma, beta=None, chunk: int = 64, init_state=None, return_state: bool = False):
     b, L, H, P = x.shape
     N = B.shape[-1]
     B = B.expand(b, L, H, N)

@@ -6,7 +6,7 @@ basis ``Q (n x r)``, ``r = rank_fraction * min(m, n)``:
 
     B = M + G                      (G is this rank's local gradient in the data-parallel variant)
     P = B Q              -> mean over ranks            (m x r)
-    P = orthonormalise(P)                              (Cholesky-QR; Householder QR fallback; or Newton-Schulz)
+    P = orthonormalise(P)                              (Newton-Schulz on the GEMM kernel; Cholesky-QR / Householder QR)
     R = Bᵀ P             -> mean over ranks            (n x r)
     M = B - (1 - mu) P Rᵀ                              (error feedback: what the low-rank step missed stays in M)
     Q = R with unit-norm columns
@@ -16,6 +16,12 @@ Only ``P`` and ``R`` (``(m + n) r`` numbers instead of ``m n``) cross the networ
 and processed as batches: the products run on the tcgen05 GEMM (bf16 operands, fp32 accumulation) and the two means
 use the peer-memory all-reduce kernel when a :class:`~ml_experiments_b200.parallel.symm.SymmWorld` is given, NCCL when
 only a process group exists, nothing for a single process.
+
+Orthonormalisation on CUDA defaults to ``ortho="ns"``: five Polar-Express Newton-Schulz iterations on the stacked
+``m x r`` blocks, i.e. 15 batched tcgen05 GEMMs with no factorisation, no library call and no host synchronisation
+(Cholesky-QR has to read back whether the factorisation succeeded). The columns come out orthonormal up to the
+iteration's tolerance (singular values within a few percent of 1); what the slightly inexact projector misses stays in
+the momentum through the error-feedback line. ``"cholqr"`` and ``"qr"`` remain for CPU runs and exact comparisons.
 """
 from __future__ import annotations
 
@@ -29,6 +35,14 @@ from ..ops import gemm as G
 
 def orthonormalize(P: torch.Tensor, method: str = "cholqr") -> torch.Tensor:
     """Orthonormal basis of the column space of each ``P[b] (m x r)`` (fp32)."""
+    if method == "ns":
+        from ..ops.newton_schulz import POLAR_EXPRESS_COEFFS, newton_schulz_, newton_schulz_torch
+
+        scale = P.float().norm(dim=(-2, -1), keepdim=True) * 1.02 + 1e-6
+        if P.is_cuda and P.dim() == 3 and all(d % 8 == 0 for d in P.shape[-2:]):
+            X = (P.float() / scale).to(torch.bfloat16).contiguous()
+            return newton_schulz_(X, POLAR_EXPRESS_COEFFS).float()
+        return newton_schulz_torch(P, POLAR_EXPRESS_COEFFS, eps=1e-6, norm_scale=1.02).float()
     if method == "qr":
         return torch.linalg.qr(P, mode="reduced").Q
     gram = P.transpose(-1, -2) @ P
@@ -52,8 +66,10 @@ def _bmm(a: torch.Tensor, b: torch.Tensor, a_t: bool = False) -> torch.Tensor:
 
 class Dion(torch.optim.Optimizer):
     def __init__(self, params, lr: float = 0.01, mu: float = 0.95, rank_fraction: float = 0.25, weight_decay: float = 0.0,
-                 ortho: str = "cholqr", world=None, process_group=None, seed: int = 0):
+                 ortho: str | None = None, world=None, process_group=None, seed: int = 0):
         params = [*params]
+        if ortho is None:
+            ortho = "ns" if params and params[0].is_cuda else "cholqr"
         super().__init__(params, dict(lr=lr, mu=mu, rank_fraction=rank_fraction, weight_decay=weight_decay))
         self.ortho, self.world, self.group, self.seed = ortho, world, process_group, seed
         self.distributed = world is not None or (dist.is_initialized() and dist.get_world_size(process_group) > 1)
@@ -71,7 +87,13 @@ class Dion(torch.optim.Optimizer):
             r = max(8, r // 8 * 8) if min(m, n) >= 8 else r
             dev = plist[0].device
             Q = torch.linalg.qr(torch.randn(k, n, r, generator=gen)).Q.to(dev)
-            g = dict(m=m, n=n, r=r, k=k, plist=plist, Q=Q.float(), M=torch.zeros(k, m, n, device=dev))
+            g = dict(m=m, n=n, r=r, k=k, plist=plist, Q=Q.float(), M=torch.zeros(k, m, n, device=dev),
+                     G=torch.empty(k, m, n, device=dev))
+            slot, g["gviews"] = 0, []
+            for p in plist:
+                c = p.numel() // (m * n)
+                g["gviews"].append(g["G"][slot:slot + c].view(p.shape))
+                slot += c
             if self.world is not None:
                 g["P_buf"] = self.world.alloc(k * m * r, torch.float32)
                 g["R_buf"] = self.world.alloc(k * n * r, torch.float32)
@@ -95,7 +117,7 @@ class Dion(torch.optim.Optimizer):
             o.allreduce_mean(buf.ptrs, w.rank, min(n, buf.local.numel() // 4 * 4), 0, w.flags.local, w.flags.ptrs, CH_F32_IN, e,
                              status(t.device))
             o.comm_wait(w.flags.local, w.world, CH_F32_OUT, e, status(t.device))
-            return flat.view_as(t).clone()
+            return flat.view_as(t)        # the next all-reduce of this buffer is enqueued after every consumer of the view
         dist.all_reduce(t, op=dist.ReduceOp.AVG, group=self.group)
         return t
 
@@ -108,12 +130,12 @@ class Dion(torch.optim.Optimizer):
         lr, mu, wd = float(hp["lr"]), float(hp["mu"]), float(hp["weight_decay"])
         for g in self._groups:
             m, n = g["m"], g["n"]
-            Gs = torch.cat([p.grad.float().reshape(-1, m, n) for p in g["plist"]], 0)
-            B = g["M"] + Gs
+            torch._foreach_copy_(g["gviews"], [p.grad for p in g["plist"]])     # one multi-tensor copy (and cast) into the stack
+            B = g["M"].add_(g["G"])
             P = self._mean(_bmm(B, g["Q"]), g.get("P_buf"))
             P = orthonormalize(P.float(), self.ortho)
             R = self._mean(_bmm(B, P, a_t=True), g.get("R_buf"))
-            g["M"] = B - (1 - mu) * _bmm(P, R.transpose(-1, -2).contiguous())
+            B.sub_(_bmm(P, R.transpose(-1, -2).contiguous()), alpha=1 - mu)      # M <- B - (1 - mu) P Rᵀ, in place
             Qn = R / R.norm(dim=-2, keepdim=True).clamp(min=1e-8)
             g["Q"] = Qn
             upd = _bmm(P, Qn.transpose(-1, -2).contiguous())

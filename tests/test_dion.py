@@ -57,3 +57,23 @@ def test_dion_reduces_loss():
         opt.step()
         losses.append(loss.item())
     assert losses[-1] < 0.9 * losses[0]
+
+
+def test_newton_schulz_orthonormalisation_trains_too():
+    """``ortho="ns"`` (the CUDA default: GEMMs only, no factorisation): columns near-orthonormal, loss still falls."""
+    P = torch.randn(2, 64, 16)
+    Qm = orthonormalize(P, "ns")
+    s = torch.linalg.svdvals(Qm)
+    assert s.max() < 1.3 and s.min() > 0.6
+    torch.manual_seed(1)
+    A, Y = torch.randn(256, 64), torch.randn(256, 32)
+    W = torch.zeros(32, 64, requires_grad=True)
+    opt = Dion([W], lr=0.05, mu=0.9, ortho="ns")
+    losses = []
+    for _ in range(100):
+        loss = ((A @ W.T - Y) ** 2).mean()
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        losses.append(loss.item())
+    assert losses[-1] < 0.9 * losses[0]
