@@ -308,11 +308,80 @@ def evaluate(model, data: PreloadedDataset, task_type, amp: bool):
     return correct / max(total, 1), losses
 
 
+# ------------------------------------------------------------------------------------------------ sample selection
+def hard_fraction(epoch: int, epochs: int, start: float, end: float) -> float:
+    """Share of each batch that is back-propagated at ``epoch``: linear from ``start`` to ``end`` over the run."""
+    t = epoch / max(epochs - 1, 1)
+    return start + (end - start) * t
+
+
+def selection_weights(per_sample: torch.Tensor, mode: str | None, fraction: float = 1.0) -> torch.Tensor:
+    """Per-sample weights for one batch from the (detached) per-sample losses.
+
+    ``None``: all ones. ``"top"``: ones on the hardest ``fraction`` of the batch, zeros elsewhere (in-batch hard mining,
+    ``--hard-start`` / ``--hard-end`` / ``--first-epoch-pct``). ``"wtf"``: +1 above the batch median, -1 below, i.e.
+    descent on the hard half and ascent on the easy half. ``"easy"``: complement of ``"top"`` (the second model of a duo)."""
+    n = per_sample.numel()
+    if mode is None or n == 0:
+        return torch.ones_like(per_sample)
+    if mode == "wtf":
+        return torch.where(per_sample > per_sample.median(), 1.0, -1.0).to(per_sample.dtype)   # torch.median: the lower middle
+    k = min(max(int(round(n * fraction)), 1), n)
+    hard = torch.zeros_like(per_sample)
+    hard[per_sample.topk(k).indices] = 1.0
+    if mode == "top":
+        return hard
+    if mode == "easy":
+        easy = 1.0 - hard
+        return easy if easy.sum() > 0 else hard
+    raise ValueError(f"unknown selection mode {mode}")
+
+
+def weighted_mean(per_sample: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    return (per_sample * w).sum() / w.abs().sum().clamp(min=1.0)
+
+
+class DuoModel(nn.Module):
+    """Two copies of an architecture trained on complementary parts of every batch (one on the hardest share, the
+    other on the rest, ranked by the merged prediction's loss) and merged at inference (``--duo``)."""
+
+    MERGE_STRATEGIES = ("mean", "max", "logsum", "harmonic")
+
+    def __init__(self, model_hard: nn.Module, model_easy: nn.Module, merge: str = "mean"):
+        super().__init__()
+        if merge not in self.MERGE_STRATEGIES:
+            raise ValueError(f"merge must be one of {self.MERGE_STRATEGIES}")
+        self.model_hard, self.model_easy, self.merge = model_hard, model_easy, merge
+
+    def merge_logits(self, a, b):
+        if self.merge == "mean":
+            return 0.5 * (a + b)
+        if self.merge == "max":
+            return torch.maximum(a, b)
+        if self.merge == "logsum":
+            return F.log_softmax(a.float(), -1) + F.log_softmax(b.float(), -1)
+        return 2 * a * b / (a + b + 1e-8)
+
+    def forward_both(self, x):
+        a, b = self.model_hard(x), self.model_easy(x)
+        return self.merge_logits(a, b), a, b
+
+    def forward(self, x):
+        return self.forward_both(x)[0]
+
+
 def train_model(model, train: PreloadedDataset, test: PreloadedDataset, epochs: int, lr: float, task_type: str = "classification",
                 warmup_epochs: int = 2, cosine_start: float = 0.1, swa: bool = False, swa_start: float = 0.8, swa_lr: float = 1e-5,
                 hard_mining: bool = False, amp: bool = False, label_smoothing: float = 0.1, self_distill: bool = False,
                 distill_alpha: float = 0.5, distill_temp: float = 2.0, distill_merge: str | None = None, distill_merge_alpha: float = 0.5,
-                checkpoint_dir: str | None = None, model_name: str = "model", verbose: bool = True, weight_decay: float = 0.01):
+                checkpoint_dir: str | None = None, model_name: str = "model", verbose: bool = True, weight_decay: float = 0.01,
+                hard_start: float | None = None, hard_end: float | None = None, first_epoch_pct: float | None = None,
+                wtf_mode: bool = False, distill_adaptive: bool = False):
+    """Trains ``model`` (or both halves of a :class:`DuoModel`). In-batch selection: with ``hard_start`` / ``hard_end`` only
+    the hardest share of each batch is back-propagated (share moving linearly over the epochs), ``first_epoch_pct``
+    does that for the first epoch only, ``wtf_mode`` ascends on the easy half. ``distill_adaptive`` blends the
+    teacher and the labels per sample: easy samples follow the teacher, hard ones the labels."""
+    duo = isinstance(model, DuoModel)
     opt = torch.optim.AdamW(model.parameters(), lr=lr, weight_decay=weight_decay)
     steps = epochs * len(train)
     sched = torch.optim.lr_scheduler.LambdaLR(opt, lambda s: lr_lambda(s, steps, min(warmup_epochs, max(epochs - 1, 0)) * len(train), cosine_start))
@@ -327,14 +396,38 @@ def train_model(model, train: PreloadedDataset, test: PreloadedDataset, epochs: 
             for gp in opt.param_groups:
                 gp["lr"] = swa_lr
         for idx, x, y in train.batches(weights if hard_mining else None):
+            frac, mode = 1.0, None
+            if wtf_mode:
+                mode = "wtf"
+            elif first_epoch_pct is not None and epoch == 0:
+                frac, mode = first_epoch_pct, "top"
+            elif hard_start is not None:
+                frac, mode = hard_fraction(epoch, epochs, hard_start, hard_end if hard_end is not None else hard_start), "top"
             with torch.autocast(x.device.type, dtype=torch.bfloat16, enabled=amp):
-                logits = model(x)
-                loss = _loss_per_sample(logits, y, task_type, label_smoothing).mean()
-                if teacher is not None:
+                if duo:
+                    logits, la, lb = model.forward_both(x)
+                    rank_by = _loss_per_sample(logits, y, task_type).detach()
+                    f = frac if mode == "top" else 0.5
+                    pa, pb = _loss_per_sample(la, y, task_type, label_smoothing), _loss_per_sample(lb, y, task_type, label_smoothing)
+                    loss = weighted_mean(pa, selection_weights(rank_by, "top", f)) + weighted_mean(pb, selection_weights(rank_by, "easy", f))
+                else:
+                    logits = model(x)
+                    per = _loss_per_sample(logits, y, task_type, label_smoothing)
+                    w = selection_weights(per.detach(), mode, frac)
+                    loss = weighted_mean(per, w)
+                if teacher is not None and not duo:
                     with torch.no_grad():
                         tl = teacher(x)
-                    kd = F.kl_div(F.log_softmax(logits.float() / distill_temp, -1), F.softmax(tl.float() / distill_temp, -1), reduction="batchmean")
-                    loss = (1 - distill_alpha) * loss + distill_alpha * kd * distill_temp ** 2
+                    kd_rows = F.kl_div(F.log_softmax(logits.float() / distill_temp, -1), F.softmax(tl.float() / distill_temp, -1),
+                                       reduction="none").sum(-1)
+                    if kd_rows.dim() > 1:
+                        kd_rows = kd_rows.mean(tuple(range(1, kd_rows.dim())))
+                    if distill_adaptive:
+                        # rank of each sample's label loss inside the batch in [0, 1]: 0 (easy) -> all teacher, 1 (hard) -> all labels
+                        r = per.detach().argsort().argsort().float() / max(per.numel() - 1, 1)
+                        loss = (r * per + (1 - r) * kd_rows * distill_temp ** 2).mean()
+                    else:
+                        loss = (1 - distill_alpha) * loss + distill_alpha * kd_rows.mean() * distill_temp ** 2
             opt.zero_grad(set_to_none=True)
             loss.backward()
             opt.step()
@@ -396,6 +489,27 @@ def profile_one_batch(model, data: PreloadedDataset, task_type, amp, warmup: int
     print(prof.key_averages().table(sort_by="self_cuda_time_total" if data.x.is_cuda else "self_cpu_time_total", row_limit=25))
 
 
+def _train_with_ponder(model, train: PreloadedDataset, test: PreloadedDataset, a, dev, n_classes: int) -> float:
+    """``--ponder``: the classifier is trained on cross entropy plus a learned score of (logits, target)."""
+    from ..models.unified.ponder import PonderTrainConfig, PonderTrainer, PonderWrapper
+
+    class _Loader:          # PreloadedDataset batches as (inputs, labels) pairs with a length, what the trainer iterates over
+        def __init__(self, data):
+            self.data = data
+
+        def __len__(self):
+            return len(self.data)
+
+        def __iter__(self):
+            return ((x, y) for _, x, y in self.data.batches())
+
+    cfg = PonderTrainConfig(meta_lr=a.ponder_meta_lr, model_lr=a.lr, epochs=a.epochs, meta_warmup_epochs=a.ponder_meta_warmup,
+                            meta_wean_epochs=a.ponder_meta_wean, reward_scale=a.ponder_reward_scale,
+                            meta_min_supervised=a.ponder_min_supervised)
+    trainer = PonderTrainer(PonderWrapper(model, n_classes=n_classes), _Loader(train), _Loader(test), dev, cfg, squeeze_channel=False)
+    return trainer.train(a.epochs)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--model", default="all", help=f"one of {MODEL_TYPES} or 'all' or a comma list")
@@ -433,6 +547,24 @@ def main(argv=None):
     ap.add_argument("--task-vocab-size", type=int, default=None)
     ap.add_argument("--siren-conv", action="store_true")
     ap.add_argument("--jacobi-iters", type=int, default=1)
+    ap.add_argument("--hard-start", type=float, default=None, help="share of each batch back-propagated at the first epoch (hardest first)")
+    ap.add_argument("--hard-end", type=float, default=None, help="the same at the last epoch (linear in between)")
+    ap.add_argument("--first-epoch-pct", type=float, default=None, help="first epoch only: back-propagate the hardest share of each batch")
+    ap.add_argument("--wtf-mode", action="store_true", help="descent on the harder half of each batch, ascent on the easier half")
+    ap.add_argument("--duo", action="store_true", help="two models on complementary shares of each batch, merged at inference")
+    ap.add_argument("--duo-merge", default="mean", choices=DuoModel.MERGE_STRATEGIES)
+    ap.add_argument("--distill-adaptive", action="store_true", help="self-distillation with a per-sample teacher / label blend")
+    ap.add_argument("--ponder", action="store_true", help="train through the learned auxiliary loss (models/unified/ponder.py)")
+    ap.add_argument("--ponder-meta-lr", type=float, default=3e-4)
+    ap.add_argument("--ponder-reward-scale", type=float, default=100.0)
+    ap.add_argument("--ponder-min-supervised", type=float, default=0.0)
+    ap.add_argument("--ponder-meta-warmup", type=int, default=1)
+    ap.add_argument("--ponder-meta-wean", type=int, default=1)
+    # accepted for command-line compatibility with the reference harness; they have no effect here: data is always
+    # resident on the device (no loader workers, nothing to preload lazily) and nothing is traced or compiled
+    ap.add_argument("--workers", type=int, default=0, help=argparse.SUPPRESS)
+    ap.add_argument("--no-preload", dest="preload", action="store_false", help=argparse.SUPPRESS)
+    ap.add_argument("--compile", action="store_true", help=argparse.SUPPRESS)
     a = ap.parse_args(argv)
     dev = torch.device("cuda" if (a.device == "auto" and torch.cuda.is_available()) or a.device == "cuda" else "cpu")
     xa, ya, xb, yb, n_out, task_type, vocab, L = load_dataset(a.dataset, a.seq_len, a.num_train, a.num_test, a.seed, a.task_vocab_size)
@@ -451,10 +583,21 @@ def main(argv=None):
             if a.profile:
                 profile_one_batch(model, train, task_type, a.amp)
                 return results
+            if a.duo:
+                set_determinism(a.seed + run + 1000)
+                twin = build_model(kind, a.layers, n_out, L, num_channels=a.channels, kernel_size=a.kernel_size, attn_order=a.attn_order,
+                                   target_params=a.target_params, cross_layer=a.cross_layer, router_top_k=a.with_router,
+                                   jacobi_iters=a.jacobi_iters, siren_conv=a.siren_conv, vocab_size=vocab, per_token=task_type == "lm").to(dev)
+                model = DuoModel(model, twin, a.duo_merge)
+            if a.ponder and task_type != "lm":
+                accs.append(_train_with_ponder(model, train, test, a, dev, n_out))
+                continue
             hist = train_model(model, train, test, a.epochs, a.lr, task_type, cosine_start=a.cosine_start, swa=a.swa, swa_start=a.swa_start,
                                swa_lr=a.swa_lr, hard_mining=a.hard_mining, amp=a.amp, label_smoothing=a.label_smoothing, self_distill=a.self_distill,
                                distill_alpha=a.distill_alpha, distill_temp=a.distill_temp, distill_merge=a.distill_merge,
-                               distill_merge_alpha=a.distill_merge_alpha, checkpoint_dir=a.checkpoint_dir, model_name=kind)
+                               distill_merge_alpha=a.distill_merge_alpha, checkpoint_dir=a.checkpoint_dir, model_name=kind,
+                               hard_start=a.hard_start, hard_end=a.hard_end, first_epoch_pct=a.first_epoch_pct, wtf_mode=a.wtf_mode,
+                               distill_adaptive=a.distill_adaptive)
             accs.append(hist[-1]["test_acc"])
         results[kind] = dict(mean=float(np.mean(accs)), std=float(np.std(accs)), runs=accs)
         print(f"[{kind}] final test accuracy {results[kind]['mean']:.4f} +- {results[kind]['std']:.4f}", flush=True)

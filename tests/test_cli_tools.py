@@ -121,3 +121,26 @@ def test_bytemasker_and_joint_trainer_tool(tmp_path):
     j = train_bytemasker.main(["--joint", "--synthetic", "64", "--epochs", "1", "--width", "16", "--depth", "2", "--output", str(tmp_path / "j.pt"),
                                "--device", "cpu"])
     assert j["kind"] == "joint" and (tmp_path / "j.pt").exists()
+
+
+def test_scatter_harness_selection_duo_and_ponder_modes():
+    import torch
+
+    from ml_experiments_b200.cli import bench_scatter as B
+
+    per = torch.tensor([0.1, 2.0, 0.5, 1.0])
+    assert B.selection_weights(per, None).tolist() == [1, 1, 1, 1]
+    assert B.selection_weights(per, "top", 0.5).tolist() == [0, 1, 0, 1]
+    assert B.selection_weights(per, "easy", 0.5).tolist() == [1, 0, 1, 0]
+    assert B.selection_weights(per, "wtf").tolist() == [-1, 1, -1, 1]
+    assert abs(B.hard_fraction(0, 5, 0.5, 0.1) - 0.5) < 1e-9 and abs(B.hard_fraction(4, 5, 0.5, 0.1) - 0.1) < 1e-9
+    duo = B.DuoModel(torch.nn.Linear(4, 3), torch.nn.Linear(4, 3), "logsum")
+    merged, a, b = duo.forward_both(torch.randn(2, 4))
+    assert torch.allclose(merged, torch.log_softmax(a, -1) + torch.log_softmax(b, -1))
+    common = ["--model", "ripple", "--dataset", "random-image", "--layers", "1", "--num-train", "32", "--num-test", "16", "--batch-size", "16",
+              "--device", "cpu", "--target-params", "20000", "--seq-len", "64"]
+    for extra in (["--epochs", "2", "--hard-start", "0.5", "--hard-end", "0.25"], ["--epochs", "1", "--duo"],
+                  ["--epochs", "2", "--self-distill", "--distill-adaptive"], ["--epochs", "1", "--ponder"],
+                  ["--epochs", "1", "--first-epoch-pct", "0.3", "--workers", "2", "--compile"]):
+        r = B.main(common + extra)
+        assert 0.0 <= r["ripple"]["mean"] <= 1.0
