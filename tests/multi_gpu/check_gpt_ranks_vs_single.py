@@ -33,8 +33,7 @@ def main():
                     help="fused: peer-memory Muon + sharded Adam kernels; fused_allreduce: peer-memory Muon, bucket all-reduce + "
                          "replicated Adam; nccl: NCCL collectives")
     a = ap.parse_args()
-    if a.mode == "fused_allreduce":
-        os.environ["B200_SHARDED_ADAM"] = "0"
+    os.environ["B200_SHARDED_ADAM"] = "1" if a.mode == "fused" else "0"
     from ml_experiments_b200.ops.runtime import check_status
     from ml_experiments_b200.trainers.gpt_trainer import GPTTrainer, Hyperparameters, init_distributed, synthetic_batch
 
