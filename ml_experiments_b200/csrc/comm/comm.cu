@@ -4,6 +4,7 @@
 
 #include <cuda_bf16.h>
 
+#include <atomic>
 #include <stdexcept>
 #include <string>
 
@@ -425,15 +426,27 @@ void check(const char* what) {
 }
 
 int* device_counter() {
-  // one zero-initialised completion counter per device, shared by the kernels of this file (stream-ordered use)
-  static int* ctr[64] = {nullptr};
+  // One zero-initialised array of completion counters per device, shared by the kernels of this file (each kernel kind
+  // and each concurrent slot has its own entry). The zeroing must be COMPLETE before the first kernel that counts in it
+  // runs on whatever stream: a plain cudaMemset is queued on the legacy default stream, which a kernel on a non-blocking
+  // side stream does not wait for (it would count from uninitialised memory and never, or too early, announce
+  // completion). So the first call on a device zeroes the array and waits for the device once.
+  static std::atomic<int*> ctr[64];
   int dev = 0;
   cudaGetDevice(&dev);
-  if (!ctr[dev]) {
-    cudaMalloc(&ctr[dev], 64 * sizeof(int));
-    cudaMemset(ctr[dev], 0, 64 * sizeof(int));
+  if (dev < 0 || dev >= 64) dev = 0;
+  int* p = ctr[dev].load(std::memory_order_acquire);
+  if (!p) {
+    if (cudaMalloc(&p, 64 * sizeof(int)) != cudaSuccess) throw std::runtime_error("comm: cannot allocate the completion counters");
+    cudaMemset(p, 0, 64 * sizeof(int));
+    cudaDeviceSynchronize();
+    int* expected = nullptr;
+    if (!ctr[dev].compare_exchange_strong(expected, p, std::memory_order_acq_rel)) {
+      cudaFree(p);          // another host thread initialised this device first
+      p = expected;
+    }
   }
-  return ctr[dev];
+  return p;
 }
 
 }  // namespace

@@ -164,6 +164,78 @@ def bench_muon(w: SymmWorld, layers, d, iters, warmup, link_gbs, emit):
               fused_frac_of_roofline=round(roof / t_f, 3), gemm_peak=src, link_gbs=link_gbs))
 
 
+def bench_adam(w: SymmWorld, vocab: int, d: int, iters, warmup, link_gbs, emit):
+    """Embedding / head tables of the GPT-2 124M trainer (4 bf16 tables, 1 fp32 head): the fused sharded Adam (one kernel per
+    table: reduce-scatter + update + all-gather) against bucket all-reduce + replicated Adam kernel and against NCCL
+    reduce-scatter + torch Adam on the slice + all-gather."""
+    from ..optim.adam import FusedAdam
+    from .adam_dist import ShardedAdam
+
+    dev, W = w.device, w.world
+    mk = lambda dt: torch.nn.Parameter((torch.randn(vocab, d, device=dev) * 0.02).to(dt))
+    tables = [mk(torch.bfloat16) for _ in range(4)]
+    head = mk(torch.float32)
+    sharded = ShardedAdam([dict(params=[head], lr=0.008), dict(params=tables, lr=0.6)], w, betas=(0.8, 0.95), eps=1e-10)
+    for p in [head] + tables:
+        sharded.grad_views[id(p)].normal_(0, 1e-3)
+
+    def fused():
+        for p in [head] + tables:
+            p.grad = sharded.grad_views[id(p)]
+        sharded.step()
+
+    t_f = _timed(fused, iters, warmup, dev)
+    check_status()
+    # replicated: bucket all-reduce (two-shot peer kernel) + the Adam kernel on every rank
+    rep = [mk(torch.bfloat16) for _ in range(4)] + [mk(torch.float32)]
+    b16 = w.alloc(sum(p.numel() for p in rep[:4]) // (8 * W) * (8 * W), torch.bfloat16)
+    b32 = w.alloc(rep[4].numel() // (4 * W) * (4 * W), torch.float32)
+    b16.local.normal_(0, 1e-3)
+    b32.local.normal_(0, 1e-3)
+    off = 0
+    for p in rep[:4]:
+        p.grad = b16.local[off:off + p.numel()].view(p.shape) if off + p.numel() <= b16.local.numel() else torch.zeros_like(p)
+        off += p.numel()
+    rep[4].grad = b32.local[: rep[4].numel()].view(rep[4].shape) if rep[4].numel() <= b32.local.numel() else torch.zeros_like(rep[4])
+    opt = FusedAdam([dict(params=[rep[4]], lr=0.008), dict(params=rep[:4], lr=0.6)], betas=(0.8, 0.95), eps=1e-10)
+    o = ops()
+    ep = [0]
+
+    def replicated():
+        ep[0] += 1
+        e = 20_000_000 + ep[0]
+        for buf, code, ch in ((b16, 1, 2), (b32, 0, 4)):
+            o.comm_signal(w.flags.ptrs, w.rank, ch, e, w.flags.local)
+            o.allreduce_mean(buf.ptrs, w.rank, buf.local.numel(), code, w.flags.local, w.flags.ptrs, ch, e, status(dev))
+            o.comm_wait(w.flags.local, W, ch + 1, e, status(dev))
+        opt.step()
+
+    t_r = _timed(replicated, iters, warmup, dev)
+    check_status()
+    # NCCL: reduce-scatter, torch Adam on the slice, all-gather
+    ncc = []
+    for p in rep:
+        rows = p.shape[0] // W * W
+        g = torch.randn(rows, d, device=dev, dtype=p.dtype) * 1e-3
+        sl = torch.nn.Parameter(p.detach()[: rows // W].clone())
+        ncc.append(dict(g=g, gs=torch.empty(rows // W, d, device=dev, dtype=p.dtype), sl=sl, full=torch.empty(rows, d, device=dev, dtype=p.dtype)))
+    nopt = torch.optim.Adam([c["sl"] for c in ncc], lr=0.01, betas=(0.8, 0.95), eps=1e-10, fused=True)
+
+    def nccl():
+        for c in ncc:
+            dist.reduce_scatter_tensor(c["gs"], c["g"], op=dist.ReduceOp.AVG)
+            c["sl"].grad = c["gs"]
+        nopt.step()
+        for c in ncc:
+            dist.all_gather_into_tensor(c["full"], c["sl"].detach())
+
+    t_n = _timed(nccl, iters, warmup, dev)
+    byts = sum(p.numel() * p.element_size() for p in [head] + tables)
+    t_link = (W - 1) / W * byts / (link_gbs * 1e6) if W > 1 else 0.0       # per direction: gradients in, parameters out
+    emit(dict(bench="sharded_adam", world=W, tables_mbytes=round(byts / 2 ** 20, 1), fused_ms=round(t_f, 4), allreduce_plus_replicated_ms=round(t_r, 4),
+              nccl_ms=round(t_n, 4), roofline_ms=round(t_link, 4), fused_frac_of_roofline=round(t_link / t_f, 3) if W > 1 else None, link_gbs=link_gbs))
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--sizes-mb", default="1,16,128,512")
@@ -173,7 +245,7 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--link-gbs", type=float, default=770.0)
     ap.add_argument("--nvls", action="store_true", help="also time the NVSwitch-multicast (multimem) all-reduce")
-    ap.add_argument("--skip", default="", help="comma list of benches to skip (allreduce, muon_step)")
+    ap.add_argument("--skip", default="", help="comma list of benches to skip (allreduce, muon_step, sharded_adam)")
     a = ap.parse_args(argv)
     rank, world, local = (int(os.environ.get(k, d)) for k, d in (("RANK", 0), ("WORLD_SIZE", 1), ("LOCAL_RANK", 0)))
     torch.cuda.set_device(local)
@@ -186,6 +258,8 @@ def main(argv=None):
         bench_allreduce(w, [int(s) for s in a.sizes_mb.split(",")], a.iters, a.warmup, a.link_gbs, emit, a.nvls)
     if "muon_step" not in skip:
         bench_muon(w, a.layers, a.d_model, a.iters, a.warmup, a.link_gbs, emit)
+    if "sharded_adam" not in skip:
+        bench_adam(w, 50304, a.d_model, a.iters, a.warmup, a.link_gbs, emit)
     dist.barrier()
     dist.destroy_process_group()
 
