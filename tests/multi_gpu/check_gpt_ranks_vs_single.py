@@ -72,10 +72,12 @@ def main():
             rel = d / moved
             if rel > worst[1]:
                 worst = (n, rel)
-            if rel > 3e-2:
+            # Muon matrices that start at zero (the output projections) have moved only a few orthogonalised steps: bf16
+            # Newton-Schulz turns last-bit differences of the averaged gradient into a few percent of that small norm
+            if rel > (8e-2 if p.ndim >= 2 and "embed" not in n and "lm_head" not in n else 3e-2):
                 ok = False
         loss_gap = max(abs(u - v) for u, v in zip(mean_losses.tolist(), ref_losses))
-        ok = ok and loss_gap < 2e-2 and ref_losses[-1] < ref_losses[0]
+        ok = ok and loss_gap < 5e-3 and ref_losses[-1] < ref_losses[0]        # measured gap: 1e-4
         print(json.dumps({"mode": a.mode, "world": world, "ok": ok, "losses": mean_losses.tolist(), "single_losses": ref_losses,
                           "worst_param": worst[0], "worst_rel": worst[1]}), flush=True)
     flag = torch.tensor([1 if ok else 0], device=dev)
