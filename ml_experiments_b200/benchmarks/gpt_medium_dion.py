@@ -21,6 +21,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--optimizer", default="dion", choices=["dion", "muon"])
+    ap.add_argument("--ortho", default=None, choices=["ns", "cholqr", "qr"], help="Dion orthonormalisation (default: Newton-Schulz GEMMs on CUDA)")
     a = ap.parse_args()
     rank, world, local = init_dist()
     dev = torch.device("cuda", local)
@@ -30,14 +31,18 @@ def main():
     tr = GPTTrainer(cfg, Hyperparameters(seq_len=seq), device=dev, rank=rank, world_size=world, matrix_optimizer=a.optimizer)
     x, y = synthetic_batch(seq, seed=rank)
     x, y = x.to(dev), y.to(dev)
-    ms = timed_steps(lambda: tr.train_step(x, y, window=14), a.steps, a.warmup, world, dev)
+    if a.ortho and a.optimizer == "dion":
+        tr.optimizer2.ortho = a.ortho
+    losses = []
+    ms = timed_steps(lambda: losses.append(tr.train_step(x, y, window=14)), a.steps, a.warmup, world, dev)
     from ..ops.runtime import check_status
 
     check_status()
     emit(rank, metric=f"tokens/s GPT-2 medium {a.optimizer}", value=seq * world / (ms / 1e3), unit="tokens/s", ms_per_step=ms,
          n_gpus=world, config=dict(shape=a.shape, layers=cfg.num_layers, heads=cfg.num_heads, head_dim=cfg.head_dim,
-                                   tokens_per_rank=seq, optimizer=a.optimizer, comm=tr.comm_mode), dtype="bf16 (fp8 lm_head)",
-         data="synthetic")
+                                   tokens_per_rank=seq, optimizer=a.optimizer, comm=tr.comm_mode,
+                                   ortho=getattr(tr.optimizer2, "ortho", None)), dtype="bf16 (fp8 lm_head)",
+         data="synthetic", first_loss=float(losses[0]), final_loss=float(losses[-1]))
 
 
 if __name__ == "__main__":
