@@ -59,7 +59,9 @@ def main():
         except Exception:
             sw = None
         net = ddp = DistributedDataParallel(model, world=sw)
-    opt = torch.optim.AdamW(model.parameters(), lr=3e-4, weight_decay=0.01, fused=True)
+    from ..optim import FusedAdam          # this package's Adam kernel (decoupled weight decay), not a library optimizer
+
+    opt = FusedAdam(model.parameters(), lr=3e-4, weight_decay=0.01)
     if ddp is not None:
         ddp.wrap_optimizer(opt)
     g = torch.Generator().manual_seed(7 + rank)

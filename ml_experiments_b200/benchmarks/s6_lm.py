@@ -60,7 +60,9 @@ def main():
         except Exception:
             sw = None
         net = ddp = DistributedDataParallel(model, world=sw)
-    opt = torch.optim.AdamW(params, lr=3e-4, weight_decay=0.1, fused=True)
+    from ..optim import FusedAdam          # this package's Adam kernel (decoupled weight decay), not a library optimizer
+
+    opt = FusedAdam(params, lr=3e-4, weight_decay=0.1)
     if ddp is not None:
         ddp.wrap_optimizer(opt)
     g = torch.Generator().manual_seed(100 + rank)
