@@ -93,7 +93,7 @@ __device__ void block_done_then_signal(int* counter, const PeerPtrs& peer_flags,
 
 // grid (blocks per matrix, nmat)
 __global__ void __launch_bounds__(256)
-rs_momentum_kernel(PeerPtrs grads, int world, long long elem_off, long long mat_elems, float* __restrict__ mom,
+rs_momentum_kernel(PeerPtrs grads, int world, int rank, long long elem_off, long long mat_elems, float* __restrict__ mom,
                    bf16* __restrict__ u_out, float* __restrict__ sumsq, float mu, int nesterov, const int* flags,
                    int channel, int epoch, int* status) {
   __shared__ float red[8];
@@ -106,8 +106,8 @@ rs_momentum_kernel(PeerPtrs grads, int world, long long elem_off, long long mat_
   for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < mat_elems;
        i += (long long)gridDim.x * blockDim.x * 4) {
     float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int r = 0; r < world; ++r) {
-      const float4 v = __ldcg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[r]) + elem_off + base + i));
+    for (int r = 0; r < world; ++r) {   // starting after the own rank, so that the ranks pull from different peers at a time
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[(rank + 1 + r) % world]) + elem_off + base + i));
       g.x += v.x; g.y += v.y; g.z += v.z; g.w += v.w;
     }
     float4 b = *reinterpret_cast<float4*>(mom + base + i);
@@ -208,9 +208,13 @@ allreduce_kernel(PeerPtrs bufs, int world, int rank, long long lo, long long hi,
           const long long i = i0 + u * stride;
 #pragma unroll
           for (int r = 0; r < GRP; ++r)
-            if (r < nr && i < hi)
-              raw[u][r] = DT == 0 ? __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(bufs.p[r0 + r]) + i))
-                                  : __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(bufs.p[r0 + r]) + i));
+            if (r < nr && i < hi) {
+              // peers are walked starting after the own rank: at any moment the ranks pull from different GPUs instead
+              // of all from the same one (whose outbound links would be the bottleneck while the others idle)
+              const int src = (rank + 1 + r0 + r) % world;
+              raw[u][r] = DT == 0 ? __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(bufs.p[src]) + i))
+                                  : __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(bufs.p[src]) + i));
+            }
         }
 #pragma unroll
         for (int u = 0; u < UNR; ++u) {
@@ -239,13 +243,13 @@ allreduce_kernel(PeerPtrs bufs, int world, int rank, long long lo, long long hi,
         if (i >= hi) continue;
         if (DT == 0) {
           const float4 o = make_float4(a[u][0] * inv_w, a[u][1] * inv_w, a[u][2] * inv_w, a[u][3] * inv_w);
-          for (int r = 0; r < world; ++r) *reinterpret_cast<float4*>(reinterpret_cast<float*>(bufs.p[r]) + i) = o;
+          for (int r = 0; r < world; ++r) *reinterpret_cast<float4*>(reinterpret_cast<float*>(bufs.p[(rank + r) % world]) + i) = o;
         } else {
           uint4 o;
           __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
           for (int k = 0; k < 4; ++k) oh[k] = __floats2bfloat162_rn(a[u][2 * k] * inv_w, a[u][2 * k + 1] * inv_w);
-          for (int r = 0; r < world; ++r) *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(bufs.p[r]) + i) = o;
+          for (int r = 0; r < world; ++r) *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(bufs.p[(rank + r) % world]) + i) = o;
         }
       }
     }
@@ -470,7 +474,9 @@ void muon_rs_momentum(const PeerPtrs& grads, int world, long long elem_off, int 
   const int cap = (148 * 8 + nmat - 1) / nmat;
   if (bx > cap) bx = cap;
   if (bx < 1) bx = 1;
-  rs_momentum_kernel<<<dim3(bx, nmat), 256, 0, s>>>(grads, world, elem_off, mat_elems, mom, (bf16*)u_out_bf16, sumsq, mu,
+  // the owned slice starts at elem_off = rank * nmat * mat_elems: the rank only sets the order in which peers are read
+  const int rank = (int)((elem_off / ((long long)nmat * mat_elems)) % world);
+  rs_momentum_kernel<<<dim3(bx, nmat), 256, 0, s>>>(grads, world, rank, elem_off, mat_elems, mom, (bf16*)u_out_bf16, sumsq, mu,
                                                      nesterov, flags, channel, epoch, status);
   check("muon_rs_momentum");
 }

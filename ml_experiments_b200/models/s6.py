@@ -81,13 +81,17 @@ class S6Mixer(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:  # (B, L, d_model)
         cfg = self.cfg
         L = x.shape[1]
-        xz = linear(x, self.in_proj.weight)
-        xi, z = xz.chunk(2, dim=-1)
+        # the two halves of in_proj as two GEMMs on row slices of its weight: the scan needs x and the gate z as separate
+        # contiguous tensors, and one wide GEMM would cost a strided-to-contiguous copy of each half in the forward and a
+        # concatenation of their gradients in the backward
+        di = cfg.d_inner
+        xi = linear(x, self.in_proj.weight[:di])
+        z = linear(x, self.in_proj.weight[di:])
         xi = causal_conv1d_silu(xi, self.conv1d.weight, self.conv1d.bias)
         dbc = linear(xi, self.x_proj.weight)
         dt, Bm, Cm = torch.split(dbc, [cfg.rank, cfg.d_state, cfg.d_state], dim=-1)
         y = selective_scan(xi.contiguous(), linear(dt, self.dt_proj.weight), -torch.exp(self.A_log.float()), Bm, Cm, self.D,
-                           z.contiguous(), delta_bias=self.dt_proj.bias, delta_softplus=True)
+                           z, delta_bias=self.dt_proj.bias, delta_softplus=True)
         return linear(y, self.out_proj.weight)
 
 
