@@ -7,7 +7,8 @@
 //     G  = C B^T                                  (128 x 128, K = N)          tcgen05.mma  #1
 //     M  = G o [j <= i] exp(cs_i - cs_j) w_ij     (threads: TMEM -> registers -> bf16 -> shared memory)
 //     Y  = M x                                    (128 x P,   K = 128)        tcgen05.mma  #2
-//     Z  = C S_prev                               (128 x P,   K = N)          tcgen05.mma  #3   (state of the previous chunks)
+//     Z  = C S_prev                               (128 x P,   K = N)          tcgen05.mma  #3   (state of the previous chunks;
+//                                                                                  issued after M is built, into G's columns)
 //     y_i = Y_i + exp(cs_i) Z_i                   (epilogue)
 //     S  = exp(cs_end) S + (B o exp(cs_end - cs_j) w_j)^T x      (N x P, K = 128, accumulated in TMEM)   tcgen05.mma  #4
 // One CTA owns one (b, h) and walks its chunks in order, so the state never leaves the chip: fp32 in tensor memory for
@@ -54,7 +55,7 @@ __device__ __forceinline__ void cta_wait(uint64_t* bar, uint32_t parity, volatil
 
 // 128 threads: thread t owns time step t of the chunk (rows of G / M / Y / Z) and, for t < N, row t of the state.
 template <int N, int P>
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(128, (128 + 2 * P) <= 256 ? 2 : 1)
 ssd_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const SsdParams p) {
   constexpr int Q = 128;
@@ -64,8 +65,10 @@ ssd_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   constexpr int X_BYTES = NSP * Q * 128;           // x chunk  [Q][P]  (MN-major B of #2 and #4)
   constexpr int M_BYTES = 2 * Q * 128;             // M        [Q][Q]  (K-major A of #2)
   constexpr int S_BYTES = NSP * N * 128;           // state    [N][P]  bf16 (MN-major B of #3)
-  constexpr uint32_t G_COL = 0, Y_COL = 128, Z_COL = 128 + P, S_COL = 128 + 2 * P;
-  constexpr uint32_t TMEM_COLS = 512;
+  // Z = C S_prev reuses the columns of G: G has been read into registers (to build M) before #3 is issued. With P = 64
+  // that makes 256 tensor-memory columns per CTA, so two CTAs share an SM and hide each other's load / barrier latency.
+  constexpr uint32_t G_COL = 0, Z_COL = 0, Y_COL = 128, S_COL = 128 + P;
+  constexpr uint32_t TMEM_COLS = (128 + 2 * P) <= 256 ? 256 : 512;
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -81,8 +84,8 @@ ssd_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   float* s_g = s_warp + 4;                                   // [128] off-diagonal weights g_off of the chunk
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_g + Q);
   uint64_t* bar_load = bars;       // C, B, x of the current chunk have landed
-  uint64_t* bar_g = bars + 1;      // #1 and #3 done
-  uint64_t* bar_y = bars + 2;      // #2 and #4 done
+  uint64_t* bar_g = bars + 1;      // #1 done
+  uint64_t* bar_y = bars + 2;      // #2, #3 and #4 done
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -161,14 +164,6 @@ ssd_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         const uint64_t ad = make_smem_desc_sw128(ca + (ks / 4) * (Q * 128) + (ks % 4) * 32, 16, 1024);
         const uint64_t bd = make_smem_desc_sw128(ba + (ks / 4) * (Q * 128) + (ks % 4) * 32, 16, 1024);
         tc_mma_f16(tmem_base + G_COL, ad, bd, idesc_g, ks != 0);
-      }
-      if (have_state) {
-#pragma unroll
-        for (int ks = 0; ks < N / 16; ++ks) {   // #3: Z = C S_prev
-          const uint64_t ad = make_smem_desc_sw128(ca + (ks / 4) * (Q * 128) + (ks % 4) * 32, 16, 1024);
-          const uint64_t bd = make_smem_desc_sw128(sa + ks * 2048, N * 128, 1024);
-          tc_mma_f16(tmem_base + Z_COL, ad, bd, idesc_y, ks != 0);
-        }
       }
       tc_commit(bar_g);
     }
@@ -260,6 +255,14 @@ ssd_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         const uint64_t ad = make_smem_desc_sw128(ma + (ks / 4) * (Q * 128) + (ks % 4) * 32, 16, 1024);
         const uint64_t bd = make_smem_desc_sw128(xa + ks * 2048, Q * 128, 1024);
         tc_mma_f16(tmem_base + Y_COL, ad, bd, idesc_y, ks != 0);
+      }
+      if (have_state) {
+#pragma unroll
+        for (int ks = 0; ks < N / 16; ++ks) {   // #3: Z = C S_prev (into the columns G occupied)
+          const uint64_t ad = make_smem_desc_sw128(ca + (ks / 4) * (Q * 128) + (ks % 4) * 32, 16, 1024);
+          const uint64_t bd = make_smem_desc_sw128(sa + ks * 2048, N * 128, 1024);
+          tc_mma_f16(tmem_base + Z_COL, ad, bd, idesc_y, ks != 0);
+        }
       }
 #pragma unroll
       for (int ks = 0; ks < Q / 16; ++ks) {   // #4: S += (B o w)^T x

@@ -26,11 +26,10 @@ def _lib():
     return lib
 
 
-def _case(seed, t, h, doc_len, window):
+def _case(seed, t, h, doc_len, window, d=128):
     from ml_experiments_b200.ops import attention as A
 
     torch.manual_seed(seed)
-    d = 128
     qkv = torch.randn(t, 3, h, d, device="cuda", dtype=torch.bfloat16)
     q, k, v = qkv[:, 0], qkv[:, 1], qkv[:, 2]
     starts = torch.zeros(t, dtype=torch.bool, device="cuda")
@@ -71,6 +70,26 @@ def test_noalloc_matches_regular_backward_twice():
         for name, g, w in zip(("dq", "dk", "dv"), got, want):
             rel = ((g.float() - w.float()).norm() / w.float().norm()).item()
             assert rel < 2e-2, (name, rel)
+
+
+def test_noalloc_head_dim_64():
+    """The entry point takes both head sizes of the kernel; any other is refused with an argument error."""
+    from ml_experiments_b200.ops import attention as A
+    from ml_experiments_b200.ops.runtime import check_status
+
+    lib = _lib()
+    q, k, v, o, lse, d_o, ds, de = _case(2, 1024, 4, 512, 0, d=64)
+    want = A.flash_attention_backward(q, k, v, o, d_o, lse, ds, de, 0.12, 0)
+    got = _call(lib, q, k, v, o, lse, d_o, ds, de, 0)
+    torch.cuda.synchronize()
+    check_status()
+    for name, g, w in zip(("dq", "dk", "dv"), got, want):
+        rel = ((g.float() - w.float()).norm() / w.float().norm()).item()
+        assert rel < 2e-2, (name, rel)
+    z = torch.zeros(8, device="cuda")
+    p = z.data_ptr()
+    rc = lib.b200_attn_bwd_noalloc(p, p, p, p, p, p, p, p, p, p, p, 128, 1, 96, 1, 1, 1, 1, 1, 1, 1, 1, 0.1, 0, None, None)
+    assert rc == -1 and b"head_dim" in lib.b200_attn_bwd_noalloc_error()
 
 
 def test_noalloc_rejects_oversized_problem():
