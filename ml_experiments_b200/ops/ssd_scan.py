@@ -85,13 +85,17 @@ def _exclusive_state_pass(log_a, s, s0=None, block: int = 64):
 
 
 def kernel_supported(x, B, C) -> bool:
+    """True when the tcgen05 kernel takes this call: CUDA, supported shapes, and bf16 compute asked for (bf16 inputs, or
+    fp32 / fp16 inputs inside a bf16 autocast region: the operands are then rounded to bf16 for the tensor cores, the
+    state and all accumulations stay fp32)."""
     import os
 
-    if not (x.is_cuda and x.dtype == torch.bfloat16 and os.environ.get("B200_SSD_KERNEL", "1") == "1"):
+    if not x.is_cuda or os.environ.get("B200_SSD_KERNEL", "1") != "1" or B.shape != C.shape or x.dim() != 4 or B.dim() != 4:
         return False
+    bf16_compute = x.dtype == torch.bfloat16 or (torch.is_autocast_enabled() and torch.get_autocast_gpu_dtype() == torch.bfloat16)
     b, L, H, P = x.shape
     Hb = B.shape[2]
-    return L % 128 == 0 and B.shape[-1] in (64, 128) and P in (64, 128) and H % Hb == 0 and B.shape == C.shape
+    return bf16_compute and L % 128 == 0 and B.shape[-1] in (64, 128) and P in (64, 128) and Hb > 0 and H % Hb == 0
 
 
 def _fold_weights(log_alpha, gamma, beta):
@@ -110,6 +114,8 @@ def ssd_forward_kernel(x, B, C, log_alpha, gamma, beta=None, init_state=None, re
     from .runtime import ops, status
 
     g_off, g_diag = _fold_weights(log_alpha, gamma, beta)
+    out_dtype = x.dtype
+    x, B, C = (t if t.dtype == torch.bfloat16 else t.to(torch.bfloat16) for t in (x, B, C))
     y = torch.empty_like(x)
     b, L, H, P = x.shape
     N = B.shape[-1]
@@ -117,6 +123,8 @@ def ssd_forward_kernel(x, B, C, log_alpha, gamma, beta=None, init_state=None, re
     init = None if init_state is None else init_state.float().contiguous()
     ops().ssd_fwd(x.contiguous(), B.contiguous(), C.contiguous(), log_alpha.float().contiguous(), g_off, g_diag, y, init, fin,
                   status(x.device))
+    if y.dtype != out_dtype:
+        y = y.to(out_dtype)
     return (y, fin) if return_state else y
 
 
@@ -154,7 +162,7 @@ def ssd_chunk_scan(x, B, C, log_alpha, gamma, beta=None, chunk: int = 64, init_s
     ``x [b,L,H,P]``; ``B, C [b,L,H,N]`` (a size-1 head dim broadcasts: grouped B/C); ``log_alpha, gamma, beta [b,L,H]``.
     Returns ``y [b,L,H,P]`` (and the final state ``[b,H,N,P]`` if ``return_state``).
     """
-    if kernel_supported(x, B, C) and B.dtype == torch.bfloat16 and C.dtype == torch.bfloat16:
+    if kernel_supported(x, B, C):
         y, st = _SsdKernelFn.apply(x, B, C, log_alpha, gamma, beta, init_state, return_state)
         return (y, st) if return_state else y
     return _ssd_chunk_scan_torch(x, B, C, log_alpha, gamma, beta, chunk, init_state, return_state)

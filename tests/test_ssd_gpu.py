@@ -53,3 +53,17 @@ def test_autograd_path_and_fallback_agree():
     assert (y.float() - y2.float()).abs().max() < 3e-2 * y2.float().abs().max()
     for a, r in zip(leaves, ref_leaves):
         assert a.grad is not None and torch.allclose(a.grad.float(), r.grad.float(), rtol=1e-3, atol=1e-5)
+
+
+def test_fp32_inputs_take_the_kernel_only_under_bf16_autocast():
+    from ml_experiments_b200.ops.ssd_scan import _ssd_chunk_scan_torch, kernel_supported, ssd_chunk_scan
+
+    x, B, C, la, g, bt = _inputs(1, 256, 2, 2, 64, 64, True, seed=5)
+    x, B, C = x.float(), B.float(), C.float()
+    assert not kernel_supported(x, B, C)
+    ref = _ssd_chunk_scan_torch(x, B, C, la, g, bt)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        assert kernel_supported(x, B, C)
+        y = ssd_chunk_scan(x, B, C, la, g, bt)
+    assert y.dtype == x.dtype
+    assert (y - ref).abs().max() < 3e-2 * ref.abs().max()
