@@ -179,6 +179,7 @@ def run_ours(args, rank, local, world):
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
             "gpu_launches": launches,
             "first_loss": first_loss, "final_loss": losses[-1] if losses else None,
+            "e2e_loss_min_max": [min(losses), max(losses)] if losses else None,
         }), flush=True)
     # a run whose loss never moved (or is not finite) did not train: fail loudly instead of reporting a throughput
     final = losses[-1] if losses else float("nan")
