@@ -274,3 +274,27 @@ def test_analysis_tables_and_wall_clock(tmp_path):
     table = W.wall_clock_table(("mamba1", "mamba2", "attention", "gla", "long_conv"), (32,), batch=1, heads=2, head_dim=8, dstate=8, iters=1, warmup=0,
                                backward=True, device="cpu")
     assert table[0]["seq_len"] == 32 and all(table[0][k] > 0 for k in W.OPERATORS)
+
+
+def test_example_sweeps_build_train_configs(tmp_path, monkeypatch):
+    """The ready-made sweeps yield one config per (model, learning rate); a shrunken one trains through the harness."""
+    from ml_experiments_b200.zoology.experiments import mqar_examples as E
+    assert len(E.configs) == 1 and len(E.basic_sweep()) == 4
+    sweep = E.mqar_sweep(families=("attention", "mamba2"), scale=1e-3)
+    assert len({c.sweep_id for c in sweep}) == 1 and len(sweep) % 4 == 0
+    assert [s.num_kv_pairs for s in sweep[0].data.train_configs] == [4, 8, 16, 32, 64]
+    assert max(s.input_seq_len for s in sweep[0].data.test_configs) == 1024 and sweep[0].slice_keys == ["num_kv_pairs"]
+    forget = E.forgetting_sweep(families=("attention",), scale=1e-3)
+    assert isinstance(forget[0].data.train_configs[0], ForgettingMQARConfig) and forget[0].data.test_configs[-1].input_seq_len == 2048
+    comp = E.composition_sweep(families=("based",), scale=1e-3)
+    assert isinstance(comp[0].data.train_configs[0], CompositionalMQARConfig)
+    circ = E.circuits_sweep("majority", seq_lens=(8, 16), families=("attention",), num_train=16, num_test=8)
+    assert circ and circ[0].model.vocab_size == 3 and circ[0].slice_keys == ["input_seq_len"]
+    # a tiny instance of the multi-length sweep steps through the trainer
+    from ml_experiments_b200.zoology.train import train
+    monkeypatch.chdir(tmp_path)
+    tiny = E.mqar_sweep(families=("attention",), lrs=[1e-3], max_epochs=1, batch_size=8, vocab_size=64,
+                        train=((16, 16, 2),), test=((16, 8, 2),))
+    c = min(tiny, key=lambda t: t.model.d_model)
+    c.data.cache_dir = str(tmp_path)
+    train(c)
