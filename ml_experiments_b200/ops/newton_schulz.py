@@ -41,7 +41,11 @@ def newton_schulz_torch(G_: torch.Tensor, coeffs=NS5_COEFFS, eps: float = 1e-7, 
 def newton_schulz_(X: torch.Tensor, coeffs=NS5_COEFFS, work: dict | None = None) -> torch.Tensor:
     """Orthogonalises the batch ``X [B, r, c]`` (bf16, CUDA, already divided by its Frobenius norm).
 
-    Returns a tensor holding the result (either ``X`` or the ping-pong buffer kept in ``work``)."""
+    Returns a tensor holding the result: the ping-pong buffer kept in ``work`` after an odd number of iterations, ``X``
+    itself after an even number. ``X`` is overwritten either way. The ping-pong buffer of a ``work`` dict never changes
+    identity, so a caller that passes the same ``X`` every step never meets a GEMM whose output aliases its operand
+    (handing the buffers back swapped would make the second call run ``X <- a X + B X`` in place: tiles of ``X`` that
+    other CTAs still have to read would be overwritten)."""
     assert X.is_cuda and X.dtype == torch.bfloat16 and X.dim() == 3
     bsz, r, c = X.shape
     wide = r <= c
@@ -54,6 +58,7 @@ def newton_schulz_(X: torch.Tensor, coeffs=NS5_COEFFS, work: dict | None = None)
                 torch.empty(bsz, n, n, dtype=torch.bfloat16, device=X.device), torch.empty_like(X))
         work[key] = bufs
     A, Bm, X2 = bufs
+    assert X2.data_ptr() != X.data_ptr(), "newton_schulz_: X must not be the work dict's own ping-pong buffer"
     for a_, b_, c_ in coeffs:
         if wide:
             G.gemm(X, X, out=A)
@@ -65,7 +70,6 @@ def newton_schulz_(X: torch.Tensor, coeffs=NS5_COEFFS, work: dict | None = None)
         else:
             G.gemm(X, Bm, out=X2, epilogue=G.EPI_AXPBY, aux=X, alpha=1.0, beta=a_)
         X, X2 = X2, X
-    work[key] = (A, Bm, X2)
     return X
 
 

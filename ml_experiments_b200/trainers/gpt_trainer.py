@@ -174,7 +174,7 @@ class GPTTrainer:
         for opt in self.optimizers:
             for g in opt.param_groups:
                 g["lr"] = g["initial_lr"] * lr_mul
-        if self.sharded_adam and len(micro) == 1:
+        if self.sharded_adam and len(micro) == 1 and os.environ.get("B200_ADAM_EARLY", "1") == "1":
             self.model._grad_hooks = {id(self.model.lm_head.weight): self._head_grad_ready}
         loss = None
         for x, y in micro:
