@@ -106,7 +106,7 @@ class GPTTrainer:
 
                     sw = SymmWorld.create(rank, world_size, self.device)
                     self.optimizer2 = md.FusedDistMuon(hidden, sw, lr=hp_.muon_lr, momentum=hp_.muon_momentum)
-                    if os.environ.get("B200_SHARDED_ADAM", "0") == "1":     # opt-in until validated on real multi-GPU runs
+                    if os.environ.get("B200_SHARDED_ADAM", "1") == "1":     # "0": bucket all-reduce + replicated Adam instead
                         # Adam state sharded over the ranks; reduce-scatter, update and all-gather are one kernel per
                         # table, the head's launched from backward as soon as its gradient exists
                         from ..parallel.adam_dist import ShardedAdam
