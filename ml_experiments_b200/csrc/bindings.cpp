@@ -14,6 +14,7 @@
 #include "gemm/gemm.h"
 #include "mra/mra.h"
 #include "scan/s6_scan.h"
+#include "scan/jacobi.h"
 #include "scan/ssd.h"
 #include "window/window_attn.h"
 #include "wkv/wkv.h"
@@ -437,6 +438,71 @@ void s6_set_states_per_thread(int64_t fwd_qs, int64_t bwd_qs, const Tensor& like
   b200::s6_set_states_per_thread((int)fwd_qs, (int)bwd_qs);
 }
 
+static void jacobi_fill(b200::JacobiArgs& a, const Tensor& Bm, const Tensor& Cm, const Tensor& theta, const Tensor& xr, const Tensor& alpha,
+                        const Tensor& gamma, const Tensor& conv_w, const Tensor& conv_b, const c10::optional<Tensor>& inj_lambda,
+                        const c10::optional<Tensor>& ro_lambda, int64_t n_iters) {
+  TORCH_CHECK(Bm.dim() == 4 && Cm.dim() == 4 && Bm.sizes() == Cm.sizes(), "jacobi: B / C maps [batch, R, L, N] (any strides)");
+  a.batch = (int)Bm.size(0); a.R = (int)Bm.size(1); a.L = (int)Bm.size(2); a.N = (int)Bm.size(3); a.n_iters = (int)n_iters;
+  const int64_t rows = (int64_t)a.batch * a.L;
+  for (const Tensor* t : {&Bm, &Cm, &theta, &xr, &alpha, &gamma, &conv_w, &conv_b})
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kFloat, "jacobi: fp32 CUDA tensors");
+  TORCH_CHECK(theta.is_contiguous() && theta.numel() == rows * (a.N / 2), "jacobi: theta [batch, L, N/2] contiguous");
+  TORCH_CHECK(alpha.is_contiguous() && alpha.numel() == rows * a.N, "jacobi: alpha [batch, L, N] contiguous");
+  TORCH_CHECK(gamma.is_contiguous() && gamma.numel() == rows, "jacobi: gamma [batch, L] contiguous");
+  TORCH_CHECK(xr.dim() == 3 && xr.size(0) == a.batch && xr.size(1) == a.R && xr.size(2) == a.L, "jacobi: x_r [batch, R, L] (any strides)");
+  TORCH_CHECK(conv_w.is_contiguous() && conv_w.numel() == 3 * a.N && conv_b.is_contiguous() && conv_b.numel() == a.N, "jacobi: taps [N, 3], bias [N]");
+  a.Bm = Bm.data_ptr<float>(); a.b_sb = Bm.stride(0); a.b_sr = Bm.stride(1); a.b_sl = Bm.stride(2); a.b_sn = Bm.stride(3);
+  a.Cm = Cm.data_ptr<float>(); a.c_sb = Cm.stride(0); a.c_sr = Cm.stride(1); a.c_sl = Cm.stride(2); a.c_sn = Cm.stride(3);
+  a.theta = theta.data_ptr<float>(); a.alpha = alpha.data_ptr<float>(); a.gamma = gamma.data_ptr<float>();
+  a.xr = xr.data_ptr<float>(); a.x_sb = xr.stride(0); a.x_sr = xr.stride(1); a.x_sl = xr.stride(2);
+  a.conv_w = conv_w.data_ptr<float>(); a.conv_b = conv_b.data_ptr<float>();
+  auto scalar = [](const c10::optional<Tensor>& t) -> const float* {
+    if (!t.has_value()) return nullptr;
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kFloat && t->numel() == 1, "jacobi: mix weights are fp32 device scalars");
+    return t->data_ptr<float>();
+  };
+  a.inj_lambda = scalar(inj_lambda); a.ro_lambda = scalar(ro_lambda);
+  a.stream = cur_stream();
+}
+
+void jacobi_fwd(const Tensor& Bm, const Tensor& Cm, const Tensor& theta, const Tensor& xr, const Tensor& alpha, const Tensor& gamma,
+                const Tensor& conv_w, const Tensor& conv_b, const c10::optional<Tensor>& inj_lambda, const c10::optional<Tensor>& ro_lambda,
+                int64_t n_iters, Tensor gated, const c10::optional<Tensor>& Hs) {
+  const c10::cuda::CUDAGuard guard(Bm.device());
+  b200::JacobiArgs a;
+  jacobi_fill(a, Bm, Cm, theta, xr, alpha, gamma, conv_w, conv_b, inj_lambda, ro_lambda, n_iters);
+  const int64_t state = (int64_t)a.batch * a.R * a.L * a.N;
+  TORCH_CHECK(gated.scalar_type() == at::kFloat && gated.is_contiguous() && gated.numel() == state, "jacobi_fwd: gated fp32 [batch, L, R * N]");
+  a.gated = gated.data_ptr<float>();
+  if (Hs.has_value()) {
+    TORCH_CHECK(Hs->scalar_type() == at::kFloat && Hs->is_contiguous() && Hs->numel() == state * n_iters, "jacobi_fwd: states fp32 [n_iters, batch, R, L, N]");
+    a.Hs = Hs->data_ptr<float>();
+  }
+  b200::jacobi_fwd(a);
+}
+
+void jacobi_bwd(const Tensor& dgated, const Tensor& Hs, const Tensor& Bm, const Tensor& Cm, const Tensor& theta, const Tensor& xr,
+                const Tensor& alpha, const Tensor& gamma, const Tensor& conv_w, const Tensor& conv_b, const c10::optional<Tensor>& inj_lambda,
+                const c10::optional<Tensor>& ro_lambda, int64_t n_iters, Tensor dBm, Tensor dCm, Tensor dtheta, Tensor dxr, Tensor dalpha,
+                Tensor dgamma, Tensor dconv_w, Tensor dconv_b, Tensor dlam) {
+  const c10::cuda::CUDAGuard guard(Bm.device());
+  b200::JacobiArgs a;
+  jacobi_fill(a, Bm, Cm, theta, xr, alpha, gamma, conv_w, conv_b, inj_lambda, ro_lambda, n_iters);
+  const int64_t state = (int64_t)a.batch * a.R * a.L * a.N, rows = (int64_t)a.batch * a.L;
+  auto out = [](Tensor& t, int64_t n, const char* what) -> float* {
+    TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kFloat && t.is_contiguous() && t.numel() == n, "jacobi_bwd: ", what);
+    return t.data_ptr<float>();
+  };
+  TORCH_CHECK(dgated.scalar_type() == at::kFloat && dgated.is_contiguous() && dgated.numel() == state, "jacobi_bwd: dgated fp32 [batch, L, R * N]");
+  TORCH_CHECK(Hs.scalar_type() == at::kFloat && Hs.is_contiguous() && Hs.numel() == state * n_iters, "jacobi_bwd: states fp32 [n_iters, batch, R, L, N]");
+  a.dgated = dgated.data_ptr<float>(); a.Hs = const_cast<float*>(Hs.data_ptr<float>());
+  a.dBm = out(dBm, state, "dB [batch, R, L, N]"); a.dCm = out(dCm, state, "dC [batch, R, L, N]");
+  a.dtheta = out(dtheta, rows * (a.N / 2), "dtheta"); a.dxr = out(dxr, rows * a.R, "dx_r [batch, R, L]");
+  a.dalpha = out(dalpha, rows * a.N, "dalpha"); a.dgamma = out(dgamma, rows, "dgamma");
+  a.dconv_w = out(dconv_w, 3 * a.N, "dtaps"); a.dconv_b = out(dconv_b, a.N, "dbias"); a.dlam = out(dlam, 2, "dlam [2]");
+  b200::jacobi_bwd(a);
+}
+
 bool ssd_fwd_supported(int64_t L, int64_t H, int64_t Hb, int64_t N, int64_t P) {
   return b200::ssd_fwd_supported((int)L, (int)H, (int)Hb, (int)N, (int)P);
 }
@@ -774,6 +840,8 @@ TORCH_LIBRARY(b200, m) {
   m.def("allreduce_mean_multimem(int mc_ptr, int world, int rank, int n, int dtype, Tensor flags, int[] peer_flags, int channel, int epoch, Tensor(a!) status) -> ()");
   m.def("allreduce_mean(int[] buf_ptrs, int rank, int n, int dtype, Tensor flags, int[] peer_flags, int channel, int epoch, Tensor(a!) status) -> ()");
   m.def("s6_set_states_per_thread(int fwd_qs, int bwd_qs, Tensor like) -> ()");
+  m.def("jacobi_fwd(Tensor Bm, Tensor Cm, Tensor theta, Tensor xr, Tensor alpha, Tensor gamma, Tensor conv_w, Tensor conv_b, Tensor? inj_lambda, Tensor? ro_lambda, int n_iters, Tensor(a!) gated, Tensor(b!)? Hs) -> ()");
+  m.def("jacobi_bwd(Tensor dgated, Tensor Hs, Tensor Bm, Tensor Cm, Tensor theta, Tensor xr, Tensor alpha, Tensor gamma, Tensor conv_w, Tensor conv_b, Tensor? inj_lambda, Tensor? ro_lambda, int n_iters, Tensor(a!) dBm, Tensor(b!) dCm, Tensor(c!) dtheta, Tensor(d!) dxr, Tensor(e!) dalpha, Tensor(f!) dgamma, Tensor(g!) dconv_w, Tensor(h!) dconv_b, Tensor(i!) dlam) -> ()");
   m.def("ssd_fwd(Tensor x, Tensor B, Tensor C, Tensor log_a, Tensor g_off, Tensor g_diag, Tensor(a!) y, Tensor? init_state, Tensor(b!)? final_state, Tensor(c!) status) -> ()");
   m.def("s6_scan_fwd(Tensor u, Tensor delta, Tensor? delta_bias, bool softplus, Tensor A, Tensor Bm, Tensor Cm, Tensor? Dv, Tensor? z, Tensor(a!)? y_pre, Tensor(b!) out, Tensor(c!)? state) -> ()");
   m.def("s6_scan_bwd(Tensor u, Tensor delta, Tensor? delta_bias, bool softplus, Tensor A, Tensor Bm, Tensor Cm, Tensor? Dv, Tensor? z, Tensor? y_pre, Tensor dout, Tensor state, Tensor(a!) du, Tensor(b!) ddelta, Tensor(c!) dA, Tensor(d!) dB_part, Tensor(e!) dC_part, Tensor(f!)? dD, Tensor(g!)? dz, Tensor(h!)? ddelta_bias) -> ()");
@@ -831,6 +899,8 @@ TORCH_LIBRARY_IMPL(b200, CUDA, m) {
   m.impl("allreduce_mean", &allreduce_mean);
   m.impl("s6_set_states_per_thread", &s6_set_states_per_thread);
   m.impl("ssd_fwd", &ssd_fwd);
+  m.impl("jacobi_fwd", &jacobi_fwd);
+  m.impl("jacobi_bwd", &jacobi_bwd);
   m.impl("s6_scan_fwd", &s6_scan_fwd);
   m.impl("s6_scan_bwd", &s6_scan_bwd);
   m.impl("causal_conv1d_silu_fwd", &causal_conv1d_silu_fwd);

@@ -134,8 +134,18 @@ class MIMOJacobiSSM_ND(nn.Module):
         return (H, inject), self._readout(H, Cm)
 
     def forward(self, x):
+        proj = self._project(x)
+        if x.is_cuda and self.ndim == 1 and x.dim() == 3 and self.diffuse_se is None:
+            # 1-D grids without the squeeze-excite (a global mean per iteration) run every iteration in one kernel
+            from ..ops.jacobi_iter import jacobi_iterate, kernel_supported
+            if kernel_supported(self.N, self.n_iters):
+                Bm, Cm, theta, xr, alpha, gamma = proj
+                gated = jacobi_iterate(Bm, Cm, theta.squeeze(1), xr.squeeze(-1), alpha.squeeze(1), gamma.squeeze(1).squeeze(-1),
+                                       self.diffuse.weight, self.diffuse.bias, self.inject_lambda if self.diff_inject else None,
+                                       self.readout_lambda if self.diff_readout else None, self.n_iters)
+                return self.act(self.out_proj(gated))
         H, prev = self.init_state(x)
-        Cm, proj = None, self._project(x)
+        Cm = None
         for it in range(self.n_iters):
             H, prev, Cm = self._iterate(x, H, prev, it, proj)
         return self._readout(H, Cm)

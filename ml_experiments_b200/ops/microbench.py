@@ -52,7 +52,7 @@ def _doc_bounds(t: int, doc_len: int):
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("op", choices=["gemm", "attn_fwd", "attn_bwd", "softcap_ce", "s6_fwd", "s6_bwd", "gather_fwd", "gather_bwd",
-                                   "newton_schulz", "ssd", "tele_fwd", "tele_bwd", "alc_fwd", "alc_bwd", "rms_act"])
+                                   "newton_schulz", "ssd", "jacobi", "jacobi_bwd", "tele_fwd", "tele_bwd", "alc_fwd", "alc_bwd", "rms_act"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -187,6 +187,30 @@ def main(argv=None):
         fn = lambda: newton_schulz_(X.clone(), work=work)
         small, big = min(a.m, a.n), max(a.m, a.n)
         flops = 5 * a.batch * (2.0 * small * small * big * 2 + 2.0 * small ** 3)
+    elif a.op in ("jacobi", "jacobi_bwd"):
+        # MIMO-Jacobi iteration (state 64, rank 4, 12 iterations) on [batch, seq]: fused kernel against the PyTorch loop
+        from .jacobi_iter import jacobi_iterate, jacobi_iterate_torch
+        b, L, R, n, iters_ = a.batch, a.seq, 4, 64, 12
+        mk = lambda *s: torch.randn(*s, device=dev)
+        args = [mk(b, L, n, R).permute(0, 3, 1, 2), mk(b, L, n, R).permute(0, 3, 1, 2), mk(b, L, n // 2), mk(b, L, R).permute(0, 2, 1),
+                torch.sigmoid(mk(b, L, n)), torch.sigmoid(mk(b, L)), mk(n, 3) * 0.4, mk(n) * 0.1]
+        train = a.op == "jacobi_bwd"
+        if train:
+            args = [t.requires_grad_(True) for t in args]
+
+        def run(f):
+            if not train:
+                with torch.no_grad():
+                    return f(*args, None, None, iters_)
+            y = f(*args, None, None, iters_)
+            y.backward(torch.ones_like(y))
+            return y
+        torch_ms = _time(lambda: run(jacobi_iterate_torch), max(a.iters // 4, 2), 1)
+        fn = lambda: run(jacobi_iterate)
+        state = b * R * L * n * 4.0
+        # forward: B, C in, gated out (+ the n saved states when training); backward: the saved states, dgated, dB, dC
+        bytes_ = state * (3 + (iters_ if train else 0)) + (state * (iters_ + 3) if train else 0)
+        extra = {"torch_formulation_ms": round(torch_ms, 4)}
     else:  # ssd
         from .ssd_scan import ssd_chunk_scan
         b, L, h, p, n = a.batch, a.seq, a.heads, a.head_dim, 64

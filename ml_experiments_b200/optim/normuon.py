@@ -37,6 +37,31 @@ def polar_express(G: torch.Tensor) -> torch.Tensor:
     return newton_schulz_torch(G, POLAR_EXPRESS_COEFFS, eps=1e-6, norm_scale=1.02)
 
 
+def _reshape_hint(p):
+    """The bank's optimizer view: the reference hangs a tuple named ``reshape`` on the parameter (shadowing the tensor
+    method of that name; modded-nanogpt/train_gpt.py:1125); ``reshape_to`` is accepted as well."""
+    for name in ("reshape", "reshape_to"):
+        hint = getattr(p, name, None)
+        if isinstance(hint, (tuple, list)):
+            return tuple(hint)
+    return None
+
+
+_vector_cache: dict = {}
+
+
+def _device_vector(values: tuple, repeat: int, device) -> torch.Tensor:
+    """Per-matrix multipliers as a device vector; the few distinct tuples of a schedule are uploaded once each."""
+    key = (values, repeat, str(device))
+    t = _vector_cache.get(key)
+    if t is None:
+        if len(_vector_cache) > 4096:
+            _vector_cache.clear()
+        t = torch.tensor(values, dtype=torch.float32).repeat_interleave(repeat).to(device)
+        _vector_cache[key] = t
+    return t
+
+
 def _cuda_stack(t: torch.Tensor) -> bool:
     return t.is_cuda and t.dim() >= 2 and t.is_contiguous() and t.dtype in (torch.bfloat16, torch.float32)
 
@@ -60,8 +85,12 @@ def normuon_step_(p: torch.Tensor, mantissa, v: torch.Tensor, second_momentum: t
         m16 = None if mantissa is None else mantissa.view(torch.int16) if mantissa.element_size() == 2 else None
         if mantissa is not None and m16 is None:
             raise TypeError("the mantissa buffer of a bf16 parameter must be a 16-bit integer tensor on CUDA")
-        lr_t = torch.tensor(list(lr), dtype=torch.float32, device=v.device) if per_matrix else None
-        wd_t = torch.tensor(list(wd_lr), dtype=torch.float32, device=v.device) if per_matrix else None
+        lr_t = wd_t = None
+        if per_matrix:      # one value per leading index of p; a leading index may hold several matrices (4-D banks)
+            rep = p3.shape[0] // len(lr)
+            assert rep * len(lr) == p3.shape[0], (p.shape, len(lr))
+            lr_t = _device_vector(tuple(lr), rep, v.device)
+            wd_t = _device_vector(tuple(wd_lr), rep, v.device)
         o.normuon_update(p3, m16, v3, stat.reshape(-1), red_cols, 0.0 if per_matrix else float(lr),
                          0.0 if per_matrix else float(wd_lr), lr_t, wd_t)
         return
@@ -151,7 +180,7 @@ class NorMuonAndAdam:
                               wd_mul=t.get("wd_mul", 1.0), lr=t.get("lr", base["lr"]),
                               weight_decay=t.get("weight_decay", base["weight_decay"]), eps=t.get("eps", base.get("eps", 1e-10)),
                               momentum=t.get("momentum", base.get("momentum", 0.95)), beta2=t.get("beta2", base.get("beta2", 0.95)),
-                              reshape=tuple(t["reshape"]) if t.get("reshape") else getattr(p, "reshape_to", None),
+                              reshape=tuple(t["reshape"]) if t.get("reshape") else _reshape_hint(p),
                               per_matrix_lr_mul=t.get("per_matrix_lr_mul"))
             if self.world_size == 1:
                 cfg.comms = "none"

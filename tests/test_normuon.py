@@ -193,3 +193,20 @@ def test_normuon_decay_is_scaled_by_the_effective_lr():
     lr_eff = 0.02 * 2.0
     want = p0 - p0 * ((v * p0) >= 0) * (0.5 * 1.5 * 0.02) * lr_eff - v * lr_eff
     assert torch.allclose(p.detach(), want, atol=1e-6), (p.detach() - want).abs().max()
+
+
+def test_bank_reshape_hint_and_per_matrix_rates():
+    """A bank parameter carries its optimizer view as a tuple attribute named ``reshape`` (the reference's convention,
+    modded-nanogpt/train_gpt.py:1125); per-matrix multipliers index the leading axis of THAT view: with [1, 2] per layer
+    the second matrix of every layer (the output projection) moves twice as far."""
+    torch.manual_seed(7)
+    p = torch.nn.Parameter(torch.zeros(3, 2, 16, 8))
+    p.reshape = (6, 16, 8)
+    opt = NorMuonAndAdam([("mlp", p)], {"mlp": dict(optim="normuon", comms="none", lr=0.02, weight_decay=0.0, per_matrix_lr_mul=[1.0, 2.0] * 3)},
+                         world_size=1, rank=0)
+    assert opt.cfgs["mlp"].reshape == (6, 16, 8)
+    p.grad = torch.randn(3, 2, 16, 8)
+    opt.step()
+    moved = p.detach().view(6, -1).norm(dim=1)
+    ratio = moved[1::2] / moved[0::2]
+    assert torch.allclose(ratio, torch.full((3,), 2.0), rtol=0.15), ratio
