@@ -70,16 +70,63 @@ def mqar_table(df: pd.DataFrame, metric: str = "best_acc") -> pd.DataFrame:
     return d.pivot_table(index=["seq_len", "mixer"], columns="d_model", values=metric, aggfunc="max").sort_index()
 
 
+PALETTE = ["#222222", "#59A14F", "#4E79A7", "#E15759", "#F28E2B", "#76B7B2", "#9C755F", "#EDC948", "#B07AA1", "#BAB0AC", "#D3722C"]
+
+
+def _svg_panels(d: pd.DataFrame, lens, metric: str, path: str) -> None:
+    """Dependency-free figure: the same panels as the matplotlib one, written as SVG (log2 x axis, y from 0 to 1 or to
+    the data's maximum)."""
+    import math
+    W, H, L, R, T, B = 300, 230, 46, 10, 26, 36
+    mixers = sorted(d["mixer"].unique())
+    color = {m: PALETTE[i % len(PALETTE)] for i, m in enumerate(mixers)}
+    xs = sorted(d["d_model"].unique())
+    lx = [math.log2(x) for x in xs]
+    x0, x1 = min(lx) - 0.2, max(lx) + 0.2
+    ymax = max(1.0, float(d[metric].max()))
+    px = lambda v: L + (math.log2(v) - x0) / max(x1 - x0, 1e-9) * (W - L - R)
+    py = lambda v: T + (1 - v / ymax) * (H - T - B)
+    out = [f'<svg xmlns="http://www.w3.org/2000/svg" width="{W * len(lens)}" height="{H + 16 * ((len(mixers) + 3) // 4)}" font-family="sans-serif" font-size="10">',
+           '<rect width="100%" height="100%" fill="white"/>']
+    for i, sl in enumerate(lens):
+        ox = i * W
+        out.append(f'<g transform="translate({ox},0)"><text x="{W / 2}" y="14" text-anchor="middle" font-size="11">seq_len {sl}</text>')
+        out.append(f'<rect x="{L}" y="{T}" width="{W - L - R}" height="{H - T - B}" fill="none" stroke="#888"/>')
+        for k in range(5):
+            v = ymax * k / 4
+            out.append(f'<line x1="{L}" x2="{W - R}" y1="{py(v):.1f}" y2="{py(v):.1f}" stroke="#ddd"/><text x="{L - 4}" y="{py(v) + 3:.1f}" text-anchor="end">{v:.2f}</text>')
+        for x in xs:
+            out.append(f'<text x="{px(x):.1f}" y="{H - B + 12}" text-anchor="middle">{x}</text>')
+        out.append(f'<text x="{W / 2}" y="{H - 6}" text-anchor="middle">d_model</text>')
+        for m, g in d[d["seq_len"] == sl].groupby("mixer"):
+            g = g.sort_values("d_model")
+            pts = " ".join(f"{px(a):.1f},{py(b):.1f}" for a, b in zip(g["d_model"], g[metric]))
+            out.append(f'<polyline points="{pts}" fill="none" stroke="{color[m]}" stroke-width="1.5"/>')
+            out += [f'<circle cx="{px(a):.1f}" cy="{py(b):.1f}" r="2.5" fill="{color[m]}"/>' for a, b in zip(g["d_model"], g[metric])]
+        out.append("</g>")
+    for j, m in enumerate(mixers):
+        x, y = 10 + (j % 4) * 150, H + 12 + 16 * (j // 4)
+        out.append(f'<rect x="{x}" y="{y - 8}" width="10" height="10" fill="{color[m]}"/><text x="{x + 14}" y="{y + 1}">{m}</text>')
+    out.append("</svg>")
+    with open(path, "w") as f:
+        f.write("\n".join(out))
+
+
 def plot_mqar(df: pd.DataFrame, path: str, metric: str = "best_acc") -> bool:
-    """One panel per sequence length, accuracy against d_model, one line per mixer. False when matplotlib is absent."""
+    """One panel per sequence length, accuracy against d_model, one line per mixer (the figure of the reference's
+    zoology/analysis/mqar_plotting_example.py). With matplotlib the file type follows the extension; without it, or for
+    a ``.svg`` path, a plain SVG is written. Always returns True once the file exists."""
+    d = best_by(df.assign(mixer=df["mixer"].map(short_mixer)), metric=metric)
+    lens = sorted(d["seq_len"].unique())
     try:
+        if path.endswith(".svg"):
+            raise ImportError
         import matplotlib
         matplotlib.use("Agg")
         import matplotlib.pyplot as plt
     except ImportError:
-        return False
-    d = best_by(df.assign(mixer=df["mixer"].map(short_mixer)), metric=metric)
-    lens = sorted(d["seq_len"].unique())
+        _svg_panels(d, lens, metric, path if path.endswith(".svg") else path + ".svg")
+        return True
     fig, axes = plt.subplots(1, len(lens), figsize=(4 * len(lens), 3.2), squeeze=False)
     for ax, L in zip(axes[0], lens):
         for mixer, g in d[d["seq_len"] == L].groupby("mixer"):
@@ -107,7 +154,8 @@ def main(argv=None):
     table = mqar_table(df)
     print(table.to_string() if not table.empty else "no runs found")
     if a.plot and not df.empty:
-        print("figure written" if plot_mqar(df, a.plot) else "matplotlib is not installed: no figure")
+        plot_mqar(df, a.plot)
+        print("figure written")
     return table
 
 

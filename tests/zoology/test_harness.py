@@ -271,6 +271,9 @@ def test_analysis_tables_and_wall_clock(tmp_path):
     assert t.loc[(256, "Mamba"), 256] == 0.8 and t.loc[(256, "Mamba"), 64] == 0.4
     assert len(R.best_by(df)) == 5
     assert R.load_results(str(tmp_path / "none.csv")).empty
+    assert R.plot_mqar(df, str(tmp_path / "fig.svg"))                                     # the figure needs no plotting library
+    svg = (tmp_path / "fig.svg").read_text()
+    assert svg.startswith("<svg") and svg.count("<polyline") == 3 and "seq_len 256" in svg and "Mamba" in svg
     table = W.wall_clock_table(("mamba1", "mamba2", "attention", "gla", "long_conv"), (32,), batch=1, heads=2, head_dim=8, dstate=8, iters=1, warmup=0,
                                backward=True, device="cpu")
     assert table[0]["seq_len"] == 32 and all(table[0][k] > 0 for k in W.OPERATORS)
