@@ -95,9 +95,10 @@ class SequenceClassifier(nn.Module):
     """Scalar inputs in [0, 1] (or token ids when ``vocab_size`` is given) -> blocks -> mean pool -> classes; with
     ``per_token`` the head is applied at every position (the LM shell)."""
 
-    def __init__(self, block_fn, width: int, n_layers: int, n_out: int, seq_len: int, vocab_size: int | None = None, per_token: bool = False):
+    def __init__(self, block_fn, width: int, n_layers: int, n_out: int, seq_len: int, vocab_size: int | None = None, per_token: bool = False,
+                 token_head: nn.Module | None = None):
         super().__init__()
-        self.per_token = per_token
+        self.per_token, self.token_head = per_token, token_head
         self.embed = nn.Embedding(vocab_size, width) if vocab_size else nn.Linear(1, width)
         self.embed_norm, self.pos_norm, self.norm = RMSNorm(width), RMSNorm(width), RMSNorm(width)
         self.pos_embed = nn.Parameter(torch.randn(1, seq_len, width) * 0.02)
@@ -110,6 +111,8 @@ class SequenceClassifier(nn.Module):
         for layer in self.layers:
             h = layer(h)
         h = self.norm(h)
+        if self.token_head is not None and not self.per_token:
+            return self.token_head(h)          # a head that reads all tokens (query-group head) instead of mean pool + linear
         return self.head(h) if self.per_token else self.head(h.mean(dim=1))
 
 
@@ -128,6 +131,17 @@ class _PerToken(nn.Module):
         finally:
             handle.remove()
         return self.head(feats[-1])
+
+
+class _AsImage(nn.Module):
+    """Hands the flat ``(B, H * W)`` rows of the resident dataset to a model that wants ``(B, H, W)``."""
+
+    def __init__(self, core: nn.Module, grid):
+        super().__init__()
+        self.core, self.grid = core, tuple(grid)
+
+    def forward(self, x):
+        return self.core(x.view(x.shape[0], *self.grid))
 
 
 def count_params(model: nn.Module) -> int:
@@ -161,8 +175,14 @@ def find_config_for_params(make, target_params: int, head_options=(2, 4, 8), min
 def build_model(model_type: str, layers: int, n_out: int, seq_len: int, num_channels: int = 4, kernel_size: int = 17,
                 attn_order: str = "tele,conv,lowrank", target_params: int = 400_000, cross_layer: bool = False, router_top_k: int = 0,
                 jacobi_iters: int = 12, siren_conv: bool = False, vocab_size: int | None = None, per_token: bool = False,
-                embed_2d: tuple[int, int] | None = None):
+                embed_2d: tuple[int, int] | None = None, use_ssm: bool = False, ml_decoder: bool = False, hier_kw: dict | None = None):
+    """``use_ssm``: a chunk-scan state-space mixer after every attention / hierarchical block; ``ml_decoder``: query-group
+    head instead of mean pool + linear; ``hier_kw``: ``conv_position`` / ``attn_residual`` / ``merge_mode`` /
+    ``lowrank_hier`` of the hierarchical block."""
+    from .scatter_grid import QueryGroupHead, WithSSM
     max_len = max(seq_len, 64)
+    hier_kw = hier_kw or {}
+    ssm = (lambda make_block, w, h: (lambda: WithSSM(make_block(), w, h, 1))) if use_ssm else (lambda make_block, w, h: make_block)
     if model_type in ("ripple", "ripple-channel", "flat"):
         def make(w, _h):
             if model_type == "ripple":
@@ -178,15 +198,16 @@ def build_model(model_type: str, layers: int, n_out: int, seq_len: int, num_chan
         core = make(width, num_channels)
         return _PerToken(core, width, n_out) if per_token else core
     blocks = {
-        "attention": lambda w, h: (lambda: AttentionBlock(w, num_heads=h)),
-        "hier": lambda w, h: (lambda: HierarchicalLocalBlock(w, window_size=kernel_size, num_channels=h)),
+        "attention": lambda w, h: ssm(lambda: AttentionBlock(w, num_heads=h), w, h),
+        "hier": lambda w, h: ssm(lambda: HierarchicalLocalBlock(w, window_size=kernel_size, num_channels=h, **hier_kw), w, h),
         "sgsb": lambda w, h: (lambda: SGSBBlockND(w, kernel_size=kernel_size, ndim=1, num_channels=h)),
         "conv": lambda w, h: (lambda: ConvBlock(w, kernel_size=kernel_size)),
         "gather": lambda w, h: (lambda: TelephoneAttentionBlock(w, num_heads=h, max_seq_len=max_len)),
     }
     if model_type not in blocks:
         raise ValueError(f"Unknown model type: {model_type}")
-    make = lambda w, h: SequenceClassifier(blocks[model_type](w, h), w, layers, n_out, seq_len, vocab_size=vocab_size, per_token=per_token)
+    make = lambda w, h: SequenceClassifier(blocks[model_type](w, h), w, layers, n_out, seq_len, vocab_size=vocab_size, per_token=per_token,
+                                           token_head=QueryGroupHead(w, n_out) if ml_decoder and not per_token else None)
     width, heads = find_config_for_params(make, target_params)
     return make(width, heads)
 
@@ -309,6 +330,32 @@ def evaluate(model, data: PreloadedDataset, task_type, amp: bool):
 
 
 # ------------------------------------------------------------------------------------------------ sample selection
+def ensemble_teacher_logits(logit_history, loss_history, top_k: int = 3) -> torch.Tensor:
+    """``logit_history``: per epoch ``[N, classes]``; ``loss_history``: per epoch ``[N]`` (``inf`` where the sample was
+    misclassified). Per sample the ``top_k`` lowest-loss epochs are averaged with weights proportional to 1 / loss;
+    a sample never classified correctly gets zero logits (a uniform teacher)."""
+    logits, losses = torch.stack(logit_history), torch.stack(loss_history)
+    k = min(top_k, losses.shape[0])
+    best, where = losses.topk(k, dim=0, largest=False)
+    picked = torch.gather(logits, 0, where.unsqueeze(-1).expand(-1, -1, logits.shape[-1]))
+    w = torch.where(torch.isfinite(best), 1.0 / (best + 1e-8), torch.zeros_like(best))
+    w = w / w.sum(dim=0, keepdim=True).clamp_min(1e-8)
+    return (picked * w.unsqueeze(-1)).sum(dim=0)
+
+
+@torch.no_grad()
+def _logits_and_losses(model, data: "PreloadedDataset", amp: bool):
+    """Logits and per-sample cross entropy of every sample of ``data`` in storage order."""
+    model.eval()
+    outs = []
+    for i in range(0, len(data.x), data.batch_size):
+        with torch.autocast(data.x.device.type, dtype=torch.bfloat16, enabled=amp):
+            outs.append(model(data.x[i:i + data.batch_size]).float())
+    logits = torch.cat(outs)
+    model.train()
+    return logits, F.cross_entropy(logits, data.y, reduction="none")
+
+
 def hard_fraction(epoch: int, epochs: int, start: float, end: float) -> float:
     """Share of each batch that is back-propagated at ``epoch``: linear from ``start`` to ``end`` over the run."""
     t = epoch / max(epochs - 1, 1)
@@ -376,11 +423,16 @@ def train_model(model, train: PreloadedDataset, test: PreloadedDataset, epochs: 
                 distill_alpha: float = 0.5, distill_temp: float = 2.0, distill_merge: str | None = None, distill_merge_alpha: float = 0.5,
                 checkpoint_dir: str | None = None, model_name: str = "model", verbose: bool = True, weight_decay: float = 0.01,
                 hard_start: float | None = None, hard_end: float | None = None, first_epoch_pct: float | None = None,
-                wtf_mode: bool = False, distill_adaptive: bool = False):
+                wtf_mode: bool = False, distill_adaptive: bool = False, distill_from_merged: bool = False, distill_ensemble: bool = False,
+                distill_ensemble_k: int = 3):
     """Trains ``model`` (or both halves of a :class:`DuoModel`). In-batch selection: with ``hard_start`` / ``hard_end`` only
     the hardest share of each batch is back-propagated (share moving linearly over the epochs), ``first_epoch_pct``
     does that for the first epoch only, ``wtf_mode`` ascends on the easy half. ``distill_adaptive`` blends the
-    teacher and the labels per sample: easy samples follow the teacher, hard ones the labels."""
+    teacher and the labels per sample: easy samples follow the teacher, hard ones the labels. ``distill_from_merged``:
+    the teacher of the next epoch is the weight merge of the previous teacher and the current model (``distill_merge``
+    names the rule, exponential average by default). ``distill_ensemble``: the teacher is no model but a table of
+    logits per training sample, the inverse-loss-weighted mean over the ``distill_ensemble_k`` epochs in which that sample
+    was classified correctly with the lowest loss (:func:`ensemble_teacher_logits`)."""
     duo = isinstance(model, DuoModel)
     opt = torch.optim.AdamW(model.parameters(), lr=lr, weight_decay=weight_decay)
     steps = epochs * len(train)
@@ -388,6 +440,9 @@ def train_model(model, train: PreloadedDataset, test: PreloadedDataset, epochs: 
     swa_model = torch.optim.swa_utils.AveragedModel(model) if swa else None
     swa_epoch = int(epochs * swa_start)
     teacher, weights, history = None, None, []
+    if distill_from_merged and not distill_merge:
+        distill_merge = "ema"
+    table, logit_hist, loss_hist = None, [], []      # ensemble distillation: teacher logits per training sample
     for epoch in range(epochs):
         model.train()
         t0, seen, correct, total = time.perf_counter(), 0, 0.0, 0
@@ -415,9 +470,9 @@ def train_model(model, train: PreloadedDataset, test: PreloadedDataset, epochs: 
                     per = _loss_per_sample(logits, y, task_type, label_smoothing)
                     w = selection_weights(per.detach(), mode, frac)
                     loss = weighted_mean(per, w)
-                if teacher is not None and not duo:
+                if (teacher is not None or table is not None) and not duo:
                     with torch.no_grad():
-                        tl = teacher(x)
+                        tl = table[idx] if table is not None else teacher(x)
                     kd_rows = F.kl_div(F.log_softmax(logits.float() / distill_temp, -1), F.softmax(tl.float() / distill_temp, -1),
                                        reduction="none").sum(-1)
                     if kd_rows.dim() > 1:
@@ -441,7 +496,13 @@ def train_model(model, train: PreloadedDataset, test: PreloadedDataset, epochs: 
         if hard_mining:
             _, per = evaluate(model, train, task_type, amp)
             weights = per.clamp(min=1e-6)
-        if self_distill:
+        if self_distill and distill_ensemble and task_type == "classification" and not duo:
+            logits_all, per = _logits_and_losses(model, train, amp)
+            wrong = logits_all.argmax(-1) != train.y
+            logit_hist.append(logits_all)
+            loss_hist.append(per.masked_fill(wrong, float("inf")))
+            table = ensemble_teacher_logits(logit_hist, loss_hist, distill_ensemble_k)
+        elif self_distill:
             if teacher is not None and distill_merge:
                 merged = merge_teacher_student(teacher.state_dict(), model.state_dict(), distill_merge_alpha, distill_merge)
                 teacher.load_state_dict(merged)
@@ -554,6 +615,19 @@ def main(argv=None):
     ap.add_argument("--duo", action="store_true", help="two models on complementary shares of each batch, merged at inference")
     ap.add_argument("--duo-merge", default="mean", choices=DuoModel.MERGE_STRATEGIES)
     ap.add_argument("--distill-adaptive", action="store_true", help="self-distillation with a per-sample teacher / label blend")
+    ap.add_argument("--2d", dest="mode_2d", action="store_true", help="image-native models on an (H, W) grid (square images unless --grid is given)")
+    ap.add_argument("--3d", dest="mode_3d", action="store_true", help="volume-native models: colour planes become the depth axis of an (H, W, 3) grid")
+    ap.add_argument("--grid", default=None, help="H,W or H,W,D of the inputs for --2d / --3d when they are not square")
+    ap.add_argument("--ssm", action="store_true", help="add a state-space mixer after every attention / local / hierarchical block")
+    ap.add_argument("--conv-position", default="both", choices=["pre", "post", "both"], help="hierarchical block: convolution before / after the attention")
+    ap.add_argument("--merge-mode", default="lowrank", choices=["gate", "learned", "lowrank"], help="hierarchical block: how levels are merged")
+    ap.add_argument("--lowrank-hier", dest="lowrank_hier", action="store_true", default=True, help="hierarchical block: low-rank full attention per level (default)")
+    ap.add_argument("--no-lowrank-hier", dest="lowrank_hier", action="store_false", help="hierarchical block: windowed attention per level")
+    ap.add_argument("--no-attn-residual", action="store_true", help="hierarchical block: no residual around the attention")
+    ap.add_argument("--ml-decoder", action="store_true", help="query-group classification head instead of mean pool + linear")
+    ap.add_argument("--distill-from-merged", action="store_true", help="self-distillation teacher = weight merge of the previous teacher and the model")
+    ap.add_argument("--distill-ensemble", action="store_true", help="self-distillation teacher = per-sample ensemble of the best epochs' logits")
+    ap.add_argument("--distill-ensemble-k", type=int, default=3)
     ap.add_argument("--ponder", action="store_true", help="train through the learned auxiliary loss (models/unified/ponder.py)")
     ap.add_argument("--ponder-meta-lr", type=float, default=3e-4)
     ap.add_argument("--ponder-reward-scale", type=float, default=100.0)
@@ -568,15 +642,44 @@ def main(argv=None):
     a = ap.parse_args(argv)
     dev = torch.device("cuda" if (a.device == "auto" and torch.cuda.is_available()) or a.device == "cuda" else "cpu")
     xa, ya, xb, yb, n_out, task_type, vocab, L = load_dataset(a.dataset, a.seq_len, a.num_train, a.num_test, a.seed, a.task_vocab_size)
+    hier_kw = dict(conv_position=a.conv_position, attn_residual=not a.no_attn_residual, merge_mode=a.merge_mode, lowrank_hier=a.lowrank_hier)
+    grid = None
+    if a.mode_2d or a.mode_3d:
+        if task_type != "classification":
+            raise SystemExit("--2d / --3d are for classification datasets")
+        if a.grid:
+            grid = tuple(int(v) for v in a.grid.split(","))
+        else:
+            cells = L // 3 if a.mode_3d else L
+            side = int(round(cells ** 0.5))
+            grid = (side, side, 3) if a.mode_3d else (side, side)
+        if int(np.prod(grid)) != L or len(grid) != (3 if a.mode_3d else 2):
+            raise SystemExit(f"inputs of {L} values do not fill a grid {grid}: pass --grid H,W{',D' if a.mode_3d else ''}")
+
+    def make_model(kind: str):
+        from .scatter_grid import GRID_MODEL_TYPES, build_grid_model
+        if grid is not None and kind in GRID_MODEL_TYPES:
+            return build_grid_model(kind, a.layers, n_out, grid, num_channels=a.channels, kernel_size=min(a.kernel_size, 7 if len(grid) == 2 else 5),
+                                    use_ssm=a.ssm, ml_decoder=a.ml_decoder, **(hier_kw if kind == "hier" else {})).to(dev)
+        if a.mode_3d:
+            raise SystemExit(f"--3d has the model types {GRID_MODEL_TYPES}")
+        as_image = grid is not None and kind in ("ripple", "ripple-channel")      # these embed (B, H, W) pixel grids themselves
+        core = build_model(kind, a.layers, n_out, L, num_channels=a.channels, kernel_size=a.kernel_size, attn_order=a.attn_order,
+                           target_params=a.target_params, cross_layer=a.cross_layer, router_top_k=a.with_router, jacobi_iters=a.jacobi_iters,
+                           siren_conv=a.siren_conv, vocab_size=vocab, per_token=task_type == "lm", use_ssm=a.ssm, ml_decoder=a.ml_decoder,
+                           hier_kw=hier_kw, embed_2d=grid if as_image else None)
+        return (_AsImage(core, grid) if as_image else core).to(dev)
+
     kinds = MODEL_TYPES if a.model == "all" else a.model.split(",")
+    if grid is not None and a.model == "all":
+        from .scatter_grid import GRID_MODEL_TYPES
+        kinds = GRID_MODEL_TYPES + ([k for k in ("ripple", "ripple-channel", "flat") if not a.mode_3d])
     results = {}
     for kind in kinds:
         accs = []
         for run in range(a.runs):
             set_determinism(a.seed + run)
-            model = build_model(kind, a.layers, n_out, L, num_channels=a.channels, kernel_size=a.kernel_size, attn_order=a.attn_order,
-                                target_params=a.target_params, cross_layer=a.cross_layer, router_top_k=a.with_router, jacobi_iters=a.jacobi_iters,
-                                siren_conv=a.siren_conv, vocab_size=vocab, per_token=task_type == "lm").to(dev)
+            model = make_model(kind)
             train = PreloadedDataset(xa, ya, dev, a.batch_size, True, a.seed + run)
             test = PreloadedDataset(xb, yb, dev, a.batch_size, False)
             print(f"[{kind}] {count_params(model):,} parameters, sequence length {L}, {task_type}", flush=True)
@@ -585,9 +688,7 @@ def main(argv=None):
                 return results
             if a.duo:
                 set_determinism(a.seed + run + 1000)
-                twin = build_model(kind, a.layers, n_out, L, num_channels=a.channels, kernel_size=a.kernel_size, attn_order=a.attn_order,
-                                   target_params=a.target_params, cross_layer=a.cross_layer, router_top_k=a.with_router,
-                                   jacobi_iters=a.jacobi_iters, siren_conv=a.siren_conv, vocab_size=vocab, per_token=task_type == "lm").to(dev)
+                twin = make_model(kind)
                 model = DuoModel(model, twin, a.duo_merge)
             if a.ponder and task_type != "lm":
                 accs.append(_train_with_ponder(model, train, test, a, dev, n_out))
@@ -597,7 +698,8 @@ def main(argv=None):
                                distill_alpha=a.distill_alpha, distill_temp=a.distill_temp, distill_merge=a.distill_merge,
                                distill_merge_alpha=a.distill_merge_alpha, checkpoint_dir=a.checkpoint_dir, model_name=kind,
                                hard_start=a.hard_start, hard_end=a.hard_end, first_epoch_pct=a.first_epoch_pct, wtf_mode=a.wtf_mode,
-                               distill_adaptive=a.distill_adaptive)
+                               distill_adaptive=a.distill_adaptive, distill_from_merged=a.distill_from_merged,
+                               distill_ensemble=a.distill_ensemble, distill_ensemble_k=a.distill_ensemble_k)
             accs.append(hist[-1]["test_acc"])
         results[kind] = dict(mean=float(np.mean(accs)), std=float(np.std(accs)), runs=accs)
         print(f"[{kind}] final test accuracy {results[kind]['mean']:.4f} +- {results[kind]['std']:.4f}", flush=True)

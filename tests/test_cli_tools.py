@@ -144,3 +144,33 @@ def test_scatter_harness_selection_duo_and_ponder_modes():
                   ["--epochs", "1", "--first-epoch-pct", "0.3", "--workers", "2", "--compile"]):
         r = B.main(common + extra)
         assert 0.0 <= r["ripple"]["mean"] <= 1.0
+
+
+def test_scatter_harness_grid_models_ssm_stage_heads_and_ensemble_teacher():
+    import torch
+
+    from ml_experiments_b200.cli import bench_scatter as B
+    from ml_experiments_b200.cli import scatter_grid as G
+
+    # per-sample ensemble teacher: best-k correctly classified epochs, weights 1 / loss
+    lg = [torch.tensor([[1.0, 0.0], [0.0, 1.0]]), torch.tensor([[3.0, 0.0], [0.0, 5.0]]), torch.tensor([[9.0, 0.0], [0.0, 7.0]])]
+    ls = [torch.tensor([1.0, float("inf")]), torch.tensor([0.5, float("inf")]), torch.tensor([4.0, float("inf")])]
+    t = B.ensemble_teacher_logits(lg, ls, top_k=2)
+    assert torch.allclose(t[0], (torch.tensor([3.0, 0.0]) * 2 + torch.tensor([1.0, 0.0]) * 1) / 3) and t[1].abs().sum() == 0
+    # the query-group head reads all tokens; the state-space stage keeps the block's shape on every grid rank
+    head = G.QueryGroupHead(32, 250)
+    assert head(torch.randn(2, 5, 7, 32)).shape == (2, 250) and head.groups == 100 and head.per_group == 3
+    for nd, shape in ((1, (2, 16, 32)), (2, (2, 4, 4, 32)), (3, (2, 4, 4, 3, 32))):
+        blk = G.WithSSM(torch.nn.Identity(), 32, 4, nd)
+        assert blk(torch.randn(*shape)).shape == shape
+    common = ["--dataset", "random-image", "--layers", "1", "--num-train", "32", "--num-test", "16", "--batch-size", "16", "--device", "cpu",
+              "--target-params", "20000", "--epochs", "1", "--kernel-size", "3"]
+    runs = [(["--model", "hier,conv", "--2d", "--seq-len", "64", "--merge-mode", "gate", "--conv-position", "pre", "--no-attn-residual", "--no-lowrank-hier"], ("hier", "conv")),
+            (["--model", "attention,local", "--3d", "--seq-len", "48", "--ssm", "--ml-decoder"], ("attention", "local")),
+            (["--model", "ripple", "--2d", "--seq-len", "64"], ("ripple",)),
+            (["--model", "attention,hier", "--seq-len", "32", "--ssm", "--ml-decoder", "--merge-mode", "learned"], ("attention", "hier")),
+            (["--model", "conv", "--seq-len", "32", "--epochs", "3", "--self-distill", "--distill-ensemble", "--distill-ensemble-k", "2"], ("conv",)),
+            (["--model", "conv", "--seq-len", "32", "--epochs", "3", "--self-distill", "--distill-from-merged"], ("conv",))]
+    for extra, kinds in runs:
+        r = B.main(common + extra)
+        assert set(r) == set(kinds) and all(0.0 <= v["mean"] <= 1.0 for v in r.values()), (extra, r)

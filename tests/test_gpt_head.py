@@ -184,3 +184,39 @@ def test_medium_track_model_trains_and_evaluates():
     tg_mask[50:] = -1
     l2 = m(ids2, tg_mask, seqlens, cfg1)
     assert torch.allclose(l1, l2, rtol=1e-4)
+
+
+@pytest.mark.gpu
+def test_medium_track_model_gpu_matches_cpu_and_steps():
+    """The medium-track GPT on the CUDA kernels (flash attention, tcgen05 linears, soft-capped CE) agrees with its fp32
+    CPU evaluation, and a few Adam steps through its backward lower the loss."""
+    import copy
+
+    from ml_experiments_b200.models.gpt_head import ForwardScheduleConfig
+    from ml_experiments_b200.models.gpt_medium import GPTMedium
+
+    torch.manual_seed(0)
+    m = GPTMedium(vocab_size=1000, num_heads=2, head_dim=128, model_dim=256, max_seq_len=1024, world_size=1)
+    with torch.no_grad():
+        for p in m.parameters():
+            if p.ndim >= 2 and p.abs().sum() == 0:
+                p.normal_(0, 0.02)
+    T = 512
+    x, y = torch.randint(0, 1000, (T,)), torch.randint(0, 1000, (T,))
+    seqlens = torch.tensor([0, 200, 512], dtype=torch.int32)
+    cfg = ForwardScheduleConfig(torch.tensor([1.0, 0.5]), 1, 2)
+    want = m.train()(x, y, seqlens, cfg) / T
+    g = copy.deepcopy(m).cuda().bfloat16()
+    cfg_g = ForwardScheduleConfig(cfg.mtp_weights.cuda(), 1, 2)
+    args = (x.cuda(), y.cuda(), seqlens.cuda(), cfg_g)
+    got = g(*args) / T
+    assert abs(got.item() - want.item()) / want.item() < 3e-2
+    opt = torch.optim.Adam(g.parameters(), lr=3e-3)
+    losses = []
+    for _ in range(6):
+        loss = g(*args) / T
+        opt.zero_grad(set_to_none=True)
+        loss.backward()
+        opt.step()
+        losses.append(loss.item())
+    assert all(l == l for l in losses) and losses[-1] < losses[0] - 0.05, losses
