@@ -20,6 +20,8 @@
 // adjoint stencil in shared memory; the parameter gradients of the tile read the saved states.
 #include "jacobi.h"
 
+#include "common/per_device.h"
+
 #include <stdexcept>
 #include <string>
 
@@ -438,12 +440,11 @@ void launch_fwd(const JacobiArgs& a) {
   using G = Geo<N, kFwdItems>;
   const int TL = G::W - 2 * (a.n_iters - 1);
   const size_t smem = 2ull * G::W * N * sizeof(float);
-  static bool cfg[64] = {};
+  static PerDeviceOnce cfg;   // the shared-memory opt-in is a per-device attribute
   int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !cfg[dev]) {
+  if (cfg.pending(&dev)) {
     cudaFuncSetAttribute(jacobi_fwd_kernel<N, kFwdItems>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    cfg[dev] = true;
+    cfg.done(dev);
   }
   dim3 grid((a.L + TL - 1) / TL, a.R, a.batch);
   jacobi_fwd_kernel<N, kFwdItems><<<grid, kThreads, smem, a.stream>>>(a);
@@ -456,12 +457,11 @@ void launch_bwd(const JacobiArgs& a) {
   size_t smem = 2ull * G::W * N * sizeof(float);
   const size_t red = (size_t)kThreads * 18 * sizeof(float);
   if (smem < red) smem = red;
-  static bool cfg[64] = {};
+  static PerDeviceOnce cfg;
   int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !cfg[dev]) {
+  if (cfg.pending(&dev)) {
     cudaFuncSetAttribute(jacobi_bwd_kernel<N, kBwdItems>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    cfg[dev] = true;
+    cfg.done(dev);
   }
   dim3 grid((a.L + TL - 1) / TL, a.batch);
   jacobi_bwd_kernel<N, kBwdItems><<<grid, kThreads, smem, a.stream>>>(a);
