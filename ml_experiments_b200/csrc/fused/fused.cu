@@ -3,6 +3,8 @@
 // One warp owns one row wherever a row reduction is needed; all global accesses are 16-byte vectors.
 #include "fused.h"
 
+#include "common/per_device.h"
+
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 
@@ -866,10 +868,11 @@ void softcap_ce(const void* logits, const long long* targets, float* loss_rows, 
   if (n_predict < 1 || n_predict > 4) throw std::runtime_error("softcap_ce: 1 to 4 prediction offsets");
   const size_t cache_bytes = (size_t)V * 2;
   if (grad && g_ce_cache && cache_bytes <= 110 * 1024) {   // two rows per SM
-    static bool attr_set = false;
-    if (!attr_set) {
+    static PerDeviceOnce attr;   // the shared-memory opt-in is a per-device attribute
+    int dev = 0;
+    if (attr.pending(&dev)) {
       cudaFuncSetAttribute(softcap_ce_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
-      attr_set = true;
+      attr.done(dev);
     }
     softcap_ce_kernel<true><<<T, 1024, cache_bytes, s>>>((const bf16*)logits, targets, loss_rows, (uint8_t*)grad, grad_is_bf16,
                                                         T, V, ld, cap, 1.f / div, shift, loss_scale, grad_scale, mtp_w,
