@@ -508,7 +508,8 @@ bool ssd_fwd_supported(int64_t L, int64_t H, int64_t Hb, int64_t N, int64_t P) {
 }
 
 void ssd_fwd(const Tensor& x, const Tensor& Bm, const Tensor& Cm, const Tensor& log_a, const Tensor& g_off, const Tensor& g_diag,
-             Tensor y, const c10::optional<Tensor>& init_state, const c10::optional<Tensor>& final_state, Tensor status) {
+             Tensor y, const c10::optional<Tensor>& init_state, const c10::optional<Tensor>& final_state, Tensor status,
+             const c10::optional<Tensor>& chunk_states) {
   const c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(x.dim() == 4 && Bm.dim() == 4 && Cm.dim() == 4, "ssd_fwd: x [b, L, H, P], B / C [b, L, Hb, N]");
   for (const Tensor* t : {&x, &Bm, &Cm, (const Tensor*)&y}) TORCH_CHECK(t->scalar_type() == at::kBFloat16 && t->is_contiguous(), "ssd_fwd: bf16 contiguous x, B, C, y");
@@ -527,8 +528,48 @@ void ssd_fwd(const Tensor& x, const Tensor& Bm, const Tensor& Cm, const Tensor& 
   a.x = x.data_ptr(); a.B = Bm.data_ptr(); a.C = Cm.data_ptr(); a.y = y.data_ptr();
   a.log_a = log_a.data_ptr<float>(); a.g_off = g_off.data_ptr<float>(); a.g_diag = g_diag.data_ptr<float>();
   a.init_state = st(init_state); a.final_state = st(final_state);
+  if (chunk_states.has_value()) {
+    TORCH_CHECK(chunk_states->scalar_type() == at::kFloat && chunk_states->is_contiguous() && chunk_states->numel() == ns * (a.L / 128),
+                "ssd_fwd: chunk states fp32 [b, H, L / 128, N, P]");
+    a.chunk_states = chunk_states->data_ptr<float>();
+  }
   a.status = status.data_ptr<int>(); a.stream = cur_stream();
   b200::ssd_fwd_sm100(a);
+}
+
+Tensor ssd_flip_time(const Tensor& src) {
+  const c10::cuda::CUDAGuard guard(src.device());
+  TORCH_CHECK(src.is_cuda() && src.is_contiguous() && src.dim() >= 3, "ssd_flip_time: contiguous [batch, L, ...]");
+  Tensor dst = at::empty_like(src);
+  const int64_t row_bytes = src.numel() / (src.size(0) * src.size(1)) * src.element_size();
+  b200::ssd_flip_time(src.data_ptr(), dst.data_ptr(), (int)src.size(0), (int)src.size(1), row_bytes, cur_stream());
+  return dst;
+}
+
+void ssd_bwd_post(const Tensor& x, const Tensor& dy, const Tensor& y, const Tensor& dx_rev, const Tensor& dB_rev, const Tensor& dC_heads,
+                  const Tensor& Bm, const Tensor& Cm, const Tensor& g_off, const Tensor& g_diag, Tensor dx, Tensor dB, Tensor dC,
+                  Tensor d_goff, Tensor d_gdiag, Tensor inner) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  b200::SsdPostArgs a;
+  a.batch = (int)x.size(0); a.L = (int)x.size(1); a.H = (int)x.size(2); a.P = (int)x.size(3);
+  a.Hb = (int)Bm.size(2); a.N = (int)Bm.size(3);
+  const int64_t np = x.numel(), nn = (int64_t)a.batch * a.L * a.H * a.N, ng = Bm.numel(), ns = (int64_t)a.batch * a.L * a.H;
+  auto b16 = [](const Tensor& t, int64_t n, const char* what) -> void* {
+    TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.is_contiguous() && t.numel() == n, "ssd_bwd_post: bf16 contiguous ", what);
+    return t.data_ptr();
+  };
+  auto f32 = [](const Tensor& t, int64_t n, const char* what) -> float* {
+    TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kFloat && t.is_contiguous() && t.numel() == n, "ssd_bwd_post: fp32 contiguous ", what);
+    return t.data_ptr<float>();
+  };
+  a.x = b16(x, np, "x"); a.dy = b16(dy, np, "dy"); a.y = b16(y, np, "y"); a.dx_rev = b16(dx_rev, np, "dx_rev");
+  a.dB_rev = b16(dB_rev, nn, "dB_rev"); a.dC_heads = b16(dC_heads, nn, "dC_heads");
+  a.B = b16(Bm, ng, "B"); a.C = b16(Cm, ng, "C");
+  a.g_off = f32(g_off, ns, "g_off"); a.g_diag = f32(g_diag, ns, "g_diag");
+  a.dx = b16(dx, np, "dx"); a.dB = b16(dB, ng, "dB"); a.dC = b16(dC, ng, "dC");
+  a.d_goff = f32(d_goff, ns, "d_goff"); a.d_gdiag = f32(d_gdiag, ns, "d_gdiag"); a.inner = f32(inner, ns, "inner");
+  a.stream = cur_stream();
+  b200::ssd_bwd_post(a);
 }
 
 void s6_scan_fwd(const Tensor& u, const Tensor& delta, const c10::optional<Tensor>& delta_bias, bool softplus, const Tensor& A,
@@ -842,7 +883,9 @@ TORCH_LIBRARY(b200, m) {
   m.def("s6_set_states_per_thread(int fwd_qs, int bwd_qs, Tensor like) -> ()");
   m.def("jacobi_fwd(Tensor Bm, Tensor Cm, Tensor theta, Tensor xr, Tensor alpha, Tensor gamma, Tensor conv_w, Tensor conv_b, Tensor? inj_lambda, Tensor? ro_lambda, int n_iters, Tensor(a!) gated, Tensor(b!)? Hs) -> ()");
   m.def("jacobi_bwd(Tensor dgated, Tensor Hs, Tensor Bm, Tensor Cm, Tensor theta, Tensor xr, Tensor alpha, Tensor gamma, Tensor conv_w, Tensor conv_b, Tensor? inj_lambda, Tensor? ro_lambda, int n_iters, Tensor(a!) dBm, Tensor(b!) dCm, Tensor(c!) dtheta, Tensor(d!) dxr, Tensor(e!) dalpha, Tensor(f!) dgamma, Tensor(g!) dconv_w, Tensor(h!) dconv_b, Tensor(i!) dlam) -> ()");
-  m.def("ssd_fwd(Tensor x, Tensor B, Tensor C, Tensor log_a, Tensor g_off, Tensor g_diag, Tensor(a!) y, Tensor? init_state, Tensor(b!)? final_state, Tensor(c!) status) -> ()");
+  m.def("ssd_flip_time(Tensor src) -> Tensor");
+  m.def("ssd_bwd_post(Tensor x, Tensor dy, Tensor y, Tensor dx_rev, Tensor dB_rev, Tensor dC_heads, Tensor B, Tensor C, Tensor g_off, Tensor g_diag, Tensor(a!) dx, Tensor(b!) dB, Tensor(c!) dC, Tensor(d!) d_goff, Tensor(e!) d_gdiag, Tensor(f!) inner) -> ()");
+  m.def("ssd_fwd(Tensor x, Tensor B, Tensor C, Tensor log_a, Tensor g_off, Tensor g_diag, Tensor(a!) y, Tensor? init_state, Tensor(b!)? final_state, Tensor(c!) status, Tensor(d!)? chunk_states=None) -> ()");
   m.def("s6_scan_fwd(Tensor u, Tensor delta, Tensor? delta_bias, bool softplus, Tensor A, Tensor Bm, Tensor Cm, Tensor? Dv, Tensor? z, Tensor(a!)? y_pre, Tensor(b!) out, Tensor(c!)? state) -> ()");
   m.def("s6_scan_bwd(Tensor u, Tensor delta, Tensor? delta_bias, bool softplus, Tensor A, Tensor Bm, Tensor Cm, Tensor? Dv, Tensor? z, Tensor? y_pre, Tensor dout, Tensor state, Tensor(a!) du, Tensor(b!) ddelta, Tensor(c!) dA, Tensor(d!) dB_part, Tensor(e!) dC_part, Tensor(f!)? dD, Tensor(g!)? dz, Tensor(h!)? ddelta_bias) -> ()");
   m.def("causal_conv1d_silu_fwd(Tensor x, Tensor w, Tensor? bias, Tensor(a!) y) -> ()");
@@ -899,6 +942,8 @@ TORCH_LIBRARY_IMPL(b200, CUDA, m) {
   m.impl("allreduce_mean", &allreduce_mean);
   m.impl("s6_set_states_per_thread", &s6_set_states_per_thread);
   m.impl("ssd_fwd", &ssd_fwd);
+  m.impl("ssd_flip_time", &ssd_flip_time);
+  m.impl("ssd_bwd_post", &ssd_bwd_post);
   m.impl("jacobi_fwd", &jacobi_fwd);
   m.impl("jacobi_bwd", &jacobi_bwd);
   m.impl("s6_scan_fwd", &s6_scan_fwd);

@@ -45,6 +45,7 @@ struct SsdParams {
   __nv_bfloat16* y;         // [b, L, H, P]
   const float* init_state;  // [b, H, N, P] or null
   float* final_state;       // [b, H, N, P] or null
+  float* chunk_states;      // [b, H, nchunks, N, P] or null: the state after every chunk
   int* status;
 };
 
@@ -302,15 +303,19 @@ ssd_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       const bool last = c + 1 == p.nchunks;
       uint8_t* srow = sS + tid * 128;
       float* fin = (last && p.final_state) ? p.final_state + ((long long)bh * N + tid) * P : nullptr;
+      float* cst = p.chunk_states ? p.chunk_states + (((long long)bh * p.nchunks + c) * N + tid) * P : nullptr;
 #pragma unroll
       for (int cblk = 0; cblk < P / 32; ++cblk) {
         uint32_t v[32];
         tmem_ld_32x32b_x32(tmem_base + lane_off + S_COL + cblk * 32, v);
         tmem_ld_wait();
-        if (fin) {
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+          float* dst = which == 0 ? fin : cst;
+          if (!dst) continue;
 #pragma unroll
           for (int i = 0; i < 32; i += 4)
-            *reinterpret_cast<float4*>(fin + cblk * 32 + i) = make_float4(__uint_as_float(v[i]), __uint_as_float(v[i + 1]),
+            *reinterpret_cast<float4*>(dst + cblk * 32 + i) = make_float4(__uint_as_float(v[i]), __uint_as_float(v[i + 1]),
                                                                           __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
         }
         if (!last) {
@@ -365,7 +370,7 @@ void launch(const SsdArgs& a) {
   p.L = a.L; p.H = a.H; p.Hb = a.Hb; p.nchunks = a.L / Q;
   p.log_a = a.log_a; p.g_off = a.g_off; p.g_diag = a.g_diag;
   p.y = reinterpret_cast<__nv_bfloat16*>(a.y);
-  p.init_state = a.init_state; p.final_state = a.final_state; p.status = a.status;
+  p.init_state = a.init_state; p.final_state = a.final_state; p.chunk_states = a.chunk_states; p.status = a.status;
   kern<<<a.batch * a.H, 128, smem, a.stream>>>(tx, tb, tc, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) throw std::runtime_error(std::string("ssd launch: ") + cudaGetErrorString(e));

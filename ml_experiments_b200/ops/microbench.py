@@ -52,7 +52,7 @@ def _doc_bounds(t: int, doc_len: int):
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("op", choices=["gemm", "attn_fwd", "attn_bwd", "softcap_ce", "s6_fwd", "s6_bwd", "gather_fwd", "gather_bwd",
-                                   "newton_schulz", "ssd", "jacobi", "jacobi_bwd", "tele_fwd", "tele_bwd", "alc_fwd", "alc_bwd", "rms_act"])
+                                   "newton_schulz", "ssd", "ssd_bwd", "jacobi", "jacobi_bwd", "tele_fwd", "tele_bwd", "alc_fwd", "alc_bwd", "rms_act"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -222,16 +222,24 @@ def main(argv=None):
 
         from .ssd_scan import _ssd_chunk_scan_torch
 
-        with torch.no_grad():
-            fn_t = lambda: _ssd_chunk_scan_torch(x, Bm, Cm, la, gm)
-            torch_ms = _time(fn_t, max(a.iters // 4, 2), 2)          # the batched-GEMM formulation, for the ratio
-        fn_inner = lambda: ssd_chunk_scan(x, Bm, Cm, la, gm)
+        train = a.op == "ssd_bwd"
+        if train:       # forward + backward: four launches of the kernel against autograd through the GEMM formulation
+            for t in (x, Bm, Cm, la, gm):
+                t.requires_grad_(True)
 
-        def fn():
-            with torch.no_grad():
-                return fn_inner()
+        def run(f):
+            if not train:
+                with torch.no_grad():
+                    return f(x, Bm, Cm, la, gm)
+            y = f(x, Bm, Cm, la, gm)
+            y.backward(torch.ones_like(y))
+            return y
+        torch_ms = _time(lambda: run(_ssd_chunk_scan_torch), max(a.iters // 4, 2), 2)          # the batched-GEMM formulation, for the ratio
+        fn = lambda: run(ssd_chunk_scan)
         flops = 2.0 * b * L * h * (128 * n + 128 * p + 2 * n * p)     # kernel: 128-step chunks
         bytes_ = (x.numel() * 2 + Bm.numel() * 2) * 2.0 + la.numel() * 12.0
+        if train:
+            flops, bytes_ = 4 * flops, 4 * bytes_
         extra = {"torch_formulation_ms": round(torch_ms, 4)}
     ms = _time(fn, a.iters, a.warmup)
     check_status()

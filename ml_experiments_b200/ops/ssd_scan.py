@@ -14,8 +14,12 @@ Differentiable through autograd. ``ssd_scan_ref`` is the sequential fp32 oracle.
 
 On a B200 with bf16 inputs and supported shapes (``L % 128 == 0``, ``N`` and ``P`` in {64, 128}) the forward runs in ONE
 hand-written kernel (``csrc/scan/ssd_sm100.cu``): a CTA per (batch, head) walks 128-step chunks with the four
-products on tcgen05 and the running state resident in tensor memory; the backward differentiates the batched-GEMM
-formulation below (recomputed from the saved inputs). ``B200_SSD_KERNEL=0`` disables the kernel path.
+products on tcgen05 and the running state resident in tensor memory. The backward is three more launches of the SAME
+kernel (:class:`_SsdKernelGradFn`): the gradients of ``x`` and ``B`` are scans of the same form run backwards in time
+with the roles of the operands exchanged, the gradient of ``C`` is one forwards in time, and the gradients of the
+decays and weights are row / column sums that follow from ``y``, ``dy``, ``x`` and ``dx`` elementwise. Calls with an
+initial or returned state differentiate the batched-GEMM formulation below instead. ``B200_SSD_KERNEL=0`` disables
+the kernel path.
 """
 from __future__ import annotations
 
@@ -128,6 +132,87 @@ def ssd_forward_kernel(x, B, C, log_alpha, gamma, beta=None, init_state=None, re
     return (y, fin) if return_state else y
 
 
+_Q = 128      # steps per chunk of the kernel
+
+
+def _launch(x, B, C, log_a, g_off, g_diag, states: bool = False):
+    """One launch of the kernel; with ``states`` also the fp32 state after every 128-step chunk ``[b, H, L/128, N, P]``."""
+    from .runtime import add_launches, ops, status
+
+    y = torch.empty_like(x)
+    b, L, H, P = x.shape
+    st = torch.empty(b, H, L // _Q, B.shape[-1], P, dtype=torch.float32, device=x.device) if states else None
+    ops().ssd_fwd(x, B, C, log_a, g_off, g_diag, y, None, None, status(x.device), st)
+    add_launches(1)
+    return (y, st) if states else y
+
+
+class _SsdKernelGradFn(torch.autograd.Function):
+    """``y_i = g_diag_i (C_i.B_i) x_i + sum_{j<i} exp(cs_i - cs_j) g_off_j (C_i.B_j) x_j`` with ``cs`` the running sum of
+    ``log_a``; forward and backward on the tcgen05 kernel.
+
+    With ``E_ij = exp(cs_i - cs_j) (C_i.B_j)`` for ``j < i``:
+
+    * ``dx_j = g_off_j sum_{i>j} E_ij dy_i + diag``: the same scan backwards in time, "queries" ``B``, "keys" ``C``,
+      values ``dy`` (the decay between reversed neighbours ``t'-1, t'`` is ``log_a`` of the later original step);
+    * ``dC_i = sum_{j<i} E_ij g_off_j (dy_i.x_j) B_j + diag``: forwards in time, queries ``dy``, keys ``x``, values ``B``
+      (state of shape ``[P, N]`` instead of ``[N, P]``);
+    * ``dB_j = g_off_j sum_{i>j} E_ij (dy_i.x_j) C_i + diag``: backwards in time, queries ``x``, keys ``dy``, values ``C``;
+    * ``d g_off_j = x_j . DX_j`` with ``DX`` the first scan before its ``g_off`` factor, ``d g_diag_i = (C_i.B_i)(dy_i.x_i)``;
+    * every pair ``j < t <= i`` sees ``log_a_t``, so ``d log_a_t = sum_{i>=t} R_i - sum_{j>=t} K_j`` with the row sums
+      ``R_i = dy_i . (y_i - diag_i)`` and column sums ``K_j = g_off_j d g_off_j`` (pairs on one side of ``t`` cancel).
+      The cancellation is only left to the sums inside a chunk: the part of later chunks is the number of pairs that
+      straddle the chunk's end, and that is the inner product of the forward state at that boundary with the state of
+      the backwards-in-time scan there (both are written by the kernel in fp32), so the rounding noise of ``y`` and
+      ``dx`` (bf16) does not accumulate along the sequence.
+    """
+
+    @staticmethod
+    def forward(ctx, x, B, C, log_a, g_off, g_diag):
+        bf = lambda t: (t if t.dtype == torch.bfloat16 else t.to(torch.bfloat16)).contiguous()
+        f32 = lambda t: t.float().contiguous()
+        xb, Bb, Cb, la, go, gd = bf(x), bf(B), bf(C), f32(log_a), f32(g_off), f32(g_diag)
+        need_grad = any(t.requires_grad for t in (x, B, C, log_a, g_off, g_diag))
+        y, S = _launch(xb, Bb, Cb, la, go, gd, states=True) if need_grad else (_launch(xb, Bb, Cb, la, go, gd), None)
+        ctx.save_for_backward(xb, Bb, Cb, la, go, gd, y, S)
+        ctx.dtypes = (x.dtype, B.dtype, C.dtype, log_a.dtype, g_off.dtype, g_diag.dtype)
+        return y if y.dtype == x.dtype else y.to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from .runtime import add_launches, ops
+
+        x, B, C, la, go, gd, y, S = ctx.saved_tensors
+        b, L, H, P = x.shape
+        Hb, N = B.shape[2], B.shape[3]
+        rep = H // Hb
+        o = ops()
+        flip = o.ssd_flip_time                                   # time reversal of a contiguous [b, L, ...] tensor
+        dyb = dy.to(torch.bfloat16).contiguous()
+        heads = lambda t: t if rep == 1 else t.repeat_interleave(rep, dim=2).contiguous()
+        ones, zeros = torch.ones_like(la), torch.zeros_like(la)
+        la_r = torch.cat([zeros[:, :1], la[:, 1:].flip(1)], dim=1).contiguous()   # decay between reversed neighbours
+        dy_r, B_r, C_r = flip(dyb), flip(B), flip(C)
+        dx_rev, Lam = _launch(dy_r, C_r, B_r, la_r, ones, zeros, states=True)                     # [b, L, H, P], reversed
+        dC_h = _launch(heads(B), x, dyb, la, go, gd)                                              # [b, L, H, N]
+        dB_rev = _launch(heads(C_r), dy_r, flip(x), la_r, ones, zeros)                            # [b, L, H, N], reversed
+        dx, dB, dC = torch.empty_like(x), torch.empty_like(B), torch.empty_like(C)
+        d_goff, d_gdiag, inner = torch.empty_like(la), torch.empty_like(la), torch.empty_like(la)
+        o.ssd_bwd_post(x, dyb, y, dx_rev, dB_rev, dC_h, B, C, go, gd, dx, dB, dC, d_goff, d_gdiag, inner)
+        add_launches(5)
+        nc = L // _Q
+        inner = inner.view(b, nc, _Q, H).flip(2).cumsum(2).flip(2)                                # sums to the chunk's end
+        if nc > 1:
+            # pairs (i, j) on the two sides of the boundary after chunk c: <forward state after c, backwards state
+            # reaching the first step of chunk c+1> times that step's decay
+            pairs = (S[:, :, :nc - 1] * Lam[:, :, :nc - 1].flip(2)).sum((-1, -2)).permute(0, 2, 1)          # [b, nc-1, H]
+            later = torch.cat([torch.exp(la[:, _Q::_Q]) * pairs, zeros[:, :1]], dim=1)
+            inner = inner + later.unsqueeze(2)
+        d_la = inner.reshape(b, L, H)
+        outs = (dx, dB, dC, d_la, d_goff, d_gdiag)
+        return tuple(t.to(dt) if need else None for t, dt, need in zip(outs, ctx.dtypes, ctx.needs_input_grad))
+
+
 class _SsdKernelFn(torch.autograd.Function):
     """Kernel forward; backward = autograd through the batched-GEMM formulation on the saved inputs."""
 
@@ -163,6 +248,9 @@ def ssd_chunk_scan(x, B, C, log_alpha, gamma, beta=None, chunk: int = 64, init_s
     Returns ``y [b,L,H,P]`` (and the final state ``[b,H,N,P]`` if ``return_state``).
     """
     if kernel_supported(x, B, C):
+        if init_state is None and not return_state:
+            g_off, g_diag = _fold_weights(log_alpha, gamma, beta)      # differentiable: beta's look-back folds into g_off
+            return _SsdKernelGradFn.apply(x, B, C, log_alpha, g_off, g_diag)
         y, st = _SsdKernelFn.apply(x, B, C, log_alpha, gamma, beta, init_state, return_state)
         return (y, st) if return_state else y
     return _ssd_chunk_scan_torch(x, B, C, log_alpha, gamma, beta, chunk, init_state, return_state)
