@@ -586,7 +586,7 @@ void s6_scan_fwd(const Tensor& u, const Tensor& delta, const c10::optional<Tenso
   if (y_pre.has_value()) chk_bf16c(*y_pre, "y_pre");
   if (state.has_value())
     TORCH_CHECK(state->scalar_type() == at::kFloat && state->is_contiguous() &&
-                state->numel() == (int64_t)B * b200::s6_num_chunks(L) * Din * N, "state: fp32 [B, ceil(L/16), 4, Din, 4]");
+                state->numel() == (int64_t)B * b200::s6_num_chunks(L) * Din * N, "state: fp32 [B, tiles, 4, Din, 4] with tiles = s6_num_chunks(L)");
   b200::s6_scan_fwd(u.data_ptr(), delta.data_ptr(), delta.scalar_type() == at::kBFloat16, optf(delta_bias), softplus, A.data_ptr<float>(), Bm.data_ptr<float>(),
                     Cm.data_ptr<float>(), optf(Dv), optp(z), y_pre.has_value() ? y_pre->data_ptr() : nullptr, out.data_ptr(),
                     state.has_value() ? state->data_ptr<float>() : nullptr, B, L, Din, N, cur_stream());
@@ -605,7 +605,7 @@ void s6_scan_bwd(const Tensor& u, const Tensor& delta, const c10::optional<Tenso
   TORCH_CHECK(ddelta.scalar_type() == delta.scalar_type() && ddelta.is_contiguous() && delta.is_contiguous() && ddelta.sizes() == u.sizes() && dA.scalar_type() == at::kFloat &&
               dB_part.scalar_type() == at::kFloat && dC_part.scalar_type() == at::kFloat, "s6_scan_bwd: fp32 gradient buffers");
   TORCH_CHECK(dB_part.numel() == (int64_t)B * b200::s6_channel_blocks(Din) * L * N && dC_part.numel() == dB_part.numel(), "partial buffers: [B, ceil(Din/32), L, N]");
-  TORCH_CHECK(state.scalar_type() == at::kFloat && state.numel() == (int64_t)B * b200::s6_num_chunks(L) * Din * N, "state: [B, ceil(L/16), 4, Din, 4]");
+  TORCH_CHECK(state.scalar_type() == at::kFloat && state.numel() == (int64_t)B * b200::s6_num_chunks(L) * Din * N, "state: fp32 [B, tiles, 4, Din, 4] with tiles = s6_num_chunks(L)");
   b200::s6_scan_bwd(u.data_ptr(), delta.data_ptr(), delta.scalar_type() == at::kBFloat16, optf(delta_bias), softplus, A.data_ptr<float>(), Bm.data_ptr<float>(),
                     Cm.data_ptr<float>(), optf(Dv), optp(z), optp(y_pre), dout.data_ptr(), state.data_ptr<float>(), du.data_ptr(),
                     ddelta.data_ptr(), dA.data_ptr<float>(), dB_part.data_ptr<float>(), dC_part.data_ptr<float>(),

@@ -12,6 +12,8 @@ import torch.nn.functional as F
 
 from .runtime import ops
 
+TILE = 16     # time steps per tile and per state checkpoint of the kernels (SUB in csrc/scan/s6_scan.cu)
+
 
 def selective_scan_ref(u, delta, A, B, C, D=None, z=None, delta_bias=None, delta_softplus=False):
     """Sequential fp32 oracle (any device)."""
@@ -60,7 +62,7 @@ class _S6Scan(torch.autograd.Function):
         D32 = None if D is None else D.float().contiguous()
         b32 = None if delta_bias is None else delta_bias.float().contiguous()
         need_grad = any(t is not None and t.requires_grad for t in (u, delta, A, B, C, D, z, delta_bias))
-        state = torch.empty(bsz, (L + 15) // 16, 4, din, 4, dtype=torch.float32, device=u.device) if need_grad else None
+        state = torch.empty(bsz, (L + TILE - 1) // TILE, 4, din, 4, dtype=torch.float32, device=u.device) if need_grad else None
         y_pre = torch.empty_like(u16) if (need_grad and z16 is not None) else None
         out = torch.empty_like(u16)
         o.s6_scan_fwd(u16, d32, b32, bool(delta_softplus), A32, B32, C32, D32, z16, y_pre, out, state)
