@@ -20,6 +20,15 @@ from .runtime import ops, status
 EPI_NONE, EPI_RELU2, EPI_AXPBY, EPI_RELU2_BWD = 0, 1, 2, 3
 
 
+def _overlap(x: torch.Tensor, y: torch.Tensor) -> bool:
+    """True when the memory spans of two tensors intersect (conservative for strided views)."""
+    if x.numel() == 0 or y.numel() == 0 or x.device != y.device:
+        return False
+    span = lambda t: (t.data_ptr(), t.data_ptr() + (sum((n - 1) * abs(st) for n, st in zip(t.shape, t.stride())) + 1) * t.element_size())
+    (x0, x1), (y0, y1) = span(x), span(y)
+    return x0 < y1 and y0 < x1
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, out: torch.Tensor | None = None, out_dtype=None,
          a_mn: bool = False, b_mn: bool = False, epilogue: int = EPI_NONE, aux: torch.Tensor | None = None,
          alpha: float = 1.0, beta: float = 0.0, split_k: int = 1, accumulate: bool = False) -> torch.Tensor:
@@ -30,6 +39,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, out: torch.Tensor | None = None, o
         if out_dtype is None:
             out_dtype = torch.float32 if (split_k > 1 or accumulate) else torch.bfloat16
         out = torch.empty(*a.shape[:-2], m, n, dtype=out_dtype, device=a.device)
+    elif _overlap(out, a) or _overlap(out, b):
+        # an output tile is stored while other CTAs still read the operand panels: the result would depend on timing
+        raise ValueError("gemm: `out` must not alias an operand")
     ops().gemm(a, b, out, aux, a_mn, b_mn, epilogue, alpha, beta, split_k, accumulate, status(a.device))
     return out
 

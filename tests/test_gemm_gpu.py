@@ -91,3 +91,18 @@ def test_gemm_fp8(a_mn, b_mn):
     ref = _ref(a, b, a_mn, b_mn)
     out = gemm(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32, alpha=0.25)
     assert _rel_err(out, 0.25 * ref) < 2e-3
+
+
+def test_output_aliasing_an_operand_is_refused():
+    """In-place products are a timing-dependent race between CTAs (one stores a tile of the operand another still
+    reads); the front end rejects them instead of returning numbers that are right most of the time."""
+    from ml_experiments_b200.ops import gemm as G
+
+    x = torch.randn(4, 256, 256, device="cuda").bfloat16()
+    w = torch.randn(4, 256, 256, device="cuda").bfloat16()
+    with pytest.raises(ValueError, match="alias"):
+        G.gemm(w, x, b_mn=True, out=x)
+    with pytest.raises(ValueError, match="alias"):
+        G.gemm(x, w, out=x[:, :, :])
+    out = torch.empty_like(x)
+    G.gemm(w, x, b_mn=True, out=out, epilogue=G.EPI_AXPBY, aux=x, alpha=1.0, beta=0.5)      # aux may be an operand
