@@ -315,70 +315,73 @@ qkv_post_bwd_kernel(const float* __restrict__ dq, const bf16* __restrict__ dk, c
                     bf16* __restrict__ dve, float* __restrict__ dlam, int T, int H, float eps) {
   constexpr int LPR = D / 16;
   __shared__ float red[2][8];
-  const long long row = ((long long)blockIdx.x * 256 + threadIdx.x) / LPR;
   const int sub = threadIdx.x % LPR;
   const int lane = threadIdx.x & 31;
   const int wib = threadIdx.x >> 5;
-  const bool active = row < (long long)T * 3 * H;
-  const long long rr = active ? row : 0;
-  const int t = (int)(rr / (3 * H));
-  const int slot = (int)(rr % (3 * H));
-  const bf16* src = qkv + rr * D;
-  bf16* dst = dqkv + rr * D;
-  float s0 = 0.f, s1 = 0.f;
-  float a[8], b[8], ga[8], gb[8];
-  load8(src + sub * 8, a);
-  load8(src + D / 2 + sub * 8, b);
-  if (slot < 2 * H) {
-    const int hh = slot < H ? slot : slot - H;
-    const long long g0 = ((long long)t * H + hh) * D;
-    float y1[8], y2[8], c[8], s8[8];
-    if (slot < H) { load8f(dq + g0 + sub * 8, y1); load8f(dq + g0 + D / 2 + sub * 8, y2); }
-    else { load8(dk + g0 + sub * 8, y1); load8(dk + g0 + D / 2 + sub * 8, y2); }
-    load8f(cs + (long long)t * (D / 2) + sub * 8, c);
-    load8f(sn + (long long)t * (D / 2) + sub * 8, s8);
-    float ss = 0.f, dot = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      ga[i] = y1[i] * c[i] - y2[i] * s8[i];  // transpose of the rotation
-      gb[i] = y1[i] * s8[i] + y2[i] * c[i];
-      ss += a[i] * a[i] + b[i] * b[i];
-      dot += a[i] * ga[i] + b[i] * gb[i];
-    }
-    ss = group_sum<LPR>(ss);
-    dot = group_sum<LPR>(dot);
-    const float r = rsqrtf(ss / D + eps);
-    const float coef = dot * r * r * r / D;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) { ga[i] = r * ga[i] - a[i] * coef; gb[i] = r * gb[i] - b[i] * coef; }
-    if (active) { store8(dst + sub * 8, ga); store8(dst + D / 2 + sub * 8, gb); }
-  } else {
-    const int hv = slot - 2 * H;
-    const long long g0 = ((long long)t * H + hv) * D;
-    const float l0 = lam[0], l1 = lam[1];
-    load8(dv + g0 + sub * 8, ga);
-    load8(dv + g0 + D / 2 + sub * 8, gb);
-    float o1[8], o2[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      s0 += ga[i] * a[i] + gb[i] * b[i];
-      o1[i] = l0 * ga[i];
-      o2[i] = l0 * gb[i];
-    }
-    if (active) { store8(dst + sub * 8, o1); store8(dst + D / 2 + sub * 8, o2); }
-    if (ve) {
-      float e1[8], e2[8];
-      load8(ve + g0 + sub * 8, e1);
-      load8(ve + g0 + D / 2 + sub * 8, e2);
-#pragma unroll
+  const long long total = (long long)T * 3 * H;
+  const long long ngroups = (total * LPR + 255) / 256;   // 256-thread groups of rows; a block walks them with a stride
+  float s0 = 0.f, s1 = 0.f;                              // so that the two sums cost one atomic per block, not per group
+  for (long long grp = blockIdx.x; grp < ngroups; grp += gridDim.x) {
+    const long long row = (grp * 256 + threadIdx.x) / LPR;
+    const bool active = row < total;
+    const long long rr = active ? row : 0;
+    const int t = (int)(rr / (3 * H));
+    const int slot = (int)(rr % (3 * H));
+    const bf16* src = qkv + rr * D;
+    bf16* dst = dqkv + rr * D;
+    float a[8], b[8], ga[8], gb[8];
+    load8(src + sub * 8, a);
+    load8(src + D / 2 + sub * 8, b);
+    if (slot < 2 * H) {
+      const int hh = slot < H ? slot : slot - H;
+      const long long g0 = ((long long)t * H + hh) * D;
+      float y1[8], y2[8], c[8], s8[8];
+      if (slot < H) { load8f(dq + g0 + sub * 8, y1); load8f(dq + g0 + D / 2 + sub * 8, y2); }
+      else { load8(dk + g0 + sub * 8, y1); load8(dk + g0 + D / 2 + sub * 8, y2); }
+      load8f(cs + (long long)t * (D / 2) + sub * 8, c);
+      load8f(sn + (long long)t * (D / 2) + sub * 8, s8);
+      float ss = 0.f, dot = 0.f;
+  #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        s1 += ga[i] * e1[i] + gb[i] * e2[i];
-        o1[i] = l1 * ga[i];
-        o2[i] = l1 * gb[i];
+        ga[i] = y1[i] * c[i] - y2[i] * s8[i];  // transpose of the rotation
+        gb[i] = y1[i] * s8[i] + y2[i] * c[i];
+        ss += a[i] * a[i] + b[i] * b[i];
+        dot += a[i] * ga[i] + b[i] * gb[i];
       }
-      if (dve && active) { store8(dve + g0 + sub * 8, o1); store8(dve + g0 + D / 2 + sub * 8, o2); }
+      ss = group_sum<LPR>(ss);
+      dot = group_sum<LPR>(dot);
+      const float r = rsqrtf(ss / D + eps);
+      const float coef = dot * r * r * r / D;
+  #pragma unroll
+      for (int i = 0; i < 8; ++i) { ga[i] = r * ga[i] - a[i] * coef; gb[i] = r * gb[i] - b[i] * coef; }
+      if (active) { store8(dst + sub * 8, ga); store8(dst + D / 2 + sub * 8, gb); }
+    } else {
+      const int hv = slot - 2 * H;
+      const long long g0 = ((long long)t * H + hv) * D;
+      const float l0 = lam[0], l1 = lam[1];
+      load8(dv + g0 + sub * 8, ga);
+      load8(dv + g0 + D / 2 + sub * 8, gb);
+      float o1[8], o2[8];
+  #pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (active) s0 += ga[i] * a[i] + gb[i] * b[i];
+        o1[i] = l0 * ga[i];
+        o2[i] = l0 * gb[i];
+      }
+      if (active) { store8(dst + sub * 8, o1); store8(dst + D / 2 + sub * 8, o2); }
+      if (ve) {
+        float e1[8], e2[8];
+        load8(ve + g0 + sub * 8, e1);
+        load8(ve + g0 + D / 2 + sub * 8, e2);
+  #pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          if (active) s1 += ga[i] * e1[i] + gb[i] * e2[i];
+          o1[i] = l1 * ga[i];
+          o2[i] = l1 * gb[i];
+        }
+        if (dve && active) { store8(dve + g0 + sub * 8, o1); store8(dve + g0 + D / 2 + sub * 8, o2); }
+      }
     }
-    if (!active) { s0 = 0.f; s1 = 0.f; }
   }
   s0 = warp_sum(s0);
   s1 = warp_sum(s1);
@@ -822,7 +825,8 @@ void qkv_post_bwd(const float* dq, const void* dk, const void* dv, const void* q
                   int H, int D, float eps, cudaStream_t s) {
   const long long rows = (long long)T * 3 * H;
   const int rpb = 256 / (D / 16);
-  const int blocks = (int)((rows + rpb - 1) / rpb);
+  int blocks = (int)((rows + rpb - 1) / rpb);
+  if (blocks > 148 * 4) blocks = 148 * 4;     // 64 registers: four resident blocks of 256 threads per SM
   if (D == 128) qkv_post_bwd_kernel<128><<<blocks, 256, 0, s>>>(dq, (const bf16*)dk, (const bf16*)dv, (const bf16*)qkv, (const bf16*)ve, lam, cos, sin, (bf16*)dqkv, (bf16*)dve, dlam, T, H, eps);
   else if (D == 64) qkv_post_bwd_kernel<64><<<blocks, 256, 0, s>>>(dq, (const bf16*)dk, (const bf16*)dv, (const bf16*)qkv, (const bf16*)ve, lam, cos, sin, (bf16*)dqkv, (bf16*)dve, dlam, T, H, eps);
   else throw std::runtime_error("qkv_post: head_dim must be 64 or 128");

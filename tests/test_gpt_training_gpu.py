@@ -56,9 +56,11 @@ def test_loss_falls_and_tracks_the_autograd_trainer(fp8):
     # copies of the matrices, e4m3 head operands and e5m2 logit gradients; the oracle rounds activations to bf16 at
     # other places) and both orthogonalise with bf16 Newton-Schulz, which amplifies differences of small singular
     # directions. The measured gap stays below 2 % of the loss over the 30 steps; 6 % leaves room for other seeds
-    # while a stale weight copy, a lost gradient path or a wrong optimizer scale shows up as tens of percent.
+    # while a stale weight copy, a lost gradient path or a wrong optimizer scale shows up as tens of percent. Once
+    # the batch is memorised the loss is of the order 1e-2, where rounding differences are no longer small against it:
+    # an absolute 2e-3 (0.02 % of the starting loss) is allowed on top.
     for s, (u, v) in enumerate(zip(la, lb)):
-        assert abs(u - v) <= 0.06 * v, (s, u, v)
+        assert abs(u - v) <= 0.06 * v + 2e-3, (s, u, v)
 
 
 def test_head_shadow_is_refreshed_by_the_adam_kernel():
