@@ -26,11 +26,15 @@ class _Saved:
     __slots__ = ("x_in", "x_mix", "xn", "qkv", "qkvp", "y", "lse", "x_a", "xn2", "h", "skip", "skip_idx")
 
 
-def _wgrad(dy: Tensor, x: Tensor, out_shape) -> Tensor:
-    """dW[out, in] = dyᵀ · x with both operands consumed MN-major; split-K fills the machine for small outputs."""
+def _wgrad(dy: Tensor, x: Tensor, out_shape, out: Tensor | None = None) -> Tensor:
+    """dW[out, in] = dyᵀ · x with both operands consumed MN-major; split-K fills the machine for small outputs.
+    ``out``: an fp32 buffer of ``out_shape`` to write into (the optimizer's stacked gradient slot of this matrix)."""
     n_out, n_in = dy.shape[1], x.shape[1]
     sk = G.auto_split_k(n_out, n_in, dy.shape[0])
-    return G.gemm(dy, x, a_mn=True, b_mn=True, split_k=sk, out_dtype=torch.float32).view(out_shape)
+    if out is not None and (out.dtype != torch.float32 or not out.is_contiguous()):
+        out = None
+    dst = None if out is None else out.view(n_out, n_in)
+    return G.gemm(dy, x, a_mn=True, b_mn=True, split_k=sk, out=dst, out_dtype=torch.float32).view(out_shape)
 
 
 def _forward_backward(model, input_seq: Tensor, target_seq: Tensor, swb: int, need_grad: bool):
@@ -154,15 +158,15 @@ def _forward_backward(model, input_seq: Tensor, target_seq: Tensor, swb: int, ne
             dx = dx + dskips.pop(i)
         mlp = blk.mlp
         dpre = G.gemm(dx, w16(mlp.c_proj.weight), b_mn=True, epilogue=G.EPI_RELU2_BWD, aux=s.h)
-        put(mlp.c_proj.weight, _wgrad(dx, s.h, mlp.c_proj.weight.shape))
+        put(mlp.c_proj.weight, _wgrad(dx, s.h, mlp.c_proj.weight.shape, out_buf(mlp.c_proj.weight)))
         dxn2 = G.gemm(dpre, w16(mlp.c_fc.weight), b_mn=True)
-        put(mlp.c_fc.weight, _wgrad(dpre, s.xn2, mlp.c_fc.weight.shape))
+        put(mlp.c_fc.weight, _wgrad(dpre, s.xn2, mlp.c_fc.weight.shape, out_buf(mlp.c_fc.weight)))
         del dpre
         dx_a = Fz.norm_bwd_add(dxn2, s.x_a, dx, EPS)
         if blk.attn is not None:
             a = blk.attn
             dy = G.gemm(dx_a, w16(a.c_proj.weight), b_mn=True)
-            put(a.c_proj.weight, _wgrad(dx_a, s.y.view(T, HD), a.c_proj.weight.shape))
+            put(a.c_proj.weight, _wgrad(dx_a, s.y.view(T, HD), a.c_proj.weight.shape, out_buf(a.c_proj.weight)))
             q4 = s.qkvp.view(T, 3, H, D)
             if dq_acc is None:
                 dq_acc = torch.zeros(T, H, D, dtype=torch.float32, device=dev)
@@ -187,7 +191,7 @@ def _forward_backward(model, input_seq: Tensor, target_seq: Tensor, swb: int, ne
                 else:
                     dve_wait[vi] = dve
             dxn = G.gemm(dqkv, w16(a.qkv_w).view(3 * HD, C), b_mn=True)
-            put(a.qkv_w, _wgrad(dqkv, s.xn, a.qkv_w.shape))
+            put(a.qkv_w, _wgrad(dqkv, s.xn, a.qkv_w.shape, out_buf(a.qkv_w)))
             dx_mix = Fz.norm_bwd_add(dxn, s.x_mix, dx_a, EPS)
         else:
             dx_mix = dx_a

@@ -122,7 +122,10 @@ class Muon(torch.optim.Optimizer):
             t = self._pending_shard.get(f"mom_{r}x{c}")
             if t is not None:
                 ent["mom"].copy_(t[: ent["total"]])
-        torch._foreach_copy_(ent["gviews"], [p.grad for p, _ in plist])
+        # gradients the producing GEMM already wrote into their slot of the stack (see `grad_views`) need no copy
+        pairs = [(gv, p.grad) for (p, _), gv in zip(plist, ent["gviews"]) if p.grad.data_ptr() != gv.data_ptr()]
+        if pairs:
+            torch._foreach_copy_([a for a, _ in pairs], [b for _, b in pairs])
         ent["sumsq"].zero_()
         o.muon_momentum(ent["grads"], ent["mom"], ent["stack"], ent["sumsq"], mu, nesterov, 1.0)
         o.stack_scale_by_inv_norm(ent["stack"], ent["sumsq"], ent["total"], r * c, 1e-7)
@@ -147,6 +150,20 @@ class Muon(torch.optim.Optimizer):
             else:
                 p.add_(upd.to(p.dtype), alpha=alpha)
             slot += nmat
+
+    def grad_views(self) -> dict:
+        """``{id(param): fp32 view}`` of the stacked gradient buffers of the fused step. A backward that writes a
+        matrix's gradient into its view (and makes that view ``p.grad``) saves the step's copy of all gradients into
+        the stacks."""
+        out = {}
+        for group in self.param_groups:
+            params = list(group["params"])
+            if not params or not all(p.is_cuda and p.is_contiguous() and p.dim() >= 2 for p in params):
+                continue
+            for ent in self._slots(params):
+                for (p, _), gv in zip(ent["plist"], ent["gviews"]):
+                    out[id(p)] = gv
+        return out
 
     # -- the same checkpoint interface as the distributed forms (parallel/muon_dist.py): per-shape momentum stacks
     def sharded_state(self) -> dict:

@@ -271,6 +271,19 @@ class MuonShardEngine:
         self._streams = None
         self._concurrent = False
 
+    def grad_views(self) -> dict:
+        """``{id(param): fp32 view}`` of this rank's peer-mapped gradient stacks: a backward that writes a matrix's
+        gradient there (and makes the view ``p.grad``) needs no copy in :meth:`publish_grads`. Safe to overwrite once
+        :meth:`apply` of the previous step has returned: every peer has pushed by then, and a peer pushes after its
+        last read of these stacks."""
+        out = {}
+        for g in self.groups:
+            flat, slot = g["g_full"].local.view(g["padded"], g["r"], g["c"]), 0
+            for p, nmat in g["plist"]:
+                out[id(p)] = flat[slot:slot + nmat].view(p.shape)
+                slot += nmat
+        return out
+
     @torch.no_grad()
     def publish_grads(self):
         from ..ops.runtime import status
@@ -281,8 +294,10 @@ class MuonShardEngine:
             flat = g["g_full"].local.view(g["padded"], g["r"], g["c"])
             for p, nmat in g["plist"]:
                 if p.grad is not None:
-                    views.append(flat[slot:slot + nmat].view(p.shape))
-                    srcs.append(p.grad if p.grad.dtype == torch.float32 else p.grad.float())
+                    view = flat[slot:slot + nmat].view(p.shape)
+                    if p.grad.data_ptr() != view.data_ptr():      # not written in place by the producing kernel
+                        views.append(view)
+                        srcs.append(p.grad if p.grad.dtype == torch.float32 else p.grad.float())
                 slot += nmat
             if views:
                 torch._foreach_copy_(views, srcs)
@@ -359,6 +374,9 @@ class FusedDistMuon(torch.optim.Optimizer):
         params = [*params]
         super().__init__(params, dict(lr=lr, momentum=momentum, nesterov=nesterov, ns_steps=ns_steps))
         self.engine = MuonShardEngine(params, world)
+
+    def grad_views(self) -> dict:
+        return self.engine.grad_views()
 
     def sharded_state(self) -> dict:
         return _momentum_shards(self.engine.groups)

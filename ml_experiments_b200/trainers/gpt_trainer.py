@@ -136,6 +136,11 @@ class GPTTrainer:
         if self.optimizer1 is None:
             self.optimizer1 = FusedAdam(adam_groups, betas=(0.8, 0.95), eps=1e-10)
         self.optimizers = [self.optimizer1, self.optimizer2]
+        # the Muon forms that keep their gradients in stacks let the weight-gradient GEMMs write there directly
+        if self.device.type == "cuda" and hasattr(self.optimizer2, "grad_views") and os.environ.get("B200_GRAD_IN_PLACE", "1") == "1":
+            views = dict(getattr(model, "_grad_out", None) or {})
+            views.update(self.optimizer2.grad_views())
+            model._grad_out = views
         # B200_OVERLAP_SYNC=1 runs the bucket all-reduce on a side stream beside the Muon step (measured: no gain at 2 or 8 GPUs)
         # (only beside the fused Muon step: Dion's own all-reduces share the bucket all-reduce's flag channel and counter)
         self.overlap_sync = (self.comm_mode == "fused-p2p" and hasattr(self.comm, "start_async")
