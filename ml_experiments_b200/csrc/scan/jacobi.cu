@@ -294,6 +294,11 @@ __global__ void __launch_bounds__(kThreads) jacobi_bwd_kernel(const JacobiArgs p
         *reinterpret_cast<float2*>(A + w * N + ch[0]) = make_float2(aG[0], aG[1]);
         *reinterpret_cast<float2*>(A + w * N + ch[2]) = make_float2(aG[2], aG[3]);
         if (own[k]) {
+          if (it > 1) {   // the states the next (earlier) iteration reads: ask for their lines now, no register held
+            const float* nxt = p.Hs + ((((long long)(it - 2) * p.batch + b) * p.R + r) * p.L + l) * N;
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(nxt + ch[0]));
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(nxt + ch[2]));
+          }
           // injections of this iteration (angle (it+1) theta) and of the previous one (angle it * theta)
           float rb[4], rbp[4], inj[4], injp[4];
           rot(c[k][0], s[k][0], Bq[k][0], Bq[k][1], rb[0], rb[1]);
