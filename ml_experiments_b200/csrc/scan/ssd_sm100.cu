@@ -158,6 +158,16 @@ ssd_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   for (int c = 0; c < p.nchunks; ++c) {
     const bool have_state = has_init || c > 0;
     cta_wait(bar_load, c & 1, abort_flag, p.status, ERR_WAIT_SMEM_FULL);
+    if (tid == 32 && c + 1 < p.nchunks) {
+      // the operand buffers are single (two CTAs share an SM instead): the next chunk's loads can only be issued when
+      // this chunk's products are done, so at least have their tiles waiting in L2 by then
+      const int row1 = b * p.L + (c + 1) * Q;
+      for (int s = 0; s < NSN; ++s) {
+        tma_prefetch_3d(&tmC, s * 64, row1, hb);
+        tma_prefetch_3d(&tmB, s * 64, row1, hb);
+      }
+      for (int s = 0; s < NSP; ++s) tma_prefetch_3d(&tmX, s * 64, row1, h);
+    }
     if (tid == 0) {
       tc_fence_after_sync();
 #pragma unroll
