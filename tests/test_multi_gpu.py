@@ -54,3 +54,11 @@ def test_survivors_detect_a_rank_that_left_between_steps(tmp_path):
     assert outs[world - 1].startswith("injected steps=3"), outs
     for k in range(world - 1):
         assert outs[k].startswith(f"detected:{world - 1} steps=3"), outs
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_sharded_optimizer_state_survives_save_and_resume(tmp_path):
+    """Every rank saves its shard of the Muon momentum and the Adam moments; a fresh trainer that loads them continues
+    on the trajectory of the run that never stopped."""
+    r = _torchrun("tests/multi_gpu/check_checkpoint_resume.py", "--dir", str(tmp_path))
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
