@@ -825,6 +825,37 @@ bool norm_io_bf16(const Tensor& t, const char* n) {
   return t.scalar_type() == at::kBFloat16;
 }
 
+static void norm_rope_args(const Tensor& x, const Tensor& f1, const Tensor& f2, int64_t& rows, int& H, int& T, int& D, int& W) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 4 && x.scalar_type() == at::kBFloat16 && x.stride(3) == 1, "norm_rope: x bf16 [batch, T, H, D], unit stride over D");
+  TORCH_CHECK(x.size(0) == 1 || x.stride(0) == x.size(1) * x.stride(1), "norm_rope: batch entries must follow each other token-wise");
+  T = (int)x.size(1); H = (int)x.size(2); D = (int)x.size(3);
+  rows = x.size(0) * x.size(1) * x.size(2);
+  TORCH_CHECK(f1.scalar_type() == at::kBFloat16 && f2.scalar_type() == at::kBFloat16 && f1.is_contiguous() && f2.is_contiguous() &&
+              f1.dim() == 2 && f1.sizes() == f2.sizes() && f1.size(0) >= T && (f1.size(1) == D || f1.size(1) == 2 * D),
+              "norm_rope: tables bf16 [>= T, D or 2 D]");
+  W = (int)f1.size(1);
+  TORCH_CHECK(W == D || H % 2 == 0, "norm_rope: the paired table needs an even number of heads");
+}
+
+void norm_rope_fwd(const Tensor& x, const Tensor& f1, const Tensor& f2, Tensor y, Tensor rstd, double eps) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  int64_t rows; int H, T, D, W;
+  norm_rope_args(x, f1, f2, rows, H, T, D, W);
+  TORCH_CHECK(y.scalar_type() == at::kBFloat16 && y.is_contiguous() && y.numel() == rows * D && rstd.scalar_type() == at::kFloat && rstd.numel() == rows, "norm_rope_fwd: outputs");
+  b200::norm_rope_fwd(x.data_ptr(), x.stride(1), x.stride(2), f1.data_ptr(), f2.data_ptr(), W, y.data_ptr(), rstd.data_ptr<float>(), rows, H, T, D,
+                      (float)eps, cur_stream());
+}
+
+void norm_rope_bwd(const Tensor& x, const Tensor& f1, const Tensor& f2, const Tensor& rstd, const Tensor& dy, Tensor dx) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  int64_t rows; int H, T, D, W;
+  norm_rope_args(x, f1, f2, rows, H, T, D, W);
+  TORCH_CHECK(dy.scalar_type() == at::kBFloat16 && dy.is_contiguous() && dy.numel() == rows * D && dx.scalar_type() == at::kBFloat16 && dx.is_contiguous() &&
+              dx.numel() == rows * D && rstd.numel() == rows, "norm_rope_bwd: dy / dx bf16 contiguous");
+  b200::norm_rope_bwd(x.data_ptr(), x.stride(1), x.stride(2), f1.data_ptr(), f2.data_ptr(), W, rstd.data_ptr<float>(), dy.data_ptr(), dx.data_ptr(), rows,
+                      H, T, D, cur_stream());
+}
+
 void rms_act_fwd(const Tensor& x, const Tensor& w, Tensor y, Tensor rstd, double eps, int64_t act) {
   const c10::cuda::CUDAGuard guard(x.device());
   const bool xb = norm_io_bf16(x, "x"), yb = norm_io_bf16(y, "y");
@@ -890,6 +921,8 @@ TORCH_LIBRARY(b200, m) {
   m.def("s6_scan_bwd(Tensor u, Tensor delta, Tensor? delta_bias, bool softplus, Tensor A, Tensor Bm, Tensor Cm, Tensor? Dv, Tensor? z, Tensor? y_pre, Tensor dout, Tensor state, Tensor(a!) du, Tensor(b!) ddelta, Tensor(c!) dA, Tensor(d!) dB_part, Tensor(e!) dC_part, Tensor(f!)? dD, Tensor(g!)? dz, Tensor(h!)? ddelta_bias) -> ()");
   m.def("causal_conv1d_silu_fwd(Tensor x, Tensor w, Tensor? bias, Tensor(a!) y) -> ()");
   m.def("causal_conv1d_silu_bwd(Tensor x, Tensor w, Tensor? bias, Tensor dy, Tensor(a!) dx, Tensor(b!) dw, Tensor(c!)? dbias) -> ()");
+  m.def("norm_rope_fwd(Tensor x, Tensor f1, Tensor f2, Tensor(a!) y, Tensor(b!) rstd, float eps) -> ()");
+  m.def("norm_rope_bwd(Tensor x, Tensor f1, Tensor f2, Tensor rstd, Tensor dy, Tensor(a!) dx) -> ()");
   m.def("rms_act_fwd(Tensor x, Tensor w, Tensor(a!) y, Tensor(b!) rstd, float eps, int act) -> ()");
   m.def("rms_act_bwd(Tensor x, Tensor w, Tensor rstd, Tensor dy, Tensor(a!) dx, Tensor(b!) dw, int act) -> ()");
   m.def("tele_fused_fwd(Tensor x, Tensor freq, Tensor phase, Tensor kern, Tensor expo, Tensor(a!) out, int H, int half, float max_rec) -> ()");
@@ -950,6 +983,8 @@ TORCH_LIBRARY_IMPL(b200, CUDA, m) {
   m.impl("s6_scan_bwd", &s6_scan_bwd);
   m.impl("causal_conv1d_silu_fwd", &causal_conv1d_silu_fwd);
   m.impl("causal_conv1d_silu_bwd", &causal_conv1d_silu_bwd);
+  m.impl("norm_rope_fwd", &norm_rope_fwd);
+  m.impl("norm_rope_bwd", &norm_rope_bwd);
   m.impl("rms_act_fwd", &rms_act_fwd);
   m.impl("rms_act_bwd", &rms_act_bwd);
   m.impl("tele_fused_fwd", &tele_fused_fwd);

@@ -79,6 +79,14 @@ void scale_by_inv_norm(void* x_bf16, const float* sumsq, long long n, float eps,
 // p (fp32) += alpha * u (bf16) ; optionally also writes the bf16 copy p_bf16 used by the forward GEMMs
 void axpy_bf16_to_f32(float* p, const void* u_bf16, void* p_bf16, long long n, float alpha, cudaStream_t s);
 
+// ---- RMS norm + rotary of the current speedrun GPT (norm_rope.cu): x [batch, T, H, D] bf16 with element strides st
+// (between tokens; batch entries are T * st apart) and sh (between heads), tables [T_max, tab_w] bf16 (tab_w = D, or 2 D
+// for the paired-head layout), y / dx / dy contiguous [batch * T * H, D], rstd [batch * T * H].
+void norm_rope_fwd(const void* x, long long st, long long sh, const void* f1, const void* f2, int tab_w, void* y, float* rstd,
+                   long long rows, int H, int T, int D, float eps, cudaStream_t s);
+void norm_rope_bwd(const void* x, long long st, long long sh, const void* f1, const void* f2, int tab_w, const float* rstd,
+                   const void* dy, void* dx, long long rows, int H, int T, int D, cudaStream_t s);
+
 // ---- NorMuon (normuon.cu) ---------------------------------------------------------------------
 // v : stack [nmat][R][C] (bf16 or fp32). red_cols != 0: statistics per row (reduced over the C columns), else per column.
 // stat : scratch [nmat][R or C], receives the per-row / per-column scale; second : running second moment, same shape.

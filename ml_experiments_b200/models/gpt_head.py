@@ -21,6 +21,7 @@ from ..ops.attention import attention_reference, flash_attention
 from ..ops.fp8_linear import CastedLinearT
 from ..ops.fused import softcapped_cross_entropy
 from ..ops.linear import linear, linear_t
+from ..ops.norm_rope import norm_rotary
 
 BLOCK = 128  # attention block / window granularity in tokens
 
@@ -136,19 +137,19 @@ class CausalSelfAttention(nn.Module):
         assert B == 1, "packed variable-length sequences need B == 1"
         H, D = self.num_heads, self.head_dim
         q, k, v = linear(x, a.sa_lambdas[0] * qkvo_w[:self.dim * 3].type_as(x)).view(B, T, 3 * H, D).chunk(3, dim=-2)
-        q, k = norm(q), norm(k)
         gate_in = x[..., :12]
+        f1, f2 = a.yarn.factor1, a.yarn.factor2          # QK norm and the rotary map are one kernel on CUDA
         if self.paired:
             # [T, H, D] reinterpreted as [2T, H/2, D] exactly as the reference does (a flat view: head h of token t lands at
             # position 2t + h // (H/2) of head h % (H/2)); rotary angles come from the paired table (positions 2t, 2t+1)
-            q = a.yarn.rotary(q.reshape(B, T, H // 2, 2 * D)).view(B, 2 * T, H // 2, D)
-            k = a.yarn.rotary(k.reshape(B, T, H // 2, 2 * D)).view(B, 2 * T, H // 2, D)
+            q = norm_rotary(q, f1, f2).view(B, 2 * T, H // 2, D)
+            k = norm_rotary(k, f1, f2).view(B, 2 * T, H // 2, D)
             v = v.reshape(B, 2 * T, H // 2, D)
             if a.ve is not None:
                 v = v + 2 * torch.sigmoid(F.linear(gate_in, a.ve_gate_w)).view(B, 2 * T, H // 2, 1) * a.ve.view_as(v)
             y = _attend(q[0], k[0], v[0], a.seqlens, a.bm_size, a.yarn.attn_scale, 2)
         else:
-            q, k = a.yarn.rotary(q), a.yarn.rotary(k)
+            q, k = norm_rotary(q, f1, f2), norm_rotary(k, f1, f2)
             if a.key_offset:  # shift the stationary half of the key one token forward: one-layer induction
                 k = torch.cat([k[..., :D // 2], torch.cat([k[:, :1, :, D // 2:], k[:, :-1, :, D // 2:]], dim=1)], dim=-1)
             if a.ve is not None:

@@ -16,6 +16,7 @@ import torch.nn.functional as F
 
 from ..ops.fused import softcapped_cross_entropy
 from ..ops.linear import linear, linear_t
+from ..ops.norm_rope import norm_rotary
 from .gpt import CastedLinear
 from .gpt_head import BLOCK, ForwardScheduleConfig, Yarn, _attend, next_multiple_of_n, norm
 
@@ -54,7 +55,7 @@ class CausalSelfAttention(nn.Module):
         assert B == 1, "packed variable-length sequences need B == 1"
         H, D = self.num_heads, self.head_dim
         q, k, v = linear(x, sa_lambdas[0] * self.qkvo_w[: self.dim * 3].type_as(x)).view(B, T, 3 * H, D).chunk(3, dim=-2)
-        q, k = yarn.rotary(norm(q)), yarn.rotary(norm(k))
+        q, k = norm_rotary(q, yarn.factor1, yarn.factor2), norm_rotary(k, yarn.factor1, yarn.factor2)
         if key_offset:  # the two stationary quarter-bands of the key move one token forward
             prev = torch.cat([k[:, :1], k[:, :-1]], dim=1)
             band = torch.zeros(D, dtype=torch.bool, device=k.device)

@@ -211,3 +211,27 @@ def test_embed_scatter_add_two_sources():
     table.zero_()
     ops().embed_scatter_add(idx, a.float(), table)
     assert torch.allclose(table, torch.zeros(rows, c, device="cuda").index_add_(0, idx.long(), a.float()), rtol=1e-4, atol=1e-3)
+
+
+@pytest.mark.parametrize("D,H,paired,strided", [(128, 6, False, True), (128, 6, True, True), (64, 4, False, False), (64, 4, True, True)])
+def test_norm_rotary_kernel_matches_the_eager_composition(D, H, paired, strided):
+    """RMS norm + rotary map of the current speedrun GPT in one kernel (forward, backward) against F.rms_norm + the table
+    multiply in fp32; x is the q slice of a fused projection when ``strided``."""
+    from ml_experiments_b200.models.gpt_head import Yarn
+    from ml_experiments_b200.ops.norm_rope import norm_rotary, norm_rotary_ref
+
+    torch.manual_seed(0)
+    B, T = 1, 300
+    yarn = Yarn(D, 512, paired=paired).cuda()
+    base = torch.randn(B, T, 3 * H, D, device="cuda").bfloat16()
+    leaf = base.clone().requires_grad_(True)
+    x = leaf.chunk(3, dim=-2)[1] if strided else leaf[:, :, :H].contiguous()
+    y = norm_rotary(x, yarn.factor1, yarn.factor2)
+    w = torch.randn_like(y.float())
+    (y.float() * w).sum().backward()
+    ref_leaf = base.float().clone().requires_grad_(True)
+    xr = ref_leaf.chunk(3, dim=-2)[1] if strided else ref_leaf[:, :, :H]
+    yr = norm_rotary_ref(xr, yarn.factor1.float(), yarn.factor2.float(), eps=torch.finfo(torch.bfloat16).eps)
+    (yr * w).sum().backward()
+    rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm()).item()
+    assert rel(y, yr) < 1e-2 and rel(leaf.grad, ref_leaf.grad) < 1e-2, (rel(y, yr), rel(leaf.grad, ref_leaf.grad))
