@@ -856,6 +856,58 @@ void norm_rope_bwd(const Tensor& x, const Tensor& f1, const Tensor& f2, const Te
                       H, T, D, cur_stream());
 }
 
+void rowscale_add_fwd(const c10::optional<Tensor>& a, const Tensor& g, const Tensor& b, Tensor out) {
+  const c10::cuda::CUDAGuard guard(b.device());
+  TORCH_CHECK(b.is_cuda() && b.dim() == 4 && b.scalar_type() == at::kBFloat16 && b.is_contiguous(), "rowscale_add: b bf16 contiguous [batch, T, H, D]");
+  const int H = (int)b.size(2), D = (int)b.size(3);
+  const int64_t rows = b.numel() / D;
+  TORCH_CHECK(g.scalar_type() == at::kBFloat16 && g.is_contiguous() && g.numel() == rows, "rowscale_add: g bf16 [batch * T * H]");
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.is_contiguous() && out.numel() == b.numel(), "rowscale_add: out");
+  const void* ap = nullptr;
+  int64_t st = 0, sh = 0;
+  if (a.has_value()) {
+    TORCH_CHECK(a->scalar_type() == at::kBFloat16 && a->sizes() == b.sizes() && a->stride(3) == 1 &&
+                (a->size(0) == 1 || a->stride(0) == a->size(1) * a->stride(1)), "rowscale_add: a bf16 [batch, T, H, D], unit stride over D");
+    ap = a->data_ptr(); st = a->stride(1); sh = a->stride(2);
+  }
+  b200::rowscale_add_fwd(ap, st, sh, g.data_ptr(), b.data_ptr(), out.data_ptr(), rows, H, D, cur_stream());
+}
+
+void rowscale_add_bwd(const Tensor& g, const Tensor& b, const Tensor& dout, Tensor db, Tensor dg) {
+  const c10::cuda::CUDAGuard guard(b.device());
+  const int D = (int)b.size(-1);
+  const int64_t rows = b.numel() / D;
+  for (const Tensor* t : {&b, &dout, (const Tensor*)&db})
+    TORCH_CHECK(t->scalar_type() == at::kBFloat16 && t->is_contiguous() && t->numel() == rows * D, "rowscale_add_bwd: bf16 contiguous [rows, D]");
+  TORCH_CHECK(g.numel() == rows && dg.numel() == rows && dg.scalar_type() == at::kBFloat16 && g.scalar_type() == at::kBFloat16 && g.is_contiguous() && dg.is_contiguous(), "rowscale_add_bwd: g, dg bf16 [rows]");
+  b200::rowscale_add_bwd(g.data_ptr(), b.data_ptr(), dout.data_ptr(), db.data_ptr(), dg.data_ptr(), rows, D, cur_stream());
+}
+
+static void lincomb_check(const Tensor& t, int64_t n, const char* what) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.is_contiguous() && t.numel() == n, "lincomb3: bf16 contiguous ", what);
+}
+
+void lincomb3_fwd(const Tensor& x, const Tensor& y, const c10::optional<Tensor>& z, const Tensor& c, Tensor out) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int64_t n = x.numel();
+  lincomb_check(x, n, "x"); lincomb_check(y, n, "y"); lincomb_check(out, n, "out");
+  if (z.has_value()) lincomb_check(*z, n, "z");
+  TORCH_CHECK(c.is_cuda() && c.scalar_type() == at::kFloat && c.is_contiguous() && c.numel() >= (z.has_value() ? 3 : 2), "lincomb3: c fp32 on the device");
+  b200::lincomb3_fwd(x.data_ptr(), y.data_ptr(), z.has_value() ? z->data_ptr() : nullptr, c.data_ptr<float>(), out.data_ptr(), n, cur_stream());
+}
+
+void lincomb3_bwd(const Tensor& x, const Tensor& y, const c10::optional<Tensor>& z, const Tensor& c, const Tensor& dout, Tensor dx, Tensor dy,
+                  const c10::optional<Tensor>& dz, Tensor dc) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int64_t n = x.numel();
+  lincomb_check(x, n, "x"); lincomb_check(y, n, "y"); lincomb_check(dout, n, "dout"); lincomb_check(dx, n, "dx"); lincomb_check(dy, n, "dy");
+  TORCH_CHECK(z.has_value() == dz.has_value(), "lincomb3_bwd: z and dz go together");
+  if (z.has_value()) { lincomb_check(*z, n, "z"); lincomb_check(*dz, n, "dz"); }
+  TORCH_CHECK(dc.scalar_type() == at::kFloat && dc.is_contiguous() && dc.numel() >= 3, "lincomb3_bwd: dc fp32 [3], zeroed");
+  b200::lincomb3_bwd(x.data_ptr(), y.data_ptr(), z.has_value() ? z->data_ptr() : nullptr, c.data_ptr<float>(), dout.data_ptr(), dx.data_ptr(),
+                     dy.data_ptr(), dz.has_value() ? dz->data_ptr() : nullptr, dc.data_ptr<float>(), n, cur_stream());
+}
+
 void rms_act_fwd(const Tensor& x, const Tensor& w, Tensor y, Tensor rstd, double eps, int64_t act) {
   const c10::cuda::CUDAGuard guard(x.device());
   const bool xb = norm_io_bf16(x, "x"), yb = norm_io_bf16(y, "y");
@@ -923,6 +975,10 @@ TORCH_LIBRARY(b200, m) {
   m.def("causal_conv1d_silu_bwd(Tensor x, Tensor w, Tensor? bias, Tensor dy, Tensor(a!) dx, Tensor(b!) dw, Tensor(c!)? dbias) -> ()");
   m.def("norm_rope_fwd(Tensor x, Tensor f1, Tensor f2, Tensor(a!) y, Tensor(b!) rstd, float eps) -> ()");
   m.def("norm_rope_bwd(Tensor x, Tensor f1, Tensor f2, Tensor rstd, Tensor dy, Tensor(a!) dx) -> ()");
+  m.def("rowscale_add_fwd(Tensor? a, Tensor g, Tensor b, Tensor(a!) out) -> ()");
+  m.def("rowscale_add_bwd(Tensor g, Tensor b, Tensor dout, Tensor(a!) db, Tensor(b!) dg) -> ()");
+  m.def("lincomb3_fwd(Tensor x, Tensor y, Tensor? z, Tensor c, Tensor(a!) out) -> ()");
+  m.def("lincomb3_bwd(Tensor x, Tensor y, Tensor? z, Tensor c, Tensor dout, Tensor(a!) dx, Tensor(b!) dy, Tensor(c!)? dz, Tensor(d!) dc) -> ()");
   m.def("rms_act_fwd(Tensor x, Tensor w, Tensor(a!) y, Tensor(b!) rstd, float eps, int act) -> ()");
   m.def("rms_act_bwd(Tensor x, Tensor w, Tensor rstd, Tensor dy, Tensor(a!) dx, Tensor(b!) dw, int act) -> ()");
   m.def("tele_fused_fwd(Tensor x, Tensor freq, Tensor phase, Tensor kern, Tensor expo, Tensor(a!) out, int H, int half, float max_rec) -> ()");
@@ -985,6 +1041,10 @@ TORCH_LIBRARY_IMPL(b200, CUDA, m) {
   m.impl("causal_conv1d_silu_bwd", &causal_conv1d_silu_bwd);
   m.impl("norm_rope_fwd", &norm_rope_fwd);
   m.impl("norm_rope_bwd", &norm_rope_bwd);
+  m.impl("rowscale_add_fwd", &rowscale_add_fwd);
+  m.impl("rowscale_add_bwd", &rowscale_add_bwd);
+  m.impl("lincomb3_fwd", &lincomb3_fwd);
+  m.impl("lincomb3_bwd", &lincomb3_bwd);
   m.impl("rms_act_fwd", &rms_act_fwd);
   m.impl("rms_act_bwd", &rms_act_bwd);
   m.impl("tele_fused_fwd", &tele_fused_fwd);

@@ -87,6 +87,14 @@ void norm_rope_fwd(const void* x, long long st, long long sh, const void* f1, co
 void norm_rope_bwd(const void* x, long long st, long long sh, const void* f1, const void* f2, int tab_w, const float* rstd,
                    const void* dy, void* dx, long long rows, int H, int T, int D, cudaStream_t s);
 
+// ---- row-scaled add and three-term linear combination (rowops.cu); all activations bf16
+void rowscale_add_fwd(const void* a, long long st, long long sh, const void* g, const void* b, void* out, long long rows, int H,
+                      int D, cudaStream_t s);
+void rowscale_add_bwd(const void* g, const void* b, const void* dout, void* db, void* dg, long long rows, int D, cudaStream_t s);
+void lincomb3_fwd(const void* x, const void* y, const void* z, const float* c, void* out, long long n, cudaStream_t s);
+void lincomb3_bwd(const void* x, const void* y, const void* z, const float* c, const void* dout, void* dx, void* dy, void* dz,
+                  float* dc, long long n, cudaStream_t s);
+
 // ---- NorMuon (normuon.cu) ---------------------------------------------------------------------
 // v : stack [nmat][R][C] (bf16 or fp32). red_cols != 0: statistics per row (reduced over the C columns), else per column.
 // stat : scratch [nmat][R or C], receives the per-row / per-column scale; second : running second moment, same shape.

@@ -22,6 +22,7 @@ from ..ops.fp8_linear import CastedLinearT
 from ..ops.fused import softcapped_cross_entropy
 from ..ops.linear import linear, linear_t
 from ..ops.norm_rope import norm_rotary
+from ..ops.rowops import lincomb3, rowscale_add
 
 BLOCK = 128  # attention block / window granularity in tokens
 
@@ -139,23 +140,23 @@ class CausalSelfAttention(nn.Module):
         q, k, v = linear(x, a.sa_lambdas[0] * qkvo_w[:self.dim * 3].type_as(x)).view(B, T, 3 * H, D).chunk(3, dim=-2)
         gate_in = x[..., :12]
         f1, f2 = a.yarn.factor1, a.yarn.factor2          # QK norm and the rotary map are one kernel on CUDA
+        # value-embedding mix v + 2 sigmoid(gate) * ve: one kernel in the [T, H, D] layout (reinterpreting the result as
+        # [2T, H/2, D] afterwards is the same flat order the reference mixes in)
+        if a.ve is not None:
+            v = rowscale_add(v, 2 * torch.sigmoid(F.linear(gate_in, a.ve_gate_w)).view(B, T, H), a.ve.view(B, T, H, D))
         if self.paired:
             # [T, H, D] reinterpreted as [2T, H/2, D] exactly as the reference does (a flat view: head h of token t lands at
             # position 2t + h // (H/2) of head h % (H/2)); rotary angles come from the paired table (positions 2t, 2t+1)
             q = norm_rotary(q, f1, f2).view(B, 2 * T, H // 2, D)
             k = norm_rotary(k, f1, f2).view(B, 2 * T, H // 2, D)
             v = v.reshape(B, 2 * T, H // 2, D)
-            if a.ve is not None:
-                v = v + 2 * torch.sigmoid(F.linear(gate_in, a.ve_gate_w)).view(B, 2 * T, H // 2, 1) * a.ve.view_as(v)
             y = _attend(q[0], k[0], v[0], a.seqlens, a.bm_size, a.yarn.attn_scale, 2)
         else:
             q, k = norm_rotary(q, f1, f2), norm_rotary(k, f1, f2)
             if a.key_offset:  # shift the stationary half of the key one token forward: one-layer induction
                 k = torch.cat([k[..., :D // 2], torch.cat([k[:, :1, :, D // 2:], k[:, :-1, :, D // 2:]], dim=1)], dim=-1)
-            if a.ve is not None:
-                v = v + 2 * torch.sigmoid(F.linear(gate_in, a.ve_gate_w)).view(B, T, H, 1) * a.ve.view_as(v)
             y = _attend(q[0], k[0], v[0], a.seqlens, a.bm_size, a.yarn.attn_scale, 1)
-        y = y.reshape(B, T, H, D) * torch.sigmoid(F.linear(gate_in, a.attn_gate_w)).view(B, T, H, 1)
+        y = rowscale_add(None, torch.sigmoid(F.linear(gate_in, a.attn_gate_w)).view(B, T, H), y.reshape(B, T, H, D))
         return linear(y.reshape(B, T, H * D), a.sa_lambdas[1] * qkvo_w[self.dim * 3:].type_as(y))
 
 
@@ -284,10 +285,10 @@ class GPT(nn.Module):
                             key_offset[i], attn_gates[i], ve_gates[i])
             if i == 6:
                 x = x + torch.sigmoid(skip_l) * 2 * torch.sigmoid(self.skip_gate(x0[..., :12])) * skips.pop()
-            if i == 0:
-                x = (resid[0] + self.x0_lambdas[0]) * x + bigram_l[0] * x0_bigram
+            if i == 0:   # x is x0 here: its two coefficients add up
+                x = lincomb3(x, x0_bigram, None, torch.stack([resid[0] + self.x0_lambdas[0], bigram_l[0]]))
             else:
-                x = resid[i] * x + self.x0_lambdas[i] * x0 + bigram_l[i] * x0_bigram
+                x = lincomb3(x, x0, x0_bigram, torch.stack([resid[i], self.x0_lambdas[i], bigram_l[i]]))
             x = self.blocks[i](x, args, attn_w[self.layer_to_attn_idx[i]] if i in self.layer_to_attn_idx else None,
                                fcs[self.layer_to_mlp_idx[i]], projs[self.layer_to_mlp_idx[i]])
             if i == 3:

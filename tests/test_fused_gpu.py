@@ -235,3 +235,47 @@ def test_norm_rotary_kernel_matches_the_eager_composition(D, H, paired, strided)
     (yr * w).sum().backward()
     rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm()).item()
     assert rel(y, yr) < 1e-2 and rel(leaf.grad, ref_leaf.grad) < 1e-2, (rel(y, yr), rel(leaf.grad, ref_leaf.grad))
+
+
+@pytest.mark.parametrize("D,with_a", [(128, True), (64, True), (128, False)])
+def test_rowscale_add_kernel(D, with_a):
+    from ml_experiments_b200.ops.rowops import rowscale_add
+
+    torch.manual_seed(1)
+    B, T, H = 1, 257, 6
+    qkv = torch.randn(B, T, 3 * H, D, device="cuda").bfloat16().requires_grad_(True)
+    g = torch.rand(B, T, H, device="cuda").bfloat16().requires_grad_(True)
+    b = torch.randn(B, T, H, D, device="cuda").bfloat16().requires_grad_(True)
+    a = qkv.chunk(3, dim=-2)[2] if with_a else None          # the strided v slice of a fused projection
+    out = rowscale_add(a, g, b)
+    w = torch.randn_like(out.float())
+    (out.float() * w).sum().backward()
+    got = [t.grad.clone() for t in (qkv, g, b)] if with_a else [None, g.grad.clone(), b.grad.clone()]
+    q2, g2, b2 = (t.detach().float().requires_grad_(True) for t in (qkv, g, b))
+    ref = (q2.chunk(3, dim=-2)[2] if with_a else 0) + g2.unsqueeze(-1) * b2
+    (ref * w).sum().backward()
+    rel = lambda x, y: ((x.float() - y.float()).norm() / y.float().norm().clamp_min(1e-12)).item()
+    assert rel(out, ref) < 1e-2
+    for x, y in zip(got, (q2.grad, g2.grad, b2.grad)):
+        if x is not None:
+            assert rel(x, y) < 1e-2
+
+
+@pytest.mark.parametrize("terms", [2, 3])
+def test_lincomb3_kernel(terms):
+    from ml_experiments_b200.ops.rowops import lincomb3
+
+    torch.manual_seed(2)
+    xs = [torch.randn(1, 1000, 768, device="cuda").bfloat16().requires_grad_(True) for _ in range(terms)]
+    c = torch.tensor([0.7, -1.3, 0.4][:terms], device="cuda", requires_grad=True)
+    out = lincomb3(xs[0], xs[1], xs[2] if terms == 3 else None, c)
+    w = torch.randn_like(out.float())
+    (out.float() * w).sum().backward()
+    xr = [t.detach().float().requires_grad_(True) for t in xs]
+    cr = c.detach().clone().requires_grad_(True)
+    ref = sum(cr[i] * xr[i] for i in range(terms))
+    (ref * w).sum().backward()
+    rel = lambda x, y: ((x.float() - y.float()).norm() / y.float().norm().clamp_min(1e-12)).item()
+    assert rel(out, ref) < 1e-2 and rel(c.grad, cr.grad) < 1e-2
+    for t, r in zip(xs, xr):
+        assert rel(t.grad, r.grad) < 1e-2
