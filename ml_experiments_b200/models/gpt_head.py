@@ -20,7 +20,7 @@ import torch.nn.functional as F
 from ..ops.attention import attention_reference, flash_attention
 from ..ops.fp8_linear import CastedLinearT
 from ..ops.fused import softcapped_cross_entropy
-from ..ops.linear import linear, linear_t
+from ..ops.linear import linear, linear_t, mlp_relu2
 from ..ops.norm_rope import norm_rotary
 from ..ops.rowops import lincomb3, rowscale_add
 
@@ -137,7 +137,7 @@ class CausalSelfAttention(nn.Module):
         B, T = x.shape[:2]
         assert B == 1, "packed variable-length sequences need B == 1"
         H, D = self.num_heads, self.head_dim
-        q, k, v = linear(x, a.sa_lambdas[0] * qkvo_w[:self.dim * 3].type_as(x)).view(B, T, 3 * H, D).chunk(3, dim=-2)
+        q, k, v = linear(x, a.sa_lambdas[0] * qkvo_w[:self.dim * 3].type_as(x)).view(B, T, 3, H, D).unbind(2)   # unbind: one stack in the backward
         gate_in = x[..., :12]
         f1, f2 = a.yarn.factor1, a.yarn.factor2          # QK norm and the rotary map are one kernel on CUDA
         # value-embedding mix v + 2 sigmoid(gate) * ve: one kernel in the [T, H, D] layout (reinterpreting the result as
@@ -168,8 +168,7 @@ class PairedHeadCausalSelfAttention(CausalSelfAttention):
 class MLP(nn.Module):
     def forward(self, x, c_fc, c_proj):
         """``relu(x @ c_fc.T)^2 @ c_proj`` with both weights stored ``[4 d, d]``."""
-        h = linear(x, c_fc.type_as(x), relu2=True)
-        return linear_t(h, c_proj.type_as(x))
+        return mlp_relu2(x, c_fc.type_as(x), c_proj.type_as(x))
 
 
 class Block(nn.Module):

@@ -15,7 +15,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops.fused import softcapped_cross_entropy
-from ..ops.linear import linear, linear_t
+from ..ops.linear import linear, linear_t, mlp_relu2
 from ..ops.norm_rope import norm_rotary
 from .gpt import CastedLinear
 from .gpt_head import BLOCK, ForwardScheduleConfig, Yarn, _attend, next_multiple_of_n, norm
@@ -54,7 +54,7 @@ class CausalSelfAttention(nn.Module):
         B, T = x.shape[:2]
         assert B == 1, "packed variable-length sequences need B == 1"
         H, D = self.num_heads, self.head_dim
-        q, k, v = linear(x, sa_lambdas[0] * self.qkvo_w[: self.dim * 3].type_as(x)).view(B, T, 3 * H, D).chunk(3, dim=-2)
+        q, k, v = linear(x, sa_lambdas[0] * self.qkvo_w[: self.dim * 3].type_as(x)).view(B, T, 3, H, D).unbind(2)
         q, k = norm_rotary(q, yarn.factor1, yarn.factor2), norm_rotary(k, yarn.factor1, yarn.factor2)
         if key_offset:  # the two stationary quarter-bands of the key move one token forward
             prev = torch.cat([k[:, :1], k[:, :-1]], dim=1)
@@ -78,7 +78,7 @@ class MLP(nn.Module):
         self.c_proj = _label(nn.Parameter(torch.zeros(4 * dim, dim)), "mlp", lr_mul=2.0)
 
     def forward(self, x):
-        return linear_t(linear(x, self.c_fc.type_as(x), relu2=True), self.c_proj.type_as(x))
+        return mlp_relu2(x, self.c_fc.type_as(x), self.c_proj.type_as(x))
 
 
 class Block(nn.Module):

@@ -33,7 +33,7 @@ class _Linear(torch.autograd.Function):
         x16, w16, h = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.shape[-1]).to(torch.bfloat16).contiguous()
         if ctx.epilogue == G.EPI_RELU2:  # d relu(z)^2 / dz = 2 relu(z) = 2 sqrt(h)
-            dy2 = (dy2.float() * 2 * h.float().sqrt()).to(torch.bfloat16)
+            dy2 = dy2 * h.sqrt().mul_(2)
         dx = dw = None
         if ctx.needs_input_grad[0]:
             dx = G.gemm(dy2, w16, b_mn=True).view(ctx.x_shape).to(ctx.x_dtype)
@@ -85,3 +85,43 @@ def linear_t(x: torch.Tensor, w_t: torch.Tensor) -> torch.Tensor:
     if not (x.is_cuda and w_t.shape[0] % 8 == 0 and w_t.shape[1] % 8 == 0 and x.numel() > 0):
         return x @ w_t.to(x.dtype)
     return _LinearT.apply(x, w_t)
+
+
+class _MlpRelu2(torch.autograd.Function):
+    """``relu(x @ Wfc.T)^2 @ Wproj`` (both weights stored ``[hidden, d]``) as one autograd node: four GEMMs in the
+    backward, the ``2 relu(z)`` factor of the activation applied in the epilogue of the first of them, so no
+    elementwise pass over the ``[T, hidden]`` tensors is left (a chain of two separate nodes has to form
+    ``dh * 2 sqrt(h)`` with PyTorch operators between its GEMMs)."""
+
+    @staticmethod
+    def forward(ctx, x, w_fc, w_proj):
+        to16 = lambda t: (t if t.dtype == torch.bfloat16 else t.to(torch.bfloat16)).contiguous()
+        x16, fc16, pj16 = to16(x.reshape(-1, x.shape[-1])), to16(w_fc), to16(w_proj)
+        h = G.gemm(x16, fc16, epilogue=G.EPI_RELU2)
+        y = G.gemm(h, pj16, b_mn=True)
+        ctx.save_for_backward(x16, fc16, pj16, h)
+        ctx.x_shape, ctx.dtypes = x.shape, (x.dtype, w_fc.dtype, w_proj.dtype)
+        return y.view(*x.shape[:-1], w_proj.shape[1])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x16, fc16, pj16, h = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1]).to(torch.bfloat16).contiguous()
+        dpre = G.gemm(dy2, pj16, epilogue=G.EPI_RELU2_BWD, aux=h)            # (dy @ Wproj.T) * 2 relu(z)
+        dx = dfc = dpj = None
+        if ctx.needs_input_grad[2]:
+            dpj = G.gemm(h, dy2, a_mn=True, b_mn=True, split_k=G.auto_split_k(pj16.shape[0], pj16.shape[1], h.shape[0]),
+                         out_dtype=torch.float32).to(ctx.dtypes[2])
+        if ctx.needs_input_grad[0]:
+            dx = G.gemm(dpre, fc16, b_mn=True).view(ctx.x_shape).to(ctx.dtypes[0])
+        if ctx.needs_input_grad[1]:
+            dfc = G.gemm(dpre, x16, a_mn=True, b_mn=True, split_k=G.auto_split_k(fc16.shape[0], fc16.shape[1], x16.shape[0]),
+                         out_dtype=torch.float32).to(ctx.dtypes[1])
+        return dx, dfc, dpj
+
+
+def mlp_relu2(x: torch.Tensor, w_fc: torch.Tensor, w_proj: torch.Tensor) -> torch.Tensor:
+    """``relu(x @ w_fc.T)**2 @ w_proj`` with ``w_fc, w_proj`` of shape ``(hidden, d)``."""
+    if not (_ok(x, w_fc) and w_proj.shape[1] % 8 == 0 and w_fc.shape == w_proj.shape):
+        return F.relu(F.linear(x, w_fc.to(x.dtype))).square() @ w_proj.to(x.dtype)
+    return _MlpRelu2.apply(x, w_fc, w_proj)

@@ -279,3 +279,22 @@ def test_lincomb3_kernel(terms):
     assert rel(out, ref) < 1e-2 and rel(c.grad, cr.grad) < 1e-2
     for t, r in zip(xs, xr):
         assert rel(t.grad, r.grad) < 1e-2
+
+
+def test_mlp_relu2_node_matches_autograd():
+    from ml_experiments_b200.ops.linear import mlp_relu2
+
+    torch.manual_seed(3)
+    x = (torch.randn(1, 512, 256, device="cuda") * 0.5).bfloat16().requires_grad_(True)
+    wf = (torch.randn(1024, 256, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    wp = (torch.randn(1024, 256, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    y = mlp_relu2(x, wf, wp)
+    w = torch.randn_like(y.float())
+    (y.float() * w).sum().backward()
+    xr, fr, pr = (t.detach().float().requires_grad_(True) for t in (x, wf, wp))
+    yr = torch.relu(xr @ fr.T).square() @ pr
+    (yr * w).sum().backward()
+    rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm()).item()
+    assert rel(y, yr) < 2e-2
+    for a, b in ((x.grad, xr.grad), (wf.grad, fr.grad), (wp.grad, pr.grad)):
+        assert rel(a, b) < 2e-2, rel(a, b)
