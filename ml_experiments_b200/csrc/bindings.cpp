@@ -308,6 +308,17 @@ void axpy_bf16_to_f32(Tensor p, const Tensor& u, const c10::optional<Tensor>& p_
 }
 
 
+void adam_cautious(Tensor p, const Tensor& g, Tensor m, Tensor v, double b1, double b2, double eps, double step_size, double wd_lr) {
+  const c10::cuda::CUDAGuard guard(p.device());
+  const bool pb = p.scalar_type() == at::kBFloat16, gb = g.scalar_type() == at::kBFloat16;
+  TORCH_CHECK(p.is_cuda() && p.is_contiguous() && g.is_contiguous() && m.is_contiguous() && v.is_contiguous(), "adam_cautious: contiguous CUDA tensors");
+  TORCH_CHECK((pb || p.scalar_type() == at::kFloat) && (gb || g.scalar_type() == at::kFloat), "adam_cautious: p, g bf16 or fp32");
+  TORCH_CHECK(m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat && g.numel() == p.numel() && m.numel() == p.numel() && v.numel() == p.numel(),
+              "adam_cautious: fp32 moments of p's size");
+  b200::adam_cautious(p.data_ptr(), pb, g.data_ptr(), gb, m.data_ptr<float>(), v.data_ptr<float>(), p.numel(), (float)b1, (float)b2, (float)eps,
+                      (float)step_size, (float)wd_lr, cur_stream());
+}
+
 void normuon_scales(const Tensor& v, Tensor stat, Tensor second, bool red_cols, double beta2) {
   const c10::cuda::CUDAGuard guard(v.device());
   TORCH_CHECK(v.dim() == 3 && v.is_contiguous(), "normuon_scales: v [nmat, R, C] contiguous");
@@ -949,6 +960,7 @@ TORCH_LIBRARY(b200, m) {
   m.def("cast_fp8(Tensor x, Tensor(a!) out, float scale) -> ()");
   m.def("softcap_ce(Tensor logits, Tensor targets, Tensor(a!) loss_rows, Tensor(b!)? grad, float cap, float div, float loss_scale, float grad_scale, float shift=0.0, Tensor? mtp_w=None) -> ()");
   m.def("adam_step(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, float lr, float beta1, float beta2, float eps, float wd, float bias1, float bias2, float grad_scale, Tensor(d!)? shadow=None, float shadow_scale=1.0) -> ()");
+  m.def("adam_cautious(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, float b1, float b2, float eps, float step_size, float wd_lr) -> ()");
   m.def("normuon_scales(Tensor v, Tensor(a!) stat, Tensor(b!) second, bool red_cols, float beta2) -> ()");
   m.def("normuon_update(Tensor(a!) p, Tensor(b!)? mant, Tensor v, Tensor? scale, bool scale_per_row, float lr, float wd_lr, Tensor? lr_mat=None, Tensor? wd_mat=None) -> ()");
   m.def("muon_momentum(Tensor g, Tensor(a!) buf, Tensor(b!) out, Tensor(c!) sumsq, float mu, bool nesterov, float grad_scale) -> ()");
@@ -1015,6 +1027,7 @@ TORCH_LIBRARY_IMPL(b200, CUDA, m) {
   m.impl("cast_fp8", &cast_fp8);
   m.impl("softcap_ce", &softcap_ce);
   m.impl("adam_step", &adam_step);
+  m.impl("adam_cautious", &adam_cautious);
   m.impl("normuon_scales", &normuon_scales);
   m.impl("normuon_update", &normuon_update);
   m.impl("muon_momentum", &muon_momentum);

@@ -102,6 +102,8 @@ void normuon_scales(const void* v, int v_is_bf16, float* stat, float* second, in
                     float beta2, cudaStream_t s);
 // p -= p * [u * p >= 0] * wd_lr + u * lr with u = v * scale (scale may be null). p fp32, or bf16 with an optional
 // uint16 mantissa buffer (p and mant together are one fp32 number). lr_mat / wd_mat (optional): values per matrix.
+void adam_cautious(void* p, int p_is_bf16, const void* g, int g_is_bf16, float* m, float* v, long long n, float b1, float b2,
+                   float eps, float step_size, float wd_lr, cudaStream_t s);
 void normuon_update(void* p, int p_is_bf16, unsigned short* mant, const void* v, int v_is_bf16, const float* scale,
                     int nmat, int R, int C, int scale_per_row, float lr, float wd_lr, const float* lr_mat,
                     const float* wd_mat, cudaStream_t s);

@@ -148,7 +148,39 @@ void chk(const char* what) {
   if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
 }
 
+
+// Adam with the cautious weight decay of the combined optimizer (modded-nanogpt/train_gpt.py:654-691): moments in fp32,
+//   upd = m / (sqrt(v) + eps) * step_size;  upd += p * [upd * p > 0] * wd_lr;  p -= upd      (one pass over p, g, m, v)
+template <typename TP, typename TG>
+__global__ void adam_cautious_kernel(TP* __restrict__ p, const TG* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
+                                     long long n, float b1, float b2, float eps, float step_size, float wd_lr) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float gi = ldf(g + i), pi = ldf(p + i);
+    const float mi = b1 * m[i] + (1.f - b1) * gi;
+    const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
+    m[i] = mi;
+    v[i] = vi;
+    float upd = mi / (sqrtf(vi) + eps) * step_size;
+    if (upd * pi > 0.f) upd += pi * wd_lr;
+    p[i] = (TP)(pi - upd);
+  }
+}
+
 }  // namespace
+
+void adam_cautious(void* p, int p_is_bf16, const void* g, int g_is_bf16, float* m, float* v, long long n, float b1, float b2,
+                   float eps, float step_size, float wd_lr, cudaStream_t s) {
+  if (n <= 0) return;
+  long long bl = (n + 255) / 256;
+  if (bl > 148 * 16) bl = 148 * 16;
+#define AC(TP, TG) adam_cautious_kernel<TP, TG><<<(int)bl, 256, 0, s>>>((TP*)p, (const TG*)g, m, v, n, b1, b2, eps, step_size, wd_lr)
+  if (p_is_bf16 && g_is_bf16) AC(bf16, bf16);
+  else if (p_is_bf16) AC(bf16, float);
+  else if (g_is_bf16) AC(float, bf16);
+  else AC(float, float);
+#undef AC
+  chk("adam_cautious");
+}
 
 void normuon_scales(const void* v, int v_is_bf16, float* stat, float* second, int nmat, int R, int C, int red_cols,
                     float beta2, cudaStream_t s) {

@@ -129,6 +129,16 @@ def cautious_update_(p: torch.Tensor, mantissa: torch.Tensor | None, upd: torch.
 
 
 def adam_cautious_(p, g, exp_avg, exp_avg_sq, beta1, beta2, eps, step_size, wd_lr) -> None:
+    """Adam step with the decay applied only where it agrees in sign with the update. One kernel on CUDA
+    (``csrc/fused/normuon.cu::adam_cautious_kernel``: p and g bf16 or fp32, fp32 moments), the operator chain elsewhere."""
+    if (p.is_cuda and p.is_contiguous() and g.is_contiguous() and p.dtype in (torch.bfloat16, torch.float32)
+            and g.dtype in (torch.bfloat16, torch.float32) and exp_avg.dtype == torch.float32 and exp_avg.is_contiguous()
+            and exp_avg_sq.dtype == torch.float32 and exp_avg_sq.is_contiguous() and g.shape == p.shape):
+        from ..ops.runtime import add_launches, ops
+        ops().adam_cautious(p, g, exp_avg, exp_avg_sq, float(beta1), float(beta2), float(eps), float(step_size), float(wd_lr))
+        add_launches(1)
+        return
+    g = g.float()
     exp_avg.mul_(beta1).add_(g, alpha=1 - beta1)
     exp_avg_sq.mul_(beta2).addcmul_(g, g, value=1 - beta2)
     upd = exp_avg / (exp_avg_sq.sqrt() + eps) * step_size
@@ -257,7 +267,7 @@ class NorMuonAndAdam:
         p_slice = self._shard(label, self._view(label))
         # the decay is scheduled by the learning rate twice: lr_eff**2 * weight_decay * wd_mul
         # (modded-nanogpt/train_gpt.py:658-672)
-        adam_cautious_(p_slice, g.float(), st["exp_avg"], st["exp_avg_sq"], b1, b2, cfg.eps, step_size,
+        adam_cautious_(p_slice, g, st["exp_avg"], st["exp_avg_sq"], b1, b2, cfg.eps, step_size,
                        lr * lr * cfg.weight_decay * cfg.wd_mul)
 
     def _normuon(self, label: str, g: torch.Tensor) -> None:
@@ -441,7 +451,7 @@ class DistAdam(torch.optim.Optimizer):
                 t = st["step"]
                 # lr = group lr * param.lr_mul ; decay = lr * wd * wd_mul * lr (modded-nanogpt/train_gpt_medium.py:805-826)
                 lr = hp["lr"] * getattr(p, "lr_mul", 1.0)
-                adam_cautious_(p_slice, g.float(), st["exp_avg"], st["exp_avg_sq"], b1, b2, hp["eps"],
+                adam_cautious_(p_slice, g, st["exp_avg"], st["exp_avg_sq"], b1, b2, hp["eps"],
                                lr * math.sqrt(1 - b2 ** t) / (1 - b1 ** t),
                                lr * lr * hp["weight_decay"] * getattr(p, "wd_mul", 1.0))
                 if sharded:

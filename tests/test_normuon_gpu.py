@@ -69,3 +69,23 @@ def test_combined_optimizer_runs_on_the_kernels():
         # bf16 Newton-Schulz on different back ends (tcgen05 vs CPU matmul) differs in the last bits; three steps of
         # lr 0.023 * O(0.1) updates stay within a few 1e-3
         assert torch.allclose(pg[k].detach().float().cpu(), pc[k].detach().float(), atol=5e-3), (k, (pg[k].detach().float().cpu() - pc[k].detach().float()).abs().max())
+
+
+@pytest.mark.parametrize("p_dtype,g_dtype", [(torch.bfloat16, torch.bfloat16), (torch.float32, torch.bfloat16), (torch.float32, torch.float32)])
+def test_adam_cautious_kernel_matches_the_operator_chain(p_dtype, g_dtype):
+    from ml_experiments_b200.optim.normuon import adam_cautious_
+
+    torch.manual_seed(4)
+    n = (1000, 96)
+    p0 = (torch.randn(*n, device="cuda") * 0.3).to(p_dtype)
+    m0, v0 = torch.randn(*n, device="cuda") * 1e-3, torch.rand(*n, device="cuda") * 1e-5
+    for _ in range(2):
+        g = (torch.randn(*n, device="cuda") * 1e-2).to(g_dtype)
+        p, m, v = p0.clone(), m0.clone(), v0.clone()
+        adam_cautious_(p, g, m, v, 0.75, 0.95, 1e-10, 3e-3, 2e-4)                      # kernel
+        q, mr, vr = p0.float().cpu(), m0.cpu(), v0.cpu()
+        adam_cautious_(q, g.float().cpu(), mr, vr, 0.75, 0.95, 1e-10, 3e-3, 2e-4)      # operator chain (CPU, fp32)
+        assert torch.allclose(m.cpu(), mr, rtol=1e-5, atol=1e-9) and torch.allclose(v.cpu(), vr, rtol=1e-5, atol=1e-12)
+        want = q.to(p_dtype).float()
+        assert torch.allclose(p.float().cpu(), want, rtol=1e-2 if p_dtype == torch.bfloat16 else 1e-5, atol=1e-6)
+        p0, m0, v0 = p, m, v
