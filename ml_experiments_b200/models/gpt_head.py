@@ -18,7 +18,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops.attention import attention_reference, flash_attention
-from ..ops.fp8_linear import CastedLinearT
+from ..ops.fp8_linear import CastedLinearT, head_ce_loss
 from ..ops.fused import softcapped_cross_entropy
 from ..ops.linear import linear, linear_t, mlp_relu2
 from ..ops.norm_rope import norm_rotary
@@ -295,7 +295,10 @@ class GPT(nn.Module):
             if i == 7:
                 x_backout = x
         x = norm(x - backout_l * x_backout)
-        logits = self.lm_head(x)
+        head = self.lm_head
+        if self.training and head.use_fp8 and x.is_cuda:      # projection + loss as one node (no [T, V] gradient passes)
+            return head_ce_loss(x.flatten(0, -2), head.weight, target_seq, schedule_cfg.mtp_weights, head.x_s, head.w_s, head.grad_s)
+        logits = head(x)
         if self.training:
             return softcapped_cross_entropy(logits.view(-1, logits.size(-1)), target_seq, schedule_cfg.mtp_weights).sum()
         z = 23 * torch.sigmoid((logits.float() + 5) / 7.5)

@@ -36,6 +36,47 @@ class _MMT(torch.autograd.Function):
         return grad_x, grad_w, None, None, None
 
 
+class _HeadCE(torch.autograd.Function):
+    """fp8 output projection and the soft-capped multi-token cross entropy as ONE autograd node returning the summed
+    loss. The loss kernel writes ``dL/dlogits / grad_s`` straight in e5m2 while it computes the loss, so between the
+    three GEMMs there is no bf16 gradient of the logits, no cast pass over it and no ``[T, V] x [T, 1]`` multiply by the
+    incoming gradient: the node's incoming gradient is a scalar and scales the two small results instead."""
+
+    @staticmethod
+    def forward(ctx, x, w, targets, mtp_weights, x_s, w_s, grad_s, A, B, C):
+        x8 = Fz.cast_fp8(x.contiguous(), 1.0 / x_s, torch.float8_e4m3fn)
+        w8 = Fz.cast_fp8(w.contiguous(), 1.0 / w_s, torch.float8_e4m3fn)
+        logits = G.gemm(x8, w8, b_mn=True, alpha=x_s * w_s)
+        g8 = torch.empty(logits.shape, dtype=torch.float8_e5m2, device=x.device)
+        mw = None if mtp_weights is None else mtp_weights.float().contiguous()
+        rows = Fz.softcap_ce(logits, targets.contiguous(), grad_out=g8, cap=A, div=C, shift=B, grad_scale=1.0 / grad_s, mtp_weights=mw)
+        ctx.save_for_backward(x8, w8, g8)
+        ctx.scales = (x_s, w_s, grad_s)
+        return rows.sum()
+
+    @staticmethod
+    def backward(ctx, gout):
+        x8, w8, g8 = ctx.saved_tensors
+        x_s, w_s, grad_s = ctx.scales
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = G.gemm(g8, w8, alpha=grad_s * w_s)
+            dx = dx * gout.to(dx.dtype)
+        if ctx.needs_input_grad[1]:
+            dw = G.gemm(x8, g8, a_mn=True, b_mn=True, out_dtype=torch.float32, alpha=x_s * grad_s)
+            dw = dw * gout.float()
+        return dx, dw, None, None, None, None, None, None, None, None
+
+
+def head_ce_loss(x, w, targets, mtp_weights=None, x_s: float = 1.0, w_s: float = 1.0, grad_s: float = 1.0,
+                 A: float = 23.0, B: float = 5.0, C: float = 7.5) -> torch.Tensor:
+    """``sum_t loss_t`` of ``softcapped_cross_entropy(x @ w, targets, mtp_weights)`` with ``w [K, V]``: the fused node on a
+    GPU (bf16 ``x``, K and V multiples of 16), the two separate operators elsewhere."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and w.shape[0] % 16 == 0 and w.shape[1] % 16 == 0:
+        return _HeadCE.apply(x, w.to(torch.bfloat16), targets, mtp_weights, float(x_s), float(w_s), float(grad_s), A, B, C)
+    return Fz.softcapped_cross_entropy(x @ w.to(x.dtype), targets, mtp_weights, A, B, C).sum()
+
+
 def mm_t(x: torch.Tensor, w: torch.Tensor, x_s: float = 1.0, w_s: float = 1.0, grad_s: float = 1.0) -> torch.Tensor:
     """``x [M, K] @ w [K, N]`` in fp8 on a GPU (K and N multiples of 16); plain matmul elsewhere."""
     if x.is_cuda and x.dtype == torch.bfloat16 and w.shape[0] % 16 == 0 and w.shape[1] % 16 == 0:

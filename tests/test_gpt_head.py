@@ -220,3 +220,31 @@ def test_medium_track_model_gpu_matches_cpu_and_steps():
         opt.step()
         losses.append(loss.item())
     assert all(l == l for l in losses) and losses[-1] < losses[0] - 0.05, losses
+
+
+@pytest.mark.gpu
+def test_fused_head_and_loss_node_matches_the_two_operators():
+    """fp8 projection + multi-token loss as one node against ``mm_t`` followed by ``softcapped_cross_entropy`` (same
+    quantisation of x and w; the logit gradient is quantised to e5m2 before the incoming 1 / T instead of after it)."""
+    from ml_experiments_b200.ops.fp8_linear import head_ce_loss, mm_t
+    from ml_experiments_b200.ops.fused import softcapped_cross_entropy
+
+    torch.manual_seed(5)
+    T, K, V = 1024, 256, 2048
+    x0 = torch.randn(T, K, device="cuda").bfloat16()
+    w0 = (torch.randn(K, V, device="cuda") * 0.05).bfloat16()
+    tg = torch.randint(0, V, (T,), device="cuda")
+    mw = torch.tensor([1.0, 0.5, 0.25], device="cuda")
+    scales = dict(x_s=100 / 448, w_s=1.6 / 448, grad_s=0.75 / 448)
+    outs = []
+    for fused in (True, False):
+        x, w = x0.clone().requires_grad_(True), w0.clone().requires_grad_(True)
+        if fused:
+            loss = head_ce_loss(x, w, tg, mw, **scales) / T
+        else:
+            loss = softcapped_cross_entropy(mm_t(x, w, **scales), tg, mw).sum() / T
+        loss.backward()
+        outs.append((loss.item(), x.grad.float(), w.grad.float()))
+    (l1, dx1, dw1), (l2, dx2, dw2) = outs
+    rel = lambda a, b: ((a - b).norm() / b.norm()).item()
+    assert abs(l1 - l2) < 1e-3 * abs(l2) and rel(dx1, dx2) < 8e-2 and rel(dw1, dw2) < 8e-2, (l1, l2, rel(dx1, dx2), rel(dw1, dw2))
