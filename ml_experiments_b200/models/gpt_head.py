@@ -19,7 +19,7 @@ import torch.nn.functional as F
 
 from ..ops.attention import attention_reference, flash_attention
 from ..ops.fp8_linear import CastedLinearT, head_ce_loss
-from ..ops.fused import softcapped_cross_entropy
+from ..ops.fused import embedding, softcapped_cross_entropy
 from ..ops.linear import linear, linear_t, mlp_relu2
 from ..ops.norm_rope import norm_rotary
 from ..ops.rowops import lincomb3, rowscale_add
@@ -265,9 +265,9 @@ class GPT(nn.Module):
             bm[i] = long_bm
         bm[6] = None
         key_offset = [b == long_bm for b in bm]
-        x = self.embed(input_seq)
-        x0_bigram = self.bigram_embed(bigram_input_seq)[None]
-        ve = [e(input_seq) for e in self.value_embeds]
+        x = embedding(input_seq, self.embed.weight)
+        x0_bigram = embedding(bigram_input_seq, self.bigram_embed.weight)[None]
+        ve = [embedding(input_seq, e.weight) for e in self.value_embeds]
         ve = [ve[0], ve[1]] + [None] * (L - 5) + [ve[2], ve[3], ve[4]]
         smear = smear_l * torch.sigmoid(self.smear_gate(x[1:, :12]))
         x = torch.cat([x[:1], x[1:] + smear * x[:-1]])

@@ -298,3 +298,20 @@ def test_mlp_relu2_node_matches_autograd():
     assert rel(y, yr) < 2e-2
     for a, b in ((x.grad, xr.grad), (wf.grad, fr.grad), (wp.grad, pr.grad)):
         assert rel(a, b) < 2e-2, rel(a, b)
+
+
+def test_embedding_op_matches_torch():
+    from ml_experiments_b200.ops.fused import embedding
+
+    torch.manual_seed(6)
+    table = torch.randn(3000, 768, device="cuda").bfloat16().requires_grad_(True)
+    idx = torch.randint(0, 3000, (4096,), device="cuda")
+    idx[:64] = 7                                               # a heavily repeated row
+    out = embedding(idx, table)
+    w = torch.randn_like(out.float()).bfloat16()
+    (out.float() * w.float()).sum().backward()
+    ref_t = table.detach().float().requires_grad_(True)
+    ref = torch.nn.functional.embedding(idx, ref_t)
+    (ref * w.float()).sum().backward()
+    assert torch.equal(out.float(), ref)
+    assert ((table.grad.float() - ref_t.grad).norm() / ref_t.grad.norm()).item() < 5e-3
