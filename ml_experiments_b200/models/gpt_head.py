@@ -133,7 +133,8 @@ class CausalSelfAttention(nn.Module):
         self.num_heads, self.head_dim, self.dim, self.paired = num_heads, head_dim, dim, paired
         assert num_heads * head_dim == dim, "num_heads * head_dim must equal model_dim"
 
-    def forward(self, x, a: AttnArgs, qkvo_w):
+    def forward(self, x, a: AttnArgs, qkvo_w, residual=None):
+        """``residual``: added to the output inside the output projection's GEMM (the block's skip connection)."""
         B, T = x.shape[:2]
         assert B == 1, "packed variable-length sequences need B == 1"
         H, D = self.num_heads, self.head_dim
@@ -157,7 +158,7 @@ class CausalSelfAttention(nn.Module):
                 k = torch.cat([k[..., :D // 2], torch.cat([k[:, :1, :, D // 2:], k[:, :-1, :, D // 2:]], dim=1)], dim=-1)
             y = _attend(q[0], k[0], v[0], a.seqlens, a.bm_size, a.yarn.attn_scale, 1)
         y = rowscale_add(None, torch.sigmoid(F.linear(gate_in, a.attn_gate_w)).view(B, T, H), y.reshape(B, T, H, D))
-        return linear(y.reshape(B, T, H * D), a.sa_lambdas[1] * qkvo_w[self.dim * 3:].type_as(y))
+        return linear(y.reshape(B, T, H * D), a.sa_lambdas[1] * qkvo_w[self.dim * 3:].type_as(y), residual=residual)
 
 
 class PairedHeadCausalSelfAttention(CausalSelfAttention):
@@ -166,9 +167,9 @@ class PairedHeadCausalSelfAttention(CausalSelfAttention):
 
 
 class MLP(nn.Module):
-    def forward(self, x, c_fc, c_proj):
-        """``relu(x @ c_fc.T)^2 @ c_proj`` with both weights stored ``[4 d, d]``."""
-        return mlp_relu2(x, c_fc.type_as(x), c_proj.type_as(x))
+    def forward(self, x, c_fc, c_proj, residual=None):
+        """``relu(x @ c_fc.T)^2 @ c_proj (+ residual)`` with both weights stored ``[4 d, d]``."""
+        return mlp_relu2(x, c_fc.type_as(x), c_proj.type_as(x), residual)
 
 
 class Block(nn.Module):
@@ -178,10 +179,10 @@ class Block(nn.Module):
         self.mlp = MLP() if has_mlp else None
 
     def forward(self, x, attn_args, qkvo_w=None, c_fc=None, c_proj=None):
-        if self.attn is not None:
-            x = x + self.attn(norm(x), attn_args, qkvo_w)
+        if self.attn is not None:      # the skip connections are added in the epilogue of each branch's last GEMM
+            x = self.attn(norm(x), attn_args, qkvo_w, residual=x)
         if self.mlp is not None:
-            x = x + self.mlp(norm(x), c_fc, c_proj)
+            x = self.mlp(norm(x), c_fc, c_proj, residual=x)
         return x
 
 

@@ -17,6 +17,7 @@ import torch.nn.functional as F
 from ..ops.fused import softcapped_cross_entropy
 from ..ops.linear import linear, linear_t, mlp_relu2
 from ..ops.norm_rope import norm_rotary
+from ..ops.rowops import lincomb3, rowscale_add
 from .gpt import CastedLinear
 from .gpt_head import BLOCK, ForwardScheduleConfig, Yarn, _attend, next_multiple_of_n, norm
 
@@ -64,9 +65,9 @@ class CausalSelfAttention(nn.Module):
             k = torch.where(band, prev, k)
         gate_in = x[..., :16]
         if ve is not None:
-            v = v + 2 * torch.sigmoid(self.value_embed_gate(gate_in)).view(B, T, H, 1) * ve.view_as(v)
+            v = rowscale_add(v, 2 * torch.sigmoid(self.value_embed_gate(gate_in)).view(B, T, H), ve.view(B, T, H, D))
         y = _attend(q[0], k[0], v[0], seqlens, bm_size, yarn.attn_scale, 1)
-        y = y.reshape(B, T, H, D) * torch.sigmoid(self.attn_gate(gate_in)).view(B, T, H, 1)
+        y = rowscale_add(None, torch.sigmoid(self.attn_gate(gate_in)).view(B, T, H), y.reshape(B, T, H, D))
         return linear(y.reshape(B, T, H * D), sa_lambdas[1] * self.qkvo_w[self.dim * 3:].type_as(y))
 
 
@@ -140,7 +141,10 @@ class GPTMedium(nn.Module):
                 gate = torch.sigmoid(skip_l[skip_idx]) * 2 * torch.sigmoid(self.skip_gates[skip_idx](x0[..., :16]))
                 skip_idx += 1
                 x = x + gate * skips.pop()
-            x = (resid[0] + x0l[0, 0]) * x + x0l[0, 1] * x02 if i == 0 else resid[i] * x + x0l[i, 0] * x0 + x0l[i, 1] * x02
+            if i == 0:   # x is x0 here: its two coefficients add up
+                x = lincomb3(x, x02, None, torch.stack([resid[0] + x0l[0, 0], x0l[0, 1]]))
+            else:
+                x = lincomb3(x, x0, x02, torch.stack([resid[i], x0l[i, 0], x0l[i, 1]]))
             x = self.blocks[i](x, ve=ve[i], sa_lambdas=sa[i], seqlens=seqlens, bm_size=long_bm if i in LONG_LAYERS else short_bm,
                                yarn=self.yarn, key_offset=i in LONG_LAYERS)
             if i in SKIP_IN:

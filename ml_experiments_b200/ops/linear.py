@@ -16,16 +16,27 @@ def _ok(x: torch.Tensor, w: torch.Tensor) -> bool:
     return x.is_cuda and x.shape[-1] % 8 == 0 and w.shape[0] % 8 == 0 and x.numel() > 0
 
 
+def _residual_operand(residual, rows: int, cols: int):
+    """The residual as a bf16 ``[rows, cols]`` operand of the GEMM epilogue, or ``None`` when it cannot be one."""
+    if residual is None or residual.dtype != torch.bfloat16 or residual.numel() != rows * cols or not residual.is_contiguous():
+        return None
+    return residual.view(rows, cols)
+
+
 class _Linear(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, epilogue):
+    def forward(ctx, x, w, epilogue, residual=None):
         x2 = x.reshape(-1, x.shape[-1])
         x16 = x2 if x2.dtype == torch.bfloat16 else x2.to(torch.bfloat16)
         w16 = w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)
         x16, w16 = x16.contiguous(), w16.contiguous()
-        y = G.gemm(x16, w16, epilogue=epilogue)
+        if residual is not None:      # out = x W^T + residual in the GEMM epilogue (the caller checked the operand)
+            y = G.gemm(x16, w16, epilogue=G.EPI_AXPBY, aux=residual.view(x16.shape[0], w16.shape[0]), alpha=1.0, beta=1.0)
+        else:
+            y = G.gemm(x16, w16, epilogue=epilogue)
         ctx.save_for_backward(x16, w16, y if epilogue == G.EPI_RELU2 else None)
         ctx.epilogue, ctx.x_shape, ctx.x_dtype, ctx.w_dtype = epilogue, x.shape, x.dtype, w.dtype
+        ctx.has_res = residual is not None
         return y.view(*x.shape[:-1], w.shape[0])
 
     @staticmethod
@@ -40,15 +51,23 @@ class _Linear(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             sk = G.auto_split_k(w16.shape[0], w16.shape[1], x16.shape[0])
             dw = G.gemm(dy2, x16, a_mn=True, b_mn=True, split_k=sk, out_dtype=torch.float32).to(ctx.w_dtype)
-        return dx, dw, None
+        return dx, dw, None, (dy if ctx.has_res else None)
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, relu2: bool = False) -> torch.Tensor:
-    """bf16 tensor-core linear layer; ``relu2=True`` fuses ``relu(.)**2`` into the GEMM epilogue (no bias then)."""
+def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, relu2: bool = False,
+           residual: torch.Tensor | None = None) -> torch.Tensor:
+    """bf16 tensor-core linear layer; ``relu2=True`` fuses ``relu(.)**2`` into the GEMM epilogue (no bias then);
+    ``residual`` (the output's shape) is added in the epilogue as well when it is a dense bf16 tensor."""
     if not _ok(x, w):
         y = F.linear(x, w.to(x.dtype), None if bias is None else bias.to(x.dtype))
-        return F.relu(y).square() if relu2 else y
-    y = _Linear.apply(x, w, G.EPI_RELU2 if (relu2 and bias is None) else G.EPI_NONE)
+        y = F.relu(y).square() if relu2 else y
+        return y if residual is None else residual + y
+    if residual is not None:
+        rows = x.numel() // x.shape[-1]
+        if relu2 or bias is not None or _residual_operand(residual, rows, w.shape[0]) is None or residual.shape[:-1] != x.shape[:-1]:
+            return residual + linear(x, w, bias, relu2)
+        return _Linear.apply(x, w, G.EPI_NONE, residual)
+    y = _Linear.apply(x, w, G.EPI_RELU2 if (relu2 and bias is None) else G.EPI_NONE, None)
     if bias is not None:
         y = y + bias.to(y.dtype)
         if relu2:
@@ -94,13 +113,16 @@ class _MlpRelu2(torch.autograd.Function):
     ``dh * 2 sqrt(h)`` with PyTorch operators between its GEMMs)."""
 
     @staticmethod
-    def forward(ctx, x, w_fc, w_proj):
+    def forward(ctx, x, w_fc, w_proj, residual=None):
         to16 = lambda t: (t if t.dtype == torch.bfloat16 else t.to(torch.bfloat16)).contiguous()
         x16, fc16, pj16 = to16(x.reshape(-1, x.shape[-1])), to16(w_fc), to16(w_proj)
         h = G.gemm(x16, fc16, epilogue=G.EPI_RELU2)
-        y = G.gemm(h, pj16, b_mn=True)
+        if residual is not None:
+            y = G.gemm(h, pj16, b_mn=True, epilogue=G.EPI_AXPBY, aux=residual.view(h.shape[0], pj16.shape[1]), alpha=1.0, beta=1.0)
+        else:
+            y = G.gemm(h, pj16, b_mn=True)
         ctx.save_for_backward(x16, fc16, pj16, h)
-        ctx.x_shape, ctx.dtypes = x.shape, (x.dtype, w_fc.dtype, w_proj.dtype)
+        ctx.x_shape, ctx.dtypes, ctx.has_res = x.shape, (x.dtype, w_fc.dtype, w_proj.dtype), residual is not None
         return y.view(*x.shape[:-1], w_proj.shape[1])
 
     @staticmethod
@@ -117,11 +139,15 @@ class _MlpRelu2(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             dfc = G.gemm(dpre, x16, a_mn=True, b_mn=True, split_k=G.auto_split_k(fc16.shape[0], fc16.shape[1], x16.shape[0]),
                          out_dtype=torch.float32).to(ctx.dtypes[1])
-        return dx, dfc, dpj
+        return dx, dfc, dpj, (dy if ctx.has_res else None)
 
 
-def mlp_relu2(x: torch.Tensor, w_fc: torch.Tensor, w_proj: torch.Tensor) -> torch.Tensor:
-    """``relu(x @ w_fc.T)**2 @ w_proj`` with ``w_fc, w_proj`` of shape ``(hidden, d)``."""
+def mlp_relu2(x: torch.Tensor, w_fc: torch.Tensor, w_proj: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+    """``relu(x @ w_fc.T)**2 @ w_proj (+ residual)`` with ``w_fc, w_proj`` of shape ``(hidden, d)``; a dense bf16
+    ``residual`` of the output's shape is added in the epilogue of the second GEMM."""
     if not (_ok(x, w_fc) and w_proj.shape[1] % 8 == 0 and w_fc.shape == w_proj.shape):
-        return F.relu(F.linear(x, w_fc.to(x.dtype))).square() @ w_proj.to(x.dtype)
-    return _MlpRelu2.apply(x, w_fc, w_proj)
+        y = F.relu(F.linear(x, w_fc.to(x.dtype))).square() @ w_proj.to(x.dtype)
+        return y if residual is None else residual + y
+    if residual is not None and (_residual_operand(residual, x.numel() // x.shape[-1], w_proj.shape[1]) is None or residual.shape[:-1] != x.shape[:-1]):
+        return residual + _MlpRelu2.apply(x, w_fc, w_proj, None)
+    return _MlpRelu2.apply(x, w_fc, w_proj, residual)

@@ -315,3 +315,26 @@ def test_embedding_op_matches_torch():
     (ref * w.float()).sum().backward()
     assert torch.equal(out.float(), ref)
     assert ((table.grad.float() - ref_t.grad).norm() / ref_t.grad.norm()).item() < 5e-3
+
+
+def test_linear_and_mlp_nodes_add_the_residual_in_the_epilogue():
+    from ml_experiments_b200.ops.linear import linear, mlp_relu2
+
+    torch.manual_seed(7)
+    x = (torch.randn(1, 384, 256, device="cuda") * 0.5).bfloat16().requires_grad_(True)
+    r = torch.randn(1, 384, 256, device="cuda").bfloat16().requires_grad_(True)
+    w = (torch.randn(256, 256, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    wf = (torch.randn(1024, 256, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    wp = (torch.randn(1024, 256, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm()).item()
+    for fused, plain in ((lambda: linear(x, w, residual=r), lambda: r + linear(x, w)),
+                         (lambda: mlp_relu2(x, wf, wp, residual=r), lambda: r + mlp_relu2(x, wf, wp))):
+        outs = []
+        for f in (fused, plain):
+            for t in (x, r, w, wf, wp):
+                t.grad = None
+            y = f()
+            y.float().square().mean().backward()
+            outs.append((y.detach(), x.grad.clone(), r.grad.clone()))
+        (y1, dx1, dr1), (y2, dx2, dr2) = outs
+        assert rel(y1, y2) < 1e-2 and rel(dx1, dx2) < 2e-2 and rel(dr1, dr2) < 1e-2
