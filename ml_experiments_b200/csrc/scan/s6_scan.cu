@@ -241,6 +241,30 @@ __device__ __forceinline__ float reduce4(const float (&v)[4], int lane) {
   return p;
 }
 
+// One tile's inputs exactly as they lie in memory: filled by 16-byte cp.async copies one tile ahead of its use, so the
+// backward never waits for global memory at the start of a tile (the walk over the sequence is serial per block, and
+// that wait was its largest stall).
+template <typename DT>
+struct RawTile {
+  DT delta[SUB][CB];
+  bf16 u[SUB][CB];
+  bf16 dout[SUB][CB];
+  bf16 z[SUB][CB];
+  bf16 yp[SUB][CB];
+  float B[SUB][NS];
+  float C[SUB][NS];
+  float st[4][CB][4];   // the state checkpoint of the tile: [group of four states][channel][state in group]
+};
+
+// 16 bytes global -> shared; `bytes` (0..16) of them are read, the rest of the destination is zero-filled
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, int bytes) {
+  const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 // grid (ceil(Din / 32), batch), 32 * 16 / QS threads. dout is the gradient of `out`; with z given the gate's backward is applied
 // here (dy = dout * silu(z), dz = dout * y_pre * silu'(z)).
 template <typename DT, int QS>
@@ -251,7 +275,7 @@ s6_bwd_kernel(const bf16* __restrict__ u, const DT* __restrict__ delta, const fl
               const bf16* __restrict__ dout, const float* __restrict__ state, bf16* __restrict__ du,
               DT* __restrict__ ddelta, float* __restrict__ dA, float* __restrict__ dB_part,
               float* __restrict__ dC_part, float* __restrict__ dD, bf16* __restrict__ dz,
-              float* __restrict__ ddelta_bias, int L, int Din) {
+              float* __restrict__ ddelta_bias, int L, int Din, int piped) {
   constexpr int NW = Shape<QS>::NW, NT = Shape<QS>::NT, RPT = Shape<QS>::RPT, BCPT = Shape<QS>::BCPT;
   __shared__ __align__(16) BwdSmem<QS> s;
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
@@ -269,44 +293,101 @@ s6_bwd_kernel(const bf16* __restrict__ u, const DT* __restrict__ delta, const fl
   const float bias = (dok && delta_bias) ? delta_bias[d] : 0.f;
   const float dsk = (dok && Dv) ? Dv[d] : 0.f;
   float dDa = 0.f, dbias = 0.f;
+  // two RawTile buffers in dynamic shared memory; the host passes piped = 0 (and no dynamic memory) when rows are not
+  // 16-byte aligned (Din % 8 != 0) or the variant's static arrays leave no room for them
+  extern __shared__ __align__(16) unsigned char s6_dyn_smem[];
+  RawTile<DT>* raw = reinterpret_cast<RawTile<DT>*>(s6_dyn_smem);
+  auto issue_tile = [&](int tile, int buf) {
+    RawTile<DT>& r = raw[buf];
+    const int t0 = tile * SUB;
+    constexpr int CPR = CB * (int)sizeof(bf16) / 16;       // chunks per bf16 row (4)
+    constexpr int DPR = CB * (int)sizeof(DT) / 16;         // chunks per delta row (4 or 8)
+    constexpr int N16 = SUB * CPR, ND = SUB * DPR, NBC = SUB * NS * 4 / 16, NST = 4 * CB * 4 * 4 / 16;
+    const int nz = z ? N16 : 0;
+    const int total = ND + 2 * N16 + 2 * nz + 2 * NBC + NST;
+    for (int c = tid; c < total; c += NT) {
+      int i = c;
+      if (i < ND) {
+        const int row = i / DPR, part = i % DPR, per = 16 / (int)sizeof(DT), ch = d0 + part * per;
+        const int ok = (t0 + row < L) ? max(0, min(16, (Din - ch) * (int)sizeof(DT))) : 0;
+        cp_async16(&r.delta[row][part * per], delta + ((long long)b * L + min(t0 + row, L - 1)) * Din + min(ch, Din - per), ok);
+        continue;
+      }
+      i -= ND;
+      if (i < 2 * N16 + 2 * nz) {
+        const int which = i / N16, j = i % N16, row = j / CPR, part = j % CPR, ch = d0 + part * 8;
+        const int ok = (t0 + row < L) ? max(0, min(16, (Din - ch) * 2)) : 0;
+        const bf16* src = which == 0 ? u : which == 1 ? dout : which == 2 ? z : y_pre;
+        bf16* dst = which == 0 ? &r.u[row][part * 8] : which == 1 ? &r.dout[row][part * 8] : which == 2 ? &r.z[row][part * 8] : &r.yp[row][part * 8];
+        cp_async16(dst, src + ((long long)b * L + min(t0 + row, L - 1)) * Din + min(ch, Din - 8), ok);
+        continue;
+      }
+      i -= 2 * N16 + 2 * nz;
+      if (i < 2 * NBC) {
+        const int which = i / NBC, j = i % NBC, row = j / 4, part = j % 4;
+        const int ok = (t0 + row < L) ? 16 : 0;
+        const float* src = (which == 0 ? Bm : Cm) + ((long long)b * L + min(t0 + row, L - 1)) * NS + part * 4;
+        cp_async16(which == 0 ? &r.B[row][part * 4] : &r.C[row][part * 4], src, ok);
+        continue;
+      }
+      i -= 2 * NBC;
+      {
+        const int g = i / CB, chn = i % CB;
+        const int ok = (d0 + chn < Din) ? 16 : 0;
+        cp_async16(&r.st[g][chn][0], &state[state_off(b, nsub, tile, g * 4, Din, min(d0 + chn, Din - 1))], ok);
+      }
+    }
+    cp_async_commit();
+  };
+  if (piped) issue_tile(nsub - 1, 0);
   for (int tile = nsub - 1; tile >= 0; --tile) {
     const int t0 = tile * SUB;
+    const int buf = (nsub - 1 - tile) & 1;
+    if (piped) {
+      if (tile > 0) { issue_tile(tile - 1, buf ^ 1); cp_async_wait<1>(); }
+      else cp_async_wait<0>();
+      __syncthreads();   // this tile's copies, issued by all threads, are visible to all
+    }
+    const RawTile<DT>& rt = raw[buf];
     float sp[RPT];  // d softplus / d raw for the rows this thread stages (and writes back)
 #pragma unroll
     for (int j = 0; j < RPT; ++j) {
       const int t = w + NW * j;
       const bool ok = dok && t0 + t < L;
       const long long off = ((long long)b * L + t0 + t) * Din + d;
-      float dtv = ok ? ld(delta, off) : 0.f;
+      float dtv = ok ? (piped ? (float)rt.delta[t][lane] : ld(delta, off)) : 0.f;
       sp[j] = 1.f;
       if (softplus) {
         const float raw = dtv + bias;
         sp[j] = raw > 20.f ? 1.f : sigmoidf(raw);
         dtv = ok ? softplusf(raw) : 0.f;
       }
-      float g = ok ? __bfloat162float(dout[off]) : 0.f;
+      float g = ok ? __bfloat162float(piped ? rt.dout[t][lane] : dout[off]) : 0.f;
       if (z && ok) {
-        const float zv = __bfloat162float(z[off]), sg = sigmoidf(zv);
-        if (dz) dz[off] = __float2bfloat16_rn(g * __bfloat162float(y_pre[off]) * sg * (1.f + zv * (1.f - sg)));
+        const float zv = __bfloat162float(piped ? rt.z[t][lane] : z[off]), sg = sigmoidf(zv);
+        if (dz) dz[off] = __float2bfloat16_rn(g * __bfloat162float(piped ? rt.yp[t][lane] : y_pre[off]) * sg * (1.f + zv * (1.f - sg)));
         g *= zv * sg;
       }
       s.dt[t][lane] = dtv;
-      s.u[t][lane] = ok ? __bfloat162float(u[off]) : 0.f;
+      s.u[t][lane] = ok ? __bfloat162float(piped ? rt.u[t][lane] : u[off]) : 0.f;
       s.dy[t][lane] = g;
     }
 #pragma unroll
     for (int j = 0; j < BCPT; ++j) {
       const int i = tid + NT * j, t = t0 + i / NS;
       const long long off = ((long long)b * L + t) * NS + (i % NS);
-      s.B[i / NS][i % NS] = t < L ? Bm[off] : 0.f;
-      s.C[i / NS][i % NS] = t < L ? Cm[off] : 0.f;
+      s.B[i / NS][i % NS] = t < L ? (piped ? rt.B[i / NS][i % NS] : Bm[off]) : 0.f;
+      s.C[i / NS][i % NS] = t < L ? (piped ? rt.C[i / NS][i % NS] : Cm[off]) : 0.f;
     }
     float h0[QS];
 #pragma unroll
     for (int k = 0; k < QS; ++k) h0[k] = 0.f;
-    if (dok) ldv<QS>(h0, &state[state_off(b, nsub, tile, w * QS, Din, d)]);
+    if (dok) {
+      if (piped) ldv<QS>(h0, &rt.st[(w * QS) >> 2][lane][(w * QS) & 3]);
+      else ldv<QS>(h0, &state[state_off(b, nsub, tile, w * QS, Din, d)]);
+    }
     __syncthreads();
-    if (tile > 0) {  // warm L1 with the rows of the tile processed next (one tile earlier in time)
+    if (tile > 0 && !piped) {  // warm L1 with the rows of the tile processed next (one tile earlier in time)
 #pragma unroll
       for (int j = 0; j < RPT; ++j) {
         const long long off = ((long long)b * L + t0 - SUB + w + NW * j) * Din + d;
@@ -439,10 +520,10 @@ void s6_set_states_per_thread(int fwd_qs, int bwd_qs) {
   s6_fwd_kernel<DT, QS><<<grid, Shape<QS>::NT, 0, st>>>((const bf16*)u, (const DT*)delta, delta_bias, softplus ? 1 : 0, \
                                                         A, Bm, Cm, Dv, (const bf16*)z, (bf16*)y_pre, (bf16*)out, state, L, Din)
 #define S6_BWD(DT, QS)                                                                                               \
-  s6_bwd_kernel<DT, QS><<<grid, Shape<QS>::NT, 0, st>>>((const bf16*)u, (const DT*)delta, delta_bias, softplus ? 1 : 0, \
+  s6_bwd_kernel<DT, QS><<<grid, Shape<QS>::NT, piped ? 2 * sizeof(RawTile<DT>) : 0, st>>>((const bf16*)u, (const DT*)delta, delta_bias, softplus ? 1 : 0, \
                                                         A, Bm, Cm, Dv, (const bf16*)z, (const bf16*)y_pre,            \
                                                         (const bf16*)dout, state, (bf16*)du, (DT*)ddelta, dA, dB_part, \
-                                                        dC_part, dD, (bf16*)dz, ddelta_bias, L, Din)
+                                                        dC_part, dD, (bf16*)dz, ddelta_bias, L, Din, piped)
 
 void s6_scan_fwd(const void* u, const void* delta, bool delta_bf16, const float* delta_bias, bool softplus,
                  const float* A, const float* Bm, const float* Cm, const float* Dv, const void* z, void* y_pre, void* out,
@@ -466,6 +547,9 @@ void s6_scan_bwd(const void* u, const void* delta, bool delta_bf16, const float*
   if (z && !y_pre) throw std::runtime_error("s6_scan_bwd: the gate's backward needs y_pre");
   dim3 grid(s6_channel_blocks(Din), batch);
   const bool q2 = g_bwd_qs == 2;
+  // input tiles are copied one tile ahead when the rows allow 16-byte copies (static + dynamic shared memory of the
+  // four-states-per-thread variant stays under the 48 KB that need no opt-in)
+  const int piped = (!q2 && Din % 8 == 0) ? 1 : 0;
   if (delta_bf16) {
     if (q2) S6_BWD(bf16, 2); else S6_BWD(bf16, 4);
   } else {
