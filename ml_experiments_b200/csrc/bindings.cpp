@@ -929,14 +929,21 @@ void rms_act_fwd(const Tensor& x, const Tensor& w, Tensor y, Tensor rstd, double
   b200::rms_act_fwd(x.data_ptr(), xb, w.data_ptr<float>(), y.data_ptr(), yb, rstd.data_ptr<float>(), R, C, (float)eps, (int)act, cur_stream());
 }
 
-void rms_act_bwd(const Tensor& x, const Tensor& w, const Tensor& rstd, const Tensor& dy, Tensor dx, Tensor dw, int64_t act) {
+void rms_act_bwd(const Tensor& x, const Tensor& w, const Tensor& rstd, const Tensor& dy, const c10::optional<Tensor>& dres,
+                 Tensor dx, Tensor dw, int64_t act) {
   const c10::cuda::CUDAGuard guard(x.device());
   const bool xb = norm_io_bf16(x, "x"), gb = norm_io_bf16(dy, "dy");
   TORCH_CHECK(norm_io_bf16(dx, "dx") == xb && dx.numel() == x.numel() && dy.numel() == x.numel(), "dx: x's dtype and shape; dy: x's shape");
   const int C = (int)x.size(-1);
   const int64_t R = x.numel() / C;
   chk_rows_f32(w, C, "weight"); chk_rows_f32(rstd, R, "rstd"); chk_rows_f32(dw, C, "dw");
-  b200::rms_act_bwd(x.data_ptr(), xb, w.data_ptr<float>(), rstd.data_ptr<float>(), dy.data_ptr(), gb, dx.data_ptr(), dw.data_ptr<float>(), R, C,
+  const void* res = nullptr;
+  if (dres.has_value()) {
+    TORCH_CHECK(dres->is_cuda() && dres->is_contiguous() && dres->scalar_type() == x.scalar_type() && dres->numel() == x.numel(),
+                "dres: a dense tensor of x's dtype and shape");
+    res = dres->data_ptr();
+  }
+  b200::rms_act_bwd(x.data_ptr(), xb, w.data_ptr<float>(), rstd.data_ptr<float>(), dy.data_ptr(), gb, res, dx.data_ptr(), dw.data_ptr<float>(), R, C,
                     (int)act, cur_stream());
 }
 
@@ -992,7 +999,7 @@ TORCH_LIBRARY(b200, m) {
   m.def("lincomb3_fwd(Tensor x, Tensor y, Tensor? z, Tensor c, Tensor(a!) out) -> ()");
   m.def("lincomb3_bwd(Tensor x, Tensor y, Tensor? z, Tensor c, Tensor dout, Tensor(a!) dx, Tensor(b!) dy, Tensor(c!)? dz, Tensor(d!) dc) -> ()");
   m.def("rms_act_fwd(Tensor x, Tensor w, Tensor(a!) y, Tensor(b!) rstd, float eps, int act) -> ()");
-  m.def("rms_act_bwd(Tensor x, Tensor w, Tensor rstd, Tensor dy, Tensor(a!) dx, Tensor(b!) dw, int act) -> ()");
+  m.def("rms_act_bwd(Tensor x, Tensor w, Tensor rstd, Tensor dy, Tensor? dres, Tensor(a!) dx, Tensor(b!) dw, int act) -> ()");
   m.def("tele_fused_fwd(Tensor x, Tensor freq, Tensor phase, Tensor kern, Tensor expo, Tensor(a!) out, int H, int half, float max_rec) -> ()");
   m.def("tele_fused_bwd(Tensor x, Tensor freq, Tensor phase, Tensor kern, Tensor expo, Tensor dout, Tensor(a!) dx, Tensor(b!) dfreq, Tensor(c!) dphase, Tensor(d!) dkern, Tensor(e!) dexpo_h, int H, int half, float max_rec) -> ()");
   m.def("alc_fused_fwd(Tensor x, Tensor half_w, Tensor center, Tensor kern, Tensor(a!) out, int H, int half) -> ()");

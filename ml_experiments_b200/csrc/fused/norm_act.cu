@@ -3,6 +3,8 @@
 
 #include <cuda_bf16.h>
 
+#include <algorithm>
+#include <cstdint>
 #include <stdexcept>
 #include <string>
 
@@ -69,7 +71,8 @@ rms_act_fwd_kernel(const TI* __restrict__ x, const float* __restrict__ w, TO* __
 template <typename TI, typename TO, int ACT>
 __global__ void __launch_bounds__(256)
 rms_act_bwd_kernel(const TI* __restrict__ x, const float* __restrict__ w, const float* __restrict__ rstd,
-                   const TO* __restrict__ dy, TI* __restrict__ dx, float* __restrict__ dw, long long R, int C) {
+                   const TO* __restrict__ dy, const TI* __restrict__ dres, TI* __restrict__ dx, float* __restrict__ dw,
+                   long long R, int C) {
   extern __shared__ float s_dw[];  // [C]
   for (int c = threadIdx.x; c < C; c += 256) s_dw[c] = 0.f;
   __syncthreads();
@@ -101,7 +104,7 @@ rms_act_bwd_kernel(const TI* __restrict__ x, const float* __restrict__ w, const 
     for (int c = lane; c < C; c += 32) {
       const float xh = ldf(x, base + c) * rs, wc = w[c];
       const float g = ldf(dy, base + c) * act_grad<ACT>(wc * xh);
-      stf(dx, base + c, rs * (g * wc - xh * dot));
+      stf(dx, base + c, rs * (g * wc - xh * dot) + (dres ? ldf(dres, base + c) : 0.f));
     }
   }
 #pragma unroll
@@ -109,6 +112,82 @@ rms_act_bwd_kernel(const TI* __restrict__ x, const float* __restrict__ w, const 
     const int c = lane + 32 * i;
     if (c < C && acc[i] != 0.f) atomicAdd(&s_dw[c], acc[i]);
   }
+  __syncthreads();
+  for (int c = threadIdx.x; c < C; c += 256) {
+    const float v = s_dw[c];
+    if (v != 0.f) atomicAdd(&dw[c], v);
+  }
+}
+
+// Backward for bf16 rows of C = 256 * VPL columns: a lane owns VPL groups of 8 adjacent columns, reads x and dy once with
+// 16-byte loads, keeps the weight-gradient sums of all its columns in registers over the rows it walks, and can add a
+// second incoming gradient (`dres`: that of a skip connection around the norm) to dx in the same pass.
+template <int VPL, int ACT>
+__global__ void __launch_bounds__(256)
+rms_act_bwd_vec_kernel(const bf16* __restrict__ x, const float* __restrict__ w, const float* __restrict__ rstd,
+                       const bf16* __restrict__ dy, const bf16* __restrict__ dres, bf16* __restrict__ dx,
+                       float* __restrict__ dw, long long R) {
+  constexpr int C = VPL * 256;
+  __shared__ float s_dw[C];
+  for (int c = threadIdx.x; c < C; c += 256) s_dw[c] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const long long warps = (long long)gridDim.x * 8;
+  const float invC = 1.f / (float)C;
+  float acc[VPL][8];
+#pragma unroll
+  for (int j = 0; j < VPL; ++j)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[j][e] = 0.f;
+  for (long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5); row < R; row += warps) {
+    const long long base = row * C;
+    const float rs = rstd[row];
+    uint4 xr[VPL], gr[VPL];
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      const long long o = base + (j * 32 + lane) * 8;
+      xr[j] = *reinterpret_cast<const uint4*>(x + o);
+      gr[j] = *reinterpret_cast<const uint4*>(dy + o);
+    }
+    float dot = 0.f;
+    float gw[VPL][8], xh[VPL][8];
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      const int c0 = (j * 32 + lane) * 8;
+      const float4 w0 = *reinterpret_cast<const float4*>(w + c0), w1 = *reinterpret_cast<const float4*>(w + c0 + 4);
+      const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+      const bf16* xb = reinterpret_cast<const bf16*>(&xr[j]);
+      const bf16* gb = reinterpret_cast<const bf16*>(&gr[j]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float h = __bfloat162float(xb[e]) * rs;
+        const float g = __bfloat162float(gb[e]) * act_grad<ACT>(wv[e] * h);
+        xh[j][e] = h;
+        gw[j][e] = g * wv[e];
+        dot = fmaf(gw[j][e], h, dot);
+        acc[j][e] = fmaf(g, h, acc[j][e]);
+      }
+    }
+    dot = warp_sum(dot) * invC;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      const long long o = base + (j * 32 + lane) * 8;
+      uint4 rr = make_uint4(0u, 0u, 0u, 0u);
+      if (dres) rr = *reinterpret_cast<const uint4*>(dres + o);
+      const bf16* rb = reinterpret_cast<const bf16*>(&rr);
+      uint4 out;
+      bf16* ob = reinterpret_cast<bf16*>(&out);
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        ob[e] = __float2bfloat16(fmaf(rs, gw[j][e] - xh[j][e] * dot, __bfloat162float(rb[e])));
+      *reinterpret_cast<uint4*>(dx + o) = out;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < VPL; ++j)
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+      if (acc[j][e] != 0.f) atomicAdd(&s_dw[(j * 32 + lane) * 8 + e], acc[j][e]);
   __syncthreads();
   for (int c = threadIdx.x; c < C; c += 256) {
     const float v = s_dw[c];
@@ -150,12 +229,29 @@ void rms_act_fwd(const void* x, bool x_bf16, const float* w, void* y, bool y_bf1
   chk("rms_act_fwd");
 }
 
-void rms_act_bwd(const void* x, bool x_bf16, const float* w, const float* rstd, const void* dy, bool dy_bf16, void* dx,
-                 float* dw, long long R, int C, int act, cudaStream_t s) {
+void rms_act_bwd(const void* x, bool x_bf16, const float* w, const float* rstd, const void* dy, bool dy_bf16,
+                 const void* dres, void* dx, float* dw, long long R, int C, int act, cudaStream_t s) {
   if (C < 1 || C > 4096) throw std::runtime_error("rms_act: row length must be in [1, 4096]");
   if (R == 0) return;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(dx) |
+                         reinterpret_cast<uintptr_t>(dres) | reinterpret_cast<uintptr_t>(w)) & 15) == 0;
+  if (x_bf16 && dy_bf16 && aligned && C % 256 == 0 && C <= 1024) {
+    const int grid = (int)std::min<long long>((R + 7) / 8, 148LL * 4);
+#define RMS_VEC(VPL_)                                                                                                  \
+  DISPATCH_ACT(act, rms_act_bwd_vec_kernel<VPL_, ACT_><<<grid, 256, 0, s>>>((const bf16*)x, w, rstd, (const bf16*)dy,  \
+                                                                             (const bf16*)dres, (bf16*)dx, dw, R))
+    switch (C / 256) {
+      case 1: RMS_VEC(1); break;
+      case 2: RMS_VEC(2); break;
+      case 3: RMS_VEC(3); break;
+      default: RMS_VEC(4); break;
+    }
+#undef RMS_VEC
+    chk("rms_act_bwd");
+    return;
+  }
   DISPATCH_ACT(act, DISPATCH_IO(x_bf16, dy_bf16, {
-    rms_act_bwd_kernel<TI_, TO_, ACT_><<<grid_for(R), 256, (size_t)C * sizeof(float), s>>>((const TI_*)x, w, rstd, (const TO_*)dy, (TI_*)dx, dw, R, C);
+    rms_act_bwd_kernel<TI_, TO_, ACT_><<<grid_for(R), 256, (size_t)C * sizeof(float), s>>>((const TI_*)x, w, rstd, (const TO_*)dy, (const TI_*)dres, (TI_*)dx, dw, R, C);
   }));
   chk("rms_act_bwd");
 }

@@ -19,8 +19,8 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops.causal_conv import causal_conv1d_silu
-from ..ops.norm_act import rms_norm_act
-from ..ops.linear import linear
+from ..ops.norm_act import rms_norm_act, rms_norm_act_skip
+from ..ops.linear import linear, linear_pair
 from ..ops.selective_scan import selective_scan
 
 
@@ -78,21 +78,21 @@ class S6Mixer(nn.Module):
         self.D = nn.Parameter(torch.ones(di))
         self.out_proj = nn.Linear(di, cfg.d_model, bias=False)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:  # (B, L, d_model)
+    def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:  # (B, L, d_model)
+        """``residual`` (the block's skip connection) is added in the epilogue of the output projection."""
         cfg = self.cfg
         L = x.shape[1]
-        # the two halves of in_proj as two GEMMs on row slices of its weight: the scan needs x and the gate z as separate
-        # contiguous tensors, and one wide GEMM would cost a strided-to-contiguous copy of each half in the forward and a
-        # concatenation of their gradients in the backward
+        # the two halves of in_proj as two GEMMs on row ranges of its weight (one autograd node): the scan needs x and the
+        # gate z as separate contiguous tensors, and one wide GEMM would cost a strided-to-contiguous copy of each half in
+        # the forward and a concatenation of their gradients in the backward
         di = cfg.d_inner
-        xi = linear(x, self.in_proj.weight[:di])
-        z = linear(x, self.in_proj.weight[di:])
+        xi, z = linear_pair(x, self.in_proj.weight, di)
         xi = causal_conv1d_silu(xi, self.conv1d.weight, self.conv1d.bias)
         dbc = linear(xi, self.x_proj.weight)
         dt, Bm, Cm = torch.split(dbc, [cfg.rank, cfg.d_state, cfg.d_state], dim=-1)
         y = selective_scan(xi.contiguous(), linear(dt, self.dt_proj.weight), -torch.exp(self.A_log.float()), Bm, Cm, self.D,
                            z, delta_bias=self.dt_proj.bias, delta_softplus=True)
-        return linear(y, self.out_proj.weight)
+        return linear(y, self.out_proj.weight, residual=residual)
 
 
 class S6Block(nn.Module):
@@ -102,7 +102,10 @@ class S6Block(nn.Module):
         self.mixer = S6Mixer(cfg)
 
     def forward(self, x):
-        return x + self.mixer(self.norm(x))
+        if x.is_cuda:   # the skip's gradient joins the norm's inside the norm's backward kernel
+            h, skip = rms_norm_act_skip(x, self.norm.weight, self.norm.eps)
+            return self.mixer(h, residual=skip)
+        return self.mixer(self.norm(x), residual=x)
 
 
 class S6LM(nn.Module):

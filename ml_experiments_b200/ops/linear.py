@@ -75,6 +75,49 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, r
     return y
 
 
+class _LinearPair(torch.autograd.Function):
+    """``(x @ W[:split].T, x @ W[split:].T)`` as one node: two forward GEMMs on row ranges of ``W`` (each output dense,
+    no strided halves of one wide output), and in the backward the second data-gradient GEMM adds the first one's
+    result in its epilogue and the two weight-gradient GEMMs write the row ranges of one ``W``-shaped buffer. Two
+    separate nodes would leave autograd an elementwise add of the two ``dx`` and a zero-fill + copy + add per half of
+    ``dW``."""
+
+    @staticmethod
+    def forward(ctx, x, w, split):
+        x16 = x.reshape(-1, x.shape[-1]).to(torch.bfloat16).contiguous()
+        w16 = w.to(torch.bfloat16).contiguous()
+        ctx.save_for_backward(x16, w16)
+        ctx.split, ctx.x_shape, ctx.x_dtype, ctx.w_dtype = split, x.shape, x.dtype, w.dtype
+        ya, yb = G.gemm(x16, w16[:split]), G.gemm(x16, w16[split:])
+        return ya.view(*x.shape[:-1], split), yb.view(*x.shape[:-1], w.shape[0] - split)
+
+    @staticmethod
+    def backward(ctx, dya, dyb):
+        x16, w16 = ctx.saved_tensors
+        s = ctx.split
+        da = dya.reshape(-1, dya.shape[-1]).to(torch.bfloat16).contiguous()
+        db = dyb.reshape(-1, dyb.shape[-1]).to(torch.bfloat16).contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = G.gemm(da, w16[:s], b_mn=True)
+            dx = G.gemm(db, w16[s:], b_mn=True, epilogue=G.EPI_AXPBY, aux=dx, alpha=1.0, beta=1.0).view(ctx.x_shape).to(ctx.x_dtype)
+        if ctx.needs_input_grad[1]:
+            dw = torch.empty(w16.shape, dtype=torch.float32, device=w16.device)
+            for rows, dy2 in ((slice(0, s), da), (slice(s, None), db)):
+                sk = G.auto_split_k(dy2.shape[1], w16.shape[1], x16.shape[0])
+                G.gemm(dy2, x16, a_mn=True, b_mn=True, split_k=sk, out=dw[rows])
+            dw = dw.to(ctx.w_dtype)
+        return dx, dw, None
+
+
+def linear_pair(x: torch.Tensor, w: torch.Tensor, split: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """The two halves ``x @ w[:split].T`` and ``x @ w[split:].T`` of one projection as separate dense tensors."""
+    if not (_ok(x, w) and split % 8 == 0 and (w.shape[0] - split) % 8 == 0 and w.shape[1] % 8 == 0):
+        y = F.linear(x, w.to(x.dtype))
+        return y[..., :split], y[..., split:]
+    return _LinearPair.apply(x, w, split)
+
+
 class _LinearT(torch.autograd.Function):
     """``y = x @ W`` for a weight stored ``(in_features, out_features)``: all three GEMMs read it as stored."""
 

@@ -40,8 +40,34 @@ class _RmsAct(torch.autograd.Function):
             dy = dy.float()
         dx = torch.empty_like(xc)
         dw = torch.zeros_like(w32)
-        ops().rms_act_bwd(xc, w32, rstd, dy.contiguous(), dx, dw, ctx.act)
+        ops().rms_act_bwd(xc, w32, rstd, dy.contiguous(), None, dx, dw, ctx.act)
         return dx, dw.to(ctx.wdtype), None, None, None
+
+
+class _RmsActSkip(torch.autograd.Function):
+    """``(norm(x), x)``: the second output is the skip connection around the norm, so that the backward kernel adds the
+    skip's gradient to the norm's in the pass that writes ``dx`` (autograd would run an elementwise add after it)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, eps, act):
+        xc = x.contiguous()
+        w32 = weight.detach().float().contiguous()
+        y = torch.empty_like(xc)
+        rstd = torch.empty(xc.numel() // xc.shape[-1], dtype=torch.float32, device=x.device)
+        ops().rms_act_fwd(xc, w32, y, rstd, eps, act)
+        ctx.save_for_backward(xc, w32, rstd)
+        ctx.act, ctx.wdtype = act, weight.dtype
+        return y, x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, dy, dskip):
+        xc, w32, rstd = ctx.saved_tensors
+        if dy.dtype not in (torch.bfloat16, torch.float32):
+            dy = dy.float()
+        dx = torch.empty_like(xc)
+        dw = torch.zeros_like(w32)
+        ops().rms_act_bwd(xc, w32, rstd, dy.contiguous(), dskip.to(xc.dtype).contiguous(), dx, dw, ctx.act)
+        return dx, dw.to(ctx.wdtype), None, None
 
 
 def rms_norm_act(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, act: str = "none", out_dtype=None) -> torch.Tensor:
@@ -51,3 +77,12 @@ def rms_norm_act(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, act: 
     if not ok:
         return rms_norm_act_ref(x, weight, eps, act, out_dtype)
     return _RmsAct.apply(x, weight, float(eps), _ACTS[act], out_dtype)
+
+
+def rms_norm_act_skip(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, act: str = "none") -> tuple[torch.Tensor, torch.Tensor]:
+    """``(rms_norm_act(x), x)`` for a pre-norm residual block ``skip + f(norm(x))``: use the returned ``x`` as the skip
+    and both gradients meet inside the norm's backward kernel."""
+    ok = x.is_cuda and x.dtype in (torch.bfloat16, torch.float32) and 1 <= x.shape[-1] <= 4096 and weight.numel() == x.shape[-1]
+    if not ok:
+        return rms_norm_act_ref(x, weight, eps, act), x
+    return _RmsActSkip.apply(x, weight, float(eps), _ACTS[act])

@@ -300,6 +300,26 @@ def test_mlp_relu2_node_matches_autograd():
         assert rel(a, b) < 2e-2, rel(a, b)
 
 
+def test_linear_pair_node_matches_autograd():
+    """Two outputs from row ranges of one weight; the backward sums the two data gradients in a GEMM epilogue and
+    writes both weight gradients into one buffer (unequal halves; one of them small enough for split-K)."""
+    from ml_experiments_b200.ops.linear import linear_pair
+
+    torch.manual_seed(11)
+    x = (torch.randn(2, 1024, 256, device="cuda") * 0.5).bfloat16().requires_grad_(True)
+    w = (torch.randn(512 + 128, 256, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    ya, yb = linear_pair(x, w, 512)
+    assert ya.shape == (2, 1024, 512) and yb.shape == (2, 1024, 128) and ya.is_contiguous() and yb.is_contiguous()
+    ga, gb = torch.randn_like(ya.float()), torch.randn_like(yb.float())
+    ((ya.float() * ga).sum() + (yb.float() * gb).sum()).backward()
+    xr, wr = (t.detach().float().requires_grad_(True) for t in (x, w))
+    yr = xr @ wr.T
+    ((yr[..., :512] * ga).sum() + (yr[..., 512:] * gb).sum()).backward()
+    rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm()).item()
+    assert rel(ya, yr[..., :512]) < 1e-2 and rel(yb, yr[..., 512:]) < 1e-2
+    assert rel(x.grad, xr.grad) < 2e-2 and rel(w.grad, wr.grad) < 2e-2
+
+
 def test_embedding_op_matches_torch():
     from ml_experiments_b200.ops.fused import embedding
 

@@ -56,7 +56,7 @@ def test_adaptive_local_fused(B, L, H, D, K, half):
         assert _rel(a.grad, b.grad) < 2e-2, (name, _rel(a.grad, b.grad))
 
 
-@pytest.mark.parametrize("C", [1, 4, 8, 64, 256, 300, 1024])
+@pytest.mark.parametrize("C", [1, 4, 8, 64, 256, 300, 512, 768, 1024])
 @pytest.mark.parametrize("act", ["none", "silu", "sigmoid", "tanh"])
 @pytest.mark.parametrize("dtypes", [(torch.bfloat16, torch.float32), (torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16)])
 def test_rms_norm_act(C, act, dtypes):
@@ -75,4 +75,24 @@ def test_rms_norm_act(C, act, dtypes):
     ya.backward(gy.to(dout))
     yb.backward(gy.to(dout).float())
     tol = 2e-2 if torch.bfloat16 in dtypes else 1e-4
+    assert _rel(xa.grad, xb.grad) < tol and _rel(wa.grad, wb.grad) < tol
+
+
+@pytest.mark.parametrize("C,dtype", [(768, torch.bfloat16), (1024, torch.bfloat16), (300, torch.bfloat16), (256, torch.float32)])
+def test_rms_norm_act_skip_adds_the_skip_gradient_in_the_backward_kernel(C, dtype):
+    """``h, skip = rms_norm_act_skip(x, w)``; ``out = skip + f(h)``: dx = norm backward + the skip's gradient, from one
+    kernel (16-byte path for bf16 rows of 256 k columns, several rows per warp; the general path otherwise)."""
+    from ml_experiments_b200.ops.norm_act import rms_norm_act_ref, rms_norm_act_skip
+
+    g = torch.Generator().manual_seed(C)
+    x = torch.randn(6000, C, generator=g).to("cuda", dtype)
+    w = (torch.rand(C, generator=g) + 0.5).to("cuda")
+    xa, wa = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    xb, wb = x.float().clone().requires_grad_(True), w.clone().requires_grad_(True)
+    h, skip = rms_norm_act_skip(xa, wa, 1e-6, "silu")
+    (skip.float() * 0.5 + torch.sin(h.float())).sum().backward()
+    hb = rms_norm_act_ref(xb, wb, 1e-6, "silu", torch.float32)
+    (xb * 0.5 + torch.sin(hb)).sum().backward()
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
+    assert _rel(h, hb) < (1e-2 if dtype == torch.bfloat16 else 1e-5)
     assert _rel(xa.grad, xb.grad) < tol and _rel(wa.grad, wb.grad) < tol
