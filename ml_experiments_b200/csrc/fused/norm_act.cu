@@ -119,17 +119,47 @@ rms_act_bwd_kernel(const TI* __restrict__ x, const float* __restrict__ w, const 
   }
 }
 
-// Backward for bf16 rows of C = 256 * VPL columns: a lane owns VPL groups of 8 adjacent columns, reads x and dy once with
-// 16-byte loads, keeps the weight-gradient sums of all its columns in registers over the rows it walks, and can add a
-// second incoming gradient (`dres`: that of a skip connection around the norm) to dx in the same pass.
+// two bf16 packed in a 32-bit word <-> fp32 (element 0 in the low half)
+__device__ __forceinline__ float bf_lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+__device__ __forceinline__ uint32_t bf_pack(float lo, float hi) {
+  const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&p);
+}
+
+// 16 bytes from shared memory, re-read at every use (a plain load of loop-invariant data would be hoisted into
+// registers for the whole row loop, which the kernel below cannot spare)
+__device__ __forceinline__ float4 lds128_volatile(const float* p) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"((uint32_t)__cvta_generic_to_shared(p)));
+  return v;
+}
+
+// 16 bytes from global memory that the compiler may not merge with an earlier load of the same address
+__device__ __forceinline__ uint4 ldg128_again(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+// Backward for bf16 rows of C = 256 * VPL columns: a lane owns VPL groups of 8 adjacent columns, moves everything with
+// 16-byte accesses, keeps the weight-gradient sums of all its columns in registers over the rows it walks, and can add
+// a second incoming gradient (`dres`: that of a skip connection around the norm) to dx in the same pass. x and dy are
+// read twice (the second time from L1): holding a row between the passes costs the registers of the second resident block.
 template <int VPL, int ACT>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 rms_act_bwd_vec_kernel(const bf16* __restrict__ x, const float* __restrict__ w, const float* __restrict__ rstd,
                        const bf16* __restrict__ dy, const bf16* __restrict__ dres, bf16* __restrict__ dx,
                        float* __restrict__ dw, long long R) {
   constexpr int C = VPL * 256;
   __shared__ float s_dw[C];
-  for (int c = threadIdx.x; c < C; c += 256) s_dw[c] = 0.f;
+  __shared__ __align__(16) float s_w[C];
+  for (int c = threadIdx.x; c < C; c += 256) {
+    s_dw[c] = 0.f;
+    s_w[c] = w[c];
+  }
   __syncthreads();
   const int lane = threadIdx.x & 31;
   const long long warps = (long long)gridDim.x * 8;
@@ -139,48 +169,57 @@ rms_act_bwd_vec_kernel(const bf16* __restrict__ x, const float* __restrict__ w, 
   for (int j = 0; j < VPL; ++j)
 #pragma unroll
     for (int e = 0; e < 8; ++e) acc[j][e] = 0.f;
+#pragma unroll 1
   for (long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5); row < R; row += warps) {
     const long long base = row * C;
     const float rs = rstd[row];
-    uint4 xr[VPL], gr[VPL];
-#pragma unroll
-    for (int j = 0; j < VPL; ++j) {
-      const long long o = base + (j * 32 + lane) * 8;
-      xr[j] = *reinterpret_cast<const uint4*>(x + o);
-      gr[j] = *reinterpret_cast<const uint4*>(dy + o);
-    }
     float dot = 0.f;
-    float gw[VPL][8], xh[VPL][8];
+    {  // pass 1: the row's dot product and the weight-gradient terms
+      uint4 xr[VPL], gr[VPL];
 #pragma unroll
-    for (int j = 0; j < VPL; ++j) {
-      const int c0 = (j * 32 + lane) * 8;
-      const float4 w0 = *reinterpret_cast<const float4*>(w + c0), w1 = *reinterpret_cast<const float4*>(w + c0 + 4);
-      const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-      const bf16* xb = reinterpret_cast<const bf16*>(&xr[j]);
-      const bf16* gb = reinterpret_cast<const bf16*>(&gr[j]);
+      for (int j = 0; j < VPL; ++j) {
+        const long long o = base + (j * 32 + lane) * 8;
+        xr[j] = *reinterpret_cast<const uint4*>(x + o);
+        gr[j] = *reinterpret_cast<const uint4*>(dy + o);
+      }
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const float h = __bfloat162float(xb[e]) * rs;
-        const float g = __bfloat162float(gb[e]) * act_grad<ACT>(wv[e] * h);
-        xh[j][e] = h;
-        gw[j][e] = g * wv[e];
-        dot = fmaf(gw[j][e], h, dot);
-        acc[j][e] = fmaf(g, h, acc[j][e]);
+      for (int j = 0; j < VPL; ++j) {
+        const int c0 = (j * 32 + lane) * 8;
+        const float4 w0 = lds128_volatile(s_w + c0), w1 = lds128_volatile(s_w + c0 + 4);
+        const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        const uint32_t xp[4] = {xr[j].x, xr[j].y, xr[j].z, xr[j].w};
+        const uint32_t gp[4] = {gr[j].x, gr[j].y, gr[j].z, gr[j].w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float h0 = bf_lo(xp[q]) * rs, h1 = bf_hi(xp[q]) * rs;
+          const float g0 = bf_lo(gp[q]) * act_grad<ACT>(wv[2 * q] * h0), g1 = bf_hi(gp[q]) * act_grad<ACT>(wv[2 * q + 1] * h1);
+          dot = fmaf(g0 * wv[2 * q], h0, dot);
+          dot = fmaf(g1 * wv[2 * q + 1], h1, dot);
+          acc[j][2 * q] = fmaf(g0, h0, acc[j][2 * q]);
+          acc[j][2 * q + 1] = fmaf(g1, h1, acc[j][2 * q + 1]);
+        }
       }
     }
     dot = warp_sum(dot) * invC;
+    // pass 2: x and dy again (the warp's own lines, still in L1), the skip's gradient, dx out
 #pragma unroll
     for (int j = 0; j < VPL; ++j) {
-      const long long o = base + (j * 32 + lane) * 8;
-      uint4 rr = make_uint4(0u, 0u, 0u, 0u);
-      if (dres) rr = *reinterpret_cast<const uint4*>(dres + o);
-      const bf16* rb = reinterpret_cast<const bf16*>(&rr);
-      uint4 out;
-      bf16* ob = reinterpret_cast<bf16*>(&out);
+      const int c0 = (j * 32 + lane) * 8;
+      const uint4 rr = dres ? *reinterpret_cast<const uint4*>(dres + base + c0) : make_uint4(0u, 0u, 0u, 0u);
+      const uint4 xv = ldg128_again(x + base + c0), gv = ldg128_again(dy + base + c0);
+      const float4 w0 = lds128_volatile(s_w + c0), w1 = lds128_volatile(s_w + c0 + 4);
+      const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+      const uint32_t xp[4] = {xv.x, xv.y, xv.z, xv.w};
+      const uint32_t gp[4] = {gv.x, gv.y, gv.z, gv.w};
+      const uint32_t rp[4] = {rr.x, rr.y, rr.z, rr.w};
+      uint32_t op[4];
 #pragma unroll
-      for (int e = 0; e < 8; ++e)
-        ob[e] = __float2bfloat16(fmaf(rs, gw[j][e] - xh[j][e] * dot, __bfloat162float(rb[e])));
-      *reinterpret_cast<uint4*>(dx + o) = out;
+      for (int q = 0; q < 4; ++q) {
+        const float h0 = bf_lo(xp[q]) * rs, h1 = bf_hi(xp[q]) * rs;
+        const float g0 = bf_lo(gp[q]) * act_grad<ACT>(wv[2 * q] * h0), g1 = bf_hi(gp[q]) * act_grad<ACT>(wv[2 * q + 1] * h1);
+        op[q] = bf_pack(fmaf(rs, g0 * wv[2 * q] - h0 * dot, bf_lo(rp[q])), fmaf(rs, g1 * wv[2 * q + 1] - h1 * dot, bf_hi(rp[q])));
+      }
+      *reinterpret_cast<uint4*>(dx + base + c0) = make_uint4(op[0], op[1], op[2], op[3]);
     }
   }
 #pragma unroll

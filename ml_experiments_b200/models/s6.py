@@ -20,7 +20,7 @@ import torch.nn.functional as F
 
 from ..ops.causal_conv import causal_conv1d_silu
 from ..ops.norm_act import rms_norm_act, rms_norm_act_skip
-from ..ops.linear import linear, linear_pair
+from ..ops.linear import linear, linear_pair, linear_tee
 from ..ops.selective_scan import selective_scan
 
 
@@ -88,7 +88,7 @@ class S6Mixer(nn.Module):
         di = cfg.d_inner
         xi, z = linear_pair(x, self.in_proj.weight, di)
         xi = causal_conv1d_silu(xi, self.conv1d.weight, self.conv1d.bias)
-        dbc = linear(xi, self.x_proj.weight)
+        dbc, xi = linear_tee(xi, self.x_proj.weight)   # the scan's gradient of xi is added in x_proj's backward GEMM
         dt, Bm, Cm = torch.split(dbc, [cfg.rank, cfg.d_state, cfg.d_state], dim=-1)
         y = selective_scan(xi.contiguous(), linear(dt, self.dt_proj.weight), -torch.exp(self.A_log.float()), Bm, Cm, self.D,
                            z, delta_bias=self.dt_proj.bias, delta_softplus=True)

@@ -75,6 +75,40 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, r
     return y
 
 
+class _LinearTee(torch.autograd.Function):
+    """``(x @ W.T, x)``: the second output stands for ``x`` in its other uses, so that their gradient arrives here and is
+    added in the epilogue of the data-gradient GEMM (autograd would add the two gradients of ``x`` in a pass of its own)."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        x16 = x.reshape(-1, x.shape[-1])
+        w16 = w.to(torch.bfloat16).contiguous()
+        ctx.save_for_backward(x16, w16)
+        ctx.x_shape, ctx.w_dtype = x.shape, w.dtype
+        return G.gemm(x16, w16).view(*x.shape[:-1], w.shape[0]), x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, dy, dtee):
+        x16, w16 = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1]).to(torch.bfloat16).contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            other = dtee.reshape(-1, dtee.shape[-1]).to(torch.bfloat16).contiguous()
+            dx = G.gemm(dy2, w16, b_mn=True, epilogue=G.EPI_AXPBY, aux=other, alpha=1.0, beta=1.0).view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            sk = G.auto_split_k(w16.shape[0], w16.shape[1], x16.shape[0])
+            dw = G.gemm(dy2, x16, a_mn=True, b_mn=True, split_k=sk, out_dtype=torch.float32).to(ctx.w_dtype)
+        return dx, dw
+
+
+def linear_tee(x: torch.Tensor, w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """``(x @ w.T, x)`` for an ``x`` with further consumers: feed them the returned ``x`` and the sum of the two
+    gradients costs no pass of its own. Both outputs must be used in the differentiated result."""
+    if not (_ok(x, w) and x.dtype == torch.bfloat16 and x.is_contiguous()):
+        return linear(x, w), x
+    return _LinearTee.apply(x, w)
+
+
 class _LinearPair(torch.autograd.Function):
     """``(x @ W[:split].T, x @ W[split:].T)`` as one node: two forward GEMMs on row ranges of ``W`` (each output dense,
     no strided halves of one wide output), and in the backward the second data-gradient GEMM adds the first one's

@@ -52,7 +52,7 @@ def _doc_bounds(t: int, doc_len: int):
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("op", choices=["gemm", "attn_fwd", "attn_bwd", "softcap_ce", "s6_fwd", "s6_bwd", "gather_fwd", "gather_bwd",
-                                   "newton_schulz", "ssd", "ssd_bwd", "jacobi", "jacobi_bwd", "tele_fwd", "tele_bwd", "alc_fwd", "alc_bwd", "rms_act"])
+                                   "newton_schulz", "ssd", "ssd_bwd", "jacobi", "jacobi_bwd", "tele_fwd", "tele_bwd", "alc_fwd", "alc_bwd", "rms_act", "rms_act_bwd"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -179,6 +179,15 @@ def main(argv=None):
         w = torch.ones(a.channels, device=dev)
         fn = lambda: rms_norm_act(x, w, 1e-6, "silu", torch.float32)
         bytes_ = x.numel() * 6.0
+    elif a.op == "rms_act_bwd":
+        # backward of the bf16 RMSNorm with the gradient of a skip connection added in the same kernel
+        from .runtime import ops
+        x = torch.randn(a.batch * a.seq, a.channels, device=dev, dtype=bf)
+        dy, dres, dx = torch.randn_like(x), torch.randn_like(x), torch.empty_like(x)
+        w, rstd = torch.ones(a.channels, device=dev), torch.rsqrt(x.float().pow(2).mean(-1) + 1e-6)
+        dw = torch.zeros(a.channels, device=dev)
+        fn = lambda: ops().rms_act_bwd(x, w, rstd, dy, dres, dx, dw, 0)
+        bytes_ = x.numel() * 8.0
     elif a.op == "newton_schulz":
         from .newton_schulz import newton_schulz_
         X = torch.randn(a.batch, a.m, a.n, device=dev, dtype=bf)

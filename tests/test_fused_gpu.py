@@ -320,6 +320,21 @@ def test_linear_pair_node_matches_autograd():
     assert rel(x.grad, xr.grad) < 2e-2 and rel(w.grad, wr.grad) < 2e-2
 
 
+def test_linear_tee_adds_the_other_gradient_in_the_epilogue():
+    from ml_experiments_b200.ops.linear import linear_tee
+
+    torch.manual_seed(12)
+    x = (torch.randn(2, 640, 256, device="cuda") * 0.5).bfloat16().requires_grad_(True)
+    w = (torch.randn(96, 256, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    y, x2 = linear_tee(x, w)
+    gy = torch.randn_like(y.float())
+    ((y.float() * gy).sum() + x2.float().pow(2).sum()).backward()
+    xr, wr = (t.detach().float().requires_grad_(True) for t in (x, w))
+    ((xr @ wr.T * gy).sum() + xr.pow(2).sum()).backward()
+    rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm()).item()
+    assert rel(y, xr.detach() @ wr.detach().T) < 1e-2 and rel(x.grad, xr.grad) < 1e-2 and rel(w.grad, wr.grad) < 2e-2
+
+
 def test_embedding_op_matches_torch():
     from ml_experiments_b200.ops.fused import embedding
 
