@@ -550,7 +550,8 @@ void ssd_fwd(const Tensor& x, const Tensor& Bm, const Tensor& Cm, const Tensor& 
 
 Tensor ssd_flip_time(const Tensor& src) {
   const c10::cuda::CUDAGuard guard(src.device());
-  TORCH_CHECK(src.is_cuda() && src.is_contiguous() && src.dim() >= 3, "ssd_flip_time: contiguous [batch, L, ...]");
+  TORCH_CHECK(src.is_cuda() && src.is_contiguous() && src.dim() >= 3 && (reinterpret_cast<uintptr_t>(src.data_ptr()) & 15) == 0 && src.numel() > 0,
+              "ssd_flip_time: contiguous, 16-byte aligned [batch, L, ...]");
   Tensor dst = at::empty_like(src);
   const int64_t row_bytes = src.numel() / (src.size(0) * src.size(1)) * src.element_size();
   b200::ssd_flip_time(src.data_ptr(), dst.data_ptr(), (int)src.size(0), (int)src.size(1), row_bytes, cur_stream());
@@ -836,9 +837,19 @@ bool norm_io_bf16(const Tensor& t, const char* n) {
   return t.scalar_type() == at::kBFloat16;
 }
 
+// The row kernels move 4 bf16 (8 bytes) per lane: the base address and every stride a row offset is built from must be
+// multiples of 8 bytes, or the access faults on the device. Views with odd offsets are refused here, on the host.
+static bool aligned8(const Tensor& t) { return (reinterpret_cast<uintptr_t>(t.data_ptr()) & 7) == 0; }
+static bool strides_mult4(const Tensor& t) {
+  for (int i = 0; i + 1 < t.dim(); ++i)
+    if (t.size(i) > 1 && t.stride(i) % 4 != 0) return false;
+  return true;
+}
+
 static void norm_rope_args(const Tensor& x, const Tensor& f1, const Tensor& f2, int64_t& rows, int& H, int& T, int& D, int& W) {
   TORCH_CHECK(x.is_cuda() && x.dim() == 4 && x.scalar_type() == at::kBFloat16 && x.stride(3) == 1, "norm_rope: x bf16 [batch, T, H, D], unit stride over D");
   TORCH_CHECK(x.size(0) == 1 || x.stride(0) == x.size(1) * x.stride(1), "norm_rope: batch entries must follow each other token-wise");
+  TORCH_CHECK(aligned8(x) && strides_mult4(x) && aligned8(f1) && aligned8(f2), "norm_rope: x and the tables must be 8-byte aligned, x's strides multiples of 4 elements");
   T = (int)x.size(1); H = (int)x.size(2); D = (int)x.size(3);
   rows = x.size(0) * x.size(1) * x.size(2);
   TORCH_CHECK(f1.scalar_type() == at::kBFloat16 && f2.scalar_type() == at::kBFloat16 && f1.is_contiguous() && f2.is_contiguous() &&
@@ -852,7 +863,8 @@ void norm_rope_fwd(const Tensor& x, const Tensor& f1, const Tensor& f2, Tensor y
   const c10::cuda::CUDAGuard guard(x.device());
   int64_t rows; int H, T, D, W;
   norm_rope_args(x, f1, f2, rows, H, T, D, W);
-  TORCH_CHECK(y.scalar_type() == at::kBFloat16 && y.is_contiguous() && y.numel() == rows * D && rstd.scalar_type() == at::kFloat && rstd.numel() == rows, "norm_rope_fwd: outputs");
+  TORCH_CHECK(y.scalar_type() == at::kBFloat16 && y.is_contiguous() && y.numel() == rows * D && rstd.scalar_type() == at::kFloat && rstd.numel() == rows &&
+              aligned8(y), "norm_rope_fwd: outputs");
   b200::norm_rope_fwd(x.data_ptr(), x.stride(1), x.stride(2), f1.data_ptr(), f2.data_ptr(), W, y.data_ptr(), rstd.data_ptr<float>(), rows, H, T, D,
                       (float)eps, cur_stream());
 }
@@ -862,7 +874,7 @@ void norm_rope_bwd(const Tensor& x, const Tensor& f1, const Tensor& f2, const Te
   int64_t rows; int H, T, D, W;
   norm_rope_args(x, f1, f2, rows, H, T, D, W);
   TORCH_CHECK(dy.scalar_type() == at::kBFloat16 && dy.is_contiguous() && dy.numel() == rows * D && dx.scalar_type() == at::kBFloat16 && dx.is_contiguous() &&
-              dx.numel() == rows * D && rstd.numel() == rows, "norm_rope_bwd: dy / dx bf16 contiguous");
+              dx.numel() == rows * D && rstd.numel() == rows && aligned8(dy) && aligned8(dx), "norm_rope_bwd: dy / dx bf16 contiguous, 8-byte aligned");
   b200::norm_rope_bwd(x.data_ptr(), x.stride(1), x.stride(2), f1.data_ptr(), f2.data_ptr(), W, rstd.data_ptr<float>(), dy.data_ptr(), dx.data_ptr(), rows,
                       H, T, D, cur_stream());
 }
@@ -874,11 +886,13 @@ void rowscale_add_fwd(const c10::optional<Tensor>& a, const Tensor& g, const Ten
   const int64_t rows = b.numel() / D;
   TORCH_CHECK(g.scalar_type() == at::kBFloat16 && g.is_contiguous() && g.numel() == rows, "rowscale_add: g bf16 [batch * T * H]");
   TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.is_contiguous() && out.numel() == b.numel(), "rowscale_add: out");
+  TORCH_CHECK(aligned8(b) && aligned8(out), "rowscale_add: b and out must be 8-byte aligned");
   const void* ap = nullptr;
   int64_t st = 0, sh = 0;
   if (a.has_value()) {
     TORCH_CHECK(a->scalar_type() == at::kBFloat16 && a->sizes() == b.sizes() && a->stride(3) == 1 &&
                 (a->size(0) == 1 || a->stride(0) == a->size(1) * a->stride(1)), "rowscale_add: a bf16 [batch, T, H, D], unit stride over D");
+    TORCH_CHECK(aligned8(*a) && strides_mult4(*a), "rowscale_add: a must be 8-byte aligned with strides that are multiples of 4 elements");
     ap = a->data_ptr(); st = a->stride(1); sh = a->stride(2);
   }
   b200::rowscale_add_fwd(ap, st, sh, g.data_ptr(), b.data_ptr(), out.data_ptr(), rows, H, D, cur_stream());
@@ -889,13 +903,13 @@ void rowscale_add_bwd(const Tensor& g, const Tensor& b, const Tensor& dout, Tens
   const int D = (int)b.size(-1);
   const int64_t rows = b.numel() / D;
   for (const Tensor* t : {&b, &dout, (const Tensor*)&db})
-    TORCH_CHECK(t->scalar_type() == at::kBFloat16 && t->is_contiguous() && t->numel() == rows * D, "rowscale_add_bwd: bf16 contiguous [rows, D]");
+    TORCH_CHECK(t->scalar_type() == at::kBFloat16 && t->is_contiguous() && t->numel() == rows * D && aligned8(*t), "rowscale_add_bwd: bf16 contiguous [rows, D], 8-byte aligned");
   TORCH_CHECK(g.numel() == rows && dg.numel() == rows && dg.scalar_type() == at::kBFloat16 && g.scalar_type() == at::kBFloat16 && g.is_contiguous() && dg.is_contiguous(), "rowscale_add_bwd: g, dg bf16 [rows]");
   b200::rowscale_add_bwd(g.data_ptr(), b.data_ptr(), dout.data_ptr(), db.data_ptr(), dg.data_ptr(), rows, D, cur_stream());
 }
 
 static void lincomb_check(const Tensor& t, int64_t n, const char* what) {
-  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.is_contiguous() && t.numel() == n, "lincomb3: bf16 contiguous ", what);
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.is_contiguous() && t.numel() == n && aligned8(t), "lincomb3: bf16 contiguous, 8-byte aligned ", what);
 }
 
 void lincomb3_fwd(const Tensor& x, const Tensor& y, const c10::optional<Tensor>& z, const Tensor& c, Tensor out) {
@@ -930,7 +944,7 @@ void rms_act_fwd(const Tensor& x, const Tensor& w, Tensor y, Tensor rstd, double
 }
 
 void rms_act_bwd(const Tensor& x, const Tensor& w, const Tensor& rstd, const Tensor& dy, const c10::optional<Tensor>& dres,
-                 Tensor dx, Tensor dw, int64_t act) {
+                 const c10::optional<Tensor>& dlead, Tensor dx, Tensor dw, int64_t act) {
   const c10::cuda::CUDAGuard guard(x.device());
   const bool xb = norm_io_bf16(x, "x"), gb = norm_io_bf16(dy, "dy");
   TORCH_CHECK(norm_io_bf16(dx, "dx") == xb && dx.numel() == x.numel() && dy.numel() == x.numel(), "dx: x's dtype and shape; dy: x's shape");
@@ -943,8 +957,16 @@ void rms_act_bwd(const Tensor& x, const Tensor& w, const Tensor& rstd, const Ten
                 "dres: a dense tensor of x's dtype and shape");
     res = dres->data_ptr();
   }
-  b200::rms_act_bwd(x.data_ptr(), xb, w.data_ptr<float>(), rstd.data_ptr<float>(), dy.data_ptr(), gb, res, dx.data_ptr(), dw.data_ptr<float>(), R, C,
-                    (int)act, cur_stream());
+  const void* lead_p = nullptr;
+  int lead = 0;
+  if (dlead.has_value()) {
+    TORCH_CHECK(dlead->is_cuda() && dlead->is_contiguous() && dlead->scalar_type() == dy.scalar_type() && dlead->dim() >= 1 &&
+                dlead->size(-1) <= C && dlead->numel() == R * dlead->size(-1), "dlead: dense [rows, lead <= C] of dy's dtype");
+    lead_p = dlead->data_ptr();
+    lead = (int)dlead->size(-1);
+  }
+  b200::rms_act_bwd(x.data_ptr(), xb, w.data_ptr<float>(), rstd.data_ptr<float>(), dy.data_ptr(), gb, res, lead_p, lead, dx.data_ptr(),
+                    dw.data_ptr<float>(), R, C, (int)act, cur_stream());
 }
 
 }  // namespace
@@ -999,7 +1021,7 @@ TORCH_LIBRARY(b200, m) {
   m.def("lincomb3_fwd(Tensor x, Tensor y, Tensor? z, Tensor c, Tensor(a!) out) -> ()");
   m.def("lincomb3_bwd(Tensor x, Tensor y, Tensor? z, Tensor c, Tensor dout, Tensor(a!) dx, Tensor(b!) dy, Tensor(c!)? dz, Tensor(d!) dc) -> ()");
   m.def("rms_act_fwd(Tensor x, Tensor w, Tensor(a!) y, Tensor(b!) rstd, float eps, int act) -> ()");
-  m.def("rms_act_bwd(Tensor x, Tensor w, Tensor rstd, Tensor dy, Tensor? dres, Tensor(a!) dx, Tensor(b!) dw, int act) -> ()");
+  m.def("rms_act_bwd(Tensor x, Tensor w, Tensor rstd, Tensor dy, Tensor? dres, Tensor? dlead, Tensor(a!) dx, Tensor(b!) dw, int act) -> ()");
   m.def("tele_fused_fwd(Tensor x, Tensor freq, Tensor phase, Tensor kern, Tensor expo, Tensor(a!) out, int H, int half, float max_rec) -> ()");
   m.def("tele_fused_bwd(Tensor x, Tensor freq, Tensor phase, Tensor kern, Tensor expo, Tensor dout, Tensor(a!) dx, Tensor(b!) dfreq, Tensor(c!) dphase, Tensor(d!) dkern, Tensor(e!) dexpo_h, int H, int half, float max_rec) -> ()");
   m.def("alc_fused_fwd(Tensor x, Tensor half_w, Tensor center, Tensor kern, Tensor(a!) out, int H, int half) -> ()");

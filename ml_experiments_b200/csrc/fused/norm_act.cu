@@ -71,8 +71,8 @@ rms_act_fwd_kernel(const TI* __restrict__ x, const float* __restrict__ w, TO* __
 template <typename TI, typename TO, int ACT>
 __global__ void __launch_bounds__(256)
 rms_act_bwd_kernel(const TI* __restrict__ x, const float* __restrict__ w, const float* __restrict__ rstd,
-                   const TO* __restrict__ dy, const TI* __restrict__ dres, TI* __restrict__ dx, float* __restrict__ dw,
-                   long long R, int C) {
+                   const TO* __restrict__ dy, const TI* __restrict__ dres, const TO* __restrict__ dlead, int lead,
+                   TI* __restrict__ dx, float* __restrict__ dw, long long R, int C) {
   extern __shared__ float s_dw[];  // [C]
   for (int c = threadIdx.x; c < C; c += 256) s_dw[c] = 0.f;
   __syncthreads();
@@ -84,26 +84,28 @@ rms_act_bwd_kernel(const TI* __restrict__ x, const float* __restrict__ w, const 
     const long long base = row * C;
     const float rs = rstd[row];
     float dot = 0.f;
+    // gradient of the normed row: dy plus, in the first `lead` columns, the gradient that came in through the slice
+    auto gin = [&](int c) { return ldf(dy, base + c) + (c < lead ? ldf(dlead, row * lead + c) : 0.f); };
 #pragma unroll
     for (int i = 0; i < 8; ++i) {  // the first 256 columns accumulate dw in registers
       const int c = lane + 32 * i;
       if (c < C) {
         const float xh = ldf(x, base + c) * rs, wc = w[c];
-        const float g = ldf(dy, base + c) * act_grad<ACT>(wc * xh);
+        const float g = gin(c) * act_grad<ACT>(wc * xh);
         dot += g * wc * xh;
         acc[i] += g * xh;
       }
     }
     for (int c = lane + 256; c < C; c += 32) {
       const float xh = ldf(x, base + c) * rs, wc = w[c];
-      const float g = ldf(dy, base + c) * act_grad<ACT>(wc * xh);
+      const float g = gin(c) * act_grad<ACT>(wc * xh);
       dot += g * wc * xh;
       atomicAdd(&s_dw[c], g * xh);
     }
     dot = warp_sum(dot) * invC;
     for (int c = lane; c < C; c += 32) {
       const float xh = ldf(x, base + c) * rs, wc = w[c];
-      const float g = ldf(dy, base + c) * act_grad<ACT>(wc * xh);
+      const float g = gin(c) * act_grad<ACT>(wc * xh);
       stf(dx, base + c, rs * (g * wc - xh * dot) + (dres ? ldf(dres, base + c) : 0.f));
     }
   }
@@ -151,8 +153,8 @@ __device__ __forceinline__ uint4 ldg128_again(const void* p) {
 template <int VPL, int ACT>
 __global__ void __launch_bounds__(256, 2)
 rms_act_bwd_vec_kernel(const bf16* __restrict__ x, const float* __restrict__ w, const float* __restrict__ rstd,
-                       const bf16* __restrict__ dy, const bf16* __restrict__ dres, bf16* __restrict__ dx,
-                       float* __restrict__ dw, long long R) {
+                       const bf16* __restrict__ dy, const bf16* __restrict__ dres, const bf16* __restrict__ dlead, int lead,
+                       bf16* __restrict__ dx, float* __restrict__ dw, long long R) {
   constexpr int C = VPL * 256;
   __shared__ float s_dw[C];
   __shared__ __align__(16) float s_w[C];
@@ -192,7 +194,11 @@ rms_act_bwd_vec_kernel(const bf16* __restrict__ x, const float* __restrict__ w, 
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const float h0 = bf_lo(xp[q]) * rs, h1 = bf_hi(xp[q]) * rs;
-          const float g0 = bf_lo(gp[q]) * act_grad<ACT>(wv[2 * q] * h0), g1 = bf_hi(gp[q]) * act_grad<ACT>(wv[2 * q + 1] * h1);
+          float g0 = bf_lo(gp[q]), g1 = bf_hi(gp[q]);
+          if (j == 0 && c0 + 2 * q < lead) g0 += __bfloat162float(dlead[row * lead + c0 + 2 * q]);
+          if (j == 0 && c0 + 2 * q + 1 < lead) g1 += __bfloat162float(dlead[row * lead + c0 + 2 * q + 1]);
+          g0 *= act_grad<ACT>(wv[2 * q] * h0);
+          g1 *= act_grad<ACT>(wv[2 * q + 1] * h1);
           dot = fmaf(g0 * wv[2 * q], h0, dot);
           dot = fmaf(g1 * wv[2 * q + 1], h1, dot);
           acc[j][2 * q] = fmaf(g0, h0, acc[j][2 * q]);
@@ -216,7 +222,11 @@ rms_act_bwd_vec_kernel(const bf16* __restrict__ x, const float* __restrict__ w, 
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
         const float h0 = bf_lo(xp[q]) * rs, h1 = bf_hi(xp[q]) * rs;
-        const float g0 = bf_lo(gp[q]) * act_grad<ACT>(wv[2 * q] * h0), g1 = bf_hi(gp[q]) * act_grad<ACT>(wv[2 * q + 1] * h1);
+        float g0 = bf_lo(gp[q]), g1 = bf_hi(gp[q]);
+        if (j == 0 && c0 + 2 * q < lead) g0 += __bfloat162float(dlead[row * lead + c0 + 2 * q]);
+        if (j == 0 && c0 + 2 * q + 1 < lead) g1 += __bfloat162float(dlead[row * lead + c0 + 2 * q + 1]);
+        g0 *= act_grad<ACT>(wv[2 * q] * h0);
+        g1 *= act_grad<ACT>(wv[2 * q + 1] * h1);
         op[q] = bf_pack(fmaf(rs, g0 * wv[2 * q] - h0 * dot, bf_lo(rp[q])), fmaf(rs, g1 * wv[2 * q + 1] - h1 * dot, bf_hi(rp[q])));
       }
       *reinterpret_cast<uint4*>(dx + base + c0) = make_uint4(op[0], op[1], op[2], op[3]);
@@ -269,7 +279,10 @@ void rms_act_fwd(const void* x, bool x_bf16, const float* w, void* y, bool y_bf1
 }
 
 void rms_act_bwd(const void* x, bool x_bf16, const float* w, const float* rstd, const void* dy, bool dy_bf16,
-                 const void* dres, void* dx, float* dw, long long R, int C, int act, cudaStream_t s) {
+                 const void* dres, const void* dlead, int lead, void* dx, float* dw, long long R, int C, int act,
+                 cudaStream_t s) {
+  if (dlead == nullptr) lead = 0;
+  if (lead < 0 || lead > C) throw std::runtime_error("rms_act: lead columns out of range");
   if (C < 1 || C > 4096) throw std::runtime_error("rms_act: row length must be in [1, 4096]");
   if (R == 0) return;
   const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(dx) |
@@ -278,7 +291,8 @@ void rms_act_bwd(const void* x, bool x_bf16, const float* w, const float* rstd, 
     const int grid = (int)std::min<long long>((R + 7) / 8, 148LL * 4);
 #define RMS_VEC(VPL_)                                                                                                  \
   DISPATCH_ACT(act, rms_act_bwd_vec_kernel<VPL_, ACT_><<<grid, 256, 0, s>>>((const bf16*)x, w, rstd, (const bf16*)dy,  \
-                                                                             (const bf16*)dres, (bf16*)dx, dw, R))
+                                                                             (const bf16*)dres, (const bf16*)dlead, lead,    \
+                                                                             (bf16*)dx, dw, R))
     switch (C / 256) {
       case 1: RMS_VEC(1); break;
       case 2: RMS_VEC(2); break;
@@ -290,7 +304,7 @@ void rms_act_bwd(const void* x, bool x_bf16, const float* w, const float* rstd, 
     return;
   }
   DISPATCH_ACT(act, DISPATCH_IO(x_bf16, dy_bf16, {
-    rms_act_bwd_kernel<TI_, TO_, ACT_><<<grid_for(R), 256, (size_t)C * sizeof(float), s>>>((const TI_*)x, w, rstd, (const TO_*)dy, (const TI_*)dres, (TI_*)dx, dw, R, C);
+    rms_act_bwd_kernel<TI_, TO_, ACT_><<<grid_for(R), 256, (size_t)C * sizeof(float), s>>>((const TI_*)x, w, rstd, (const TO_*)dy, (const TI_*)dres, (const TO_*)dlead, lead, (TI_*)dx, dw, R, C);
   }));
   chk("rms_act_bwd");
 }

@@ -13,6 +13,8 @@ enum NormAct { NORM_ACT_NONE = 0, NORM_ACT_SILU = 1, NORM_ACT_SIGMOID = 2, NORM_
 void rms_act_fwd(const void* x, bool x_bf16, const float* w, void* y, bool y_bf16, float* rstd, long long R, int C, float eps,
                  int act, cudaStream_t s);
 // dres: optional second gradient of x's shape and dtype (a skip connection around the norm), added to dx.
+// dlead: optional [R, lead] gradient (dy's dtype) of the first `lead` columns of y, added to dy's on the fly.
 void rms_act_bwd(const void* x, bool x_bf16, const float* w, const float* rstd, const void* dy, bool dy_bf16,
-                 const void* dres, void* dx, float* dw, long long R, int C, int act, cudaStream_t s);
+                 const void* dres, const void* dlead, int lead, void* dx, float* dw, long long R, int C, int act,
+                 cudaStream_t s);
 }  // namespace b200

@@ -21,14 +21,36 @@ from ..ops.attention import attention_reference, flash_attention
 from ..ops.fp8_linear import CastedLinearT, head_ce_loss
 from ..ops.fused import embedding, softcapped_cross_entropy
 from ..ops.linear import linear, linear_t, mlp_relu2
+from ..ops.norm_act import rms_norm_act, rms_norm_act_skip
 from ..ops.norm_rope import norm_rotary
 from ..ops.rowops import lincomb3, rowscale_add
 
 BLOCK = 128  # attention block / window granularity in tokens
 
 
+_ONES: dict = {}
+
+
+def _ones(n: int, device) -> torch.Tensor:
+    key = (n, str(device))
+    if key not in _ONES:
+        _ONES[key] = torch.ones(n, device=device)
+    return _ONES[key]
+
+
 def norm(x):
+    if x.is_cuda and x.dtype == torch.bfloat16:   # weightless RMSNorm on the row kernel (unit weights, eps of the dtype)
+        return rms_norm_act(x, _ones(x.size(-1), x.device), torch.finfo(x.dtype).eps)
     return F.rms_norm(x, (x.size(-1),))
+
+
+def norm_skip(x, lead_cols: int = 0):
+    """``(norm(x), x[, norm(x)[..., :lead_cols]])`` for ``x + f(norm(x))``: on CUDA the skip's gradient (and that of the
+    leading columns, the gates' input) joins the norm's in one backward kernel."""
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        return rms_norm_act_skip(x, _ones(x.size(-1), x.device), torch.finfo(x.dtype).eps, lead_cols=lead_cols)
+    h = F.rms_norm(x, (x.size(-1),))
+    return (h, x, h[..., :lead_cols]) if lead_cols else (h, x)
 
 
 def next_multiple_of_n(v, *, n: int) -> int:
@@ -133,13 +155,14 @@ class CausalSelfAttention(nn.Module):
         self.num_heads, self.head_dim, self.dim, self.paired = num_heads, head_dim, dim, paired
         assert num_heads * head_dim == dim, "num_heads * head_dim must equal model_dim"
 
-    def forward(self, x, a: AttnArgs, qkvo_w, residual=None):
-        """``residual``: added to the output inside the output projection's GEMM (the block's skip connection)."""
+    def forward(self, x, a: AttnArgs, qkvo_w, residual=None, gate_in=None):
+        """``residual``: added to the output inside the output projection's GEMM (the block's skip connection).
+        ``gate_in``: ``x[..., :12]`` when the caller already has it as a tensor of its own."""
         B, T = x.shape[:2]
         assert B == 1, "packed variable-length sequences need B == 1"
         H, D = self.num_heads, self.head_dim
         q, k, v = linear(x, a.sa_lambdas[0] * qkvo_w[:self.dim * 3].type_as(x)).view(B, T, 3, H, D).unbind(2)   # unbind: one stack in the backward
-        gate_in = x[..., :12]
+        gate_in = x[..., :12] if gate_in is None else gate_in
         f1, f2 = a.yarn.factor1, a.yarn.factor2          # QK norm and the rotary map are one kernel on CUDA
         # value-embedding mix v + 2 sigmoid(gate) * ve: one kernel in the [T, H, D] layout (reinterpreting the result as
         # [2T, H/2, D] afterwards is the same flat order the reference mixes in)
@@ -180,9 +203,11 @@ class Block(nn.Module):
 
     def forward(self, x, attn_args, qkvo_w=None, c_fc=None, c_proj=None):
         if self.attn is not None:      # the skip connections are added in the epilogue of each branch's last GEMM
-            x = self.attn(norm(x), attn_args, qkvo_w, residual=x)
+            h, skip, gate_in = norm_skip(x, 12)
+            x = self.attn(h, attn_args, qkvo_w, residual=skip, gate_in=gate_in)
         if self.mlp is not None:
-            x = self.mlp(norm(x), c_fc, c_proj, residual=x)
+            h, skip = norm_skip(x)
+            x = self.mlp(h, c_fc, c_proj, residual=skip)
         return x
 
 

@@ -186,7 +186,7 @@ def main(argv=None):
         dy, dres, dx = torch.randn_like(x), torch.randn_like(x), torch.empty_like(x)
         w, rstd = torch.ones(a.channels, device=dev), torch.rsqrt(x.float().pow(2).mean(-1) + 1e-6)
         dw = torch.zeros(a.channels, device=dev)
-        fn = lambda: ops().rms_act_bwd(x, w, rstd, dy, dres, dx, dw, 0)
+        fn = lambda: ops().rms_act_bwd(x, w, rstd, dy, dres, None, dx, dw, 0)
         bytes_ = x.numel() * 8.0
     elif a.op == "newton_schulz":
         from .newton_schulz import newton_schulz_

@@ -78,10 +78,12 @@ def test_rms_norm_act(C, act, dtypes):
     assert _rel(xa.grad, xb.grad) < tol and _rel(wa.grad, wb.grad) < tol
 
 
-@pytest.mark.parametrize("C,dtype", [(768, torch.bfloat16), (1024, torch.bfloat16), (300, torch.bfloat16), (256, torch.float32)])
-def test_rms_norm_act_skip_adds_the_skip_gradient_in_the_backward_kernel(C, dtype):
-    """``h, skip = rms_norm_act_skip(x, w)``; ``out = skip + f(h)``: dx = norm backward + the skip's gradient, from one
-    kernel (16-byte path for bf16 rows of 256 k columns, several rows per warp; the general path otherwise)."""
+@pytest.mark.parametrize("C,dtype,lead", [(768, torch.bfloat16, 12), (1024, torch.bfloat16, 0), (512, torch.bfloat16, 9), (300, torch.bfloat16, 12),
+                                          (256, torch.float32, 5)])
+def test_rms_norm_act_skip_adds_the_skip_gradient_in_the_backward_kernel(C, dtype, lead):
+    """``h, skip[, first] = rms_norm_act_skip(x, w)``; ``out = skip + f(h) + g(first)``: dx = norm backward of (dh with
+    d first added into its leading columns) + the skip's gradient, from one kernel (16-byte path for bf16 rows of 256 k
+    columns, several rows per warp; the general path otherwise)."""
     from ml_experiments_b200.ops.norm_act import rms_norm_act_ref, rms_norm_act_skip
 
     g = torch.Generator().manual_seed(C)
@@ -89,10 +91,17 @@ def test_rms_norm_act_skip_adds_the_skip_gradient_in_the_backward_kernel(C, dtyp
     w = (torch.rand(C, generator=g) + 0.5).to("cuda")
     xa, wa = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
     xb, wb = x.float().clone().requires_grad_(True), w.clone().requires_grad_(True)
-    h, skip = rms_norm_act_skip(xa, wa, 1e-6, "silu")
-    (skip.float() * 0.5 + torch.sin(h.float())).sum().backward()
+    outs = rms_norm_act_skip(xa, wa, 1e-6, "silu", lead_cols=lead)
+    h, skip = outs[0], outs[1]
+    loss = (skip.float() * 0.5 + torch.sin(h.float())).sum()
+    if lead:
+        assert outs[2].shape == (6000, lead) and torch.equal(outs[2], h[:, :lead])
+        loss = loss + (outs[2].float() * 3.0).pow(2).sum()
+    loss.backward()
     hb = rms_norm_act_ref(xb, wb, 1e-6, "silu", torch.float32)
-    (xb * 0.5 + torch.sin(hb)).sum().backward()
+    hq = hb.detach().to(dtype).float() + (hb - hb.detach())          # the slice's consumer sees the rounded output
+    loss_b = (xb * 0.5 + torch.sin(hb)).sum() + ((hq[:, :lead] * 3.0).pow(2).sum() if lead else 0.0)
+    loss_b.backward()
     tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
     assert _rel(h, hb) < (1e-2 if dtype == torch.bfloat16 else 1e-5)
     assert _rel(xa.grad, xb.grad) < tol and _rel(wa.grad, wb.grad) < tol
