@@ -133,8 +133,40 @@ def _attend(q, k, v, seqlens, window_tokens: int, scale: float, factor: int):
     de = torch.minimum(de, pos + window_tokens + 1)
     blocks = -(-window_tokens // BLOCK) + 1
     if q.is_cuda and q.shape[-1] == 128 and q.dtype == torch.bfloat16:
-        return flash_attention(q.contiguous(), k.contiguous(), v.contiguous(), ds, de, scale, blocks)
+        # the kernel reads rows through a token stride: a [T, H, D] slice of the fused QKV output needs no copy
+        rows = lambda t: t if (t.stride(2) == 1 and t.stride(1) == t.shape[2] and t.stride(0) % 8 == 0) else t.contiguous()
+        return flash_attention(rows(q), rows(k), rows(v), ds, de, scale, blocks)
     return attention_reference(q, k, v, ds, scale, blocks).to(q.dtype)
+
+
+class _KeyOffset(torch.autograd.Function):
+    """The stationary (second) half of every key row replaced by that of the previous token (token 0 keeps its own):
+    ``cat([k[..., :D/2], cat([k[:, :1, :, D/2:], k[:, :-1, :, D/2:]], 1)], -1)`` as one copy + one shifted half-row
+    copy, and the same two copies in the backward (the nested ``cat`` costs two unaligned concatenations forward and three
+    zero-filled full-size slice gradients plus their sums backward)."""
+
+    @staticmethod
+    def forward(ctx, k):
+        h = k.shape[-1] // 2
+        out = k.clone(memory_format=torch.contiguous_format)
+        out[:, 1:, :, h:] = k[:, :-1, :, h:]
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        h = g.shape[-1] // 2
+        dk = g.clone(memory_format=torch.contiguous_format)
+        T = g.shape[1]
+        if T > 1:
+            dk[:, :-1, :, h:] = g[:, 1:, :, h:]
+            dk[:, 0, :, h:] += g[:, 0, :, h:]
+            dk[:, -1, :, h:] = 0
+        return dk
+
+
+def key_offset(k: torch.Tensor) -> torch.Tensor:
+    """``k [B, T, H, D]``: shift the second half of the head dimension one token forward."""
+    return _KeyOffset.apply(k)
 
 
 @dataclass
@@ -178,7 +210,7 @@ class CausalSelfAttention(nn.Module):
         else:
             q, k = norm_rotary(q, f1, f2), norm_rotary(k, f1, f2)
             if a.key_offset:  # shift the stationary half of the key one token forward: one-layer induction
-                k = torch.cat([k[..., :D // 2], torch.cat([k[:, :1, :, D // 2:], k[:, :-1, :, D // 2:]], dim=1)], dim=-1)
+                k = key_offset(k)
             y = _attend(q[0], k[0], v[0], a.seqlens, a.bm_size, a.yarn.attn_scale, 1)
         y = rowscale_add(None, torch.sigmoid(F.linear(gate_in, a.attn_gate_w)).view(B, T, H), y.reshape(B, T, H, D))
         return linear(y.reshape(B, T, H * D), a.sa_lambdas[1] * qkvo_w[self.dim * 3:].type_as(y), residual=residual)

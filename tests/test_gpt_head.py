@@ -62,6 +62,20 @@ def test_paired_head_attention_is_attention_over_the_interleaved_sequence():
     assert torch.allclose(got, want, atol=1e-4), (got - want).abs().max()
 
 
+def test_key_offset_node_is_the_nested_concatenation():
+    """Value and gradient of the shift of the keys' stationary half against the two ``cat`` calls it replaces."""
+    from ml_experiments_b200.models.gpt_head import key_offset
+
+    for T in (1, 2, 9):
+        k = torch.randn(1, T, 3, 8, dtype=torch.float64, requires_grad=True)
+        ref = torch.cat([k[..., :4], torch.cat([k[:, :1, :, 4:], k[:, :-1, :, 4:]], dim=1)], dim=-1)
+        out = key_offset(k)
+        w = torch.randn_like(out)
+        g_ref, = torch.autograd.grad((ref * w).sum(), k)
+        g_out, = torch.autograd.grad((out * w).sum(), k)
+        assert torch.equal(ref, out) and torch.allclose(g_ref, g_out)
+
+
 def test_mtp_loss_reference_matches_definition():
     torch.manual_seed(2)
     T, V = 7, 16
