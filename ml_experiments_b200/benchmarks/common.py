@@ -1,6 +1,7 @@
 """Shared timing helpers: CUDA-event timing bracketed by barrier + synchronize, maximum over ranks."""
 from __future__ import annotations
 
+import atexit
 import json
 import os
 
@@ -15,7 +16,17 @@ def init_dist():
     if world > 1 and not dist.is_initialized():
         dist.init_process_group("nccl" if torch.cuda.is_available() else "gloo",
                                 device_id=torch.device("cuda", local) if torch.cuda.is_available() else None)
+        atexit.register(_teardown)
     return rank, world, local
+
+
+def _teardown():
+    """Leave the process group at interpreter exit (the benchmark scripts return from ``main`` without doing so)."""
+    if dist.is_initialized():
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
 
 
 def timed_steps(step_fn, steps: int, warmup: int, world: int, device) -> float:
