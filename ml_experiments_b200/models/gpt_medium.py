@@ -19,7 +19,7 @@ from ..ops.linear import linear, linear_t, mlp_relu2
 from ..ops.norm_rope import norm_rotary
 from ..ops.rowops import lincomb3, rowscale_add
 from .gpt import CastedLinear
-from .gpt_head import BLOCK, ForwardScheduleConfig, Yarn, _attend, next_multiple_of_n, norm
+from .gpt_head import BLOCK, ForwardScheduleConfig, Yarn, _attend, next_multiple_of_n, norm, norm_skip
 
 VE_LAYERS = (0, 1, 2, 3, 4, 11, 12, 13, 14, 15)
 LONG_LAYERS = (0, 4, 11, 15)
@@ -51,7 +51,9 @@ class CausalSelfAttention(nn.Module):
             self.value_embed_gate = CastedLinear(16, num_heads)
             _label(self.value_embed_gate.weight, "value_embed_gate", lr_mul=0.1)
 
-    def forward(self, x, ve, sa_lambdas, seqlens, bm_size: int, yarn: Yarn, key_offset: bool):
+    def forward(self, x, ve, sa_lambdas, seqlens, bm_size: int, yarn: Yarn, key_offset: bool, residual=None, gate_in=None):
+        """``residual`` (the block's skip connection) is added in the output projection's GEMM epilogue; ``gate_in`` is
+        ``x[..., :16]`` when the caller already holds it as a tensor of its own."""
         B, T = x.shape[:2]
         assert B == 1, "packed variable-length sequences need B == 1"
         H, D = self.num_heads, self.head_dim
@@ -63,12 +65,12 @@ class CausalSelfAttention(nn.Module):
             band[D // 4: D // 2] = True
             band[3 * D // 4:] = True
             k = torch.where(band, prev, k)
-        gate_in = x[..., :16]
+        gate_in = x[..., :16] if gate_in is None else gate_in
         if ve is not None:
             v = rowscale_add(v, 2 * torch.sigmoid(self.value_embed_gate(gate_in)).view(B, T, H), ve.view(B, T, H, D))
         y = _attend(q[0], k[0], v[0], seqlens, bm_size, yarn.attn_scale, 1)
         y = rowscale_add(None, torch.sigmoid(self.attn_gate(gate_in)).view(B, T, H), y.reshape(B, T, H, D))
-        return linear(y.reshape(B, T, H * D), sa_lambdas[1] * self.qkvo_w[self.dim * 3:].type_as(y))
+        return linear(y.reshape(B, T, H * D), sa_lambdas[1] * self.qkvo_w[self.dim * 3:].type_as(y), residual=residual)
 
 
 class MLP(nn.Module):
@@ -78,8 +80,8 @@ class MLP(nn.Module):
         self.c_fc = _label(nn.Parameter(torch.empty(4 * dim, dim).uniform_(-bound, bound)), "mlp")
         self.c_proj = _label(nn.Parameter(torch.zeros(4 * dim, dim)), "mlp", lr_mul=2.0)
 
-    def forward(self, x):
-        return mlp_relu2(x, self.c_fc.type_as(x), self.c_proj.type_as(x))
+    def forward(self, x, residual=None):
+        return mlp_relu2(x, self.c_fc.type_as(x), self.c_proj.type_as(x), residual)
 
 
 class Block(nn.Module):
@@ -88,8 +90,10 @@ class Block(nn.Module):
         self.attn, self.mlp = CausalSelfAttention(dim, head_dim, num_heads, layer_idx), MLP(dim)
 
     def forward(self, x, **attn_args):
-        x = x + self.attn(norm(x), **attn_args)
-        return x + self.mlp(norm(x))
+        h, skip, gate_in = norm_skip(x, 16)       # skip and gate-input gradients join the norm's backward kernel
+        x = self.attn(h, residual=skip, gate_in=gate_in, **attn_args)
+        h, skip = norm_skip(x)
+        return self.mlp(h, residual=skip)
 
 
 class GPTMedium(nn.Module):
