@@ -61,7 +61,14 @@ class ResidualConvBlock(nn.Module):
         self.activation = nn.ReLU()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:  # (B, L, C)
-        y = self.conv(x.transpose(1, 2)).transpose(1, 2)
+        if x.device.type == "cpu" and x.is_contiguous():
+            # (B, L, C) in memory IS the channels-last layout of a (B, C, 1, L) image: the library convolution takes it and
+            # returns it without the two layout copies (and their two copies in the backward) of the channel-first call
+            c = self.conv
+            y = F.conv2d(x.permute(0, 2, 1).unsqueeze(2), c.weight.unsqueeze(2), c.bias, padding=(0, c.padding[0]))
+            y = y.squeeze(2).permute(0, 2, 1)
+        else:
+            y = self.conv(x.transpose(1, 2)).transpose(1, 2)
         y = y[:, : x.shape[1]]  # an even window with pad k//2 yields L+1 positions; keep the first L
         return F.relu(self.norm(y)) + x
 
