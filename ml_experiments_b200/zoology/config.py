@@ -49,20 +49,23 @@ class BaseConfig(BaseModel):
             print(self)
 
 
-class FunctionConfig(BaseConfig):
+class _ByImportString(BaseConfig):
+    """``name``: dotted import path of a class or function; ``kwargs``: keyword arguments bound at instantiation."""
     name: str
     kwargs: dict = {}
 
-    def instantiate(self):
-        return partial(import_from_str(self.name), **self.kwargs)
+    def _target(self):
+        return import_from_str(self.name)
 
 
-class ModuleConfig(BaseConfig):
-    name: str
-    kwargs: dict = {}
-
+class ModuleConfig(_ByImportString):
     def instantiate(self, **kwargs):
-        return import_from_str(self.name)(**kwargs, **self.kwargs)
+        return self._target()(**kwargs, **self.kwargs)
+
+
+class FunctionConfig(_ByImportString):
+    def instantiate(self):
+        return partial(self._target(), **self.kwargs)
 
 
 class DataSegmentConfig(BaseConfig):
@@ -86,21 +89,24 @@ class DataConfig(BaseConfig):
 
 
 class ModelConfig(BaseConfig):
-    sequence_mixer: Optional[ModuleConfig] = None
-    state_mixer: ModuleConfig = ModuleConfig(name="zoology.mixers.mlp.MLP", kwargs={"hidden_mult": 4})
+    name: str = "default"
+    # size
     d_model: int = 128
     n_layers: int = 2
+    vocab_size: int = 8_192
+    pad_vocab_size_multiple: int = 1
     max_position_embeddings: int = 64
+    # blocks
+    block_type: Literal["TransformerBlock", "MambaBlock", "Mamba2Block"] = "TransformerBlock"
+    sequence_mixer: Optional[ModuleConfig] = None
+    state_mixer: ModuleConfig = ModuleConfig(name="zoology.mixers.mlp.MLP", kwargs={"hidden_mult": 4})
+    layer_norm_epsilon: float = 1e-5
+    # embeddings and regularisation
     learnable_word_embeddings: bool = True
     embedding_init_type: Literal["default", "spherical", "normal"] = "default"
-    vocab_size: int = 8_192
-    resid_dropout: float = 0.0
     embed_dropout: float = 0.1
+    resid_dropout: float = 0.0
     drop_path: float = 0.0
-    layer_norm_epsilon: float = 1e-5
-    pad_vocab_size_multiple: int = 1
-    block_type: Literal["TransformerBlock", "MambaBlock", "Mamba2Block"] = "TransformerBlock"
-    name: str = "default"
 
 
 class LoggerConfig(BaseConfig):
@@ -109,18 +115,21 @@ class LoggerConfig(BaseConfig):
 
 
 class TrainConfig(BaseConfig):
-    data: DataConfig
     model: ModelConfig
+    data: DataConfig
     logger: LoggerConfig = LoggerConfig()
-    max_epochs: int = 100
-    loss_type: Literal["ce", "mse", "ce_embed"] = "ce"
-    input_type: Literal["discrete", "continuous"] = "discrete"
-    early_stopping_metric: Optional[str] = "valid/accuracy"  # None disables early stopping
-    early_stopping_threshold: float = 0.99
-    slice_keys: List[str] = []
+    # identification of a run inside a sweep
+    run_id: Optional[str] = "default"
+    sweep_id: Optional[str] = None
+    launch_id: Optional[str] = None
+    seed: int = 123
+    # optimisation
     learning_rate: float = 1e-3
     weight_decay: float = 0.1
-    seed: int = 123
-    launch_id: Optional[str] = None
-    sweep_id: Optional[str] = None
-    run_id: Optional[str] = "default"
+    max_epochs: int = 100
+    input_type: Literal["discrete", "continuous"] = "discrete"
+    loss_type: Literal["ce", "mse", "ce_embed"] = "ce"
+    # evaluation
+    slice_keys: List[str] = []
+    early_stopping_metric: Optional[str] = "valid/accuracy"  # None disables early stopping
+    early_stopping_threshold: float = 0.99
