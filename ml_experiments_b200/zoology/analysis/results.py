@@ -38,7 +38,7 @@ def load_results(csv_path: str | None = None, log_dir: str | None = None) -> pd.
             model, data = cfg.get("model", {}), cfg.get("data", {})
             mixer = (model.get("sequence_mixer") or {}).get("name", "")
             train_cfgs = data.get("train_configs") or [{}]
-            rows.append({"run_id": cfg.get("run_id", os.path.basename(path)[:-6]), "mixer": mixer, "d_model": model.get("d_model"),
+            rows.append({"run_id": cfg.get("run_id", os.path.basename(path)[:-6]), "mixer": mixer, "model": model.get("name"), "d_model": model.get("d_model"),
                          "n_layers": model.get("n_layers"), "vocab_size": model.get("vocab_size"), "seq_len": train_cfgs[0].get("input_seq_len"),
                          "lr": cfg.get("learning_rate"), "n_params": n_params, "state_size": state, "best_acc": best["valid/accuracy"],
                          "best_loss": best.get("valid/loss"), "best_epoch": best.get("epoch")})
@@ -143,18 +143,72 @@ def plot_mqar(df: pd.DataFrame, path: str, metric: str = "best_acc") -> bool:
     return True
 
 
+def state_tradeoff_table(df: pd.DataFrame, metric: str = "best_acc", family: str = "model") -> pd.DataFrame:
+    """Recall against memory (the figure of zoology/experiments/paper_configs/arxiv24_based_figure2/plot.py): per model
+    family and recurrent-state size the best ``metric`` over learning rates, plus ``on_frontier``: no run of the same
+    family reaches at least this accuracy with a smaller state."""
+    need = {family, "state_size", metric}
+    if df.empty or not need <= set(df.columns):
+        return pd.DataFrame(columns=[family, "state_size", metric, "on_frontier"])
+    d = df.dropna(subset=["state_size", metric]).copy()
+    d[family] = d[family].fillna(d["mixer"].map(short_mixer)) if "mixer" in d else d[family]
+    d = d.groupby([family, "state_size"], as_index=False)[metric].max().sort_values([family, "state_size"])
+    best_so_far = d.groupby(family)[metric].cummax()
+    prev_best = best_so_far.groupby(d[family]).shift(1)
+    d["on_frontier"] = prev_best.isna() | (d[metric] > prev_best)
+    return d.reset_index(drop=True)
+
+
+def plot_state_tradeoff(df: pd.DataFrame, path: str, metric: str = "best_acc", family: str = "model") -> bool:
+    """Scatter of every (family, state size) point with the family's frontier as a line; SVG, log2 x axis."""
+    import math
+    t = state_tradeoff_table(df, metric, family)
+    if t.empty:
+        return False
+    W, H, L, R, T, B = 520, 340, 52, 130, 20, 40
+    fams = sorted(t[family].unique())
+    color = {m: PALETTE[i % len(PALETTE)] for i, m in enumerate(fams)}
+    lx = [math.log2(max(float(v), 1.0)) for v in t["state_size"]]
+    x0, x1 = min(lx) - 0.3, max(lx) + 0.3
+    ymax = max(1.0, float(t[metric].max()))
+    px = lambda v: L + (math.log2(max(float(v), 1.0)) - x0) / max(x1 - x0, 1e-9) * (W - L - R)
+    py = lambda v: T + (1 - v / ymax) * (H - T - B)
+    out = [f'<svg xmlns="http://www.w3.org/2000/svg" width="{W}" height="{H}" font-family="sans-serif" font-size="10">',
+           '<rect width="100%" height="100%" fill="white"/>', f'<rect x="{L}" y="{T}" width="{W - L - R}" height="{H - T - B}" fill="none" stroke="#888"/>']
+    for k in range(5):
+        v = ymax * k / 4
+        out.append(f'<line x1="{L}" x2="{W - R}" y1="{py(v):.1f}" y2="{py(v):.1f}" stroke="#ddd"/><text x="{L - 4}" y="{py(v) + 3:.1f}" text-anchor="end">{v:.2f}</text>')
+    for e in range(int(math.ceil(x0)), int(math.floor(x1)) + 1, max(1, int((x1 - x0) // 8) or 1)):
+        out.append(f'<text x="{px(2 ** e):.1f}" y="{H - B + 12}" text-anchor="middle">2^{e}</text>')
+    out.append(f'<text x="{(L + W - R) / 2}" y="{H - 8}" text-anchor="middle">recurrent state size (elements)</text>')
+    for j, m in enumerate(fams):
+        g = t[t[family] == m]
+        out += [f'<circle cx="{px(a):.1f}" cy="{py(b):.1f}" r="2.5" fill="{color[m]}" fill-opacity="0.55"/>' for a, b in zip(g["state_size"], g[metric])]
+        f_ = g[g["on_frontier"]]
+        if len(f_) > 1:
+            pts = " ".join(f"{px(a):.1f},{py(b):.1f}" for a, b in zip(f_["state_size"], f_[metric]))
+            out.append(f'<polyline points="{pts}" fill="none" stroke="{color[m]}" stroke-width="1.5"/>')
+        out.append(f'<rect x="{W - R + 10}" y="{T + 14 * j}" width="10" height="10" fill="{color[m]}"/><text x="{W - R + 24}" y="{T + 9 + 14 * j}">{m}</text>')
+    out.append("</svg>")
+    with open(path if path.endswith(".svg") else path + ".svg", "w") as f:
+        f.write("\n".join(out))
+    return True
+
+
 def main(argv=None):
     import argparse
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--csv", default=os.environ.get("ZOOLOGY_CSV", "zoology_results.csv"))
     ap.add_argument("--log-dir", default=os.environ.get("ZOOLOGY_LOG_DIR"))
-    ap.add_argument("--plot", default=None, help="write the MQAR figure to this file")
+    ap.add_argument("--plot", default=None, help="write the figure to this file")
+    ap.add_argument("--figure", choices=["mqar", "tradeoff"], default="mqar",
+                    help="mqar: accuracy against width per sequence length; tradeoff: accuracy against recurrent-state size per family")
     a = ap.parse_args(argv)
     df = load_results(a.csv, a.log_dir)
-    table = mqar_table(df)
+    table = mqar_table(df) if a.figure == "mqar" else state_tradeoff_table(df)
     print(table.to_string() if not table.empty else "no runs found")
     if a.plot and not df.empty:
-        plot_mqar(df, a.plot)
+        (plot_mqar if a.figure == "mqar" else plot_state_tradeoff)(df, a.plot)
         print("figure written")
     return table
 

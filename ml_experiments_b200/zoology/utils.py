@@ -25,6 +25,9 @@ _MODULE_ALIASES = {
     "ml_experiments_b200.zoology.mixers.mra.mra": "ml_experiments_b200.zoology.mixers.mra",
     "ml_experiments_b200.zoology.mixers.h3.h3": "ml_experiments_b200.zoology.mixers.h3",
     "ml_experiments_b200.zoology.mixers.rwkv5": "ml_experiments_b200.zoology.mixers.rwkv",
+    # the reference's feature-map package is one module here
+    **{f"ml_experiments_b200.zoology.mixers.feature_maps.{m}": "ml_experiments_b200.zoology.mixers.feature_maps"
+       for m in ("base", "taylor", "performer", "cosformer", "all_poly", "exp_dim")},
 }
 
 
