@@ -96,6 +96,31 @@ def composition_sweep(**kw) -> list[TrainConfig]:
     return mqar_sweep(segment=CompositionalMQARConfig, name="composition", **kw)
 
 
+def continuous_sweep(kv_train=((4, 100_000), (8, 20_000), (16, 20_000), (32, 20_000), (64, 20_000)), kv_test=(4, 8, 16, 32, 64, 128, 256),
+                     families=("attention", "sliding_window", "gated_delta_net", "ttt"), lrs=None, max_epochs: int = 32, batch_size: int = 256,
+                     scale: float = 1.0, vocab_size: int = VOCAB_SIZE) -> list[TrainConfig]:
+    """Recall on continuous inputs (zoology/experiments/011126/mqar_continuous.py): keys and values are fixed unit
+    vectors instead of learned token embeddings (``input_type="continuous"``, spherical frozen embeddings), one-layer
+    models without the short convolution, the sequence as long as its key-value pairs need."""
+    from ..data.stacked_mqar import ContinuousMQARConfig
+
+    lrs = np.logspace(-3, -1.5, 4) if lrs is None else lrs
+    tr = [ContinuousMQARConfig(num_examples=max(int(n * scale), 8), num_kv_pairs=kv) for kv, n in kv_train]
+    te = [ContinuousMQARConfig(num_examples=max(int(1_000 * scale), 8), num_kv_pairs=kv) for kv in kv_test]
+    L = max((c.num_passes + 1) * c.num_kv_pairs for c in tr + te)
+    factory_kwargs = {"state_mixer": dict(name="torch.nn.Identity", kwargs={}), "vocab_size": vocab_size}
+    models: list = []
+    for fam in families:
+        models = getattr(models_repo, f"add_{fam}")(models, None, L, factory_kwargs, num_layers=1)
+    for m in models:
+        m.embedding_init_type, m.learnable_word_embeddings = "spherical", False
+    data = DataConfig(train_configs=tr, test_configs=te, batch_size=(batch_size, max(batch_size // 8, 1)))
+    out = _sweep(data, models, lrs, max_epochs, "zoology-continuous", "continuous-mqar")
+    for c in out:
+        c.input_type = "continuous"
+    return out
+
+
 def circuits_sweep(task: str = "parity", seq_lens=(8, 16, 32, 64), families=("attention", "based", "mamba2"), lrs=(1e-3, 3e-3),
                    num_train: int = 100_000, num_test: int = 1_000, max_epochs: int = 32) -> list[TrainConfig]:
     """Parity / majority over bit strings of several lengths (state-tracking probes)."""

@@ -70,3 +70,11 @@ def test_state_tradeoff_table_marks_the_frontier(tmp_path):
     assert t.loc[2, "best_acc"] == 0.9                                             # best run of the duplicated point
     out = tmp_path / "tradeoff.svg"
     assert plot_state_tradeoff(df, str(out)) and out.read_text().startswith("<svg")
+
+
+def test_continuous_input_sweep_shapes():
+    from ml_experiments_b200.zoology.experiments.mqar_examples import continuous_sweep
+
+    cs = continuous_sweep(scale=1e-4)
+    assert cs and all(c.input_type == "continuous" and c.model.n_layers == 1 and not c.model.learnable_word_embeddings for c in cs)
+    assert {c.model.name for c in cs} == {"attention", "sliding-window-attention", "gated_delta_net", "ttt_linear", "ttt_mlp"}
