@@ -1,0 +1,4 @@
+"""``heuristic_secrets.models.telephone_attention``: telephone attention (reference:
+src/heuristic_secrets/models/telephone_attention.py). Re-exports."""
+# ruff: noqa: F401
+from ...models.ripple_ops import SDPAttention, TelephoneAttentionND, llama_rmsnorm

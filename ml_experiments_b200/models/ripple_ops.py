@@ -46,6 +46,26 @@ def relu_squared(x: torch.Tensor) -> torch.Tensor:
     return F.relu(x).square()
 
 
+class ReLUSquared(nn.Module):
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return relu_squared(x)
+
+
+class SDPAttention(nn.Module):
+    """Plain full softmax attention over ``(B, L, C)`` (the comparison arm of the telephone operator's self-benchmark,
+    src/heuristic_secrets/models/telephone_attention.py:316-333)."""
+
+    def __init__(self, channels: int, num_heads: int = 8):
+        super().__init__()
+        self.num_heads, self.head_dim = num_heads, channels // num_heads
+        self.qkv, self.out = nn.Linear(channels, 3 * channels), nn.Linear(channels, channels)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        B, L, C = x.shape
+        q, k, v = (t.transpose(1, 2) for t in self.qkv(x).view(B, L, 3, self.num_heads, self.head_dim).unbind(2))
+        return self.out(F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(B, L, C))
+
+
 def rope_sequence(x: torch.Tensor, base: float = 10000.0) -> torch.Tensor:
     """Half-split rotation by sequence position; ``x`` is ``(B, L, H, d)``."""
     L, d = x.shape[1], x.shape[-1]

@@ -85,6 +85,64 @@ class SqueezeExciteND(nn.Module):
         return x * scale.view(x.shape[0], *([1] * (x.dim() - 2)), -1)
 
 
+class SEBlock1d(nn.Module):
+    """Channel gate from the sequence mean of ``(B, L, C)``: ``x * sigmoid(fc2(silu(fc1(mean_L x))) [+ bias])``
+    (src/heuristic_secrets/models/scatter_attention.py:487-506)."""
+
+    def __init__(self, channels: int, reduction: int = 4):
+        super().__init__()
+        self.fc1, self.fc2 = nn.Linear(channels, max(1, channels // reduction)), nn.Linear(max(1, channels // reduction), channels)
+
+    def forward(self, x, bias=None):
+        s = self.fc2(F.silu(self.fc1(x.mean(dim=1))))
+        return x * torch.sigmoid(s if bias is None else s + bias).unsqueeze(1)
+
+
+class ScatterAttention1d(nn.Module):
+    """Position-wise reweighting of a scalar sequence ``(B, L)`` by a learned splat pattern
+    (src/heuristic_secrets/models/scatter_attention.py:374-484): every position throws ``num_samples`` weights at warped
+    offsets ``sign(k) |k|^beta * stride`` around itself (+ a shared deformation), with an envelope
+    ``strength / (1 + |k|)^alpha`` (separate exponents for the two directions) and a per-sample gain; the weights landing
+    on a position (bilinear between its two neighbours) are averaged by their hit mass and normalised over the sequence.
+    The pattern does not depend on the batch entry, so it is built once per call as an ``[L]`` map (the reference
+    expands it to ``[B, L, K]`` before splatting). ``film_biases``: optional scalar offsets to the base parameters."""
+
+    def __init__(self, num_samples: int = 16, max_offset: float = 32.0, init_stride: float = 1.0, init_beta: float = 1.0,
+                 init_alpha: float = 1.0, init_strength: float = 1.0):
+        super().__init__()
+        self.num_samples, self.max_offset = num_samples, max_offset
+        scalar = lambda v: nn.Parameter(torch.tensor(float(v)))
+        self.base_deformation, self.base_stride, self.base_strength = scalar(0.0), scalar(init_stride), scalar(init_strength)
+        self.base_beta_fwd, self.base_beta_bwd = scalar(init_beta), scalar(init_beta)
+        self.base_alpha_fwd, self.base_alpha_bwd = scalar(init_alpha), scalar(init_alpha)
+        self.sample_bias = nn.Parameter(torch.zeros(num_samples))
+        self.register_buffer("k_indices", torch.arange(num_samples, dtype=torch.float32) - num_samples // 2)
+
+    def weight_map(self, L: int, film_biases: dict | None = None) -> torch.Tensor:
+        fb = film_biases or {}
+        pos_param = lambda name: F.softplus(getattr(self, f"base_{name}") + fb.get(name, 0))
+        k, ka = self.k_indices, self.k_indices.abs()
+        fwd = k >= 0
+        stride = pos_param("stride")
+        offsets = torch.where(fwd, ka ** pos_param("beta_fwd"), -(ka ** pos_param("beta_bwd"))) * stride
+        shift = (self.base_deformation + fb.get("deformation", 0)).clamp(-self.max_offset, self.max_offset)
+        pos = (torch.arange(L, device=k.device, dtype=k.dtype)[:, None] + shift + offsets[None, :]).clamp(0, L - 1)       # [L, K]
+        envelope = pos_param("strength") / (1 + ka) ** torch.where(fwd, pos_param("alpha_fwd"), pos_param("alpha_bwd"))
+        w = (envelope * (1 + (self.sample_bias + fb.get("sample_bias", 0)).tanh())).expand(L, -1)
+        lo = pos.floor().long().clamp(0, L - 1)
+        hi = (lo + 1).clamp(0, L - 1)
+        frac = pos - lo.to(pos.dtype)
+        mass, hits = pos.new_zeros(L), pos.new_zeros(L)
+        for idx, share in ((lo, 1 - frac), (hi, frac)):
+            mass = mass.index_add(0, idx.reshape(-1), (share * w).reshape(-1))
+            hits = hits.index_add(0, idx.reshape(-1), share.reshape(-1))
+        avg = mass / hits.clamp(min=1e-6)
+        return avg / avg.sum().clamp(min=1e-6)
+
+    def forward(self, x, film_biases=None):
+        return x * self.weight_map(x.shape[1], film_biases)
+
+
 class KernelNetND(nn.Module):
     """SIREN from grid coordinates to one kernel value per channel."""
 

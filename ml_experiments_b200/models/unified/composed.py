@@ -116,6 +116,47 @@ class EmbedPooler(nn.Module):
         return self.proj(self.pooler(h, mask))
 
 
+class PooledGate(nn.Module):
+    """A backbone over the sequence, one learned-query pooling of its output, and two heads on the pooled vector:
+    ``num_features`` features of this branch and one bias per feature of the whole model (the branch's own included).
+    The attention and state-space "gates" of the reference's earlier two-branch classifier
+    (src/heuristic_secrets/models/composed.py:206-316) are this module with different backbones."""
+
+    def __init__(self, backbone: nn.Module, width: int, num_other_features: int, num_features: int = 4):
+        super().__init__()
+        self.backbone, self.pooler = backbone, LearnedPooler(width, num_queries=1)
+        self.feature_proj = nn.Linear(width, num_features)
+        self.bias_proj = nn.Linear(width, num_other_features + num_features)
+
+    def forward(self, h, mask=None):
+        pooled = self.pooler(self.backbone(h, mask), mask)
+        return self.feature_proj(pooled), self.bias_proj(pooled)
+
+
+class AttentionGate(PooledGate):
+    def __init__(self, width: int, depth: int, num_heads: int, ffn_mult: int, dropout: float, num_other_features: int, num_attn_features: int = 4):
+        from .attention import AttentionBackbone
+        super().__init__(AttentionBackbone(width, depth, num_heads, ffn_mult, dropout), width, num_other_features, num_attn_features)
+        self.num_attn_features = num_attn_features
+
+
+class SSMGate(PooledGate):
+    def __init__(self, width: int, depth: int, state_size: int, conv_kernel: int, conv_groups: int, expand: int, dropout: float,
+                 num_other_features: int, num_ssm_features: int = 4):
+        from .ssm import SSMBackbone
+        super().__init__(SSMBackbone(width, depth, state_size, conv_kernel, conv_groups, expand, dropout), width, num_other_features, num_ssm_features)
+        self.num_ssm_features = num_ssm_features
+
+
+class SSMGate3(PooledGate):
+    def __init__(self, width: int, depth: int, state_size: int, n_heads: int, expand: int, dropout: float, num_other_features: int,
+                 num_ssm_features: int = 4, use_conv: bool = False, conv_kernel: int = 7, conv_groups: int = 4):
+        from .ssm import SSMBackbone3
+        super().__init__(SSMBackbone3(width, depth, state_size, n_heads, expand, dropout, use_conv, conv_kernel, conv_groups), width,
+                         num_other_features, num_ssm_features)
+        self.num_ssm_features = num_ssm_features
+
+
 class HeuristicEmbed(nn.Module):
     """Scalar heuristic (one precomputed number per sample) -> small feature vector."""
 

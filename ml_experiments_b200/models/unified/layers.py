@@ -107,6 +107,14 @@ def query_pool(h, queries, mask, scale: float, nan_safe: bool = False):
     return torch.bmm(a, h)
 
 
+def check_nan(t: torch.Tensor, name: str) -> None:
+    """Debugging aid, active with ``DEBUG_NAN=1`` in the environment: raises when a CUDA tensor holds a NaN (one
+    device-to-host sync per call, hence off by default)."""
+    import os
+    if os.environ.get("DEBUG_NAN", "0") == "1" and t.device.type == "cuda" and torch.isnan(t).any():
+        raise RuntimeError(f"NaN in {name}: shape {tuple(t.shape)}, {int(torch.isnan(t).sum())} NaN, {int(torch.isinf(t).sum())} inf")
+
+
 class LearnedPooler(nn.Module):
     def __init__(self, width: int, num_queries: int = 1):
         super().__init__()
