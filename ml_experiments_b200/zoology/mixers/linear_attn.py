@@ -15,6 +15,16 @@ from ...ops.linear_recurrence import chunk_delta_rule, chunk_gla, dplr_recurrent
 from .norms import RMSNorm, RMSNormGated
 
 
+
+def elu_p1(x):
+    """``elu(x) + 1``: a positive feature map for queries / keys."""
+    return F.elu(x, 1.0, False) + 1.0
+
+
+def sum_norm(x):
+    """Normalise the last dimension to sum to one."""
+    return x / x.sum(-1, keepdim=True)
+
 class ShortConvolution(nn.Module):
     """Causal depthwise convolution over time on ``[B, T, C]`` with optional SiLU."""
 
@@ -92,10 +102,6 @@ class GatedLinearAttention(nn.Module):
         return self.key_dim * self.head_v_dim + _conv_state(self)
 
 
-def _sum_norm(x):
-    return x / x.sum(-1, keepdim=True)
-
-
 class DeltaNet(nn.Module):
     def __init__(self, mode: str = "chunk", d_model: int = None, expand_k: float = 1.0, expand_v: float = 1.0, num_heads: int = 4,
                  use_beta: bool = True, use_gate: bool = False, use_short_conv: bool = True, conv_size: int = 4, conv_bias: bool = False,
@@ -135,7 +141,7 @@ class DeltaNet(nn.Module):
         elif self.qk_activation == "elu":
             q, k = F.elu(q) + 1, F.elu(k) + 1
         if self.qk_norm == "sum":
-            q, k = _sum_norm(q), _sum_norm(k)
+            q, k = sum_norm(q), sum_norm(k)
         else:
             q, k = F.normalize(q.float(), dim=-1), F.normalize(k.float(), dim=-1)
         beta = self.b_proj(x).sigmoid() if self.use_beta else x.new_ones(*x.shape[:2], self.num_heads)
