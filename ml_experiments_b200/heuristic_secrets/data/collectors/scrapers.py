@@ -110,6 +110,20 @@ class GenericFixtureCollector(FixtureScraper):
             self.name = name
 
 
+# CredData's own category labels (possibly several, colon-separated, e.g. "Auth:Token") -> the categories used here;
+# the first keyword found in the label decides
+_CREDDATA_LABELS = (("password", SecretCategory.PASSWORD), ("auth", SecretCategory.AUTH_TOKEN), ("token", SecretCategory.AUTH_TOKEN),
+                    ("secret", SecretCategory.GENERIC_SECRET), ("key", SecretCategory.API_KEY), ("api", SecretCategory.API_KEY),
+                    ("private", SecretCategory.PRIVATE_KEY), ("certificate", SecretCategory.PRIVATE_KEY), ("credentials", SecretCategory.PASSWORD),
+                    ("generic", SecretCategory.GENERIC_SECRET), ("seed", SecretCategory.GENERIC_SECRET), ("salt", SecretCategory.GENERIC_SECRET))
+
+
+def map_creddata_category(category_str: str) -> SecretCategory:
+    """Category of a CredData row from its label column (src/heuristic_secrets/data/collectors/creddata.py:20-51)."""
+    label = (category_str or "").lower()
+    return next((cat for key, cat in _CREDDATA_LABELS if key in label), SecretCategory.GENERIC_SECRET)
+
+
 class CredDataCollector(Collector):
     """Samsung CredData: ``meta/*.csv`` rows (file, line span, value span, ground truth ``T`` / ``F``, category) joined
     with the downloaded files under ``data/``."""
@@ -148,5 +162,5 @@ class CredDataCollector(Collector):
                     val = lines[line_no - 1][s:e]
                     if len(val) >= 4:
                         truth = row.get("GroundTruth", "F").strip().upper() == "T"
-                        cat = infer_category(row.get("Category", ""), val) if truth else SecretCategory.FP_OTHER
+                        cat = map_creddata_category(row.get("Category", "")) if truth else SecretCategory.FP_OTHER
                         yield ValidatorSample(val, int(truth), self.name, cat.value)
