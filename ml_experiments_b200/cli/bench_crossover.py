@@ -15,7 +15,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..models.ripple_ops import AdaptiveLocalConv, LowRankAttention, TelephoneAttentionND
-from ..models.scatter import AdaptiveConvND, HierarchicalLocalAttention, LocalAttention
+from ..models.scatter import AdaptiveConvND, HierarchicalLocalAttention, LocalAttentionND, LowRankAttentionND, SGSBAttention
 
 
 class FullAttention(nn.Module):
@@ -29,7 +29,7 @@ class FullAttention(nn.Module):
         return self.out(F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(B, L, C))
 
 
-def make_op(name: str, width: int, heads: int, L: int):
+def make_op(name: str, width: int, heads: int, L: int, checkpoint: bool = False):
     if name == "attention":
         return FullAttention(width, heads)
     if name == "tele":
@@ -40,10 +40,14 @@ def make_op(name: str, width: int, heads: int, L: int):
         return LowRankAttention(width, num_heads=heads)
     if name == "scatter":
         return AdaptiveConvND(width, ndim=1, num_channels=heads)
-    if name == "gather":
-        return LocalAttention(width, kernel_size=17, num_channels=heads)
+    if name == "gather":         # soft-window local attention (optionally with gradient checkpointing of its chunks)
+        return LocalAttentionND(width, kernel_size=17, ndim=1, num_channels=heads, checkpoint=checkpoint)
     if name == "hier":
         return HierarchicalLocalAttention(width, window_size=17, num_channels=heads)
+    if name == "sgsb":           # local attention gated by a low-rank global summary
+        return SGSBAttention(width, kernel_size=17, num_channels=heads)
+    if name == "lowrank_nd":     # SIREN-downsampled full attention, upsampled back
+        return LowRankAttentionND(width, window_size=17, ndim=1, num_channels=heads)
     raise ValueError(name)
 
 
@@ -84,7 +88,8 @@ def measure(op, x, iters: int, warmup: int, amp: bool):
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--lengths", default="1024,4096,16384")
-    ap.add_argument("--ops", default="attention,tele,conv,lowrank,scatter,gather,hier")
+    ap.add_argument("--ops", default="attention,tele,conv,lowrank,scatter,gather,hier,sgsb,lowrank_nd")
+    ap.add_argument("--checkpoint", action="store_true", help="gradient checkpointing inside the local-attention operator")
     ap.add_argument("--width", type=int, default=256)
     ap.add_argument("--heads", type=int, default=4)
     ap.add_argument("--batch", type=int, default=4)
@@ -98,7 +103,7 @@ def main(argv=None):
         x = torch.randn(a.batch, L, a.width, device=a.device, requires_grad=True)
         for name in a.ops.split(","):
             torch.manual_seed(0)
-            op = make_op(name, a.width, a.heads, L).to(a.device)
+            op = make_op(name, a.width, a.heads, L, a.checkpoint).to(a.device)
             try:
                 f, b, mem = measure(op, x, a.iters, a.warmup, a.amp)
                 row = dict(op=name, seq_len=L, fwd_ms=round(f, 3), bwd_ms=round(b, 3), peak_mib=round(mem, 1))
