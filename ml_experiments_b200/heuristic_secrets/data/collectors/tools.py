@@ -43,6 +43,16 @@ def plausible(value: str, min_len: int = 10) -> bool:
     return any(c.isalnum() for c in v)
 
 
+def clean_literal(value: str, min_len: int = 8) -> bool:
+    """A literal that can stand alone as a sample: one line without tabs or escape sequences (what is left of a
+    mis-parsed multi-line construct has them), not a stop word, a few distinct symbols, not prose."""
+    if not min_len <= len(value) <= 4096 or value != value.strip():
+        return False
+    if any(c in value for c in "\n\t\r\\") or value.lower() in _STOPWORDS:
+        return False
+    return len(set(value)) >= 3 and value.count(" ") <= 3 and any(c.isalnum() for c in value)
+
+
 def go_strings(block: str) -> list[str]:
     out = []
     for m in _GO_STRING.finditer(block):
@@ -97,6 +107,30 @@ class _RepoCollector(Collector):
         """``(value, label, file name)`` before filtering and de-duplication."""
         raise NotImplementedError
 
+    # -- text-level helpers (one file's text in, literals or spans out) ----------------------------------------------
+    def _is_valid_secret(self, value: str) -> bool:
+        return clean_literal(value)
+
+    @staticmethod
+    def _find_all_positions(text: str, secret: str) -> list[tuple[int, int]]:
+        """Character offsets ``(start, end)`` of every non-overlapping occurrence of ``secret`` in ``text``."""
+        out, at = [], text.find(secret) if secret else -1
+        while at >= 0:
+            out.append((at, at + len(secret)))
+            at = text.find(secret, at + len(secret))
+        return out
+
+    def _positives_in(self, text: str, filename: str = "") -> Iterator[str]:
+        """Positive literals of one fixture file (per tool: see the sub-classes)."""
+        return iter(())
+
+    def _file_to_span_sample(self, text: str, filename: str = "") -> SpanFinderSample | None:
+        """The file's text with the byte offsets of every positive literal found in it; ``None`` without any."""
+        starts, ends, vals = _byte_spans(text, {v for v in self._positives_in(text, filename) if v})
+        if not starts:
+            return None
+        return SpanFinderSample(text, starts, ends, self.name, [infer_category(filename, v).value for v in vals])
+
     def span_files(self) -> Iterator[Path]:
         return iter(())
 
@@ -125,6 +159,25 @@ class GitleaksCollector(_RepoCollector):
     repo_url = "https://github.com/gitleaks/gitleaks"
     _SAMPLE = re.compile(r'GenerateSampleSecrets?\s*\(\s*"[^"]*"\s*,\s*("(?:[^"\\]|\\.)*"|`[^`]*`)')
     _SLICE = re.compile(r"\b(tps|fps)\s*(?::=|=)\s*(?:append\([^,]+,\s*)?\[\]string\s*\{(.*?)\n\s*\}", re.S)
+
+    _LITERAL = re.compile(r':=\s*("(?:[^"\\]|\\.)*"|`[^`]*`)')
+
+    def _extract_secrets_from_go(self, code: str) -> Iterator[str]:
+        """True positives of a rule file: second arguments of ``GenerateSampleSecrets`` and the ``tps`` string slices."""
+        for m in self._SAMPLE.finditer(code):
+            yield from (v for v in go_strings(m.group(1)) if self._is_valid_secret(v))
+        for m in self._SLICE.finditer(code):
+            if m.group(1) == "tps":
+                yield from (v for v in go_strings(m.group(2)) if self._is_valid_secret(v))
+
+    def _extract_string_literals_from_go(self, code: str) -> Iterator[str]:
+        """String literals assigned with ``:=`` in ``testdata`` Go files."""
+        for m in self._LITERAL.finditer(code):
+            yield from (v for v in go_strings(m.group(1)) if self._is_valid_secret(v))
+
+    def _positives_in(self, text, filename=""):
+        yield from self._extract_secrets_from_go(text)
+        yield from self._extract_string_literals_from_go(text)
 
     def _rule_files(self):
         d = self.repo() / "cmd" / "generate" / "config" / "rules"
@@ -170,6 +223,42 @@ class DetectSecretsCollector(_RepoCollector):
     _PAIR = re.compile(r"""\(\s*(?:[rRbBuUfF]{0,2})(?P<q>'|")(?P<v>(?:\\.|(?!(?P=q)).)*)(?P=q)\s*,\s*(?P<flag>True|False)\s*,?\s*\)""")
     _CONST = re.compile(r"""^(?P<name>[A-Z][A-Z0-9_]{2,})\s*=\s*(?:[rRbBuU]{0,2})(?P<q>'|")(?P<v>(?:\\.|(?!(?P=q)).)*)(?P=q)\s*$""", re.M)
 
+    _ASSIGN = re.compile(r"""^[ \t]*(?:self\.)?[A-Za-z_]\w*[ \t]*=[ \t]*(?:[rRbBuU]{0,2})(?P<q>'|")(?P<v>(?:\\.|(?!(?P=q)).)*)(?P=q)[ \t]*$""", re.M)
+    _INI = re.compile(r"""^[ \t]*[^\[\]#;=\n][^=\n]*?=[ \t]*['"]?([^'"\n#;]+?)['"]?[ \t]*(?:[#;].*)?$""", re.M)
+    _ENV = re.compile(r"""^[ \t]*(?:export[ \t]+)?[A-Za-z_][A-Za-z0-9_]*=['"]?([^'"\n]+?)['"]?[ \t]*$""", re.M)
+    _YAML = re.compile(r"""^\s*[\w.-]*(?:key|secret|token|password|passwd|credential)[\w.-]*\s*:\s*['"]?([^'"#\n]+?)['"]?\s*(?:#.*)?$""", re.M | re.I)
+
+    def _extract_constants_from_python(self, code: str) -> Iterator[str]:
+        """Positive literals of a plugin test: string constants assigned to a name or a ``self.`` attribute, and the
+        first element of parametrised ``(line, should_flag)`` cases whose flag is ``True``."""
+        seen = set()
+        for m in self._ASSIGN.finditer(code):
+            seen.add(m.group("v"))
+        for m in self._PAIR.finditer(code):
+            if m.group("flag") == "True":
+                seen.add(self._secret_in(m.group("v")))
+        negatives = {self._secret_in(m.group("v")) for m in self._PAIR.finditer(code) if m.group("flag") == "False"}
+        yield from (v for v in seen if self._is_valid_secret(v) and v not in negatives)
+
+    def _extract_secrets_from_ini(self, content: str) -> Iterator[str]:
+        yield from (m.group(1).strip() for m in self._INI.finditer(content) if self._is_valid_secret(m.group(1).strip()))
+
+    def _extract_secrets_from_env(self, content: str) -> Iterator[str]:
+        yield from (m.group(1).strip() for m in self._ENV.finditer(content) if self._is_valid_secret(m.group(1).strip()))
+
+    def _extract_secrets_from_yaml(self, content: str) -> Iterator[str]:
+        yield from (m.group(1).strip() for m in self._YAML.finditer(content) if self._is_valid_secret(m.group(1).strip()))
+
+    def _positives_in(self, text, filename=""):
+        name = filename.lower()
+        if name.endswith((".yaml", ".yml")):
+            return self._extract_secrets_from_yaml(text)
+        if name.endswith((".ini", ".cfg", ".conf")):
+            return self._extract_secrets_from_ini(text)
+        if ".env" in name:
+            return self._extract_secrets_from_env(text)
+        return self._extract_constants_from_python(text)
+
     def _plugin_tests(self):
         d = self.repo() / "tests" / "plugins"
         return sorted(d.glob("*_test.py")) if d.exists() else []
@@ -192,17 +281,9 @@ class DetectSecretsCollector(_RepoCollector):
             for m in self._CONST.finditer(code):
                 yield m.group("v"), 1, f.name
         for f in self._test_data():
-            text = f.read_text(errors="ignore")
-            if f.suffix in (".yaml", ".yml"):
-                pat = r"""^\s*[\w.-]*(?:key|secret|token|password|passwd|credential)[\w.-]*\s*:\s*['"]?([^'"#\n]+?)['"]?\s*(?:#.*)?$"""
-            elif f.suffix in (".ini", ".cfg", ".conf"):
-                pat = r"""^\s*[\w.-]+\s*=\s*['"]?([A-Za-z0-9+/=_\-]{10,})['"]?\s*(?:[#;].*)?$"""
-            elif ".env" in f.name:
-                pat = r"""^\s*(?:export\s+)?[A-Za-z_][A-Za-z0-9_]*=['"]?([^'"\n]+?)['"]?\s*$"""
-            else:
-                continue
-            for m in re.finditer(pat, text, re.M | re.I):
-                yield m.group(1).strip(), 1, f.name
+            if f.suffix in (".yaml", ".yml", ".ini", ".cfg", ".conf") or ".env" in f.name:
+                for v in self._positives_in(f.read_text(errors="ignore"), f.name):
+                    yield v, 1, f.name
 
     def span_files(self):
         return iter(self._plugin_tests() + [p for p in self._test_data() if p.suffix in (".yaml", ".yml", ".ini", ".cfg", ".conf", ".py", ".txt") or ".env" in p.name])
@@ -215,6 +296,24 @@ class TrufflehogCollector(_RepoCollector):
     _ASSIGN = re.compile(r"\b(validPattern|invalidPattern|secret|token|key|password|complexPattern)\w*\s*(?::=|=)\s*(\"(?:[^\"\\]|\\.)*\"|`[^`]*`)")
     _CASE = re.compile(r"input:\s*(\"(?:[^\"\\]|\\.)*\"|`[^`]*`|\w+)\s*,\s*want:\s*(nil|\[\]string\s*\{(.*?)\})", re.S)
 
+    @staticmethod
+    def _longest_token(snippet: str) -> str:
+        """Patterns are usually whole config snippets: the credential is the longest token without spaces or punctuation."""
+        return max(re.findall(r"[^\s\"'=:,;{}\[\]()<>]+", snippet) or [snippet], key=len)
+
+    def _extract_from_go_test(self, code: str) -> Iterator[str]:
+        """Positive literals of a detector's unit test: ``validPattern`` / ``secret`` / ``token`` ... assignments of a
+        string literal and the ``want: []string{...}`` lists. Integration tests fetch their secrets at run time
+        (``common.GetSecret`` / ``MustGetField``): no literal is assigned there, so nothing is taken from them."""
+        for m in self._ASSIGN.finditer(code):
+            if not m.group(1).startswith("invalid"):
+                yield from (t for t in (self._longest_token(v) for v in go_strings(m.group(2))) if self._is_valid_secret(t))
+        for m in self._CASE.finditer(code):
+            yield from (v for v in go_strings(m.group(3) or "") if self._is_valid_secret(v))
+
+    def _positives_in(self, text, filename=""):
+        return self._extract_from_go_test(text)
+
     def _tests(self):
         d = self.repo() / "pkg" / "detectors"
         return sorted(d.rglob("*_test.go")) if d.exists() else []
@@ -225,17 +324,14 @@ class TrufflehogCollector(_RepoCollector):
             for m in self._ASSIGN.finditer(code):
                 label = 0 if m.group(1).startswith("invalid") else 1
                 for v in go_strings(m.group(2)):
-                    # patterns are usually whole config snippets: the credential is the longest token without spaces
-                    token = max(re.findall(r"[^\s\"'=:,;{}\[\]()<>]+", v) or [v], key=len)
-                    yield token, label, f.parent.name + "_" + f.name
+                    yield self._longest_token(v), label, f.parent.name + "_" + f.name
             for m in self._CASE.finditer(code):
                 wants = go_strings(m.group(3) or "")
                 for v in wants:
                     yield v, 1, f.parent.name + "_" + f.name
                 if not wants and m.group(1)[0] in "\"`":         # a case that must stay silent: its input is a negative
                     for v in go_strings(m.group(1)):
-                        token = max(re.findall(r"[^\s\"'=:,;{}\[\]()<>]+", v) or [v], key=len)
-                        yield token, 0, f.parent.name + "_" + f.name
+                        yield self._longest_token(v), 0, f.parent.name + "_" + f.name
 
     def span_files(self):
         return iter(self._tests())

@@ -6,3 +6,5 @@ from ...models.ripple import (
 )
 from ...models.ripple_channel import ChannelMixer, ChannelSegment, RippleChannelClassifier
 from ...models.ripple_ops import CausalSelfAttention, ReLUSquared, relu_squared
+
+HAS_TRITON = True   # "a fused kernel path exists": the CUDA kernels of this package stand where the reference has Triton programs

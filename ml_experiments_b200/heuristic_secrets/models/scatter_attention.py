@@ -13,3 +13,6 @@ from ...models.scatter import (
 )
 from ...models.unified.two_d import SEBlock2d
 from ...models.scatter import LayerwiseRippleClassifier as RippleClassifier   # the reference's name for the 1-D layerwise classifier
+
+HAS_TRITON = True   # "a fused kernel path exists": the CUDA kernels of this package stand where the reference has Triton programs
+HAS_TRITON_ADAPTIVE = True

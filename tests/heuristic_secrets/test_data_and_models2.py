@@ -38,10 +38,15 @@ def test_scraper_and_builder(tmp_path):
     reg = CollectorRegistry()
     reg.register(Local, root=tmp_path / "repo")
     reg.register(UUIDGenerator, count=40, seed=0)
-    res = DataBuilder(tmp_path / "out", reg, seed=1).build()
-    assert res.per_source == {"local": 2, "generated_uuids": 40} and sum(res.validator_counts.values()) == 42
+    res = DataBuilder(tmp_path / "out", registry=reg, seed=1, no_fetch=True).build()
+    assert {k: v["samples"] for k, v in res.sources.items()} == {"local": 2, "generated_uuids": 40} and res.sources["local"]["spans"] == 1
+    assert sum(res.splits["validator"].values()) == 42 and res.deduplication == {"validator_before": 42, "validator_after": 42}
     train = list(read_jsonl(tmp_path / "out" / "splits" / "validator" / "train.jsonl", ValidatorSample))
-    assert len(train) == res.validator_counts["train"] and (tmp_path / "out" / "manifest.json").exists()
+    assert len(train) == res.splits["validator"]["train"]
+    import json
+    on_disk = json.loads((tmp_path / "out" / "manifest.json").read_text())
+    assert {"created_at", "sources", "splits", "deduplication"} <= set(on_disk) and on_disk["splits"] == res.splits
+    assert DataBuilder(tmp_path / "o2", sources=["generated_uuids", "no_such_source"], no_fetch=True).registry.names() == ["generated_uuids"]
     docs = [s for split in ("train", "val", "test") for s in read_jsonl(tmp_path / "out" / "splits" / "documents" / f"{split}.jsonl", SpanFinderSample)]
     assert len(docs) == 1 and len(docs[0].starts) == 2
     raw = docs[0].text.encode()

@@ -1,0 +1,46 @@
+"""The reference's package names as import aliases of this package, and (when the reference's own test folder is
+available) the drop-in check: the reference's tests run against this package."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+
+def test_alias_hook_serves_the_same_module_objects():
+    import ml_experiments_b200.compat as compat
+
+    served = compat.install(override=True)
+    try:
+        assert served == ["heuristic_secrets", "zoology"]
+        import heuristic_secrets
+        import heuristic_secrets.models as hm
+        from heuristic_secrets.data.collectors.gitleaks import GitleaksCollector
+        from heuristic_secrets.spanfinder.model import SpanFinderModel
+        from zoology.mixers.mamba_ssm.ops.selective_scan_interface import selective_scan_fn
+
+        import ml_experiments_b200.heuristic_secrets.models as real
+        from ml_experiments_b200.heuristic_secrets.spanfinder.model import SpanFinderModel as RealSpanFinder
+
+        assert hm.Model is real.Model and SpanFinderModel is RealSpanFinder and heuristic_secrets.Detector is not None
+        assert GitleaksCollector().name == "gitleaks" and callable(selective_scan_fn)
+    finally:
+        compat.uninstall()
+    assert "heuristic_secrets" not in sys.modules
+
+
+REF_TESTS = os.environ.get("ML_EXPERIMENTS_REFERENCE_TESTS", "")
+
+
+@pytest.mark.skipif(not os.path.isdir(REF_TESTS), reason="set ML_EXPERIMENTS_REFERENCE_TESTS to the reference's tests folder")
+def test_reference_test_suite_runs_against_this_package(tmp_path):
+    """Tests that need the network (cloning a repository) and the telephone test, which passes a constructor argument
+    the reference's own class does not take, are left out. A handful of tests fail against the reference's own code
+    (they predate its current constructors); what is asserted here is a floor on the number that pass."""
+    cmd = [sys.executable, "-m", "ml_experiments_b200.compat", "pytest", REF_TESTS, "-q", "-p", "no:cacheprovider",
+           f"--ignore={REF_TESTS}/data/test_git_utils.py", f"--ignore={REF_TESTS}/models/test_triton_telephone.py", "--rootdir", str(tmp_path)]
+    env = dict(os.environ, PYTHONDONTWRITEBYTECODE="1", PYTHONPATH=os.pathsep.join([os.getcwd(), os.environ.get("PYTHONPATH", "")]))
+    out = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=1800).stdout
+    tail = out.strip().splitlines()[-1]
+    passed = int(tail.split(" passed")[0].split()[-1])
+    assert passed >= 120, tail
