@@ -7,26 +7,31 @@ import sys
 import pytest
 
 
+_CHECK = """
+import sys
+import ml_experiments_b200.compat as compat
+served = compat.install(override=True)
+assert served == ["heuristic_secrets", "zoology"], served
+import heuristic_secrets
+import heuristic_secrets.models as hm
+from heuristic_secrets.data.collectors.gitleaks import GitleaksCollector
+from heuristic_secrets.spanfinder.model import SpanFinderModel
+from zoology.mixers.mamba_ssm.ops.selective_scan_interface import selective_scan_fn
+import ml_experiments_b200.heuristic_secrets.models as real
+from ml_experiments_b200.heuristic_secrets.spanfinder.model import SpanFinderModel as RealSpanFinder
+assert hm.Model is real.Model and SpanFinderModel is RealSpanFinder and heuristic_secrets.Detector is not None
+assert GitleaksCollector().name == "gitleaks" and callable(selective_scan_fn)
+compat.uninstall()
+assert "heuristic_secrets" not in sys.modules
+print("ok")
+"""
+
+
 def test_alias_hook_serves_the_same_module_objects():
-    import ml_experiments_b200.compat as compat
-
-    served = compat.install(override=True)
-    try:
-        assert served == ["heuristic_secrets", "zoology"]
-        import heuristic_secrets
-        import heuristic_secrets.models as hm
-        from heuristic_secrets.data.collectors.gitleaks import GitleaksCollector
-        from heuristic_secrets.spanfinder.model import SpanFinderModel
-        from zoology.mixers.mamba_ssm.ops.selective_scan_interface import selective_scan_fn
-
-        import ml_experiments_b200.heuristic_secrets.models as real
-        from ml_experiments_b200.heuristic_secrets.spanfinder.model import SpanFinderModel as RealSpanFinder
-
-        assert hm.Model is real.Model and SpanFinderModel is RealSpanFinder and heuristic_secrets.Detector is not None
-        assert GitleaksCollector().name == "gitleaks" and callable(selective_scan_fn)
-    finally:
-        compat.uninstall()
-    assert "heuristic_secrets" not in sys.modules
+    """In a fresh interpreter (other tests of this suite import the reference's real package under the same name)."""
+    env = dict(os.environ, PYTHONPATH=os.getcwd())
+    r = subprocess.run([sys.executable, "-c", _CHECK], capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0 and r.stdout.strip().endswith("ok"), r.stderr[-2000:]
 
 
 REF_TESTS = os.environ.get("ML_EXPERIMENTS_REFERENCE_TESTS", "")
