@@ -49,3 +49,48 @@ def test_reference_test_suite_runs_against_this_package(tmp_path):
     tail = out.strip().splitlines()[-1]
     passed = int(tail.split(" passed")[0].split()[-1])
     assert passed >= 120, tail
+
+
+REF_EXPERIMENTS = os.environ.get("ML_EXPERIMENTS_REFERENCE_ZOOLOGY_EXPERIMENTS", "")
+
+_EXPERIMENTS = """
+import glob, os, runpy, sys, torch
+import ml_experiments_b200.compat as compat
+compat.install(override=True)
+from zoology.model import LanguageModel
+root = sys.argv[1]
+loaded, stale, ran = 0, 0, 0
+for f in sorted(glob.glob(os.path.join(root, "**", "*.py"), recursive=True)):
+    if os.path.basename(f) in ("__init__.py", "plot.py", "models_repo.py"):
+        continue
+    try:
+        configs = runpy.run_path(f)["configs"]
+    except Exception as e:     # scripts written for an earlier DataConfig (num_train_examples / builder) or a module that no longer exists
+        assert type(e).__name__ in ("ValidationError", "ModuleNotFoundError"), (f, repr(e))
+        stale += 1
+        continue
+    loaded += 1
+    seen = set()
+    for cfg in configs:
+        m = cfg.model
+        key = (m.name, str(m.sequence_mixer.name), m.d_model)
+        if key in seen or m.d_model > 64 or ran >= 40:
+            continue
+        seen.add(key)
+        model = LanguageModel(m.model_copy(update={"vocab_size": 64})).eval()
+        with torch.no_grad():
+            assert torch.isfinite(model(torch.randint(0, 64, (2, 32)))).all(), key
+        ran += 1
+print(loaded, stale, ran)
+"""
+
+
+@pytest.mark.skipif(not os.path.isdir(REF_EXPERIMENTS), reason="set ML_EXPERIMENTS_REFERENCE_ZOOLOGY_EXPERIMENTS to zoology/experiments of the reference")
+def test_reference_experiment_scripts_build_their_models_here():
+    """Every sweep script of the reference that its own current config classes accept loads through the alias hook, and
+    the models it describes are constructed and run forward by this package."""
+    env = dict(os.environ, PYTHONPATH=os.getcwd(), PYTHONDONTWRITEBYTECODE="1")
+    r = subprocess.run([sys.executable, "-c", _EXPERIMENTS, REF_EXPERIMENTS], capture_output=True, text=True, env=env, timeout=1800)
+    assert r.returncode == 0, r.stderr[-3000:]
+    loaded, stale, ran = (int(v) for v in r.stdout.strip().splitlines()[-1].split())
+    assert loaded >= 18 and ran >= 10, (loaded, stale, ran)
