@@ -35,6 +35,25 @@ class MaskWindow:
     mask: list[int]
     secret_ids: list[str] = field(default_factory=list)
     kind: str = "line"
+    source: str = ""
+    categories: list[str] | None = None
+
+    # the reference's record for the same thing is ``LineSample(bytes, mask, has_secret, source, ...)``: its attribute
+    # names read the same data here
+    @property
+    def bytes(self):
+        return self.data
+
+    @property
+    def has_secret(self) -> bool:
+        return any(self.mask)
+
+
+class LineSample(MaskWindow):
+    """:class:`MaskWindow` built with the reference's argument names (src/heuristic_secrets/bytemasker/dataset.py:36-43)."""
+
+    def __init__(self, bytes, mask, has_secret: bool | None = None, source: str = "", categories=None, secret_ids=None):
+        super().__init__(data=bytes, mask=list(mask), secret_ids=list(secret_ids or []), kind="line", source=source, categories=categories)
 
 
 def secret_id(raw: bytes) -> str:

@@ -4,7 +4,7 @@ from __future__ import annotations
 
 import torch
 
-from ..training import BinaryTaskTrainer, TrainMetrics, get_device  # noqa: F401
+from ..training import BinaryTaskTrainer, TrainMetrics, get_device, set_seed  # noqa: F401
 from .model import JointConfig, JointSecretDetector
 
 

@@ -94,3 +94,41 @@ def test_reference_experiment_scripts_build_their_models_here():
     assert r.returncode == 0, r.stderr[-3000:]
     loaded, stale, ran = (int(v) for v in r.stdout.strip().splitlines()[-1].split())
     assert loaded >= 18 and ran >= 10, (loaded, stale, ran)
+
+
+REF_SCRIPTS = os.environ.get("ML_EXPERIMENTS_REFERENCE_SCRIPTS", "")
+
+_SCRIPTS = """
+import glob, os, runpy, sys
+import ml_experiments_b200.compat as compat
+compat.install(override=True)
+ok, bad = [], []
+for f in sorted(glob.glob(os.path.join(sys.argv[1], "*.py"))):
+    name = os.path.basename(f)
+    if name == "__init__.py":
+        continue
+    try:
+        sys.argv = [f]
+        runpy.run_path(f, run_name="_imported_")          # module level only: imports and definitions, no main()
+        ok.append(name)
+    except BaseException as e:
+        bad.append(name + ": " + type(e).__name__ + ": " + str(e)[:120])
+print("RESULT", len(ok))
+print("\\n".join("BAD " + b for b in bad))
+"""
+
+# scripts whose imports fail against the reference's own package too: a module path of the author's checkout (``src.``), an
+# external generator that is not a dependency (``snakes2``), a module that is not in the tree (``joint.pruned_model``);
+# ``diagnose_gather_mem`` runs its diagnosis at import time and exits
+_EXPECTED_BAD = ("diagnose_gather_mem.py", "diagnose_telephone.py", "generate_pathx.py", "train_pruned.py")
+
+
+@pytest.mark.skipif(not os.path.isdir(REF_SCRIPTS), reason="set ML_EXPERIMENTS_REFERENCE_SCRIPTS to the reference's scripts folder")
+def test_reference_scripts_find_everything_they_import_here():
+    env = dict(os.environ, PYTHONPATH=os.getcwd(), PYTHONDONTWRITEBYTECODE="1")
+    r = subprocess.run([sys.executable, "-c", _SCRIPTS, REF_SCRIPTS], capture_output=True, text=True, env=env, timeout=1800)
+    assert r.returncode == 0, r.stderr[-3000:]
+    lines = r.stdout.strip().splitlines()               # the scripts print at import time: only the marked lines count
+    n_ok = int(next(l for l in lines if l.startswith("RESULT ")).split()[1])
+    bad = [l[4:] for l in lines if l.startswith("BAD ") and not l[4:].startswith(_EXPECTED_BAD)]
+    assert n_ok >= 23 and not bad, (n_ok, bad)
