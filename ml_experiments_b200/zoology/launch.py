@@ -16,6 +16,10 @@ from datetime import datetime
 
 
 def load_configs(python_file: str) -> list:
+    # sweep files written for the reference import ``zoology.config`` / ``zoology.data...``: serve those names from this
+    # package (a real ``zoology`` installation, if there is one, keeps precedence)
+    from ..compat import install
+    install()
     spec = importlib.util.spec_from_file_location("config_module", python_file)
     module = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(module)
