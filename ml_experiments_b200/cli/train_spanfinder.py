@@ -49,8 +49,8 @@ def main(argv=None):
     cfg = getattr(SpanFinderConfig, a.preset)()
     model = SpanFinderModel(cfg)
     if a.data_dir and not a.synthetic:
-        train_ds = load_spanfinder_dataset(Path(a.data_dir), "train", a.chunk_size, a.chunk_overlap)
-        val_ds = load_spanfinder_dataset(Path(a.data_dir), "val", a.chunk_size, a.chunk_overlap)
+        train_ds, _ = load_spanfinder_dataset(Path(a.data_dir), "train", a.chunk_size, a.chunk_overlap)
+        val_ds, _ = load_spanfinder_dataset(Path(a.data_dir), "val", a.chunk_size, a.chunk_overlap)
         train_b = create_batches(train_ds, a.batch_size, shuffle=True, seed=a.seed)
         val_b = create_batches(val_ds, a.batch_size, shuffle=False)
         source = str(a.data_dir)

@@ -15,6 +15,7 @@ which a secret occurs on both sides.
 """
 from __future__ import annotations
 
+import functools
 import hashlib
 import json
 import os
@@ -217,6 +218,32 @@ class LineMaskDataset(torch.utils.data.Dataset):
 
     def __init__(self, windows: list[MaskWindow]):
         self.windows = windows
+
+    # the attribute names the reference's dataset exposes (src/heuristic_secrets/bytemasker/dataset.py:281-313), computed
+    # on first use: index lists of windows with / without a secret, per-window tensors and lengths
+    @property
+    def lines(self) -> list[MaskWindow]:
+        return self.windows
+
+    @functools.cached_property
+    def secret_lines(self) -> list[int]:
+        return [i for i, w in enumerate(self.windows) if w.has_secret]
+
+    @functools.cached_property
+    def clean_lines(self) -> list[int]:
+        return [i for i, w in enumerate(self.windows) if not w.has_secret]
+
+    @functools.cached_property
+    def lengths(self) -> list[int]:
+        return [len(w.data) for w in self.windows]
+
+    @functools.cached_property
+    def byte_tensors(self) -> list[torch.Tensor]:
+        return [self[i][0] for i in range(len(self))]
+
+    @functools.cached_property
+    def mask_tensors(self) -> list[torch.Tensor]:
+        return [self[i][1] for i in range(len(self))]
 
     def __len__(self) -> int:
         return len(self.windows)

@@ -4,6 +4,7 @@ from __future__ import annotations
 
 import json
 import random
+from dataclasses import dataclass
 from pathlib import Path
 
 import torch
@@ -53,7 +54,22 @@ def create_batches(ds: SpanFinderDataset, batch_size: int = 1024, shuffle: bool 
     return [collate_chunks([ds[i] for i in order[k:k + batch_size]]) for k in range(0, len(order), batch_size)]
 
 
-def load_spanfinder_dataset(data_dir: Path, split: str = "train", chunk_size: int = 512, chunk_overlap: int = 64):
+@dataclass
+class SpanFinderDatasetStats:
+    total_samples: int
+    total_chunks: int
+    total_spans: int
+    avg_chunks_per_sample: float
+    chunk_size: int
+    chunk_overlap: int
+
+
+def load_spanfinder_dataset(data_dir: Path, split: str = "train", chunk_size: int = 512,
+                            chunk_overlap: int = 64) -> tuple[SpanFinderDataset, SpanFinderDatasetStats]:
+    """``(dataset, stats)`` of ``<data_dir>/splits/documents/<split>.jsonl`` cut into overlapping chunks."""
     path = Path(data_dir) / "splits" / "documents" / f"{split}.jsonl"
     samples = [SpanFinderSample.from_dict(json.loads(line)) for line in open(path) if line.strip()]
-    return SpanFinderDataset(samples, chunk_size, chunk_overlap)
+    ds = SpanFinderDataset(samples, chunk_size, chunk_overlap)
+    stats = SpanFinderDatasetStats(len(samples), len(ds), sum(len(s.starts) for s in samples), len(ds) / len(samples) if samples else 0.0,
+                                   chunk_size, chunk_overlap)
+    return ds, stats

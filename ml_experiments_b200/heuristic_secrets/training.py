@@ -39,9 +39,20 @@ class TrainMetrics:
     recall: float = 0.0
     f1: float = 0.0
     threshold: float = 0.5
+    accuracy: float = 0.0
+    fp_rate: float = 0.0     # false positives / negatives
+    fn_rate: float = 0.0     # false negatives / positives
 
     def __str__(self) -> str:
         return f"loss={self.loss:.4f} P={self.precision:.4f} R={self.recall:.4f} F1={self.f1:.4f} thr={self.threshold:.2f}"
+
+
+def rates(pred: torch.Tensor, truth: torch.Tensor) -> dict:
+    """``accuracy``, ``fp_rate`` (share of the negatives flagged), ``fn_rate`` (share of the positives missed)."""
+    n, pos = max(truth.numel(), 1), float(truth.sum())
+    neg = truth.numel() - pos
+    return {"accuracy": float((pred == truth).sum()) / n, "fp_rate": float((pred & ~truth).sum()) / neg if neg else 0.0,
+            "fn_rate": float((~pred & truth).sum()) / pos if pos else 0.0}
 
 
 def prf(pred: torch.Tensor, truth: torch.Tensor) -> tuple[float, float, float]:
@@ -166,7 +177,8 @@ class BinaryTaskTrainer:
             self.swa_model.update_parameters(self.model)
             self.swa_scheduler.step()
         p, r, f1 = prf(torch.cat(preds), torch.cat(truths)) if preds else (0.0, 0.0, 0.0)
-        return TrainMetrics(tot / max(len(order), 1), p, r, f1)
+        extra = rates(torch.cat(preds), torch.cat(truths)) if preds else {}
+        return TrainMetrics(tot / max(len(order), 1), p, r, f1, **extra)
 
     def finalize_swa(self) -> None:
         if self.swa_active:
@@ -187,11 +199,12 @@ class BinaryTaskTrainer:
         probs, truths = torch.cat(probs), torch.cat(truths)
         if optimize_threshold and self.threshold_search:
             self.optimal_threshold = find_threshold(probs, truths, self.threshold_search_steps)
-        p, r, f1 = prf(probs >= self.optimal_threshold, truths >= 0.5)
+        pred, truth = probs >= self.optimal_threshold, truths >= 0.5
+        p, r, f1 = prf(pred, truth)
         if f1 > self.best_f1:
             self.best_f1 = f1
             self.best_state = {k: v.detach().cpu().clone() for k, v in self.model.state_dict().items()}
-        return TrainMetrics(tot / len(self.val_data), p, r, f1, self.optimal_threshold)
+        return TrainMetrics(tot / len(self.val_data), p, r, f1, self.optimal_threshold, **rates(pred, truth))
 
     def fit(self, verbose: bool = False) -> TrainMetrics:
         m = TrainMetrics()
