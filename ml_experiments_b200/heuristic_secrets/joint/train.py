@@ -1,5 +1,5 @@
-"""Joint detector training (reference: src/heuristic_secrets/joint/train.py). Batches are
-``(byte_ids, lengths, labels)``; the loss is the classification loss of the Validator stage."""
+"""Joint detector training (reference: src/heuristic_secrets/joint/train.py); the loss is the classification loss of the
+Validator stage."""
 from __future__ import annotations
 
 import torch
@@ -9,9 +9,14 @@ from .model import JointConfig, JointSecretDetector
 
 
 class JointTrainer(BinaryTaskTrainer):
+    """Batches are ``(byte_ids, labels, lengths)`` as the reference's trainer unpacks them
+    (src/heuristic_secrets/joint/train.py:165) or ``(byte_ids, lengths, labels)``: the floating-point one of the last two
+    is the label vector."""
+
     def _forward(self, batch):
-        ids, lengths, labels = (t.to(self.device) for t in batch)
-        return self.model(ids, lengths)["cls_logits"].squeeze(-1), labels.float(), None
+        ids, a, b = (t.to(self.device) for t in batch)
+        labels, lengths = (a, b) if a.is_floating_point() else (b, a)
+        return self.model(ids, lengths.long())["cls_logits"].squeeze(-1), labels.float(), None
 
 
 def load_checkpoint(path, device: torch.device | None = None, text_freq=None, secret_freq=None) -> JointSecretDetector:
