@@ -33,6 +33,10 @@ def main(argv=None):
         x, y = pathfinder.generate(n, a.size, a.seed + 1000 * i, contour_length=a.contour_length, marker_radius=a.marker_radius,
                                    continuity=a.continuity)
         np.savez_compressed(out / f"{split}.npz", x=x, y=y)
+        # the flat per-split cache the reference's trainer reads (scripts/train_pathx.py:48-60): pixel rows, labels and
+        # the index lists of the two classes
+        np.savez_compressed(out / f"pathx_{split}_cache.npz", pixels=x.reshape(len(x), -1), labels=y.astype(np.int64),
+                            pos_indices=np.flatnonzero(y == 1), neg_indices=np.flatnonzero(y == 0))
         print(f"{split}: {n} images of {a.size}x{a.size} -> {out / (split + '.npz')} ({y.mean():.2f} positive)")
     return out
 

@@ -76,6 +76,9 @@ def test_pathfinder_generator_and_pathx_trainers(tmp_path):
     assert 0.005 < (x > 0).mean() < 0.5                       # sparse strokes on a dark canvas
     generate_pathx.main(["--output-dir", str(tmp_path / "gen"), "--n-train", "8", "--n-val", "4", "--n-test", "0", "--size", "32"])
     assert np.load(tmp_path / "gen" / "train.npz")["x"].shape == (8, 32, 32)
+    flat = np.load(tmp_path / "gen" / "pathx_train_cache.npz")      # the per-split cache the reference's Path-X trainer reads
+    assert flat["pixels"].shape == (8, 1024) and sorted(flat["pos_indices"].tolist() + flat["neg_indices"].tolist()) == list(range(8))
+    assert (flat["labels"][flat["pos_indices"]] == 1).all()
     common = ["--size", "16", "--n-train", "32", "--n-val", "16", "--embed-width", "16", "--attn-window", "16", "--data-dir", str(tmp_path / "d"),
               "--device", "cpu", "--batch-size", "16"]
     s1 = train_pathx.main(common + ["--epochs", "2", "--mode", "1d", "--arch", "conv", "--output", str(tmp_path / "o1")])
