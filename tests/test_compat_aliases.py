@@ -6,6 +6,8 @@ import sys
 
 import pytest
 
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
 
 _CHECK = """
 import sys
@@ -29,7 +31,7 @@ print("ok")
 
 def test_alias_hook_serves_the_same_module_objects():
     """In a fresh interpreter (other tests of this suite import the reference's real package under the same name)."""
-    env = dict(os.environ, PYTHONPATH=os.getcwd())
+    env = dict(os.environ, PYTHONPATH=REPO)
     r = subprocess.run([sys.executable, "-c", _CHECK], capture_output=True, text=True, env=env, timeout=600)
     assert r.returncode == 0 and r.stdout.strip().endswith("ok"), r.stderr[-2000:]
 
@@ -44,7 +46,7 @@ def test_reference_test_suite_runs_against_this_package(tmp_path):
     (they predate its current constructors); what is asserted here is a floor on the number that pass."""
     cmd = [sys.executable, "-m", "ml_experiments_b200.compat", "pytest", REF_TESTS, "-q", "-p", "no:cacheprovider",
            f"--ignore={REF_TESTS}/data/test_git_utils.py", f"--ignore={REF_TESTS}/models/test_triton_telephone.py", "--rootdir", str(tmp_path)]
-    env = dict(os.environ, PYTHONDONTWRITEBYTECODE="1", PYTHONPATH=os.pathsep.join([os.getcwd(), os.environ.get("PYTHONPATH", "")]))
+    env = dict(os.environ, PYTHONDONTWRITEBYTECODE="1", PYTHONPATH=os.pathsep.join([REPO, os.environ.get("PYTHONPATH", "")]))
     out = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=1800).stdout
     tail = out.strip().splitlines()[-1]
     passed = int(tail.split(" passed")[0].split()[-1])
@@ -89,7 +91,7 @@ print(loaded, stale, ran)
 def test_reference_experiment_scripts_build_their_models_here():
     """Every sweep script of the reference that its own current config classes accept loads through the alias hook, and
     the models it describes are constructed and run forward by this package."""
-    env = dict(os.environ, PYTHONPATH=os.getcwd(), PYTHONDONTWRITEBYTECODE="1")
+    env = dict(os.environ, PYTHONPATH=REPO, PYTHONDONTWRITEBYTECODE="1")
     r = subprocess.run([sys.executable, "-c", _EXPERIMENTS, REF_EXPERIMENTS], capture_output=True, text=True, env=env, timeout=1800)
     assert r.returncode == 0, r.stderr[-3000:]
     loaded, stale, ran = (int(v) for v in r.stdout.strip().splitlines()[-1].split())
@@ -125,7 +127,7 @@ _EXPECTED_BAD = ("diagnose_gather_mem.py", "diagnose_telephone.py", "generate_pa
 
 @pytest.mark.skipif(not os.path.isdir(REF_SCRIPTS), reason="set ML_EXPERIMENTS_REFERENCE_SCRIPTS to the reference's scripts folder")
 def test_reference_scripts_find_everything_they_import_here():
-    env = dict(os.environ, PYTHONPATH=os.getcwd(), PYTHONDONTWRITEBYTECODE="1")
+    env = dict(os.environ, PYTHONPATH=REPO, PYTHONDONTWRITEBYTECODE="1")
     r = subprocess.run([sys.executable, "-c", _SCRIPTS, REF_SCRIPTS], capture_output=True, text=True, env=env, timeout=1800)
     assert r.returncode == 0, r.stderr[-3000:]
     lines = r.stdout.strip().splitlines()               # the scripts print at import time: only the marked lines count
