@@ -169,12 +169,29 @@ def stratified_component_split(windows: list[MaskWindow], fractions=(0.8, 0.1, 0
     return splits
 
 
-def create_bucketed_batches(windows: list[MaskWindow], batch_size: int = 64, shuffle: bool = True, seed: int | None = None):
-    """Batches ``(byte_ids, masks, lengths)`` grouped by length bucket."""
+def compute_length_bins(lengths: list[int], n_bins: int = 8) -> list[int]:
+    """Bucket edges at the ``1/n_bins .. (n_bins-1)/n_bins`` quantiles of ``lengths`` plus the maximum (equal-population
+    buckets for a given data set, as an alternative to the fixed ``BUCKETS``)."""
+    if not lengths:
+        return [512]
+    ordered = sorted(lengths)
+    return sorted({ordered[len(ordered) * i // n_bins] for i in range(1, n_bins)} | {ordered[-1]})
+
+
+def create_bucketed_batches(windows, batch_size: int = 64, shuffle: bool = True, seed: int | None = None, indices: list[int] | None = None,
+                            show_progress: bool = False, length_bins: list[int] | None = None):
+    """Batches ``(byte_ids, masks, lengths)`` grouped by length bucket. ``windows``: a list of :class:`MaskWindow` or a
+    :class:`LineMaskDataset` (then ``indices`` selects windows of it, the call form of the reference,
+    src/heuristic_secrets/bytemasker/dataset.py:351-416); ``length_bins`` replaces the default bucket edges."""
+    if isinstance(windows, LineMaskDataset):
+        windows = windows.windows if indices is None else [windows.windows[i] for i in indices]
+    elif indices is not None:
+        windows = [windows[i] for i in indices]
+    edges = tuple(sorted(length_bins)) if length_bins else BUCKETS
     rng = random.Random(seed)
     buckets: dict[int, list[MaskWindow]] = {}
     for w in windows:
-        b = next((x for x in BUCKETS if len(w.data) <= x), BUCKETS[-1])
+        b = next((x for x in edges if len(w.data) <= x), edges[-1] + 1)
         buckets.setdefault(b, []).append(w)
     batches = []
     for members in buckets.values():
