@@ -93,7 +93,9 @@ class TelephoneAttentionND(nn.Module):
 
     def __init__(self, channels: int, ndim: int = 1, num_heads: int = 1, max_freq: float = 16.0, min_freq: float = 1.0,
                  max_kernel_size: int = 64, chunk_size: int = 1024, checkpoint: bool = True, use_triton: bool = True,
-                 scale_power: float = 0.5625, max_seq_len: int = 8192):
+                 scale_power: float = 0.5625, max_seq_len: int = 8192, max_samples: int | None = None):
+        # max_samples: argument of an earlier version of the operator with a fixed tap count; accepted so that configs
+        # written for it still construct (the tap count follows the sequence length: L ** scale_power)
         super().__init__()
         self.channels, self.ndim, self.num_heads = channels, ndim, num_heads
         self.head_dim = channels // num_heads

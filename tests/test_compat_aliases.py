@@ -41,16 +41,17 @@ REF_TESTS = os.environ.get("ML_EXPERIMENTS_REFERENCE_TESTS", "")
 
 @pytest.mark.skipif(not os.path.isdir(REF_TESTS), reason="set ML_EXPERIMENTS_REFERENCE_TESTS to the reference's tests folder")
 def test_reference_test_suite_runs_against_this_package(tmp_path):
-    """Tests that need the network (cloning a repository) and the telephone test, which passes a constructor argument
-    the reference's own class does not take, are left out. A handful of tests fail against the reference's own code
-    (they predate its current constructors); what is asserted here is a floor on the number that pass."""
+    """Tests that need the network (cloning a repository) are left out. A handful of tests fail against the reference's
+    own code (they predate its current constructors; the telephone tests pass a ``max_samples`` argument its class no longer
+    takes and cannot run there at all: here the argument is accepted and they pass, the CUDA-only ones on a GPU); what is
+    asserted is a floor on the number that pass."""
     cmd = [sys.executable, "-m", "ml_experiments_b200.compat", "pytest", REF_TESTS, "-q", "-p", "no:cacheprovider",
-           f"--ignore={REF_TESTS}/data/test_git_utils.py", f"--ignore={REF_TESTS}/models/test_triton_telephone.py", "--rootdir", str(tmp_path)]
+           f"--ignore={REF_TESTS}/data/test_git_utils.py", "--rootdir", str(tmp_path)]
     env = dict(os.environ, PYTHONDONTWRITEBYTECODE="1", PYTHONPATH=os.pathsep.join([REPO, os.environ.get("PYTHONPATH", "")]))
     out = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=1800).stdout
     tail = out.strip().splitlines()[-1]
     passed = int(tail.split(" passed")[0].split()[-1])
-    assert passed >= 120, tail
+    assert passed >= 127, tail
 
 
 REF_EXPERIMENTS = os.environ.get("ML_EXPERIMENTS_REFERENCE_ZOOLOGY_EXPERIMENTS", "")
