@@ -35,6 +35,11 @@ class SpanFinderConfig:
     def to_dict(self) -> dict:
         return {f.name: getattr(self, f.name) for f in fields(self)}
 
+    # read access under the field names of the older API (the constructor accepts them as well)
+    embed_dim = property(lambda self: self.width)
+    hidden_dim = property(lambda self: self.width)
+    num_layers = property(lambda self: self.cnn_depth)
+
     @classmethod
     def from_dict(cls, d: dict) -> "SpanFinderConfig":
         known = {f.name for f in fields(cls)} | set(_ALIASES) | _IGNORED
