@@ -30,7 +30,21 @@ class _AliasFinder(importlib.abc.MetaPathFinder, importlib.abc.Loader):
 
     def _real(self, name: str) -> str | None:
         top = name.split(".", 1)[0]
-        return None if top not in self.names else self.names[top] + name[len(top):]
+        if top not in self.names:
+            return None
+        real = self.names[top] + name[len(top):]
+        if top == "zoology":      # modules the reference splits into sub-packages and this package keeps in one file
+            from .zoology.utils import _MODULE_ALIASES
+            real = _MODULE_ALIASES.get(real, real)
+        return real
+
+    def _has_aliased_children(self, name: str) -> bool:
+        """``name`` is one module here but a package with sub-modules in the reference (``feature_maps``, ``h3``, ...)."""
+        if name.split(".", 1)[0] != "zoology":
+            return False
+        from .zoology.utils import _MODULE_ALIASES
+        prefix = self.names["zoology"] + name[len("zoology"):] + "."
+        return any(k.startswith(prefix) for k in _MODULE_ALIASES)
 
     def find_spec(self, name, path=None, target=None):
         real = self._real(name)
@@ -39,13 +53,29 @@ class _AliasFinder(importlib.abc.MetaPathFinder, importlib.abc.Loader):
         try:
             spec = importlib.util.find_spec(real)
         except (ImportError, ValueError):
+            spec = None
+        children = self._has_aliased_children(name)
+        if spec is None and not children:
             return None
-        if spec is None:
-            return None
-        return importlib.util.spec_from_loader(name, self, is_package=spec.submodule_search_locations is not None)
+        is_pkg = children or spec.submodule_search_locations is not None
+        return importlib.util.spec_from_loader(name, self, is_package=is_pkg)
 
     def create_module(self, spec):
-        return importlib.import_module(self._real(spec.name))
+        import types
+        try:
+            real = importlib.import_module(self._real(spec.name))
+        except ImportError:           # a package of the reference with no counterpart of its own here: only its sub-modules map
+            empty = types.ModuleType(spec.name)
+            empty.__path__ = []
+            return empty
+        if hasattr(real, "__path__") or not self._has_aliased_children(spec.name):
+            return real
+        # a single module standing in for a package of the reference: a stand-in with the same contents and an (empty)
+        # search path, so that ``import pkg.sub`` reaches this finder for ``sub``
+        proxy = types.ModuleType(spec.name, real.__doc__)
+        proxy.__dict__.update({k: v for k, v in vars(real).items() if k not in ("__name__", "__spec__", "__loader__", "__path__")})
+        proxy.__path__ = []
+        return proxy
 
     def exec_module(self, module):          # the real module is already executed
         return None

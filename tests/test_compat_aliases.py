@@ -23,6 +23,13 @@ import ml_experiments_b200.heuristic_secrets.models as real
 from ml_experiments_b200.heuristic_secrets.spanfinder.model import SpanFinderModel as RealSpanFinder
 assert hm.Model is real.Model and SpanFinderModel is RealSpanFinder and heuristic_secrets.Detector is not None
 assert GitleaksCollector().name == "gitleaks" and callable(selective_scan_fn)
+# sub-packages of the reference that are one module (or none) here
+from zoology.mixers.feature_maps.taylor import TaylorExp
+from zoology.mixers.h3.h3 import H3
+from zoology.mixers.nystromformer.nystromformer import NystromAttention
+from zoology.mixers.scatterbrain.attn import SBLocalAttention
+import ml_experiments_b200.zoology.mixers.feature_maps as fm
+assert TaylorExp is fm.TaylorExp and H3.__module__.endswith("mixers.h3") and NystromAttention.__module__.endswith("mixers.nystrom")
 compat.uninstall()
 assert "heuristic_secrets" not in sys.modules
 print("ok")
