@@ -25,6 +25,10 @@ _MODULE_ALIASES = {
     "ml_experiments_b200.zoology.mixers.mra.mra": "ml_experiments_b200.zoology.mixers.mra",
     "ml_experiments_b200.zoology.mixers.h3.h3": "ml_experiments_b200.zoology.mixers.h3",
     "ml_experiments_b200.zoology.mixers.rwkv5": "ml_experiments_b200.zoology.mixers.rwkv",
+    **{f"ml_experiments_b200.zoology.mixers.h3.{m}": "ml_experiments_b200.zoology.mixers.h3" for m in ("ss_kernel", "ss_kernel_diag", "ss_kernel_shift", "ssm_utils")},
+    "ml_experiments_b200.zoology.mixers.scatterbrain.feature_maps_sb": "ml_experiments_b200.zoology.mixers.scatterbrain",
+    "ml_experiments_b200.zoology.mixers.scatterbrain.projection_utils": "ml_experiments_b200.zoology.mixers.scatterbrain",
+    "ml_experiments_b200.zoology.analysis.utils": "ml_experiments_b200.zoology.utils",
     # the reference's feature-map package is one module here
     **{f"ml_experiments_b200.zoology.mixers.feature_maps.{m}": "ml_experiments_b200.zoology.mixers.feature_maps"
        for m in ("base", "taylor", "performer", "cosformer", "all_poly", "exp_dim")},
