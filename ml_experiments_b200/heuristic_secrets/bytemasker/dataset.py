@@ -135,6 +135,47 @@ def windows_from_document(s: SpanFinderSample, max_len: int = 512, rng: random.R
     return out
 
 
+# -- the reference's names for the three window kinds and its constants (src/heuristic_secrets/bytemasker/dataset.py:16-270) --
+CACHE_DIR = Path(".cache/bytemasker")
+DEFAULT_MAX_LEN, DEFAULT_PREFIX_LEN, DEFAULT_SUFFIX_LEN, DEFAULT_MIDDLE_LEN = 512, 64, 64, 384
+DEFAULT_MULTILINE_MAX_LINES, DEFAULT_MULTILINE_OVERLAP, DEFAULT_MULTILINE_MIN_LINES, DEFAULT_MULTILINE_MAX_BYTES = 9, 2, 4, 512
+
+
+def _windows_of_kind(sample: SpanFinderSample, kind: str, max_len: int) -> list[MaskWindow]:
+    big = 1 << 30 if kind == "line" else max_len          # whole lines come back unsplit; ``window_line`` splits them
+    out = [w for w in windows_from_document(sample, big, random.Random(0)) if w.kind == kind]
+    for w in out:
+        w.source = sample.source
+    return out
+
+
+def extract_lines_with_masks(sample: SpanFinderSample) -> list[MaskWindow]:
+    """One window per non-blank line of the document with its per-byte secret mask."""
+    return _windows_of_kind(sample, "line", DEFAULT_MAX_LEN)
+
+
+def window_line(line: MaskWindow, max_len: int = DEFAULT_MAX_LEN, prefix_len: int = DEFAULT_PREFIX_LEN, suffix_len: int = DEFAULT_SUFFIX_LEN,
+                middle_len: int = DEFAULT_MIDDLE_LEN) -> list[MaskWindow]:
+    return window_long_line(line, max_len, prefix_len, suffix_len, middle_len)
+
+
+def extract_multiline_windows(sample: SpanFinderSample, max_lines: int = DEFAULT_MULTILINE_MAX_LINES, overlap: int = DEFAULT_MULTILINE_OVERLAP,
+                              min_lines: int = DEFAULT_MULTILINE_MIN_LINES, max_bytes: int = DEFAULT_MULTILINE_MAX_BYTES) -> list[MaskWindow]:
+    """Windows of several consecutive lines (2 to 9, drawn per window) no longer than ``max_bytes``."""
+    return _windows_of_kind(sample, "multi", max_bytes)
+
+
+def extract_secret_only_samples(sample: SpanFinderSample, max_bytes: int = DEFAULT_MAX_LEN) -> list[MaskWindow]:
+    """The bare secret of every true span as a window of its own (mask all ones)."""
+    return _windows_of_kind(sample, "secret", max_bytes)
+
+
+def stratified_split_samples(samples: list[MaskWindow], train_ratio: float = 0.88, val_ratio: float = 0.12, seed: int | None = None):
+    """``(train, val)`` with every group of windows that share a secret on one side."""
+    train, val, _ = stratified_component_split(samples, (train_ratio, val_ratio, 0.0), seed or 0)
+    return train, val
+
+
 def stratified_component_split(windows: list[MaskWindow], fractions=(0.8, 0.1, 0.1), seed: int = 0):
     """Connected components over shared secret ids, assigned greedily to the split furthest below its quota."""
     parent = list(range(len(windows)))

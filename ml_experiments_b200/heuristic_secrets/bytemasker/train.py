@@ -11,6 +11,17 @@ from ..training import BinaryTaskTrainer, TrainMetrics, get_device  # noqa: F401
 from .model import ByteMaskerConfig, ByteMaskerModel
 
 
+def compute_metrics(preds: torch.Tensor, targets: torch.Tensor, lengths: torch.Tensor, threshold: float = 0.5):
+    """``(precision, recall, f1, fp_rate, fn_rate)`` over the valid bytes of a padded batch of logits
+    (src/heuristic_secrets/bytemasker/train.py:33-72)."""
+    from ..training import prf, rates
+    valid = torch.arange(preds.shape[1], device=preds.device)[None, :] < lengths[:, None]
+    pred, truth = (torch.sigmoid(preds) >= threshold)[valid], targets[valid] >= 0.5
+    p, r, f1 = prf(pred, truth)
+    extra = rates(pred, truth)
+    return p, r, f1, extra["fp_rate"], extra["fn_rate"]
+
+
 class ByteMaskerTrainer(BinaryTaskTrainer):
     def __init__(self, model, train_data=None, val_data=None, clean_data=None, *, train_dataset=None, val_dataset=None, batch_size: int = 64,
                  train_on_secret_lines_only: bool = True, val_clean_ratio: float = 1.0, **kw):

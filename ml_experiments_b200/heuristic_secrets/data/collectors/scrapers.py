@@ -118,6 +118,9 @@ _CREDDATA_LABELS = (("password", SecretCategory.PASSWORD), ("auth", SecretCatego
                     ("generic", SecretCategory.GENERIC_SECRET), ("seed", SecretCategory.GENERIC_SECRET), ("salt", SecretCategory.GENERIC_SECRET))
 
 
+CREDDATA_CATEGORY_MAP = dict(_CREDDATA_LABELS)
+
+
 def map_creddata_category(category_str: str) -> SecretCategory:
     """Category of a CredData row from its label column (src/heuristic_secrets/data/collectors/creddata.py:20-51)."""
     label = (category_str or "").lower()

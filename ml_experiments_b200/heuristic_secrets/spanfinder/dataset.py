@@ -14,6 +14,21 @@ from ..data.types import SpanFinderSample
 from ..pipeline.chunker import Chunker
 
 
+@dataclass
+class ChunkedSample:
+    """One chunk of a document with its span labels (the record type of the reference's dataset; this dataset keeps
+    ``(byte_ids, targets)`` pairs and builds the record on request: :meth:`SpanFinderDataset.chunk`)."""
+    byte_ids: torch.Tensor
+    targets: torch.Tensor
+    length: int
+    is_first: bool = False
+    is_last: bool = False
+
+
+def load_jsonl(path) -> list[SpanFinderSample]:
+    return [SpanFinderSample.from_dict(json.loads(line)) for line in open(path) if line.strip()]
+
+
 class SpanFinderDataset(Dataset):
     def __init__(self, samples: list[SpanFinderSample], chunk_size: int = 512, chunk_overlap: int = 64):
         self.chunker = Chunker(chunk_size, chunk_overlap)
@@ -32,6 +47,10 @@ class SpanFinderDataset(Dataset):
 
     def __len__(self):
         return len(self.items)
+
+    def chunk(self, i: int) -> ChunkedSample:
+        ids, tgt = self.items[i]
+        return ChunkedSample(ids, tgt, len(ids))
 
     def __getitem__(self, i):
         return self.items[i]

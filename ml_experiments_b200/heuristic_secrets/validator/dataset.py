@@ -15,6 +15,9 @@ from ..data.types import ValidatorSample
 from .features import FrequencyTable, extract_features
 
 BUCKETS = (64, 128, 256, 512, 1024, 2048, 4096)
+CACHE_DIR = Path(".cache/validator")
+VALIDATOR_MAX_BYTE_LEN = 4096
+LENGTH_BINS = list(BUCKETS)      # the name the reference uses for the same edges
 
 
 @dataclass
