@@ -130,6 +130,70 @@ class CosFormerFeatureMap(FeatureMap):
         return 2 * self.input_dim
 
 
+class FullSpaceMap(nn.Module):
+    """``[x, -x]`` along the feature dimension, clamped positive: lets a positive map see both signs of its input."""
+
+    def __init__(self, head_dim_idx: int = -1, eps: float = 1e-12, **kwargs):
+        super().__init__()
+        self.head_dim_idx, self.eps = head_dim_idx, eps
+
+    def forward(self, x, fmap=None):
+        return torch.cat([x, -x], dim=self.head_dim_idx).clamp(min=self.eps)
+
+
+class ExpDim(FeatureMap):
+    """The "spiky" maps of the feature-map ablations (zoology/mixers/feature_maps/exp_dim.py): an exponential of the
+    (temperature-scaled) input per element or normalised over the feature dimension. ``fullspace`` doubles the
+    features with the negated input. Sub-classes choose the normalisation."""
+    normalise = "none"          # none | max | softmax | abs-softmax
+    halfspace = False           # only the positive half (no doubling)
+
+    def __init__(self, fullspace: bool = True, **kwargs):
+        super().__init__(**kwargs)
+        self.fs_map = FullSpaceMap(head_dim_idx=self.head_dim_idx, eps=self.eps) if fullspace else nn.Identity()
+
+    def forward(self, x):
+        d = self.head_dim_idx
+        if self.normalise == "abs-softmax":            # softmax of |x|, routed to the half of its sign
+            w = x.abs().softmax(dim=d) if self.halfspace else (x * self.temp).abs().softmax(dim=d)
+            if self.halfspace:
+                return ((x >= 0) * w).clamp(min=self.eps)
+            xs = x * self.temp
+            return torch.stack([(xs >= 0) * w, (xs < 0) * w], dim=-1).flatten(-2).clamp(min=self.eps)
+        x = x * self.temp
+        if self.normalise == "softmax":
+            pos = torch.softmax(x, dim=d)
+            return (pos if self.halfspace else torch.cat([pos, torch.softmax(-x, dim=d)], dim=d)).clamp(min=self.eps)
+        if self.normalise == "max":
+            x = x - x.amax(d, keepdim=True)
+        return torch.exp(self.fs_map(x))
+
+    def expanded_size(self) -> int:
+        doubled = (self.normalise in ("softmax", "abs-softmax") and not self.halfspace) or \
+                  (self.normalise in ("none", "max") and isinstance(self.fs_map, FullSpaceMap))
+        return self.input_dim * (2 if doubled else 1)
+
+
+class ExpMaxNorm(ExpDim):
+    normalise = "max"
+
+
+class SoftmaxDim(ExpDim):
+    normalise = "softmax"
+
+
+class SoftmaxDimHalfspace(ExpDim):
+    normalise, halfspace = "softmax", True
+
+
+class ExpSumNorm(ExpDim):
+    normalise = "abs-softmax"
+
+
+class ExpSumNormHalfspace(ExpDim):
+    normalise, halfspace = "abs-softmax", True
+
+
 _MAPS = {None: FeatureMap, "none": FeatureMap, "identity": FeatureMap, "taylor_exp": TaylorExp, "performer": PerformerFeatureMap,
          "cosformer": CosFormerFeatureMap, "pos_elu": PosELU, "relu": ReLU, "square": Square, "all_poly": AllPolyMap}
 

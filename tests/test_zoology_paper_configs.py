@@ -78,3 +78,21 @@ def test_continuous_input_sweep_shapes():
     cs = continuous_sweep(scale=1e-4)
     assert cs and all(c.input_type == "continuous" and c.model.n_layers == 1 and not c.model.learnable_word_embeddings for c in cs)
     assert {c.model.name for c in cs} == {"attention", "sliding-window-attention", "gated_delta_net", "ttt_linear", "ttt_mlp"}
+
+
+def test_spiky_feature_maps():
+    """Shapes, positivity and normalisation of the exponential feature maps; they resolve under the reference's path."""
+    from ml_experiments_b200.zoology.mixers import feature_maps as F
+    from ml_experiments_b200.zoology.utils import import_from_str
+
+    torch.manual_seed(0)
+    x = torch.randn(2, 3, 5, 8)
+    assert import_from_str("zoology.mixers.feature_maps.exp_dim.SoftmaxDim") is F.SoftmaxDim
+    for name, width in (("ExpDim", 16), ("ExpMaxNorm", 16), ("SoftmaxDim", 16), ("SoftmaxDimHalfspace", 8), ("ExpSumNorm", 16), ("ExpSumNormHalfspace", 8)):
+        m = getattr(F, name)(input_dim=8, temp=0.7)
+        y = m(x)
+        assert y.shape == (2, 3, 5, width) == (2, 3, 5, m.expanded_size()) and (y > 0).all()
+    assert torch.allclose(F.ExpDim(input_dim=8)(x), torch.cat([x, -x], -1).exp())
+    assert torch.allclose(F.ExpMaxNorm(input_dim=8, fullspace=False)(x).amax(-1), torch.ones(2, 3, 5))
+    assert torch.allclose(F.SoftmaxDim(input_dim=8)(x).sum(-1), torch.full((2, 3, 5), 2.0), atol=1e-5)
+    assert torch.allclose(F.ExpSumNorm(input_dim=8)(x).sum(-1), torch.ones(2, 3, 5), atol=1e-5)      # each |x| weight lands in one half
