@@ -92,7 +92,7 @@ def test_spiky_feature_maps():
         m = getattr(F, name)(input_dim=8, temp=0.7)
         y = m(x)
         assert y.shape == (2, 3, 5, width) == (2, 3, 5, m.expanded_size()) and (y > 0).all()
-    assert torch.allclose(F.ExpDim(input_dim=8)(x), torch.cat([x, -x], -1).exp())
+    assert torch.allclose(F.ExpDim(input_dim=8)(x), torch.cat([x, -x], -1).clamp(min=1e-12).exp())      # the doubling clamps first
     assert torch.allclose(F.ExpMaxNorm(input_dim=8, fullspace=False)(x).amax(-1), torch.ones(2, 3, 5))
     assert torch.allclose(F.SoftmaxDim(input_dim=8)(x).sum(-1), torch.full((2, 3, 5), 2.0), atol=1e-5)
     assert torch.allclose(F.ExpSumNorm(input_dim=8)(x).sum(-1), torch.ones(2, 3, 5), atol=1e-5)      # each |x| weight lands in one half
