@@ -64,3 +64,13 @@ def mamba_inner_ref(xz, conv1d_weight, conv1d_bias, x_proj_weight, delta_proj_we
 
 def mamba_inner_fn(*args, **kwargs):
     return mamba_inner_ref(*args, _scan=_scan_cl, **kwargs)
+
+
+class SelectiveScanFn:
+    """The reference exposes ``autograd.Function`` classes; here differentiation goes through the operators, so ``apply``
+    is the function."""
+    apply = staticmethod(selective_scan_fn)
+
+
+class MambaInnerFn:
+    apply = staticmethod(mamba_inner_fn)

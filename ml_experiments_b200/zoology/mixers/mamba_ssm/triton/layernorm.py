@@ -1,2 +1,2 @@
 # ruff: noqa: F401
-from ...norms import RMSNorm, layer_norm_fn, rms_norm_fn
+from ...norms import RMSNorm, layer_norm_fn, layer_norm_ref, rms_norm_fn, rms_norm_ref

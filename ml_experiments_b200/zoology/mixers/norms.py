@@ -43,6 +43,16 @@ def layer_norm_fn(x, weight, bias=None, residual=None, eps: float = 1e-6, prenor
     return (y, res) if prenorm else y
 
 
+def rms_norm_ref(x, weight, bias=None, residual=None, eps: float = 1e-6, prenorm: bool = False, upcast: bool = False):
+    """Plain-PyTorch statement of :func:`rms_norm_fn` (the two are the same code here; the reference keeps a Triton kernel
+    and this oracle)."""
+    return rms_norm_fn(x, weight, bias, residual=residual, eps=eps, prenorm=prenorm, residual_in_fp32=upcast)
+
+
+def layer_norm_ref(x, weight, bias=None, residual=None, eps: float = 1e-6, prenorm: bool = False, upcast: bool = False):
+    return layer_norm_fn(x, weight, bias, residual=residual, eps=eps, prenorm=prenorm, residual_in_fp32=upcast)
+
+
 class RMSNormGated(nn.Module):
     def __init__(self, hidden_size: int, eps: float = 1e-5, group_size: int | None = None, norm_before_gate: bool = True,
                  device=None, dtype=None):

@@ -95,3 +95,18 @@ def unflatten(d: dict, sep: str = ".") -> dict:
         return node
 
     return listify(root)
+
+
+def fetch_wandb_runs(project_name: str | None = None, filters: dict | None = None, csv_path: str | None = None, log_dir: str | None = None, **kwargs):
+    """Runs of a sweep as a ``pandas.DataFrame``, one row per run. The reference downloads them from a wandb project
+    (zoology/analysis/utils.py); training boxes here have no network, so the rows come from what the trainer writes
+    locally (results CSV, JSON-lines logs: :func:`ml_experiments_b200.zoology.analysis.results.load_results`).
+    ``filters``: column -> value (or list of values) to keep, e.g. ``{"sweep_id": "based-figure2-1a2b3c"}``."""
+    import os
+
+    from .analysis.results import load_results
+    df = load_results(csv_path or os.environ.get("ZOOLOGY_CSV", "zoology_results.csv"), log_dir or os.environ.get("ZOOLOGY_LOG_DIR"))
+    for col, want in (filters or {}).items():
+        if col in df.columns:
+            df = df[df[col].isin(want if isinstance(want, (list, tuple, set)) else [want])]
+    return df.reset_index(drop=True)
