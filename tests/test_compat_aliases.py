@@ -142,3 +142,41 @@ def test_reference_scripts_find_everything_they_import_here():
     n_ok = int(next(l for l in lines if l.startswith("RESULT ")).split()[1])
     bad = [l[4:] for l in lines if l.startswith("BAD ") and not l[4:].startswith(_EXPECTED_BAD)]
     assert n_ok >= 23 and not bad, (n_ok, bad)
+
+
+REF_SRC = os.environ.get("ML_EXPERIMENTS_REFERENCE_PACKAGE", "")       # .../src/heuristic_secrets of the reference
+
+_NAMES = """
+import importlib, os, re, sys
+import ml_experiments_b200.compat as compat
+compat.install(override=True)
+root = sys.argv[1]
+total = missing = unimportable = 0
+for r, _, fs in os.walk(root):
+    for f in sorted(fs):
+        if not f.endswith(".py"):
+            continue
+        rel = os.path.relpath(os.path.join(r, f), root)[:-3].replace(os.sep, ".")
+        name = "heuristic_secrets" if rel == "__init__" else "heuristic_secrets." + (rel[:-9] if rel.endswith(".__init__") else rel)
+        src = open(os.path.join(r, f)).read()
+        names = set(n for n in re.findall(r"^(?:class|def) (\\w+)", src, re.M) if not n.startswith("_"))
+        try:
+            mod = importlib.import_module(name)
+        except Exception:
+            unimportable += 1
+            continue
+        total += len(names)
+        missing += sum(not hasattr(mod, n) for n in names)
+print(total, missing, unimportable)
+"""
+
+
+@pytest.mark.skipif(not os.path.isdir(REF_SRC), reason="set ML_EXPERIMENTS_REFERENCE_PACKAGE to src/heuristic_secrets of the reference")
+def test_public_names_of_the_reference_package_exist_under_the_same_module_paths():
+    """Every module of the reference's package imports under its own path, and (nearly) every public class / function
+    defined in it is an attribute of the module served here."""
+    env = dict(os.environ, PYTHONPATH=REPO, PYTHONDONTWRITEBYTECODE="1")
+    r = subprocess.run([sys.executable, "-c", _NAMES, REF_SRC], capture_output=True, text=True, env=env, timeout=900)
+    assert r.returncode == 0, r.stderr[-3000:]
+    total, missing, unimportable = (int(v) for v in r.stdout.strip().splitlines()[-1].split())
+    assert unimportable == 0 and total > 300 and missing <= 0.1 * total, (total, missing, unimportable)
