@@ -101,6 +101,48 @@ def download(creddata_dir: Path, out: Path | None = None, tmp: Path | None = Non
     return report
 
 
+# -- the helper names of the reference's downloader (src/heuristic_secrets/data/collectors/creddata_download.py:26-240) --
+def get_words_in_path(creddata_dir: Path) -> list[str]:
+    return json.loads((Path(creddata_dir) / "word_in_path.json").read_text())
+
+
+get_file_scope = file_scope
+get_new_repo_id = new_repo_id
+
+
+def download_repo(repo_id: str, repo_url: str, tmp_dir: Path) -> bool:
+    """True when the pinned commit could be checked out under ``tmp_dir``."""
+    try:
+        fetch_repo(repo_id, repo_url, Path(tmp_dir))
+        return True
+    except (subprocess.SubprocessError, OSError):
+        return False
+
+
+def read_meta_csv(meta_file: Path) -> list[dict]:
+    import csv
+    if not Path(meta_file).exists():
+        return []
+    with open(meta_file, newline="", errors="ignore") as fh:
+        return list(csv.DictReader(fh))
+
+
+def process_repo(repo_id: str, repo_url: str, tmp_dir: Path, meta_dir: Path, data_dir: Path, words_in_path: list[str]) -> int:
+    """Fetch one repository and copy its files into the corpus layout; returns the number of files written (0 when the
+    fetch failed). ``meta_dir`` is not needed here: the copy keeps every text file, the labels are joined at collection."""
+    if not download_repo(repo_id, repo_url, tmp_dir):
+        return 0
+    return copy_repo_files(Path(tmp_dir) / repo_id, repo_id, Path(data_dir).parent, words_in_path)
+
+
+def run_download(creddata_dir: Path, skip_download: bool = False, jobs: int = 1) -> dict:
+    """The whole download as a dictionary of counts (``jobs`` is accepted; repositories are fetched one after another)."""
+    if skip_download:
+        return {"fetched": 0, "failed": 0, "files": 0, "skipped": True}
+    r = download(Path(creddata_dir))
+    return {"fetched": len(r.fetched), "failed": len(r.failed), "files": r.files, "skipped": False}
+
+
 def main(argv=None) -> int:
     import argparse
 
